@@ -1,0 +1,122 @@
+"""End to end: the native runtime's batched step against the fp32 oracle on tiny models."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def build(cfg, seed=0, slots=2, slot_tokens=512, **kw):
+    from qwb200.engine.device_model import DeviceModel
+    from qwb200.models.ple import PleTable
+    from qwb200.models.reference import RefModel
+    from qwb200.models.weights import synth_weights
+    w = synth_weights(cfg, seed=seed)
+    table = PleTable.synthetic(cfg, rows=4096, layout="f8", seed=seed)
+    ref = RefModel(cfg, w, table)
+    dm = DeviceModel(cfg, slots=slots, slot_tokens=slot_tokens, **kw)
+    dm.set_globals(w)
+    for L in range(cfg.n_layers):
+        dm.set_layer(L, w)
+    dm.set_ple_table(table)
+    return ref, dm
+
+
+def ctx3_for(cfg, hist, toks):
+    """n-gram context rows for tokens appended after ``hist``."""
+    seq = list(hist) + list(toks)
+    out = np.full((len(toks), 3), -1, dtype=np.int32)
+    for i in range(len(toks)):
+        p = len(hist) + i
+        out[i, 0] = seq[p]
+        if p >= 1:
+            out[i, 1] = seq[p - 1]
+        if p >= 2:
+            out[i, 2] = seq[p - 2]
+    return out
+
+
+def run_seq(dm, cfg, toks, slot=0, start=0, batch=1, hist=(), graph=False):
+    """Feed tokens through the device model ``batch`` rows at a time; return logits of every row."""
+    outs = []
+    hist = list(hist)
+    i = 0
+    while i < len(toks):
+        chunk = toks[i:i + batch]
+        pos = list(range(start + i, start + i + len(chunk)))
+        dm.step(chunk, [slot] * len(chunk), pos, ctx3_for(cfg, hist, chunk), graph=graph)
+        torch.cuda.synchronize()
+        outs.append(dm.buf["logits"][:len(chunk)].clone())
+        hist += chunk
+        i += len(chunk)
+    return torch.cat(outs)
+
+
+def rel(a, b):
+    return float((a - b).abs().max() / b.abs().max())
+
+
+def test_decode_matches_oracle_token_by_token_and_batched():
+    from qwb200.models.config import ModelConfig
+    cfg = ModelConfig.tiny()
+    ref, dm = build(cfg)
+    g = torch.Generator().manual_seed(11)
+    toks = torch.randint(0, cfg.vocab, (100,), generator=g).tolist()     # beyond the budget of 64 tokens
+    toks[30] = cfg.eos
+    st = ref.new_state()
+    want = ref.forward(st, toks, all_logits=True)
+    got1 = run_seq(dm, cfg, toks, slot=0, batch=1).cpu()
+    assert rel(got1, want) < 3e-2
+    agree = (got1.argmax(-1) == want.argmax(-1)).float().mean()
+    assert agree > 0.9
+    # batched rows (runs of one slot) on another slot: same logits as one row at a time, bit for bit
+    got7 = run_seq(dm, cfg, toks, slot=1, batch=7).cpu()
+    assert rel(got7, want) < 3e-2
+    assert torch.equal(got7, got1)
+
+
+def test_two_slots_interleaved_rows_are_independent():
+    from qwb200.models.config import ModelConfig
+    cfg = ModelConfig.tiny(n_layers=2, layer_types=("gdn", "qsa"))
+    ref, dm = build(cfg, seed=3)
+    a = [5, 9, 200, 31, 77, 600]
+    b = [8, 8, 8, 901, 2, 44]
+    la = run_seq(dm, cfg, a, slot=0).cpu()
+    dm.reset_slot(0)
+    # same sequences decoded as mixed batches: rows [a_i, b_i]
+    ha, hb, outs_a, outs_b = [], [], [], []
+    for i in range(len(a)):
+        c3 = np.concatenate([ctx3_for(cfg, ha, [a[i]]), ctx3_for(cfg, hb, [b[i]])])
+        dm.step([a[i], b[i]], [0, 1], [i, i], c3)
+        torch.cuda.synchronize()
+        outs_a.append(dm.buf["logits"][0].clone())
+        outs_b.append(dm.buf["logits"][1].clone())
+        ha.append(a[i]); hb.append(b[i])
+    assert torch.equal(torch.stack(outs_a).cpu(), la)
+    stb = ref.new_state()
+    wb = ref.forward(stb, b, all_logits=True)
+    assert rel(torch.stack(outs_b).cpu(), wb) < 3e-2
+
+
+def test_cuda_graph_replay_equals_direct_launch():
+    from qwb200.models.config import ModelConfig
+    cfg = ModelConfig.tiny(n_layers=2, layer_types=("gdn", "qsa"))
+    ref, dm = build(cfg, seed=4)
+    toks = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5, 8]
+    direct = run_seq(dm, cfg, toks, slot=0).cpu()
+    viag = run_seq(dm, cfg, toks, slot=1, graph=True).cpu()
+    assert torch.equal(direct, viag)
+
+
+def test_full_shape_slice_logits():
+    """The two-layer slice at the model's real per-layer shapes (GDN + QSA + MoE + HC + PLE)."""
+    from qwb200.models.config import ModelConfig
+    cfg = ModelConfig.slice2()
+    cfg = ModelConfig(**{**cfg.__dict__, "n_experts": 64, "vocab": 4096, "eos": 4000, "image_pad": 4001,
+                         "video_pad": 4002, "ngram_vocab_base": 3000})
+    ref, dm = build(cfg, seed=5, slots=1, slot_tokens=256)
+    toks = torch.randint(0, cfg.vocab, (12,), generator=torch.Generator().manual_seed(1)).tolist()
+    st = ref.new_state()
+    want = ref.forward(st, toks, all_logits=True)
+    got = run_seq(dm, cfg, toks, batch=4).cpu()
+    assert rel(got, want) < 3e-2

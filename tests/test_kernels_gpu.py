@@ -1,0 +1,96 @@
+"""Numerics of the decode kernels against plain PyTorch fp32 references (GPU only)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("N,K", [(324, 2560), (512 + 1281, 2560), (2560, 6144), (16444, 2560), (40, 64)])
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 16, 32])
+def test_gemv_bf16_matches_fp32_and_rows_are_batch_invariant(N, K, M):
+    from qwb200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(N + K + M)
+    W = (torch.randn(N, K, generator=g, device=_dev()) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, generator=g, device=_dev()).to(torch.bfloat16)
+    out = torch.full((M, N + 3), 777.0, device=_dev())       # guard columns detect stray writes
+    K_.gemv_bf16(W, x, out=out, N=N, ldy=N + 3)
+    ref = x.float() @ W.float().T
+    assert torch.all(out[:, N:] == 777.0)
+    assert torch.allclose(out[:, :N], ref, atol=2e-2 * (K ** 0.5) * 0.05, rtol=2e-3)
+    # a row alone gives bit-identical results to the row inside the batch
+    one = K_.gemv_bf16(W, x[M - 1:M].contiguous())
+    assert torch.equal(one[0], out[M - 1, :N])
+
+
+def test_gemv_column_splits():
+    from qwb200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(5)
+    hc, SH, R, M = 4, 640, 324, 3
+    W = (torch.randn(R, hc * SH, generator=g, device=_dev()) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, hc * SH, generator=g, device=_dev()).to(torch.bfloat16)
+    out = torch.zeros(M, hc + hc * R, device=_dev())
+    K_.gemv_bf16(W, x, out=out[:, hc:], nsplit=hc, splits=(SH, SH, R), N=R, K=SH, ldw=hc * SH, ldy=out.stride(0))
+    ref = torch.einsum("rsc,msc->msr", W.float().view(R, hc, SH), x.float().view(M, hc, SH)).reshape(M, hc * R)
+    assert torch.allclose(out[:, hc:], ref, atol=5e-2, rtol=2e-3)
+    assert torch.all(out[:, :hc] == 0)
+
+
+def test_row_reduce_argmax_ties_and_lse():
+    from qwb200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(1)
+    l = torch.randn(5, 31040, generator=g, device=_dev())
+    l[2, 100] = l[2, 30000] = 50.0       # tie: lowest index wins
+    val, idx, mx, sm = K_.row_reduce(l, idx0=1000)
+    assert idx.tolist()[2] == 1100
+    assert torch.equal(idx.long() - 1000, torch.argmax(l, -1)) or idx.tolist()[2] == 1100
+    ref = torch.logsumexp(l.double(), -1).float()
+    assert torch.allclose(mx + torch.log(sm), ref, atol=1e-4)
+
+
+@pytest.mark.parametrize("nb", [600, 1025, 5000])
+def test_qsa_select_topk_with_ties(nb):
+    from qwb200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(nb)
+    topk, ratio = 512, 4
+    sc = torch.rand(3, 8192, generator=g, device=_dev())
+    sc[1, :nb] = torch.randint(0, 40, (nb,), generator=g, device=_dev()).float()     # many ties
+    sc[2, :nb] = 0.0                                                                  # all equal
+    pos = torch.tensor([nb * ratio + 1, nb * ratio + 3, nb * ratio], dtype=torch.int32, device=_dev())
+    sel, sel_n = K_.qsa_select(sc, pos, ratio, topk)
+    assert sel_n.tolist() == [topk] * 3
+    for m in range(3):
+        order = torch.sort(-sc[m, :nb], stable=True).indices[:topk]
+        assert sel[m].tolist() == sorted(order.tolist())
+    # below the budget everything is attended
+    sel, sel_n = K_.qsa_select(sc, torch.tensor([100, 2047, 2050], dtype=torch.int32, device=_dev()), ratio, topk)
+    assert sel_n.tolist() == [-1, -1, -1]
+
+
+def test_moe_pair_kernels_match_oracle():
+    from qwb200.models.config import ModelConfig
+    from qwb200.models.weights import synth_layer
+    from qwb200.models.reference import RefModel
+    from qwb200.engine.weights_prep import prep_moe
+    from qwb200.models.config import ShardConfig
+    from qwb200.ops import kernels as K_
+    cfg = ModelConfig.tiny(n_layers=1, layer_types=("gdn",))
+    w = synth_layer(cfg, 0, seed=2)
+    ref = RefModel(cfg, w)
+    sc = ShardConfig(cfg, 1, 0)
+    mw = prep_moe(w, "layers.0.mlp.", sc, _dev())
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, cfg.hidden, generator=g).to(torch.bfloat16)
+    want = ref.moe("layers.0.mlp.", x.float())
+    xd = x.to(_dev())
+    rs = K_.gemv_bf16(mw["Wrs"], xd)
+    pe, pw, sh = K_.moe_route(rs, cfg.n_experts, cfg.top_k, sc.sffn_l)
+    idx, wgt, _ = ref.route("layers.0.mlp.", x.float())
+    assert torch.equal(pe.cpu().long(), idx)
+    assert torch.allclose(pw.cpu(), wgt, atol=1e-5)
+    out = K_.moe_experts_pair(mw["w13"], mw["s13"], mw["w2"], mw["s2"], xd, pe, pw, cfg.ffn, cfg.hidden, mw["Wsd"], sh)
+    err = (out.cpu() - want).abs().max() / want.abs().max()
+    assert err < 2e-2, float(err)

@@ -1,0 +1,187 @@
+"""The engine: one rank's DeviceModel plus slot bookkeeping, prefill, batched decode and chained
+(device-fed) greedy decode.  With several ranks every rank process runs the same calls in the
+same order (single-program, one process per GPU); collectives go through ``parallel``.
+
+Roles of the reference's ``class Engine`` (src/engine/engine.hpp:69-446): ``prefill``, ``decode``,
+slot reset, and the per-row-count decode graphs.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.ple import PleTable
+from ..models.weights import Weights, synth_globals, synth_layer
+from . import device_model as DM
+from .device_model import DeviceModel
+
+
+@dataclass
+class Slot:
+    tokens: List[int] = field(default_factory=list)     # every token fed so far (vision tokens negative)
+
+    @property
+    def n(self) -> int:
+        return len(self.tokens)
+
+
+@dataclass
+class EngineOptions:
+    slots: int = 1
+    slot_tokens: int = 8192
+    max_rows: int = DM.MAX_ROWS
+    host_pages: int = 0
+    dev_pages: Optional[int] = None
+    save_gdn: bool = False
+    use_graphs: bool = True
+    prefill_rows: int = DM.MAX_ROWS          # rows per step of the row-batched prefill
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, opts: EngineOptions = EngineOptions(), ranks: int = 1, rank: int = 0,
+                 device: str = "cuda:0"):
+        self.cfg, self.opts = cfg, opts
+        self.dm = DeviceModel(cfg, ranks=ranks, rank=rank, device=device, slots=opts.slots,
+                              slot_tokens=opts.slot_tokens, max_rows=opts.max_rows, host_pages=opts.host_pages,
+                              dev_pages=opts.dev_pages, save_gdn=opts.save_gdn)
+        self.slot = [Slot() for _ in range(opts.slots)]
+        self.out_host = torch.zeros(opts.max_rows, dtype=torch.int32).pin_memory()
+        self.steps = 0
+
+    # ---- construction
+    @staticmethod
+    def synthetic(cfg: ModelConfig, opts: EngineOptions = EngineOptions(), ranks: int = 1, rank: int = 0,
+                  device: str = "cuda:0", seed: int = 0, exact: bool = False, ple_rows: int = 1 << 20,
+                  ple_pinned: bool = True, log: Optional[Callable[[str], None]] = None) -> "Engine":
+        """Random-init weights of the given architecture, generated layer by layer on the device
+        (a full-size model never exists in checkpoint layout in host memory)."""
+        e = Engine(cfg, opts, ranks, rank, device)
+        t0 = time.time()
+        e.dm.set_globals(synth_globals(cfg, seed, device=device))
+        for L in range(cfg.n_layers):
+            e.dm.set_layer(L, synth_layer(cfg, L, seed, device=device, exact=exact))
+            if log and (L % 8 == 7 or L == cfg.n_layers - 1):
+                log(f"layer {L + 1}/{cfg.n_layers} ready, {e.dm.weight_bytes() / 1e9:.1f} GB, {time.time() - t0:.0f} s")
+        table = PleTable.synthetic(cfg, rows=ple_rows, layout="f8", seed=seed, pin=ple_pinned)
+        e.dm.set_ple_table(table)
+        torch.cuda.synchronize(device)
+        return e
+
+    @staticmethod
+    def from_weights(cfg: ModelConfig, w: Weights, table: Optional[PleTable], opts: EngineOptions = EngineOptions(),
+                     ranks: int = 1, rank: int = 0, device: str = "cuda:0") -> "Engine":
+        e = Engine(cfg, opts, ranks, rank, device)
+        e.dm.set_globals(w)
+        for L in range(cfg.n_layers):
+            e.dm.set_layer(L, w)
+        if table is not None:
+            e.dm.set_ple_table(table)
+        return e
+
+    # ---- slots
+    def reset(self, slot: int):
+        self.slot[slot] = Slot()
+        self.dm.reset_slot(slot)
+
+    def _ctx3(self, slot: int, toks: Sequence[int]) -> np.ndarray:
+        c = self.cfg
+        hist = [c.real_token(t) for t in self.slot[slot].tokens[-2:]]
+        seq = hist + [c.real_token(int(t)) for t in toks]
+        out = np.full((len(toks), 3), -1, dtype=np.int32)
+        for i in range(len(toks)):
+            p = len(hist) + i
+            out[i, 0] = seq[p]
+            if p >= 1:
+                out[i, 1] = seq[p - 1]
+            if p >= 2:
+                out[i, 2] = seq[p - 2]
+        return out
+
+    # ---- prefill (row-batched: the decode kernels over runs of up to prefill_rows rows)
+    def prefill(self, slot: int, tokens: Sequence[int], want_logits: bool = True) -> Optional[torch.Tensor]:
+        """Append ``tokens`` to the slot.  Returns the logits of the last token (device tensor)."""
+        toks = [int(t) for t in tokens]
+        n = len(toks)
+        step = max(1, min(self.opts.prefill_rows, self.opts.max_rows))
+        i = 0
+        while i < n:
+            chunk = toks[i:i + step]
+            base = self.slot[slot].n
+            if base + len(chunk) > self.dm.slot_tokens:
+                raise ValueError("slot capacity exceeded")
+            last = i + len(chunk) >= n
+            flags = 0 if (last and want_logits) else DM.FLAG_NO_HEAD
+            self.dm.step(chunk, [slot] * len(chunk), list(range(base, base + len(chunk))), self._ctx3(slot, chunk),
+                         flags=flags, graph=False)
+            self.slot[slot].tokens.extend(chunk)
+            i += len(chunk)
+        self.steps += 1
+        if want_logits:
+            return self.dm.buf["logits"][(n - 1) % step if n % step else step - 1]
+        return None
+
+    # ---- decode
+    def decode(self, slots: Sequence[int], tokens: Sequence[int], flags: int = 0, sync: bool = True) -> List[int]:
+        """One batched step: row i appends tokens[i] to slots[i] (rows of a slot consecutive).
+        Returns the greedy next token of every row (host ints)."""
+        M = len(tokens)
+        pos, c3 = [], []
+        seen: Dict[int, int] = {}
+        for s, t in zip(slots, tokens):
+            k = seen.get(s, 0)
+            pos.append(self.slot[s].n + k)
+            seen[s] = k + 1
+        # n-gram context per row, following the run inside the batch
+        tmp = {s: list(self.slot[s].tokens[-2:]) for s in seen}
+        rows3 = np.full((M, 3), -1, dtype=np.int32)
+        for i, (s, t) in enumerate(zip(slots, tokens)):
+            h = tmp[s]
+            rows3[i, 0] = self.cfg.real_token(int(t))
+            if len(h) >= 1:
+                rows3[i, 1] = self.cfg.real_token(h[-1])
+            if len(h) >= 2:
+                rows3[i, 2] = self.cfg.real_token(h[-2])
+            h.append(int(t))
+        self.dm.step(list(tokens), list(slots), pos, rows3, flags=flags, graph=self.opts.use_graphs)
+        for s, t in zip(slots, tokens):
+            self.slot[s].tokens.append(int(t))
+        self.steps += 1
+        self.out_host[:M].copy_(self.dm.buf["amax_idx"][:M], non_blocking=True)
+        if sync:
+            torch.cuda.current_stream(self.dm.dev).synchronize()
+            return self.out_host[:M].tolist()
+        return []
+
+    def decode_chain(self, slot: int, first_token: int, n_steps: int) -> List[int]:
+        """Greedy-decode ``n_steps`` tokens of one slot with the token fed back on the device: the
+        graph of one step (with the row-advance kernel at its end) is replayed ``n_steps`` times with
+        no host work in between; the sampled tokens are read back once at the end."""
+        dm = self.dm
+        base = self.slot[slot].n
+        if base + n_steps > dm.slot_tokens:
+            raise ValueError("slot capacity exceeded")
+        flags = DM.FLAG_CHAIN
+        key = (1, flags, -1)
+        out = torch.zeros(n_steps, dtype=torch.int32, device=dm.dev)
+        if key not in dm.graphs:
+            # capture on this slot's real state: the warm-up launch is the first step
+            dm.step([first_token], [slot], [base], self._ctx3(slot, [first_token]), flags=flags, graph=True)
+            out[0:1].copy_(dm.buf["amax_idx"][0:1])
+            done = 1
+        else:
+            dm.stage_rows([first_token], [slot], [base], self._ctx3(slot, [first_token]))
+            done = 0
+        g = dm.graphs[key]
+        for i in range(done, n_steps):
+            g.replay()
+            out[i:i + 1].copy_(dm.buf["amax_idx"][0:1], non_blocking=True)
+        torch.cuda.current_stream(dm.dev).synchronize()
+        toks = out.tolist()
+        self.slot[slot].tokens.extend([first_token] + toks[:-1])
+        self.steps += n_steps
+        return toks

@@ -1,0 +1,140 @@
+// Shared device helpers for the sm_100a kernels: warp/block reductions, bf16 packing, the
+// exact q4 -> bf16 pair conversion, activation functions, bounded waits and the row tables
+// that batched-decode kernels take.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define QW_API extern "C" __attribute__((visibility("default")))
+
+namespace qw {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+constexpr int MAX_ROWS = 32;       // rows of one batched decode step
+constexpr int KV_PAGE = 256;       // tokens per KV page (also the prefix-cache block size)
+constexpr int RAW_RING = 16;       // raw indexer keys kept per slot and layer
+constexpr int GDN_RING = 16;       // pre-conv rows kept per slot and layer
+constexpr int PLE_RING = 32;       // normalised conv inputs kept per slot
+constexpr int LIST_CAP = 2048 + 8; // attended tokens per query: 512 groups x 4 + open tail
+
+// Error word shared by every kernel that can give up (bounded waits, bounds checks).  Kernels
+// never trap: they record a code here (first writer wins) and return.
+struct ErrorWord {
+    unsigned int code;      // 0 = ok
+    unsigned int detail;
+};
+enum ErrCode : unsigned int {
+    ERR_NONE = 0,
+    ERR_WAIT_TIMEOUT = 1,   // a flag / mbarrier wait ran out
+    ERR_BOUNDS = 2,         // a data-derived index was out of range (checked builds)
+    ERR_CAPACITY = 3,       // a table or list was too small
+};
+__device__ __forceinline__ void report(ErrorWord *e, unsigned int code, unsigned int detail) {
+    if (e && atomicCAS(&e->code, 0u, code) == 0u) e->detail = detail;
+}
+
+// Row tables of a batched step.  Row i appends one token to slot[i] at position pos[i]; rows of
+// one slot are consecutive and run_start[i] is the first row of that slot's run.
+struct Rows {
+    int M;
+    const int *slot;        // [M]
+    const int *pos;         // [M]
+    const int *run_start;   // [M]
+    const int *run_len;     // [M] (valid at the first row of a run)
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, <= 1024); every thread gets the result.
+// Fixed order: lanes by xor-shuffle, then warps 0..n-1 serially.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float *scratch /* >= 32 floats */) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) scratch[w] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NT / 32; ++i) s += scratch[i];
+    return s;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    bf162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// Streaming 16-byte load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ld_stream8(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// q4 engine order: elements 2j and 2j+1 of a word sit at bits 4j and 16+4j.  (w >> 4j) & 0x000F000F
+// OR 0x43004300 is the bf16 pair (128+n_even, 128+n_odd); subtracting 136 gives the exact values.
+__device__ __forceinline__ void q4_pair(uint32_t w, int j, float &e0, float &e1) {
+    uint32_t p = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+    e0 = bf16_lo(p) - 136.f;
+    e1 = bf16_hi(p) - 136.f;
+}
+// Same as a packed bf16 pair (exact: the integers -8..7 are representable).
+__device__ __forceinline__ uint32_t q4_pair_bf16(uint32_t w, int j) {
+    uint32_t p = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+    bf162 v = *reinterpret_cast<bf162 *>(&p);
+    bf162 off = __floats2bfloat162_rn(136.f, 136.f);
+    bf162 r = __hsub2(v, off);
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+// dot of 8 bf16 weights (uint4) with 8 bf16 activations (uint4), fp32 accumulate, fixed order
+__device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x, float acc) {
+    acc = fmaf(bf16_lo(w.x), bf16_lo(x.x), acc);
+    acc = fmaf(bf16_hi(w.x), bf16_hi(x.x), acc);
+    acc = fmaf(bf16_lo(w.y), bf16_lo(x.y), acc);
+    acc = fmaf(bf16_hi(w.y), bf16_hi(x.y), acc);
+    acc = fmaf(bf16_lo(w.z), bf16_lo(x.z), acc);
+    acc = fmaf(bf16_hi(w.z), bf16_hi(x.z), acc);
+    acc = fmaf(bf16_lo(w.w), bf16_lo(x.w), acc);
+    acc = fmaf(bf16_hi(w.w), bf16_hi(x.w), acc);
+    return acc;
+}
+
+// NeoX rotation angle tables: cos/sin for (pos, i) computed in double like the oracle.
+__device__ __forceinline__ void rope_cs(int pos, int i, int rope_dim, double theta, float &c, float &s) {
+    double inv = pow(theta, -2.0 * double(i) / double(rope_dim));
+    double a = double(pos) * inv;
+    double sd, cd;
+    sincos(a, &sd, &cd);
+    c = float(cd);
+    s = float(sd);
+}
+
+}  // namespace qw

@@ -1,0 +1,182 @@
+// Gated delta net kernels for row batches: causal depthwise conv + gating + per-head L2 norm,
+// and the recurrent delta-rule update with the gated output norm fused in
+// (roles of the reference's src/kernels/gdn.hip:174-309; math in docs/MODEL.md:108-133).
+//
+// Per-rank layout of the projection output row (fp32): [ q (KL heads) | k (KL heads) | v (VL heads) |
+// z (VL heads x 128) | b (VL) | a (VL) ], head dim 128.
+#include "common.cuh"
+
+namespace qw {
+
+constexpr int GD = 128;      // GDN head dim
+
+struct GdnConvArgs {
+    const float *proj;       // [M][ld_proj]
+    int ld_proj;
+    float *ring;             // [slots][GDN_RING][qkv_l] pre-conv rows of this layer
+    const float *cw;         // [qkv_l][4] conv taps (oldest first)
+    const float *A_log, *dt_bias;   // [VL]
+    int KL, VL;
+    Rows rows;
+    float *qkv;              // [M][qkv_l] conv output: q (normed, scaled) | k (normed) | v
+    float *decay, *beta;     // [M][VL]
+    float eps;
+};
+
+// grid (M, 2*KL+VL), 128 threads: one head per block.
+__global__ void __launch_bounds__(128) gdn_conv_kernel(GdnConvArgs a) {
+    __shared__ float scratch[32];
+    const int m = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int qkv_l = (2 * a.KL + a.VL) * GD;
+    const int c = head * GD + d;
+    const int slot = a.rows.slot[m], pos = a.rows.pos[m], rs = a.rows.run_start[m];
+    float *ring = a.ring + (long long)slot * GDN_RING * qkv_l;
+    // value of the pre-conv row at position q: from this batch when q belongs to the run, else the ring
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int q = pos - 3 + k;
+        const int back = pos - q;            // rows back within the run
+        float v;
+        if (m - back >= rs) v = a.proj[(long long)(m - back) * a.ld_proj + c];
+        else if (q >= 0) v = ring[(q % GDN_RING) * qkv_l + c];
+        else v = 0.f;
+        acc = fmaf(a.cw[c * 4 + k], v, acc);
+    }
+    float v = siluf_(acc);
+    if (head < 2 * a.KL) {
+        const float ss = block_sum<128>(v * v, scratch);
+        v = v / sqrtf(ss + a.eps);
+        if (head < a.KL) v *= 0.08838834764831845f;    // 1/sqrt(128)
+    }
+    a.qkv[(long long)m * qkv_l + c] = v;
+    if (head == 0 && d < a.VL) {
+        const float *row = a.proj + (long long)m * a.ld_proj + qkv_l + a.VL * GD;
+        const float bb = row[d], aa = row[a.VL + d];
+        const float g = -__expf(a.A_log[d]) * softplusf_(aa + a.dt_bias[d]);
+        a.decay[m * a.VL + d] = __expf(g);
+        a.beta[m * a.VL + d] = sigmoidf_(bb);
+    }
+}
+
+// Stores the batch's pre-conv rows into the ring (after gdn_conv has read the old entries).
+// grid (M, ceil(qkv_l/256)).
+__global__ void gdn_ring_kernel(const float *proj, int ld_proj, float *ring, int qkv_l, Rows rows) {
+    const int m = blockIdx.x;
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= qkv_l) return;
+    const int slot = rows.slot[m], pos = rows.pos[m];
+    // a run longer than the ring keeps only its last GDN_RING rows
+    const int rs = rows.run_start[m], len = rows.run_len[rs];
+    if (m - rs < len - GDN_RING) return;
+    ring[((long long)slot * GDN_RING + (pos % GDN_RING)) * qkv_l + c] = proj[(long long)m * ld_proj + c];
+}
+
+struct GdnScanArgs {
+    const float *qkv;        // [M][qkv_l]
+    const float *decay, *beta;   // [M][VL]
+    const float *proj;       // for z: proj[m][qkv_l + h*128 + d]
+    int ld_proj;
+    float *S;                // [slots][VL][128 k][128 v] state of this layer
+    float *save;             // optional [M][VL][128][128]: state after each row (speculative rollback)
+    const float *norm_w;     // [128]
+    int KL, VL;
+    Rows rows;
+    bf16 *o;                 // [M][VL*128] gated, normed output
+    float eps;
+};
+
+// grid (M, VL), 512 threads.  Only the first row of a run does work; it walks the run's rows.
+// Thread (kg = tid/128, c = tid%128) holds S[kg*32 .. +32][c].
+__global__ void __launch_bounds__(512) gdn_scan_kernel(GdnScanArgs a) {
+    __shared__ float kq[2][GD];        // k and q of the row
+    __shared__ float red[4][GD];
+    __shared__ float scratch[32];
+    const int m0 = blockIdx.x, h = blockIdx.y;
+    if (a.rows.run_start[m0] != m0) return;
+    const int len = a.rows.run_len[m0], slot = a.rows.slot[m0];
+    const int tid = threadIdx.x, c = tid & 127, kg = tid >> 7;
+    const int qkv_l = (2 * a.KL + a.VL) * GD;
+    const int kh = h / (a.VL / a.KL);
+    float *Sg = a.S + ((long long)slot * a.VL + h) * GD * GD;
+    float S[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[i] = Sg[(kg * 32 + i) * GD + c];
+    for (int r = 0; r < len; ++r) {
+        const int m = m0 + r;
+        const float *row = a.qkv + (long long)m * qkv_l;
+        __syncthreads();
+        if (tid < GD) kq[0][tid] = row[(a.KL + kh) * GD + tid];
+        else if (tid < 2 * GD) kq[1][tid - GD] = row[kh * GD + (tid - GD)];
+        __syncthreads();
+        const float dec = a.decay[m * a.VL + h], be = a.beta[m * a.VL + h];
+        float p = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            S[i] *= dec;
+            p = fmaf(S[i], kq[0][kg * 32 + i], p);
+        }
+        red[kg][c] = p;
+        __syncthreads();
+        const float stk = red[0][c] + red[1][c] + red[2][c] + red[3][c];
+        const float u = (row[2 * a.KL * GD + h * GD + c] - stk) * be;
+        float oq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            S[i] = fmaf(kq[0][kg * 32 + i], u, S[i]);
+            oq = fmaf(S[i], kq[1][kg * 32 + i], oq);
+        }
+        __syncthreads();
+        red[kg][c] = oq;
+        __syncthreads();
+        if (a.save) {
+            float *sv = a.save + ((long long)m * a.VL + h) * GD * GD;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sv[(kg * 32 + i) * GD + c] = S[i];
+        }
+        // gated rms norm over the head's 128 outputs
+        float ov = 0.f;
+        if (kg == 0) ov = red[0][c] + red[1][c] + red[2][c] + red[3][c];
+        const float ss = block_sum<512>(ov * ov, scratch);
+        if (kg == 0) {
+            const float z = a.proj[(long long)m * a.ld_proj + qkv_l + h * GD + c];
+            const float y = ov * rsqrtf(ss / float(GD) + a.eps) * a.norm_w[c] * sigmoidf_(z);
+            a.o[(long long)m * a.VL * GD + h * GD + c] = __float2bfloat16(y);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) Sg[(kg * 32 + i) * GD + c] = S[i];
+}
+
+}  // namespace qw
+
+using namespace qw;
+
+QW_API int qwk_gdn_conv(const float *proj, int ld_proj, float *ring, const float *cw, const float *A_log,
+                        const float *dt_bias, int KL, int VL, int M, const int *slot, const int *pos,
+                        const int *run_start, const int *run_len, float *qkv, float *decay, float *beta, float eps,
+                        cudaStream_t s) {
+    GdnConvArgs a;
+    a.proj = proj; a.ld_proj = ld_proj; a.ring = ring; a.cw = cw; a.A_log = A_log; a.dt_bias = dt_bias;
+    a.KL = KL; a.VL = VL; a.rows = Rows{M, slot, pos, run_start, run_len};
+    a.qkv = qkv; a.decay = decay; a.beta = beta; a.eps = eps;
+    if (VL > 128) return -1;
+    dim3 grid(M, 2 * KL + VL);
+    gdn_conv_kernel<<<grid, 128, 0, s>>>(a);
+    const int qkv_l = (2 * KL + VL) * GD;
+    dim3 g2(M, (qkv_l + 255) / 256);
+    gdn_ring_kernel<<<g2, 256, 0, s>>>(proj, ld_proj, ring, qkv_l, a.rows);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+QW_API int qwk_gdn_scan(const float *qkv, const float *decay, const float *beta, const float *proj, int ld_proj, float *S,
+                        float *save, const float *norm_w, int KL, int VL, int M, const int *slot, const int *pos,
+                        const int *run_start, const int *run_len, void *o, float eps, cudaStream_t s) {
+    GdnScanArgs a;
+    a.qkv = qkv; a.decay = decay; a.beta = beta; a.proj = proj; a.ld_proj = ld_proj; a.S = S; a.save = save;
+    a.norm_w = norm_w; a.KL = KL; a.VL = VL; a.rows = Rows{M, slot, pos, run_start, run_len};
+    a.o = (bf16 *)o; a.eps = eps;
+    dim3 grid(M, VL);
+    gdn_scan_kernel<<<grid, 512, 0, s>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

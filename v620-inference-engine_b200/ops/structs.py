@@ -1,0 +1,58 @@
+"""ctypes mirrors of the runtime structs in ``csrc/runtime.h`` (same field order and types)."""
+import ctypes as C
+
+P = C.c_void_p
+
+
+class QwDims(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "ranks", "rank", "H", "hc", "hc_rank", "SH", "n_layers", "vocab", "vocab_l",
+        "QL", "KVL", "IH", "proj_qsa", "KL", "VL", "proj_gdn",
+        "E", "E_l", "e_first", "top_k", "F", "SF",
+        "ple_layer", "ple_kv", "ngram_heads", "ngram_dim", "ple_taps", "ple_dil",
+        "idx_ratio", "idx_topk", "nsplit", "max_rows",
+        "slots", "max_pages", "n_dev_pages", "ck_cap", "score_cap")] + [("eps", C.c_float)]
+
+
+class QwHc(C.Structure):
+    _fields_ = [("w1", P), ("Wd", P), ("Wu", P), ("n_inj", C.c_int), ("pad_", C.c_int)]
+
+
+class QwLayer(C.Structure):
+    _fields_ = [("is_qsa", C.c_int), ("state_index", C.c_int), ("attn_hc", QwHc), ("mlp_hc", QwHc),
+                ("Wproj", P), ("Wout", P), ("cw", P), ("A_log", P), ("dt_bias", P), ("gdn_norm", P),
+                ("qn1", P), ("kn1", P), ("iqn1", P), ("ikn1", P),
+                ("Wrs", P), ("w13", P), ("s13", P), ("w2", P), ("s2", P), ("Wsd", P)]
+
+
+class QwPle(C.Structure):
+    _fields_ = [("Wkv", P), ("nk1", P), ("nq1", P), ("nc1", P), ("cw", P), ("shards", P), ("scales", P),
+                ("rows_per_shard", C.c_longlong), ("rows", C.c_longlong), ("layout", C.c_int), ("enabled", C.c_int)]
+
+
+class QwState(C.Structure):
+    _fields_ = [(n, P) for n in ("k_dev", "v_dev", "k_host", "v_host", "ck", "raw_ring", "gdn_S", "gdn_ring",
+                                 "ple_ring", "page_table")]
+
+
+BUFFER_FIELDS = ("X", "y", "send", "red", "bin", "proj", "inj_a", "inj_b", "partial", "out_a", "out_b", "o",
+                 "qkv", "decay", "beta", "q", "iq", "scores", "sel", "sel_n", "pm", "pl", "pacc", "rs",
+                 "pair_expert", "pair_w", "sh_h", "moe_h", "ple_e", "ple_kv", "ple_send", "ple_red", "ple_gv",
+                 "ple_nc", "logits", "amax_val", "amax_idx", "lse_max", "lse_sum", "gdn_save", "hidden_out")
+
+
+class QwBuffers(C.Structure):
+    _fields_ = [(n, P) for n in BUFFER_FIELDS]
+
+
+class QwRows(C.Structure):
+    _fields_ = [("M", C.c_int), ("max_groups", C.c_int), ("tokens", P), ("slot", P), ("pos", P), ("run_start", P),
+                ("run_len", P), ("ctx3", P)]
+
+
+COMM_FN = C.CFUNCTYPE(None, P, C.c_int, C.c_int, P, P, C.c_int, C.c_int, P)
+
+
+class QwModel(C.Structure):
+    _fields_ = [("d", QwDims), ("layers", C.POINTER(QwLayer)), ("final_hc", QwHc), ("ple", QwPle), ("embed", P),
+                ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P)]
