@@ -18,11 +18,16 @@ struct Ctx {
     cudaStream_t s;
     int site;
     int err;
+    long long launches;
 };
 
-#define QW_TRY(expr)                       \
+long long g_last_launches = 0;   // kernels enqueued by the most recent qwrt_decode call
+
+// Runs a launcher that enqueues `n` kernels; remembers the first failure and counts the launches.
+#define QW_TRYN(n, expr)                   \
     do {                                   \
         int rc__ = (expr);                 \
+        c.launches += (n);                 \
         if (rc__ != 0 && c.err == 0) c.err = rc__ * 1000 - __LINE__; \
     } while (0)
 
@@ -41,9 +46,9 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const QwBuffers &b = md.b;
     const int M = c.rows->M, ld = hc_send(d);
     const int down = d.hc_rank + w.n_inj;
-    QW_TRY(qwk_hc_pre(b.X, pend, d.SH, inj_prev, d.hc, w.w1, d.SH, d.hc, b.y, b.send, ld, M, c.s));
+    QW_TRYN(1, qwk_hc_pre(b.X, pend, d.SH, inj_prev, d.hc, w.w1, d.SH, d.hc, b.y, b.send, ld, M, c.s));
     // part[s][j] = Wd[j][s][:] . y[s][:]  -> send[m][hc + s*down + j]
-    QW_TRY(qwk_gemv_bf16(w.Wd, b.y, b.send + d.hc, nullptr, down, d.SH, M, d.hc * d.SH, d.hc * d.SH, ld, 0, d.hc,
+    QW_TRYN(1, qwk_gemv_bf16(w.Wd, b.y, b.send + d.hc, nullptr, down, d.SH, M, d.hc * d.SH, d.hc * d.SH, ld, 0, d.hc,
                          d.SH, d.SH, down, c.s));
     const float *red = b.send;
     if (d.ranks > 1) {
@@ -52,7 +57,7 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     } else {
         ++c.site;
     }
-    QW_TRY(qwk_hc_up_mix(red, ld, w.Wu, b.y, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
+    QW_TRYN(1, qwk_hc_up_mix(red, ld, w.Wu, b.y, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
                          d.rank * d.SH, c.s));
     comm(c, 1, b.bin, b.bin, M, d.SH);
 }
@@ -64,17 +69,17 @@ void gdn_block(Ctx &c, const QwLayer &L, int flags) {
     const QwRows &r = *c.rows;
     const int M = r.M, gi = L.state_index;
     const int qkv_l = (2 * d.KL + d.VL) * 128;
-    QW_TRY(qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
-    QW_TRY(qwk_gdn_conv(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, d.KL, d.VL, M, r.slot, r.pos,
+    QW_TRYN(1, qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(2, qwk_gdn_conv(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, d.KL, d.VL, M, r.slot, r.pos,
                         r.run_start, r.run_len, b.qkv, b.decay, b.beta, d.eps, c.s));
     float *save = nullptr;
     if ((flags & QWRT_SAVE_GDN) && b.gdn_save)
         save = b.gdn_save + (size_t)gi * d.max_rows * d.VL * 128 * 128;
-    QW_TRY(qwk_gdn_scan(b.qkv, b.decay, b.beta, b.proj, d.proj_gdn, md.st.gdn_S[gi], save, L.gdn_norm, d.KL, d.VL, M,
+    QW_TRYN(1, qwk_gdn_scan(b.qkv, b.decay, b.beta, b.proj, d.proj_gdn, md.st.gdn_S[gi], save, L.gdn_norm, d.KL, d.VL, M,
                         r.slot, r.pos, r.run_start, r.run_len, b.o, d.eps, c.s));
     (void)qkv_l;
     const int K = d.VL * 128;
-    QW_TRY(qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
 void qsa_block(Ctx &c, const QwLayer &L) {
@@ -84,20 +89,20 @@ void qsa_block(Ctx &c, const QwLayer &L) {
     const QwRows &r = *c.rows;
     const QwState &st = md.st;
     const int M = r.M, qi = L.state_index;
-    QW_TRY(qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_qsa, d.H, M, d.H, d.H, d.proj_qsa, 0, 1, 0, 0, 0, c.s));
-    QW_TRY(qwk_qsa_prep(b.proj, d.proj_qsa, d.QL, d.KVL, d.IH, L.qn1, L.kn1, L.iqn1, L.ikn1, M, r.slot, r.pos,
+    QW_TRYN(1, qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_qsa, d.H, M, d.H, d.H, d.proj_qsa, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN((M <= 16 - d.idx_ratio ? 1 : 2), qwk_qsa_prep(b.proj, d.proj_qsa, d.QL, d.KVL, d.IH, L.qn1, L.kn1, L.iqn1, L.ikn1, M, r.slot, r.pos,
                         r.run_start, r.run_len, st.k_dev[qi], st.v_dev[qi], st.k_host ? st.k_host[qi] : nullptr,
                         st.v_host ? st.v_host[qi] : nullptr, d.n_dev_pages, st.page_table, d.max_pages, b.q, b.iq,
                         st.raw_ring[qi], st.ck[qi], d.ck_cap, d.idx_ratio, d.eps, c.s));
-    QW_TRY(qwk_qsa_scores(b.iq, d.IH, st.ck[qi], d.ck_cap, M, r.slot, r.pos, d.idx_ratio, d.idx_topk, b.scores,
+    QW_TRYN((r.max_groups > d.idx_topk ? 1 : 0), qwk_qsa_scores(b.iq, d.IH, st.ck[qi], d.ck_cap, M, r.slot, r.pos, d.idx_ratio, d.idx_topk, b.scores,
                           d.score_cap, r.max_groups, c.s));
-    QW_TRY(qwk_qsa_select(b.scores, d.score_cap, M, r.pos, d.idx_ratio, d.idx_topk, b.sel, b.sel_n, c.s));
-    QW_TRY(qwk_qsa_attend(b.q, d.QL, d.KVL, M, r.slot, r.pos, st.k_dev[qi], st.v_dev[qi],
+    QW_TRYN(1, qwk_qsa_select(b.scores, d.score_cap, M, r.pos, d.idx_ratio, d.idx_topk, b.sel, b.sel_n, c.s));
+    QW_TRYN(2, qwk_qsa_attend(b.q, d.QL, d.KVL, M, r.slot, r.pos, st.k_dev[qi], st.v_dev[qi],
                           st.k_host ? st.k_host[qi] : nullptr, st.v_host ? st.v_host[qi] : nullptr, d.n_dev_pages,
                           st.page_table, d.max_pages, b.sel, b.sel_n, d.idx_topk, d.idx_ratio, d.nsplit, b.pm, b.pl,
                           b.pacc, b.proj, d.proj_qsa, b.o, c.s));
     const int K = d.QL * 256;
-    QW_TRY(qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
 void moe_block(Ctx &c, const QwLayer &L) {
@@ -106,10 +111,10 @@ void moe_block(Ctx &c, const QwLayer &L) {
     const QwBuffers &b = md.b;
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
-    QW_TRY(qwk_gemv_bf16(L.Wrs, b.bin, b.rs, nullptr, nrs, d.H, M, d.H, d.H, nrs, 0, 1, 0, 0, 0, c.s));
-    QW_TRY(qwk_moe_route(b.rs, nrs, M, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert, b.pair_w, b.sh_h, c.s));
-    QW_TRY(qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
-    QW_TRY(qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
+    QW_TRYN(1, qwk_gemv_bf16(L.Wrs, b.bin, b.rs, nullptr, nrs, d.H, M, d.H, d.H, nrs, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_moe_route(b.rs, nrs, M, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert, b.pair_w, b.sh_h, c.s));
+    QW_TRYN(1, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
+    QW_TRYN(1, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
                                 d.SF, b.partial, d.H, c.s));
 }
 
@@ -132,10 +137,10 @@ void ple_block(Ctx &c) {
     const QwRows &r = *c.rows;
     const QwPle &p = md.ple;
     const int M = r.M;
-    QW_TRY(qwk_ple_gather(r.ctx3, p.shards, p.scales, p.rows_per_shard, p.rows, p.layout, d.ngram_dim, d.ngram_heads,
+    QW_TRYN(1, qwk_ple_gather(r.ctx3, p.shards, p.scales, p.rows_per_shard, p.rows, p.layout, d.ngram_dim, d.ngram_heads,
                           b.ple_e, nullptr, M, c.s));
-    QW_TRY(qwk_gemv_bf16(p.Wkv, b.ple_e, b.ple_kv, nullptr, d.ple_kv, d.H, M, d.H, d.H, d.ple_kv, 0, 1, 0, 0, 0, c.s));
-    QW_TRY(qwk_ple_stats(b.ple_kv, d.ple_kv, b.X, p.nk1, p.nq1, d.SH, d.hc, b.ple_send, 16, M, c.s));
+    QW_TRYN(1, qwk_gemv_bf16(p.Wkv, b.ple_e, b.ple_kv, nullptr, d.ple_kv, d.H, M, d.H, d.H, d.ple_kv, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_ple_stats(b.ple_kv, d.ple_kv, b.X, p.nk1, p.nq1, d.SH, d.hc, b.ple_send, 16, M, c.s));
     const float *red = b.ple_send;
     if (d.ranks > 1) {
         comm(c, 0, b.ple_send, b.ple_red, M, 16);
@@ -143,7 +148,7 @@ void ple_block(Ctx &c) {
     } else {
         ++c.site;
     }
-    QW_TRY(qwk_ple_apply(b.ple_kv, d.ple_kv, red, 16, p.nc1, p.cw, d.SH, d.hc, d.H, d.eps, d.ple_taps, d.ple_dil,
+    QW_TRYN(3, qwk_ple_apply(b.ple_kv, d.ple_kv, red, 16, p.nc1, p.cw, d.SH, d.hc, d.H, d.eps, d.ple_taps, d.ple_dil,
                          b.ple_gv, b.ple_nc, md.st.ple_ring, b.X, M, r.slot, r.pos, r.run_start, r.run_len, c.s));
 }
 
@@ -151,19 +156,19 @@ void ple_block(Ctx &c) {
 
 extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
                                                                    int n_layers_run, cudaStream_t stream) {
-    Ctx c{md, rows, stream, 0, 0};
+    Ctx c{md, rows, stream, 0, 0, 0};
     const QwDims &d = md->d;
     const QwBuffers &b = md->b;
     const int M = rows->M;
     if (M < 1 || M > d.max_rows) return -1;
     if (n_layers_run < 0 || n_layers_run > d.n_layers) n_layers_run = d.n_layers;
-    QW_TRY(qwk_embed_rows(rows->tokens, md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, stream));
+    QW_TRYN(1, qwk_embed_rows(rows->tokens, md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, stream));
     const float *pend = nullptr;
     float *inj_attn = b.inj_a, *inj_mlp = b.inj_b;
     for (int l = 0; l < n_layers_run; ++l) {
         const QwLayer &L = md->layers[l];
         if (l == d.ple_layer && md->ple.enabled) {
-            if (pend) QW_TRY(qwk_hc_pre(b.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, stream));
+            if (pend) QW_TRYN(1, qwk_hc_pre(b.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, stream));
             pend = nullptr;
             ple_block(c);
         }
@@ -181,13 +186,17 @@ extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel 
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
         cudaMemcpyAsync(b.hidden_out, b.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, stream);
     if (!(flags & QWRT_NO_HEAD)) {
-        QW_TRY(qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
+        QW_TRYN(1, qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
                              stream));
-        QW_TRY(qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
+        QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
                               b.lse_sum, stream));
         if ((flags & QWRT_CHAIN) && d.ranks == 1)
-            QW_TRY(qwk_advance_rows(const_cast<int *>(rows->tokens), const_cast<int *>(rows->pos),
+            QW_TRYN(1, qwk_advance_rows(const_cast<int *>(rows->tokens), const_cast<int *>(rows->pos),
                                     const_cast<int *>(rows->ctx3), b.amax_idx, M, stream));
     }
+    g_last_launches = c.launches;
     return c.err;
 }
+
+// Kernels enqueued by the most recent qwrt_decode call (what one replay of its graph launches).
+extern "C" __attribute__((visibility("default"))) long long qwrt_last_launches() { return g_last_launches; }

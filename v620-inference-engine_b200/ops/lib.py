@@ -128,6 +128,8 @@ def load(required: Optional[bool] = None) -> Optional[ctypes.CDLL]:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
+    if hasattr(lib, "qwrt_last_launches"):
+        lib.qwrt_last_launches.restype = ctypes.c_longlong
     _lib = lib
     return lib
 
