@@ -62,6 +62,9 @@ class DeviceModel:
         self._alloc_buffers(save_gdn)
         self._alloc_rows()
         qlib.check(self.lib.qwk_rope_init(C.c_double(cfg.rope_theta), cfg.rope_dim), "rope_init")
+        # error word for kernels with bounded waits: (code, detail), 0 = ok
+        self.err_word = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        self.lib.qwk_set_error_word(C.c_void_p(self.err_word.data_ptr()))
         self._init_ngram()
         self.comm_cb = None
 
@@ -147,6 +150,7 @@ class DeviceModel:
             "ple_red": ((R, 16), f32), "ple_gv": ((R, sc.xw), f32), "ple_nc": ((R, sc.xw), f32),
             "logits": ((R, sc.vocab_l), f32), "amax_val": ((R,), f32), "amax_idx": ((R,), i32),
             "lse_max": ((R,), f32), "lse_sum": ((R,), f32), "hidden_out": ((R, c.hc, sc.sh), f32),
+            "X2": ((R, c.hc, sc.sh), f32), "ticket": ((4,), i32),
         }
         if save_gdn:
             shapes["gdn_save"] = ((c.n_gdn, R, sc.gdn_vl, c.gdn_dim, c.gdn_dim), f32)
@@ -325,6 +329,12 @@ class DeviceModel:
             # the warm-up executed the step once for real; the capture only records it
             return
         g.replay()
+
+    def check_error(self):
+        """Raise if a kernel gave up on a bounded wait or failed a bounds check."""
+        code, detail = self.err_word.tolist()
+        if code:
+            raise RuntimeError(f"device error word: code {code} detail {detail}")
 
     def set_comm(self, fn):
         """Install the collective hook (a Python callable wrapped as a C callback)."""

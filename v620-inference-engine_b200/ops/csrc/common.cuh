@@ -36,6 +36,9 @@ enum ErrCode : unsigned int {
 __device__ __forceinline__ void report(ErrorWord *e, unsigned int code, unsigned int detail) {
     if (e && atomicCAS(&e->code, 0u, code) == 0u) e->detail = detail;
 }
+// Device address of the error word every launcher hands to its kernel (set once by the host through
+// qwk_set_error_word; null until then, in which case kernels only give up silently).
+extern ErrorWord *g_err_ptr;
 
 // Row tables of a batched step.  Row i appends one token to slot[i] at position pos[i]; rows of
 // one slot are consecutive and run_start[i] is the first row of that slot's run.
@@ -126,6 +129,32 @@ __device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x, float acc)
     acc = fmaf(bf16_hi(w.w), bf16_hi(x.w), acc);
     return acc;
 }
+
+// ---- programmatic dependent launch (PDL) -------------------------------------------------
+// Every kernel of the decode step is launched with the programmatic-stream-serialization
+// attribute.  A kernel first lets its successor start (pdl_trigger), prefetches weights — which
+// no kernel writes — and only then waits for its predecessor to finish and flush (pdl_wait)
+// before it touches activations.  Every block must reach pdl_wait before it exits: a grid that
+// completes without waiting would let its successor run ahead of the grid before it.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+constexpr int NUM_SMS = 148;
 
 // NeoX rotation angle tables: cos/sin for (pos, i) computed in double like the oracle.
 __device__ __forceinline__ void rope_cs(int pos, int i, int rope_dim, double theta, float &c, float &s) {

@@ -148,6 +148,133 @@ __global__ void __launch_bounds__(512) gdn_scan_kernel(GdnScanArgs a) {
     for (int i = 0; i < 32; ++i) Sg[(kg * 32 + i) * GD + c] = S[i];
 }
 
+// ------------------------------------------------------------------------------------------
+// Fused decode step for short runs (M <= GDN_RING - 4): conv + gating + L2 norm + delta-rule update +
+// gated norm in one kernel, and the ring store.  grid (M, VL), 512 threads; the block of (run start,
+// head h) walks the run.  q/k of the head's key head are recomputed by each of the value heads that
+// share it.  Ring entries written here (positions of the run) never alias the entries read
+// (positions before the run) because the run is shorter than the ring minus the conv window.
+// ------------------------------------------------------------------------------------------
+struct GdnFusedArgs {
+    const float *proj;
+    int ld_proj;
+    float *ring;
+    const float *cw, *A_log, *dt_bias, *norm_w;
+    int KL, VL;
+    Rows rows;
+    float *S, *save;
+    bf16 *o;
+    float eps;
+};
+
+__global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
+    __shared__ float kq[2][GD];
+    __shared__ float vv[GD];
+    __shared__ float red[4][GD];
+    __shared__ float scratch[32];
+    __shared__ float s_gate[2];
+    const int m0 = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, c = tid & 127, kg = tid >> 7;
+    const int qkv_l = (2 * a.KL + a.VL) * GD;
+    const int rep = a.VL / a.KL, kh = h / rep;
+    // conv taps of this thread's channel (weights: independent of the predecessor)
+    int ch = -1;
+    if (kg == 0) ch = kh * GD + c;                       // q
+    else if (kg == 1) ch = (a.KL + kh) * GD + c;         // k
+    else if (kg == 2) ch = (2 * a.KL + h) * GD + c;      // v
+    float tap[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ch >= 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tap[k] = a.cw[ch * 4 + k];
+    }
+    pdl_wait();
+    pdl_trigger();
+    if (a.rows.run_start[m0] != m0) return;
+    const int len = a.rows.run_len[m0], slot = a.rows.slot[m0];
+    float *ring = a.ring + (long long)slot * GDN_RING * qkv_l;
+    float *Sg = a.S + ((long long)slot * a.VL + h) * GD * GD;
+    float S[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[i] = Sg[(kg * 32 + i) * GD + c];
+    for (int r = 0; r < len; ++r) {
+        const int m = m0 + r, pos = a.rows.pos[m];
+        // conv + silu for q / k / v channels
+        float val = 0.f;
+        if (ch >= 0) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int back = 3 - k, q = pos - back;
+                float x;
+                if (r - back >= 0) x = a.proj[(long long)(m - back) * a.ld_proj + ch];
+                else if (q >= 0) x = ring[(q % GDN_RING) * qkv_l + ch];
+                else x = 0.f;
+                acc = fmaf(tap[k], x, acc);
+            }
+            val = siluf_(acc);
+        }
+        // L2 norms of q (warps 0-3) and k (warps 4-7)
+        const float ssw = warp_sum(kg < 2 ? val * val : 0.f);
+        __syncthreads();
+        if ((tid & 31) == 0) scratch[tid >> 5] = ssw;
+        if (tid == 0) {
+            const float *row = a.proj + (long long)m * a.ld_proj + qkv_l + a.VL * GD;
+            const float g = -__expf(a.A_log[h]) * softplusf_(row[a.VL + h] + a.dt_bias[h]);
+            s_gate[0] = __expf(g);
+            s_gate[1] = sigmoidf_(row[h]);
+        }
+        __syncthreads();
+        if (kg == 0) {
+            const float ss = scratch[0] + scratch[1] + scratch[2] + scratch[3];
+            kq[1][c] = val / sqrtf(ss + a.eps) * 0.08838834764831845f;
+        } else if (kg == 1) {
+            const float ss = scratch[4] + scratch[5] + scratch[6] + scratch[7];
+            kq[0][c] = val / sqrtf(ss + a.eps);
+        } else if (kg == 2) {
+            vv[c] = val;
+        }
+        __syncthreads();
+        const float dec = s_gate[0], be = s_gate[1];
+        float p = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            S[i] *= dec;
+            p = fmaf(S[i], kq[0][kg * 32 + i], p);
+        }
+        red[kg][c] = p;
+        __syncthreads();
+        const float stk = red[0][c] + red[1][c] + red[2][c] + red[3][c];
+        const float u = (vv[c] - stk) * be;
+        float oq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            S[i] = fmaf(kq[0][kg * 32 + i], u, S[i]);
+            oq = fmaf(S[i], kq[1][kg * 32 + i], oq);
+        }
+        __syncthreads();
+        red[kg][c] = oq;
+        __syncthreads();
+        if (a.save) {
+            float *sv = a.save + ((long long)m * a.VL + h) * GD * GD;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sv[(kg * 32 + i) * GD + c] = S[i];
+        }
+        float ov = 0.f;
+        if (kg == 0) ov = red[0][c] + red[1][c] + red[2][c] + red[3][c];
+        const float ss = block_sum<512>(ov * ov, scratch);
+        if (kg == 0) {
+            const float z = a.proj[(long long)m * a.ld_proj + qkv_l + h * GD + c];
+            const float y = ov * rsqrtf(ss / float(GD) + a.eps) * a.norm_w[c] * sigmoidf_(z);
+            a.o[(long long)m * a.VL * GD + h * GD + c] = __float2bfloat16(y);
+        }
+        // ring store of this row's pre-conv values: v channels by every head, q/k by the first head of the group
+        if (ch >= 0 && (kg == 2 || h % rep == 0))
+            ring[(pos % GDN_RING) * qkv_l + ch] = a.proj[(long long)m * a.ld_proj + ch];
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) Sg[(kg * 32 + i) * GD + c] = S[i];
+}
+
 }  // namespace qw
 
 using namespace qw;
@@ -180,3 +307,24 @@ QW_API int qwk_gdn_scan(const float *qkv, const float *decay, const float *beta,
     gdn_scan_kernel<<<grid, 512, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// One GDN step for M rows: the fused kernel for short batches, else conv + ring + scan.
+QW_API int qwk_gdn_step(const float *proj, int ld_proj, float *ring, const float *cw, const float *A_log,
+                        const float *dt_bias, const float *norm_w, int KL, int VL, int M, const int *slot, const int *pos,
+                        const int *run_start, const int *run_len, float *S, float *save, float *qkv, float *decay,
+                        float *beta, void *o, float eps, cudaStream_t s) {
+    if (M <= GDN_RING - 4) {
+        GdnFusedArgs a;
+        a.proj = proj; a.ld_proj = ld_proj; a.ring = ring; a.cw = cw; a.A_log = A_log; a.dt_bias = dt_bias;
+        a.norm_w = norm_w; a.KL = KL; a.VL = VL; a.rows = Rows{M, slot, pos, run_start, run_len};
+        a.S = S; a.save = save; a.o = (bf16 *)o; a.eps = eps;
+        cudaError_t e = launch_pdl(gdn_fused_kernel, dim3(M, VL), dim3(512), 0, s, a);
+        return e == cudaSuccess ? 0 : -2;
+    }
+    int rc = qwk_gdn_conv(proj, ld_proj, ring, cw, A_log, dt_bias, KL, VL, M, slot, pos, run_start, run_len, qkv, decay,
+                          beta, eps, s);
+    if (rc) return rc;
+    return qwk_gdn_scan(qkv, decay, beta, proj, ld_proj, S, save, norm_w, KL, VL, M, slot, pos, run_start, run_len, o,
+                        eps, s);
+}
+

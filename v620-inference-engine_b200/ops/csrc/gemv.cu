@@ -1,109 +1,41 @@
-// Decode-path matrix-vector kernels: y[m][n] = sum_k W[n][k] x[m][k] for M <= 32 rows against
-// one read of the weights.  bf16 weights (dense layers) and q4 weights (routed experts, per
-// (row, expert) pair).  Memory-bound by design: 16-byte streaming loads, several in flight per
-// lane, fp32 accumulation in a fixed order so a row's result does not depend on how many other
-// rows share the step (the role of the reference's src/kernels/gemv.hip:8-42 and
-// src/kernels/moe_experts.hip:189-246).
-#include "common.cuh"
+// Decode-path matrix-vector kernel: y[m][n] = sum_k W[n][k] x[m][k] for M <= 32 rows against one
+// read of the bf16 weights.  Memory-bound by design:
+//   * a persistent grid (a multiple of the SM count) strides over (row group, column split) items,
+//     so every SM streams the same share of the matrix and there is no partial last wave;
+//   * 16-byte streaming loads that bypass L1, four in flight per lane;
+//   * launched with programmatic dependent launch: before it waits for its predecessor it asks
+//     the L2 to prefetch the weight rows of its first items (weights are never written), so HBM
+//     keeps streaming across the kernel boundary;
+//   * fp32 accumulation in a fixed order, so a row's result does not depend on how many other rows
+//     share the step.
+// (Role of the reference's src/kernels/gemv.hip:8-42.)
+#include "gemv.cuh"
+#include "sgemv.cuh"
 
 namespace qw {
-
-// ------------------------------------------------------------------------------------------
-// bf16 GEMV.  Block = 8 warps.  `wpr` warps cooperate on one output row (K split between them,
-// partials summed in warp order), so a block covers 8/wpr rows.  blockIdx.y selects a column
-// split (used by the hyper-connection down projection, which needs per-stream partial sums).
-// ------------------------------------------------------------------------------------------
-struct GemvArgs {
-    const bf16 *W;      // [N][ldw]
-    const bf16 *x;      // [M][ldx]
-    float *y;           // [M][ldy]
-    int N, K, M;
-    int ldw, ldx, ldy;
-    int wpr;            // warps per row: 1, 2, 4 or 8
-    int accumulate;     // y += instead of y =
-    // column splits (gridDim.y): element offsets added per split
-    long long w_split, x_split, y_split;
-    bf16 *y_bf16;       // optional second output in bf16 (same indexing as y), may be null
-};
 
 template <int MT>
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(GemvArgs a) {
     __shared__ float part[8][MT];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wpr = a.wpr;
-    const int rpb = 8 / wpr;
-    const int row = blockIdx.x * rpb + warp / wpr;
-    const int kw = warp % wpr;
-    const bf16 *W = a.W + (long long)blockIdx.y * a.w_split;
-    const bf16 *x = a.x + (long long)blockIdx.y * a.x_split;
-    float *y = a.y + (long long)blockIdx.y * a.y_split;
-    const int nchunk = a.K >> 3;
-    const int stride = wpr * 32;
-    for (int m0 = 0; m0 < a.M; m0 += MT) {
-        float acc[MT];
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-        if (row < a.N) {
-            const uint4 *wp = reinterpret_cast<const uint4 *>(W + (long long)row * a.ldw);
-            for (int c = kw * 32 + lane; c < nchunk; c += 4 * stride) {
-                uint4 w[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (c + u * stride < nchunk) w[u] = ld_stream(wp + c + u * stride);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (c + u * stride < nchunk) {
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            if (m0 + m < a.M) {
-                                const uint4 xv = __ldg(reinterpret_cast<const uint4 *>(x + (long long)(m0 + m) * a.ldx) + c + u * stride);
-                                acc[m] = dot8(w[u], xv, acc[m]);
-                            }
-                        }
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
-        if (wpr > 1) {
-            __syncthreads();
-            if (lane == 0) {
-#pragma unroll
-                for (int m = 0; m < MT; ++m) part[warp][m] = acc[m];
-            }
-            __syncthreads();
-            if (kw == 0) {
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    float s = 0.f;
-                    for (int j = 0; j < wpr; ++j) s += part[warp + j][m];
-                    acc[m] = s;
-                }
-            }
-        }
-        if (kw == 0 && lane == 0 && row < a.N) {
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m0 + m < a.M) {
-                    const long long o = (long long)(m0 + m) * a.ldy + row;
-                    float v = acc[m];
-                    if (a.accumulate) v += y[o];
-                    y[o] = v;
-                    if (a.y_bf16) (a.y_bf16 + (long long)blockIdx.y * a.y_split)[o] = __float2bfloat16(v);
-                }
-            }
-        }
-    }
+    gemv_body<MT>(a, part);
 }
 
-static inline int pick_wpr(int N, int nsplit) {
-    // aim for >= ~4 blocks per SM without shrinking a warp's K share below one pass
-    long long rows = (long long)N * nsplit;
-    if (rows >= 148 * 4 * 8) return 1;
-    if (rows >= 148 * 4 * 4) return 2;
-    if (rows >= 148 * 4 * 2) return 4;
-    return 8;
+template <int MT>
+__global__ void __launch_bounds__(256, 1) sgemv_kernel(SGemvArgs a) {
+    extern __shared__ __align__(128) unsigned char sg_smem[];
+    sgemv_body<MT>(a, sg_smem);
+}
+
+template <int MT>
+static cudaError_t launch_sgemv(SGemvArgs &a, cudaStream_t s) {
+    int grid;
+    const size_t smem = sgemv_plan(a, MT, grid);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaFuncSetAttribute(sgemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured = 200 * 1024;
+    }
+    return launch_pdl(sgemv_kernel<MT>, dim3(grid), dim3(256), smem, s, a);
 }
 
 }  // namespace qw
@@ -117,18 +49,29 @@ QW_API int qwk_gemv_bf16(const void *W, const void *x, float *y, void *y_bf16, i
                          cudaStream_t s) {
     if (N <= 0 || M <= 0) return 0;
     if ((K & 7) || (ldw & 7) || (ldx & 7)) return -1;
+    if (nsplit <= 1 && (size_t)K * 2 <= 16384) {
+        // the streaming kernel: bulk-async weight pipeline, one block per SM
+        SGemvArgs g;
+        g.W = (const bf16 *)W; g.x = (const bf16 *)x; g.y = y; g.y_bf16 = (bf16 *)y_bf16;
+        g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.err = g_err_ptr;
+        cudaError_t e;
+        if (M == 1) e = launch_sgemv<1>(g, s);
+        else if (M == 2) e = launch_sgemv<2>(g, s);
+        else if (M <= 4) e = launch_sgemv<4>(g, s);
+        else e = launch_sgemv<8>(g, s);
+        return e == cudaSuccess ? 0 : -2;
+    }
     GemvArgs a;
     a.W = (const bf16 *)W; a.x = (const bf16 *)x; a.y = y; a.y_bf16 = (bf16 *)y_bf16;
     a.N = N; a.K = K; a.M = M; a.ldw = ldw; a.ldx = ldx; a.ldy = ldy;
     a.accumulate = accumulate;
+    a.nsplit = nsplit < 1 ? 1 : nsplit;
     a.w_split = w_split; a.x_split = x_split; a.y_split = y_split;
-    if (nsplit < 1) nsplit = 1;
-    a.wpr = pick_wpr(N, nsplit);
-    const int rpb = 8 / a.wpr;
-    dim3 grid((N + rpb - 1) / rpb, nsplit);
-    if (M == 1) gemv_bf16_kernel<1><<<grid, 256, 0, s>>>(a);
-    else if (M == 2) gemv_bf16_kernel<2><<<grid, 256, 0, s>>>(a);
-    else if (M <= 4) gemv_bf16_kernel<4><<<grid, 256, 0, s>>>(a);
-    else gemv_bf16_kernel<8><<<grid, 256, 0, s>>>(a);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    const int grid = gemv_plan(a);
+    cudaError_t e;
+    if (M == 1) e = launch_pdl(gemv_bf16_kernel<1>, dim3(grid), dim3(256), 0, s, a);
+    else if (M == 2) e = launch_pdl(gemv_bf16_kernel<2>, dim3(grid), dim3(256), 0, s, a);
+    else if (M <= 4) e = launch_pdl(gemv_bf16_kernel<4>, dim3(grid), dim3(256), 0, s, a);
+    else e = launch_pdl(gemv_bf16_kernel<8>, dim3(grid), dim3(256), 0, s, a);
+    return e == cudaSuccess ? 0 : -2;
 }

@@ -53,50 +53,64 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(float *X, const float *pend
 }
 
 constexpr int UP_ROWS = 4;     // rows per block of hc_up_mix
+constexpr int UP_MAXI = 5;     // 16-byte weight pieces per lane: covers mixer ranks up to 320
 
 // grid (ceil(SH/8), ceil(M/UP_ROWS)), 256 threads.  hc must be 4 (one 8-lane group per stream).
+// y[s][c] = bf16(X[s][c] * w1[s][c]) is recomputed here exactly as hc_down_kernel computed it.
 __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
-                                                        const bf16 *y, int SH, int hc, int R, int hc_down, float inv_H,
-                                                        float eps, int M, float *inj, int ld_inj, bf16 *bin, int ld_bin,
-                                                        int bin_col0) {
+                                                        const float *X, const float *w1, int SH, int hc, int R, int hc_down,
+                                                        float inv_H, float eps, int M, float *inj, int ld_inj, bf16 *bin,
+                                                        int ld_bin, int bin_col0) {
     extern __shared__ float sm[];
     float *u = sm;                         // [UP_ROWS][R]
     float *rs = sm + UP_ROWS * R;          // [UP_ROWS][hc]
     const int m0 = blockIdx.y * UP_ROWS;
     const int nrow = min(UP_ROWS, M - m0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 8 + warp;
+    const int s = lane >> 3, li = lane & 7;
+    const int nch = R >> 3;
+    // weights first: they do not depend on the predecessor
+    uint4 w[UP_MAXI];
+    if (c < SH) {
+        const uint4 *wp = reinterpret_cast<const uint4 *>(Wu + ((long long)c * hc + s) * R);
+#pragma unroll
+        for (int i = 0; i < UP_MAXI; ++i)
+            if (li + 8 * i < nch) w[i] = ld_stream(wp + li + 8 * i);
+    }
+    pdl_wait();
+    pdl_trigger();
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
-        const int mm = i / hc, s = i % hc;
-        rs[mm * hc + s] = rsqrtf(red[(long long)(m0 + mm) * ld_red + s] * inv_H + eps);
+        const int mm = i / hc, ss = i % hc;
+        rs[mm * hc + ss] = rsqrtf(red[(long long)(m0 + mm) * ld_red + ss] * inv_H + eps);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nrow * hc_down; i += 256) {
         const int mm = i / hc_down, j = i % hc_down;
         const float *p = red + (long long)(m0 + mm) * ld_red + hc + j;
         float d = 0.f;
-        for (int s = 0; s < hc; ++s) d = fmaf(rs[mm * hc + s], p[s * hc_down], d);
+        for (int ss = 0; ss < hc; ++ss) d = fmaf(rs[mm * hc + ss], p[ss * hc_down], d);
         if (j < R) u[mm * R + j] = siluf_(d / float(hc));
         else if (inj && blockIdx.x == 0) inj[(long long)(m0 + mm) * ld_inj + (j - R)] = d;
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * 8 + warp;
     if (c >= SH) return;
-    const int s = lane >> 3, li = lane & 7;
-    const uint4 *wp = reinterpret_cast<const uint4 *>(Wu + ((long long)c * hc + s) * R);
-    const int nch = R >> 3;
     float acc[UP_ROWS];
 #pragma unroll
     for (int mm = 0; mm < UP_ROWS; ++mm) acc[mm] = 0.f;
-    for (int ch = li; ch < nch; ch += 8) {
-        const uint4 w = ld_stream(wp + ch);
-        const float wf[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
-                             bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
 #pragma unroll
-        for (int mm = 0; mm < UP_ROWS; ++mm) {
-            if (mm < nrow) {
-                const float *uu = u + mm * R + ch * 8;
+    for (int i = 0; i < UP_MAXI; ++i) {
+        const int ch = li + 8 * i;
+        if (ch < nch) {
+            const float wf[8] = {bf16_lo(w[i].x), bf16_hi(w[i].x), bf16_lo(w[i].y), bf16_hi(w[i].y),
+                                 bf16_lo(w[i].z), bf16_hi(w[i].z), bf16_lo(w[i].w), bf16_hi(w[i].w)};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[mm] = fmaf(wf[i], uu[i], acc[mm]);
+            for (int mm = 0; mm < UP_ROWS; ++mm) {
+                if (mm < nrow) {
+                    const float *uu = u + mm * R + ch * 8;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[mm] = fmaf(wf[k], uu[k], acc[mm]);
+                }
             }
         }
     }
@@ -108,12 +122,132 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         g += __shfl_xor_sync(0xffffffffu, g, 4);
         float v = 0.f;
         if (mm < nrow) {
-            const float yv = __bfloat162float(y[((long long)(m0 + mm) * hc + s) * SH + c]);
+            const float xv = X[((long long)(m0 + mm) * hc + s) * SH + c] * w1[s * SH + c];
+            const float yv = __bfloat162float(__float2bfloat16(xv));
             v = sigmoidf_(g) * yv * rs[mm * hc + s];
         }
         v += __shfl_xor_sync(0xffffffffu, v, 8);
         v += __shfl_xor_sync(0xffffffffu, v, 16);
         if (lane == 0 && mm < nrow) bin[(long long)(m0 + mm) * ld_bin + bin_col0 + c] = __float2bfloat16(v / float(hc));
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Fused mixer front end: deferred combine + per-stream sum of squares + down projection.
+//   Xout[m][s][:] = Xin[m][s][:] + pend[m][:] * 2*sigmoid(inj_prev[m][s]/hc)     (when pend != null)
+//   send[m][s]               = sum_c X^2
+//   send[m][hc + s*down + j] = sum_c Wd[j][s][c] * bf16(X[s][c] * w1[s][c])
+// Every block rebuilds the bf16 row slice it needs in shared memory (the residual is tiny and
+// sits in L2); blocks with blockIdx.x == 0 also store X and the sums of squares.  X is written
+// to a second buffer because other blocks still read the old one.
+// grid (ceil(down/rpb), hc, ceil(M/8)), 256 threads, dynamic smem 8*SH bf16.
+// ------------------------------------------------------------------------------------------
+struct HcDownArgs {
+    const float *Xin;
+    float *Xout;            // null: no combine, X stays where it is
+    const float *pend;      // [M][ld_pend] or null
+    int ld_pend;
+    const float *inj_prev;  // [M][hc]
+    const float *w1;        // [hc][SH]
+    const bf16 *Wd;         // [down][hc][SH]
+    float *send;            // [M][ld_send]
+    int ld_send, SH, hc, down, M, wpr;
+};
+
+__global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    bf16 *ybuf = reinterpret_cast<bf16 *>(smraw);          // [8][SH]
+    __shared__ float part[8][8];
+    __shared__ float scratch[32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = blockIdx.y, m0 = blockIdx.z * 8;
+    const int nrow = min(8, a.M - m0);
+    const int wpr = a.wpr, rpb = 8 / wpr;
+    const int j = blockIdx.x * rpb + warp / wpr, kw = warp % wpr;
+    const int nchunk = a.SH >> 3;
+    const bf16 *wrow = a.Wd + ((long long)j * a.hc + s) * a.SH;
+    // weights first: prefetch this warp's share of its row into registers / L2
+    uint4 w0[4];
+    const int stride = wpr * 32;
+    if (j < a.down) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = kw * 32 + lane + u * stride;
+            if (c < nchunk) w0[u] = ld_stream(reinterpret_cast<const uint4 *>(wrow) + c);
+        }
+    }
+    pdl_wait();
+    pdl_trigger();
+    for (int r = 0; r < nrow; ++r) {           // the whole block builds each row slice: short dependent chains
+        const int m = m0 + r;
+        const float *xin = a.Xin + ((long long)m * a.hc + s) * a.SH;
+        float coef = 0.f;
+        if (a.pend) coef = 2.f * sigmoidf_(a.inj_prev[(long long)m * a.hc + s] / float(a.hc));
+        float ss = 0.f;
+        for (int c = threadIdx.x * 4; c < a.SH; c += 1024) {
+            float4 v = *reinterpret_cast<const float4 *>(xin + c);
+            if (a.pend) {
+                const float4 p = *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
+                v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
+                v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
+                if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.Xout + ((long long)m * a.hc + s) * a.SH + c) = v;
+            }
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            const float4 ww = *reinterpret_cast<const float4 *>(a.w1 + s * a.SH + c);
+            uint2 pk;
+            pk.x = pack_bf16(v.x * ww.x, v.y * ww.y);
+            pk.y = pack_bf16(v.z * ww.z, v.w * ww.w);
+            *reinterpret_cast<uint2 *>(ybuf + r * a.SH + c) = pk;
+        }
+        if (blockIdx.x == 0) {                 // block-uniform: only these blocks need the sum of squares
+            ss = block_sum<256>(ss, scratch);
+            if (threadIdx.x == 0) a.send[(long long)m * a.ld_send + s] = ss;
+        }
+    }
+    __syncthreads();
+    float acc[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+    if (j < a.down) {
+        for (int c0 = kw * 32 + lane, first = 1; c0 < nchunk; c0 += 4 * stride, first = 0) {
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * stride;
+                if (c < nchunk) w[u] = first ? w0[u] : ld_stream(reinterpret_cast<const uint4 *>(wrow) + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * stride;
+                if (c < nchunk) {
+#pragma unroll
+                    for (int m = 0; m < 8; ++m)
+                        if (m < nrow) acc[m] = dot8(w[u], *reinterpret_cast<const uint4 *>(ybuf + m * a.SH + c * 8), acc[m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m] = warp_sum(acc[m]);
+    if (wpr > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) part[warp][m] = acc[m];
+        }
+        __syncthreads();
+        if (kw == 0) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                float t = 0.f;
+                for (int q = 0; q < wpr; ++q) t += part[warp + q][m];
+                acc[m] = t;
+            }
+        }
+    }
+    if (kw == 0 && lane == 0 && j < a.down) {
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+            if (m < nrow) a.send[(long long)(m0 + m) * a.ld_send + a.hc + s * a.down + j] = acc[m];
     }
 }
 
@@ -134,13 +268,38 @@ QW_API int qwk_hc_pre(float *X, const float *pend, int ld_pend, const float *inj
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const void *y, int SH, int hc, int R, int n_inj,
-                         int H, float eps, int M, float *inj, int ld_inj, void *bin, int ld_bin, int bin_col0,
-                         cudaStream_t s) {
-    if (hc != 4 || (R & 7)) return -1;
+QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const float *X, const float *w1, int SH, int hc,
+                         int R, int n_inj, int H, float eps, int M, float *inj, int ld_inj, void *bin, int ld_bin,
+                         int bin_col0, cudaStream_t s) {
+    if (hc != 4 || (R & 7) || R > 8 * 8 * UP_MAXI) return -1;
     dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
     const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc);
-    hc_up_mix_kernel<<<grid, 256, smem, s>>>(red, ld_red, (const bf16 *)Wu, (const bf16 *)y, SH, hc, R, R + n_inj,
-                                             1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    cudaError_t e = launch_pdl(hc_up_mix_kernel, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
+                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0);
+    return e == cudaSuccess ? 0 : -2;
+}
+
+// Fused combine + sum of squares + down projection (see hc_down_kernel).  Xout == null keeps X in place.
+QW_API int qwk_hc_down(const float *Xin, float *Xout, const float *pend, int ld_pend, const float *inj_prev,
+                       const float *w1, const void *Wd, float *send, int ld_send, int SH, int hc, int down, int M,
+                       cudaStream_t s) {
+    if ((SH & 7) || (pend && !Xout)) return -1;
+    HcDownArgs a;
+    a.Xin = Xin; a.Xout = Xout; a.pend = pend; a.ld_pend = ld_pend; a.inj_prev = inj_prev; a.w1 = w1;
+    a.Wd = (const bf16 *)Wd; a.send = send; a.ld_send = ld_send; a.SH = SH; a.hc = hc; a.down = down; a.M = M;
+    const long long rows = (long long)down * hc;
+    a.wpr = rows >= NUM_SMS * 8 * 2 ? 1 : (rows >= NUM_SMS * 4 * 2 ? 2 : (rows >= NUM_SMS * 2 * 2 ? 4 : 8));
+    if ((SH >> 3) < a.wpr * 32) {          // short rows: do not spread a row over more warps than it has pieces
+        while (a.wpr > 1 && (SH >> 3) < a.wpr * 32) a.wpr >>= 1;
+    }
+    const int rpb = 8 / a.wpr;
+    dim3 grid((down + rpb - 1) / rpb, hc, (M + 7) / 8);
+    const size_t smem = (size_t)8 * SH * sizeof(bf16);
+    static bool attr_set = false;
+    if (!attr_set && smem > 48 * 1024) {
+        cudaFuncSetAttribute(hc_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr_set = true;
+    }
+    cudaError_t e = launch_pdl(hc_down_kernel, grid, dim3(256), smem, s, a);
+    return e == cudaSuccess ? 0 : -2;
 }

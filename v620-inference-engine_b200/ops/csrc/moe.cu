@@ -1,101 +1,143 @@
-// Decode-path MoE kernels: router (softmax, top-k by repeated argmax with ties to the lowest
-// index, renormalisation, expert-parallel filter), the shared expert's gated activation, and
-// the per-(row, expert) q4 matrix-vector products with the weighted combine fused into the down
-// projection (roles of the reference's src/kernels/moe_route.hip:65-224 and
-// src/kernels/moe_experts.hip:189-246).
-#include "common.cuh"
+// Decode-path MoE kernels.
+//   moe_router : one kernel = the router / shared-gate / shared gate-up matrix-vector product, and,
+//                in the block that finishes last, the routing itself (softmax, top-k by repeated
+//                argmax with ties to the lowest index, renormalisation, expert-parallel filter) and
+//                the shared expert's gated activation.
+//   moe_gate_up_pair / moe_down_combine : q4 matrix-vector products per (row, expert) pair, 32
+//                weights (16 bytes) per lane and load, all loads of a warp independent, with the
+//                weighted combine and the shared expert's down projection fused into the second.
+// (Roles of the reference's src/kernels/moe_route.hip:65-224 and src/kernels/moe_experts.hip:189-246.)
+#include "sgemv.cuh"
 
 namespace qw {
 
-constexpr int MAX_TOPK = 16;
-
-// One block per row.  Warp 0 routes; all threads then apply the shared expert's activation.
-// rs[m] = [ router logits (E) | shared gate logit (1) | shared gate rows (F) | shared up rows (F) ].
-__global__ void __launch_bounds__(256) moe_route_kernel(const float *rs, int ld_rs, int E, int top_k, int F, int e_first,
-                                                        int e_local, int *pair_expert, float *pair_w, bf16 *sh_h) {
-    const int m = blockIdx.x;
-    const float *l = rs + (long long)m * ld_rs;
-    const int lane = threadIdx.x & 31;
-    if (threadIdx.x < 32) {
-        float v[32];     // E <= 1024
-        float mx = -INFINITY;
+// Routing of row m from rs[m] = [ router logits (E) | shared gate logit | shared gate rows (F) | shared up rows (F) ].
+// One warp per row.
+__device__ __forceinline__ void route_row(const float *l, int E, int top_k, int e_first, int e_local, int *pair_expert,
+                                          float *pair_w, int lane) {
+    float v[32];     // E <= 1024
+    float mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int e = lane + 32 * i;
-            v[i] = e < E ? l[e] : -INFINITY;
-            mx = fmaxf(mx, v[i]);
+    for (int i = 0; i < 32; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < E ? __ldcg(l + e) : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;
+    float topsum = 0.f, mine_w = 0.f;
+    int mine_e = -1;
+    for (int j = 0; j < top_k; ++j) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {      // ascending index: strict > keeps the lowest index
+            if (v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
         }
-        mx = warp_max(mx);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;
-        float topsum = 0.f, mine_w = 0.f;
-        int mine_e = -1;
-        for (int j = 0; j < top_k; ++j) {
-            float bv = -1.f;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {      // ascending index: strict > keeps the lowest index
-                if (v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-            topsum += bv;
-            if (lane == j) { mine_e = bi; mine_w = bv; }
-            if ((bi & 31) == lane) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (i == (bi >> 5)) v[i] = -1.f;
-            }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (lane < top_k) {
-            const int loc = mine_e - e_first;
-            const bool local = loc >= 0 && loc < e_local;
-            pair_expert[m * top_k + lane] = local ? loc : -1;
-            pair_w[m * top_k + lane] = mine_w / topsum;
+        topsum += bv;
+        if (lane == j) { mine_e = bi; mine_w = bv; }
+        if ((bi & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i == (bi >> 5)) v[i] = -1.f;
         }
     }
-    if (sh_h) {
-        const float sg = sigmoidf_(l[E]);
-        for (int f = threadIdx.x; f < F; f += blockDim.x)
-            sh_h[(long long)m * F + f] = __float2bfloat16(siluf_(l[E + 1 + f]) * l[E + 1 + F + f] * sg);
+    if (lane < top_k) {
+        const int loc = mine_e - e_first;
+        const bool local = loc >= 0 && loc < e_local;
+        pair_expert[lane] = local ? loc : -1;
+        pair_w[lane] = mine_w / topsum;
     }
 }
 
-// integer dot of 16 q4 values (2 words) with 16 bf16 activations
-__device__ __forceinline__ float dot_q4x16(const uint2 w, const uint4 x0, const uint4 x1) {
+struct RouteArgs {
+    int E, top_k, F, e_first, e_local;
+    int *pair_expert;     // [M][top_k]
+    float *pair_w;
+    bf16 *sh_h;           // [M][F] or null
+    unsigned int *ticket; // zero before the launch; the last block resets it
+};
+
+__device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, const RouteArgs &r) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int m = warp; m < M; m += nw)
+        route_row(rs + (long long)m * ld_rs, r.E, r.top_k, r.e_first, r.e_local, r.pair_expert + m * r.top_k,
+                  r.pair_w + m * r.top_k, lane);
+    if (r.sh_h) {
+        for (int i = threadIdx.x; i < M * r.F; i += blockDim.x) {
+            const int m = i / r.F, f = i % r.F;
+            const float *l = rs + (long long)m * ld_rs;
+            const float sg = sigmoidf_(__ldcg(l + r.E));
+            r.sh_h[i] = __float2bfloat16(siluf_(__ldcg(l + r.E + 1 + f)) * __ldcg(l + r.E + 1 + r.F + f) * sg);
+        }
+    }
+}
+
+// Router GEMV (streaming kernel) with the routing done by the block that finishes last.
+template <int MT>
+__global__ void __launch_bounds__(256, 1) moe_router_kernel(SGemvArgs a, RouteArgs r) {
+    extern __shared__ __align__(128) unsigned char sg_smem[];
+    __shared__ unsigned int s_last;
+    sgemv_body<MT>(a, sg_smem);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(r.ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    route_all(a.y, a.ldy, a.M, r);
+    if (threadIdx.x == 0) *r.ticket = 0u;
+}
+
+template <int MT>
+static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t s) {
+    int grid;
+    const size_t smem = sgemv_plan(a, MT, grid);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(moe_router_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured = true;
+    }
+    return launch_pdl(moe_router_kernel<MT>, dim3(grid), dim3(256), smem, s, a, r);
+}
+
+// Stand-alone routing (tests, and callers that computed the logits elsewhere).  One block.
+__global__ void __launch_bounds__(256) moe_route_kernel(const float *rs, int ld_rs, int M, RouteArgs r) {
+    pdl_wait();
+    pdl_trigger();
+    route_all(rs, ld_rs, M, r);
+}
+
+// 32 q4 values (one 16-byte load, engine order) dot 32 bf16 activations.
+__device__ __forceinline__ float dot_q4x32(const uint4 w, const uint4 *x) {
     float a = 0.f, e0, e1;
-    q4_pair(w.x, 0, e0, e1); a = fmaf(e0, bf16_lo(x0.x), a); a = fmaf(e1, bf16_hi(x0.x), a);
-    q4_pair(w.x, 1, e0, e1); a = fmaf(e0, bf16_lo(x0.y), a); a = fmaf(e1, bf16_hi(x0.y), a);
-    q4_pair(w.x, 2, e0, e1); a = fmaf(e0, bf16_lo(x0.z), a); a = fmaf(e1, bf16_hi(x0.z), a);
-    q4_pair(w.x, 3, e0, e1); a = fmaf(e0, bf16_lo(x0.w), a); a = fmaf(e1, bf16_hi(x0.w), a);
-    q4_pair(w.y, 0, e0, e1); a = fmaf(e0, bf16_lo(x1.x), a); a = fmaf(e1, bf16_hi(x1.x), a);
-    q4_pair(w.y, 1, e0, e1); a = fmaf(e0, bf16_lo(x1.y), a); a = fmaf(e1, bf16_hi(x1.y), a);
-    q4_pair(w.y, 2, e0, e1); a = fmaf(e0, bf16_lo(x1.z), a); a = fmaf(e1, bf16_hi(x1.z), a);
-    q4_pair(w.y, 3, e0, e1); a = fmaf(e0, bf16_lo(x1.w), a); a = fmaf(e1, bf16_hi(x1.w), a);
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint4 xv = x[q];
+        q4_pair(ww[q], 0, e0, e1); a = fmaf(e0, bf16_lo(xv.x), a); a = fmaf(e1, bf16_hi(xv.x), a);
+        q4_pair(ww[q], 1, e0, e1); a = fmaf(e0, bf16_lo(xv.y), a); a = fmaf(e1, bf16_hi(xv.y), a);
+        q4_pair(ww[q], 2, e0, e1); a = fmaf(e0, bf16_lo(xv.z), a); a = fmaf(e1, bf16_hi(xv.z), a);
+        q4_pair(ww[q], 3, e0, e1); a = fmaf(e0, bf16_lo(xv.w), a); a = fmaf(e1, bf16_hi(xv.w), a);
+    }
     return a;
 }
 
-// q4 row (K values) dot bf16 activation row; lanes stride over 16-element pieces.
-__device__ __forceinline__ float q4_row_dot(const uint32_t *wrow, const bf16 *srow, const bf16 *x, int K, int lane) {
-    float acc = 0.f;
-    const int pieces = K >> 4;
-    for (int i = lane; i < pieces; i += 32) {
-        const uint2 w = ld_stream8(wrow + 2 * i);
-        const float sc = __bfloat162float(srow[i >> 3]);
-        const uint4 x0 = __ldg(reinterpret_cast<const uint4 *>(x) + 2 * i);
-        const uint4 x1 = __ldg(reinterpret_cast<const uint4 *>(x) + 2 * i + 1);
-        acc = fmaf(sc, dot_q4x16(w, x0, x1), acc);
-    }
-    return acc;
-}
+constexpr int GU_T = 5;      // 16-byte pieces per lane over the gate+up row pair: K <= 2560
+constexpr int DN_T = 8;      // pieces per lane over top_k down rows: top_k * F/32 <= 256
 
 // h[p][f] = silu(gate_e[f] . x_m) * (up_e[f] . x_m) for pair p = (m, j).  grid (ceil(F/8), pairs).
 __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w13, const bf16 *s13, const bf16 *x, int ldx,
                                                                const int *pair_expert, int top_k, int F, int K, bf16 *h) {
+    pdl_wait();
+    pdl_trigger();
     const int p = blockIdx.y;
     const int e = pair_expert[p];
     if (e < 0) return;
@@ -103,11 +145,35 @@ __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w
     const int f = blockIdx.x * 8 + warp;
     if (f >= F) return;
     const int m = p / top_k;
-    const long long rg = (long long)e * 2 * F + f, ru = rg + F;
-    const int kw = K >> 3, ks = K >> 7;
-    const bf16 *xr = x + (long long)m * ldx;
-    float g = q4_row_dot(w13 + rg * kw, s13 + rg * ks, xr, K, lane);
-    float u = q4_row_dot(w13 + ru * kw, s13 + ru * ks, xr, K, lane);
+    const int cpr = K >> 5;                    // 16-byte pieces per row
+    const int ks = K >> 7;
+    const long long rg = (long long)e * 2 * F + f;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + (long long)m * ldx);
+    uint4 w[GU_T];
+    float sc[GU_T];
+#pragma unroll
+    for (int t = 0; t < GU_T; ++t) {
+        const int i = lane + 32 * t;
+        if (i < 2 * cpr) {
+            const int up = i >= cpr, ch = up ? i - cpr : i;
+            const long long row = rg + (up ? F : 0);
+            w[t] = ld_stream(reinterpret_cast<const uint4 *>(w13 + row * (K >> 3)) + ch);
+            sc[t] = __bfloat162float(s13[row * ks + (ch >> 2)]);
+        }
+    }
+    float g = 0.f, u = 0.f;
+#pragma unroll
+    for (int t = 0; t < GU_T; ++t) {
+        const int i = lane + 32 * t;
+        if (i < 2 * cpr) {
+            const int up = i >= cpr, ch = up ? i - cpr : i;
+            uint4 xv[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xv[q] = __ldg(xr + ch * 4 + q);
+            const float d = sc[t] * dot_q4x32(w[t], xv);
+            if (up) u += d; else g += d;
+        }
+    }
     g = warp_sum(g);
     u = warp_sum(u);
     if (lane == 0) h[(long long)p * F + f] = __float2bfloat16(siluf_(g) * u);
@@ -121,22 +187,57 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
     const int m = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * 8 + warp;
+    // the shared expert's row does not depend on the routing: fetch it before waiting
+    uint4 sw[3];
+    const int sch = SF >> 3;
+    if (shared_down && c < H) {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+            if (lane + 32 * t < sch) sw[t] = ld_stream(reinterpret_cast<const uint4 *>(shared_down + (long long)c * ld_sd) + lane + 32 * t);
+    }
+    pdl_wait();
+    pdl_trigger();
     if (c >= H) return;
-    const int kw = F >> 3, ks = F >> 7;
+    const int cpr = F >> 5, ks = F >> 7;
+    const int total = top_k * cpr;
+    uint4 w[DN_T];
+    float sc[DN_T];
+#pragma unroll
+    for (int t = 0; t < DN_T; ++t) {
+        const int i = lane + 32 * t;
+        sc[t] = 0.f;
+        if (i < total) {
+            const int j = i / cpr, ch = i - j * cpr;
+            const int p = m * top_k + j;
+            const int e = pair_expert[p];
+            if (e >= 0) {
+                const long long r = (long long)e * H + c;
+                w[t] = ld_stream(reinterpret_cast<const uint4 *>(w2 + r * (F >> 3)) + ch);
+                sc[t] = __bfloat162float(s2[r * ks + (ch >> 2)]) * pair_w[p];
+            } else {
+                w[t] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);   // all zeros in q4
+            }
+        }
+    }
     float acc = 0.f;
-    for (int j = 0; j < top_k; ++j) {
-        const int p = m * top_k + j;
-        const int e = pair_expert[p];
-        if (e < 0) continue;
-        const long long r = (long long)e * H + c;
-        const float d = q4_row_dot(w2 + r * kw, s2 + r * ks, h + (long long)p * F, F, lane);
-        acc = fmaf(pair_w[p], d, acc);
+#pragma unroll
+    for (int t = 0; t < DN_T; ++t) {
+        const int i = lane + 32 * t;
+        if (i < total) {
+            const int j = i / cpr, ch = i - j * cpr;
+            const uint4 *hp = reinterpret_cast<const uint4 *>(h + (long long)(m * top_k + j) * F) + ch * 4;
+            uint4 xv[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xv[q] = __ldg(hp + q);
+            acc = fmaf(sc[t], dot_q4x32(w[t], xv), acc);
+        }
     }
     if (shared_down) {
-        const uint4 *wp = reinterpret_cast<const uint4 *>(shared_down + (long long)c * ld_sd);
         const uint4 *xp = reinterpret_cast<const uint4 *>(sh_h + (long long)m * SF);
         float a = 0.f;
-        for (int i = lane; i < (SF >> 3); i += 32) a = dot8(ld_stream(wp + i), __ldg(xp + i), a);
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+            if (lane + 32 * t < sch) a = dot8(sw[t], __ldg(xp + lane + 32 * t), a);
         acc += a;
     }
     acc = warp_sum(acc);
@@ -147,29 +248,55 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
 
 using namespace qw;
 
+static RouteArgs make_route(int E, int top_k, int F, int e_first, int e_local, int *pair_expert, float *pair_w,
+                            void *sh_h, unsigned int *ticket) {
+    RouteArgs r;
+    r.E = E; r.top_k = top_k; r.F = F; r.e_first = e_first; r.e_local = e_local;
+    r.pair_expert = pair_expert; r.pair_w = pair_w; r.sh_h = (bf16 *)sh_h; r.ticket = ticket;
+    return r;
+}
+
+// rs = Wrs . x, then routing + shared activation in the same launch.  `ticket` is one zeroed word.
+QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, int K, int M, int ldx, int E, int top_k,
+                          int F, int e_first, int e_local, int *pair_expert, float *pair_w, void *sh_h,
+                          unsigned int *ticket, cudaStream_t s) {
+    if (E > 1024 || top_k > 32 || (K & 7) || (ldx & 7)) return -1;
+    SGemvArgs a;
+    a.W = (const bf16 *)Wrs; a.x = (const bf16 *)x; a.y = rs; a.y_bf16 = nullptr;
+    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.err = g_err_ptr;
+    RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
+    cudaError_t e;
+    if (M == 1) e = launch_router<1>(a, r, s);
+    else if (M == 2) e = launch_router<2>(a, r, s);
+    else if (M <= 4) e = launch_router<4>(a, r, s);
+    else e = launch_router<8>(a, r, s);
+    return e == cudaSuccess ? 0 : -2;
+}
+
 QW_API int qwk_moe_route(const float *rs, int ld_rs, int M, int E, int top_k, int F, int e_first, int e_local,
                          int *pair_expert, float *pair_w, void *sh_h, cudaStream_t s) {
-    if (E > 1024 || top_k > 32 || top_k > MAX_TOPK) return -1;
-    moe_route_kernel<<<M, 256, 0, s>>>(rs, ld_rs, E, top_k, F, e_first, e_local, pair_expert, pair_w, (bf16 *)sh_h);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    if (E > 1024 || top_k > 32) return -1;
+    RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, nullptr);
+    cudaError_t e = launch_pdl(moe_route_kernel, dim3(1), dim3(256), 0, s, rs, ld_rs, M, r);
+    return e == cudaSuccess ? 0 : -2;
 }
 
 QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x, int ldx, const int *pair_expert, int M,
                                 int top_k, int F, int K, void *h, cudaStream_t s) {
-    if ((K & 127) || (ldx & 7)) return -1;
+    if ((K & 127) || (ldx & 7) || 2 * (K >> 5) > 32 * GU_T) return -1;
     dim3 grid((F + 7) / 8, M * top_k);
-    moe_gate_up_pair_kernel<<<grid, 256, 0, s>>>((const uint32_t *)w13, (const bf16 *)s13, (const bf16 *)x, ldx,
-                                                 pair_expert, top_k, F, K, (bf16 *)h);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    cudaError_t e = launch_pdl(moe_gate_up_pair_kernel, grid, dim3(256), 0, s, (const uint32_t *)w13, (const bf16 *)s13,
+                               (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h);
+    return e == cudaSuccess ? 0 : -2;
 }
 
 QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, const int *pair_expert,
                                 const float *pair_w, int M, int top_k, int F, int H, const void *shared_down, int ld_sd,
                                 const void *sh_h, int SF, float *out, int ldo, cudaStream_t s) {
-    if ((F & 127) || (SF & 7)) return -1;
+    if ((F & 127) || (SF & 7) || top_k * (F >> 5) > 32 * DN_T || (SF >> 3) > 96) return -1;
     dim3 grid((H + 7) / 8, M);
-    moe_down_combine_kernel<<<grid, 256, 0, s>>>((const uint32_t *)w2, (const bf16 *)s2, (const bf16 *)h, pair_expert,
-                                                 pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
-                                                 (const bf16 *)sh_h, SF, out, ldo);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    cudaError_t e = launch_pdl(moe_down_combine_kernel, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
+                               (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                               (const bf16 *)sh_h, SF, out, ldo);
+    return e == cudaSuccess ? 0 : -2;
 }

@@ -9,6 +9,17 @@
 #include "runtime.h"
 
 #include "kernels.h"
+#include "common.cuh"
+
+namespace qw {
+ErrorWord *g_err_ptr = nullptr;
+}
+
+// Registers the device error word (8 bytes, zeroed by the caller) that kernels with bounded waits report to.
+extern "C" __attribute__((visibility("default"))) int qwk_set_error_word(void *p) {
+    qw::g_err_ptr = (qw::ErrorWord *)p;
+    return 0;
+}
 
 namespace {
 
@@ -19,6 +30,7 @@ struct Ctx {
     int site;
     int err;
     long long launches;
+    float *X, *Xalt;     // current residual buffer and its ping-pong partner
 };
 
 long long g_last_launches = 0;   // kernels enqueued by the most recent qwrt_decode call
@@ -46,10 +58,14 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const QwBuffers &b = md.b;
     const int M = c.rows->M, ld = hc_send(d);
     const int down = d.hc_rank + w.n_inj;
-    QW_TRYN(1, qwk_hc_pre(b.X, pend, d.SH, inj_prev, d.hc, w.w1, d.SH, d.hc, b.y, b.send, ld, M, c.s));
-    // part[s][j] = Wd[j][s][:] . y[s][:]  -> send[m][hc + s*down + j]
-    QW_TRYN(1, qwk_gemv_bf16(w.Wd, b.y, b.send + d.hc, nullptr, down, d.SH, M, d.hc * d.SH, d.hc * d.SH, ld, 0, d.hc,
-                         d.SH, d.SH, down, c.s));
+    // fused: deferred combine (into the partner buffer) + sums of squares + down projection
+    QW_TRYN(1, qwk_hc_down(c.X, pend ? c.Xalt : nullptr, pend, d.SH, inj_prev, w.w1, w.Wd, b.send, ld, d.SH, d.hc, down, M,
+                           c.s));
+    if (pend) {
+        float *t = c.X;
+        c.X = c.Xalt;
+        c.Xalt = t;
+    }
     const float *red = b.send;
     if (d.ranks > 1) {
         comm(c, 0, b.send, b.red, M, ld);
@@ -57,7 +73,7 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     } else {
         ++c.site;
     }
-    QW_TRYN(1, qwk_hc_up_mix(red, ld, w.Wu, b.y, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
+    QW_TRYN(1, qwk_hc_up_mix(red, ld, w.Wu, c.X, w.w1, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
                          d.rank * d.SH, c.s));
     comm(c, 1, b.bin, b.bin, M, d.SH);
 }
@@ -70,13 +86,12 @@ void gdn_block(Ctx &c, const QwLayer &L, int flags) {
     const int M = r.M, gi = L.state_index;
     const int qkv_l = (2 * d.KL + d.VL) * 128;
     QW_TRYN(1, qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
-    QW_TRYN(2, qwk_gdn_conv(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, d.KL, d.VL, M, r.slot, r.pos,
-                        r.run_start, r.run_len, b.qkv, b.decay, b.beta, d.eps, c.s));
     float *save = nullptr;
     if ((flags & QWRT_SAVE_GDN) && b.gdn_save)
         save = b.gdn_save + (size_t)gi * d.max_rows * d.VL * 128 * 128;
-    QW_TRYN(1, qwk_gdn_scan(b.qkv, b.decay, b.beta, b.proj, d.proj_gdn, md.st.gdn_S[gi], save, L.gdn_norm, d.KL, d.VL, M,
-                        r.slot, r.pos, r.run_start, r.run_len, b.o, d.eps, c.s));
+    QW_TRYN((M <= 12 ? 1 : 3), qwk_gdn_step(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, L.gdn_norm,
+                                            d.KL, d.VL, M, r.slot, r.pos, r.run_start, r.run_len, md.st.gdn_S[gi], save,
+                                            b.qkv, b.decay, b.beta, b.o, d.eps, c.s));
     (void)qkv_l;
     const int K = d.VL * 128;
     QW_TRYN(1, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
@@ -111,8 +126,8 @@ void moe_block(Ctx &c, const QwLayer &L) {
     const QwBuffers &b = md.b;
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
-    QW_TRYN(1, qwk_gemv_bf16(L.Wrs, b.bin, b.rs, nullptr, nrs, d.H, M, d.H, d.H, nrs, 0, 1, 0, 0, 0, c.s));
-    QW_TRYN(1, qwk_moe_route(b.rs, nrs, M, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert, b.pair_w, b.sh_h, c.s));
+    QW_TRYN(1, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
+                              b.pair_w, b.sh_h, b.ticket, c.s));
     QW_TRYN(1, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
     QW_TRYN(1, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
                                 d.SF, b.partial, d.H, c.s));
@@ -140,7 +155,7 @@ void ple_block(Ctx &c) {
     QW_TRYN(1, qwk_ple_gather(r.ctx3, p.shards, p.scales, p.rows_per_shard, p.rows, p.layout, d.ngram_dim, d.ngram_heads,
                           b.ple_e, nullptr, M, c.s));
     QW_TRYN(1, qwk_gemv_bf16(p.Wkv, b.ple_e, b.ple_kv, nullptr, d.ple_kv, d.H, M, d.H, d.H, d.ple_kv, 0, 1, 0, 0, 0, c.s));
-    QW_TRYN(1, qwk_ple_stats(b.ple_kv, d.ple_kv, b.X, p.nk1, p.nq1, d.SH, d.hc, b.ple_send, 16, M, c.s));
+    QW_TRYN(1, qwk_ple_stats(b.ple_kv, d.ple_kv, c.X, p.nk1, p.nq1, d.SH, d.hc, b.ple_send, 16, M, c.s));
     const float *red = b.ple_send;
     if (d.ranks > 1) {
         comm(c, 0, b.ple_send, b.ple_red, M, 16);
@@ -149,14 +164,14 @@ void ple_block(Ctx &c) {
         ++c.site;
     }
     QW_TRYN(3, qwk_ple_apply(b.ple_kv, d.ple_kv, red, 16, p.nc1, p.cw, d.SH, d.hc, d.H, d.eps, d.ple_taps, d.ple_dil,
-                         b.ple_gv, b.ple_nc, md.st.ple_ring, b.X, M, r.slot, r.pos, r.run_start, r.run_len, c.s));
+                         b.ple_gv, b.ple_nc, md.st.ple_ring, c.X, M, r.slot, r.pos, r.run_start, r.run_len, c.s));
 }
 
 }  // namespace
 
 extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
                                                                    int n_layers_run, cudaStream_t stream) {
-    Ctx c{md, rows, stream, 0, 0, 0};
+    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2};
     const QwDims &d = md->d;
     const QwBuffers &b = md->b;
     const int M = rows->M;
@@ -168,7 +183,7 @@ extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel 
     for (int l = 0; l < n_layers_run; ++l) {
         const QwLayer &L = md->layers[l];
         if (l == d.ple_layer && md->ple.enabled) {
-            if (pend) QW_TRYN(1, qwk_hc_pre(b.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, stream));
+            if (pend) QW_TRYN(1, qwk_hc_pre(c.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, stream));
             pend = nullptr;
             ple_block(c);
         }
@@ -184,7 +199,7 @@ extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel 
     }
     mix(c, md->final_hc, pend, inj_mlp, nullptr);
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
-        cudaMemcpyAsync(b.hidden_out, b.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, stream);
+        cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, stream);
     if (!(flags & QWRT_NO_HEAD)) {
         QW_TRYN(1, qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
                              stream));

@@ -101,6 +101,8 @@ typedef struct QwBuffers {
     float *lse_max, *lse_sum;
     float *gdn_save;     // optional [n_gdn][rows][VL][128][128]
     float *hidden_out;   // optional [rows][hc][SH]: X after the last combine (MTP input)
+    float *X2;           // second residual buffer: a mixer with a deferred combine writes X here and the two swap
+    unsigned int *ticket;// one zeroed word for the router kernel's last-block election
 } QwBuffers;
 
 typedef struct QwRows {

@@ -38,7 +38,7 @@ class QwState(C.Structure):
 BUFFER_FIELDS = ("X", "y", "send", "red", "bin", "proj", "inj_a", "inj_b", "partial", "out_a", "out_b", "o",
                  "qkv", "decay", "beta", "q", "iq", "scores", "sel", "sel_n", "pm", "pl", "pacc", "rs",
                  "pair_expert", "pair_w", "sh_h", "moe_h", "ple_e", "ple_kv", "ple_send", "ple_red", "ple_gv",
-                 "ple_nc", "logits", "amax_val", "amax_idx", "lse_max", "lse_sum", "gdn_save", "hidden_out")
+                 "ple_nc", "logits", "amax_val", "amax_idx", "lse_max", "lse_sum", "gdn_save", "hidden_out", "X2", "ticket")
 
 
 class QwBuffers(C.Structure):
