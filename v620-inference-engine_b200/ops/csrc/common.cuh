@@ -156,6 +156,49 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 constexpr int NUM_SMS = 148;
 
+// ---- L2 prefetch plan ----------------------------------------------------------------------
+// Weights never depend on activations, so every kernel of the decode step starts by asking the L2
+// to fetch the weights of the kernels a few tens of MB *ahead* of it in launch order.  HBM then
+// streams continuously, decoupled from the chain of short dependent kernels, which find their
+// weights in L2.  The runtime computes the ranges (up to three per kernel) and hands them to the
+// next launcher through g_pf; a launcher copies g_pf into its kernel's arguments and clears it.
+struct PfArgs {
+    const char *p[3];
+    unsigned long long n[3];
+};
+extern PfArgs g_pf;          // host side: ranges for the next launch (all zero = none)
+inline PfArgs take_pf() {
+    PfArgs r = g_pf;
+    g_pf = PfArgs{};
+    return r;
+}
+
+__device__ __forceinline__ void l2_prefetch_bulk(const void *p, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// Every warp of the grid takes 8 KB pieces of the ranges round-robin; lane 0 issues the prefetch.
+__device__ __forceinline__ void pf_issue(const PfArgs &pf) {
+    if ((threadIdx.x & 31) != 0) return;
+    const unsigned CH = 8192;
+    const unsigned wpb = (blockDim.x * blockDim.y * blockDim.z) >> 5;
+    const unsigned long long bid = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    const unsigned long long gw = bid * wpb + ((threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z)) >> 5);
+    const unsigned long long nw = (unsigned long long)gridDim.x * gridDim.y * gridDim.z * wpb;
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+        const unsigned long long n = pf.n[r];
+        if (!n) continue;
+        const unsigned long long nch = (n + CH - 1) / CH;
+        for (unsigned long long i = gw; i < nch; i += nw) {
+            unsigned long long len = n - i * CH;
+            if (len > CH) len = CH;
+            len &= ~15ull;
+            if (len) l2_prefetch_bulk(pf.p[r] + i * CH, (unsigned)len);
+        }
+    }
+}
+
 // NeoX rotation angle tables: cos/sin for (pos, i) computed in double like the oracle.
 __device__ __forceinline__ void rope_cs(int pos, int i, int rope_dim, double theta, float &c, float &s) {
     double inv = pow(theta, -2.0 * double(i) / double(rope_dim));

@@ -165,6 +165,7 @@ struct GdnFusedArgs {
     float *S, *save;
     bf16 *o;
     float eps;
+    PfArgs pf;
 };
 
 __global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
@@ -187,6 +188,7 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) tap[k] = a.cw[ch * 4 + k];
     }
+    pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
     if (a.rows.run_start[m0] != m0) return;
@@ -317,7 +319,7 @@ QW_API int qwk_gdn_step(const float *proj, int ld_proj, float *ring, const float
         GdnFusedArgs a;
         a.proj = proj; a.ld_proj = ld_proj; a.ring = ring; a.cw = cw; a.A_log = A_log; a.dt_bias = dt_bias;
         a.norm_w = norm_w; a.KL = KL; a.VL = VL; a.rows = Rows{M, slot, pos, run_start, run_len};
-        a.S = S; a.save = save; a.o = (bf16 *)o; a.eps = eps;
+        a.S = S; a.save = save; a.o = (bf16 *)o; a.eps = eps; a.pf = take_pf();
         cudaError_t e = launch_pdl(gdn_fused_kernel, dim3(M, VL), dim3(512), 0, s, a);
         return e == cudaSuccess ? 0 : -2;
     }

@@ -20,22 +20,34 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(GemvArgs a) {
     gemv_body<MT>(a, part);
 }
 
-template <int MT>
-__global__ void __launch_bounds__(256, 1) sgemv_kernel(SGemvArgs a) {
+template <int NT>
+__global__ void __launch_bounds__(SG_THREADS, 1) sgemv_kernel(SGemvArgs a) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
-    sgemv_body<MT>(a, sg_smem);
+    sgemv_body<NT>(a, sg_smem);
 }
 
-template <int MT>
+constexpr size_t SG_SMEM_MAX = 224 * 1024;
+
+template <int NT>
+static cudaError_t launch_sgemv_nt(SGemvArgs &a, size_t smem, int grid, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(sgemv_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SG_SMEM_MAX);
+        configured = true;
+    }
+    return launch_pdl(sgemv_kernel<NT>, dim3(grid), dim3(SG_THREADS), smem, s, a);
+}
+
+// Up to 8 activation rows per pass, or 16 when they fit in shared memory next to the weight stages.
 static cudaError_t launch_sgemv(SGemvArgs &a, cudaStream_t s) {
     int grid;
-    const size_t smem = sgemv_plan(a, MT, grid);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaFuncSetAttribute(sgemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        configured = 200 * 1024;
+    if (a.M > 8) {
+        const size_t smem2 = sgemv_plan(a, 2, grid);
+        if (smem2 <= SG_SMEM_MAX) return launch_sgemv_nt<2>(a, smem2, grid, s);
     }
-    return launch_pdl(sgemv_kernel<MT>, dim3(grid), dim3(256), smem, s, a);
+    const size_t smem1 = sgemv_plan(a, 1, grid);
+    if (smem1 > SG_SMEM_MAX) return cudaErrorInvalidValue;
+    return launch_sgemv_nt<1>(a, smem1, grid, s);
 }
 
 }  // namespace qw
@@ -49,16 +61,12 @@ QW_API int qwk_gemv_bf16(const void *W, const void *x, float *y, void *y_bf16, i
                          cudaStream_t s) {
     if (N <= 0 || M <= 0) return 0;
     if ((K & 7) || (ldw & 7) || (ldx & 7)) return -1;
-    if (nsplit <= 1 && (size_t)K * 2 <= 16384) {
+    if (nsplit <= 1 && (K & 15) == 0 && (size_t)K * 2 <= 16384) {
         // the streaming kernel: bulk-async weight pipeline, one block per SM
         SGemvArgs g;
         g.W = (const bf16 *)W; g.x = (const bf16 *)x; g.y = y; g.y_bf16 = (bf16 *)y_bf16;
-        g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.err = g_err_ptr;
-        cudaError_t e;
-        if (M == 1) e = launch_sgemv<1>(g, s);
-        else if (M == 2) e = launch_sgemv<2>(g, s);
-        else if (M <= 4) e = launch_sgemv<4>(g, s);
-        else e = launch_sgemv<8>(g, s);
+        g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.err = g_err_ptr; g.pf = take_pf();
+        const cudaError_t e = launch_sgemv(g, s);
         return e == cudaSuccess ? 0 : -2;
     }
     GemvArgs a;

@@ -60,7 +60,7 @@ constexpr int UP_MAXI = 5;     // 16-byte weight pieces per lane: covers mixer r
 __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
                                                         const float *X, const float *w1, int SH, int hc, int R, int hc_down,
                                                         float inv_H, float eps, int M, float *inj, int ld_inj, bf16 *bin,
-                                                        int ld_bin, int bin_col0) {
+                                                        int ld_bin, int bin_col0, PfArgs pf) {
     extern __shared__ float sm[];
     float *u = sm;                         // [UP_ROWS][R]
     float *rs = sm + UP_ROWS * R;          // [UP_ROWS][hc]
@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         for (int i = 0; i < UP_MAXI; ++i)
             if (li + 8 * i < nch) w[i] = ld_stream(wp + li + 8 * i);
     }
+    pf_issue(pf);
     pdl_wait();
     pdl_trigger();
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
@@ -152,6 +153,7 @@ struct HcDownArgs {
     const bf16 *Wd;         // [down][hc][SH]
     float *send;            // [M][ld_send]
     int ld_send, SH, hc, down, M, wpr;
+    PfArgs pf;
 };
 
 __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
@@ -176,6 +178,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
             if (c < nchunk) w0[u] = ld_stream(reinterpret_cast<const uint4 *>(wrow) + c);
         }
     }
+    pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
     for (int r = 0; r < nrow; ++r) {           // the whole block builds each row slice: short dependent chains
@@ -275,7 +278,7 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
     dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
     const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc);
     cudaError_t e = launch_pdl(hc_up_mix_kernel, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0);
+                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf());
     return e == cudaSuccess ? 0 : -2;
 }
 
@@ -286,7 +289,7 @@ QW_API int qwk_hc_down(const float *Xin, float *Xout, const float *pend, int ld_
     if ((SH & 7) || (pend && !Xout)) return -1;
     HcDownArgs a;
     a.Xin = Xin; a.Xout = Xout; a.pend = pend; a.ld_pend = ld_pend; a.inj_prev = inj_prev; a.w1 = w1;
-    a.Wd = (const bf16 *)Wd; a.send = send; a.ld_send = ld_send; a.SH = SH; a.hc = hc; a.down = down; a.M = M;
+    a.Wd = (const bf16 *)Wd; a.send = send; a.ld_send = ld_send; a.SH = SH; a.hc = hc; a.down = down; a.M = M; a.pf = take_pf();
     const long long rows = (long long)down * hc;
     a.wpr = rows >= NUM_SMS * 8 * 2 ? 1 : (rows >= NUM_SMS * 4 * 2 ? 2 : (rows >= NUM_SMS * 2 * 2 ? 4 : 8));
     if ((SH >> 3) < a.wpr * 32) {          // short rows: do not spread a row over more warps than it has pieces

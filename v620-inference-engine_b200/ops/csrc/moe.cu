@@ -63,6 +63,10 @@ struct RouteArgs {
     float *pair_w;
     bf16 *sh_h;           // [M][F] or null
     unsigned int *ticket; // zero before the launch; the last block resets it
+    // expert weights, so the block that routes can pull the chosen experts into L2 right away
+    const char *w13, *w2;
+    unsigned long long w13_bytes, w2_bytes;     // per expert
+    int prefetch_rows;                           // rows (from 0) whose experts are prefetched
 };
 
 __device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, const RouteArgs &r) {
@@ -81,11 +85,11 @@ __device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, con
 }
 
 // Router GEMV (streaming kernel) with the routing done by the block that finishes last.
-template <int MT>
-__global__ void __launch_bounds__(256, 1) moe_router_kernel(SGemvArgs a, RouteArgs r) {
+template <int NT>
+__global__ void __launch_bounds__(SG_THREADS, 1) moe_router_kernel(SGemvArgs a, RouteArgs r) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
     __shared__ unsigned int s_last;
-    sgemv_body<MT>(a, sg_smem);
+    sgemv_body<NT>(a, sg_smem);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = atomicAdd(r.ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
@@ -96,16 +100,24 @@ __global__ void __launch_bounds__(256, 1) moe_router_kernel(SGemvArgs a, RouteAr
     if (threadIdx.x == 0) *r.ticket = 0u;
 }
 
-template <int MT>
-static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t s) {
-    int grid;
-    const size_t smem = sgemv_plan(a, MT, grid);
+template <int NT>
+static cudaError_t launch_router_nt(SGemvArgs &a, const RouteArgs &r, size_t smem, int grid, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(moe_router_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(moe_router_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         configured = true;
     }
-    return launch_pdl(moe_router_kernel<MT>, dim3(grid), dim3(256), smem, s, a, r);
+    return launch_pdl(moe_router_kernel<NT>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
+}
+
+static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t s) {
+    int grid;
+    if (a.M > 8) {
+        const size_t smem2 = sgemv_plan(a, 2, grid);
+        if (smem2 <= 224 * 1024) return launch_router_nt<2>(a, r, smem2, grid, s);
+    }
+    const size_t smem1 = sgemv_plan(a, 1, grid);
+    return launch_router_nt<1>(a, r, smem1, grid, s);
 }
 
 // Stand-alone routing (tests, and callers that computed the logits elsewhere).  One block.
@@ -135,7 +147,8 @@ constexpr int DN_T = 8;      // pieces per lane over top_k down rows: top_k * F/
 
 // h[p][f] = silu(gate_e[f] . x_m) * (up_e[f] . x_m) for pair p = (m, j).  grid (ceil(F/8), pairs).
 __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w13, const bf16 *s13, const bf16 *x, int ldx,
-                                                               const int *pair_expert, int top_k, int F, int K, bf16 *h) {
+                                                               const int *pair_expert, int top_k, int F, int K, bf16 *h, PfArgs pf) {
+    pf_issue(pf);
     pdl_wait();
     pdl_trigger();
     const int p = blockIdx.y;
@@ -183,7 +196,8 @@ __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w
 __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w2, const bf16 *s2, const bf16 *h,
                                                                const int *pair_expert, const float *pair_w, int top_k,
                                                                int F, int H, const bf16 *shared_down, int ld_sd,
-                                                               const bf16 *sh_h, int SF, float *out, int ldo) {
+                                                               const bf16 *sh_h, int SF, float *out, int ldo, PfArgs pf) {
+    pf_issue(pf);
     const int m = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * 8 + warp;
@@ -253,23 +267,23 @@ static RouteArgs make_route(int E, int top_k, int F, int e_first, int e_local, i
     RouteArgs r;
     r.E = E; r.top_k = top_k; r.F = F; r.e_first = e_first; r.e_local = e_local;
     r.pair_expert = pair_expert; r.pair_w = pair_w; r.sh_h = (bf16 *)sh_h; r.ticket = ticket;
+    r.w13 = r.w2 = nullptr; r.w13_bytes = r.w2_bytes = 0; r.prefetch_rows = 0;
     return r;
 }
 
 // rs = Wrs . x, then routing + shared activation in the same launch.  `ticket` is one zeroed word.
 QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, int K, int M, int ldx, int E, int top_k,
                           int F, int e_first, int e_local, int *pair_expert, float *pair_w, void *sh_h,
-                          unsigned int *ticket, cudaStream_t s) {
-    if (E > 1024 || top_k > 32 || (K & 7) || (ldx & 7)) return -1;
+                          unsigned int *ticket, const void *w13, const void *w2, long long w13_bytes, long long w2_bytes,
+                          cudaStream_t s) {
+    if (E > 1024 || top_k > 32 || (K & 15) || (ldx & 7)) return -1;
     SGemvArgs a;
     a.W = (const bf16 *)Wrs; a.x = (const bf16 *)x; a.y = rs; a.y_bf16 = nullptr;
-    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.err = g_err_ptr;
+    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.err = g_err_ptr; a.pf = take_pf();
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
-    cudaError_t e;
-    if (M == 1) e = launch_router<1>(a, r, s);
-    else if (M == 2) e = launch_router<2>(a, r, s);
-    else if (M <= 4) e = launch_router<4>(a, r, s);
-    else e = launch_router<8>(a, r, s);
+    r.w13 = (const char *)w13; r.w2 = (const char *)w2; r.w13_bytes = w13_bytes; r.w2_bytes = w2_bytes;
+    r.prefetch_rows = 0;       // one block cannot pull 24 MB through its copy engine fast enough: measured 2x slower; kept off
+    const cudaError_t e = launch_router(a, r, s);
     return e == cudaSuccess ? 0 : -2;
 }
 
@@ -286,7 +300,7 @@ QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x,
     if ((K & 127) || (ldx & 7) || 2 * (K >> 5) > 32 * GU_T) return -1;
     dim3 grid((F + 7) / 8, M * top_k);
     cudaError_t e = launch_pdl(moe_gate_up_pair_kernel, grid, dim3(256), 0, s, (const uint32_t *)w13, (const bf16 *)s13,
-                               (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h);
+                               (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf());
     return e == cudaSuccess ? 0 : -2;
 }
 
@@ -297,6 +311,6 @@ QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, c
     dim3 grid((H + 7) / 8, M);
     cudaError_t e = launch_pdl(moe_down_combine_kernel, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
                                (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
-                               (const bf16 *)sh_h, SF, out, ldo);
+                               (const bf16 *)sh_h, SF, out, ldo, take_pf());
     return e == cudaSuccess ? 0 : -2;
 }

@@ -11,8 +11,11 @@
 #include "kernels.h"
 #include "common.cuh"
 
+#include <vector>
+
 namespace qw {
 ErrorWord *g_err_ptr = nullptr;
+PfArgs g_pf = {};
 }
 
 // Registers the device error word (8 bytes, zeroed by the caller) that kernels with bounded waits report to.
@@ -23,6 +26,11 @@ extern "C" __attribute__((visibility("default"))) int qwk_set_error_word(void *p
 
 namespace {
 
+struct WRange {
+    const char *p;
+    size_t n;
+};
+
 struct Ctx {
     const QwModel *md;
     const QwRows *rows;
@@ -31,16 +39,38 @@ struct Ctx {
     int err;
     long long launches;
     float *X, *Xalt;     // current residual buffer and its ping-pong partner
+    // L2 prefetch planning: a dry walk records the weights of every prefetch-capable launch in
+    // order; the real walk hands launch k the ranges plan[k]
+    bool dry;
+    int op;
+    std::vector<WRange> *ops;
+    const std::vector<qw::PfArgs> *plan;
 };
 
-long long g_last_launches = 0;   // kernels enqueued by the most recent qwrt_decode call
+long long g_last_launches = 0;
+int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the L2 prefetch front is kept; 0 = off (measured: no gain on B200)   // kernels enqueued by the most recent qwrt_decode call
 
 // Runs a launcher that enqueues `n` kernels; remembers the first failure and counts the launches.
 #define QW_TRYN(n, expr)                   \
     do {                                   \
-        int rc__ = (expr);                 \
-        c.launches += (n);                 \
-        if (rc__ != 0 && c.err == 0) c.err = rc__ * 1000 - __LINE__; \
+        if (!c.dry) {                      \
+            int rc__ = (expr);             \
+            c.launches += (n);             \
+            if (rc__ != 0 && c.err == 0) c.err = rc__ * 1000 - __LINE__; \
+        }                                  \
+    } while (0)
+
+// A launch whose kernel issues L2 prefetches for later kernels; `wptr`/`wbytes` are the weights it reads.
+#define QW_OP(n, wptr, wbytes, expr)                                              \
+    do {                                                                          \
+        if (c.dry) {                                                              \
+            c.ops->push_back(WRange{(const char *)(wptr), (size_t)(wbytes)});     \
+        } else {                                                                  \
+            if (c.plan && c.op < (int)c.plan->size()) qw::g_pf = (*c.plan)[c.op]; \
+            ++c.op;                                                               \
+            QW_TRYN(n, expr);                                                     \
+            qw::g_pf = qw::PfArgs{};                                              \
+        }                                                                         \
     } while (0)
 
 inline int hc_send(const QwDims &d) { return d.hc + d.hc * (d.hc_rank + d.hc); }
@@ -48,6 +78,7 @@ inline int hc_send(const QwDims &d) { return d.hc + d.hc * (d.hc_rank + d.hc); }
 void comm(Ctx &c, int kind, const void *src, void *dst, int rows, int n) {
     const QwModel &md = *c.md;
     ++c.site;
+    if (c.dry) return;
     if (md.d.ranks > 1 && md.comm) md.comm(md.comm_user, kind, c.site, src, dst, rows, n, c.s);
 }
 
@@ -59,8 +90,8 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const int M = c.rows->M, ld = hc_send(d);
     const int down = d.hc_rank + w.n_inj;
     // fused: deferred combine (into the partner buffer) + sums of squares + down projection
-    QW_TRYN(1, qwk_hc_down(c.X, pend ? c.Xalt : nullptr, pend, d.SH, inj_prev, w.w1, w.Wd, b.send, ld, d.SH, d.hc, down, M,
-                           c.s));
+    QW_OP(1, w.Wd, (size_t)down * d.hc * d.SH * 2,
+          qwk_hc_down(c.X, pend ? c.Xalt : nullptr, pend, d.SH, inj_prev, w.w1, w.Wd, b.send, ld, d.SH, d.hc, down, M, c.s));
     if (pend) {
         float *t = c.X;
         c.X = c.Xalt;
@@ -73,8 +104,9 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     } else {
         ++c.site;
     }
-    QW_TRYN(1, qwk_hc_up_mix(red, ld, w.Wu, c.X, w.w1, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
-                         d.rank * d.SH, c.s));
+    QW_OP(1, w.Wu, (size_t)d.SH * d.hc * d.hc_rank * 2,
+          qwk_hc_up_mix(red, ld, w.Wu, c.X, w.w1, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
+                        d.rank * d.SH, c.s));
     comm(c, 1, b.bin, b.bin, M, d.SH);
 }
 
@@ -85,16 +117,23 @@ void gdn_block(Ctx &c, const QwLayer &L, int flags) {
     const QwRows &r = *c.rows;
     const int M = r.M, gi = L.state_index;
     const int qkv_l = (2 * d.KL + d.VL) * 128;
-    QW_TRYN(1, qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, L.Wproj, (size_t)d.proj_gdn * d.H * 2,
+          qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
     float *save = nullptr;
     if ((flags & QWRT_SAVE_GDN) && b.gdn_save)
         save = b.gdn_save + (size_t)gi * d.max_rows * d.VL * 128 * 128;
-    QW_TRYN((M <= 12 ? 1 : 3), qwk_gdn_step(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, L.gdn_norm,
+    if (M <= 12) {
+        QW_OP(1, nullptr, 0, qwk_gdn_step(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, L.gdn_norm,
                                             d.KL, d.VL, M, r.slot, r.pos, r.run_start, r.run_len, md.st.gdn_S[gi], save,
                                             b.qkv, b.decay, b.beta, b.o, d.eps, c.s));
+    } else {
+        QW_TRYN(3, qwk_gdn_step(b.proj, d.proj_gdn, md.st.gdn_ring[gi], L.cw, L.A_log, L.dt_bias, L.gdn_norm,
+                                            d.KL, d.VL, M, r.slot, r.pos, r.run_start, r.run_len, md.st.gdn_S[gi], save,
+                                            b.qkv, b.decay, b.beta, b.o, d.eps, c.s));
+    }
     (void)qkv_l;
     const int K = d.VL * 128;
-    QW_TRYN(1, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, L.Wout, (size_t)d.H * K * 2, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
 void qsa_block(Ctx &c, const QwLayer &L) {
@@ -104,7 +143,8 @@ void qsa_block(Ctx &c, const QwLayer &L) {
     const QwRows &r = *c.rows;
     const QwState &st = md.st;
     const int M = r.M, qi = L.state_index;
-    QW_TRYN(1, qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_qsa, d.H, M, d.H, d.H, d.proj_qsa, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, L.Wproj, (size_t)d.proj_qsa * d.H * 2,
+          qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_qsa, d.H, M, d.H, d.H, d.proj_qsa, 0, 1, 0, 0, 0, c.s));
     QW_TRYN((M <= 16 - d.idx_ratio ? 1 : 2), qwk_qsa_prep(b.proj, d.proj_qsa, d.QL, d.KVL, d.IH, L.qn1, L.kn1, L.iqn1, L.ikn1, M, r.slot, r.pos,
                         r.run_start, r.run_len, st.k_dev[qi], st.v_dev[qi], st.k_host ? st.k_host[qi] : nullptr,
                         st.v_host ? st.v_host[qi] : nullptr, d.n_dev_pages, st.page_table, d.max_pages, b.q, b.iq,
@@ -117,7 +157,7 @@ void qsa_block(Ctx &c, const QwLayer &L) {
                           st.page_table, d.max_pages, b.sel, b.sel_n, d.idx_topk, d.idx_ratio, d.nsplit, b.pm, b.pl,
                           b.pacc, b.proj, d.proj_qsa, b.o, c.s));
     const int K = d.QL * 256;
-    QW_TRYN(1, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, L.Wout, (size_t)d.H * K * 2, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
 void moe_block(Ctx &c, const QwLayer &L) {
@@ -126,10 +166,10 @@ void moe_block(Ctx &c, const QwLayer &L) {
     const QwBuffers &b = md.b;
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
-    QW_TRYN(1, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
-                              b.pair_w, b.sh_h, b.ticket, c.s));
-    QW_TRYN(1, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
-    QW_TRYN(1, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
+    QW_OP(1, L.Wrs, (size_t)nrs * d.H * 2, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
+                              b.pair_w, b.sh_h, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
+    QW_OP(1, nullptr, 0, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
+    QW_OP(1, L.Wsd, (size_t)d.H * d.SF * 2, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
                                 d.SF, b.partial, d.H, c.s));
 }
 
@@ -154,7 +194,8 @@ void ple_block(Ctx &c) {
     const int M = r.M;
     QW_TRYN(1, qwk_ple_gather(r.ctx3, p.shards, p.scales, p.rows_per_shard, p.rows, p.layout, d.ngram_dim, d.ngram_heads,
                           b.ple_e, nullptr, M, c.s));
-    QW_TRYN(1, qwk_gemv_bf16(p.Wkv, b.ple_e, b.ple_kv, nullptr, d.ple_kv, d.H, M, d.H, d.H, d.ple_kv, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, p.Wkv, (size_t)d.ple_kv * d.H * 2,
+          qwk_gemv_bf16(p.Wkv, b.ple_e, b.ple_kv, nullptr, d.ple_kv, d.H, M, d.H, d.H, d.ple_kv, 0, 1, 0, 0, 0, c.s));
     QW_TRYN(1, qwk_ple_stats(b.ple_kv, d.ple_kv, c.X, p.nk1, p.nq1, d.SH, d.hc, b.ple_send, 16, M, c.s));
     const float *red = b.ple_send;
     if (d.ranks > 1) {
@@ -169,21 +210,24 @@ void ple_block(Ctx &c) {
 
 }  // namespace
 
-extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
-                                                                   int n_layers_run, cudaStream_t stream) {
-    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2};
+// The launch sequence of one step.  With c.dry it only records the weights of the prefetch-capable
+// launches; otherwise it enqueues the kernels.
+static void walk(Ctx &c, int flags, int n_layers_run) {
+    const QwModel *md = c.md;
     const QwDims &d = md->d;
     const QwBuffers &b = md->b;
-    const int M = rows->M;
-    if (M < 1 || M > d.max_rows) return -1;
-    if (n_layers_run < 0 || n_layers_run > d.n_layers) n_layers_run = d.n_layers;
-    QW_TRYN(1, qwk_embed_rows(rows->tokens, md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, stream));
+    const int M = c.rows->M;
+    c.X = b.X;
+    c.Xalt = b.X2;
+    c.site = 0;
+    c.op = 0;
+    QW_TRYN(1, qwk_embed_rows(c.rows->tokens, c.md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, c.s));
     const float *pend = nullptr;
     float *inj_attn = b.inj_a, *inj_mlp = b.inj_b;
     for (int l = 0; l < n_layers_run; ++l) {
-        const QwLayer &L = md->layers[l];
-        if (l == d.ple_layer && md->ple.enabled) {
-            if (pend) QW_TRYN(1, qwk_hc_pre(c.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, stream));
+        const QwLayer &L = c.md->layers[l];
+        if (l == d.ple_layer && c.md->ple.enabled) {
+            if (pend) QW_TRYN(1, qwk_hc_pre(c.X, pend, d.SH, inj_mlp, d.hc, nullptr, d.SH, d.hc, nullptr, nullptr, 0, M, c.s));
             pend = nullptr;
             ple_block(c);
         }
@@ -197,21 +241,78 @@ extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel 
         // before anything overwrites `partial`, so with one rank it can be used in place.
         pend = scatter(c, b.out_b);
     }
-    mix(c, md->final_hc, pend, inj_mlp, nullptr);
+    mix(c, c.md->final_hc, pend, inj_mlp, nullptr);
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
-        cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, stream);
+        if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
     if (!(flags & QWRT_NO_HEAD)) {
-        QW_TRYN(1, qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
-                             stream));
+        QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
+                             c.s));
         QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
-                              b.lse_sum, stream));
+                              b.lse_sum, c.s));
         if ((flags & QWRT_CHAIN) && d.ranks == 1)
-            QW_TRYN(1, qwk_advance_rows(const_cast<int *>(rows->tokens), const_cast<int *>(rows->pos),
-                                    const_cast<int *>(rows->ctx3), b.amax_idx, M, stream));
+            QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
+                                    const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
     }
+}
+
+// Ranges of later kernels' weights that launch k asks the L2 to fetch: the plan keeps the prefetch
+// front `lookahead` bytes past the end of launch k's own weights.
+static void make_plan(const std::vector<WRange> &ops, size_t lookahead, std::vector<qw::PfArgs> &plan) {
+    const int n = (int)ops.size();
+    std::vector<size_t> cum(n + 1, 0);
+    for (int k = 0; k < n; ++k) cum[k + 1] = cum[k] + ops[k].n;
+    plan.assign(n, qw::PfArgs{});
+    size_t issued = n ? cum[1] : 0;
+    for (int k = 0; k < n; ++k) {
+        if (issued < cum[k + 1]) issued = cum[k + 1];
+        const size_t target = cum[k + 1] + lookahead < cum[n] ? cum[k + 1] + lookahead : cum[n];
+        int r = 0;
+        while (issued < target && r < 3) {
+            int j = k + 1;
+            while (j < n && cum[j + 1] <= issued) ++j;      // the launch whose weights contain `issued`
+            if (j >= n) break;
+            const size_t off = issued - cum[j];
+            size_t len = ops[j].n - off;
+            if (issued + len > target) len = target - issued;
+            len &= ~(size_t)15;
+            if (!len) { issued = cum[j + 1]; continue; }
+            plan[k].p[r] = ops[j].p + off;
+            plan[k].n[r] = len;
+            issued += len;
+            ++r;
+        }
+    }
+}
+
+extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
+                                                                   int n_layers_run, cudaStream_t stream) {
+    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2, false, 0, nullptr, nullptr};
+    const QwDims &d = md->d;
+    const QwBuffers &b = md->b;
+    const int M = rows->M;
+    if (M < 1 || M > d.max_rows) return -1;
+    if (n_layers_run < 0 || n_layers_run > d.n_layers) n_layers_run = d.n_layers;
+    // dry walk -> weight list -> prefetch plan -> real walk
+    std::vector<WRange> ops;
+    std::vector<qw::PfArgs> plan;
+    ops.reserve(1024);
+    c.dry = true;
+    c.ops = &ops;
+    walk(c, flags, n_layers_run);
+    make_plan(ops, (size_t)g_lookahead_mb << 20, plan);
+    c.dry = false;
+    c.plan = &plan;
+    c.launches = 0;
+    walk(c, flags, n_layers_run);
     g_last_launches = c.launches;
     return c.err;
 }
 
 // Kernels enqueued by the most recent qwrt_decode call (what one replay of its graph launches).
+// Sets the prefetch distance in MB (0 disables L2 prefetching).
+extern "C" __attribute__((visibility("default"))) int qwrt_set_lookahead_mb(int mb) {
+    g_lookahead_mb = mb < 0 ? 0 : mb;
+    return 0;
+}
+
 extern "C" __attribute__((visibility("default"))) long long qwrt_last_launches() { return g_last_launches; }
