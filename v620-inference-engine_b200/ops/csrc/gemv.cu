@@ -26,8 +26,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) sgemv_kernel(SGemvArgs a) {
     sgemv_body<NT>(a, sg_smem);
 }
 
-constexpr size_t SG_SMEM_MAX = 224 * 1024;
-
 template <int NT>
 static cudaError_t launch_sgemv_nt(SGemvArgs &a, size_t smem, int grid, cudaStream_t s) {
     static bool configured = false;
@@ -43,10 +41,10 @@ static cudaError_t launch_sgemv(SGemvArgs &a, cudaStream_t s) {
     int grid;
     if (a.M > 8) {
         const size_t smem2 = sgemv_plan(a, 2, grid);
-        if (smem2 <= SG_SMEM_MAX) return launch_sgemv_nt<2>(a, smem2, grid, s);
+        if (smem2) return launch_sgemv_nt<2>(a, smem2, grid, s);
     }
     const size_t smem1 = sgemv_plan(a, 1, grid);
-    if (smem1 > SG_SMEM_MAX) return cudaErrorInvalidValue;
+    if (!smem1) return cudaErrorInvalidValue;
     return launch_sgemv_nt<1>(a, smem1, grid, s);
 }
 
@@ -65,7 +63,7 @@ QW_API int qwk_gemv_bf16(const void *W, const void *x, float *y, void *y_bf16, i
         // the streaming kernel: bulk-async weight pipeline, one block per SM
         SGemvArgs g;
         g.W = (const bf16 *)W; g.x = (const bf16 *)x; g.y = y; g.y_bf16 = (bf16 *)y_bf16;
-        g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.err = g_err_ptr; g.pf = take_pf();
+        g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.nsplit = 1; g.w_split = 0; g.err = g_err_ptr; g.pf = take_pf();
         const cudaError_t e = launch_sgemv(g, s);
         return e == cudaSuccess ? 0 : -2;
     }

@@ -114,7 +114,7 @@ static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t 
     int grid;
     if (a.M > 8) {
         const size_t smem2 = sgemv_plan(a, 2, grid);
-        if (smem2 <= 224 * 1024) return launch_router_nt<2>(a, r, smem2, grid, s);
+        if (smem2) return launch_router_nt<2>(a, r, smem2, grid, s);
     }
     const size_t smem1 = sgemv_plan(a, 1, grid);
     return launch_router_nt<1>(a, r, smem1, grid, s);
@@ -279,7 +279,7 @@ QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, in
     if (E > 1024 || top_k > 32 || (K & 15) || (ldx & 7)) return -1;
     SGemvArgs a;
     a.W = (const bf16 *)Wrs; a.x = (const bf16 *)x; a.y = rs; a.y_bf16 = nullptr;
-    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.err = g_err_ptr; a.pf = take_pf();
+    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.nsplit = 1; a.w_split = 0; a.err = g_err_ptr; a.pf = take_pf();
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
     r.w13 = (const char *)w13; r.w2 = (const char *)w2; r.w13_bytes = w13_bytes; r.w2_bytes = w2_bytes;
     r.prefetch_rows = 0;       // one block cannot pull 24 MB through its copy engine fast enough: measured 2x slower; kept off
