@@ -120,3 +120,33 @@ def test_full_shape_slice_logits():
     want = ref.forward(st, toks, all_logits=True)
     got = run_seq(dm, cfg, toks, batch=4).cpu()
     assert rel(got, want) < 3e-2
+
+
+def test_row_batched_prefill_and_chained_decode_match_stepwise():
+    """32-row prefill steps and the device-fed chained decode against one-token steps."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.models.ple import PleTable
+    from qwb200.models.weights import synth_weights
+    cfg = ModelConfig.tiny()
+    w = synth_weights(cfg, seed=9)
+    table = PleTable.synthetic(cfg, rows=4096, layout="f8", seed=9)
+    toks = torch.randint(0, cfg.vocab, (75,), generator=torch.Generator().manual_seed(2)).tolist()
+    a = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=False))
+    t, want = None, []
+    for x in toks:
+        t = a.decode([0], [x])[0]
+    last_logits = a.dm.buf["logits"][0].clone()
+    for _ in range(10):
+        want.append(t)
+        t = a.decode([0], [t])[0]
+    b = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=True))
+    lg = b.prefill(0, toks)
+    torch.cuda.synchronize()
+    assert rel(lg.cpu(), last_logits.cpu()) < 2e-2
+    first = int(b.dm.buf["amax_idx"][(len(toks) - 1) % 32])
+    assert first == want[0]
+    got = [first] + b.decode_chain(0, first, 9)
+    assert got == want
+    got2 = b.decode_chain(0, got[-1], 3)          # second call replays the captured graph from the start
+    assert got2[0] == t                          # `t` is what the stepwise engine produced after want[-1]

@@ -165,8 +165,11 @@ class DeviceModel:
 
     def _alloc_rows(self):
         R = self.max_rows
-        self.rows_host = torch.zeros(8 * R, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else \
-            torch.zeros(8 * R, dtype=torch.int32)
+        # ring of pinned staging buffers: a buffer is refilled only after the copy that read it has run
+        self.rows_ring = [torch.zeros(8 * R, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self.rows_events = [None] * 4
+        self.rows_turn = 0
+        self.rows_host = self.rows_ring[0]
         self.rows_dev = torch.zeros(8 * R, dtype=torch.int32, device=self.dev)
         self.rows = S.QwRows()
         base = self.rows_dev.data_ptr()
@@ -279,6 +282,10 @@ class DeviceModel:
         """Fill the row tables (pinned host) and enqueue their copy to the device."""
         M, R = len(tokens), self.max_rows
         assert 1 <= M <= R
+        turn = self.rows_turn = (self.rows_turn + 1) % len(self.rows_ring)
+        if self.rows_events[turn] is not None:
+            self.rows_events[turn].synchronize()
+        self.rows_host = self.rows_ring[turn]
         h = self.rows_host.numpy()
         h[0:M] = [self.cfg.real_token(int(t)) for t in tokens]
         h[R:R + M] = slots
@@ -300,6 +307,9 @@ class DeviceModel:
             ctx3[:, 0] = h[0:M]
         h[5 * R:5 * R + 3 * M] = np.asarray(ctx3, dtype=np.int32).reshape(-1)
         self.rows_dev.copy_(self.rows_host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.dev))
+        self.rows_events[turn] = ev
         self.rows.M = M
         self.rows.max_groups = (int(max(pos)) + 1) // self.cfg.idx_ratio
 

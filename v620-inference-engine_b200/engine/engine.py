@@ -51,6 +51,7 @@ class Engine:
                               dev_pages=opts.dev_pages, save_gdn=opts.save_gdn)
         self.slot = [Slot() for _ in range(opts.slots)]
         self.out_host = torch.zeros(opts.max_rows, dtype=torch.int32).pin_memory()
+        self.merge_argmax = None        # set by the NCCL backend: merges the ranks' (max, argmax) after a step
         self.steps = 0
 
     # ---- construction
@@ -122,6 +123,8 @@ class Engine:
             i += len(chunk)
         self.steps += 1
         if want_logits:
+            if self.merge_argmax is not None:
+                self.merge_argmax(len(chunk))
             return self.dm.buf["logits"][(n - 1) % step if n % step else step - 1]
         return None
 
@@ -151,6 +154,8 @@ class Engine:
         for s, t in zip(slots, tokens):
             self.slot[s].tokens.append(int(t))
         self.steps += 1
+        if self.merge_argmax is not None:
+            self.merge_argmax(M)            # vocabulary-parallel argmax merged outside the graph (NCCL backend)
         self.out_host[:M].copy_(self.dm.buf["amax_idx"][:M], non_blocking=True)
         if sync:
             torch.cuda.current_stream(self.dm.dev).synchronize()
@@ -162,6 +167,8 @@ class Engine:
         graph of one step (with the row-advance kernel at its end) is replayed ``n_steps`` times with
         no host work in between; the sampled tokens are read back once at the end."""
         dm = self.dm
+        if self.merge_argmax is not None:
+            raise RuntimeError("chained decode needs the device-side argmax merge (p2p backend)")
         base = self.slot[slot].n
         if base + n_steps > dm.slot_tokens:
             raise ValueError("slot capacity exceeded")

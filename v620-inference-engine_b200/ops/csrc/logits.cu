@@ -82,9 +82,43 @@ __global__ void advance_rows_kernel(int *tokens, int *pos, int *ctx3, const int 
     pos[m] += 1;
 }
 
+// Vocabulary-parallel argmax: every rank packs its (value, index) per row into its column pair of the
+// gathered matrix; after the all-gather every rank picks the best pair (ties to the lowest index).
+__global__ void amax_pack_kernel(const float *val, const int *idx, float *pairs, int M, int rank, int ranks) {
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    pairs[(long long)m * ranks * 2 + rank * 2] = val[m];
+    pairs[(long long)m * ranks * 2 + rank * 2 + 1] = __int_as_float(idx[m]);
+}
+__global__ void amax_merge_kernel(const float *pairs, int M, int ranks, int *out_idx, float *out_val) {
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < ranks; ++r) {
+        const float v = __ldcg(pairs + (long long)m * ranks * 2 + r * 2);
+        const int i = __float_as_int(__ldcg(pairs + (long long)m * ranks * 2 + r * 2 + 1));
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    out_idx[m] = bi;
+    if (out_val) out_val[m] = bv;
+}
+
 }  // namespace qw
 
 using namespace qw;
+
+QW_API int qwk_amax_pack(const float *val, const int *idx, float *pairs, int M, int rank, int ranks, cudaStream_t s) {
+    return launch_pdl(amax_pack_kernel, dim3((M + 63) / 64), dim3(64), 0, s, val, idx, pairs, M, rank, ranks) == cudaSuccess ? 0 : -2;
+}
+QW_API int qwk_amax_merge(const float *pairs, int M, int ranks, int *out_idx, float *out_val, cudaStream_t s) {
+    return launch_pdl(amax_merge_kernel, dim3((M + 63) / 64), dim3(64), 0, s, pairs, M, ranks, out_idx, out_val) == cudaSuccess ? 0 : -2;
+}
+
 
 QW_API int qwk_advance_rows(int *tokens, int *pos, int *ctx3, const int *next, int M, cudaStream_t s) {
     advance_rows_kernel<<<(M + 63) / 64, 64, 0, s>>>(tokens, pos, ctx3, next, M);

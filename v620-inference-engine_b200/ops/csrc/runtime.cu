@@ -79,6 +79,15 @@ void comm(Ctx &c, int kind, const void *src, void *dst, int rows, int n) {
     const QwModel &md = *c.md;
     ++c.site;
     if (c.dry) return;
+    if (md.d.ranks > 1 && md.p2p) {
+        int rc = 0;
+        if (kind == 0) rc = qwk_p2p_allreduce(md.p2p, (unsigned)c.site, (const float *)src, (float *)dst, rows, n, c.s);
+        else if (kind == 1) rc = qwk_p2p_allgather(md.p2p, (unsigned)c.site, 1, md.off_bin, rows, n, 2, c.s);
+        else rc = qwk_p2p_reduce_scatter(md.p2p, (unsigned)c.site, (const float *)src, (float *)dst, rows, n, c.s);
+        c.launches += 1;
+        if (rc != 0 && c.err == 0) c.err = rc * 1000 - __LINE__;
+        return;
+    }
     if (md.d.ranks > 1 && md.comm) md.comm(md.comm_user, kind, c.site, src, dst, rows, n, c.s);
 }
 
@@ -221,6 +230,7 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     c.Xalt = b.X2;
     c.site = 0;
     c.op = 0;
+    if (d.ranks > 1 && md->p2p) QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
     QW_TRYN(1, qwk_embed_rows(c.rows->tokens, c.md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, c.s));
     const float *pend = nullptr;
     float *inj_attn = b.inj_a, *inj_mlp = b.inj_b;
@@ -249,7 +259,16 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
                              c.s));
         QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
                               b.lse_sum, c.s));
-        if ((flags & QWRT_CHAIN) && d.ranks == 1)
+        if (d.ranks > 1 && md->p2p && md->amax_pairs) {
+            // vocabulary-parallel argmax: gather every rank's (value, index) and merge on the device
+            QW_TRYN(1, qwk_amax_pack(b.amax_val, b.amax_idx, md->amax_pairs, M, d.rank, d.ranks, c.s));
+            ++c.site;
+            if (!c.dry) {
+                QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_amax, M, 2, 4, c.s));
+            }
+            QW_TRYN(1, qwk_amax_merge(md->amax_pairs, M, d.ranks, b.amax_idx, b.amax_val, c.s));
+        }
+        if ((flags & QWRT_CHAIN) && (d.ranks == 1 || md->p2p))
             QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
                                     const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
     }

@@ -130,6 +130,10 @@ typedef struct QwModel {
     QwBuffers b;
     QwCommFn comm;
     void *comm_user;
+    const void *p2p;           // QwP2P (p2p.cu): when set, collectives run as this library's peer-memory kernels
+    float *amax_pairs;         // [rows][ranks*2] inside the symmetric region (gather target of the argmax merge)
+    long long off_amax;        // its offset inside the region
+    long long off_bin;         // offset of b.bin inside the region
 } QwModel;
 
 // flags of qwrt_decode

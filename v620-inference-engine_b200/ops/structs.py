@@ -55,4 +55,11 @@ COMM_FN = C.CFUNCTYPE(None, P, C.c_int, C.c_int, P, P, C.c_int, C.c_int, P)
 
 class QwModel(C.Structure):
     _fields_ = [("d", QwDims), ("layers", C.POINTER(QwLayer)), ("final_hc", QwHc), ("ple", QwPle), ("embed", P),
-                ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P)]
+                ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P),
+                ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong)]
+
+
+class QwP2P(C.Structure):
+    _fields_ = [("peer", P * 8), ("ranks", C.c_int), ("rank", C.c_int), ("base", P), ("off_flags", C.c_longlong * 4),
+                ("off_recv", C.c_longlong * 4), ("slot_bytes", C.c_longlong * 4), ("off_bin", C.c_longlong),
+                ("off_amax", C.c_longlong)]
