@@ -46,6 +46,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: run a model with fewer layers (marks the result invalid)")
     ap.add_argument("--ple-rows", type=int, default=1 << 22)
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end loop (default: --steps)")
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
+                    help="multi-GPU collectives: this library's peer-memory kernels, or the NCCL baseline")
     ap.add_argument("--profile-step", action="store_true",
                     help="bracket one extra chained decode step with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -81,7 +83,7 @@ def main():
     t0 = time.time()
     if world > 1:
         from qwb200.parallel.dist_engine import make_engine
-        eng = make_engine(cfg, opts, world, rank, dev, ple_rows=args.ple_rows, log=log)
+        eng = make_engine(cfg, opts, world, rank, dev, ple_rows=args.ple_rows, log=log, comm=args.comm)
     else:
         eng = Engine.synthetic(cfg, opts, device=dev, ple_rows=args.ple_rows, log=log)
     log(f"model ready in {time.time() - t0:.1f} s: {eng.dm.weight_bytes() / 1e9:.1f} GB of weights on rank {rank}")
@@ -100,13 +102,24 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    chained = eng.merge_argmax is None      # the NCCL baseline merges the argmax on the host side of the graph
+
+    def run_steps(tok, n):
+        if chained:
+            return eng.decode_chain(0, tok, n)
+        out = []
+        for _ in range(n):
+            tok = eng.decode([0], [tok])[0]
+            out.append(tok)
+        return out
+
     # ---- device-timed: chained greedy decode, one graph replay per token
-    toks = eng.decode_chain(0, first, W)
+    toks = run_steps(first, W)
     launches = int(eng.dm.lib.qwrt_last_launches()) if hasattr(eng.dm.lib, "qwrt_last_launches") else 0
     if args.profile_step:
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
-        toks = eng.decode_chain(0, toks[-1], 1)
+        toks = run_steps(toks[-1], 1)
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
     sampler = ClockSampler(local)
@@ -114,7 +127,7 @@ def main():
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    toks2 = eng.decode_chain(0, toks[-1], K)
+    toks2 = run_steps(toks[-1], K)
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
@@ -146,7 +159,7 @@ def main():
             "data": "synthetic (random-init weights, random token context, synthetic fp8 PLE table)",
             "config": {"model": "Qwen3.8-Flash-Next 180B hybrid MoE" if valid else f"{args.model} layers={cfg.n_layers} (not the named model)",
                        "global_batch": 1, "seq_len": args.context,
-                       "parallelism": f"tp{world}+ep{world}" if world > 1 else "single GPU",
+                       "parallelism": f"tp{world}+ep{world} ({args.comm} collectives)" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: every step streams ~9.8 GB of weights",
                        "ple_rows": args.ple_rows, "generated": K},
             "clocks": clocks,
