@@ -1,0 +1,232 @@
+// Dense bf16 GEMM on the 5th-generation tensor cores: C[T][N] = A[T][K] . W[N][K]^T, fp32 accumulate in
+// tensor memory, fp32 or bf16 output (prefill path: projections, mixers, router with fp32 output,
+// lm_head; role of the reference's rocBLAS call sites, src/kernels/gemm.hip:10-18).
+//
+// One CTA computes a 128 x 128 output tile.  Warp roles:
+//   warp 0   : TMA producer - one thread issues cp.async.bulk.tensor loads (no multicast) of the
+//              128 x 64 A tile and the 128 x 64 W tile of each k block into a 6-stage ring of
+//              128B-swizzled shared-memory tiles, completing on the stage's "full" mbarrier;
+//   warp 1   : allocates 128 TMEM columns, and one thread issues tcgen05.mma (M=128, N=128, K=16, four per
+//              k block) reading both operands straight from shared memory through matrix descriptors;
+//              tcgen05.commit releases a stage ("empty" mbarrier) and finally signals the epilogue;
+//   warps 2-5: epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32 output rows),
+//              convert and store.
+// Every mbarrier wait is bounded; a wait that runs out records an error, the pipeline drains and the
+// TMEM allocation is released before the kernel returns.
+#include <cuda.h>
+
+#include "stream.cuh"
+
+namespace qw {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 6;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;     // 16 KB each
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
+    // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                           // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset
+    d |= (uint64_t)1 << 46;                           // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct GemmTcArgs {
+    float *C32;          // one of the two outputs
+    bf16 *C16;
+    int T, N, K, ldc;
+    ErrorWord *err;
+};
+
+__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                         const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
+    extern __shared__ unsigned char raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);
+    uint64_t *empty = full + TC_STAGES;
+    uint64_t *done = empty + TC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BN, t0 = blockIdx.y * TC_BM;
+    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) break;
+                mbar_expect_tx(full + s, TC_STAGE_BYTES);
+                unsigned char *st = smem + s * TC_STAGE_BYTES;
+                tma_load_2d(st, &mapA, kb * TC_BK, t0, full + s);
+                tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, n0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A/B bf16, both K-major, N and M of the tile
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                ok = mbar_wait(full + s, (unsigned)(kb / TC_STAGES) & 1u, a.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
+                    umma_bf16(tmem, da, db, idesc, (kb | k) ? 1u : 0u);
+                }
+                umma_commit(empty + s);          // the stage is free once these MMAs have read it
+            }
+            umma_commit(done);                   // accumulator complete (arrives even after a failed wait)
+        }
+    } else {
+        // epilogue warps 2..5: TMEM lane quarter = warp % 4
+        const bool ok = mbar_wait(done, 0, a.err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3;
+        const int row = t0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < a.T) {
+                    const int nmax = a.N - (n0 + c0);
+                    if (a.C32) {
+                        float *o = a.C32 + (long long)row * a.ldc + n0 + c0;
+                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        } else {
+                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
+                        }
+                    } else {
+                        bf16 *o = a.C16 + (long long)row * a.ldc + n0 + c0;
+                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pk;
+                                pk.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                                pk.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                                pk.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                                pk.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                                *reinterpret_cast<uint4 *>(o + j) = pk;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __float2bfloat16(__uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major matrix [rows][cols] (row stride ld elements), box = 64 columns x box_rows rows, 128B swizzle.
+static bool make_map(CUtensorMap *m, const void *base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace qw
+
+using namespace qw;
+
+// C = A . W^T.  A bf16 [T][lda], W bf16 [N][ldw], C fp32 (out_bf16 = 0) or bf16 [T][ldc].
+// Base addresses 16-byte aligned, lda/ldw multiples of 8 elements, K a multiple of 8.
+QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
+                            int out_bf16, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -1;
+    CUtensorMap mA, mW;
+    if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_BN)) return -3;
+    GemmTcArgs a;
+    a.C32 = out_bf16 ? nullptr : (float *)C;
+    a.C16 = out_bf16 ? (bf16 *)C : nullptr;
+    a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        configured = true;
+    }
+    dim3 grid((N + TC_BN - 1) / TC_BN, (T + TC_BM - 1) / TC_BM);
+    gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -90,3 +90,18 @@ def moe_experts_pair(w13, s13, w2, s2, x, pair_expert, pair_w, F: int, H: int, s
                                         _p(shared_down), 0 if shared_down is None else shared_down.stride(0),
                                         _p(sh_h), SF, _p(out), H, _s()), "moe_down_combine")
     return out
+
+
+def gemm_bf16_tc(A: torch.Tensor, W: torch.Tensor, out_dtype=torch.float32, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ W.T on the tcgen05 tensor cores.  A bf16 [T, K], W bf16 [N, K]; C fp32 or bf16 [T, N]."""
+    lib = qlib.load(required=True)
+    assert A.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and A.is_cuda and W.is_cuda
+    assert A.stride(1) == 1 and W.stride(1) == 1
+    T, Kd = A.shape
+    N = W.shape[0]
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=A.device)
+    assert out.dtype in (torch.float32, torch.bfloat16) and out.stride(1) == 1
+    qlib.check(lib.qwk_gemm_bf16_tc(_p(A), _p(W), _p(out), T, N, Kd, A.stride(0), W.stride(0), out.stride(0),
+                                    1 if out.dtype == torch.bfloat16 else 0, _s()), "gemm_bf16_tc")
+    return out
