@@ -91,10 +91,18 @@ def main():
     # ---- context: 4,096 random tokens through the prefill path (untimed)
     g = torch.Generator().manual_seed(1234)
     ctx = torch.randint(0, cfg.vocab, (args.context,), generator=g).tolist()
+    if world == 1 and eng.opts.prefill_chunk:
+        eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, tensor maps), then start over
+        torch.cuda.synchronize()
+        eng.reset(0)
     t0 = time.time()
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pe0.record()
     eng.prefill(0, ctx, want_logits=True)
+    pe1.record()
     torch.cuda.synchronize()
-    first = int(eng.dm.buf["amax_idx"][(args.context - 1) % eng.opts.prefill_rows])
+    prefill_ms = pe0.elapsed_time(pe1)
+    first = int(eng.dm.buf["amax_idx"][eng.last_prefill_row])
     log(f"context of {args.context} tokens in {time.time() - t0:.2f} s")
 
     def barrier():
@@ -166,6 +174,8 @@ def main():
             "e2e": {"value": round(e2e_steps / (ms_e2e / 1e3), 2), "unit": "tok/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": int(eng.dm.rows_host.numel() * 4), "d2h_bytes_per_step": 4,
                     "api": "Engine.decode"},
+            "prefill": {"tokens": args.context, "ms": round(prefill_ms, 2), "tok_s": round(args.context / (prefill_ms / 1e3), 1),
+                        "path": "token-major tcgen05 GEMM" if (world == 1 and eng.opts.prefill_chunk) else "row-batched"},
             "gpu_launches": launches * K,
             "gpu_launches_per_step": launches,
             "impl": "ours",

@@ -40,6 +40,8 @@ class EngineOptions:
     save_gdn: bool = False
     use_graphs: bool = True
     prefill_rows: int = DM.MAX_ROWS          # rows per step of the row-batched prefill
+    prefill_chunk: int = 4096                # tokens per chunk of the token-major (tcgen05 GEMM) prefill; 0 = off
+    prefill_min: int = 64                    # shorter pieces use the row-batched path
 
 
 class Engine:
@@ -52,6 +54,7 @@ class Engine:
         self.slot = [Slot() for _ in range(opts.slots)]
         self.out_host = torch.zeros(opts.max_rows, dtype=torch.int32).pin_memory()
         self.merge_argmax = None        # set by the NCCL backend: merges the ranks' (max, argmax) after a step
+        self.prefiller = None           # token-major prefill, built on first use (one GPU)
         self.steps = 0
 
     # ---- construction
@@ -108,6 +111,8 @@ class Engine:
         """Append ``tokens`` to the slot.  Returns the logits of the last token (device tensor)."""
         toks = [int(t) for t in tokens]
         n = len(toks)
+        if self.dm.sc.ranks == 1 and self.opts.prefill_chunk > 0 and n >= self.opts.prefill_min:
+            return self._prefill_token_major(slot, toks, want_logits)
         step = max(1, min(self.opts.prefill_rows, self.opts.max_rows))
         i = 0
         while i < n:
@@ -125,8 +130,26 @@ class Engine:
         if want_logits:
             if self.merge_argmax is not None:
                 self.merge_argmax(len(chunk))
-            return self.dm.buf["logits"][(n - 1) % step if n % step else step - 1]
+            self.last_prefill_row = (n - 1) % step if n % step else step - 1
+            return self.dm.buf["logits"][self.last_prefill_row]
         return None
+
+    def _prefill_token_major(self, slot: int, toks: List[int], want_logits: bool):
+        from .prefill import Prefiller
+        if self.slot[slot].n + len(toks) > self.dm.slot_tokens:
+            raise ValueError("slot capacity exceeded")
+        if self.prefiller is None:
+            self.prefiller = Prefiller(self.dm, chunk=min(self.opts.prefill_chunk, max(256, self.dm.slot_tokens)))
+        T = self.prefiller.T
+        out = None
+        for i in range(0, len(toks), T):
+            chunk = toks[i:i + T]
+            last = i + T >= len(toks)
+            out = self.prefiller.run(slot, self.slot[slot].n, chunk, self._ctx3(slot, chunk), want_logits and last)
+            self.slot[slot].tokens.extend(chunk)
+        self.steps += 1
+        self.last_prefill_row = 0           # logits / argmax of the last token sit in row 0
+        return out
 
     # ---- decode
     def decode(self, slots: Sequence[int], tokens: Sequence[int], flags: int = 0, sync: bool = True) -> List[int]:

@@ -1,0 +1,240 @@
+"""Token-major prefill of one slot on one GPU.
+
+A chunk of T prompt tokens goes through the model with every dense product on the tcgen05 GEMM
+(``qwk_gemm_bf16_tc``), the routed experts as one grouped tcgen05 GEMM per projection over
+expert-sorted rows (weights of the layer dequantised q4 -> bf16 into a scratch first), and the
+stateful pieces (GDN conv + scan, QSA prep / indexer / selection / attention over the paged KV, PLE)
+on the same row-batch kernels the decode path uses, so the slot state a prefill leaves behind is the
+state the decode kernels expect (reference: ``run_prefill_rank``, src/engine/prefill.hip:46-496).
+
+PyTorch only does the bookkeeping here (buffers, the expert sort's index arithmetic); everything that
+touches activations or weights is one of this library's kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..ops import lib as qlib
+from .device_model import DeviceModel
+
+P = C.c_void_p
+
+
+def _p(t):
+    return None if t is None else P(t.data_ptr())
+
+
+class Prefiller:
+    def __init__(self, dm: DeviceModel, chunk: int = 4096, attn_rows: int = 256):
+        if dm.sc.ranks != 1:
+            raise NotImplementedError("token-major prefill runs on one GPU; multi-rank prefill uses the row-batched path")
+        self.dm, self.T, self.attn_rows = dm, chunk, attn_rows
+        self.lib = dm.lib
+        c, sc, dev = dm.cfg, dm.sc, dm.dev
+        T = chunk
+        f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+        self.hc_ld = (c.hc_down + 7) // 8 * 8
+        nrs = c.n_experts + 1 + 2 * sc.sffn_l
+        self.nrs_ld = (nrs + 7) // 8 * 8
+        self.proj_ld = (max(sc.gdn_proj_l, sc.qsa_proj_l) + 7) // 8 * 8
+        Pn = T * c.top_k
+        self.b = {
+            "X": z((T, c.hc, sc.sh), f32), "xn": z((T, c.hch), bf), "d": z((T, self.hc_ld), f32), "u": z((T, c.hc_rank), bf),
+            "inj_a": z((T, c.hc), f32), "inj_b": z((T, c.hc), f32), "g": z((T, c.hch), f32), "bin": z((T, c.hidden), bf),
+            "proj": z((T, self.proj_ld), f32), "o": z((T, max(sc.gdn_vl * c.gdn_dim, sc.qh_l * c.head_dim)), bf),
+            "out_a": z((T, c.hidden), f32), "out_b": z((T, c.hidden), f32),
+            "qkv": z((T, sc.gdn_qkv_l), f32), "decay": z((T, sc.gdn_vl), f32), "beta": z((T, sc.gdn_vl), f32),
+            "q": z((T, sc.qh_l, c.head_dim), f32), "iq": z((T, c.idx_heads, c.idx_dim), f32),
+            "scores": z((T, dm.model.d.score_cap), f32), "sel": z((T, c.idx_topk_blocks), i32), "sel_n": z((T,), i32),
+            "pm": z((attn_rows, sc.qh_l, dm.model.d.nsplit), f32), "pl": z((attn_rows, sc.qh_l, dm.model.d.nsplit), f32),
+            "pacc": z((attn_rows, sc.qh_l, dm.model.d.nsplit, c.head_dim), f32),
+            "rs": z((T, self.nrs_ld), f32), "pe": z((T, c.top_k), i32), "pw": z((T, c.top_k), f32),
+            "sh_h": z((T, sc.sffn_l), bf), "sd": z((T, c.hidden), f32),
+            "xperm": z((Pn + 128, c.hidden), bf), "h13": z((Pn, 2 * c.ffn), bf), "h": z((Pn + 128, c.ffn), bf),
+            "y": z((Pn, c.hidden), f32),
+            "w13dq": z((sc.exp_l * 2 * c.ffn, c.hidden), bf), "w2dq": z((sc.exp_l * c.hidden, c.ffn), bf),
+            "ple_e": z((T, c.hidden), bf), "ple_kv": z((T, (sc.ple_kv + 7) // 8 * 8), f32), "ple_send": z((T, 16), f32),
+            "ple_gv": z((T, sc.xw), f32), "ple_nc": z((T, sc.xw), f32),
+            "rows": z((8 * T,), i32),
+        }
+        self.rows_host = torch.zeros(8 * T, dtype=torch.int32).pin_memory()
+        self.max_tiles = Pn // 128 + sc.exp_l
+
+    # ---- helpers
+    def _s(self):
+        return P(torch.cuda.current_stream(self.dm.dev).cuda_stream)
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed: {rc}")
+
+    def gemm(self, A, W_ptr, N, K, out, ldw=None):
+        """out[:, :N] = A @ W^T with W given by pointer ([N][ldw] bf16)."""
+        T = A.shape[0]
+        self._ck(self.lib.qwk_gemm_bf16_tc(_p(A), P(W_ptr), _p(out), T, N, K, A.stride(0), ldw or K, out.stride(0),
+                                           1 if out.dtype == torch.bfloat16 else 0, self._s()), "gemm")
+
+    def _rows(self, slot, base, T, toks, ctx3):
+        Tm = self.T
+        h = self.rows_host.numpy()
+        h[0:T] = toks
+        h[Tm:Tm + T] = slot
+        h[2 * Tm:2 * Tm + T] = np.arange(base, base + T, dtype=np.int32)
+        h[3 * Tm:3 * Tm + T] = 0
+        h[4 * Tm:4 * Tm + T] = 0
+        h[4 * Tm] = T
+        h[5 * Tm:5 * Tm + 3 * T] = ctx3.reshape(-1)
+        self.b["rows"].copy_(self.rows_host, non_blocking=True)
+        r = self.b["rows"].data_ptr()
+        return {"tokens": r, "slot": r + 4 * Tm, "pos": r + 8 * Tm, "run_start": r + 12 * Tm, "run_len": r + 16 * Tm,
+                "ctx3": r + 20 * Tm}
+
+    def mix(self, hc, T, pend, inj_prev, inj_out, n_inj):
+        dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
+        s = self._s()
+        self._ck(L.qwk_hc_prenorm_T(_p(b["X"]), _p(pend), c.hidden, _p(inj_prev), P(hc["w1"].data_ptr()), sc.sh, c.hc,
+                                    C.c_float(c.eps), _p(b["xn"]), T, s), "hc_prenorm")
+        down = c.hc_rank + n_inj
+        self.gemm(b["xn"][:T], hc["Wd"].data_ptr(), down, c.hch, b["d"][:T])
+        self._ck(L.qwk_hc_mid_T(_p(b["d"]), self.hc_ld, c.hc_rank, n_inj, c.hc, _p(b["u"]), _p(inj_out), T, s), "hc_mid")
+        self.gemm(b["u"][:T], hc["Wu"].data_ptr(), c.hch, c.hc_rank, b["g"][:T])
+        self._ck(L.qwk_hc_mix_T(_p(b["g"]), _p(b["xn"]), sc.sh, _p(b["bin"]), c.hidden, T, s), "hc_mix")
+
+    # ---- one chunk
+    @torch.no_grad()
+    def run(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True):
+        dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
+        T = len(tokens)
+        assert 1 <= T <= self.T
+        s = self._s()
+        rows = self._rows(slot, base, T, [c.real_token(int(t)) for t in tokens], np.asarray(ctx3, dtype=np.int32))
+        rp = lambda k, off=0: P(rows[k] + 4 * off)
+        d = dm.model.d
+        self._ck(L.qwk_embed_rows(rp("tokens"), P(dm.globals_w["embed"].data_ptr()), c.hidden, 0, sc.sh, c.hc, c.vocab,
+                                  _p(b["X"]), T, s), "embed")
+        pend, inj_prev = None, None
+        inj_attn, inj_mlp = b["inj_a"], b["inj_b"]
+        max_groups = (base + T) // c.idx_ratio
+        for li in range(c.n_layers):
+            lw = dm.layers_w[li]
+            if li == c.ple_layer and dm.model.ple.enabled:
+                if pend is not None:
+                    self._ck(L.qwk_hc_pre(_p(b["X"]), _p(pend), c.hidden, _p(inj_prev), c.hc, None, sc.sh, c.hc, None, None, 0,
+                                          T, s), "combine")
+                    pend = None
+                pw_ = dm.ple_w
+                p = dm.model.ple
+                self._ck(L.qwk_ple_gather(rp("ctx3"), P(p.shards), P(p.scales), p.rows_per_shard, p.rows, p.layout,
+                                          c.ngram_dim, c.ngram_heads, _p(b["ple_e"]), None, T, s), "ple_gather")
+                self.gemm(b["ple_e"][:T], pw_["Wkv"].data_ptr(), sc.ple_kv, c.hidden, b["ple_kv"][:T])
+                ldk = b["ple_kv"].stride(0)
+                self._ck(L.qwk_ple_stats(_p(b["ple_kv"]), ldk, _p(b["X"]), P(pw_["nk1"].data_ptr()), P(pw_["nq1"].data_ptr()),
+                                         sc.sh, c.hc, _p(b["ple_send"]), 16, T, s), "ple_stats")
+                self._ck(L.qwk_ple_apply(_p(b["ple_kv"]), ldk, _p(b["ple_send"]), 16, P(pw_["nc1"].data_ptr()),
+                                         P(pw_["cw"].data_ptr()), sc.sh, c.hc, c.hidden, C.c_float(c.eps), c.ple_conv,
+                                         c.ple_dilation, _p(b["ple_gv"]), _p(b["ple_nc"]), _p(dm.ple_ring), _p(b["X"]), T,
+                                         rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), s), "ple_apply")
+            self.mix(lw["attn_hc"], T, pend, inj_prev, inj_attn, c.hc)
+            if lw["is_qsa"]:
+                qi = c.qsa_index(li)
+                self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.qsa_proj_l, c.hidden, b["proj"][:T])
+                ldp = self.proj_ld
+                kd, vd = dm.k_dev[qi].data_ptr(), dm.v_dev[qi].data_ptr()
+                kh = dm.k_host[qi].data_ptr() if dm.k_host else None
+                vh = dm.v_host[qi].data_ptr() if dm.v_host else None
+                self._ck(L.qwk_qsa_prep(_p(b["proj"]), ldp, sc.qh_l, sc.kvh_l, c.idx_heads, P(lw["qn1"].data_ptr()),
+                                        P(lw["kn1"].data_ptr()), P(lw["iqn1"].data_ptr()), P(lw["ikn1"].data_ptr()), T,
+                                        rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), P(kd), P(vd), P(kh) if kh else None,
+                                        P(vh) if vh else None, d.n_dev_pages, _p(dm.page_table), d.max_pages, _p(b["q"]),
+                                        _p(b["iq"]), _p(dm.raw_ring[qi]), _p(dm.ck[qi]), d.ck_cap, c.idx_ratio,
+                                        C.c_float(c.eps), s), "qsa_prep")
+                self._ck(L.qwk_qsa_scores(_p(b["iq"]), c.idx_heads, _p(dm.ck[qi]), d.ck_cap, T, rp("slot"), rp("pos"),
+                                          c.idx_ratio, c.idx_topk_blocks, _p(b["scores"]), d.score_cap, max_groups, s), "scores")
+                self._ck(L.qwk_qsa_select(_p(b["scores"]), d.score_cap, T, rp("pos"), c.idx_ratio, c.idx_topk_blocks,
+                                          _p(b["sel"]), _p(b["sel_n"]), s), "select")
+                A = self.attn_rows
+                ow = sc.qh_l * c.head_dim
+                for r0 in range(0, T, A):
+                    n = min(A, T - r0)
+                    self._ck(L.qwk_qsa_attend(P(b["q"].data_ptr() + 4 * r0 * ow), sc.qh_l, sc.kvh_l, n, rp("slot", r0),
+                                              rp("pos", r0), P(kd), P(vd), P(kh) if kh else None, P(vh) if vh else None,
+                                              d.n_dev_pages, _p(dm.page_table), d.max_pages,
+                                              P(b["sel"].data_ptr() + 4 * r0 * c.idx_topk_blocks),
+                                              P(b["sel_n"].data_ptr() + 4 * r0), c.idx_topk_blocks, c.idx_ratio, d.nsplit,
+                                              _p(b["pm"]), _p(b["pl"]), _p(b["pacc"]), P(b["proj"].data_ptr() + 4 * r0 * ldp),
+                                              ldp, P(b["o"].data_ptr() + 2 * r0 * ow), s), "attend")
+                # the attention kernels write o rows densely ([T][QL*256])
+                self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
+                                            c.hidden, 0, s), "o_proj")
+            else:
+                gi = c.gdn_index(li)
+                self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.gdn_proj_l, c.hidden, b["proj"][:T])
+                ldp = self.proj_ld
+                self._ck(L.qwk_gdn_conv(_p(b["proj"]), ldp, _p(dm.gdn_ring[gi]), P(lw["cw"].data_ptr()), P(lw["A_log"].data_ptr()),
+                                        P(lw["dt_bias"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
+                                        rp("run_start"), rp("run_len"), _p(b["qkv"]), _p(b["decay"]), _p(b["beta"]),
+                                        C.c_float(c.eps), s), "gdn_conv")
+                self._ck(L.qwk_gdn_scan(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp, _p(dm.gdn_S[gi]), None,
+                                        P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
+                                        rp("run_start"), rp("run_len"), _p(b["o"]), C.c_float(c.eps), s), "gdn_scan")
+                ow = sc.gdn_vl * c.gdn_dim
+                # gdn_scan writes o rows densely ([T][VL*128])
+                self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
+                                            c.hidden, 0, s), "gdn_out")
+            self.mix(lw["mlp_hc"], T, b["out_a"], inj_attn, inj_mlp, c.hc)
+            self.moe(lw, T)
+            pend, inj_prev = b["out_b"], inj_mlp
+        gw = dm.globals_w
+        self.mix(gw["final_hc"], T, pend, inj_prev, None, 0)
+        if want_logits:
+            last = b["bin"][T - 1:T]
+            self._ck(L.qwk_gemv_bf16(P(gw["lm_head"].data_ptr()), _p(last), _p(dm.buf["logits"]), None, sc.vocab_l, c.hidden, 1,
+                                     c.hidden, c.hidden, sc.vocab_l, 0, 1, 0, 0, 0, s), "lm_head")
+            self._ck(L.qwk_row_reduce(_p(dm.buf["logits"]), sc.vocab_l, sc.vocab_l, 0, 1, _p(dm.buf["amax_val"]),
+                                      _p(dm.buf["amax_idx"]), _p(dm.buf["lse_max"]), _p(dm.buf["lse_sum"]), s), "row_reduce")
+        return dm.buf["logits"][0] if want_logits else None
+
+    def moe(self, lw, T):
+        dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
+        s = self._s()
+        E, k, F, H = sc.exp_l, c.top_k, c.ffn, c.hidden
+        nrs = c.n_experts + 1 + 2 * sc.sffn_l
+        self.gemm(b["bin"][:T], lw["Wrs"].data_ptr(), nrs, H, b["rs"][:T])
+        self._ck(L.qwk_moe_route(_p(b["rs"]), self.nrs_ld, T, c.n_experts, k, sc.sffn_l, 0, E, _p(b["pe"]), _p(b["pw"]),
+                                 _p(b["sh_h"]), s), "route")
+        # ---- expert sort (index arithmetic only)
+        flat = b["pe"][:T].reshape(-1).long()
+        Pn = flat.numel()
+        order = torch.sort(flat, stable=True).indices
+        counts = torch.bincount(flat, minlength=E)
+        ends = torch.cumsum(counts, 0)
+        offsets = ends - counts
+        inv = torch.empty(Pn, dtype=torch.int32, device=flat.device)
+        inv[order] = torch.arange(Pn, dtype=torch.int32, device=flat.device)
+        torch.index_select(b["bin"][:T], 0, order // k, out=b["xperm"][:Pn])
+        nt = (counts + 127) // 128
+        tend = torch.cumsum(nt, 0)
+        idx = torch.arange(self.max_tiles, device=flat.device)
+        e = torch.searchsorted(tend, idx, right=True).clamp(max=E - 1)
+        local = idx - (tend[e] - nt[e])
+        valid = (counts[e] - local * 128).clamp(0, 128)
+        valid = torch.where(idx < tend[-1], valid, torch.zeros_like(valid))
+        row0 = offsets[e] + local * 128
+        zero = torch.zeros_like(row0)
+        t13 = torch.stack([row0, valid, e * (2 * F), zero], 1).to(torch.int32).contiguous()
+        t2 = torch.stack([row0, valid, e * H, zero], 1).to(torch.int32).contiguous()
+        # ---- weights of this layer: q4 -> bf16 scratch
+        self._ck(L.qwk_q4_dequant(P(lw["w13"].data_ptr()), P(lw["s13"].data_ptr()), E * 2 * F, H, _p(b["w13dq"]), s), "dequant13")
+        self._ck(L.qwk_q4_dequant(P(lw["w2"].data_ptr()), P(lw["s2"].data_ptr()), E * H, F, _p(b["w2dq"]), s), "dequant2")
+        self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["xperm"]), _p(b["w13dq"]), _p(b["h13"]), _p(t13), self.max_tiles, Pn,
+                                            E * 2 * F, 2 * F, H, H, H, 2 * F, 1, s), "experts13")
+        self._ck(L.qwk_swiglu_T(_p(b["h13"]), F, _p(b["h"]), Pn, s), "swiglu")
+        self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["h"]), _p(b["w2dq"]), _p(b["y"]), _p(t2), self.max_tiles, Pn, E * H, H, F, F,
+                                            F, H, 0, s), "experts2")
+        self.gemm(b["sh_h"][:T], lw["Wsd"].data_ptr(), H, sc.sffn_l, b["sd"][:T])
+        self._ck(L.qwk_moe_combine_T(_p(b["y"]), H, _p(inv), _p(b["pw"]), k, _p(b["sd"]), H, _p(b["out_b"]), T, s), "combine")

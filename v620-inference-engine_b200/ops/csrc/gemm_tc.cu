@@ -57,6 +57,8 @@ struct GemmTcArgs {
     bf16 *C16;
     int T, N, K, ldc;
     ErrorWord *err;
+    // grouped mode (expert-sorted rows): tiles[blockIdx.y] = {first A row, valid rows, first W row of the group, -}
+    const int4 *tiles;
 };
 
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
@@ -68,7 +70,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     uint64_t *done = empty + TC_STAGES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BN, t0 = blockIdx.y * TC_BM;
+    const int n0 = blockIdx.x * TC_BN;
+    int t0 = blockIdx.y * TC_BM, rows_valid = TC_BM, w0 = n0;
+    if (a.tiles) {
+        const int4 tl = a.tiles[blockIdx.y];
+        t0 = tl.x;
+        rows_valid = tl.y;
+        w0 = tl.z + n0;
+        if (rows_valid <= 0) return;          // unused entry of the tile table (uniform for the CTA, before any barrier)
+    }
     const int kblocks = (a.K + TC_BK - 1) / TC_BK;
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -95,7 +105,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 mbar_expect_tx(full + s, TC_STAGE_BYTES);
                 unsigned char *st = smem + s * TC_STAGE_BYTES;
                 tma_load_2d(st, &mapA, kb * TC_BK, t0, full + s);
-                tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, n0, full + s);
+                tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, w0, full + s);
             }
         }
     } else if (warp == 1) {
@@ -124,6 +134,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int q = warp & 3;
         const int row = t0 + q * 32 + lane;
+        const bool row_ok = row < a.T && q * 32 + lane < rows_valid;
         if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < TC_BN; c0 += 32) {
@@ -138,7 +149,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                       "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < a.T) {
+                if (row_ok) {
                     const int nmax = a.N - (n0 + c0);
                     if (a.C32) {
                         float *o = a.C32 + (long long)row * a.ldc + n0 + c0;
@@ -220,13 +231,34 @@ QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N,
     GemmTcArgs a;
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
-    a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr;
+    a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
         configured = true;
     }
     dim3 grid((N + TC_BN - 1) / TC_BN, (T + TC_BM - 1) / TC_BM);
+    gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Grouped form for expert-sorted rows: A bf16 [rows][lda] holds the rows of group after group, W bf16
+// [w_rows][ldw] the groups' weight matrices one after another (Nw rows each), tiles (device, int4 x max_tiles)
+// lists {first A row, valid rows (0 = unused entry), first W row of the group, 0} per 128-row tile.
+// C[row][0..Nw) = A[row] . W_group^T.
+QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const void *tiles, int max_tiles, int rows,
+                                    long long w_rows, int Nw, int K, int lda, int ldw, int ldc, int out_bf16,
+                                    cudaStream_t s) {
+    if (rows <= 0 || max_tiles <= 0) return 0;
+    if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -1;
+    CUtensorMap mA, mW;
+    if (!make_map(&mA, A, rows, K, lda, TC_BM) || !make_map(&mW, W, w_rows, K, ldw, TC_BN)) return -3;
+    GemmTcArgs a;
+    a.C32 = out_bf16 ? nullptr : (float *)C;
+    a.C16 = out_bf16 ? (bf16 *)C : nullptr;
+    a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
+    cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
     gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

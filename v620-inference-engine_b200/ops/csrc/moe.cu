@@ -121,10 +121,17 @@ static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t 
 }
 
 // Stand-alone routing (tests, and callers that computed the logits elsewhere).  One block.
+// Each block routes 8 rows (a warp per row) and applies the shared activation to them.
 __global__ void __launch_bounds__(256) moe_route_kernel(const float *rs, int ld_rs, int M, RouteArgs r) {
     pdl_wait();
     pdl_trigger();
-    route_all(rs, ld_rs, M, r);
+    const int m0 = blockIdx.x * 8;
+    const int nm = min(8, M - m0);
+    RouteArgs q = r;
+    q.pair_expert += m0 * r.top_k;
+    q.pair_w += m0 * r.top_k;
+    if (q.sh_h) q.sh_h += (long long)m0 * r.F;
+    route_all(rs + (long long)m0 * ld_rs, ld_rs, nm, q);
 }
 
 // 32 q4 values (one 16-byte load, engine order) dot 32 bf16 activations.
@@ -291,7 +298,7 @@ QW_API int qwk_moe_route(const float *rs, int ld_rs, int M, int E, int top_k, in
                          int *pair_expert, float *pair_w, void *sh_h, cudaStream_t s) {
     if (E > 1024 || top_k > 32) return -1;
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, nullptr);
-    cudaError_t e = launch_pdl(moe_route_kernel, dim3(1), dim3(256), 0, s, rs, ld_rs, M, r);
+    cudaError_t e = launch_pdl(moe_route_kernel, dim3((M + 7) / 8), dim3(256), 0, s, rs, ld_rs, M, r);
     return e == cudaSuccess ? 0 : -2;
 }
 
