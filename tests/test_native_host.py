@@ -1,0 +1,143 @@
+"""Native host runtime (C++): hasher, PLE table, block store + disk tier, sampler, chunker."""
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from qwb200.models.config import ModelConfig
+from qwb200.models.ngram import NgramHasher as PyHasher
+from qwb200.models.ple import PleTable
+from qwb200.native import host as H
+
+
+def test_native_hasher_equals_python():
+    for cfg in (ModelConfig.full(), ModelConfig.tiny()):
+        a, b = H.NgramHasher(cfg), PyHasher(cfg)
+        assert a.total_rows == b.total_rows
+        toks = [7, 9, cfg.eos, 3, 3, cfg.eos, cfg.eos, 12, -3, 5, cfg.vocab - 1]
+        assert np.array_equal(a.ids_for([], toks), b.ids_for([], toks))
+        assert np.array_equal(a.ids_for(toks[:4], toks[4:]), b.ids_for(toks[:4], toks[4:]))
+
+
+@pytest.mark.parametrize("layout", ["f8", "bf16", "int8", "int4"])
+def test_native_ple_table_equals_python(tmp_path, layout):
+    cfg = ModelConfig.tiny()
+    t = PleTable.synthetic(cfg, rows=777, layout=layout, n_shards=2, seed=3)
+    t.save(str(tmp_path))
+    nat = H.PleTableNative(str(tmp_path), cfg.ngram_dim, threads=3)
+    ids = np.random.default_rng(0).integers(0, 5000, size=(40, cfg.ngram_heads))
+    want = t.gather(ids).numpy()
+    got = nat.gather(ids)
+    assert np.allclose(got, want, rtol=0, atol=1e-6)
+
+
+def test_block_store_chain_restore_and_disk_format(tmp_path):
+    layout = 0x1234
+    st = H.BlockStore(layout, 2, ram_budget=1 << 20, disk_dir=str(tmp_path), disk_budget=1 << 22)
+    toks = list(range(1000, 1000 + 600))
+    parent, keys = st.root, []
+    for i in range(0, 600, 256):
+        blk = toks[i:i + 256]
+        k = st.save_block(parent, i, blk, bytes([i // 256 + 1]) * 1000)
+        assert k == H.BlockStore.key(parent, blk) and k != 0
+        keys.append(k)
+        parent = k
+    assert st.save_snapshot(keys[1], b"S" * 500, np.arange(5, dtype=np.float32), anchor=True)
+    path, depth = st.lookup(toks)
+    assert path == keys and depth == 2
+    path, depth = st.lookup(toks[:300] + [1, 2, 3])
+    assert path == keys[:1] and depth == 0
+    snap, lg = st.get(keys[1], snapshot=True)
+    assert snap == b"S" * 500 and lg.tolist() == [0, 1, 2, 3, 4]
+    assert st.get(keys[2]) == bytes([3]) * 1000
+    st.flush()
+    # file format: header | tokens | logits | payload
+    f = os.path.join(str(tmp_path), f"{keys[0]:016x}.qwb")
+    raw = open(f, "rb").read()
+    magic, lay, h, par, ntok, ranks, nlog, rb = struct.unpack("<8sQQQqIIQ", raw[:56])
+    assert magic == b"QWBLOCK2" and lay == layout and h == keys[0] and par == st.root and ntok == 256 and ranks == 2
+    assert nlog == 0 and rb == 500 and len(raw) == 56 + 256 * 4 + 1000
+    assert struct.unpack("<256i", raw[56:56 + 1024]) == tuple(toks[:256])
+    s = open(os.path.join(str(tmp_path), f"{keys[1]:016x}.qws"), "rb").read()
+    assert s[:8] == b"QWSNAPS1" and len(s) == 56 + 5 * 4 + 500
+    stats = st.stats()
+    assert stats["blocks"] == 3 and stats["snapshots"] == 1 and stats["disk_bytes"] > 0
+    st.close()
+    # a new store rebuilds its index from the files and serves payloads from disk
+    st2 = H.BlockStore(layout, 2, ram_budget=1 << 20, disk_dir=str(tmp_path), disk_budget=1 << 22)
+    path, depth = st2.lookup(toks)
+    assert path == keys and depth == 2
+    assert st2.info(keys[0]) == {"start": 0, "ntok": 256, "has_snap": False, "in_ram": False, "on_disk": True}
+    assert st2.info(keys[2])["start"] == 512
+    assert st2.get(keys[0]) == bytes([1]) * 1000
+    st2.close()
+    # another layout id: files are unusable and dropped
+    st3 = H.BlockStore(layout + 1, 2, ram_budget=1 << 20, disk_dir=str(tmp_path), disk_budget=1 << 22)
+    assert st3.lookup(toks)[0] == [] and not any(n.endswith(".qwb") for n in os.listdir(str(tmp_path)))
+    st3.close()
+
+
+def test_block_store_truncated_file_is_dropped(tmp_path):
+    st = H.BlockStore(7, 1, 1 << 20, str(tmp_path), 1 << 22)
+    k = st.save_block(st.root, 0, list(range(256)), b"x" * 4096)
+    st.flush()
+    st.close()
+    f = os.path.join(str(tmp_path), f"{k:016x}.qwb")
+    data = open(f, "rb").read()
+    open(f, "wb").write(data[:200])                       # fault injection: a cut-off write
+    st2 = H.BlockStore(7, 1, 1 << 20, str(tmp_path), 1 << 22)
+    assert st2.lookup(list(range(256)))[0] == [] and not os.path.exists(f)
+    st2.close()
+
+
+def test_block_store_ram_budget_evicts_lru_without_disk():
+    st = H.BlockStore(1, 1, ram_budget=2500, disk_dir=None)
+    a = st.save_block(st.root, 0, [1] * 256, b"a" * 1000)
+    b = st.save_block(st.root, 0, [2] * 256, b"b" * 1000)
+    st.lookup([1] * 256)                                  # touch a
+    c = st.save_block(st.root, 0, [3] * 256, b"c" * 1000)
+    assert st.get(b) is None and st.get(a) is not None and st.get(c) is not None
+    assert st.stats()["ram_bytes"] <= 2500
+
+
+def test_sampler_greedy_penalties_and_distribution():
+    s = H.HostSampler(seed=1)
+    logits = np.array([0.1, 2.0, 1.9, -1.0, 0.5], dtype=np.float32)
+    tok, lp = s.sample(logits, H.Sampling.make())
+    assert tok == 1 and abs(lp - (2.0 - np.log(np.exp(logits.astype(np.float64)).sum()))) < 1e-5
+    # repetition + presence penalties move the argmax
+    tok, _ = s.sample(logits, H.Sampling.make(repetition_penalty=2.0), hist=[1], prompt_end=0)
+    assert tok == 2
+    tok, _ = s.sample(logits, H.Sampling.make(presence_penalty=0.5), hist=[1], prompt_end=0)
+    assert tok == 2
+    tok, _ = s.sample(logits, H.Sampling.make(presence_penalty=0.5), hist=[1], prompt_end=1)     # prompt tokens do not count
+    assert tok == 1
+    # top-k 2 never leaves the top two; frequencies follow the renormalised softmax
+    p = H.Sampling.make(temperature=1.0, top_k=2)
+    draws = [s.sample(logits, p)[0] for _ in range(4000)]
+    assert set(draws) == {1, 2}
+    f1 = draws.count(1) / 4000
+    assert abs(f1 - 1 / (1 + np.exp(-0.1))) < 0.03
+    # top-p keeps the smallest prefix reaching p; min-p is relative to the best token
+    assert {s.sample(logits, H.Sampling.make(temperature=1.0, top_p=0.3))[0] for _ in range(200)} == {1}
+    assert {s.sample(logits, H.Sampling.make(temperature=1.0, min_p=0.95))[0] for _ in range(200)} == {1}
+    # a fixed seed gives the same token for the same history length
+    p = H.Sampling.make(temperature=1.0, seed=42)
+    assert len({s.sample(logits, p, hist=[0, 0, 0])[0] for _ in range(20)}) == 1
+    ids, lps = H.HostSampler.top_logprobs(logits, 3)
+    assert ids.tolist() == [1, 2, 4] and lps[0] > lps[1] > lps[2]
+
+
+def test_chunker_tiles_and_is_position_independent():
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, 50000, size=6000).tolist()
+    toks[1500] = 99999                                     # a message boundary
+    ch = H.chunk_prompt(toks, 99999)
+    assert ch[0][0] == 0 and sum(c[1] for c in ch) == len(toks)
+    assert all(a[0] + a[1] == b[0] for a, b in zip(ch, ch[1:]))
+    assert any(c[0] == 1500 for c in ch) and all(c[1] <= 2048 for c in ch)
+    # content-defined: the same text after a different prefix soon falls back into the same chunks
+    ch2 = H.chunk_prompt(rng.integers(0, 50000, size=333).tolist() + toks, 99999)
+    assert len({c[2] for c in ch} & {c[2] for c in ch2}) >= len(ch) - 3

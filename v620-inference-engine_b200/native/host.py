@@ -1,0 +1,218 @@
+"""ctypes bindings of the native host runtime (``libqw_host.so``)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import build as nbuild
+
+_lib = None
+P, LL, ULL, I = C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_int
+
+
+class Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32), ("min_p", C.c_float),
+                ("presence_penalty", C.c_float), ("frequency_penalty", C.c_float), ("repetition_penalty", C.c_float),
+                ("seed", C.c_uint64)]
+
+    @staticmethod
+    def make(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0, presence_penalty=0.0, frequency_penalty=0.0,
+             repetition_penalty=1.0, seed=0) -> "Sampling":
+        return Sampling(temperature, top_p, top_k, min_p, presence_penalty, frequency_penalty, repetition_penalty, seed)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        nbuild.build()
+        L = C.CDLL(nbuild.HOST_LIB)
+        sig = {
+            "qwh_last_error": (C.c_char_p, []),
+            "qwh_ngram_new": (P, [I, I, I, I, LL, ULL, I, I]), "qwh_ngram_free": (None, [P]), "qwh_ngram_total_rows": (LL, [P]),
+            "qwh_ngram_sizes": (I, [P, P, P, P]), "qwh_ngram_ids": (I, [P, P, I, P, I, P]),
+            "qwh_pool_new": (P, [I]), "qwh_pool_free": (None, [P]),
+            "qwh_ple_open": (P, [C.c_char_p, I]), "qwh_ple_free": (None, [P]), "qwh_ple_rows": (LL, [P]), "qwh_ple_layout": (I, [P]),
+            "qwh_ple_gather": (I, [P, P, I, I, P, P]), "qwh_ple_pin": (I, [P, I, I]),
+            "qwh_st_open": (P, [C.c_char_p]), "qwh_st_add": (I, [P, C.c_char_p]), "qwh_st_free": (None, [P]), "qwh_st_count": (I, [P]),
+            "qwh_st_info": (I, [P, C.c_char_p, P, P, P, P, P]),
+            "qwh_store_new": (P, [ULL, C.c_uint, ULL, C.c_char_p, ULL]), "qwh_store_free": (None, [P]), "qwh_store_root": (ULL, []),
+            "qwh_block_key": (ULL, [ULL, P, I]), "qwh_store_save_block": (ULL, [P, ULL, LL, P, I, P, ULL]),
+            "qwh_store_save_snapshot": (I, [P, ULL, P, ULL, P, I, I]), "qwh_store_lookup": (I, [P, P, LL, P, I, P]),
+            "qwh_store_get": (LL, [P, ULL, I, P, ULL, P, I, P]), "qwh_store_block_info": (I, [P, ULL, P, P, P, P, P]),
+            "qwh_store_note_restore": (None, [P, ULL, LL]), "qwh_store_flush": (None, [P]), "qwh_store_thin": (I, [P, LL]),
+            "qwh_store_stats": (None, [P, P]),
+            "qwh_rng_new": (P, [ULL]), "qwh_rng_free": (None, [P]), "qwh_sample": (I, [P, I, P, P, LL, LL, P, P]),
+            "qwh_top_logprobs": (I, [P, I, I, P, P]), "qwh_lse": (C.c_float, [P, I]),
+            "qwh_chunk": (I, [P, LL, I, P, P, P, I]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def _err() -> str:
+    return (lib().qwh_last_error() or b"").decode()
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int32))
+
+
+class NgramHasher:
+    def __init__(self, cfg):
+        self.cfg = cfg
+        self.h = lib().qwh_ngram_new(cfg.vocab, cfg.eos, cfg.ngram, cfg.ngram_heads, cfg.ngram_vocab_base, cfg.ple_seed,
+                                     cfg.image_pad, cfg.video_pad)
+        if not self.h:
+            raise RuntimeError(_err())
+        self.total_rows = lib().qwh_ngram_total_rows(self.h)
+
+    def ids_for(self, history: Sequence[int], tokens: Sequence[int]) -> np.ndarray:
+        h, t = _i32(history), _i32(tokens)
+        out = np.zeros((len(t), self.cfg.ngram_heads), dtype=np.int64)
+        if lib().qwh_ngram_ids(self.h, h.ctypes.data, len(h), t.ctypes.data, len(t), out.ctypes.data) != 0:
+            raise RuntimeError(_err())
+        return out
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().qwh_ngram_free(self.h)
+            self.h = None
+
+
+class PleTableNative:
+    def __init__(self, path: str, width: int, threads: int = 8):
+        self.t = lib().qwh_ple_open(path.encode(), width)
+        if not self.t:
+            raise RuntimeError(_err())
+        self.width = width
+        self.pool = lib().qwh_pool_new(threads)
+        self.rows = lib().qwh_ple_rows(self.t)
+
+    def gather(self, ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, dtype=np.int64)
+        T, heads = ids.shape
+        out = np.empty((T, heads * self.width), dtype=np.float32)
+        if lib().qwh_ple_gather(self.t, ids.ctypes.data, T, heads, out.ctypes.data, self.pool) != 0:
+            raise RuntimeError(_err())
+        return out
+
+    def pin(self, lock: bool = True, wait: bool = False):
+        lib().qwh_ple_pin(self.t, int(lock), int(wait))
+
+    def __del__(self):
+        if getattr(self, "t", None):
+            lib().qwh_ple_free(self.t)
+            lib().qwh_pool_free(self.pool)
+            self.t = None
+
+
+class BlockStore:
+    """Prefix cache over opaque payloads; see src/block_store.hpp."""
+    BLOCK = 256
+
+    def __init__(self, layout: int, ranks: int, ram_budget: int, disk_dir: Optional[str] = None, disk_budget: int = 0):
+        self.s = lib().qwh_store_new(layout, ranks, ram_budget, disk_dir.encode() if disk_dir else None, disk_budget)
+        if not self.s:
+            raise RuntimeError(_err())
+        self.root = lib().qwh_store_root()
+
+    def close(self):
+        if self.s:
+            lib().qwh_store_free(self.s)
+            self.s = None
+
+    __del__ = close
+
+    @staticmethod
+    def key(parent: int, tokens: Sequence[int]) -> int:
+        t = _i32(tokens)
+        return lib().qwh_block_key(parent, t.ctypes.data, len(t))
+
+    def save_block(self, parent: int, start: int, tokens: Sequence[int], kv: bytes) -> int:
+        t = _i32(tokens)
+        buf = (C.c_char * len(kv)).from_buffer_copy(kv)
+        return lib().qwh_store_save_block(self.s, parent, start, t.ctypes.data, len(t), C.addressof(buf), len(kv))
+
+    def save_snapshot(self, key: int, snap: bytes, logits: Optional[np.ndarray] = None, anchor: bool = False) -> bool:
+        buf = (C.c_char * len(snap)).from_buffer_copy(snap)
+        lg = None if logits is None else np.ascontiguousarray(logits, dtype=np.float32)
+        return lib().qwh_store_save_snapshot(self.s, key, C.addressof(buf), len(snap), None if lg is None else lg.ctypes.data,
+                                             0 if lg is None else lg.size, int(anchor)) == 0
+
+    def lookup(self, tokens: Sequence[int]) -> Tuple[List[int], int]:
+        t = _i32(tokens)
+        keys = (C.c_ulonglong * (len(t) // self.BLOCK + 2))()
+        depth = C.c_int(0)
+        n = lib().qwh_store_lookup(self.s, t.ctypes.data, len(t), keys, len(keys), C.byref(depth))
+        return [int(keys[i]) for i in range(max(n, 0))], depth.value
+
+    def get(self, key: int, snapshot: bool = False):
+        nl = C.c_int(0)
+        size = lib().qwh_store_get(self.s, key, int(snapshot), None, 0, None, 0, C.byref(nl))
+        if size < 0:
+            return None
+        buf = C.create_string_buffer(size)
+        lg = np.empty(nl.value, dtype=np.float32)
+        lib().qwh_store_get(self.s, key, int(snapshot), buf, size, lg.ctypes.data if nl.value else None, nl.value, C.byref(nl))
+        return (buf.raw, lg) if snapshot else buf.raw
+
+    def info(self, key: int):
+        st, nt, hs, ram, dk = LL(0), I(0), I(0), I(0), I(0)
+        if lib().qwh_store_block_info(self.s, key, C.byref(st), C.byref(nt), C.byref(hs), C.byref(ram), C.byref(dk)) != 0:
+            return None
+        return {"start": st.value, "ntok": nt.value, "has_snap": bool(hs.value), "in_ram": bool(ram.value), "on_disk": bool(dk.value)}
+
+    def note_restore(self, key: int, tokens: int):
+        lib().qwh_store_note_restore(self.s, key, tokens)
+
+    def flush(self):
+        lib().qwh_store_flush(self.s)
+
+    def thin(self, gap: int) -> int:
+        return lib().qwh_store_thin(self.s, gap)
+
+    def stats(self) -> dict:
+        out = (C.c_ulonglong * 7)()
+        lib().qwh_store_stats(self.s, out)
+        names = ["hits", "tokens_restored", "snapshots_saved", "ram_bytes", "disk_bytes", "blocks", "snapshots"]
+        return dict(zip(names, [int(x) for x in out]))
+
+
+class HostSampler:
+    def __init__(self, seed: int = 0):
+        self.rng = lib().qwh_rng_new(seed)
+
+    def sample(self, logits: np.ndarray, p: Sampling, hist: Sequence[int] = (), prompt_end: int = 0) -> Tuple[int, float]:
+        lg = np.ascontiguousarray(logits, dtype=np.float32)
+        h = _i32(hist)
+        lp = C.c_float(0)
+        tok = lib().qwh_sample(lg.ctypes.data, lg.size, C.byref(p), h.ctypes.data, len(h), prompt_end, self.rng, C.byref(lp))
+        if tok < 0:
+            raise RuntimeError(_err())
+        return tok, lp.value
+
+    @staticmethod
+    def top_logprobs(logits: np.ndarray, k: int):
+        lg = np.ascontiguousarray(logits, dtype=np.float32)
+        ids, lps = np.zeros(k, dtype=np.int32), np.zeros(k, dtype=np.float32)
+        n = lib().qwh_top_logprobs(lg.ctypes.data, lg.size, k, ids.ctypes.data, lps.ctypes.data)
+        return ids[:n], lps[:n]
+
+    def __del__(self):
+        if getattr(self, "rng", None):
+            lib().qwh_rng_free(self.rng)
+            self.rng = None
+
+
+def chunk_prompt(tokens: Sequence[int], boundary: int):
+    t = _i32(tokens)
+    cap = len(t) // 128 + 8
+    st, ln, hs = np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.uint64)
+    n = lib().qwh_chunk(t.ctypes.data, len(t), boundary, st.ctypes.data, ln.ctypes.data, hs.ctypes.data, cap)
+    return [(int(st[i]), int(ln[i]), int(hs[i])) for i in range(min(n, cap))]
