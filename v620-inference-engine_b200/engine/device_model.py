@@ -105,8 +105,24 @@ class DeviceModel:
         self.gdn_S = [z(self.slots, sc.gdn_vl, c.gdn_dim, c.gdn_dim) for _ in range(c.n_gdn)]
         self.gdn_ring = [z(self.slots, GDN_RING, sc.gdn_qkv_l) for _ in range(c.n_gdn)]
         self.ple_ring = z(self.slots, PLE_RING, sc.xw)
-        # identity paging by default: slot s owns pages [s*max_pages, (s+1)*max_pages)
-        pt = torch.arange(self.slots * self.max_pages, dtype=torch.int32).view(self.slots, self.max_pages)
+        # Paging.  Everything on the device: slot s owns pages [s*max_pages, (s+1)*max_pages).  With a smaller
+        # device pool every slot keeps its first `quota` pages in HBM and the rest of its pages live in the
+        # pinned host pool (KV spill): page ids >= n_dev_pages address host memory, which the kernels read directly.
+        total = self.slots * self.max_pages
+        if self.n_dev_pages >= total:
+            pt = torch.arange(total, dtype=torch.int32).view(self.slots, self.max_pages)
+            self.dev_quota = self.max_pages
+        else:
+            quota = self.n_dev_pages // self.slots
+            spill = self.max_pages - quota
+            if self.n_host_pages < self.slots * spill:
+                raise ValueError("host_pages too small for the requested KV spill")
+            pt = torch.empty((self.slots, self.max_pages), dtype=torch.int32)
+            for s_ in range(self.slots):
+                pt[s_, :quota] = torch.arange(s_ * quota, (s_ + 1) * quota)
+                pt[s_, quota:] = self.n_dev_pages + torch.arange(s_ * spill, (s_ + 1) * spill)
+            self.dev_quota = quota
+        self.page_table_host = pt.clone()
         self.page_table = pt.to(dv)
         st = self.model.st
 

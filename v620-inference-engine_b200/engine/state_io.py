@@ -1,0 +1,117 @@
+"""Slot state export / import: KV pages for the prefix cache's blocks, recurrent state for snapshots,
+VRAM snapshots and slot copies.
+
+A KV block = one page (256 tokens) of every QSA layer; its payload per rank is, layer by layer,
+``K[n][row] bf16 | V[n][row] bf16 | ck[n/4][128] bf16`` — the reference's block payload
+(src/engine/host_tier.hip:23-30,78-90) with bf16 where it stores fp16.  The recurrent payload is
+``GDN S | GDN conv ring | PLE ring | raw-key ring`` in fp32 (host_tier.hip:121-137).  A saved state is
+valid only for the same ``state_layout_id`` (host_tier.hip:269-281): an FNV-1a hash of a version and
+every shape that enters the payloads.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import numpy as np
+import torch
+
+from .device_model import DeviceModel, KV_PAGE
+
+LAYOUT_VERSION = 1
+
+
+def _fnv(vals) -> int:
+    h = 0xcbf29ce484222325
+    for v in vals:
+        for b in int(v).to_bytes(8, "little", signed=False):
+            h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+class StateIO:
+    def __init__(self, dm: DeviceModel):
+        self.dm = dm
+        c, sc = dm.cfg, dm.sc
+        self.row = sc.kvh_l * c.head_dim
+        self.groups = KV_PAGE // c.idx_ratio
+        self.kv_page_elems = 2 * KV_PAGE * self.row + self.groups * c.idx_dim      # per layer, bf16 elements
+        self.kv_block_bytes = c.n_qsa * self.kv_page_elems * 2
+
+    def state_layout_id(self) -> int:
+        c, sc = self.dm.cfg, self.dm.sc
+        return _fnv([LAYOUT_VERSION, sc.ranks, c.n_layers, c.n_qsa, c.n_gdn, self.row, c.idx_dim, c.idx_ratio, KV_PAGE,
+                     sc.gdn_vl, c.gdn_dim, sc.gdn_qkv_l, sc.xw, self.dm.gdn_ring[0].shape[1] if c.n_gdn else 0,
+                     self.dm.ple_ring.shape[1], self.dm.raw_ring[0].shape[1] if c.n_qsa else 0])
+
+    # ---- KV pages
+    def _page_views(self, slot: int, page_index: int):
+        dm = self.dm
+        pid = int(dm.page_table_host[slot, page_index])
+        out = []
+        for qi in range(dm.cfg.n_qsa):
+            if pid < dm.n_dev_pages:
+                k, v = dm.k_dev[qi][pid], dm.v_dev[qi][pid]
+            else:
+                k, v = dm.k_host[qi][pid - dm.n_dev_pages], dm.v_host[qi][pid - dm.n_dev_pages]
+            ck = dm.ck[qi][slot, page_index * self.groups:(page_index + 1) * self.groups]
+            out.append((k, v, ck))
+        return out
+
+    def export_kv(self, slot: int, page_index: int) -> bytes:
+        parts = []
+        for k, v, ck in self._page_views(slot, page_index):
+            parts += [k.reshape(-1).to(self.dm.dev), v.reshape(-1).to(self.dm.dev), ck.reshape(-1)]
+        return torch.cat(parts).view(torch.int16).cpu().numpy().tobytes()
+
+    def import_kv(self, slot: int, page_index: int, payload: bytes) -> None:
+        assert len(payload) == self.kv_block_bytes, "KV block size does not match this engine's layout"
+        t = torch.from_numpy(np.frombuffer(payload, dtype=np.int16).copy()).view(torch.bfloat16)
+        off = 0
+        for k, v, ck in self._page_views(slot, page_index):
+            for dst in (k, v, ck):
+                n = dst.numel()
+                dst.copy_(t[off:off + n].view(dst.shape).to(dst.device))
+                off += n
+
+    # ---- recurrent state
+    def _recurrent_tensors(self, slot: int) -> List[torch.Tensor]:
+        dm = self.dm
+        ts = [t[slot] for t in dm.gdn_S] + [t[slot] for t in dm.gdn_ring] + [dm.ple_ring[slot]] + [t[slot] for t in dm.raw_ring]
+        return ts
+
+    def recurrent_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in self._recurrent_tensors(0))
+
+    def export_recurrent(self, slot: int) -> bytes:
+        return torch.cat([t.reshape(-1) for t in self._recurrent_tensors(slot)]).cpu().numpy().tobytes()
+
+    def import_recurrent(self, slot: int, payload: bytes) -> None:
+        t = torch.from_numpy(np.frombuffer(payload, dtype=np.float32).copy()).to(self.dm.dev)
+        off = 0
+        for dst in self._recurrent_tensors(slot):
+            n = dst.numel()
+            dst.copy_(t[off:off + n].view(dst.shape))
+            off += n
+        assert off == t.numel(), "recurrent payload size does not match this engine's layout"
+
+    # ---- VRAM snapshots / slot copy
+    def snapshot_save(self, slot: int):
+        """Recurrent state kept on the device (cheap: no host round trip)."""
+        return [t.clone() for t in self._recurrent_tensors(slot)]
+
+    def snapshot_restore(self, slot: int, snap) -> None:
+        for dst, src in zip(self._recurrent_tensors(slot), snap):
+            dst.copy_(src)
+
+    def slot_copy(self, src: int, dst: int, n_tokens: int) -> None:
+        """Make ``dst`` hold the first ``n_tokens`` of ``src`` (whole pages of KV + the recurrent state as it
+        is now: the caller copies at a point where the state matches ``n_tokens``)."""
+        dm = self.dm
+        pages = (n_tokens + KV_PAGE - 1) // KV_PAGE
+        for p in range(pages):
+            for (ks, vs, cs), (kd, vd, cd) in zip(self._page_views(src, p), self._page_views(dst, p)):
+                kd.copy_(ks)
+                vd.copy_(vs)
+                cd.copy_(cs)
+        for d, s in zip(self._recurrent_tensors(dst), self._recurrent_tensors(src)):
+            d.copy_(s)
