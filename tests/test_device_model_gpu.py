@@ -180,3 +180,41 @@ def test_token_major_prefill_matches_stepwise_decode():
         if ta != tb:
             break
     assert agree >= 8
+
+
+def test_speculative_greedy_equals_plain_and_mtp_matches_oracle():
+    """MTP drafts + verification give exactly the plain greedy tokens; the MTP head's logits match the oracle."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.models.ple import PleTable
+    from qwb200.models.reference import RefModel
+    from qwb200.models.weights import synth_weights
+    cfg = ModelConfig.tiny()
+    w = synth_weights(cfg, seed=13)
+    table = PleTable.synthetic(cfg, rows=4096, layout="f8", seed=13)
+    prompt = torch.randint(0, cfg.vocab, (70,), generator=torch.Generator().manual_seed(6)).tolist()
+    plain = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=False, save_gdn=True))
+    plain.prefill(0, prompt)
+    first = int(plain.dm.buf["amax_idx"][plain.last_prefill_row])
+    want = plain.generate_greedy(0, first, 24, k=0)
+    for chunked in (0, 128):
+        spec = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=False, save_gdn=True,
+                                                                prefill_chunk=chunked))
+        assert spec.mtp
+        spec.prefill(0, prompt)
+        assert int(spec.dm.buf["amax_idx"][spec.last_prefill_row]) == first
+        got = spec.generate_greedy(0, first, 24, k=3)
+        assert got == want, (chunked, got, want)
+        assert spec.spec_steps <= 24
+    # MTP logits against the fp32 oracle: draft for the position after `first`
+    ref = RefModel(cfg, w, table)
+    st = ref.new_state()
+    _, hid = ref.forward(st, prompt, return_hidden=True)
+    dl, _ = ref.mtp_forward(st, hid, prompt[1:] + [first], base=0)
+    eng = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=False, prefill_chunk=0))
+    eng.prefill(0, prompt)
+    eng.dm.buf["hidden_out"][0] = eng.slot[0].mtp_hidden
+    eng.dm.mtp_step([first], [0], [len(prompt) - 1])
+    torch.cuda.synchronize()
+    got = eng.dm.buf["logits"][0].cpu()
+    assert rel(got, dl[-1]) < 4e-2

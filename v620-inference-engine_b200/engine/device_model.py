@@ -92,16 +92,17 @@ class DeviceModel:
     def _alloc_state(self):
         c, sc, dv = self.cfg, self.sc, self.dev
         row = sc.kvh_l * c.head_dim
+        nkv = c.n_qsa + (1 if c.mtp else 0)      # the MTP layer keeps its own KV / indexer state at index n_qsa
         z = lambda *shape, dtype=torch.float32: torch.zeros(*shape, dtype=dtype, device=dv)
-        self.k_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(c.n_qsa)]
-        self.v_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(c.n_qsa)]
+        self.k_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(nkv)]
+        self.v_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(nkv)]
         self.k_host = self.v_host = None
         if self.n_host_pages:
             hp = lambda: torch.zeros(self.n_host_pages, KV_PAGE, row, dtype=torch.bfloat16).pin_memory()
-            self.k_host = [hp() for _ in range(c.n_qsa)]
-            self.v_host = [hp() for _ in range(c.n_qsa)]
-        self.ck = [z(self.slots, self.slot_tokens // c.idx_ratio, c.idx_dim, dtype=torch.bfloat16) for _ in range(c.n_qsa)]
-        self.raw_ring = [z(self.slots, RAW_RING, c.idx_dim) for _ in range(c.n_qsa)]
+            self.k_host = [hp() for _ in range(nkv)]
+            self.v_host = [hp() for _ in range(nkv)]
+        self.ck = [z(self.slots, self.slot_tokens // c.idx_ratio, c.idx_dim, dtype=torch.bfloat16) for _ in range(nkv)]
+        self.raw_ring = [z(self.slots, RAW_RING, c.idx_dim) for _ in range(nkv)]
         self.gdn_S = [z(self.slots, sc.gdn_vl, c.gdn_dim, c.gdn_dim) for _ in range(c.n_gdn)]
         self.gdn_ring = [z(self.slots, GDN_RING, sc.gdn_qkv_l) for _ in range(c.n_gdn)]
         self.ple_ring = z(self.slots, PLE_RING, sc.xw)
@@ -231,6 +232,66 @@ class DeviceModel:
             p = self.model.ple
             for k in ("Wkv", "nk1", "nq1", "nc1", "cw"):
                 setattr(p, k, pw[k].data_ptr())
+
+    def _layer_struct(self, st, lw, state_index: int):
+        st.is_qsa = 1 if lw["is_qsa"] else 0
+        st.state_index = state_index
+        st.attn_hc, st.mlp_hc = self._hc_struct(lw["attn_hc"]), self._hc_struct(lw["mlp_hc"])
+        for k in ("Wproj", "Wout", "Wrs", "w13", "s13", "w2", "s2", "Wsd"):
+            setattr(st, k, lw[k].data_ptr())
+        for k in ("cw", "A_log", "dt_bias", "gdn_norm", "qn1", "kn1", "iqn1", "ikn1"):
+            setattr(st, k, lw[k].data_ptr() if k in lw else None)
+
+    def set_mtp(self, w: Weights):
+        """Install the MTP head (a QSA decoder layer with its own mixer, the two fc matrices and norms)."""
+        c, sc, dv = self.cfg, self.sc, self.dev
+        if sc.ranks != 1:
+            raise NotImplementedError("the MTP head runs on one GPU")
+        lw = WP.prep_layer(c, w, c.n_layers, sc, dv, prefix="mtp.layers.0.", qsa=True)
+        fin = WP.prep_hc(w, "mtp.hyper_connection_mixer.", sc, False, dv)
+        R = self.max_rows
+        m = self.model.mtp
+        self.mtp_w = {
+            "layer": lw, "final_hc": fin,
+            "fc_h": w["mtp.fc_hidden.weight"].to(dv).to(torch.bfloat16).contiguous(),
+            "fc_e": w["mtp.fc_embedding.weight"].to(dv).to(torch.bfloat16).contiguous(),
+            "nh1": (1.0 + w["mtp.pre_fc_norm_hidden.weight"].to(dv).float()).contiguous(),
+            "ne1": (1.0 + w["mtp.pre_fc_norm_embedding.weight"].to(dv).float()).contiguous(),
+            "hn": torch.zeros((R * c.hc, c.hidden), dtype=torch.bfloat16, device=dv),
+            "en": torch.zeros((R, c.hidden), dtype=torch.bfloat16, device=dv),
+            "fh": torch.zeros((R * c.hc, c.hidden), dtype=torch.float32, device=dv),
+            "fe": torch.zeros((R, c.hidden), dtype=torch.float32, device=dv),
+        }
+        self._layer_struct(m.layer, lw, c.n_qsa)
+        m.final_hc = self._hc_struct(fin)
+        for k in ("fc_h", "fc_e", "nh1", "ne1", "hn", "en", "fh", "fe"):
+            setattr(m, k, self.mtp_w[k].data_ptr())
+        m.enabled = 1
+
+    def launch_mtp(self, flags: int = 0):
+        s = torch.cuda.current_stream(self.dev).cuda_stream
+        rc = self.lib.qwrt_mtp(C.byref(self.model), C.byref(self.rows), flags, C.c_void_p(s))
+        if rc != 0:
+            raise RuntimeError(f"qwrt_mtp failed: {rc}")
+
+    def mtp_step(self, tokens, slots, pos, flags: int = 0, graph: bool = False):
+        """One MTP pass: buf['hidden_out'] holds the rows' hidden states, ``tokens`` the tokens after them."""
+        self.stage_rows(tokens, slots, pos, None)
+        if not graph:
+            self.launch_mtp(flags)
+            return
+        key = ("mtp", len(tokens), flags)
+        g = self.graphs.get(key)
+        if g is None:
+            self.rows.max_groups = self.model.d.ck_cap
+            self.launch_mtp(flags)
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.launch_mtp(flags)
+            self.graphs[key] = g
+            return
+        g.replay()
 
     def set_globals(self, w: Weights):
         g = WP.prep_globals(self.cfg, w, self.sc, self.dev)

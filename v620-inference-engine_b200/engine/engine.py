@@ -24,6 +24,7 @@ from .device_model import DeviceModel
 @dataclass
 class Slot:
     tokens: List[int] = field(default_factory=list)     # every token fed so far (vision tokens negative)
+    mtp_hidden: Optional[torch.Tensor] = None            # backbone hidden of the last fed position (MTP input)
 
     @property
     def n(self) -> int:
@@ -42,6 +43,7 @@ class EngineOptions:
     prefill_rows: int = DM.MAX_ROWS          # rows per step of the row-batched prefill
     prefill_chunk: int = 4096                # tokens per chunk of the token-major (tcgen05 GEMM) prefill; 0 = off
     prefill_min: int = 64                    # shorter pieces use the row-batched path
+    mtp_track: bool = False                  # plain decode steps also keep the newest hidden state for the MTP head
 
 
 class Engine:
@@ -73,6 +75,10 @@ class Engine:
                 log(f"layer {L + 1}/{cfg.n_layers} ready, {e.dm.weight_bytes() / 1e9:.1f} GB, {time.time() - t0:.0f} s")
         table = PleTable.synthetic(cfg, rows=ple_rows, layout="f8", seed=seed, pin=ple_pinned)
         e.dm.set_ple_table(table)
+        if cfg.mtp and ranks == 1:
+            g = synth_globals(cfg, seed, device=device)
+            g.update(synth_layer(cfg, cfg.n_layers, seed, device=device, exact=exact, prefix="mtp.layers.0.", qsa=True))
+            e.dm.set_mtp(g)
         torch.cuda.synchronize(device)
         return e
 
@@ -85,6 +91,8 @@ class Engine:
             e.dm.set_layer(L, w)
         if table is not None:
             e.dm.set_ple_table(table)
+        if cfg.mtp and ranks == 1 and "mtp.fc_hidden.weight" in w:
+            e.dm.set_mtp(w)
         return e
 
     # ---- slots
@@ -122,8 +130,12 @@ class Engine:
                 raise ValueError("slot capacity exceeded")
             last = i + len(chunk) >= n
             flags = 0 if (last and want_logits) else DM.FLAG_NO_HEAD
+            if self.mtp:
+                flags |= DM.FLAG_KEEP_HIDDEN
             self.dm.step(chunk, [slot] * len(chunk), list(range(base, base + len(chunk))), self._ctx3(slot, chunk),
                          flags=flags, graph=False)
+            if self.mtp:
+                self._mtp_rows(slot, base, chunk)
             self.slot[slot].tokens.extend(chunk)
             i += len(chunk)
         self.steps += 1
@@ -133,6 +145,95 @@ class Engine:
             self.last_prefill_row = (n - 1) % step if n % step else step - 1
             return self.dm.buf["logits"][self.last_prefill_row]
         return None
+
+    # ---- MTP / speculative decoding (one GPU)
+    @property
+    def mtp(self) -> bool:
+        return bool(self.dm.model.mtp.enabled)
+
+    def _mtp_rows(self, slot: int, base: int, chunk: List[int]):
+        """After a backbone step over ``chunk`` at positions base.. (hidden states in buf['hidden_out']): run the MTP
+        rows whose next token is known (all but the last), first the row left over from the previous call."""
+        dm, sl = self.dm, self.slot[slot]
+        hid = dm.buf["hidden_out"]
+        n = len(chunk)
+        keep = hid[n - 1].clone()
+        # logits / argmax of the backbone step must survive the MTP pass
+        saved = (dm.buf["logits"][:n].clone(), dm.buf["amax_idx"][:n].clone(), dm.buf["amax_val"][:n].clone())
+        if sl.mtp_hidden is not None and base > 0:
+            # shift the rows down by one and put the pending hidden in front: rows = positions base-1 .. base+n-2
+            hid[1:n] = hid[0:n - 1].clone()
+            hid[0] = sl.mtp_hidden
+            dm.mtp_step(chunk, [slot] * n, list(range(base - 1, base - 1 + n)))
+        elif n > 1:
+            dm.mtp_step(chunk[1:], [slot] * (n - 1), list(range(base, base + n - 1)))
+        sl.mtp_hidden = keep
+        dm.buf["logits"][:n].copy_(saved[0])
+        dm.buf["amax_idx"][:n].copy_(saved[1])
+        dm.buf["amax_val"][:n].copy_(saved[2])
+
+    def draft(self, slot: int, pending: int, k: int) -> List[int]:
+        """k greedy draft tokens after ``pending`` (the sampled token that has not been decoded yet): one MTP row
+        from the backbone hidden of the last position, then chained rows from the MTP's own hidden."""
+        dm, sl = self.dm, self.slot[slot]
+        assert self.mtp and sl.mtp_hidden is not None
+        dm.buf["hidden_out"][0] = sl.mtp_hidden
+        pos = sl.n - 1
+        out, tok = [], pending
+        for j in range(k):
+            dm.mtp_step([tok], [slot], [pos + j], graph=self.opts.use_graphs)
+            tok = int(dm.buf["amax_idx"][0])
+            out.append(tok)
+        return out
+
+    def verify(self, slot: int, rows: List[int]) -> torch.Tensor:
+        """Decode ``rows`` = [pending, draft 1, ...] as one run, keeping the GDN state after every row and the hidden
+        states.  Returns the logits [len(rows), vocab] (device)."""
+        dm = self.dm
+        base = self.slot[slot].n
+        n = len(rows)
+        dm.step(rows, [slot] * n, list(range(base, base + n)), self._ctx3(slot, rows),
+                flags=DM.FLAG_SAVE_GDN | DM.FLAG_KEEP_HIDDEN, graph=self.opts.use_graphs)
+        return dm.buf["logits"][:n]
+
+    def accept(self, slot: int, rows: List[int], n_acc: int):
+        """Keep the first ``n_acc`` rows of the last verify: the GDN state after row n_acc-1 becomes the slot's state."""
+        dm, sl = self.dm, self.slot[slot]
+        if n_acc < len(rows):
+            save = dm.buf["gdn_save"]
+            for gi in range(self.cfg.n_gdn):
+                dm.gdn_S[gi][slot].copy_(save[gi, n_acc - 1])
+        base = sl.n
+        sl.mtp_hidden = dm.buf["hidden_out"][n_acc - 1].clone()
+        if n_acc == len(rows) and n_acc >= 2:
+            # every draft was accepted: the MTP layer has no row yet for the position of the last-but-one row
+            # (its next token, the last draft, is only now confirmed)
+            dm.buf["hidden_out"][0] = dm.buf["hidden_out"][n_acc - 2].clone()
+            dm.mtp_step([rows[n_acc - 1]], [slot], [base + n_acc - 2])
+        sl.tokens.extend(int(t) for t in rows[:n_acc])
+
+    def generate_greedy(self, slot: int, pending: int, n_new: int, k: int = 0) -> List[int]:
+        """Greedy continuation of ``n_new`` tokens; with k > 0 drafts are verified (the result equals k = 0)."""
+        out: List[int] = []
+        self.spec_steps = self.spec_accepted = 0
+        while len(out) < n_new:
+            if k <= 0 or not self.mtp:
+                pending = self.decode([slot], [pending])[0]
+                out.append(pending)
+                continue
+            drafts = self.draft(slot, pending, k)
+            rows = [pending] + drafts
+            logits = self.verify(slot, rows)
+            picks = torch.argmax(logits, dim=-1).tolist()
+            n_acc = 1
+            while n_acc <= k and picks[n_acc - 1] == drafts[n_acc - 1]:
+                n_acc += 1
+            self.accept(slot, rows, n_acc)
+            out.extend(picks[:n_acc])
+            pending = picks[n_acc - 1]
+            self.spec_steps += 1
+            self.spec_accepted += n_acc - 1
+        return out[:n_new]
 
     def _prefill_token_major(self, slot: int, toks: List[int], want_logits: bool):
         from .prefill import Prefiller
@@ -145,7 +246,22 @@ class Engine:
         for i in range(0, len(toks), T):
             chunk = toks[i:i + T]
             last = i + T >= len(toks)
-            out = self.prefiller.run(slot, self.slot[slot].n, chunk, self._ctx3(slot, chunk), want_logits and last)
+            base = self.slot[slot].n
+            out = self.prefiller.run(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last)
+            if self.mtp:
+                # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
+                sl = self.slot[slot]
+                keep = self.prefiller.b["X"][len(chunk) - 1].clone()
+                if sl.mtp_hidden is not None and base > 0:
+                    self.dm.buf["hidden_out"][0] = sl.mtp_hidden
+                    self.dm.mtp_step([chunk[0]], [slot], [base - 1])
+                if want_logits and last:
+                    saved = (self.dm.buf["logits"][:1].clone(), self.dm.buf["amax_idx"][:1].clone())
+                self.prefiller.mtp_pass(slot, base, len(chunk), chunk[1:])
+                if want_logits and last:
+                    self.dm.buf["logits"][:1].copy_(saved[0])
+                    self.dm.buf["amax_idx"][:1].copy_(saved[1])
+                sl.mtp_hidden = keep
             self.slot[slot].tokens.extend(chunk)
         self.steps += 1
         self.last_prefill_row = 0           # logits / argmax of the last token sit in row 0
@@ -173,7 +289,15 @@ class Engine:
             if len(h) >= 2:
                 rows3[i, 2] = self.cfg.real_token(h[-2])
             h.append(int(t))
+        track = self.mtp and self.opts.mtp_track
+        if track:
+            flags |= DM.FLAG_KEEP_HIDDEN
         self.dm.step(list(tokens), list(slots), pos, rows3, flags=flags, graph=self.opts.use_graphs)
+        if track:
+            # plain steps leave the MTP layer one row behind per token: remember the newest hidden per slot; the rows in
+            # between are caught up by _mtp_rows the next time drafts are wanted (here: simply dropped for rows > 1 back)
+            for i, s_ in enumerate(slots):
+                self.slot[s_].mtp_hidden = self.dm.buf["hidden_out"][i].clone()
         for s, t in zip(slots, tokens):
             self.slot[s].tokens.append(int(t))
         self.steps += 1

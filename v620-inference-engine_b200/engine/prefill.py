@@ -113,6 +113,7 @@ class Prefiller:
         assert 1 <= T <= self.T
         s = self._s()
         rows = self._rows(slot, base, T, [c.real_token(int(t)) for t in tokens], np.asarray(ctx3, dtype=np.int32))
+        self._last_rows = rows
         rp = lambda k, off=0: P(rows[k] + 4 * off)
         d = dm.model.d
         self._ck(L.qwk_embed_rows(rp("tokens"), P(dm.globals_w["embed"].data_ptr()), c.hidden, 0, sc.sh, c.hc, c.vocab,
@@ -140,52 +141,7 @@ class Prefiller:
                                          c.ple_dilation, _p(b["ple_gv"]), _p(b["ple_nc"]), _p(dm.ple_ring), _p(b["X"]), T,
                                          rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), s), "ple_apply")
             self.mix(lw["attn_hc"], T, pend, inj_prev, inj_attn, c.hc)
-            if lw["is_qsa"]:
-                qi = c.qsa_index(li)
-                self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.qsa_proj_l, c.hidden, b["proj"][:T])
-                ldp = self.proj_ld
-                kd, vd = dm.k_dev[qi].data_ptr(), dm.v_dev[qi].data_ptr()
-                kh = dm.k_host[qi].data_ptr() if dm.k_host else None
-                vh = dm.v_host[qi].data_ptr() if dm.v_host else None
-                self._ck(L.qwk_qsa_prep(_p(b["proj"]), ldp, sc.qh_l, sc.kvh_l, c.idx_heads, P(lw["qn1"].data_ptr()),
-                                        P(lw["kn1"].data_ptr()), P(lw["iqn1"].data_ptr()), P(lw["ikn1"].data_ptr()), T,
-                                        rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), P(kd), P(vd), P(kh) if kh else None,
-                                        P(vh) if vh else None, d.n_dev_pages, _p(dm.page_table), d.max_pages, _p(b["q"]),
-                                        _p(b["iq"]), _p(dm.raw_ring[qi]), _p(dm.ck[qi]), d.ck_cap, c.idx_ratio,
-                                        C.c_float(c.eps), s), "qsa_prep")
-                self._ck(L.qwk_qsa_scores(_p(b["iq"]), c.idx_heads, _p(dm.ck[qi]), d.ck_cap, T, rp("slot"), rp("pos"),
-                                          c.idx_ratio, c.idx_topk_blocks, _p(b["scores"]), d.score_cap, max_groups, s), "scores")
-                self._ck(L.qwk_qsa_select(_p(b["scores"]), d.score_cap, T, rp("pos"), c.idx_ratio, c.idx_topk_blocks,
-                                          _p(b["sel"]), _p(b["sel_n"]), s), "select")
-                A = self.attn_rows
-                ow = sc.qh_l * c.head_dim
-                for r0 in range(0, T, A):
-                    n = min(A, T - r0)
-                    self._ck(L.qwk_qsa_attend(P(b["q"].data_ptr() + 4 * r0 * ow), sc.qh_l, sc.kvh_l, n, rp("slot", r0),
-                                              rp("pos", r0), P(kd), P(vd), P(kh) if kh else None, P(vh) if vh else None,
-                                              d.n_dev_pages, _p(dm.page_table), d.max_pages,
-                                              P(b["sel"].data_ptr() + 4 * r0 * c.idx_topk_blocks),
-                                              P(b["sel_n"].data_ptr() + 4 * r0), c.idx_topk_blocks, c.idx_ratio, d.nsplit,
-                                              _p(b["pm"]), _p(b["pl"]), _p(b["pacc"]), P(b["proj"].data_ptr() + 4 * r0 * ldp),
-                                              ldp, P(b["o"].data_ptr() + 2 * r0 * ow), s), "attend")
-                # the attention kernels write o rows densely ([T][QL*256])
-                self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
-                                            c.hidden, 0, s), "o_proj")
-            else:
-                gi = c.gdn_index(li)
-                self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.gdn_proj_l, c.hidden, b["proj"][:T])
-                ldp = self.proj_ld
-                self._ck(L.qwk_gdn_conv(_p(b["proj"]), ldp, _p(dm.gdn_ring[gi]), P(lw["cw"].data_ptr()), P(lw["A_log"].data_ptr()),
-                                        P(lw["dt_bias"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
-                                        rp("run_start"), rp("run_len"), _p(b["qkv"]), _p(b["decay"]), _p(b["beta"]),
-                                        C.c_float(c.eps), s), "gdn_conv")
-                self._ck(L.qwk_gdn_scan(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp, _p(dm.gdn_S[gi]), None,
-                                        P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
-                                        rp("run_start"), rp("run_len"), _p(b["o"]), C.c_float(c.eps), s), "gdn_scan")
-                ow = sc.gdn_vl * c.gdn_dim
-                # gdn_scan writes o rows densely ([T][VL*128])
-                self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
-                                            c.hidden, 0, s), "gdn_out")
+            self.attn_block(lw, T, rp, max_groups, c.qsa_index(li) if lw["is_qsa"] else c.gdn_index(li))
             self.mix(lw["mlp_hc"], T, b["out_a"], inj_attn, inj_mlp, c.hc)
             self.moe(lw, T)
             pend, inj_prev = b["out_b"], inj_mlp
@@ -198,6 +154,87 @@ class Prefiller:
             self._ck(L.qwk_row_reduce(_p(dm.buf["logits"]), sc.vocab_l, sc.vocab_l, 0, 1, _p(dm.buf["amax_val"]),
                                       _p(dm.buf["amax_idx"]), _p(dm.buf["lse_max"]), _p(dm.buf["lse_sum"]), s), "row_reduce")
         return dm.buf["logits"][0] if want_logits else None
+
+    def attn_block(self, lw, T, rp, max_groups, state_index):
+        """The attention block of one layer over T rows: bin -> out_a (fp32 [T][H])."""
+        dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
+        s = self._s()
+        d = dm.model.d
+        if lw["is_qsa"]:
+            qi = state_index
+            self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.qsa_proj_l, c.hidden, b["proj"][:T])
+            ldp = self.proj_ld
+            kd, vd = dm.k_dev[qi].data_ptr(), dm.v_dev[qi].data_ptr()
+            kh = dm.k_host[qi].data_ptr() if dm.k_host else None
+            vh = dm.v_host[qi].data_ptr() if dm.v_host else None
+            self._ck(L.qwk_qsa_prep(_p(b["proj"]), ldp, sc.qh_l, sc.kvh_l, c.idx_heads, P(lw["qn1"].data_ptr()),
+                                    P(lw["kn1"].data_ptr()), P(lw["iqn1"].data_ptr()), P(lw["ikn1"].data_ptr()), T,
+                                    rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), P(kd), P(vd), P(kh) if kh else None,
+                                    P(vh) if vh else None, d.n_dev_pages, _p(dm.page_table), d.max_pages, _p(b["q"]),
+                                    _p(b["iq"]), _p(dm.raw_ring[qi]), _p(dm.ck[qi]), d.ck_cap, c.idx_ratio,
+                                    C.c_float(c.eps), s), "qsa_prep")
+            self._ck(L.qwk_qsa_scores(_p(b["iq"]), c.idx_heads, _p(dm.ck[qi]), d.ck_cap, T, rp("slot"), rp("pos"),
+                                      c.idx_ratio, c.idx_topk_blocks, _p(b["scores"]), d.score_cap, max_groups, s), "scores")
+            self._ck(L.qwk_qsa_select(_p(b["scores"]), d.score_cap, T, rp("pos"), c.idx_ratio, c.idx_topk_blocks,
+                                      _p(b["sel"]), _p(b["sel_n"]), s), "select")
+            A = self.attn_rows
+            ow = sc.qh_l * c.head_dim
+            for r0 in range(0, T, A):
+                n = min(A, T - r0)
+                self._ck(L.qwk_qsa_attend(P(b["q"].data_ptr() + 4 * r0 * ow), sc.qh_l, sc.kvh_l, n, rp("slot", r0),
+                                          rp("pos", r0), P(kd), P(vd), P(kh) if kh else None, P(vh) if vh else None,
+                                          d.n_dev_pages, _p(dm.page_table), d.max_pages,
+                                          P(b["sel"].data_ptr() + 4 * r0 * c.idx_topk_blocks),
+                                          P(b["sel_n"].data_ptr() + 4 * r0), c.idx_topk_blocks, c.idx_ratio, d.nsplit,
+                                          _p(b["pm"]), _p(b["pl"]), _p(b["pacc"]), P(b["proj"].data_ptr() + 4 * r0 * ldp),
+                                          ldp, P(b["o"].data_ptr() + 2 * r0 * ow), s), "attend")
+            # the attention kernels write o rows densely ([T][QL*256])
+            self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
+                                        c.hidden, 0, s), "o_proj")
+        else:
+            gi = state_index
+            self.gemm(b["bin"][:T], lw["Wproj"].data_ptr(), sc.gdn_proj_l, c.hidden, b["proj"][:T])
+            ldp = self.proj_ld
+            self._ck(L.qwk_gdn_conv(_p(b["proj"]), ldp, _p(dm.gdn_ring[gi]), P(lw["cw"].data_ptr()), P(lw["A_log"].data_ptr()),
+                                    P(lw["dt_bias"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
+                                    rp("run_start"), rp("run_len"), _p(b["qkv"]), _p(b["decay"]), _p(b["beta"]),
+                                    C.c_float(c.eps), s), "gdn_conv")
+            self._ck(L.qwk_gdn_scan(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp, _p(dm.gdn_S[gi]), None,
+                                    P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
+                                    rp("run_start"), rp("run_len"), _p(b["o"]), C.c_float(c.eps), s), "gdn_scan")
+            ow = sc.gdn_vl * c.gdn_dim
+            # gdn_scan writes o rows densely ([T][VL*128])
+            self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
+                                        c.hidden, 0, s), "gdn_out")
+
+    def mtp_pass(self, slot: int, base: int, T: int, next_tokens, keep_last_hidden: bool = True):
+        """MTP rows for positions base..base+T-1 whose hidden states are in X (after run()) and whose next
+        tokens are ``next_tokens`` (the last position's may be missing: it is handled when the token is known)."""
+        dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
+        w = dm.mtp_w
+        n = len(next_tokens)
+        if n == 0:
+            return
+        s = self._s()
+        if "hn" not in b:
+            z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dm.dev)
+            b["hn"], b["en"] = z((self.T * c.hc, c.hidden), torch.bfloat16), z((self.T, c.hidden), torch.bfloat16)
+            b["fh"], b["fe"] = z((self.T * c.hc, c.hidden), torch.float32), z((self.T, c.hidden), torch.float32)
+            b["mtp_tok"] = z((self.T,), torch.int32)
+        b["mtp_tok"][:n].copy_(torch.as_tensor([c.real_token(int(t)) for t in next_tokens], dtype=torch.int32), non_blocking=True)
+        rows = self._last_rows
+        rp = lambda k, off=0: P(rows[k] + 4 * off)
+        self._ck(L.qwk_mtp_norm(_p(b["X"]), _p(b["mtp_tok"]), P(dm.globals_w["embed"].data_ptr()), c.vocab, P(w["nh1"].data_ptr()),
+                                P(w["ne1"].data_ptr()), c.hidden, c.hc, C.c_float(c.eps), _p(b["hn"]), _p(b["en"]), n, s), "mtp_norm")
+        self.gemm(b["hn"][:n * c.hc], w["fc_h"].data_ptr(), c.hidden, c.hidden, b["fh"][:n * c.hc])
+        self.gemm(b["en"][:n], w["fc_e"].data_ptr(), c.hidden, c.hidden, b["fe"][:n])
+        self._ck(L.qwk_mtp_add(_p(b["fh"]), _p(b["fe"]), c.hidden, c.hc, _p(b["X"]), n, s), "mtp_add")
+        lw = w["layer"]
+        self.mix(lw["attn_hc"], n, None, None, b["inj_a"], c.hc)
+        self.attn_block(lw, n, rp, (base + n) // c.idx_ratio, c.n_qsa)
+        self.mix(lw["mlp_hc"], n, b["out_a"], b["inj_a"], b["inj_b"], c.hc)
+        self.moe(lw, n)
+        # the MTP layer's output is not needed for prompt rows: only its KV / indexer state matters
 
     def moe(self, lw, T):
         dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib

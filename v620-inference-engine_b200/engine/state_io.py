@@ -35,7 +35,7 @@ class StateIO:
         self.row = sc.kvh_l * c.head_dim
         self.groups = KV_PAGE // c.idx_ratio
         self.kv_page_elems = 2 * KV_PAGE * self.row + self.groups * c.idx_dim      # per layer, bf16 elements
-        self.kv_block_bytes = c.n_qsa * self.kv_page_elems * 2
+        self.kv_block_bytes = len(dm.k_dev) * self.kv_page_elems * 2
 
     def state_layout_id(self) -> int:
         c, sc = self.dm.cfg, self.dm.sc
@@ -48,7 +48,7 @@ class StateIO:
         dm = self.dm
         pid = int(dm.page_table_host[slot, page_index])
         out = []
-        for qi in range(dm.cfg.n_qsa):
+        for qi in range(len(dm.k_dev)):            # QSA layers, then the MTP layer's own cache
             if pid < dm.n_dev_pages:
                 k, v = dm.k_dev[qi][pid], dm.v_dev[qi][pid]
             else:

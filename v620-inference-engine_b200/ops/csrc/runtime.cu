@@ -274,6 +274,39 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     }
 }
 
+// The MTP pass (see runtime.h).
+static void walk_mtp(Ctx &c, int flags) {
+    const QwModel *md = c.md;
+    const QwDims &d = md->d;
+    const QwBuffers &b = md->b;
+    const QwMtp &t = md->mtp;
+    const int M = c.rows->M;
+    c.X = b.X;
+    c.Xalt = b.X2;
+    c.site = 0;
+    c.op = 0;
+    QW_TRYN(1, qwk_mtp_norm(b.hidden_out, c.rows->tokens, md->embed, d.vocab, t.nh1, t.ne1, d.H, d.hc, d.eps, t.hn, t.en, M, c.s));
+    QW_OP(1, t.fc_h, (size_t)d.H * d.H * 2,
+          qwk_gemv_bf16(t.fc_h, t.hn, t.fh, nullptr, d.H, d.H, M * d.hc, d.H, d.H, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, t.fc_e, (size_t)d.H * d.H * 2, qwk_gemv_bf16(t.fc_e, t.en, t.fe, nullptr, d.H, d.H, M, d.H, d.H, d.H, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_mtp_add(t.fh, t.fe, d.H, d.hc, c.X, M, c.s));
+    float *inj_attn = b.inj_a, *inj_mlp = b.inj_b;
+    mix(c, t.layer.attn_hc, nullptr, inj_mlp, inj_attn);
+    qsa_block(c, t.layer);
+    const float *out_attn = scatter(c, b.out_a);
+    mix(c, t.layer.mlp_hc, out_attn, inj_attn, inj_mlp);
+    moe_block(c, t.layer);
+    const float *pend = scatter(c, b.out_b);
+    mix(c, t.final_hc, pend, inj_mlp, nullptr);
+    if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
+    QW_OP(1, md->lm_head, (size_t)d.vocab_l * d.H * 2,
+          qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, 0, M, b.amax_val, b.amax_idx, b.lse_max, b.lse_sum, c.s));
+    if (flags & QWRT_CHAIN)
+        QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
+                                    const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
+}
+
 // Ranges of later kernels' weights that launch k asks the L2 to fetch: the plan keeps the prefetch
 // front `lookahead` bytes past the end of launch k's own weights.
 static void make_plan(const std::vector<WRange> &ops, size_t lookahead, std::vector<qw::PfArgs> &plan) {
@@ -335,3 +368,23 @@ extern "C" __attribute__((visibility("default"))) int qwrt_set_lookahead_mb(int 
 }
 
 extern "C" __attribute__((visibility("default"))) long long qwrt_last_launches() { return g_last_launches; }
+
+extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md, const QwRows *rows, int flags,
+                                                                cudaStream_t stream) {
+    if (!md->mtp.enabled || md->d.ranks != 1) return -1;
+    const int M = rows->M;
+    if (M < 1 || M * md->d.hc > md->d.max_rows * md->d.hc) return -1;
+    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2, false, 0, nullptr, nullptr};
+    std::vector<WRange> ops;
+    std::vector<qw::PfArgs> plan;
+    c.dry = true;
+    c.ops = &ops;
+    walk_mtp(c, flags);
+    make_plan(ops, (size_t)g_lookahead_mb << 20, plan);
+    c.dry = false;
+    c.plan = &plan;
+    c.launches = 0;
+    walk_mtp(c, flags);
+    g_last_launches = c.launches;
+    return c.err;
+}

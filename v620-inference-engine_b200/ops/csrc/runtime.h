@@ -60,6 +60,17 @@ typedef struct QwPle {
     int layout, enabled;
 } QwPle;
 
+typedef struct QwMtp {
+    int enabled, pad_;
+    QwLayer layer;             // a QSA decoder layer (its KV lives at state index n_qsa)
+    QwHc final_hc;
+    const void *fc_h, *fc_e;   // bf16 [H][H]
+    const float *nh1;          // (1+w) [hc*H]: pre_fc_norm_hidden
+    const float *ne1;          // (1+w) [H]: pre_fc_norm_embedding
+    void *hn, *en;             // bf16 [rows*hc][H], [rows][H]
+    float *fh, *fe;            // fp32 [rows*hc][H], [rows][H]
+} QwMtp;
+
 typedef struct QwState {
     // per QSA layer (index = state_index): host arrays of n_qsa device pointers
     void *const *k_dev;
@@ -134,6 +145,7 @@ typedef struct QwModel {
     float *amax_pairs;         // [rows][ranks*2] inside the symmetric region (gather target of the argmax merge)
     long long off_amax;        // its offset inside the region
     long long off_bin;         // offset of b.bin inside the region
+    QwMtp mtp;
 } QwModel;
 
 // flags of qwrt_decode
@@ -143,5 +155,10 @@ typedef struct QwModel {
 #define QWRT_CHAIN 8           // feed each row's argmax back as its next token and advance its position (one row per slot)
 
 int qwrt_decode(const QwModel *md, const QwRows *rows, int flags, int n_layers_run, cudaStream_t stream);
+
+// One MTP pass over the rows: input b.hidden_out (the pre-final-mixer state of each row's position) and
+// rows->tokens (the token AFTER that position); output logits / argmax of the position after that, and the MTP's
+// own pre-final-mixer state back in b.hidden_out (the input of a chained next draft).  One GPU only.
+int qwrt_mtp(const QwModel *md, const QwRows *rows, int flags, cudaStream_t stream);
 
 }  // extern "C"

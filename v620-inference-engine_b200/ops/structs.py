@@ -30,6 +30,11 @@ class QwPle(C.Structure):
                 ("rows_per_shard", C.c_longlong), ("rows", C.c_longlong), ("layout", C.c_int), ("enabled", C.c_int)]
 
 
+class QwMtp(C.Structure):
+    _fields_ = [("enabled", C.c_int), ("pad_", C.c_int), ("layer", QwLayer), ("final_hc", QwHc), ("fc_h", P), ("fc_e", P),
+                ("nh1", P), ("ne1", P), ("hn", P), ("en", P), ("fh", P), ("fe", P)]
+
+
 class QwState(C.Structure):
     _fields_ = [(n, P) for n in ("k_dev", "v_dev", "k_host", "v_host", "ck", "raw_ring", "gdn_S", "gdn_ring",
                                  "ple_ring", "page_table")]
@@ -56,7 +61,7 @@ COMM_FN = C.CFUNCTYPE(None, P, C.c_int, C.c_int, P, P, C.c_int, C.c_int, P)
 class QwModel(C.Structure):
     _fields_ = [("d", QwDims), ("layers", C.POINTER(QwLayer)), ("final_hc", QwHc), ("ple", QwPle), ("embed", P),
                 ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P),
-                ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong)]
+                ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong), ("mtp", QwMtp)]
 
 
 class QwP2P(C.Structure):
