@@ -1,0 +1,99 @@
+"""Session: prefix-cache restore equals recompute, slot choice, sampling entry points, speculative generate."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def make(tmp_path=None, slots=2, **kw):
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.models.ple import PleTable
+    from qwb200.models.weights import synth_weights
+    from qwb200.session.session import Session
+    cfg = ModelConfig.tiny()
+    w = synth_weights(cfg, seed=21)
+    table = PleTable.synthetic(cfg, rows=4096, layout="f8", seed=21)
+    eng = Engine.from_weights(cfg, w, table, EngineOptions(slots=slots, slot_tokens=1024, use_graphs=False, save_gdn=True, **kw))
+    return cfg, eng, Session(eng, host_cache_bytes=1 << 28, disk_cache_dir=str(tmp_path) if tmp_path else None,
+                             disk_cache_bytes=1 << 30, prefill_piece=256)
+
+
+def prompt_of(cfg, n, seed):
+    return torch.randint(0, cfg.vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def test_restore_from_store_equals_recompute_and_slot_choice(tmp_path):
+    from qwb200.engine.sampling import SamplingParams
+    cfg, eng, ses = make(tmp_path)
+    shared = prompt_of(cfg, 600, 1)
+    a = shared + prompt_of(cfg, 50, 2)
+    s0 = ses.acquire(a, 16)
+    assert s0 == 0 and ses.begin_prompt(s0, a) == 0
+    while not ses.prefill_some(s0, 256):
+        pass
+    la = ses.slots[s0].logits.clone()
+    ta, _ = ses.sample_prompt(s0, SamplingParams())
+    st = ses.cache_stats()
+    assert st["blocks"] == 2 and st["snapshots"] >= 2
+    # a second request sharing the 600-token prefix goes to the free slot and restores 512 tokens from the store
+    b = shared + prompt_of(cfg, 40, 3)
+    s1 = ses.acquire(b, 16)
+    assert s1 == 1
+    assert ses.begin_prompt(s1, b) == 512
+    while not ses.prefill_some(s1, 1024):
+        pass
+    lb = ses.slots[s1].logits.clone()
+    # recompute b from scratch on a fresh engine: same logits as after the restore
+    cfg2, eng2, ses2 = make(None, slots=1)
+    s = ses2.acquire(b, 16)
+    assert ses2.begin_prompt(s, b) == 0
+    while not ses2.prefill_some(s, 1024):
+        pass
+    ref = ses2.slots[s].logits
+    assert float((lb - ref).abs().max() / ref.abs().max()) < 2e-2
+    assert int(torch.argmax(lb)) == int(torch.argmax(ref))
+    # follow-up turn on slot 0: everything it holds is kept
+    ses.release(s0)
+    a2 = a + [ta] + prompt_of(cfg, 20, 4)
+    ses.e.decode([s0], [ta])                                  # the sampled token joins the slot
+    assert ses.acquire(a2, 8) == s0 and ses.begin_prompt(s0, a2) == len(a) + 1
+    ses.persist()
+    assert ses.cache_stats()["disk_bytes"] > 0 and ses.cache_stats()["hits"] == 1
+
+
+def test_generate_greedy_matches_engine_and_sampling_runs():
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session.session import StepReq
+    cfg, eng, ses = make(None, slots=2)
+    p = prompt_of(cfg, 80, 5)
+    s = ses.acquire(p, 64)
+    ses.begin_prompt(s, p)
+    while not ses.prefill_some(s, 4096):
+        pass
+    first, lp = ses.sample_prompt(s, SamplingParams())
+    assert lp <= 0
+    # reference continuation on a second engine
+    cfg2, eng2, ses2 = make(None, slots=1)
+    eng2.prefill(0, p)
+    want = eng2.generate_greedy(0, first, 20, k=0)
+    ses.set_stop_tokens(s, [])
+    got, pending = [], first
+    while len(got) < 20:
+        out = ses.generate([StepReq(s, pending, 20 - len(got), 0, SamplingParams())], k=3)[0]
+        assert 1 <= len(out.tokens) <= 4
+        got += out.tokens
+        pending = out.tokens[-1]
+    assert got[:20] == want
+    # sampled generation on another slot, with top-k / top-p and penalties
+    s2 = ses.acquire(p[:30], 32)
+    ses.begin_prompt(s2, p[:30])
+    while not ses.prefill_some(s2, 4096):
+        pass
+    sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, repetition_penalty=1.1, seed=7)
+    t, _ = ses.sample_prompt(s2, sp)
+    outs = ses.generate([StepReq(s2, t, 8, 0, sp)], k=2)
+    assert all(0 <= x < cfg.vocab for x in outs[0].tokens) and all(lp <= 1e-4 for lp in outs[0].logprobs)
+    ids, lps = ses.top_logprobs(0, 5)
+    assert len(ids) == 5 and lps[0] >= lps[-1]

@@ -1,0 +1,325 @@
+"""Session: slot bookkeeping and choice, the prefix cache (native block store + disk tier over the engine's
+state export / import), sampling, and the speculative generation loop with adaptive draft counts.
+
+This is the layer the C API exposes (reference: ``class Session``, src/session/session.hpp:37-237,
+session.cpp, prefix_cache.cpp, generate.cpp).  What is kept from the reference's behaviour:
+
+* ``acquire`` picks the free slot that can reuse the most of the prompt (then least recently used);
+* ``begin_prompt`` decides between continuing in place, restoring from the block store (KV blocks up to the
+  deepest snapshot on the prompt's path) and resetting;
+* prefill runs in pieces so other slots can decode in between, saves a KV block per 256 tokens and a
+  snapshot at the end of every piece (pieces end on block boundaries), anchoring message boundaries;
+* ``generate`` emits 1..k+1 tokens per request per step: drafts from the MTP head, one verification pass,
+  exact sampling per row, accept / rollback, acceptance EMA, and K chosen to maximise expected tokens per
+  step cost (1+a+..+a^K)/(base + beta (K-1)).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..engine.engine import Engine
+from ..engine.sampling import GpuSampler, SamplingParams
+from ..engine.state_io import StateIO
+from ..native import host as H
+
+BLOCK = 256
+SPEC_BASE, SPEC_BETA = 1.25, 0.25
+
+
+@dataclass
+class SlotInfo:
+    busy: bool = False
+    used: int = 0
+    prompt: List[int] = field(default_factory=list)      # the whole prompt of the current request
+    prompt_end: int = 0
+    stop: List[int] = field(default_factory=list)
+    logits: Optional[torch.Tensor] = None                 # logits after the prompt (device)
+    accept: float = 0.5                                    # running draft acceptance
+    drafts: List[int] = field(default_factory=list)
+    drafts_for: int = -1
+    block_keys: List[int] = field(default_factory=list)   # store keys of the slot's full blocks, in order
+    timing: Dict[str, float] = field(default_factory=lambda: {"restore_s": 0.0, "prefill_s": 0.0, "save_s": 0.0, "pin_wait_s": 0.0})
+
+
+@dataclass
+class StepReq:
+    slot: int
+    pending: int
+    budget: int
+    flags: int = 0
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+
+
+@dataclass
+class StepOut:
+    tokens: List[int]
+    logprobs: List[float]
+    first_row: int
+    stopped: bool
+
+
+def best_rate(a: float, k_max: int) -> Tuple[float, int]:
+    best, expect, p, bk = 0.0, 1.0, 1.0, 1
+    for K in range(1, k_max + 1):
+        p *= a
+        expect += p
+        rate = expect / (SPEC_BASE + SPEC_BETA * (K - 1))
+        if rate > best:
+            best, bk = rate, K
+    return best, bk
+
+
+class Session:
+    def __init__(self, engine: Engine, host_cache_bytes: int = 8 << 30, disk_cache_dir: Optional[str] = None,
+                 disk_cache_bytes: int = 0, prefill_piece: int = 2048, seed: int = 0):
+        self.e = engine
+        self.cfg = engine.cfg
+        self.io = StateIO(engine.dm)
+        n = engine.opts.slots
+        self.slots = [SlotInfo() for _ in range(n)]
+        self.clock = 0
+        self.boundary = -1
+        self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
+        self.store = H.BlockStore(self.io.state_layout_id(), engine.dm.sc.ranks, host_cache_bytes, disk_cache_dir, disk_cache_bytes)
+        self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.dm.sc.vocab_l, n, engine.opts.max_rows, seed)
+        self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
+        self.seen_chunks = set()
+        self.last_rows: Optional[torch.Tensor] = None        # logits of the last decode / generate rows
+
+    # ---- slots
+    def num_slots(self) -> int:
+        return len(self.slots)
+
+    def slot_capacity(self, slot: int) -> int:
+        return self.e.dm.slot_tokens
+
+    def _common(self, slot: int, tokens: Sequence[int]) -> int:
+        hist = self.e.slot[slot].tokens
+        n = min(len(hist), len(tokens))
+        i = 0
+        while i < n and hist[i] == tokens[i]:
+            i += 1
+        return i
+
+    def reusable(self, slot: int, tokens: Sequence[int]) -> int:
+        """Tokens of the prompt the slot could keep: everything it holds when that is a prefix of the prompt."""
+        c = self._common(slot, tokens)
+        return c if c == len(self.e.slot[slot].tokens) and c < len(tokens) else 0
+
+    def acquire(self, tokens: Sequence[int], max_new: int) -> int:
+        need = len(tokens) + max(1, max_new)
+        best, best_r = -1, -1
+        for i, si in enumerate(self.slots):
+            if si.busy or self.slot_capacity(i) < need:
+                continue
+            r = self.reusable(i, tokens)
+            if best < 0 or r > best_r or (r == best_r and si.used < self.slots[best].used):
+                best, best_r = i, r
+        if best >= 0:
+            self.clock += 1
+            self.slots[best].busy = True
+            self.slots[best].used = self.clock
+        return best
+
+    def release(self, slot: int) -> None:
+        self.slots[slot].busy = False
+        self.slots[slot].drafts = []
+
+    def set_boundary_token(self, tok: int) -> None:
+        self.boundary = tok
+
+    def set_stop_tokens(self, slot: int, ids: Sequence[int]) -> None:
+        self.slots[slot].stop = [int(t) for t in ids]
+
+    # ---- prompt
+    def begin_prompt(self, slot: int, tokens: Sequence[int]) -> int:
+        """Make the slot ready to prefill ``tokens``: keeps what it already holds, or restores the longest stored
+        prefix, or resets.  Returns the number of reused tokens."""
+        si = self.slots[slot]
+        toks = [int(t) for t in tokens]
+        si.prompt, si.prompt_end, si.logits, si.drafts = toks, len(toks), None, []
+        for k in si.timing:
+            si.timing[k] = 0.0
+        self.prompt_tokens += len(toks)
+        for st, ln, hs in H.chunk_prompt(toks, self.boundary):
+            if hs in self.seen_chunks:
+                self.blend_candidate_tokens += ln
+            self.seen_chunks.add(hs)
+        keep = self.reusable(slot, toks)
+        t0 = time.time()
+        path, depth = self.store.lookup(toks[:max(0, len(toks) - 1)])      # at least one token is left to prefill
+        stored = depth * BLOCK
+        if keep >= stored and keep > 0:
+            self.reused_tokens += keep
+            self.sampler_sync(slot, toks[:keep], keep)
+            return keep
+        self.e.reset(slot)
+        si.block_keys = []
+        self.sampler.reset_slot(slot)
+        if depth == 0:
+            return 0
+        ok = True
+        for bi, key in enumerate(path[:depth]):
+            kv = self.store.get(key)
+            if kv is None or len(kv) != self.io.kv_block_bytes:
+                ok = False
+                break
+            self.io.import_kv(slot, bi, kv)
+        snap = self.store.get(path[depth - 1], snapshot=True) if ok else None
+        if not ok or snap is None or len(snap[0]) != self.io.recurrent_bytes():
+            self.e.reset(slot)           # a payload vanished (budget) or does not fit: recompute
+            return 0
+        self.io.import_recurrent(slot, snap[0])
+        self.e.slot[slot].tokens = toks[:stored]
+        self.e.slot[slot].mtp_hidden = None
+        si.block_keys = list(path[:depth])
+        self.store.note_restore(path[depth - 1], stored)
+        self.reused_tokens += stored
+        si.timing["restore_s"] += time.time() - t0
+        self.sampler.note_tokens(slot, toks[:stored], generated=False)
+        return stored
+
+    def sampler_sync(self, slot: int, tokens: Sequence[int], prompt_end: int) -> None:
+        self.sampler.reset_slot(slot)
+        self.sampler.note_tokens(slot, tokens[:prompt_end], generated=False)
+        self.sampler.note_tokens(slot, tokens[prompt_end:], generated=True)
+
+    def prefill_some(self, slot: int, max_tokens: int) -> bool:
+        """Prefill up to ``max_tokens`` more of the slot's prompt; True once the whole prompt is in."""
+        si, sl = self.slots[slot], self.e.slot[slot]
+        done = sl.n
+        left = len(si.prompt) - done
+        if left <= 0:
+            return True
+        t0 = time.time()
+        n = min(left, max(1, max_tokens))
+        end = done + n
+        if end < len(si.prompt) and end // BLOCK * BLOCK > done:
+            end = end // BLOCK * BLOCK            # pieces end on block boundaries so a snapshot can be stored there
+        piece = si.prompt[done:end]
+        last = end >= len(si.prompt)
+        logits = self.e.prefill(slot, piece, want_logits=last)
+        self.sampler.note_tokens(slot, piece, generated=False)
+        if last:
+            si.logits = logits.clone()
+        si.timing["prefill_s"] += time.time() - t0
+        self._save_blocks(slot, snapshot=(end % BLOCK == 0))
+        return last
+
+    def _save_blocks(self, slot: int, snapshot: bool) -> None:
+        """Store the slot's new full blocks; a snapshot of the recurrent state goes with the last one when the slot
+        ends exactly on its boundary."""
+        si, sl = self.slots[slot], self.e.slot[slot]
+        t0 = time.time()
+        full = sl.n // BLOCK
+        parent = si.block_keys[-1] if si.block_keys else self.store.root
+        for bi in range(len(si.block_keys), full):
+            toks = sl.tokens[bi * BLOCK:(bi + 1) * BLOCK]
+            key = self.store.save_block(parent, bi * BLOCK, toks, self.io.export_kv(slot, bi))
+            if key == 0:
+                break
+            si.block_keys.append(key)
+            parent = key
+        if snapshot and si.block_keys and len(si.block_keys) * BLOCK == sl.n:
+            anchor = sl.n < len(si.prompt) and si.prompt[sl.n] == self.boundary
+            self.store.save_snapshot(si.block_keys[-1], self.io.export_recurrent(slot), None, anchor)
+        si.timing["save_s"] += time.time() - t0
+
+    def sample_prompt(self, slot: int, p: SamplingParams) -> Tuple[int, float]:
+        si = self.slots[slot]
+        assert si.logits is not None, "the prompt is not in yet"
+        toks, lps = self.sampler.sample(si.logits.view(1, -1), [p], [slot], [self.e.slot[slot].n],
+                                        hists=[(self.e.slot[slot].tokens, si.prompt_end)])
+        self.last_rows = si.logits.view(1, -1)
+        return toks[0], lps[0]
+
+    # ---- decode
+    def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> None:
+        self.e.decode(slots, tokens, sync=False)
+        for s, t in zip(slots, tokens):
+            self.sampler.note_tokens(s, [int(t)], generated=True)
+        self.last_rows = self.e.dm.buf["logits"][:len(tokens)]
+        self.last_row_slots = list(slots)
+
+    def sample_row(self, row: int, p: SamplingParams) -> Tuple[int, float]:
+        s = self.last_row_slots[row]
+        toks, lps = self.sampler.sample(self.last_rows[row:row + 1], [p], [s], [self.e.slot[s].n],
+                                        hists=[(self.e.slot[s].tokens, self.slots[s].prompt_end)])
+        return toks[0], lps[0]
+
+    def top_logprobs(self, row: int, k: int):
+        lg = self.last_rows[max(row, 0)].float().cpu().numpy()
+        return H.HostSampler.top_logprobs(lg, k)
+
+    def top_logprobs_prompt(self, slot: int, k: int):
+        return H.HostSampler.top_logprobs(self.slots[slot].logits.float().cpu().numpy(), k)
+
+    # ---- generation with speculative decoding
+    def draft_count(self, slot: int, k_max: int) -> int:
+        if k_max <= 1:
+            return k_max
+        rate, k = best_rate(self.slots[slot].accept, k_max)
+        return k if rate >= 1.0 else 0
+
+    def generate(self, reqs: Sequence[StepReq], k: int) -> List[StepOut]:
+        """One step for every request: decode its pending token plus up to k drafts, emit 1..k+1 tokens."""
+        outs: List[StepOut] = []
+        all_rows = []
+        row0 = 0
+        for r in reqs:
+            si, sl = self.slots[r.slot], self.e.slot[r.slot]
+            kk = min(k, r.budget - 1) if self.e.mtp else 0
+            kk = self.draft_count(r.slot, kk) if kk > 0 else 0
+            if kk > 0 and sl.mtp_hidden is None:
+                kk = 0
+            drafts = self.e.draft(r.slot, r.pending, kk) if kk > 0 else []
+            rows = [r.pending] + drafts
+            logits = self.e.verify(r.slot, rows) if (drafts or self.e.mtp) else None
+            if logits is None:
+                self.e.decode([r.slot], [r.pending], sync=False)
+                logits = self.e.dm.buf["logits"][:1]
+            logits = logits.clone()
+            n = len(rows)
+            base = sl.n
+            hist = sl.tokens + rows
+            toks, lps = self.sampler.sample(logits, [r.sampling] * n, [r.slot] * n, [base + i + 1 for i in range(n)],
+                                            hists=[(hist[:base + i + 1], si.prompt_end) for i in range(n)])
+            n_acc = 1
+            while n_acc <= len(drafts) and toks[n_acc - 1] == drafts[n_acc - 1] and toks[n_acc - 1] not in si.stop:
+                n_acc += 1
+            if drafts or self.e.mtp:
+                self.e.accept(r.slot, rows, n_acc)
+            self.sampler.note_tokens(r.slot, rows[:n_acc], generated=True)
+            if drafts:
+                si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(drafts))
+            emitted = toks[:n_acc][:r.budget]
+            stopped = bool(emitted) and emitted[-1] in si.stop
+            outs.append(StepOut(emitted, lps[:len(emitted)], row0, stopped))
+            all_rows.append(logits[:n_acc])
+            row0 += n_acc
+        self.last_rows = torch.cat(all_rows) if all_rows else None
+        self.last_row_slots = [r.slot for r, o in zip(reqs, outs) for _ in o.tokens]
+        return outs
+
+    # ---- stats / persistence
+    def cache_stats(self) -> dict:
+        s = self.store.stats()
+        s.update(prompt_tokens=self.prompt_tokens, reused_tokens=self.reused_tokens,
+                 blend_candidate_tokens=self.blend_candidate_tokens)
+        return s
+
+    def slot_timing(self, slot: int) -> dict:
+        return dict(self.slots[slot].timing)
+
+    def persist(self) -> None:
+        """Save what the slots hold (full blocks + a snapshot where a slot ends on a block boundary) and wait for the
+        disk writes."""
+        for i in range(self.num_slots()):
+            if self.e.slot[i].n >= BLOCK:
+                self._save_blocks(i, snapshot=True)
+        self.store.flush()
