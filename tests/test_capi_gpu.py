@@ -1,0 +1,75 @@
+"""The C API end to end: the server's ctypes binding -> libqw_engine.so -> session -> engine on a small random
+model, driven by the real scheduler (the reference exercises the same path from server/tests/test_e2e.py)."""
+import threading
+
+import pytest
+
+from server_fixtures import SERVER  # noqa: F401  (puts the server package on sys.path)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from qwserve.engine import Engine
+    e = Engine({"synthetic": "tiny", "slots": [2048, 2048, 2048], "prefill_chunk": 512, "host_cache_gb": 0.25, "mtp": True})
+    yield e
+    e.close()
+
+
+def run(sched, eng, prompt, n_new, temperature=0.0):
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    toks, ev = [], threading.Event()
+    r = Request(tokens=Tokens(prompt), max_new=n_new, sampling=Sampling(temperature=temperature, top_p=1.0, top_k=0, repetition_penalty=1.0, seed=7),
+                stop_ids=[], on_token=lambda t, lp, top: toks.append((t, lp)), on_done=lambda reason: ev.set())
+    sched.submit(r)
+    assert ev.wait(120), "request did not finish"
+    assert not r.error, r.error
+    return [t for t, _ in toks], [lp for _, lp in toks], r
+
+
+def test_capi_generate_plain_equals_speculative_and_cache_reuse(eng):
+    from qwserve.scheduler import Scheduler
+    assert eng.num_slots() == 3 and eng.slot_capacity(0) >= 2048 and eng.failure() == ""
+    prompt = [(i * 37 + 11) % 1000 + 5 for i in range(700)]
+    plain = Scheduler(eng, drafts=0, prefill_piece=256)
+    plain.start(watchdog=False)
+    a, lpa, ra = run(plain, eng, prompt, 24)
+    b, lpb, rb = run(plain, eng, prompt, 24)                # same prompt again: the prefix comes from a slot or the cache
+    plain.shutdown()
+    assert len(a) == 24 and a == b
+    assert rb.reused >= 256
+    assert all(lp <= 0.0 for lp in lpa)
+    if eng.has_mtp:
+        spec = Scheduler(eng, drafts=2, prefill_piece=256)
+        spec.thread.name = "spec"
+        spec.start(watchdog=False)
+        c, _, _ = run(spec, eng, prompt, 24)
+        spec.shutdown()
+        assert c == a
+    st = eng.cache_stats()
+    assert st["prompt_tokens"] >= 1400 and st["reused_tokens"] >= 256
+
+
+def test_capi_batch_of_requests_and_logprobs(eng):
+    from qwserve.scheduler import Scheduler
+    s = Scheduler(eng, drafts=0, prefill_piece=256)
+    s.start(watchdog=False)
+    p1 = [(i * 13 + 3) % 900 + 5 for i in range(300)]
+    alone, _, _ = run(s, eng, p1, 12)
+    # three at once: each must produce what it produces alone
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    outs, evs = [[], [], []], [threading.Event() for _ in range(3)]
+    prompts = [p1, [(i * 7 + 1) % 900 + 5 for i in range(280)], p1[:200]]
+    for i, p in enumerate(prompts):
+        s.submit(Request(tokens=Tokens(p), max_new=12, sampling=Sampling(temperature=0.0, top_p=1.0, repetition_penalty=1.0), stop_ids=[], logprobs=3 if i == 0 else 0,
+                         on_token=lambda t, lp, top, i=i: outs[i].append((t, top)), on_done=lambda reason, i=i: evs[i].set()))
+    assert all(e.wait(120) for e in evs)
+    s.shutdown()
+    assert [t for t, _ in outs[0]] == alone
+    tops = [top for _, top in outs[0]]
+    assert all(top is not None and len(top) == 3 for top in tops)
+    # greedy: the sampled token is the most likely one
+    assert all(top[0][0] == t for (t, top) in outs[0])

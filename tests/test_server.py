@@ -1,0 +1,307 @@
+"""HTTP + scheduler tier on a fake engine: API shapes, streaming == non-streaming, reasoning / tool routing,
+thinking budget, stop strings, admission without head-of-line blocking, failure isolation, health, dashboard
+(the reference's server tests cover the same ground: server/tests/test_api.py, test_admission.py,
+test_isolation.py, test_health.py, test_thinking.py, test_concurrency.py)."""
+import asyncio
+import json
+import threading
+import time
+
+import pytest
+
+from server_fixtures import make_prompter, make_server
+
+aiohttp = pytest.importorskip("aiohttp")
+from aiohttp.test_utils import TestClient, TestServer  # noqa: E402
+
+
+def with_client(srv, fn):
+    from qwserve.api import make_app
+
+    async def go():
+        async with TestClient(TestServer(make_app(srv))) as c:
+            return await fn(c)
+    return asyncio.run(go())
+
+
+async def sse(resp):
+    frames = []
+    async for line in resp.content:
+        line = line.decode().strip()
+        if line.startswith("data: ") and line != "data: [DONE]":
+            frames.append(json.loads(line[6:]))
+    return frames
+
+
+MSG = [{"role": "user", "content": "hi"}]
+
+
+def test_chat_plain_and_usage():
+    srv, sched, eng, pr = make_server("thinking hard</think>The answer is 4.")
+
+    async def fn(c):
+        r = await c.post("/v1/chat/completions", json={"messages": MSG, "logprobs": True, "top_logprobs": 2})
+        assert r.status == 200
+        return await r.json()
+    out = with_client(srv, fn)
+    ch = out["choices"][0]
+    assert ch["message"]["content"] == "The answer is 4."
+    assert ch["message"]["reasoning_content"] == "thinking hard"
+    assert ch["finish_reason"] == "stop"
+    u = out["usage"]
+    assert u["prompt_tokens"] == len(pr.encode(pr.render(MSG)))
+    assert u["completion_tokens_details"]["reasoning_tokens"] == len("thinking hard")
+    lp = ch["logprobs"]["content"]
+    assert len(lp) == len("thinking hard") + len("The answer is 4.") and len(lp[0]["top_logprobs"]) == 2
+    assert out["timings"]["predicted_n"] == u["completion_tokens"]
+    sched.shutdown()
+
+
+def test_stream_equals_nonstream_and_utf8():
+    text = "plan</think>naïve café 日本語 ok"
+    srv, sched, eng, pr = make_server(text)
+
+    async def fn(c):
+        a = await (await c.post("/v1/chat/completions", json={"messages": MSG})).json()
+        r = await c.post("/v1/chat/completions", json={"messages": MSG, "stream": True, "stream_options": {"include_usage": True}})
+        return a, await sse(r)
+    a, frames = with_client(srv, fn)
+    content = "".join(f["choices"][0]["delta"].get("content") or "" for f in frames if f["choices"])
+    reasoning = "".join(f["choices"][0]["delta"].get("reasoning_content") or "" for f in frames if f["choices"])
+    assert content == a["choices"][0]["message"]["content"] == "naïve café 日本語 ok"
+    assert reasoning == "plan"
+    assert "�" not in content
+    assert frames[-1]["usage"]["completion_tokens"] == a["usage"]["completion_tokens"]
+    assert [f for f in frames if f["choices"]][-1]["choices"][0]["finish_reason"] == "stop"
+    sched.shutdown()
+
+
+def test_thinking_disabled_and_budget():
+    from qwserve.prompt import resolve_thinking
+    assert resolve_thinking({"chat_template_kwargs": {"enable_thinking": False}})[0] is False
+    assert resolve_thinking({"reasoning_effort": "none"})[0] is False
+    assert resolve_thinking({"reasoning_effort": "low"}) == (True, "low", 1024)
+    assert resolve_thinking({"thinking": {"type": "enabled", "budget_tokens": 77}}) == (True, None, 77)
+    assert resolve_thinking({"thinking": {"type": "disabled"}})[0] is False
+    assert resolve_thinking({"thinking_budget": 5}, None, 100)[2] == 5
+    # a model that never stops thinking is closed by force after the budget
+    srv, sched, eng, pr = make_server("x" * 500)
+
+    async def fn(c):
+        return await (await c.post("/v1/chat/completions", json={"messages": MSG, "thinking_budget": 10, "max_tokens": 40})).json()
+    out = with_client(srv, fn)
+    m = out["choices"][0]["message"]
+    assert m["reasoning_content"].startswith("x" * 10) and len(m["reasoning_content"].strip()) == 10
+    assert m["content"].startswith("\n\n") and set(m["content"].strip()) == {"x"}
+    assert out["choices"][0]["finish_reason"] == "length"
+    assert sched.stats["forced_think_close"] == 1
+    sched.shutdown()
+
+
+def test_tool_call_routing():
+    reply = "</think>Let me look.<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n</parameter>\n</function>\n</tool_call>"
+    srv, sched, eng, pr = make_server(reply)
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {
+        "city": {"type": "string"}, "days": {"type": "integer"}}}}}]
+
+    async def fn(c):
+        a = await (await c.post("/v1/chat/completions", json={"messages": MSG, "tools": tools})).json()
+        r = await c.post("/v1/chat/completions", json={"messages": MSG, "tools": tools, "stream": True})
+        return a, await sse(r)
+    a, frames = with_client(srv, fn)
+    ch = a["choices"][0]
+    assert ch["finish_reason"] == "tool_calls" and ch["message"]["content"] == "Let me look."
+    call = ch["message"]["tool_calls"][0]
+    assert call["function"]["name"] == "get_weather" and json.loads(call["function"]["arguments"]) == {"city": "Paris", "days": 3}
+    streamed = [f["choices"][0]["delta"]["tool_calls"][0] for f in frames if f["choices"] and "tool_calls" in f["choices"][0]["delta"]]
+    assert len(streamed) == 1 and streamed[0]["function"]["name"] == "get_weather" and streamed[0]["index"] == 0
+    sched.shutdown()
+
+
+def test_stop_string_and_completions_and_tokenize():
+    srv, sched, eng, pr = make_server("one two STOP three")
+
+    async def fn(c):
+        a = await (await c.post("/v1/completions", json={"prompt": "abc", "stop": ["STOP"]})).json()
+        r = await c.post("/v1/completions", json={"prompt": "abc", "stop": "STOP", "stream": True})
+        frames = await sse(r)
+        t = await (await c.post("/tokenize", json={"prompt": "abc"})).json()
+        t2 = await (await c.post("/tokenize", json={"messages": MSG})).json()
+        m = await (await c.get("/v1/models")).json()
+        bad = await c.post("/v1/completions", json={"prompt": {"no": 1}})
+        bad2 = await c.post("/v1/chat/completions", json={"messages": MSG, "n": 2})
+        return a, frames, t, t2, m, bad.status, bad2.status
+    a, frames, t, t2, m, bad, bad2 = with_client(srv, fn)
+    assert a["choices"][0]["text"] == "one two " and a["choices"][0]["finish_reason"] == "stop"
+    assert "".join(f["choices"][0]["text"] for f in frames) == "one two "
+    assert t["count"] == 3 and t["tokens"] == pr.encode("abc") and t2["count"] == len(pr.encode(pr.render(MSG)))
+    assert m["data"][0]["id"] == "qw-test" and m["data"][0]["max_model_len"] == 4096
+    assert bad == 400 and bad2 == 400
+    sched.shutdown()
+
+
+def test_parallel_equals_serial():
+    pr = make_prompter()
+    reply = lambda prompt: pr.encode("</think>echo:" + pr.decode(prompt)[-12:])
+    srv, sched, eng, _ = make_server(reply=reply, step_seconds=0.001)
+    prompts = [f"question number {i}" for i in range(8)]
+
+    async def fn(c):
+        async def one(p):
+            return (await (await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": p}], "max_tokens": 64})).json())["choices"][0]["message"]["content"]
+        serial = [await one(p) for p in prompts]
+        par = await asyncio.gather(*[one(p) for p in prompts])
+        return serial, list(par)
+    serial, par = with_client(srv, fn)
+    assert serial == par and len(set(serial)) == 1 or serial == par
+    assert "generate" in eng.calls
+    sched.shutdown()
+
+
+def test_admission_skips_request_that_does_not_fit():
+    """A request too large for the free slots waits; later, smaller ones are admitted past it."""
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(4096, 256), step_seconds=0.002)
+    done = {}
+
+    def mk(name, n_prompt, max_new):
+        ev = threading.Event()
+        r = Request(tokens=Tokens([65] * n_prompt), max_new=max_new, sampling=Sampling(), stop_ids=[eng.eos],
+                    on_done=lambda reason, name=name, ev=ev: (done.__setitem__(name, (reason, time.time())), ev.set()))
+        return r, ev
+    eng.reply = lambda prompt: [66] * 200
+    big1, e1 = mk("big1", 1000, 300)       # takes the 4096 slot
+    big2, e2 = mk("big2", 1000, 300)       # needs the 4096 slot too: must wait
+    small, e3 = mk("small", 10, 5)         # fits the 256 slot while big2 waits
+    for r in (big1, big2, small):
+        sched.submit(r)
+    assert e3.wait(10) and e1.wait(10) and e2.wait(10)
+    assert done["small"][1] < done["big2"][1]
+    assert done["big1"][0] == done["big2"][0] == "stop" and done["small"][0] == "length"
+    sched.shutdown()
+
+
+def test_failure_isolation_and_health():
+    srv, sched, eng, pr = make_server("</think>fine", step_seconds=0.002)
+    eng.poison = pr.encode("Z")[0]
+
+    async def fn(c):
+        bad = await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "ZZZ"}]})
+        good = await c.post("/v1/chat/completions", json={"messages": MSG})
+        h = await c.get("/health")
+        return bad.status, await bad.json(), good.status, (await good.json())["choices"][0]["message"]["content"], h.status, await h.json()
+    bs, bj, gs, gc, hs, hj = with_client(srv, fn)
+    assert bs == 500 and "poisoned" in bj["error"]["message"]
+    assert gs == 200 and gc == "fine"
+    assert hs == 200 and hj["status"] == "ok" and hj["decode"]["failed"] == 1
+    # an engine that reports a failure turns /health into 503
+    eng.failed_with = "rank 2: device lost"
+
+    async def fn2(c):
+        h = await c.get("/health")
+        return h.status, await h.json()
+    hs, hj = with_client(srv, fn2)
+    assert hs == 503 and "device lost" in hj["reason"]
+    sched.shutdown()
+
+
+def test_generate_error_fails_only_the_culprit():
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(512, 512, 512), step_seconds=0.005)
+    eng.reply = lambda prompt: [66] * 30
+    res = {}
+    evs = []
+    reqs = []
+    for i in range(3):
+        ev = threading.Event()
+        evs.append(ev)
+        reqs.append(Request(tokens=Tokens([65] * 8), max_new=50, sampling=Sampling(), stop_ids=[eng.eos],
+                            on_done=lambda reason, i=i, ev=ev: (res.__setitem__(i, reason), ev.set())))
+    for r in reqs:
+        sched.submit(r)
+    while not all(r.slot >= 0 and r.prefill_done for r in reqs):
+        time.sleep(0.002)
+    eng.generate_error[reqs[1].slot] = "bad row"
+    assert all(ev.wait(10) for ev in evs)
+    assert res[1].startswith("error: bad row") and res[0] == "stop" and res[2] == "stop"
+    assert sched.health() is None
+    sched.shutdown()
+
+
+def test_hung_engine_call_is_unhealthy():
+    srv, sched, eng, pr = make_server("ok", stuck_seconds=0.2)
+    eng.generate_block = threading.Event()
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    sched.submit(Request(tokens=Tokens([65] * 4), max_new=8, sampling=Sampling(), stop_ids=[eng.eos]))
+    t0 = time.time()
+    while sched.health() is None and time.time() - t0 < 5:
+        time.sleep(0.05)
+    assert "engine call running" in (sched.health() or "")
+    eng.generate_block.set()           # let the thread go so the test process can end cleanly
+    time.sleep(0.05)
+    assert sched.health() is None
+    sched.shutdown()
+
+
+def test_short_prompts_prefill_first_and_single_caller():
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(8192, 8192), piece=512)
+    eng.reply = lambda prompt: [66]
+    evs = []
+    eng.generate_block = None
+    long_r = Request(tokens=Tokens([65] * 4000), max_new=2, sampling=Sampling(), stop_ids=[eng.eos])
+    short_r = Request(tokens=Tokens([65] * 100), max_new=2, sampling=Sampling(), stop_ids=[eng.eos])
+    for r in (long_r, short_r):
+        ev = threading.Event()
+        evs.append(ev)
+        r.on_done = lambda reason, ev=ev: ev.set()
+    sched.inbox.put(long_r)
+    sched.inbox.put(short_r)
+    assert all(ev.wait(10) for ev in evs)
+    assert short_r.t_first <= long_r.t_first
+    sched.shutdown()
+
+
+def test_dashboard_and_shutdown_persist():
+    srv, sched, eng, pr = make_server("</think>hi")
+
+    async def fn(c):
+        await c.post("/v1/chat/completions", json={"messages": MSG})
+        page = await c.get("/")
+        m = await c.get("/metrics.json")
+        return page.status, (await page.text())[:15], await m.json()
+    ps, head, m = with_client(srv, fn)
+    assert ps == 200 and head.lower().startswith("<!doctype html>")
+    assert m["model"] == "qw-test" and m["healthy"] is True and m["counts"]["completed"] == 1
+    assert eng.persisted == 1          # leaving the app persists the prefix cache
+
+
+def test_metrics_rings_and_fake_nvml():
+    from qwserve.dashboard.collector import Collector, Gpus
+    from qwserve.dashboard.metrics import Metrics
+    m = Metrics(seconds=3)
+    for i in range(5):
+        m.push({"a": i}, now=100.0 + i)
+    s = m.snapshot()
+    assert s["series"]["a"] == [2.0, 3.0, 4.0] and len(s["t"]) == 3
+    assert m.rate("c", 10, 1.0) == 0.0 and m.rate("c", 30, 3.0) == 10.0
+
+    class U:
+        gpu = 50
+    class M:
+        used, total = 2**31, 2**33
+    class Nv:
+        def nvmlInit(self): pass
+        def nvmlDeviceGetCount(self): return 2
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetUtilizationRates(self, h): return U
+        def nvmlDeviceGetMemoryInfo(self, h): return M
+        def nvmlDeviceGetPowerUsage(self, h): return 700000
+        def nvmlDeviceGetTemperature(self, h, k): return 55
+        def nvmlDeviceGetClockInfo(self, h, k): return 1900
+    g = Gpus(Nv()).sample()
+    assert len(g) == 2 and g[1]["power_w"] == 700.0 and g[0]["mem_used_gb"] == 2.0

@@ -1,0 +1,157 @@
+"""Unit tier of the server: vision preprocessing, URL fetch policy, placeholder expansion, tool-call parsing,
+output routing, detokeniser, and ctypes struct layouts against the C header
+(the reference's counterparts: server/tests/test_vision_preprocess.py, test_fetch.py, test_tool_calls.py,
+test_marshal.py)."""
+import base64
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from server_fixtures import make_tokenizer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_smart_resize_properties():
+    from qwserve.vision import smart_resize, video_smart_resize
+    for h, w in [(480, 640), (1080, 1920), (33, 3000), (4000, 3000), (17, 19)]:
+        H, W = smart_resize(h, w, 56 * 56, 1920 * 1088)
+        assert H % 32 == 0 and W % 32 == 0 and 56 * 56 <= H * W <= 1920 * 1088
+        if 56 * 56 <= h * w <= 1920 * 1088 and min(h, w) >= 32:
+            assert abs(H - h) <= 16 and abs(W - w) <= 16
+    with pytest.raises(ValueError):
+        smart_resize(10, 4000, 3136, 10**6)
+    H, W = video_smart_resize(7, 720, 1280, 128 * 32 * 32, 32 * 32 * 768)
+    assert H % 32 == 0 and W % 32 == 0 and 8 * H * W <= 32 * 32 * 768
+
+
+def test_patchify_matches_loops():
+    from qwserve.vision import patchify
+    rng = np.random.default_rng(0)
+    fr = rng.standard_normal((4, 64, 96, 3)).astype(np.float32)
+    rows, (t, h, w) = patchify(fr)
+    assert (t, h, w) == (2, 4, 6) and rows.shape == (48, 1536)
+    r = 0
+    for ti in range(t):
+        for hb in range(h // 2):
+            for wb in range(w // 2):
+                for dy in range(2):
+                    for dx in range(2):
+                        py, px = (hb * 2 + dy) * 16, (wb * 2 + dx) * 16
+                        ref = fr[ti * 2:ti * 2 + 2, py:py + 16, px:px + 16, :].transpose(3, 0, 1, 2).reshape(-1)
+                        assert np.array_equal(rows[r], ref)
+                        r += 1
+
+
+def test_image_preprocess_and_key():
+    from PIL import Image
+    from qwserve.vision import Preprocessor
+    pre = Preprocessor(None)
+    img = Image.fromarray((np.arange(100 * 130 * 3) % 255).astype(np.uint8).reshape(100, 130, 3))
+    a, b = pre.image(img), pre.image(img.copy())
+    assert a.grid == (1, 6, 8) and a.n_tokens == 12 and a.patches.shape == (48, 1536)
+    assert a.key == b.key and len(a.key) == 8
+    assert pre.image(img.transpose(Image.FLIP_LEFT_RIGHT)).key != a.key
+    assert np.abs(a.patches).max() <= 1.0 + 1e-6
+    # the two frames of an image's temporal patch are the same picture
+    r = a.patches[0].reshape(3, 2, 16, 16)
+    assert np.array_equal(r[:, 0], r[:, 1])
+
+
+def test_video_sampling_and_timestamps():
+    from qwserve.vision import Preprocessor
+    pre = Preprocessor(None)
+    frames = np.zeros((90, 64, 64, 3), np.uint8)        # 3 s at 30 fps -> 6 frames at 2 fps
+    idx = pre.sample_indices(90, 30.0)
+    assert len(idx) == 6 and idx[0] == 0 and idx[-1] == 89
+    m = pre.video(frames, 30.0)
+    assert m.kind == "video" and m.grid[0] == 3 and len(m.timestamps) == 3 and m.timestamps[0] < m.timestamps[-1]
+
+
+def test_fetch_policy(monkeypatch):
+    from qwserve import vision
+    data = b"\x89PNG fake"
+    assert vision.fetch("data:image/png;base64," + base64.b64encode(data).decode()) == data
+    for bad in ("http://127.0.0.1/x.png", "http://localhost/x", "http://10.1.2.3/x", "http://169.254.169.254/latest", "file:///etc/passwd",
+                "ftp://example.com/x"):
+        with pytest.raises(ValueError):
+            vision.check_url(bad)
+    monkeypatch.setenv("QW_MEDIA_FETCH", "0")
+    with pytest.raises(ValueError):
+        vision.check_url("https://example.com/a.png")
+    monkeypatch.setenv("QW_MEDIA_FETCH", "1")
+    monkeypatch.setenv("QW_MEDIA_ALLOW_PRIVATE", "1")
+    vision.check_url("http://127.0.0.1/x.png")
+
+
+def test_expand_placeholders():
+    from qwserve.vision import MediaItem, expand_placeholders
+    tok = make_tokenizer()
+    ipad, vpad = tok.token_to_id("<|image_pad|>"), tok.token_to_id("<|video_pad|>")
+    img = MediaItem("image", np.zeros((16, 1536), np.float32), (1, 4, 4), b"12345678")
+    vid = MediaItem("video", np.zeros((32, 1536), np.float32), (2, 4, 4), b"abcdefgh", timestamps=[0.5, 1.5])
+    ids = [1, ipad, 2, vpad, 3]
+    out = expand_placeholders(ids, [img, vid], tok)
+    assert out.count(ipad) == 4 and out.count(vpad) == 8
+    assert img.spans == [(1, 4)] and len(vid.spans) == 2 and all(out[s:s + n] == [vpad] * n for s, n in vid.spans)
+    assert "<0.5 seconds>" in tok.decode(out, skip_special_tokens=True)
+    with pytest.raises(ValueError):
+        expand_placeholders([ipad], [], tok)
+    with pytest.raises(ValueError):
+        expand_placeholders([1], [img], tok)
+    with pytest.raises(ValueError):
+        expand_placeholders([vpad], [img], tok)
+
+
+def test_tool_call_parser():
+    import json
+    from qwserve.tool_calls import parse_tool_call
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
+        "n": {"type": "integer"}, "x": {"type": "number"}, "ok": {"type": "boolean"}, "obj": {"type": "object"}, "s": {"type": "string"}}}}}]
+    txt = ("<function=f>\n<parameter=n>\n7\n</parameter>\n<parameter=x>\n1.5\n</parameter>\n<parameter=ok>\ntrue\n</parameter>\n"
+           "<parameter=obj>\n{\"a\": [1, 2]}\n</parameter>\n<parameter=s>\nif a < b and c > d:\n  pass\n</parameter>\n</function>")
+    c = parse_tool_call(txt, tools)
+    a = json.loads(c["function"]["arguments"])
+    assert a == {"n": 7, "x": 1.5, "ok": True, "obj": {"a": [1, 2]}, "s": "if a < b and c > d:\n  pass"}
+    assert c["type"] == "function" and c["id"].startswith("call_")
+    # truncated output: the open value runs to the end
+    c = parse_tool_call("<function=f>\n<parameter=s>\nhalf a val", tools)
+    assert json.loads(c["function"]["arguments"]) == {"s": "half a val"}
+    # no schema: JSON where it parses, text otherwise
+    c = parse_tool_call("<function=g>\n<parameter=k>\n[1,2]\n</parameter>\n<parameter=t>\nplain\n</parameter>\n</function>")
+    assert json.loads(c["function"]["arguments"]) == {"k": [1, 2], "t": "plain"}
+    assert parse_tool_call("no call here") is None
+
+
+def test_output_parser_and_detok():
+    from qwserve.detok import IncrementalDetok
+    from qwserve.output_parser import OutputParser, TagIds
+    p = OutputParser(TagIds(1, 2, 3, 4), start_in_think=True)
+    chans = [(r.channel if r else None) for r in map(p.push, [10, 11, 2, 12, 3, 13, 14, 4, 15, 1, 16, 2])]
+    assert chans == ["reasoning", "reasoning", None, "content", None, "tool", "tool", None, "content", None, "reasoning", None]
+    assert p.tool_tokens == [[13, 14]] and p.reasoning_tokens == 3
+    tok = make_tokenizer()
+    ids = tok.encode("añ日🙂z", add_special_tokens=False).ids
+    d = IncrementalDetok(lambda x: tok.decode(x, skip_special_tokens=False))
+    pieces = [d.push(i) for i in ids]
+    assert "".join(pieces) + d.flush() == "añ日🙂z" and all("�" not in s for s in pieces)
+    assert sum(1 for s in pieces if s == "") >= 5      # held back inside multi-byte characters
+
+
+def test_ctypes_structs_match_header(tmp_path):
+    """sizeof / offsetof as the C compiler sees the header == the ctypes mirrors."""
+    from qwserve import engine as E
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "qw/capi.h"\nint main(){'
+                   'printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(qw_sampling), offsetof(qw_sampling, seed), sizeof(qw_cache_stats),'
+                   'sizeof(qw_slot_timing), sizeof(qw_media), offsetof(qw_media, patches), sizeof(qw_step_req), offsetof(qw_step_req, sampling));return 0;}')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    want = [C.sizeof(E.Sampling), E.Sampling.seed.offset, C.sizeof(E.CacheStats), C.sizeof(E.SlotTiming), C.sizeof(E.Media),
+            E.Media.patches.offset, C.sizeof(E.StepReq), E.StepReq.sampling.offset]
+    assert got == want

@@ -1,0 +1,243 @@
+"""Python side of the C API shim (``native/src/capi.cpp``): one ``CApi`` object per ``qw_handle``.
+
+Every method takes the C call's scalars and the *addresses* of its buffers, reads / writes them with
+ctypes and forwards to the :class:`~qwb200.session.session.Session`.  ``open`` builds the engine from
+the options JSON: ``model_dir`` (a checkpoint) or ``synthetic`` (``"full" | "slice2" | "tiny"``, random
+weights), ``ple_dir`` or a synthetic table, ``slots`` (a list of capacities; the largest is used for all
+slots), ``prefill_chunk``, ``host_cache_gb``, ``disk_cache_dir``, ``disk_cache_gb``, ``devices``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import threading
+from typing import List, Optional
+
+import numpy as np
+
+
+class QwSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32), ("min_p", C.c_float),
+                ("presence_penalty", C.c_float), ("frequency_penalty", C.c_float), ("repetition_penalty", C.c_float),
+                ("seed", C.c_uint64)]
+
+
+class QwCacheStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("hits", "tokens_restored", "snapshots_saved", "ram_bytes", "disk_bytes", "blocks",
+                                          "snapshots", "prompt_tokens", "reused_tokens", "blend_candidate_tokens")]
+
+
+class QwSlotTiming(C.Structure):
+    _fields_ = [(n, C.c_double) for n in ("restore_s", "prefill_s", "save_s", "pin_wait_s")]
+
+
+class QwMedia(C.Structure):
+    _fields_ = [("hash", C.c_uint64), ("video", C.c_int32), ("t", C.c_int32), ("h", C.c_int32), ("w", C.c_int32),
+                ("patches", C.POINTER(C.c_float)), ("starts", C.POINTER(C.c_int64))]
+
+
+class QwStepReq(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("pending", C.c_int32), ("budget", C.c_int32), ("flags", C.c_int32), ("sampling", QwSampling)]
+
+
+def _i32(addr: int, n: int) -> List[int]:
+    if not addr or n <= 0:
+        return []
+    return np.ctypeslib.as_array(C.cast(addr, C.POINTER(C.c_int32)), shape=(n,)).tolist()
+
+
+def _sampling(addr: int):
+    from .engine.sampling import SamplingParams
+    if not addr:
+        return SamplingParams()
+    s = QwSampling.from_address(addr)
+    return SamplingParams(s.temperature, s.top_p, s.top_k, s.min_p, s.presence_penalty, s.frequency_penalty,
+                          s.repetition_penalty, s.seed)
+
+
+class CApi:
+    def __init__(self, session, vision=None):
+        self.s = session
+        self.vision = vision
+        self._failure = ""
+        self._lock = threading.Lock()
+
+    # ---- lifetime / health
+    def close(self):
+        try:
+            self.s.store.flush()
+        finally:
+            self.s = None
+
+    def persist(self):
+        self.s.persist()
+        return 0
+
+    def failure(self) -> str:
+        if self._failure:
+            return self._failure
+        try:
+            self.s.e.dm.check_error()
+        except RuntimeError as e:        # a kernel gave up on a bounded wait: sticky
+            self._failure = str(e)
+        return self._failure
+
+    # ---- cache
+    def set_boundary_token(self, tok):
+        self.s.set_boundary_token(tok)
+        return 0
+
+    def get_cache_stats(self, out):
+        st = self.s.cache_stats()
+        o = QwCacheStats.from_address(out)
+        for n, _ in QwCacheStats._fields_:
+            setattr(o, n, int(st.get(n, 0)))
+        return 0
+
+    def get_slot_timing(self, slot, out):
+        t = self.s.slot_timing(slot)
+        o = QwSlotTiming.from_address(out)
+        for n, _ in QwSlotTiming._fields_:
+            setattr(o, n, float(t.get(n, 0.0)))
+        return 0
+
+    # ---- slots / prompts
+    def num_slots(self):
+        return self.s.num_slots()
+
+    def slot_capacity(self, slot):
+        return self.s.slot_capacity(slot)
+
+    def _tokens(self, addr, n, media_addr, n_media):
+        toks = _i32(addr, n)
+        if n_media and self.vision is not None:
+            toks = self.vision.map_media_tokens(toks, media_addr, n_media)
+        return toks
+
+    def acquire(self, addr, n, max_new, media, n_media):
+        return self.s.acquire(self._tokens(addr, n, media, n_media), max_new)
+
+    def release(self, slot):
+        self.s.release(slot)
+        return 0
+
+    def begin_prompt(self, slot, addr, n, media, n_media):
+        toks = self._tokens(addr, n, media, n_media)
+        if n_media and self.vision is not None:
+            self.vision.stage(slot, media, n_media)
+        return self.s.begin_prompt(slot, toks)
+
+    def prefill_some(self, slot, max_tokens):
+        return 1 if self.s.prefill_some(slot, max_tokens) else 0
+
+    def set_prompt(self, slot, addr, n, media, n_media):
+        r = self.begin_prompt(slot, addr, n, media, n_media)
+        while not self.s.prefill_some(slot, 1 << 30):
+            pass
+        return r
+
+    def prefetch(self, slot, addr, n, media, n_media):
+        return 0            # the block store reads disk entries on demand during begin_prompt
+
+    def prefill_batch(self, n, slots, max_tokens, done):
+        sl = _i32(slots, n)
+        mt = np.ctypeslib.as_array(C.cast(max_tokens, C.POINTER(C.c_int64)), shape=(n,)).tolist()
+        d = np.ctypeslib.as_array(C.cast(done, C.POINTER(C.c_int32)), shape=(n,))
+        for i in range(n):
+            d[i] = 1 if self.s.prefill_some(sl[i], mt[i]) else 0
+        return 0
+
+    def has_vision(self):
+        return 1 if self.vision is not None else 0
+
+    def has_mtp(self):
+        return 1 if self.s.e.mtp else 0
+
+    def sample_prompt(self, slot, p, lp):
+        tok, l = self.s.sample_prompt(slot, _sampling(p))
+        if lp:
+            C.c_float.from_address(lp).value = l
+        return tok
+
+    # ---- decoding
+    def decode(self, n, slots, tokens):
+        self.s.decode(_i32(slots, n), _i32(tokens, n))
+        return 0
+
+    def sample_row(self, row, p, lp):
+        tok, l = self.s.sample_row(row, _sampling(p))
+        if lp:
+            C.c_float.from_address(lp).value = l
+        return tok
+
+    def set_stop_tokens(self, slot, ids, n):
+        self.s.set_stop_tokens(slot, _i32(ids, n))
+        return 0
+
+    def generate(self, n, reqs, k, tokens, logprobs, counts, first_rows, stopped):
+        from .session.session import StepReq
+        arr = (QwStepReq * n).from_address(reqs)
+        rq = [StepReq(r.slot, r.pending, r.budget, r.flags, _sampling(C.addressof(r.sampling))) for r in arr]
+        outs = self.s.generate(rq, k)
+        tk = np.ctypeslib.as_array(C.cast(tokens, C.POINTER(C.c_int32)), shape=(n * (k + 1),))
+        lp = np.ctypeslib.as_array(C.cast(logprobs, C.POINTER(C.c_float)), shape=(n * (k + 1),))
+        cn = np.ctypeslib.as_array(C.cast(counts, C.POINTER(C.c_int32)), shape=(n,))
+        fr = np.ctypeslib.as_array(C.cast(first_rows, C.POINTER(C.c_int32)), shape=(n,))
+        sp = np.ctypeslib.as_array(C.cast(stopped, C.POINTER(C.c_int32)), shape=(n,))
+        for i, o in enumerate(outs):
+            m = len(o.tokens)
+            tk[i * (k + 1): i * (k + 1) + m] = o.tokens
+            lp[i * (k + 1): i * (k + 1) + m] = o.logprobs
+            cn[i], fr[i], sp[i] = m, o.first_row, int(o.stopped)
+        return 0
+
+    def _write_top(self, pair, k, ids, lps):
+        i, l = pair
+        m = min(k, len(i))
+        np.ctypeslib.as_array(C.cast(ids, C.POINTER(C.c_int32)), shape=(k,))[:m] = i[:m]
+        np.ctypeslib.as_array(C.cast(lps, C.POINTER(C.c_float)), shape=(k,))[:m] = l[:m]
+        return m
+
+    def top_logprobs(self, row, k, ids, lps):
+        return self._write_top(self.s.top_logprobs(row, k), k, ids, lps)
+
+    def top_logprobs_prompt(self, slot, k, ids, lps):
+        return self._write_top(self.s.top_logprobs_prompt(slot, k), k, ids, lps)
+
+
+def open(options_json: str) -> CApi:
+    """Build engine + session from the options (see the module docstring)."""
+    import torch
+    from .engine.engine import Engine, EngineOptions
+    from .models.config import ModelConfig
+    from .session.session import Session
+    o = json.loads(options_json or "{}")
+    slots = o.get("slots", [8192])
+    if isinstance(slots, int):
+        slots = [8192] * slots
+    cap = int(o.get("slot_max_tokens") or max(slots))
+    devices = o.get("devices", [0])
+    dev = f"cuda:{devices[0]}"
+    opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
+                         save_gdn=bool(o.get("mtp", True)), host_pages=int(o.get("host_pages", 0)),
+                         dev_pages=o.get("dev_pages"))
+    if "model_dir" in o and o["model_dir"]:
+        from .models.config import check_hf_config
+        from .models.ple import PleTable
+        from .models.weights import load_checkpoint
+        cfg = ModelConfig.full()
+        check_hf_config(cfg, o["model_dir"])
+        w = load_checkpoint(cfg, o["model_dir"])
+        table = PleTable.load(cfg, o["ple_dir"], pin=True) if o.get("ple_dir") else None
+        eng = Engine.from_weights(cfg, w, table, opts, device=dev)
+    else:
+        kind = o.get("synthetic", "tiny")
+        cfg = {"full": ModelConfig.full, "slice2": ModelConfig.slice2, "tiny": ModelConfig.tiny}[kind]()
+        eng = Engine.synthetic(cfg, opts, device=dev, exact=(kind != "full"), ple_rows=int(o.get("ple_rows", 1 << 16)),
+                               ple_pinned=torch.cuda.is_available())
+    ses = Session(eng, host_cache_bytes=int(float(o.get("host_cache_gb", 8)) * (1 << 30)),
+                  disk_cache_dir=o.get("disk_cache_dir") or None,
+                  disk_cache_bytes=int(float(o.get("disk_cache_gb", 0)) * (1 << 30)),
+                  prefill_piece=int(o.get("prefill_piece", 2048)))
+    return CApi(ses)
