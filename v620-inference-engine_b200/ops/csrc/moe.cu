@@ -321,3 +321,46 @@ QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, c
                                (const bf16 *)sh_h, SF, out, ldo, take_pf());
     return e == cudaSuccess ? 0 : -2;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// qwk_moe_router_static: the router launch for callers that may not allocate device memory.
+// Declared and documented in no_alloc.h.  The scratch (router outputs + the block ticket) lives in this
+// file-scope array, whose address is looked up once per device.
+// ---------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_router_static_scratch[QWK_ROUTER_STATIC_SCRATCH_BYTES];
+static unsigned char *g_router_static_ptr[QWK_ROUTER_STATIC_MAX_DEVICES];     // per device, null until set up
+
+extern "C" __attribute__((visibility("default"))) int qwk_moe_router_static_setup(void) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= QWK_ROUTER_STATIC_MAX_DEVICES) return -3;
+    if (g_router_static_ptr[dev]) return 0;
+    unsigned char *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_router_static_scratch);
+    if (e != cudaSuccess || p == nullptr) return -3;
+    g_router_static_ptr[dev] = p;
+    return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int qwk_moe_router_static(const void *Wrs, const void *x, int nrs, int K, int M, int ldx, int E, int top_k, int F,
+                                 int e_first, int e_local, int *pair_expert, float *pair_w, void *sh_h, cudaStream_t s) {
+    if (E > 1024 || top_k > 32 || (K & 15) || (ldx & 7)) return -1;
+    if (M < 1 || M > QWK_ROUTER_STATIC_MAX_ROWS || nrs < 1 || nrs > QWK_ROUTER_STATIC_MAX_OUTPUTS) return -4;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= QWK_ROUTER_STATIC_MAX_DEVICES) return -3;
+    if (!g_router_static_ptr[dev] && qwk_moe_router_static_setup() != 0) return -3;
+    unsigned char *base = g_router_static_ptr[dev];
+    unsigned int *ticket = (unsigned int *)base;                       // first 256 bytes: the ticket word
+    float *rs = (float *)(base + 256);                                 // then [M][nrs] router outputs
+    // The ticket has to be zero when the kernel starts.  A finished launch leaves it at zero; the clear is
+    // for the launch that did not finish (an earlier error on the stream).
+    if (cudaMemsetAsync(ticket, 0, sizeof(unsigned int), s) != cudaSuccess) return -2;
+    SGemvArgs a;
+    a.W = (const bf16 *)Wrs; a.x = (const bf16 *)x; a.y = rs; a.y_bf16 = nullptr;
+    a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.nsplit = 1; a.w_split = 0; a.err = g_err_ptr; a.pf = take_pf();
+    RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
+    r.w13 = nullptr; r.w2 = nullptr; r.w13_bytes = 0; r.w2_bytes = 0; r.prefetch_rows = 0;
+    const cudaError_t e = launch_router(a, r, s);
+    return e == cudaSuccess ? 0 : -2;
+}
