@@ -252,11 +252,11 @@ class Engine:
                 # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
                 sl = self.slot[slot]
                 keep = self.prefiller.b["X"][len(chunk) - 1].clone()
+                if want_logits and last:             # the MTP rows below reuse the logits / argmax buffers
+                    saved = (self.dm.buf["logits"][:1].clone(), self.dm.buf["amax_idx"][:1].clone())
                 if sl.mtp_hidden is not None and base > 0:
                     self.dm.buf["hidden_out"][0] = sl.mtp_hidden
                     self.dm.mtp_step([chunk[0]], [slot], [base - 1])
-                if want_logits and last:
-                    saved = (self.dm.buf["logits"][:1].clone(), self.dm.buf["amax_idx"][:1].clone())
                 self.prefiller.mtp_pass(slot, base, len(chunk), chunk[1:])
                 if want_logits and last:
                     self.dm.buf["logits"][:1].copy_(saved[0])

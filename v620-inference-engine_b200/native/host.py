@@ -123,7 +123,7 @@ class BlockStore:
         self.root = lib().qwh_store_root()
 
     def close(self):
-        if self.s:
+        if getattr(self, "s", None) and lib is not None:      # `lib` is gone when the interpreter is shutting down
             lib().qwh_store_free(self.s)
             self.s = None
 
@@ -205,7 +205,7 @@ class HostSampler:
         return ids[:n], lps[:n]
 
     def __del__(self):
-        if getattr(self, "rng", None):
+        if getattr(self, "rng", None) and lib is not None:
             lib().qwh_rng_free(self.rng)
             self.rng = None
 

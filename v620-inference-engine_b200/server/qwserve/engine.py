@@ -164,9 +164,9 @@ class Engine:
     def top_logprobs(self, row: int, k: int):
         ids, lps = (C.c_int32 * k)(), (C.c_float * k)()
         n = self._ck(self.lib.qw_top_logprobs(self.h, row, k, ids, lps))
-        return list(ids[:n]), list(lps[:n])
+        return list(zip(ids[:n], lps[:n]))
 
     def top_logprobs_prompt(self, slot: int, k: int):
         ids, lps = (C.c_int32 * k)(), (C.c_float * k)()
         n = self._ck(self.lib.qw_top_logprobs_prompt(self.h, slot, k, ids, lps))
-        return list(ids[:n]), list(lps[:n])
+        return list(zip(ids[:n], lps[:n]))
