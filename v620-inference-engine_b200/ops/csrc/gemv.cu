@@ -24,6 +24,7 @@ template <int NT>
 __global__ void __launch_bounds__(SG_THREADS, 1) sgemv_kernel(SGemvArgs a) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
     sgemv_body<NT>(a, sg_smem);
+    fuse_publish(a.fo);
 }
 
 template <int NT>
@@ -64,9 +65,11 @@ QW_API int qwk_gemv_bf16(const void *W, const void *x, float *y, void *y_bf16, i
         SGemvArgs g;
         g.W = (const bf16 *)W; g.x = (const bf16 *)x; g.y = y; g.y_bf16 = (bf16 *)y_bf16;
         g.N = N; g.K = K; g.M = M; g.ldw = ldw; g.ldx = ldx; g.ldy = ldy; g.accumulate = accumulate; g.nsplit = 1; g.w_split = 0; g.err = g_err_ptr; g.pf = take_pf();
+        g.fi = take_fi(); g.fo = take_fo();
         const cudaError_t e = launch_sgemv(g, s);
         return e == cudaSuccess ? 0 : -2;
     }
+    if (g_fi.active || g_fo.mode) return -1;          // only the streaming kernel carries fused collectives
     GemvArgs a;
     a.W = (const bf16 *)W; a.x = (const bf16 *)x; a.y = y; a.y_bf16 = (bf16 *)y_bf16;
     a.N = N; a.K = K; a.M = M; a.ldw = ldw; a.ldx = ldx; a.ldy = ldy;

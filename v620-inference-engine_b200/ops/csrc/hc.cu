@@ -10,7 +10,7 @@
 //         u = silu(d/hc); g[s][c] = Wu[c][s] . u; block_in[c] = mean_s sigmoid(g) * y[s][c] * r_s   (hc_up_mix)
 // which uses that the down projection is linear in the un-normalised y (the algebra of the
 // reference's src/kernels/hc.hip:98-166 and src/engine/decode.hip:53-61).
-#include "common.cuh"
+#include "fuse.cuh"
 
 namespace qw {
 
@@ -60,7 +60,7 @@ constexpr int UP_MAXI = 5;     // 16-byte weight pieces per lane: covers mixer r
 __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
                                                         const float *X, const float *w1, int SH, int hc, int R, int hc_down,
                                                         float inv_H, float eps, int M, float *inj, int ld_inj, bf16 *bin,
-                                                        int ld_bin, int bin_col0, PfArgs pf) {
+                                                        int ld_bin, int bin_col0, PfArgs pf, FuseIn fi, FuseOut fo) {
     extern __shared__ float sm[];
     float *u = sm;                         // [UP_ROWS][R]
     float *rs = sm + UP_ROWS * R;          // [UP_ROWS][hc]
@@ -81,21 +81,24 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
     pf_issue(pf);
     pdl_wait();
     pdl_trigger();
+    fuse_wait(fi, false);          // fused all-reduce: every rank's partial sums have landed in the slots
+    // element i of the reduced vector: the local buffer, or the ranks' slots added in rank order
+    auto red_at = [&](long long i) -> float { return fi.active ? fuse_sum(fi, i) : red[i]; };
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
         const int mm = i / hc, ss = i % hc;
-        rs[mm * hc + ss] = rsqrtf(red[(long long)(m0 + mm) * ld_red + ss] * inv_H + eps);
+        rs[mm * hc + ss] = rsqrtf(red_at((long long)(m0 + mm) * ld_red + ss) * inv_H + eps);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nrow * hc_down; i += 256) {
         const int mm = i / hc_down, j = i % hc_down;
-        const float *p = red + (long long)(m0 + mm) * ld_red + hc + j;
+        const long long p = (long long)(m0 + mm) * ld_red + hc + j;
         float d = 0.f;
-        for (int ss = 0; ss < hc; ++ss) d = fmaf(rs[mm * hc + ss], p[ss * hc_down], d);
+        for (int ss = 0; ss < hc; ++ss) d = fmaf(rs[mm * hc + ss], red_at(p + ss * hc_down), d);
         if (j < R) u[mm * R + j] = siluf_(d / float(hc));
         else if (inj && blockIdx.x == 0) inj[(long long)(m0 + mm) * ld_inj + (j - R)] = d;
     }
     __syncthreads();
-    if (c >= SH) return;
+    if (c < SH) {
     float acc[UP_ROWS];
 #pragma unroll
     for (int mm = 0; mm < UP_ROWS; ++mm) acc[mm] = 0.f;
@@ -131,6 +134,8 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         v += __shfl_xor_sync(0xffffffffu, v, 16);
         if (lane == 0 && mm < nrow) bin[(long long)(m0 + mm) * ld_bin + bin_col0 + c] = __float2bfloat16(v / float(hc));
     }
+    }
+    fuse_publish(fo);          // fused all-gather: this rank's columns of the block input go to every peer
 }
 
 // ------------------------------------------------------------------------------------------
@@ -154,6 +159,8 @@ struct HcDownArgs {
     float *send;            // [M][ld_send]
     int ld_send, SH, hc, down, M, wpr;
     PfArgs pf;
+    FuseIn fi;              // fused reduce-scatter: `pend` is the sum of the ranks' slots
+    FuseOut fo;             // fused all-reduce of `send`
 };
 
 __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
@@ -181,6 +188,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
     pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
+    fuse_wait(a.fi, false);
     for (int r = 0; r < nrow; ++r) {           // the whole block builds each row slice: short dependent chains
         const int m = m0 + r;
         const float *xin = a.Xin + ((long long)m * a.hc + s) * a.SH;
@@ -190,7 +198,8 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
         for (int c = threadIdx.x * 4; c < a.SH; c += 1024) {
             float4 v = *reinterpret_cast<const float4 *>(xin + c);
             if (a.pend) {
-                const float4 p = *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
+                const float4 p = a.fi.active ? fuse_sum4(a.fi, (long long)m * a.ld_pend + c)
+                                             : *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
                 v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
                 v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
                 if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.Xout + ((long long)m * a.hc + s) * a.SH + c) = v;
@@ -252,6 +261,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
         for (int m = 0; m < 8; ++m)
             if (m < nrow) a.send[(long long)(m0 + m) * a.ld_send + a.hc + s * a.down + j] = acc[m];
     }
+    fuse_publish(a.fo);
 }
 
 }  // namespace qw
@@ -278,7 +288,8 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
     dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
     const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc);
     cudaError_t e = launch_pdl(hc_up_mix_kernel, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf());
+                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), take_fi(),
+                               take_fo());
     return e == cudaSuccess ? 0 : -2;
 }
 
@@ -290,6 +301,7 @@ QW_API int qwk_hc_down(const float *Xin, float *Xout, const float *pend, int ld_
     HcDownArgs a;
     a.Xin = Xin; a.Xout = Xout; a.pend = pend; a.ld_pend = ld_pend; a.inj_prev = inj_prev; a.w1 = w1;
     a.Wd = (const bf16 *)Wd; a.send = send; a.ld_send = ld_send; a.SH = SH; a.hc = hc; a.down = down; a.M = M; a.pf = take_pf();
+    a.fi = take_fi(); a.fo = take_fo();
     const long long rows = (long long)down * hc;
     a.wpr = rows >= NUM_SMS * 8 * 2 ? 1 : (rows >= NUM_SMS * 4 * 2 ? 2 : (rows >= NUM_SMS * 2 * 2 ? 4 : 8));
     if ((SH >> 3) < a.wpr * 32) {          // short rows: do not spread a row over more warps than it has pieces

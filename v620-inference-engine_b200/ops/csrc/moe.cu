@@ -203,7 +203,8 @@ __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w
 __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w2, const bf16 *s2, const bf16 *h,
                                                                const int *pair_expert, const float *pair_w, int top_k,
                                                                int F, int H, const bf16 *shared_down, int ld_sd,
-                                                               const bf16 *sh_h, int SF, float *out, int ldo, PfArgs pf) {
+                                                               const bf16 *sh_h, int SF, float *out, int ldo, PfArgs pf,
+                                                               FuseOut fo) {
     pf_issue(pf);
     const int m = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
     }
     pdl_wait();
     pdl_trigger();
-    if (c >= H) return;
+    if (c < H) {
     const int cpr = F >> 5, ks = F >> 7;
     const int total = top_k * cpr;
     uint4 w[DN_T];
@@ -263,6 +264,8 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
     }
     acc = warp_sum(acc);
     if (lane == 0) out[(long long)m * ldo + c] = acc;
+    }
+    fuse_publish(fo);          // reduce-scatter of `out`, sent by the block that finishes last
 }
 
 }  // namespace qw
@@ -287,6 +290,7 @@ QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, in
     SGemvArgs a;
     a.W = (const bf16 *)Wrs; a.x = (const bf16 *)x; a.y = rs; a.y_bf16 = nullptr;
     a.N = nrs; a.K = K; a.M = M; a.ldw = K; a.ldx = ldx; a.ldy = nrs; a.accumulate = 0; a.nsplit = 1; a.w_split = 0; a.err = g_err_ptr; a.pf = take_pf();
+    a.fi = take_fi();
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
     r.w13 = (const char *)w13; r.w2 = (const char *)w2; r.w13_bytes = w13_bytes; r.w2_bytes = w2_bytes;
     r.prefetch_rows = 0;       // one block cannot pull 24 MB through its copy engine fast enough: measured 2x slower; kept off
@@ -318,7 +322,7 @@ QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, c
     dim3 grid((H + 7) / 8, M);
     cudaError_t e = launch_pdl(moe_down_combine_kernel, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
                                (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
-                               (const bf16 *)sh_h, SF, out, ldo, take_pf());
+                               (const bf16 *)sh_h, SF, out, ldo, take_pf(), take_fo());
     return e == cudaSuccess ? 0 : -2;
 }
 

@@ -9,7 +9,7 @@
 // and flags are double-buffered by the parity of k: a rank can be at most one collective ahead of
 // any other, because each collective needs every rank's contribution.
 // (Role of the reference's src/comm/comm.hip:43-202; the transport there is PCIe P2P.)
-#include "common.cuh"
+#include "fuse.cuh"
 
 namespace qw {
 
@@ -34,15 +34,6 @@ struct P2PArgs {
     long long off_gather;        // all-gather: offset of the destination matrix inside every region
     ErrorWord *err;
 };
-
-__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __device__ __forceinline__ bool wait_flags(const P2PArgs &a, unsigned int want, int parity) {
     __shared__ int s_ok;
@@ -142,6 +133,40 @@ static void fill(P2PArgs &a, const QwP2P *p, int kind, unsigned k) {
     a.off_flags = p->off_flags[kind]; a.off_recv = p->off_recv[kind]; a.slot_bytes = p->slot_bytes[kind];
     a.err = g_err_ptr; a.scatter = 0; a.off_gather = 0; a.dst = nullptr; a.ld_dst = 0;
 }
+
+namespace qw {
+// What a producer kernel publishes for collective k of `kind` (see fuse.cuh for the modes).
+FuseOut make_fuse_out(const void *p2p, int kind, unsigned k, int mode, const void *src, int ld_src, int rows, int n,
+                      int elem, long long off_gather, unsigned int *ticket) {
+    const QwP2P *p = (const QwP2P *)p2p;
+    FuseOut o{};
+    o.mode = mode; o.ranks = p->ranks; o.rank = p->rank;
+    for (int i = 0; i < FUSE_MAX_RANKS; ++i) o.peer[i] = (char *)p->peer[i];
+    o.base = p->base; o.k = k;
+    o.off_flags = p->off_flags[kind]; o.off_recv = p->off_recv[kind]; o.slot_bytes = p->slot_bytes[kind];
+    o.off_gather = off_gather;
+    o.src = (const char *)src; o.ld_src = ld_src; o.rows = rows; o.n = n; o.elem = elem;
+    o.ticket = ticket; o.err = g_err_ptr;
+    return o;
+}
+
+// What a consumer kernel waits for (and, for a reduction, where the ranks' slots are).
+FuseIn make_fuse_in(const void *p2p, int kind, unsigned k, bool reduce) {
+    const QwP2P *p = (const QwP2P *)p2p;
+    FuseIn in{};
+    const int parity = k & 1;
+    char *local = (char *)p->peer[p->rank];
+    in.active = 1; in.ranks = p->ranks;
+    in.flags = reinterpret_cast<const unsigned int *>(local + p->off_flags[kind]) + (long long)parity * p->ranks * 16;
+    in.base = p->base; in.k = k;
+    if (reduce) {
+        in.slots = reinterpret_cast<const float *>(local + p->off_recv[kind] + (long long)parity * p->ranks * p->slot_bytes[kind]);
+        in.sstride = p->slot_bytes[kind] >> 2;
+    }
+    in.err = g_err_ptr;
+    return in;
+}
+}  // namespace qw
 
 // kind 0: dst[rows][n] = sum over ranks of src[rows][n] (fp32).
 QW_API int qwk_p2p_allreduce(const void *p2p, unsigned int k, const float *src, float *dst, int rows, int n, cudaStream_t s) {

@@ -9,13 +9,35 @@
 #include "runtime.h"
 
 #include "kernels.h"
-#include "common.cuh"
+#include "fuse.cuh"
 
 #include <vector>
 
 namespace qw {
 ErrorWord *g_err_ptr = nullptr;
 PfArgs g_pf = {};
+FuseOut g_fo = {};
+FuseIn g_fi = {};
+}
+
+// Ticket words of the fused collectives' producer kernels (each zero between launches).
+static __device__ unsigned int g_fuse_ticket_words[64];
+static unsigned int *fuse_ticket(int site) {
+    static unsigned int *base[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return nullptr;
+    if (!base[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_fuse_ticket_words) != cudaSuccess) return nullptr;
+        base[dev] = (unsigned int *)p;
+    }
+    return base[dev] + (site & 63);
+}
+static int g_fuse = 1;          // 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels
+extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int on) {
+    g_fuse = on ? 1 : 0;
+    return 0;
 }
 
 // Registers the device error word (8 bytes, zeroed by the caller) that kernels with bounded waits report to.
@@ -39,6 +61,11 @@ struct Ctx {
     int err;
     long long launches;
     float *X, *Xalt;     // current residual buffer and its ping-pong partner
+    // fused collectives: the block input's all-gather and the pending block output's reduce-scatter are
+    // waited for by the kernels that read them
+    bool fuse;
+    bool bin_pending, pend_fused;
+    int bin_site, pend_site;
     // L2 prefetch planning: a dry walk records the weights of every prefetch-capable launch in
     // order; the real walk hands launch k the ranges plan[k]
     bool dry;
@@ -70,6 +97,8 @@ int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the 
             ++c.op;                                                               \
             QW_TRYN(n, expr);                                                     \
             qw::g_pf = qw::PfArgs{};                                              \
+            qw::g_fo = qw::FuseOut{};                                             \
+            qw::g_fi = qw::FuseIn{};                                              \
         }                                                                         \
     } while (0)
 
@@ -98,6 +127,11 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const QwBuffers &b = md.b;
     const int M = c.rows->M, ld = hc_send(d);
     const int down = d.hc_rank + w.n_inj;
+    if (c.fuse && !c.dry) {
+        // the down projection consumes the pending block output's reduce-scatter and sends the all-reduce
+        if (pend && c.pend_fused) qw::g_fi = qw::make_fuse_in(md.p2p, 2, (unsigned)c.pend_site, true);
+        qw::g_fo = qw::make_fuse_out(md.p2p, 0, (unsigned)(c.site + 1), 1, b.send, ld, M, ld, 4, 0, fuse_ticket(c.site + 1));
+    }
     // fused: deferred combine (into the partner buffer) + sums of squares + down projection
     QW_OP(1, w.Wd, (size_t)down * d.hc * d.SH * 2,
           qwk_hc_down(c.X, pend ? c.Xalt : nullptr, pend, d.SH, inj_prev, w.w1, w.Wd, b.send, ld, d.SH, d.hc, down, M, c.s));
@@ -107,7 +141,15 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
         c.Xalt = t;
     }
     const float *red = b.send;
-    if (d.ranks > 1) {
+    if (c.fuse) {
+        ++c.site;
+        if (!c.dry) {
+            // the up projection consumes that all-reduce and sends its columns of the block input (all-gather)
+            qw::g_fi = qw::make_fuse_in(md.p2p, 0, (unsigned)c.site, true);
+            qw::g_fo = qw::make_fuse_out(md.p2p, 1, (unsigned)(c.site + 1), 3, (const char *)b.bin + (size_t)d.rank * d.SH * 2, d.H, M,
+                                         d.SH, 2, md.off_bin, fuse_ticket(c.site + 1));
+        }
+    } else if (d.ranks > 1) {
         comm(c, 0, b.send, b.red, M, ld);
         red = b.red;
     } else {
@@ -116,7 +158,27 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     QW_OP(1, w.Wu, (size_t)d.SH * d.hc * d.hc_rank * 2,
           qwk_hc_up_mix(red, ld, w.Wu, c.X, w.w1, d.SH, d.hc, d.hc_rank, w.n_inj, d.H, d.eps, M, inj_out, d.hc, b.bin, d.H,
                         d.rank * d.SH, c.s));
-    comm(c, 1, b.bin, b.bin, M, d.SH);
+    if (c.fuse) {
+        ++c.site;
+        c.bin_site = c.site;
+        c.bin_pending = true;          // the next kernel that reads the block input waits for it
+    } else {
+        comm(c, 1, b.bin, b.bin, M, d.SH);
+    }
+}
+
+// Before the first kernel that reads the gathered block input.
+inline void await_bin(Ctx &c) {
+    if (c.bin_pending && !c.dry) qw::g_fi = qw::make_fuse_in(c.md->p2p, 1, (unsigned)c.bin_site, false);
+    c.bin_pending = false;
+}
+
+// Before the kernel that writes the block output `partial`: it also sends the reduce-scatter.
+inline void send_partial(Ctx &c, bool fused) {
+    const QwDims &d = c.md->d;
+    if (fused && c.fuse && !c.dry)
+        qw::g_fo = qw::make_fuse_out(c.md->p2p, 2, (unsigned)(c.site + 1), 2, c.md->b.partial, d.H, c.rows->M, d.SH, 4, 0,
+                                     fuse_ticket(c.site + 1));
 }
 
 void gdn_block(Ctx &c, const QwLayer &L, int flags) {
@@ -126,6 +188,7 @@ void gdn_block(Ctx &c, const QwLayer &L, int flags) {
     const QwRows &r = *c.rows;
     const int M = r.M, gi = L.state_index;
     const int qkv_l = (2 * d.KL + d.VL) * 128;
+    await_bin(c);
     QW_OP(1, L.Wproj, (size_t)d.proj_gdn * d.H * 2,
           qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_gdn, d.H, M, d.H, d.H, d.proj_gdn, 0, 1, 0, 0, 0, c.s));
     float *save = nullptr;
@@ -142,6 +205,7 @@ void gdn_block(Ctx &c, const QwLayer &L, int flags) {
     }
     (void)qkv_l;
     const int K = d.VL * 128;
+    send_partial(c, true);
     QW_OP(1, L.Wout, (size_t)d.H * K * 2, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
@@ -152,6 +216,7 @@ void qsa_block(Ctx &c, const QwLayer &L) {
     const QwRows &r = *c.rows;
     const QwState &st = md.st;
     const int M = r.M, qi = L.state_index;
+    await_bin(c);
     QW_OP(1, L.Wproj, (size_t)d.proj_qsa * d.H * 2,
           qwk_gemv_bf16(L.Wproj, b.bin, b.proj, nullptr, d.proj_qsa, d.H, M, d.H, d.H, d.proj_qsa, 0, 1, 0, 0, 0, c.s));
     QW_TRYN((M <= 16 - d.idx_ratio ? 1 : 2), qwk_qsa_prep(b.proj, d.proj_qsa, d.QL, d.KVL, d.IH, L.qn1, L.kn1, L.iqn1, L.ikn1, M, r.slot, r.pos,
@@ -166,30 +231,41 @@ void qsa_block(Ctx &c, const QwLayer &L) {
                           st.page_table, d.max_pages, b.sel, b.sel_n, d.idx_topk, d.idx_ratio, d.nsplit, b.pm, b.pl,
                           b.pacc, b.proj, d.proj_qsa, b.o, c.s));
     const int K = d.QL * 256;
+    send_partial(c, true);
     QW_OP(1, L.Wout, (size_t)d.H * K * 2, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
-void moe_block(Ctx &c, const QwLayer &L) {
+void moe_block(Ctx &c, const QwLayer &L, bool fuse_out = true) {
     const QwModel &md = *c.md;
     const QwDims &d = md.d;
     const QwBuffers &b = md.b;
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
+    await_bin(c);
     QW_OP(1, L.Wrs, (size_t)nrs * d.H * 2, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
                               b.pair_w, b.sh_h, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
     QW_OP(1, nullptr, 0, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
+    send_partial(c, fuse_out);
     QW_OP(1, L.Wsd, (size_t)d.H * d.SF * 2, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
                                 d.SF, b.partial, d.H, c.s));
 }
 
 // partial [M][H] -> out [M][SH] (this rank's columns, summed over ranks)
-const float *scatter(Ctx &c, float *out) {
+const float *scatter(Ctx &c, float *out, bool fused = true) {
     const QwModel &md = *c.md;
     const QwDims &d = md.d;
     if (d.ranks == 1) {
         ++c.site;
         return md.b.partial;        // SH == H: the partial is the result
     }
+    if (c.fuse && fused) {
+        // the kernel that wrote `partial` has sent it; the next down projection adds up the slots
+        ++c.site;
+        c.pend_site = c.site;
+        c.pend_fused = true;
+        return out;
+    }
+    c.pend_fused = false;
     comm(c, 2, md.b.partial, out, c.rows->M, d.SH);
     return out;
 }
@@ -230,6 +306,8 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     c.Xalt = b.X2;
     c.site = 0;
     c.op = 0;
+    c.fuse = d.ranks > 1 && md->p2p && g_fuse;
+    c.bin_pending = c.pend_fused = false;
     if (d.ranks > 1 && md->p2p) QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
     QW_TRYN(1, qwk_embed_rows(c.rows->tokens, c.md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, c.s));
     const float *pend = nullptr;
@@ -246,15 +324,18 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
         else gdn_block(c, L, flags);
         const float *out_attn = scatter(c, b.out_a);
         mix(c, L.mlp_hc, out_attn, inj_attn, inj_mlp);
-        moe_block(c, L);
+        // the layer before the n-gram embedding layer hands its output to hc_pre, which reads a plain buffer
+        const bool fuse_out = !(l + 1 == d.ple_layer && c.md->ple.enabled);
+        moe_block(c, L, fuse_out);
         // The MoE output stays pending: the next mixer's hc_pre (or the final one) folds it into X
         // before anything overwrites `partial`, so with one rank it can be used in place.
-        pend = scatter(c, b.out_b);
+        pend = scatter(c, b.out_b, fuse_out);
     }
     mix(c, c.md->final_hc, pend, inj_mlp, nullptr);
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
         if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
     if (!(flags & QWRT_NO_HEAD)) {
+        await_bin(c);
         QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
                              c.s));
         QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
@@ -338,7 +419,8 @@ static void make_plan(const std::vector<WRange> &ops, size_t lookahead, std::vec
 
 extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
                                                                    int n_layers_run, cudaStream_t stream) {
-    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2, false, 0, nullptr, nullptr};
+    Ctx c{};
+    c.md = md; c.rows = rows; c.s = stream; c.X = md->b.X; c.Xalt = md->b.X2;
     const QwDims &d = md->d;
     const QwBuffers &b = md->b;
     const int M = rows->M;
@@ -374,7 +456,8 @@ extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md
     if (!md->mtp.enabled || md->d.ranks != 1) return -1;
     const int M = rows->M;
     if (M < 1 || M * md->d.hc > md->d.max_rows * md->d.hc) return -1;
-    Ctx c{md, rows, stream, 0, 0, 0, md->b.X, md->b.X2, false, 0, nullptr, nullptr};
+    Ctx c{};
+    c.md = md; c.rows = rows; c.s = stream; c.X = md->b.X; c.Xalt = md->b.X2;
     std::vector<WRange> ops;
     std::vector<qw::PfArgs> plan;
     c.dry = true;

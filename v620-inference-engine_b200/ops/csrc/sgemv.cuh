@@ -16,6 +16,7 @@
 // (fused gate/mean epilogue).
 #pragma once
 #include "mma.cuh"
+#include "fuse.cuh"
 
 namespace qw {
 
@@ -33,6 +34,8 @@ struct SGemvArgs {
     int nstage;
     ErrorWord *err;
     PfArgs pf;          // weights of later kernels to pull into L2
+    FuseIn fi = {};     // collective whose result the activation rows are (waited for before they are read)
+    FuseOut fo = {};    // collective that sends y (published by the kernel's last block)
 };
 
 constexpr int SG_HDR = 128;              // mbarriers: full[8], empty[8]
@@ -57,7 +60,7 @@ struct XFillCopy {
         for (int i = tid; i < (nm + 1) * nchunk; i += 256) {
             const int m = i / nchunk, c = i - m * nchunk;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < nm) v = __ldg(reinterpret_cast<const uint4 *>(a.x + (long long)(m0 + m) * a.ldx) + c);
+            if (m < nm) v = __ldcg(reinterpret_cast<const uint4 *>(a.x + (long long)(m0 + m) * a.ldx) + c);
             *reinterpret_cast<uint4 *>(sm.xs + (size_t)m * sm.xrow + (size_t)c * 16) = v;
         }
     }
@@ -132,6 +135,7 @@ __device__ __forceinline__ void sgemv_core(const SGemvArgs &a, unsigned char *sm
     pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
+    fuse_wait(a.fi, true);          // the peers' parts of the activation rows have landed
     const uint32_t xs_base = smem_u32(sm.xs), st_base = smem_u32(sm.stages);
     const int steps = Kc >> 4;
     bool ok = true;

@@ -97,6 +97,13 @@ def attach_p2p(eng: Engine, group=None) -> None:
     dm.graphs.clear()
 
 
+def set_fused(on: bool) -> None:
+    """Peer-memory backend: send every collective from the kernel that produces its payload and wait for it in
+    the kernel that consumes it (default), or run each collective as a kernel of its own."""
+    from ..ops import lib as qlib
+    qlib.load(True).qwrt_set_fuse(1 if on else 0)
+
+
 def attach_nccl(eng: Engine, group=None) -> None:
     """Unfused baseline: NCCL collectives through torch.distributed at every site."""
     dm = eng.dm
@@ -123,6 +130,7 @@ def attach_nccl(eng: Engine, group=None) -> None:
 
     dm.set_comm(cb)
     dm.model.p2p = None
+    eng.opts.use_graphs = False          # the collectives are enqueued from a host callback: steps are not graph-captured
 
     def merge_argmax(M):
         val, idx = b["amax_val"][:M].contiguous(), b["amax_idx"][:M].contiguous()
@@ -145,8 +153,9 @@ def make_engine(cfg: ModelConfig, opts: EngineOptions, world: int, rank: int, de
     eng = Engine.synthetic(cfg, opts, ranks=world, rank=rank, device=device, seed=seed, exact=exact,
                            ple_rows=ple_rows, log=log)
     if world > 1:
-        if comm == "p2p":
+        if comm in ("p2p", "p2p-unfused"):
             attach_p2p(eng)
+            set_fused(comm == "p2p")
         else:
             attach_nccl(eng)
     return eng

@@ -24,7 +24,7 @@ def main():
     from qwb200.models.config import ModelConfig
     from qwb200.models.ple import PleTable
     from qwb200.models.weights import synth_weights
-    from qwb200.parallel.dist_engine import attach_nccl, attach_p2p
+    from qwb200.parallel.dist_engine import attach_nccl, attach_p2p, set_fused
 
     cfg = ModelConfig.tiny(q_heads=8, kv_heads=2, gdn_qk_heads=8, gdn_v_heads=16, n_experts=32, hidden=512, ffn=256,
                            vocab=2048, eos=2000, image_pad=2001, video_pad=2002)
@@ -39,9 +39,10 @@ def main():
         want_logits.append(single.dm.buf["logits"][0].clone())
     want_logits = torch.stack(want_logits)
     ok = True
-    for backend in ("p2p", "nccl"):
+    for backend in ("p2p", "p2p-unfused", "nccl"):
         eng = Engine.from_weights(cfg, w, table, opts, ranks=world, rank=rank, device=dev)
-        (attach_p2p if backend == "p2p" else attach_nccl)(eng)
+        (attach_nccl if backend == "nccl" else attach_p2p)(eng)
+        set_fused(backend == "p2p")          # collectives inside the producer / consumer kernels, or as kernels of their own
         got_tok, got = [], []
         i, width = 0, 1
         while i < len(toks):                      # alternate 1-row and 2-row steps (runs of one slot)
@@ -74,6 +75,7 @@ def main():
     eng = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=True), ranks=world,
                               rank=rank, device=dev)
     attach_p2p(eng)
+    set_fused(True)
     eng.prefill(0, toks[:40])
     torch.cuda.synchronize()
     a = eng.decode_chain(0, toks[40], 12)

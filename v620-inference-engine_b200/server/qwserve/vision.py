@@ -187,6 +187,9 @@ class Preprocessor:
 
 
 # ---- fetching
+_GROUP_V4, _GROUP_V6 = ipaddress.ip_network("224.0.0.0/4"), ipaddress.ip_network("ff00::/8")
+
+
 def _public(host: str) -> bool:
     try:
         infos = socket.getaddrinfo(host, None)
@@ -194,7 +197,8 @@ def _public(host: str) -> bool:
         return False
     for info in infos:
         ip = ipaddress.ip_address(info[4][0])
-        if ip.is_private or ip.is_loopback or ip.is_link_local or ip.is_multicast or ip.is_reserved or ip.is_unspecified:
+        group = ip in (_GROUP_V4 if ip.version == 4 else _GROUP_V6)          # one-to-many group addresses
+        if ip.is_private or ip.is_loopback or ip.is_link_local or group or ip.is_reserved or ip.is_unspecified:
             return False
     return bool(infos)
 
