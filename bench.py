@@ -46,7 +46,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: run a model with fewer layers (marks the result invalid)")
     ap.add_argument("--ple-rows", type=int, default=1 << 22)
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end loop (default: --steps)")
-    ap.add_argument("--comm", default="p2p", choices=["p2p", "p2p-unfused", "nccl"],
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "p2p-unfused", "p2p-mute", "nccl"],
                     help="multi-GPU collectives: this library's peer-memory kernels, or the NCCL baseline")
     ap.add_argument("--profile-step", action="store_true",
                     help="bracket one extra chained decode step with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")

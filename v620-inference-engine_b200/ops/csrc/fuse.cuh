@@ -1,16 +1,20 @@
-// Collectives fused into the kernels around them (tensor / expert parallel decode).
+// Collectives fused into the kernels around them (tensor / expert parallel decode), low-latency protocol.
 //
-// A producer kernel (one that computes what a collective sends) ends with fuse_publish: the block that
-// finishes last copies the kernel's result straight into every peer's receive slot over NVLink with
-// plain peer stores and then raises this rank's sequence flag on every peer with a release store.
-// A consumer kernel (one that needs the collective's result) starts, after its weight prefetch, with
-// fuse_wait: it polls - bounded - the flags the peers raise in its own memory, and then reads the
-// result, summing the ranks' slots in rank order where the collective is a reduction, so every rank
-// computes bit-identical sums.  No kernel sits between the two: the transfer overlaps the consumer's
-// launch and weight prefetch, and a step has no collective launches at all.
+// Every value that has to cross NVLink travels as one 8-byte word {payload, sequence number}, written
+// with a single 8-byte store straight from the thread that computed it into the receive slot of every
+// rank that needs it.  A consumer polls the word itself until it carries the sequence number of the
+// collective it is waiting for - bounded - so there are no flags, no fences and no "last block": the
+// transfer starts while the producer kernel is still running and costs one NVLink crossing.
+// Reductions are done by the consumer, adding the ranks' words in rank order, so every rank computes
+// bit-identical sums.  No kernel sits between producer and consumer.
 //
-// Flags, slots, sequence numbers (`*base + k`, parity double buffering) are those of the stand-alone
-// collectives in p2p.cu, so fused and stand-alone sites can be mixed inside a step.
+//   all-reduce      hc_down  -> [every rank]        -> hc_up_mix adds the ranks' partial sums
+//   all-gather      hc_up_mix -> [every rank]       -> the block's first matrix product builds its rows
+//   reduce-scatter  out-projection / expert down    -> [owner of the column] -> hc_down adds the ranks' parts
+//
+// Sequence numbers are `*base + k` (a device counter bumped once per step + the collective's static
+// index in the step), slots are double buffered by the parity of k; both as in p2p.cu, whose
+// stand-alone collectives can be mixed with fused ones inside a step.
 // (Role of the reference's src/comm/comm.hip:43-202, where collectives are separate launches.)
 #pragma once
 #include "common.cuh"
@@ -19,30 +23,24 @@
 namespace qw {
 
 constexpr int FUSE_MAX_RANKS = 8;
-constexpr unsigned FUSE_SPIN_LIMIT = 1u << 24;      // polls before a wait gives up (about a second)
+constexpr unsigned FUSE_SPIN_LIMIT = 1u << 22;      // polls of one word before a wait gives up (about a second)
 
 struct FuseOut {
-    int mode;                    // 0 off | 1 whole rows to every rank's slot (all-reduce) | 2 column block d to rank d's
-                                 // slot (reduce-scatter) | 3 rows into place in every peer's matrix (all-gather)
+    int mode;                    // 0 off | 1 every word to every rank (all-reduce, all-gather) | 2 column c of a row to rank c / n (reduce-scatter)
     int ranks, rank;
-    char *peer[FUSE_MAX_RANKS];  // base of every rank's symmetric region
+    char *slot[FUSE_MAX_RANKS];  // on rank r: this rank's receive slot for collective k ([rows][n] words)
     const unsigned int *base;    // local: sequence base of this step
     unsigned int k;              // static index of this collective in the step
-    long long off_flags, off_recv, slot_bytes, off_gather;
-    const char *src;             // local result of this kernel
-    int ld_src;                  // row stride of src in elements
-    int rows, n, elem;           // rows x n elements of `elem` bytes per destination
-    unsigned int *ticket;        // zero before the launch; the last block resets it
-    ErrorWord *err;
+    int n;                       // words per row in a slot
 };
 
 struct FuseIn {
     int active, ranks;
-    const unsigned int *flags;   // local: flag of rank r at flags[r * 16]
+    const char *slots;           // local: slot of rank r at slots + r * slot_bytes
+    long long slot_bytes;
     const unsigned int *base;
     unsigned int k;
-    const float *slots;          // reductions: slot of rank r at slots + r * sstride
-    long long sstride;           // floats
+    int n;                       // words per row in a slot
     ErrorWord *err;
 };
 
@@ -51,9 +49,8 @@ extern FuseOut g_fo;
 extern FuseIn g_fi;
 inline FuseOut take_fo() { FuseOut r = g_fo; g_fo = FuseOut{}; return r; }
 inline FuseIn take_fi() { FuseIn r = g_fi; g_fi = FuseIn{}; return r; }
-FuseOut make_fuse_out(const void *p2p, int kind, unsigned k, int mode, const void *src, int ld_src, int rows, int n,
-                      int elem, long long off_gather, unsigned int *ticket);
-FuseIn make_fuse_in(const void *p2p, int kind, unsigned k, bool reduce);
+FuseOut make_fuse_out(const void *p2p, int kind, unsigned k, int mode, int n);
+FuseIn make_fuse_in(const void *p2p, int kind, unsigned k, int n);
 
 __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -63,100 +60,103 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_word(char *p, unsigned int payload, unsigned int seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word(const char *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
-// Every thread of every block calls this as the kernel's last statement.
-__device__ __forceinline__ void fuse_publish(const FuseOut &o) {
-    if (o.mode == 0) return;
-    __shared__ unsigned int s_fuse_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
-        s_fuse_last = atomicAdd(o.ticket, 1u) == total - 1 ? 1u : 0u;
-    }
-    __syncthreads();
-    if (!s_fuse_last) return;
-    __threadfence();
-    const unsigned int seq = __ldcg(o.base) + o.k;
-    const int parity = o.k & 1;
-    const long long row_bytes = (long long)o.n * o.elem, ld_bytes = (long long)o.ld_src * o.elem;
-    const bool wide = ((row_bytes | ld_bytes | (long long)(size_t)o.src | o.slot_bytes | o.off_recv | o.off_gather) & 15) == 0;
+__device__ __forceinline__ unsigned int fuse_seq(const FuseOut &o) { return __ldcg(o.base) + o.k; }
+__device__ __forceinline__ unsigned int fuse_seq(const FuseIn &in) { return __ldcg(in.base) + in.k; }
+
+// Producer: word `w` of row `m` goes to every rank.
+__device__ __forceinline__ void fuse_put_all(const FuseOut &o, unsigned int seq, int m, int w, unsigned int payload) {
+    const long long off = ((long long)m * o.n + w) * 8;
     for (int dd = 0; dd < o.ranks; ++dd) {
-        const int d = (o.rank + dd) % o.ranks;
-        if (o.mode == 3 && d == o.rank) continue;            // a gather's own rows are already in place
-        char *dbase;
-        long long drow, scol = 0;
-        if (o.mode == 3) {
-            dbase = o.peer[d] + o.off_gather + (long long)o.rank * row_bytes;
-            drow = (long long)o.ranks * row_bytes;
-        } else {
-            dbase = o.peer[d] + o.off_recv + ((long long)parity * o.ranks + o.rank) * o.slot_bytes;
-            drow = row_bytes;
-            if (o.mode == 2) scol = (long long)d * row_bytes;
-        }
-        if (wide) {
-            const int chunks = (int)(row_bytes >> 4);
-            for (int i = threadIdx.x; i < o.rows * chunks; i += blockDim.x) {
-                const int m = i / chunks, c = i - m * chunks;
-                const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(o.src + m * ld_bytes + scol) + c);
-                *reinterpret_cast<uint4 *>(dbase + m * drow + (long long)c * 16) = v;
-            }
-        } else {
-            const int chunks = (int)(row_bytes >> 2);
-            for (int i = threadIdx.x; i < o.rows * chunks; i += blockDim.x) {
-                const int m = i / chunks, c = i - m * chunks;
-                const unsigned int v = __ldcg(reinterpret_cast<const unsigned int *>(o.src + m * ld_bytes + scol) + c);
-                *reinterpret_cast<unsigned int *>(dbase + m * drow + (long long)c * 4) = v;
-            }
-        }
+        const int d = (o.rank + dd) % o.ranks;          // start with the own slot, spread the peers
+        st_word(o.slot[d] + off, payload, seq);
     }
-    __threadfence_system();
-    __syncthreads();
-    if ((int)threadIdx.x < o.ranks) {
-        unsigned int *f = reinterpret_cast<unsigned int *>(o.peer[threadIdx.x] + o.off_flags) + (parity * o.ranks + o.rank) * 16;
-        st_release_sys(f, seq);
-    }
-    if (threadIdx.x == 0) *o.ticket = 0u;
+}
+// Producer: column `c` of row `m` of a [rows][ranks * n] matrix goes to the rank that owns the column.
+__device__ __forceinline__ void fuse_put_col(const FuseOut &o, unsigned int seq, int m, int c, unsigned int payload) {
+    const int d = c / o.n, w = c - d * o.n;
+    st_word(o.slot[d] + ((long long)m * o.n + w) * 8, payload, seq);
 }
 
-// Threads 0..ranks-1 of the calling group poll; `named` = the group is the 256 consumer threads of the
-// streaming core (named barrier 1), otherwise the whole block.  Returns false after a timeout (the error
-// word holds where); the caller carries on so that the kernel ends.
-__device__ __forceinline__ bool fuse_wait(const FuseIn &in, bool named) {
-    if (!in.active) return true;
-    __shared__ int s_fuse_ok;
-    if (threadIdx.x == 0) s_fuse_ok = 1;
-    if (named) consumer_sync(256); else __syncthreads();
-    if ((int)threadIdx.x < in.ranks) {
-        const unsigned int want = __ldcg(in.base) + in.k;
-        const unsigned int *f = in.flags + threadIdx.x * 16;
-        unsigned int i = 0;
-        while ((int)(ld_acquire_sys(f) - want) < 0) {
-            if (++i > FUSE_SPIN_LIMIT) {
-                report(in.err, ERR_WAIT_TIMEOUT, 0x40000000u | (threadIdx.x << 24) | (in.k & 0xffffffu));
-                s_fuse_ok = 0;
-                break;
-            }
-            if (in.err && (i & 1023u) == 0 && in.err->code) { s_fuse_ok = 0; break; }     // someone already gave up
+// Consumer: the payload of word `w` of row `m` in rank r's slot, once it carries `seq`.
+__device__ __forceinline__ unsigned int fuse_get(const FuseIn &in, unsigned int seq, int r, long long word) {
+    const char *p = in.slots + r * in.slot_bytes + word * 8;
+    uint2 v = ld_word(p);
+    unsigned int i = 0;
+    while (v.y != seq) {
+        if (++i > FUSE_SPIN_LIMIT) {
+            report(in.err, ERR_WAIT_TIMEOUT, 0x40000000u | ((unsigned)r << 24) | (in.k & 0xffffffu));
+            return 0u;
         }
+        if (in.err && (i & 4095u) == 0 && in.err->code) return 0u;     // someone already gave up
+        v = ld_word(p);
     }
-    if (named) consumer_sync(256); else __syncthreads();
-    return s_fuse_ok != 0;
+    return v.x;
+}
+__device__ __forceinline__ uint4 ld_word2(const char *p) {          // two adjacent words, 16-byte aligned
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 
-// Element i of a reduced result: the ranks' slots added in rank order.
-__device__ __forceinline__ float fuse_sum(const FuseIn &in, long long i) {
+// Element `i` (row-major over [rows][n]) of a reduced result: the ranks' words added in rank order.  All the
+// loads are issued before the first one is looked at; a word that has not arrived yet is then polled.
+__device__ __forceinline__ float fuse_sum(const FuseIn &in, unsigned int seq, long long i) {
+    uint2 w[FUSE_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
+        if (r < in.ranks) w[r] = ld_word(in.slots + r * in.slot_bytes + i * 8);
     float v = 0.f;
-    for (int r = 0; r < in.ranks; ++r) v += __ldcg(in.slots + r * in.sstride + i);
+#pragma unroll
+    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
+        if (r < in.ranks) v += __uint_as_float(w[r].y == seq ? w[r].x : fuse_get(in, seq, r, i));
     return v;
 }
-__device__ __forceinline__ float4 fuse_sum4(const FuseIn &in, long long i) {
+
+// Four consecutive elements starting at `i` (i a multiple of 2).
+__device__ __forceinline__ float4 fuse_sum4(const FuseIn &in, unsigned int seq, long long i) {
+    uint4 a[FUSE_MAX_RANKS], b[FUSE_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
+        if (r < in.ranks) {
+            const char *p = in.slots + r * in.slot_bytes + i * 8;
+            a[r] = ld_word2(p);
+            b[r] = ld_word2(p + 16);
+        }
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < in.ranks; ++r) {
-        const float4 t = __ldcg(reinterpret_cast<const float4 *>(in.slots + r * in.sstride + i));
-        v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
-    }
+#pragma unroll
+    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
+        if (r < in.ranks) {
+            v.x += __uint_as_float(a[r].y == seq ? a[r].x : fuse_get(in, seq, r, i));
+            v.y += __uint_as_float(a[r].w == seq ? a[r].z : fuse_get(in, seq, r, i + 1));
+            v.z += __uint_as_float(b[r].y == seq ? b[r].x : fuse_get(in, seq, r, i + 2));
+            v.w += __uint_as_float(b[r].w == seq ? b[r].z : fuse_get(in, seq, r, i + 3));
+        }
     return v;
+}
+
+// Eight consecutive 16-bit payloads (all-gather of bf16) of rank r starting at word `i` (a multiple of 2), packed.
+__device__ __forceinline__ uint4 fuse_get8_u16(const FuseIn &in, unsigned int seq, int r, long long i) {
+    const char *p = in.slots + r * in.slot_bytes + i * 8;
+    uint4 q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = ld_word2(p + 16 * j);
+    unsigned int h[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        h[2 * j] = q[j].y == seq ? q[j].x : fuse_get(in, seq, r, i + 2 * j);
+        h[2 * j + 1] = q[j].w == seq ? q[j].z : fuse_get(in, seq, r, i + 2 * j + 1);
+    }
+    return make_uint4((h[0] & 0xffffu) | (h[1] << 16), (h[2] & 0xffffu) | (h[3] << 16), (h[4] & 0xffffu) | (h[5] << 16),
+                      (h[6] & 0xffffu) | (h[7] << 16));
 }
 
 }  // namespace qw

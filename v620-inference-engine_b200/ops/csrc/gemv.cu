@@ -24,7 +24,6 @@ template <int NT>
 __global__ void __launch_bounds__(SG_THREADS, 1) sgemv_kernel(SGemvArgs a) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
     sgemv_body<NT>(a, sg_smem);
-    fuse_publish(a.fo);
 }
 
 template <int NT>

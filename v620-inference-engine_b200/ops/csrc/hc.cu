@@ -81,9 +81,19 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
     pf_issue(pf);
     pdl_wait();
     pdl_trigger();
-    fuse_wait(fi, false);          // fused all-reduce: every rank's partial sums have landed in the slots
-    // element i of the reduced vector: the local buffer, or the ranks' slots added in rank order
-    auto red_at = [&](long long i) -> float { return fi.active ? fuse_sum(fi, i) : red[i]; };
+    // element i of the reduced vector: the local buffer, or (fused all-reduce) the ranks' words added in rank
+    // order - gathered once per block into shared memory, with every thread's loads in flight together
+    float *reds = rs + UP_ROWS * hc;       // [UP_ROWS][ld_red] (fused only)
+    if (fi.active) {
+        const unsigned int seq_in = fuse_seq(fi);
+        const int used = hc + hc * hc_down;          // what this mixer's down projection wrote of each row
+        for (int i = threadIdx.x; i < nrow * used; i += 256) {
+            const int mm = i / used, j = i - mm * used;
+            reds[mm * ld_red + j] = fuse_sum(fi, seq_in, (long long)(m0 + mm) * ld_red + j);
+        }
+        __syncthreads();
+    }
+    auto red_at = [&](long long i) -> float { return fi.active ? reds[i - (long long)m0 * ld_red] : red[i]; };
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
         const int mm = i / hc, ss = i % hc;
         rs[mm * hc + ss] = rsqrtf(red_at((long long)(m0 + mm) * ld_red + ss) * inv_H + eps);
@@ -98,7 +108,8 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         else if (inj && blockIdx.x == 0) inj[(long long)(m0 + mm) * ld_inj + (j - R)] = d;
     }
     __syncthreads();
-    if (c < SH) {
+    if (c >= SH) return;
+    const unsigned int seq_out = fo.mode ? fuse_seq(fo) : 0u;
     float acc[UP_ROWS];
 #pragma unroll
     for (int mm = 0; mm < UP_ROWS; ++mm) acc[mm] = 0.f;
@@ -132,10 +143,12 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         }
         v += __shfl_xor_sync(0xffffffffu, v, 8);
         v += __shfl_xor_sync(0xffffffffu, v, 16);
-        if (lane == 0 && mm < nrow) bin[(long long)(m0 + mm) * ld_bin + bin_col0 + c] = __float2bfloat16(v / float(hc));
+        if (lane == 0 && mm < nrow) {
+            const bf16 o = __float2bfloat16(v / float(hc));
+            if (fo.mode) fuse_put_all(fo, seq_out, m0 + mm, c, (unsigned int)__bfloat16_as_ushort(o));      // fused all-gather
+            else bin[(long long)(m0 + mm) * ld_bin + bin_col0 + c] = o;
+        }
     }
-    }
-    fuse_publish(fo);          // fused all-gather: this rank's columns of the block input go to every peer
 }
 
 // ------------------------------------------------------------------------------------------
@@ -188,7 +201,8 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
     pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
-    fuse_wait(a.fi, false);
+    const unsigned int seq_in = a.fi.active ? fuse_seq(a.fi) : 0u;
+    const unsigned int seq_out = a.fo.mode ? fuse_seq(a.fo) : 0u;
     for (int r = 0; r < nrow; ++r) {           // the whole block builds each row slice: short dependent chains
         const int m = m0 + r;
         const float *xin = a.Xin + ((long long)m * a.hc + s) * a.SH;
@@ -198,8 +212,12 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
         for (int c = threadIdx.x * 4; c < a.SH; c += 1024) {
             float4 v = *reinterpret_cast<const float4 *>(xin + c);
             if (a.pend) {
-                const float4 p = a.fi.active ? fuse_sum4(a.fi, (long long)m * a.ld_pend + c)
-                                             : *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
+                float4 p;
+                if (a.fi.active) {          // fused reduce-scatter: the ranks' parts of the block output, added in rank order
+                    p = fuse_sum4(a.fi, seq_in, (long long)m * a.ld_pend + c);
+                } else {
+                    p = *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
+                }
                 v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
                 v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
                 if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.Xout + ((long long)m * a.hc + s) * a.SH + c) = v;
@@ -213,7 +231,10 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
         }
         if (blockIdx.x == 0) {                 // block-uniform: only these blocks need the sum of squares
             ss = block_sum<256>(ss, scratch);
-            if (threadIdx.x == 0) a.send[(long long)m * a.ld_send + s] = ss;
+            if (threadIdx.x == 0) {
+                if (a.fo.mode) fuse_put_all(a.fo, seq_out, m, s, __float_as_uint(ss));      // fused all-reduce
+                else a.send[(long long)m * a.ld_send + s] = ss;
+            }
         }
     }
     __syncthreads();
@@ -259,9 +280,11 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
     if (kw == 0 && lane == 0 && j < a.down) {
 #pragma unroll
         for (int m = 0; m < 8; ++m)
-            if (m < nrow) a.send[(long long)(m0 + m) * a.ld_send + a.hc + s * a.down + j] = acc[m];
+            if (m < nrow) {
+                if (a.fo.mode) fuse_put_all(a.fo, seq_out, m0 + m, a.hc + s * a.down + j, __float_as_uint(acc[m]));
+                else a.send[(long long)(m0 + m) * a.ld_send + a.hc + s * a.down + j] = acc[m];
+            }
     }
-    fuse_publish(a.fo);
 }
 
 }  // namespace qw
@@ -286,10 +309,11 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
                          int bin_col0, cudaStream_t s) {
     if (hc != 4 || (R & 7) || R > 8 * 8 * UP_MAXI) return -1;
     dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
-    const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc);
+    const FuseIn fi = take_fi();
+    const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc + (fi.active ? UP_ROWS * ld_red : 0));
+    if (smem > 48 * 1024) return -1;
     cudaError_t e = launch_pdl(hc_up_mix_kernel, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), take_fi(),
-                               take_fo());
+                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, take_fo());
     return e == cudaSuccess ? 0 : -2;
 }
 

@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
     }
     pdl_wait();
     pdl_trigger();
-    if (c < H) {
+    if (c >= H) return;
     const int cpr = F >> 5, ks = F >> 7;
     const int total = top_k * cpr;
     uint4 w[DN_T];
@@ -263,9 +263,10 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
         acc += a;
     }
     acc = warp_sum(acc);
-    if (lane == 0) out[(long long)m * ldo + c] = acc;
+    if (lane == 0) {
+        if (fo.mode) fuse_put_col(fo, fuse_seq(fo), m, c, __float_as_uint(acc));      // fused reduce-scatter: to the column's owner
+        else out[(long long)m * ldo + c] = acc;
     }
-    fuse_publish(fo);          // reduce-scatter of `out`, sent by the block that finishes last
 }
 
 }  // namespace qw

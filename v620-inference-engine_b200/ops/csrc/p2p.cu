@@ -135,34 +135,27 @@ static void fill(P2PArgs &a, const QwP2P *p, int kind, unsigned k) {
 }
 
 namespace qw {
-// What a producer kernel publishes for collective k of `kind` (see fuse.cuh for the modes).
-FuseOut make_fuse_out(const void *p2p, int kind, unsigned k, int mode, const void *src, int ld_src, int rows, int n,
-                      int elem, long long off_gather, unsigned int *ticket) {
+// Where a producer kernel's words for collective k of `kind` go: this rank's slot on every rank.
+FuseOut make_fuse_out(const void *p2p, int kind, unsigned k, int mode, int n) {
     const QwP2P *p = (const QwP2P *)p2p;
     FuseOut o{};
+    const int parity = k & 1;
     o.mode = mode; o.ranks = p->ranks; o.rank = p->rank;
-    for (int i = 0; i < FUSE_MAX_RANKS; ++i) o.peer[i] = (char *)p->peer[i];
-    o.base = p->base; o.k = k;
-    o.off_flags = p->off_flags[kind]; o.off_recv = p->off_recv[kind]; o.slot_bytes = p->slot_bytes[kind];
-    o.off_gather = off_gather;
-    o.src = (const char *)src; o.ld_src = ld_src; o.rows = rows; o.n = n; o.elem = elem;
-    o.ticket = ticket; o.err = g_err_ptr;
+    for (int i = 0; i < p->ranks && i < FUSE_MAX_RANKS; ++i)
+        o.slot[i] = (char *)p->peer[i] + p->off_recv[kind] + ((long long)parity * p->ranks + p->rank) * p->slot_bytes[kind];
+    o.base = p->base; o.k = k; o.n = n;
     return o;
 }
 
-// What a consumer kernel waits for (and, for a reduction, where the ranks' slots are).
-FuseIn make_fuse_in(const void *p2p, int kind, unsigned k, bool reduce) {
+// Where a consumer kernel finds the ranks' words of collective k of `kind`.
+FuseIn make_fuse_in(const void *p2p, int kind, unsigned k, int n) {
     const QwP2P *p = (const QwP2P *)p2p;
     FuseIn in{};
     const int parity = k & 1;
-    char *local = (char *)p->peer[p->rank];
     in.active = 1; in.ranks = p->ranks;
-    in.flags = reinterpret_cast<const unsigned int *>(local + p->off_flags[kind]) + (long long)parity * p->ranks * 16;
-    in.base = p->base; in.k = k;
-    if (reduce) {
-        in.slots = reinterpret_cast<const float *>(local + p->off_recv[kind] + (long long)parity * p->ranks * p->slot_bytes[kind]);
-        in.sstride = p->slot_bytes[kind] >> 2;
-    }
+    in.slots = (const char *)p->peer[p->rank] + p->off_recv[kind] + (long long)parity * p->ranks * p->slot_bytes[kind];
+    in.slot_bytes = p->slot_bytes[kind];
+    in.base = p->base; in.k = k; in.n = n;
     in.err = g_err_ptr;
     return in;
 }

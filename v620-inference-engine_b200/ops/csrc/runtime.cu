@@ -20,23 +20,11 @@ FuseOut g_fo = {};
 FuseIn g_fi = {};
 }
 
-// Ticket words of the fused collectives' producer kernels (each zero between launches).
-static __device__ unsigned int g_fuse_ticket_words[64];
-static unsigned int *fuse_ticket(int site) {
-    static unsigned int *base[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return nullptr;
-    if (!base[dev]) {
-        void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_fuse_ticket_words) != cudaSuccess) return nullptr;
-        base[dev] = (unsigned int *)p;
-    }
-    return base[dev] + (site & 63);
-}
-static int g_fuse = 1;          // 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels
-extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int on) {
-    g_fuse = on ? 1 : 0;
+// 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels;
+// 2: timing diagnostic - nothing is sent or waited for, so a step costs what its kernels alone cost (results are wrong)
+static int g_fuse = 1;
+extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int mode) {
+    g_fuse = mode < 0 || mode > 2 ? 1 : mode;
     return 0;
 }
 
@@ -63,7 +51,7 @@ struct Ctx {
     float *X, *Xalt;     // current residual buffer and its ping-pong partner
     // fused collectives: the block input's all-gather and the pending block output's reduce-scatter are
     // waited for by the kernels that read them
-    bool fuse;
+    bool fuse, mute;
     bool bin_pending, pend_fused;
     int bin_site, pend_site;
     // L2 prefetch planning: a dry walk records the weights of every prefetch-capable launch in
@@ -93,6 +81,10 @@ int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the 
         if (c.dry) {                                                              \
             c.ops->push_back(WRange{(const char *)(wptr), (size_t)(wbytes)});     \
         } else {                                                                  \
+            if (c.mute) {                                                         \
+                qw::g_fo = qw::FuseOut{};                                         \
+                qw::g_fi = qw::FuseIn{};                                          \
+            }                                                                     \
             if (c.plan && c.op < (int)c.plan->size()) qw::g_pf = (*c.plan)[c.op]; \
             ++c.op;                                                               \
             QW_TRYN(n, expr);                                                     \
@@ -129,8 +121,8 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const int down = d.hc_rank + w.n_inj;
     if (c.fuse && !c.dry) {
         // the down projection consumes the pending block output's reduce-scatter and sends the all-reduce
-        if (pend && c.pend_fused) qw::g_fi = qw::make_fuse_in(md.p2p, 2, (unsigned)c.pend_site, true);
-        qw::g_fo = qw::make_fuse_out(md.p2p, 0, (unsigned)(c.site + 1), 1, b.send, ld, M, ld, 4, 0, fuse_ticket(c.site + 1));
+        if (pend && c.pend_fused) qw::g_fi = qw::make_fuse_in(md.p2p, 2, (unsigned)c.pend_site, d.SH);
+        qw::g_fo = qw::make_fuse_out(md.p2p, 0, (unsigned)(c.site + 1), 1, ld);
     }
     // fused: deferred combine (into the partner buffer) + sums of squares + down projection
     QW_OP(1, w.Wd, (size_t)down * d.hc * d.SH * 2,
@@ -145,9 +137,8 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
         ++c.site;
         if (!c.dry) {
             // the up projection consumes that all-reduce and sends its columns of the block input (all-gather)
-            qw::g_fi = qw::make_fuse_in(md.p2p, 0, (unsigned)c.site, true);
-            qw::g_fo = qw::make_fuse_out(md.p2p, 1, (unsigned)(c.site + 1), 3, (const char *)b.bin + (size_t)d.rank * d.SH * 2, d.H, M,
-                                         d.SH, 2, md.off_bin, fuse_ticket(c.site + 1));
+            qw::g_fi = qw::make_fuse_in(md.p2p, 0, (unsigned)c.site, ld);
+            qw::g_fo = qw::make_fuse_out(md.p2p, 1, (unsigned)(c.site + 1), 1, d.SH);
         }
     } else if (d.ranks > 1) {
         comm(c, 0, b.send, b.red, M, ld);
@@ -169,7 +160,7 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
 
 // Before the first kernel that reads the gathered block input.
 inline void await_bin(Ctx &c) {
-    if (c.bin_pending && !c.dry) qw::g_fi = qw::make_fuse_in(c.md->p2p, 1, (unsigned)c.bin_site, false);
+    if (c.bin_pending && !c.dry) qw::g_fi = qw::make_fuse_in(c.md->p2p, 1, (unsigned)c.bin_site, c.md->d.SH);
     c.bin_pending = false;
 }
 
@@ -177,8 +168,7 @@ inline void await_bin(Ctx &c) {
 inline void send_partial(Ctx &c, bool fused) {
     const QwDims &d = c.md->d;
     if (fused && c.fuse && !c.dry)
-        qw::g_fo = qw::make_fuse_out(c.md->p2p, 2, (unsigned)(c.site + 1), 2, c.md->b.partial, d.H, c.rows->M, d.SH, 4, 0,
-                                     fuse_ticket(c.site + 1));
+        qw::g_fo = qw::make_fuse_out(c.md->p2p, 2, (unsigned)(c.site + 1), 2, d.SH);
 }
 
 void gdn_block(Ctx &c, const QwLayer &L, int flags) {
@@ -307,6 +297,7 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     c.site = 0;
     c.op = 0;
     c.fuse = d.ranks > 1 && md->p2p && g_fuse;
+    c.mute = g_fuse == 2;
     c.bin_pending = c.pend_fused = false;
     if (d.ranks > 1 && md->p2p) QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
     QW_TRYN(1, qwk_embed_rows(c.rows->tokens, c.md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, c.s));

@@ -34,8 +34,8 @@ struct SGemvArgs {
     int nstage;
     ErrorWord *err;
     PfArgs pf;          // weights of later kernels to pull into L2
-    FuseIn fi = {};     // collective whose result the activation rows are (waited for before they are read)
-    FuseOut fo = {};    // collective that sends y (published by the kernel's last block)
+    FuseIn fi = {};     // fused all-gather: the activation rows are built from the ranks' words
+    FuseOut fo = {};    // fused reduce-scatter: y goes to the ranks that own its columns instead of memory
 };
 
 constexpr int SG_HDR = 128;              // mbarriers: full[8], empty[8]
@@ -66,16 +66,41 @@ struct XFillCopy {
     }
 };
 
+// Activation fill from a fused all-gather: column r * n + w of row m is word w of row m in rank r's slot (one bf16
+// per word).  Block 0 also leaves the dense rows in a.x for later kernels that read them from memory.
+struct XFillGather {
+    const SGemvArgs &a;
+    __device__ __forceinline__ void operator()(int /*split*/, int /*row0*/, int m0, int nm, const SGemvSmem &sm, int tid) const {
+        const unsigned int seq = fuse_seq(a.fi);
+        const int n = a.fi.n;                              // columns per rank (a multiple of 8)
+        const int nchunk = a.K >> 3;
+        for (int i = tid; i < nm * nchunk; i += 256) {
+            const int m = i / nchunk, c = (i - m * nchunk) * 8;
+            const int r = c / n, w = c - r * n;
+            const uint4 v = fuse_get8_u16(a.fi, seq, r, (long long)(m0 + m) * n + w);
+            *reinterpret_cast<uint4 *>(sm.xs + (size_t)m * sm.xrow + (size_t)c * 2) = v;
+            if (blockIdx.x == 0) *reinterpret_cast<uint4 *>(const_cast<bf16 *>(a.x) + (long long)(m0 + m) * a.ldx + c) = v;
+        }
+        for (int c = tid; c < (a.K >> 3); c += 256)
+            *reinterpret_cast<uint4 *>(sm.xs + (size_t)nm * sm.xrow + (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+};
+
 // Default epilogue: y[m][row] (+)= D.
 template <int NT>
 struct EpiStore {
     const SGemvArgs &a;
     __device__ __forceinline__ void operator()(int /*split*/, int row0, int m0, int nm, const SGemvSmem &sm, int tid) const {
+        const unsigned int seq = a.fo.mode ? fuse_seq(a.fo) : 0u;
         for (int e = tid; e < NT * 128; e += 256) {
             const int t = e >> 7, r = (e >> 3) & 15, n = e & 7;
             const int m = t * 8 + n;
             if (m < nm && row0 + r < a.N) {
                 float v = sm.sum[e];
+                if (a.fo.mode) {          // fused reduce-scatter: straight to the owner of the column
+                    fuse_put_col(a.fo, seq, m0 + m, row0 + r, __float_as_uint(v));
+                    continue;
+                }
                 const long long o = (long long)(m0 + m) * a.ldy + row0 + r;
                 if (a.accumulate) v += a.y[o];
                 a.y[o] = v;
@@ -135,7 +160,6 @@ __device__ __forceinline__ void sgemv_core(const SGemvArgs &a, unsigned char *sm
     pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
-    fuse_wait(a.fi, true);          // the peers' parts of the activation rows have landed
     const uint32_t xs_base = smem_u32(sm.xs), st_base = smem_u32(sm.stages);
     const int steps = Kc >> 4;
     bool ok = true;
@@ -222,7 +246,8 @@ static inline size_t sgemv_plan(SGemvArgs &a, int NT, int &grid, size_t extra = 
 // The plain GEMV body: default fill and store.
 template <int NT>
 __device__ __forceinline__ void sgemv_body(const SGemvArgs &a, unsigned char *smem) {
-    sgemv_core<NT>(a, smem, XFillCopy{a}, EpiStore<NT>{a});
+    if (a.fi.active) sgemv_core<NT>(a, smem, XFillGather{a}, EpiStore<NT>{a});
+    else sgemv_core<NT>(a, smem, XFillCopy{a}, EpiStore<NT>{a});
 }
 
 }  // namespace qw

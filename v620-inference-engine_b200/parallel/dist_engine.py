@@ -64,9 +64,13 @@ def attach_p2p(eng: Engine, group=None) -> None:
         off = _align(off + n)
     for k in range(4):
         take(f"flags{k}", 2 * R * 64)
-    slot0 = rows * sc.hc_send * 4
-    slot2 = rows * sc.sh * 4
+    # receive slots hold 8-byte words {payload, sequence number} for the fused collectives (the stand-alone
+    # kernels use the first half of a slot for plain fp32)
+    slot0 = rows * sc.hc_send * 8
+    slot1 = rows * sc.sh * 8
+    slot2 = rows * sc.sh * 8
     take("recv0", 2 * R * slot0)
+    take("recv1", 2 * R * slot1)
     take("recv2", 2 * R * slot2)
     take("bin", rows * c.hidden * 2)
     take("amax", rows * R * 2 * 4)
@@ -81,8 +85,9 @@ def attach_p2p(eng: Engine, group=None) -> None:
         p.off_flags[k] = lay[f"flags{k}"]
     p.off_recv[0], p.slot_bytes[0] = lay["recv0"], slot0
     p.off_recv[2], p.slot_bytes[2] = lay["recv2"], slot2
-    p.off_recv[1] = p.off_recv[3] = 0
-    p.slot_bytes[1] = p.slot_bytes[3] = 0
+    p.off_recv[1], p.slot_bytes[1] = lay["recv1"], slot1
+    p.off_recv[3] = 0
+    p.slot_bytes[3] = 0
     p.off_bin, p.off_amax = lay["bin"], lay["amax"]
     dm.p2p, dm.p2p_region = p, region
     base = region.ptrs[sc.rank]
@@ -101,7 +106,7 @@ def set_fused(on: bool) -> None:
     """Peer-memory backend: send every collective from the kernel that produces its payload and wait for it in
     the kernel that consumes it (default), or run each collective as a kernel of its own."""
     from ..ops import lib as qlib
-    qlib.load(True).qwrt_set_fuse(1 if on else 0)
+    qlib.load(True).qwrt_set_fuse(int(on))          # 2 = timing diagnostic without any exchange (wrong results)
 
 
 def attach_nccl(eng: Engine, group=None) -> None:
@@ -153,9 +158,9 @@ def make_engine(cfg: ModelConfig, opts: EngineOptions, world: int, rank: int, de
     eng = Engine.synthetic(cfg, opts, ranks=world, rank=rank, device=device, seed=seed, exact=exact,
                            ple_rows=ple_rows, log=log)
     if world > 1:
-        if comm in ("p2p", "p2p-unfused"):
+        if comm in ("p2p", "p2p-unfused", "p2p-mute"):
             attach_p2p(eng)
-            set_fused(comm == "p2p")
+            set_fused({"p2p": 1, "p2p-unfused": 0, "p2p-mute": 2}[comm])
         else:
             attach_nccl(eng)
     return eng
