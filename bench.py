@@ -48,6 +48,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end loop (default: --steps)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "p2p-unfused", "p2p-mute", "nccl"],
                     help="multi-GPU collectives: this library's peer-memory kernels, or the NCCL baseline")
+    ap.add_argument("--fuse-kinds", type=int, default=7,
+                    help="timing diagnostic (results are wrong unless 7): bit mask of the fused collective kinds that run "
+                         "(1 all-reduce, 2 all-gather, 4 reduce-scatter)")
     ap.add_argument("--profile-step", action="store_true",
                     help="bracket one extra chained decode step with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -84,6 +87,9 @@ def main():
     if world > 1:
         from qwb200.parallel.dist_engine import make_engine
         eng = make_engine(cfg, opts, world, rank, dev, ple_rows=args.ple_rows, log=log, comm=args.comm)
+        if args.fuse_kinds != 7:
+            from qwb200.ops import lib as qlib
+            qlib.load(True).qwrt_set_fuse_kinds(args.fuse_kinds)
     else:
         eng = Engine.synthetic(cfg, opts, device=dev, ple_rows=args.ple_rows, log=log)
     log(f"model ready in {time.time() - t0:.1f} s: {eng.dm.weight_bytes() / 1e9:.1f} GB of weights on rank {rank}")

@@ -72,18 +72,22 @@ __device__ __forceinline__ uint2 ld_word(const char *p) {
 __device__ __forceinline__ unsigned int fuse_seq(const FuseOut &o) { return __ldcg(o.base) + o.k; }
 __device__ __forceinline__ unsigned int fuse_seq(const FuseIn &in) { return __ldcg(in.base) + in.k; }
 
-// Producer: word `w` of row `m` goes to every rank.
+// Producer: word `w` of row `m` goes to every rank.  (Static indices only: a dynamically indexed kernel-parameter
+// array would be copied to local memory by every thread.)
 __device__ __forceinline__ void fuse_put_all(const FuseOut &o, unsigned int seq, int m, int w, unsigned int payload) {
     const long long off = ((long long)m * o.n + w) * 8;
-    for (int dd = 0; dd < o.ranks; ++dd) {
-        const int d = (o.rank + dd) % o.ranks;          // start with the own slot, spread the peers
-        st_word(o.slot[d] + off, payload, seq);
-    }
+#pragma unroll
+    for (int d = 0; d < FUSE_MAX_RANKS; ++d)
+        if (d < o.ranks) st_word(o.slot[d] + off, payload, seq);
 }
 // Producer: column `c` of row `m` of a [rows][ranks * n] matrix goes to the rank that owns the column.
 __device__ __forceinline__ void fuse_put_col(const FuseOut &o, unsigned int seq, int m, int c, unsigned int payload) {
     const int d = c / o.n, w = c - d * o.n;
-    st_word(o.slot[d] + ((long long)m * o.n + w) * 8, payload, seq);
+    char *p = o.slot[0];
+#pragma unroll
+    for (int r = 1; r < FUSE_MAX_RANKS; ++r)
+        if (r == d) p = o.slot[r];
+    st_word(p + ((long long)m * o.n + w) * 8, payload, seq);
 }
 
 // Consumer: the payload of word `w` of row `m` in rank r's slot, once it carries `seq`.
@@ -107,40 +111,50 @@ __device__ __forceinline__ uint4 ld_word2(const char *p) {          // two adjac
     return v;
 }
 
-// Element `i` (row-major over [rows][n]) of a reduced result: the ranks' words added in rank order.  All the
-// loads are issued before the first one is looked at; a word that has not arrived yet is then polled.
+// Element `i` (row-major over [rows][n]) of a reduced result: the ranks' words added in rank order.  The loads of
+// four ranks are issued before the first one is looked at; a word that has not arrived yet is then polled.
 __device__ __forceinline__ float fuse_sum(const FuseIn &in, unsigned int seq, long long i) {
-    uint2 w[FUSE_MAX_RANKS];
-#pragma unroll
-    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
-        if (r < in.ranks) w[r] = ld_word(in.slots + r * in.slot_bytes + i * 8);
     float v = 0.f;
+    for (int r0 = 0; r0 < in.ranks; r0 += 4) {
+        uint2 w[4];
 #pragma unroll
-    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
-        if (r < in.ranks) v += __uint_as_float(w[r].y == seq ? w[r].x : fuse_get(in, seq, r, i));
+        for (int r = 0; r < 4; ++r)
+            if (r0 + r < in.ranks) w[r] = ld_word(in.slots + (r0 + r) * in.slot_bytes + i * 8);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (r0 + r < in.ranks) v += __uint_as_float(w[r].y == seq ? w[r].x : fuse_get(in, seq, r0 + r, i));
+    }
     return v;
 }
 
-// Four consecutive elements starting at `i` (i a multiple of 2).
+// Two consecutive elements starting at `i` (i even), for two positions at once.
+__device__ __forceinline__ void fuse_sum2x2(const FuseIn &in, unsigned int seq, long long i0, long long i1, float2 &s0, float2 &s1) {
+    s0 = make_float2(0.f, 0.f);
+    s1 = make_float2(0.f, 0.f);
+    for (int r0 = 0; r0 < in.ranks; r0 += 4) {
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (r0 + r < in.ranks) {
+                a[r] = ld_word2(in.slots + (r0 + r) * in.slot_bytes + i0 * 8);
+                b[r] = ld_word2(in.slots + (r0 + r) * in.slot_bytes + i1 * 8);
+            }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (r0 + r < in.ranks) {
+                s0.x += __uint_as_float(a[r].y == seq ? a[r].x : fuse_get(in, seq, r0 + r, i0));
+                s0.y += __uint_as_float(a[r].w == seq ? a[r].z : fuse_get(in, seq, r0 + r, i0 + 1));
+                s1.x += __uint_as_float(b[r].y == seq ? b[r].x : fuse_get(in, seq, r0 + r, i1));
+                s1.y += __uint_as_float(b[r].w == seq ? b[r].z : fuse_get(in, seq, r0 + r, i1 + 1));
+            }
+    }
+}
+
+// Four consecutive elements starting at `i` (i even).
 __device__ __forceinline__ float4 fuse_sum4(const FuseIn &in, unsigned int seq, long long i) {
-    uint4 a[FUSE_MAX_RANKS], b[FUSE_MAX_RANKS];
-#pragma unroll
-    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
-        if (r < in.ranks) {
-            const char *p = in.slots + r * in.slot_bytes + i * 8;
-            a[r] = ld_word2(p);
-            b[r] = ld_word2(p + 16);
-        }
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int r = 0; r < FUSE_MAX_RANKS; ++r)
-        if (r < in.ranks) {
-            v.x += __uint_as_float(a[r].y == seq ? a[r].x : fuse_get(in, seq, r, i));
-            v.y += __uint_as_float(a[r].w == seq ? a[r].z : fuse_get(in, seq, r, i + 1));
-            v.z += __uint_as_float(b[r].y == seq ? b[r].x : fuse_get(in, seq, r, i + 2));
-            v.w += __uint_as_float(b[r].w == seq ? b[r].z : fuse_get(in, seq, r, i + 3));
-        }
-    return v;
+    float2 lo, hi;
+    fuse_sum2x2(in, seq, i, i + 2, lo, hi);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // Eight consecutive 16-bit payloads (all-gather of bf16) of rank r starting at word `i` (a multiple of 2), packed.

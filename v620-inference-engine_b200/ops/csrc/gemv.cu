@@ -20,20 +20,22 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(GemvArgs a) {
     gemv_body<MT>(a, part);
 }
 
-template <int NT>
+template <int NT, bool FUSED>
 __global__ void __launch_bounds__(SG_THREADS, 1) sgemv_kernel(SGemvArgs a) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
-    sgemv_body<NT>(a, sg_smem);
+    sgemv_body<NT, FUSED>(a, sg_smem);
 }
 
 template <int NT>
 static cudaError_t launch_sgemv_nt(SGemvArgs &a, size_t smem, int grid, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(sgemv_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SG_SMEM_MAX);
+        cudaFuncSetAttribute(sgemv_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SG_SMEM_MAX);
+        cudaFuncSetAttribute(sgemv_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SG_SMEM_MAX);
         configured = true;
     }
-    return launch_pdl(sgemv_kernel<NT>, dim3(grid), dim3(SG_THREADS), smem, s, a);
+    if (a.fi.active || a.fo.mode) return launch_pdl(sgemv_kernel<NT, true>, dim3(grid), dim3(SG_THREADS), smem, s, a);
+    return launch_pdl(sgemv_kernel<NT, false>, dim3(grid), dim3(SG_THREADS), smem, s, a);
 }
 
 // Up to 8 activation rows per pass, or 16 when they fit in shared memory next to the weight stages.

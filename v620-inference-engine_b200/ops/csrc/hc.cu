@@ -57,7 +57,8 @@ constexpr int UP_MAXI = 5;     // 16-byte weight pieces per lane: covers mixer r
 
 // grid (ceil(SH/8), ceil(M/UP_ROWS)), 256 threads.  hc must be 4 (one 8-lane group per stream).
 // y[s][c] = bf16(X[s][c] * w1[s][c]) is recomputed here exactly as hc_down_kernel computed it.
-__global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
+template <bool FUSED>
+__global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
                                                         const float *X, const float *w1, int SH, int hc, int R, int hc_down,
                                                         float inv_H, float eps, int M, float *inj, int ld_inj, bf16 *bin,
                                                         int ld_bin, int bin_col0, PfArgs pf, FuseIn fi, FuseOut fo) {
@@ -84,16 +85,28 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
     // element i of the reduced vector: the local buffer, or (fused all-reduce) the ranks' words added in rank
     // order - gathered once per block into shared memory, with every thread's loads in flight together
     float *reds = rs + UP_ROWS * hc;       // [UP_ROWS][ld_red] (fused only)
-    if (fi.active) {
+    if constexpr (FUSED) {
         const unsigned int seq_in = fuse_seq(fi);
-        const int used = hc + hc * hc_down;          // what this mixer's down projection wrote of each row
-        for (int i = threadIdx.x; i < nrow * used; i += 256) {
-            const int mm = i / used, j = i - mm * used;
-            reds[mm * ld_red + j] = fuse_sum(fi, seq_in, (long long)(m0 + mm) * ld_red + j);
+        // what this mixer's down projection wrote of each row (an even count), as pairs of words; a thread has
+        // the loads of two pairs from four ranks in flight at once
+        const int npair = (hc + hc * hc_down) >> 1, total = nrow * npair;
+        for (int p0 = threadIdx.x; p0 < total; p0 += 512) {
+            const int p1 = p0 + 256;
+            const bool two = p1 < total;
+            const int mm0 = p0 / npair, j0 = (p0 - mm0 * npair) * 2;
+            const int mm1 = two ? p1 / npair : mm0, j1 = two ? (p1 - mm1 * npair) * 2 : j0;
+            float2 a, b;
+            fuse_sum2x2(fi, seq_in, (long long)(m0 + mm0) * ld_red + j0, (long long)(m0 + mm1) * ld_red + j1, a, b);
+            reds[mm0 * ld_red + j0] = a.x;
+            reds[mm0 * ld_red + j0 + 1] = a.y;
+            if (two) {
+                reds[mm1 * ld_red + j1] = b.x;
+                reds[mm1 * ld_red + j1 + 1] = b.y;
+            }
         }
         __syncthreads();
     }
-    auto red_at = [&](long long i) -> float { return fi.active ? reds[i - (long long)m0 * ld_red] : red[i]; };
+    auto red_at = [&](long long i) -> float { return FUSED ? reds[i - (long long)m0 * ld_red] : red[i]; };
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
         const int mm = i / hc, ss = i % hc;
         rs[mm * hc + ss] = rsqrtf(red_at((long long)(m0 + mm) * ld_red + ss) * inv_H + eps);
@@ -109,7 +122,7 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
     }
     __syncthreads();
     if (c >= SH) return;
-    const unsigned int seq_out = fo.mode ? fuse_seq(fo) : 0u;
+    const unsigned int seq_out = FUSED ? fuse_seq(fo) : 0u;
     float acc[UP_ROWS];
 #pragma unroll
     for (int mm = 0; mm < UP_ROWS; ++mm) acc[mm] = 0.f;
@@ -145,7 +158,7 @@ __global__ void __launch_bounds__(256) hc_up_mix_kernel(const float *red, int ld
         v += __shfl_xor_sync(0xffffffffu, v, 16);
         if (lane == 0 && mm < nrow) {
             const bf16 o = __float2bfloat16(v / float(hc));
-            if (fo.mode) fuse_put_all(fo, seq_out, m0 + mm, c, (unsigned int)__bfloat16_as_ushort(o));      // fused all-gather
+            if (FUSED) fuse_put_all(fo, seq_out, m0 + mm, c, (unsigned int)__bfloat16_as_ushort(o));      // fused all-gather
             else bin[(long long)(m0 + mm) * ld_bin + bin_col0 + c] = o;
         }
     }
@@ -176,7 +189,8 @@ struct HcDownArgs {
     FuseOut fo;             // fused all-reduce of `send`
 };
 
-__global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
+template <bool FUSED>
+__global__ void __launch_bounds__(256, 3) hc_down_kernel(HcDownArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16 *ybuf = reinterpret_cast<bf16 *>(smraw);          // [8][SH]
     __shared__ float part[8][8];
@@ -201,8 +215,8 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
     pf_issue(a.pf);
     pdl_wait();
     pdl_trigger();
-    const unsigned int seq_in = a.fi.active ? fuse_seq(a.fi) : 0u;
-    const unsigned int seq_out = a.fo.mode ? fuse_seq(a.fo) : 0u;
+    const unsigned int seq_in = FUSED && a.fi.active ? fuse_seq(a.fi) : 0u;
+    const unsigned int seq_out = FUSED ? fuse_seq(a.fo) : 0u;
     for (int r = 0; r < nrow; ++r) {           // the whole block builds each row slice: short dependent chains
         const int m = m0 + r;
         const float *xin = a.Xin + ((long long)m * a.hc + s) * a.SH;
@@ -213,7 +227,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
             float4 v = *reinterpret_cast<const float4 *>(xin + c);
             if (a.pend) {
                 float4 p;
-                if (a.fi.active) {          // fused reduce-scatter: the ranks' parts of the block output, added in rank order
+                if (FUSED && a.fi.active) {          // fused reduce-scatter: the ranks' parts of the block output, added in rank order
                     p = fuse_sum4(a.fi, seq_in, (long long)m * a.ld_pend + c);
                 } else {
                     p = *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
@@ -232,7 +246,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
         if (blockIdx.x == 0) {                 // block-uniform: only these blocks need the sum of squares
             ss = block_sum<256>(ss, scratch);
             if (threadIdx.x == 0) {
-                if (a.fo.mode) fuse_put_all(a.fo, seq_out, m, s, __float_as_uint(ss));      // fused all-reduce
+                if (FUSED) fuse_put_all(a.fo, seq_out, m, s, __float_as_uint(ss));      // fused all-reduce
                 else a.send[(long long)m * a.ld_send + s] = ss;
             }
         }
@@ -281,7 +295,7 @@ __global__ void __launch_bounds__(256) hc_down_kernel(HcDownArgs a) {
 #pragma unroll
         for (int m = 0; m < 8; ++m)
             if (m < nrow) {
-                if (a.fo.mode) fuse_put_all(a.fo, seq_out, m0 + m, a.hc + s * a.down + j, __float_as_uint(acc[m]));
+                if (FUSED) fuse_put_all(a.fo, seq_out, m0 + m, a.hc + s * a.down + j, __float_as_uint(acc[m]));
                 else a.send[(long long)(m0 + m) * a.ld_send + a.hc + s * a.down + j] = acc[m];
             }
     }
@@ -312,8 +326,15 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
     const FuseIn fi = take_fi();
     const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc + (fi.active ? UP_ROWS * ld_red : 0));
     if (smem > 48 * 1024) return -1;
-    cudaError_t e = launch_pdl(hc_up_mix_kernel, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                               R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, take_fo());
+    const FuseOut fo = take_fo();
+    if ((fi.active != 0) != (fo.mode != 0)) return -1;          // the fused mixer both receives and sends
+    cudaError_t e;
+    if (fi.active)
+        e = launch_pdl(hc_up_mix_kernel<true>, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
+                       R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, fo);
+    else
+        e = launch_pdl(hc_up_mix_kernel<false>, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
+                       R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, fo);
     return e == cudaSuccess ? 0 : -2;
 }
 
@@ -336,9 +357,12 @@ QW_API int qwk_hc_down(const float *Xin, float *Xout, const float *pend, int ld_
     const size_t smem = (size_t)8 * SH * sizeof(bf16);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
-        cudaFuncSetAttribute(hc_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(hc_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(hc_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         attr_set = true;
     }
-    cudaError_t e = launch_pdl(hc_down_kernel, grid, dim3(256), smem, s, a);
+    if (a.fi.active && !a.fo.mode) return -1;          // a fused down projection always sends its all-reduce
+    cudaError_t e = a.fo.mode ? launch_pdl(hc_down_kernel<true>, grid, dim3(256), smem, s, a)
+                              : launch_pdl(hc_down_kernel<false>, grid, dim3(256), smem, s, a);
     return e == cudaSuccess ? 0 : -2;
 }

@@ -85,11 +85,11 @@ __device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, con
 }
 
 // Router GEMV (streaming kernel) with the routing done by the block that finishes last.
-template <int NT>
+template <int NT, bool FUSED>
 __global__ void __launch_bounds__(SG_THREADS, 1) moe_router_kernel(SGemvArgs a, RouteArgs r) {
     extern __shared__ __align__(128) unsigned char sg_smem[];
     __shared__ unsigned int s_last;
-    sgemv_body<NT>(a, sg_smem);
+    sgemv_body<NT, FUSED>(a, sg_smem);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = atomicAdd(r.ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
@@ -104,10 +104,12 @@ template <int NT>
 static cudaError_t launch_router_nt(SGemvArgs &a, const RouteArgs &r, size_t smem, int grid, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(moe_router_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        cudaFuncSetAttribute(moe_router_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        cudaFuncSetAttribute(moe_router_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         configured = true;
     }
-    return launch_pdl(moe_router_kernel<NT>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
+    if (a.fi.active) return launch_pdl(moe_router_kernel<NT, true>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
+    return launch_pdl(moe_router_kernel<NT, false>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
 }
 
 static cudaError_t launch_router(SGemvArgs &a, const RouteArgs &r, cudaStream_t s) {
@@ -200,6 +202,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w
 }
 
 // out[m][c] = sum_j w_j * (down_{e_j}[c] . h[p_j]) + shared_down[c] . sh_h[m].  grid (ceil(H/8), M).
+template <bool FUSED>
 __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w2, const bf16 *s2, const bf16 *h,
                                                                const int *pair_expert, const float *pair_w, int top_k,
                                                                int F, int H, const bf16 *shared_down, int ld_sd,
@@ -264,7 +267,7 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
     }
     acc = warp_sum(acc);
     if (lane == 0) {
-        if (fo.mode) fuse_put_col(fo, fuse_seq(fo), m, c, __float_as_uint(acc));      // fused reduce-scatter: to the column's owner
+        if (FUSED) fuse_put_col(fo, fuse_seq(fo), m, c, __float_as_uint(acc));      // fused reduce-scatter: to the column's owner
         else out[(long long)m * ldo + c] = acc;
     }
 }
@@ -321,9 +324,13 @@ QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, c
                                 const void *sh_h, int SF, float *out, int ldo, cudaStream_t s) {
     if ((F & 127) || (SF & 7) || top_k * (F >> 5) > 32 * DN_T || (SF >> 3) > 96) return -1;
     dim3 grid((H + 7) / 8, M);
-    cudaError_t e = launch_pdl(moe_down_combine_kernel, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
-                               (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
-                               (const bf16 *)sh_h, SF, out, ldo, take_pf(), take_fo());
+    const FuseOut fo = take_fo();
+    cudaError_t e = fo.mode ? launch_pdl(moe_down_combine_kernel<true>, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                         (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                         (const bf16 *)sh_h, SF, out, ldo, take_pf(), fo)
+                            : launch_pdl(moe_down_combine_kernel<false>, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                         (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                         (const bf16 *)sh_h, SF, out, ldo, take_pf(), fo);
     return e == cudaSuccess ? 0 : -2;
 }
 

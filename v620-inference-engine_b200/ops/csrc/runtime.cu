@@ -23,6 +23,17 @@ FuseIn g_fi = {};
 // 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels;
 // 2: timing diagnostic - nothing is sent or waited for, so a step costs what its kernels alone cost (results are wrong)
 static int g_fuse = 1;
+static int g_fuse_kinds = 7;    // timing diagnostic: bit k clear = collectives of kind k (0 all-reduce, 1 all-gather, 2 reduce-scatter) are skipped
+extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse_kinds(int mask) {
+    g_fuse_kinds = mask & 7;
+    return 0;
+}
+static qw::FuseOut fuse_out_of(const void *p2p, int kind, unsigned k, int mode, int n) {
+    return (g_fuse_kinds >> kind) & 1 ? qw::make_fuse_out(p2p, kind, k, mode, n) : qw::FuseOut{};
+}
+static qw::FuseIn fuse_in_of(const void *p2p, int kind, unsigned k, int n) {
+    return (g_fuse_kinds >> kind) & 1 ? qw::make_fuse_in(p2p, kind, k, n) : qw::FuseIn{};
+}
 extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int mode) {
     g_fuse = mode < 0 || mode > 2 ? 1 : mode;
     return 0;
@@ -121,8 +132,8 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const int down = d.hc_rank + w.n_inj;
     if (c.fuse && !c.dry) {
         // the down projection consumes the pending block output's reduce-scatter and sends the all-reduce
-        if (pend && c.pend_fused) qw::g_fi = qw::make_fuse_in(md.p2p, 2, (unsigned)c.pend_site, d.SH);
-        qw::g_fo = qw::make_fuse_out(md.p2p, 0, (unsigned)(c.site + 1), 1, ld);
+        if (pend && c.pend_fused) qw::g_fi = fuse_in_of(md.p2p, 2, (unsigned)c.pend_site, d.SH);
+        qw::g_fo = fuse_out_of(md.p2p, 0, (unsigned)(c.site + 1), 1, ld);
     }
     // fused: deferred combine (into the partner buffer) + sums of squares + down projection
     QW_OP(1, w.Wd, (size_t)down * d.hc * d.SH * 2,
@@ -137,8 +148,8 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
         ++c.site;
         if (!c.dry) {
             // the up projection consumes that all-reduce and sends its columns of the block input (all-gather)
-            qw::g_fi = qw::make_fuse_in(md.p2p, 0, (unsigned)c.site, ld);
-            qw::g_fo = qw::make_fuse_out(md.p2p, 1, (unsigned)(c.site + 1), 1, d.SH);
+            qw::g_fi = fuse_in_of(md.p2p, 0, (unsigned)c.site, ld);
+            qw::g_fo = fuse_out_of(md.p2p, 1, (unsigned)(c.site + 1), 1, d.SH);
         }
     } else if (d.ranks > 1) {
         comm(c, 0, b.send, b.red, M, ld);
@@ -160,7 +171,7 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
 
 // Before the first kernel that reads the gathered block input.
 inline void await_bin(Ctx &c) {
-    if (c.bin_pending && !c.dry) qw::g_fi = qw::make_fuse_in(c.md->p2p, 1, (unsigned)c.bin_site, c.md->d.SH);
+    if (c.bin_pending && !c.dry) qw::g_fi = fuse_in_of(c.md->p2p, 1, (unsigned)c.bin_site, c.md->d.SH);
     c.bin_pending = false;
 }
 
@@ -168,7 +179,7 @@ inline void await_bin(Ctx &c) {
 inline void send_partial(Ctx &c, bool fused) {
     const QwDims &d = c.md->d;
     if (fused && c.fuse && !c.dry)
-        qw::g_fo = qw::make_fuse_out(c.md->p2p, 2, (unsigned)(c.site + 1), 2, d.SH);
+        qw::g_fo = fuse_out_of(c.md->p2p, 2, (unsigned)(c.site + 1), 2, d.SH);
 }
 
 void gdn_block(Ctx &c, const QwLayer &L, int flags) {

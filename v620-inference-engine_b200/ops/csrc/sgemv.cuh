@@ -87,17 +87,17 @@ struct XFillGather {
 };
 
 // Default epilogue: y[m][row] (+)= D.
-template <int NT>
+template <int NT, bool FUSED = false>
 struct EpiStore {
     const SGemvArgs &a;
     __device__ __forceinline__ void operator()(int /*split*/, int row0, int m0, int nm, const SGemvSmem &sm, int tid) const {
-        const unsigned int seq = a.fo.mode ? fuse_seq(a.fo) : 0u;
+        const unsigned int seq = FUSED && a.fo.mode ? fuse_seq(a.fo) : 0u;
         for (int e = tid; e < NT * 128; e += 256) {
             const int t = e >> 7, r = (e >> 3) & 15, n = e & 7;
             const int m = t * 8 + n;
             if (m < nm && row0 + r < a.N) {
                 float v = sm.sum[e];
-                if (a.fo.mode) {          // fused reduce-scatter: straight to the owner of the column
+                if (FUSED && a.fo.mode) {          // fused reduce-scatter: straight to the owner of the column
                     fuse_put_col(a.fo, seq, m0 + m, row0 + r, __float_as_uint(v));
                     continue;
                 }
@@ -244,10 +244,14 @@ static inline size_t sgemv_plan(SGemvArgs &a, int NT, int &grid, size_t extra = 
 }
 
 // The plain GEMV body: default fill and store.
-template <int NT>
+template <int NT, bool FUSED = false>
 __device__ __forceinline__ void sgemv_body(const SGemvArgs &a, unsigned char *smem) {
-    if (a.fi.active) sgemv_core<NT>(a, smem, XFillGather{a}, EpiStore<NT>{a});
-    else sgemv_core<NT>(a, smem, XFillCopy{a}, EpiStore<NT>{a});
+    if constexpr (FUSED) {
+        if (a.fi.active) sgemv_core<NT>(a, smem, XFillGather{a}, EpiStore<NT, true>{a});
+        else sgemv_core<NT>(a, smem, XFillCopy{a}, EpiStore<NT, true>{a});
+    } else {
+        sgemv_core<NT>(a, smem, XFillCopy{a}, EpiStore<NT>{a});
+    }
 }
 
 }  // namespace qw
