@@ -240,4 +240,16 @@ def open(options_json: str) -> CApi:
                   disk_cache_dir=o.get("disk_cache_dir") or None,
                   disk_cache_bytes=int(float(o.get("disk_cache_gb", 0)) * (1 << 30)),
                   prefill_piece=int(o.get("prefill_piece", 2048)))
-    return CApi(ses)
+    vision = None
+    if o.get("vision", True) and torch.cuda.is_available():
+        from .vision import VisionConfig, VisionEncoder, VisionFrontend, synth_vision_weights
+        enc = None
+        if o.get("model_dir"):
+            enc = VisionEncoder.from_checkpoint(o["model_dir"], dev)
+        elif o.get("vision") == "synthetic":
+            vc = VisionConfig(depth=int(o.get("vision_depth", 2)), out_dim=cfg.hidden)
+            enc = VisionEncoder(vc, synth_vision_weights(vc, seed=1), dev)
+        if enc is not None:
+            vision = VisionFrontend(enc, int(float(o.get("vision_cache_gb", 2)) * (1 << 30)))
+            eng.vision_lookup = vision.lookup
+    return CApi(ses, vision)

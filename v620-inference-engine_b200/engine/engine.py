@@ -57,6 +57,7 @@ class Engine:
         self.out_host = torch.zeros(opts.max_rows, dtype=torch.int32).pin_memory()
         self.merge_argmax = None        # set by the NCCL backend: merges the ranks' (max, argmax) after a step
         self.prefiller = None           # token-major prefill, built on first use (one GPU)
+        self.vision_lookup = None       # vision token ids -> embeddings [n, hidden] (set by the vision front end)
         self.steps = 0
 
     # ---- construction
@@ -119,7 +120,10 @@ class Engine:
         """Append ``tokens`` to the slot.  Returns the logits of the last token (device tensor)."""
         toks = [int(t) for t in tokens]
         n = len(toks)
-        if self.dm.sc.ranks == 1 and self.opts.prefill_chunk > 0 and n >= self.opts.prefill_min:
+        has_media = any(t < 0 for t in toks)
+        if has_media and (self.vision_lookup is None or self.dm.sc.ranks != 1 or self.opts.prefill_chunk <= 0):
+            raise ValueError("vision tokens need a vision tower and the token-major prefill path")
+        if self.dm.sc.ranks == 1 and self.opts.prefill_chunk > 0 and (n >= self.opts.prefill_min or has_media):
             return self._prefill_token_major(slot, toks, want_logits)
         step = max(1, min(self.opts.prefill_rows, self.opts.max_rows))
         i = 0
@@ -247,7 +251,11 @@ class Engine:
             chunk = toks[i:i + T]
             last = i + T >= len(toks)
             base = self.slot[slot].n
-            out = self.prefiller.run(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last)
+            embeds = None
+            vis = [j for j, t in enumerate(chunk) if t < 0]
+            if vis:         # rows that carry vision tokens take the tower's output as their embedding
+                embeds = (torch.tensor(vis, dtype=torch.long, device=self.dm.dev), self.vision_lookup([chunk[j] for j in vis]))
+            out = self.prefiller.run(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last, embeds=embeds)
             if self.mtp:
                 # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
                 sl = self.slot[slot]

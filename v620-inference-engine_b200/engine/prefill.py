@@ -107,7 +107,7 @@ class Prefiller:
 
     # ---- one chunk
     @torch.no_grad()
-    def run(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True):
+    def run(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True, embeds=None):
         dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
         T = len(tokens)
         assert 1 <= T <= self.T
@@ -118,6 +118,10 @@ class Prefiller:
         d = dm.model.d
         self._ck(L.qwk_embed_rows(rp("tokens"), P(dm.globals_w["embed"].data_ptr()), c.hidden, 0, sc.sh, c.hc, c.vocab,
                                   _p(b["X"]), T, s), "embed")
+        if embeds is not None:          # (row indices, [n, hidden] fp32): these rows' embedding replaces the table's
+            rows_i, emb = embeds
+            X = b["X"][:T].view(T, c.hc, sc.sh)
+            X[rows_i] = emb.to(X.dtype)[:, None, :sc.sh].expand(-1, c.hc, -1)
         pend, inj_prev = None, None
         inj_attn, inj_mlp = b["inj_a"], b["inj_b"]
         max_groups = (base + T) // c.idx_ratio

@@ -23,11 +23,13 @@ def _mix(x: int) -> int:          # splitmix64 finaliser
     return x ^ (x >> 31)
 
 
-def media_key(content_hash: int, slice_index: int, token_index: int) -> int:
+def media_key(content_hash: int, slice_index: int, token_index: int, video: bool = False) -> int:
     """The (negative, 32-bit) token id of one vision token: a hash of the media's content hash and the token's place in
-    it.  Never 0 or positive, so it cannot collide with a text token."""
-    v = _mix(content_hash ^ _mix((slice_index << 32) | token_index)) & 0x7FFFFFFF
-    return -(v if v else 1)
+    it.  Never 0 or positive, so it cannot collide with a text token; the magnitude is odd for image tokens and even
+    for video tokens (``ModelConfig.real_token`` reads the pad token to hash and embed from that bit)."""
+    v = _mix(content_hash ^ _mix((slice_index << 32) | token_index)) & 0x7FFFFFFE
+    v |= 0 if video else 1
+    return -(v if v else 2)
 
 
 def assign_slices(costs: Sequence[float], ranks: int) -> List[List[int]]:
