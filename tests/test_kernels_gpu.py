@@ -91,6 +91,13 @@ def test_moe_pair_kernels_match_oracle():
     idx, wgt, _ = ref.route("layers.0.mlp.", x.float())
     assert torch.equal(pe.cpu().long(), idx)
     assert torch.allclose(pw.cpu(), wgt, atol=1e-5)
-    out = K_.moe_experts_pair(mw["w13"], mw["s13"], mw["w2"], mw["s2"], xd, pe, pw, cfg.ffn, cfg.hidden, mw["Wsd"], sh)
-    err = (out.cpu() - want).abs().max() / want.abs().max()
-    assert err < 2e-2, float(err)
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    try:
+        for mask in (0, 1, 3):          # scalar kernels, tensor-core gate/up, tensor-core gate/up and down
+            L.qwk_set_moe_mma(mask)
+            out = K_.moe_experts_pair(mw["w13"], mw["s13"], mw["w2"], mw["s2"], xd, pe, pw, cfg.ffn, cfg.hidden, mw["Wsd"], sh)
+            err = (out.cpu() - want).abs().max() / want.abs().max()
+            assert err < 2e-2, (mask, float(err))
+    finally:
+        L.qwk_set_moe_mma(1)

@@ -7,7 +7,10 @@
 //                weights (16 bytes) per lane and load, all loads of a warp independent, with the
 //                weighted combine and the shared expert's down projection fused into the second.
 // (Roles of the reference's src/kernels/moe_route.hip:65-224 and src/kernels/moe_experts.hip:189-246.)
+#include <cstdlib>
+
 #include "sgemv.cuh"
+#include "moe_mma.cuh"
 
 namespace qw {
 
@@ -276,6 +279,23 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
 
 using namespace qw;
 
+// Which routed-expert kernels run on the tensor cores: bit 0 = gate/up, bit 1 = down.  Default 1: inside the decode
+// graph the tensor-core gate/up kernel costs the same 15 us as the scalar one (the time is the router -> expert id ->
+// weights dependency chain, not the arithmetic) with a third of the instructions; the tensor-core down kernel's longer
+// per-warp chain made the step 0.3 ms slower, so the scalar one stays the default.  QW_MOE_MMA overrides at start-up.
+static int g_moe_mma = -1;
+static int moe_mma_mask() {
+    if (g_moe_mma < 0) {
+        const char *e = getenv("QW_MOE_MMA");
+        g_moe_mma = e ? atoi(e) & 3 : 1;
+    }
+    return g_moe_mma;
+}
+QW_API int qwk_set_moe_mma(int mask) {
+    g_moe_mma = mask & 3;
+    return 0;
+}
+
 static RouteArgs make_route(int E, int top_k, int F, int e_first, int e_local, int *pair_expert, float *pair_w,
                             void *sh_h, unsigned int *ticket) {
     RouteArgs r;
@@ -312,7 +332,15 @@ QW_API int qwk_moe_route(const float *rs, int ld_rs, int M, int E, int top_k, in
 
 QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x, int ldx, const int *pair_expert, int M,
                                 int top_k, int F, int K, void *h, cudaStream_t s) {
-    if ((K & 127) || (ldx & 7) || 2 * (K >> 5) > 32 * GU_T) return -1;
+    if ((K & 127) || (ldx & 7)) return -1;
+    if ((moe_mma_mask() & 1) && (F & 15) == 0 && (K >> 7) <= MM_WARPS * GU_NG) {
+        // tensor-core form: 16 rows of gate and of up per block
+        const size_t smem = (size_t)K * 2 + MM_WARPS * 2 * 16 * sizeof(float);
+        cudaError_t e = launch_pdl(moe_gate_up_mma_kernel, dim3(F / 16, M * top_k), dim3(128), smem, s, (const uint32_t *)w13,
+                                   (const bf16 *)s13, (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf());
+        return e == cudaSuccess ? 0 : -2;
+    }
+    if (2 * (K >> 5) > 32 * GU_T) return -1;
     dim3 grid((F + 7) / 8, M * top_k);
     cudaError_t e = launch_pdl(moe_gate_up_pair_kernel, grid, dim3(256), 0, s, (const uint32_t *)w13, (const bf16 *)s13,
                                (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf());
@@ -322,9 +350,24 @@ QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x,
 QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, const int *pair_expert,
                                 const float *pair_w, int M, int top_k, int F, int H, const void *shared_down, int ld_sd,
                                 const void *sh_h, int SF, float *out, int ldo, cudaStream_t s) {
-    if ((F & 127) || (SF & 7) || top_k * (F >> 5) > 32 * DN_T || (SF >> 3) > 96) return -1;
-    dim3 grid((H + 7) / 8, M);
+    if ((F & 127) || (SF & 7)) return -1;
     const FuseOut fo = take_fo();
+    if ((moe_mma_mask() & 2) && (H & 15) == 0 && top_k * (F >> 7) <= MM_WARPS * DN_NI && (SF >> 5) <= MM_WARPS * DN_NS && (ld_sd & 7) == 0) {
+        // tensor-core form: 16 output columns per block
+        const size_t smem = ((size_t)top_k * (F >> 3) + (SF >> 3)) * 16 + MM_WARPS * 16 * sizeof(float);
+        if (smem <= 48 * 1024) {
+            const dim3 g2(H / 16, M);
+            cudaError_t e = fo.mode ? launch_pdl(moe_down_mma_kernel<true>, g2, dim3(128), smem, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                                 (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                                 (const bf16 *)sh_h, SF, out, ldo, take_pf(), fo)
+                                    : launch_pdl(moe_down_mma_kernel<false>, g2, dim3(128), smem, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                                 (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                                 (const bf16 *)sh_h, SF, out, ldo, take_pf(), fo);
+            return e == cudaSuccess ? 0 : -2;
+        }
+    }
+    if (top_k * (F >> 5) > 32 * DN_T || (SF >> 3) > 96) return -1;
+    dim3 grid((H + 7) / 8, M);
     cudaError_t e = fo.mode ? launch_pdl(moe_down_combine_kernel<true>, grid, dim3(256), 0, s, (const uint32_t *)w2, (const bf16 *)s2,
                                          (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
                                          (const bf16 *)sh_h, SF, out, ldo, take_pf(), fo)

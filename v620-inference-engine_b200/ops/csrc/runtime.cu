@@ -11,6 +11,9 @@
 #include "kernels.h"
 #include "fuse.cuh"
 
+#include <cstdlib>
+#include <cstring>
+#include <string>
 #include <vector>
 
 namespace qw {
@@ -73,13 +76,38 @@ struct Ctx {
     const std::vector<qw::PfArgs> *plan;
 };
 
+// Timing diagnostic: QW_SKIP=name[,name...] leaves out every launch whose launcher call contains one of the names
+// (e.g. QW_SKIP=qwk_hc_down).  The step's results are then wrong; the step time shows what the kernels cost in place.
+bool skipped(const char *expr) {
+    static std::vector<std::string> names;
+    static bool parsed = false;
+    if (!parsed) {
+        parsed = true;
+        if (const char *e = getenv("QW_SKIP")) {
+            std::string cur;
+            for (const char *p = e;; ++p) {
+                if (*p == ',' || *p == 0) {
+                    if (!cur.empty()) names.push_back(cur);
+                    cur.clear();
+                    if (*p == 0) break;
+                } else {
+                    cur.push_back(*p);
+                }
+            }
+        }
+    }
+    for (const auto &n : names)
+        if (strstr(expr, n.c_str())) return true;
+    return false;
+}
+
 long long g_last_launches = 0;
 int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the L2 prefetch front is kept; 0 = off (measured: no gain on B200)   // kernels enqueued by the most recent qwrt_decode call
 
 // Runs a launcher that enqueues `n` kernels; remembers the first failure and counts the launches.
 #define QW_TRYN(n, expr)                   \
     do {                                   \
-        if (!c.dry) {                      \
+        if (!c.dry && !skipped(#expr)) {   \
             int rc__ = (expr);             \
             c.launches += (n);             \
             if (rc__ != 0 && c.err == 0) c.err = rc__ * 1000 - __LINE__; \
