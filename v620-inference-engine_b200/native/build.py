@@ -8,6 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "src")
 HOST_LIB = os.path.join(HERE, "libqw_host.so")
 ENGINE_LIB = os.path.join(HERE, "libqw_engine.so")
+REF_EXE = os.path.join(HERE, "qw_ref")
 
 
 def _stale(target, deps):
@@ -23,6 +24,13 @@ def build(force: bool = False, verbose: bool = False) -> None:
         if r.returncode:
             raise RuntimeError("host library build failed:\n" + r.stdout)
         print("built", HOST_LIB)
+    ref_src = os.path.join(HERE, "tools", "qw_ref.cpp")
+    if os.path.exists(ref_src) and (force or _stale(REF_EXE, deps + [ref_src])):
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-pthread", "-o", REF_EXE, ref_src], stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT, text=True)
+        if r.returncode:
+            raise RuntimeError("qw_ref build failed:\n" + r.stdout)
+        print("built", REF_EXE)
     capi = os.path.join(SRC, "capi.cpp")
     if os.path.exists(capi) and (force or _stale(ENGINE_LIB, deps)):
         inc = sysconfig.get_paths()["include"]

@@ -78,7 +78,7 @@ public:
         ns.vocab = cfg.vocab; ns.eos = cfg.eos; ns.ngram = cfg.ngram; ns.heads = cfg.ngram_heads; ns.image_pad = cfg.image_pad;
         ns.video_pad = cfg.video_pad; ns.vocab_base = cfg.ngram_vocab_base; ns.seed = cfg.ple_seed;
         hasher_ = std::make_unique<NgramHasher>(ns);
-        if (!ple_dir.empty()) table_ = std::make_unique<PleTable>(ple_dir, cfg.hidden);
+        if (!ple_dir.empty()) table_ = std::make_unique<PleTable>(ple_dir, cfg.hidden / cfg.ngram_heads);      // one row per n-gram head
         reset();
     }
 
@@ -88,8 +88,8 @@ public:
         const RefConfig &c = cfg;
         int n_gdn = 0, n_qsa = 0;
         for (int l = 0; l < c.n_layers; ++l) (c.is_qsa(l) ? n_qsa : n_gdn)++;
-        gdn_conv_.assign(size_t(n_gdn), std::vector<float>(size_t(c.gdn_conv - 1) * c.gdn_qkv(), 0.f));
-        gdn_S_.assign(size_t(n_gdn), std::vector<float>(size_t(c.gdn_v_heads) * c.gdn_dim * c.gdn_dim, 0.f));
+        gdn_conv_.assign(static_cast<size_t>(n_gdn), std::vector<float>(static_cast<size_t>(c.gdn_conv - 1) * c.gdn_qkv(), 0.f));
+        gdn_S_.assign(static_cast<size_t>(n_gdn), std::vector<float>(static_cast<size_t>(c.gdn_v_heads) * c.gdn_dim * c.gdn_dim, 0.f));
         qsa_.assign(size_t(n_qsa), Cache());
         ple_hist_.assign(size_t(c.ple_conv - 1) * c.ple_dilation * c.hch(), 0.f);
         tokens_.clear();
@@ -101,7 +101,7 @@ public:
         const RefConfig &c = cfg;
         const int H = c.hidden, HCH = c.hch();
         const int real = token >= 0 ? token : (((-token) & 1) ? c.image_pad : c.video_pad);
-        std::vector<float> X(size_t(HCH));
+        std::vector<float> X(static_cast<size_t>(HCH));
         {
             const TensorView &e = dense("embed_tokens.weight");
             const uint16_t *row = reinterpret_cast<const uint16_t *>(e.data) + size_t(real) * H;
@@ -141,7 +141,7 @@ private:
         const TensorView &t = dense(name);
         QWH_CHECK(t.dtype == DType::BF16 && t.shape.size() == 2 && size_t(t.shape[1]) == x.size(), name + ": shape");
         const int64_t out = t.shape[0], in = t.shape[1];
-        std::vector<float> y(size_t(out), 0.f);
+        std::vector<float> y(static_cast<size_t>(out), 0.f);
         const uint16_t *w = reinterpret_cast<const uint16_t *>(t.data);
         pool_.parallel_for(out, 64, [&](int64_t a, int64_t b) {
             for (int64_t r = a; r < b; ++r) {
@@ -155,7 +155,7 @@ private:
     }
     std::vector<float> vec(const std::string &name) const {
         const TensorView &t = dense(name);
-        std::vector<float> v(size_t(t.numel()));
+        std::vector<float> v(static_cast<size_t>(t.numel()));
         const uint16_t *p = reinterpret_cast<const uint16_t *>(t.data);
         if (t.dtype == DType::BF16) for (size_t i = 0; i < v.size(); ++i) v[i] = bf16_to_f32(p[i]);
         else if (t.dtype == DType::F32) std::memcpy(v.data(), t.data, v.size() * 4);
@@ -170,7 +170,7 @@ private:
         const uint32_t *w = reinterpret_cast<const uint32_t *>(pk.data);
         const uint16_t *s = reinterpret_cast<const uint16_t *>(sc.data);
         const int64_t gw = words / groups;
-        std::vector<float> y(size_t(out));
+        std::vector<float> y(static_cast<size_t>(out));
         for (int64_t r = 0; r < out; ++r) {
             float acc = 0.f;
             for (int64_t g = 0; g < groups; ++g) {
@@ -239,14 +239,14 @@ private:
         int32_t hist[2];
         const int nh = std::min<int>(2, n_tokens());
         for (int i = 0; i < nh; ++i) hist[i] = tokens_[tokens_.size() - size_t(nh) + size_t(i)];
-        std::vector<int64_t> ids(size_t(c.ngram_heads));
+        std::vector<int64_t> ids(static_cast<size_t>(c.ngram_heads));
         const int32_t tk = token;
         hasher_->ids_for(hist, nh, &tk, 1, ids.data());
-        std::vector<float> e(size_t(H));
+        std::vector<float> e(static_cast<size_t>(H));
         table_->gather(ids.data(), 1, c.ngram_heads, e.data(), &pool_);
         std::vector<float> key = linear(p + "key_proj.weight", e), val = linear(p + "value_proj.weight", e);
         std::vector<float> nk = vec(p + "norm_key.weight"), nq = vec(p + "norm_query.weight"), ncw = vec(p + "norm_conv.weight");
-        std::vector<float> q = X, gv(size_t(HCH)), nc(size_t(HCH));
+        std::vector<float> q = X, gv(static_cast<size_t>(HCH), 0.f), nc(static_cast<size_t>(HCH), 0.f);
         for (int s = 0; s < c.hc; ++s) {
             gemma_norm(key.data() + size_t(s) * H, nk.data() + size_t(s) * H, H);
             gemma_norm(q.data() + size_t(s) * H, nq.data() + size_t(s) * H, H);
@@ -282,7 +282,7 @@ private:
         std::vector<float> b = linear(p + "in_proj_b.weight", x), a = linear(p + "in_proj_a.weight", x);
         std::vector<float> cw = vec(p + "conv1d.weight");       // [qkv][conv]
         std::vector<float> &ring = gdn_conv_[size_t(gi)];       // [conv-1][qkv], oldest first
-        std::vector<float> act(size_t(QKV));
+        std::vector<float> act(static_cast<size_t>(QKV));
         for (int ch = 0; ch < QKV; ++ch) {
             float acc = 0.f;
             for (int k = 0; k < c.gdn_conv; ++k)
@@ -293,7 +293,7 @@ private:
         std::copy(qkv.begin(), qkv.end(), ring.end() - QKV);
         std::vector<float> A = vec(p + "A_log"), dt = vec(p + "dt_bias"), nw = vec(p + "norm.weight");
         const int rep = c.gdn_v_heads / c.gdn_qk_heads;
-        std::vector<float> o(size_t(c.gdn_val()));
+        std::vector<float> o(static_cast<size_t>(c.gdn_val()));
         std::vector<float> &S = gdn_S_[size_t(gi)];             // [vh][k][v]
         for (int h = 0; h < c.gdn_v_heads; ++h) {
             const int kh = h / rep;
@@ -306,7 +306,7 @@ private:
             const float sp = sp_in > 20.f ? sp_in : std::log1p(std::exp(sp_in));
             const float decay = std::exp(-std::exp(A[size_t(h)]) * sp), beta = sigmoid(b[size_t(h)]);
             float *Sh = S.data() + size_t(h) * D * D;
-            std::vector<float> u(size_t(D));
+            std::vector<float> u(static_cast<size_t>(D));
             for (int v = 0; v < D; ++v) {
                 float dot = 0.f;
                 for (int k = 0; k < D; ++k) dot += Sh[size_t(k) * D + v] * decay * (kh_[k] * kn);
@@ -345,7 +345,7 @@ private:
         cache.v.push_back(v);
         cache.raw.emplace_back(iq.begin() + size_t(c.idx_heads) * ID, iq.end());
         if ((pos + 1) % c.idx_ratio == 0) {
-            std::vector<float> mean(size_t(ID), 0.f);
+            std::vector<float> mean(static_cast<size_t>(ID), 0.f);
             for (int t = pos + 1 - c.idx_ratio; t <= pos; ++t)
                 for (int i = 0; i < ID; ++i) mean[size_t(i)] += cache.raw[size_t(t)][size_t(i)];
             for (auto &m : mean) m /= float(c.idx_ratio);
@@ -360,7 +360,7 @@ private:
             sel.resize(size_t(pos + 1));
             std::iota(sel.begin(), sel.end(), 0);
         } else {
-            std::vector<float> score(size_t(nb), 0.f);
+            std::vector<float> score(static_cast<size_t>(nb), 0.f);
             for (int g = 0; g < nb; ++g) {
                 float s = 0.f;
                 for (int h = 0; h < c.idx_heads; ++h) {
@@ -378,7 +378,7 @@ private:
             for (int t = nb * c.idx_ratio; t <= pos; ++t) sel.push_back(t);
         }
         const int rep = c.q_heads / c.kv_heads;
-        std::vector<float> o(size_t(c.q_heads) * D);
+        std::vector<float> o(static_cast<size_t>(c.q_heads) * D);
         for (int h = 0; h < c.q_heads; ++h) {
             const float *q = qg.data() + size_t(h) * 2 * D, *gate = q + D;
             const int kvh = h / rep;
@@ -418,7 +418,7 @@ private:
         std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return pr[size_t(a)] > pr[size_t(b)]; });
         float top = 0.f;
         for (int j = 0; j < c.top_k; ++j) top += pr[size_t(order[size_t(j)])];
-        std::vector<float> out(size_t(c.hidden), 0.f);
+        std::vector<float> out(static_cast<size_t>(c.hidden), 0.f);
         std::vector<std::vector<float>> ys(static_cast<size_t>(c.top_k));
         pool_.parallel_for(c.top_k, 1, [&](int64_t a, int64_t b) {
             for (int64_t j = a; j < b; ++j) {

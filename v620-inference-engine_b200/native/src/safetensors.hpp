@@ -1,6 +1,8 @@
 // Memory-mapped safetensors reader: multi-file index by tensor name with dtype/shape checks,
 // plus mlock / touch / prefetch of the mapping (role of the reference's src/core/safetensors.cpp).
 #pragma once
+#include <dirent.h>
+#include <algorithm>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -88,6 +90,21 @@ public:
         files_.push_back(f);
     }
     bool has(const std::string &n) const { return tensors_.count(n) != 0; }
+    // every *.safetensors file of a directory, in name order
+    void add_dir(const std::string &dir) {
+        std::vector<std::string> files;
+        if (DIR *d = opendir(dir.c_str())) {
+            while (dirent *e = readdir(d)) {
+                const std::string n = e->d_name;
+                if (n.size() > 12 && n.compare(n.size() - 12, 12, ".safetensors") == 0) files.push_back(dir + "/" + n);
+            }
+            closedir(d);
+        }
+        QWH_CHECK(!files.empty(), dir + ": no .safetensors files");
+        std::sort(files.begin(), files.end());
+        for (auto &f : files) add_file(f);
+    }
+
     const TensorView &get(const std::string &n) const {
         auto it = tensors_.find(n);
         if (it == tensors_.end()) fail("tensor not found: " + n);
