@@ -1,0 +1,123 @@
+"""Failure detection without a GPU: the collectives' protocol on CPU ranks (late rank, skipped push, dead rank) and
+the host heartbeat across processes over a TCP store."""
+import multiprocessing as mp
+import time
+
+import numpy as np
+import pytest
+
+
+def test_protocol_sums_are_bit_identical_and_late_rank_is_fine():
+    from qwb200.parallel.cpu_protocol import CpuWorld, run_ranks
+    R, n = 4, 37
+    w = CpuWorld(R, 64)
+    rng = np.random.default_rng(0)
+    vals = rng.standard_normal((3, R, n)).astype(np.float32)
+
+    def body(rk):
+        outs = []
+        for step in range(3):
+            rk.bump()
+            if rk.rank == 2 and step == 1:
+                time.sleep(0.15)                  # a late rank inside the limit
+            rk.put_all(1, vals[step, rk.rank])
+            a = rk.reduce(1, n)
+            rk.put_cols(2, np.tile(vals[step, rk.rank, :8], R))
+            b = rk.reduce(2, 8)
+            outs.append((a, b))
+        return outs
+    res = run_ranks(w, body, spin_seconds=2.0)
+    assert all(e.code == 0 for e in w.err)
+    for step in range(3):
+        want = np.zeros(n, np.float32)
+        for r in range(R):
+            want += vals[step, r]                 # rank order: what every rank must have computed
+        for r in range(R):
+            assert np.array_equal(res[r][step][0], want)
+            assert np.array_equal(res[r][step][1], res[0][step][1])
+
+
+def test_skipped_push_times_out_with_the_culprit_and_stops_all_waits():
+    from qwb200.parallel.cpu_protocol import ERR_WAIT_TIMEOUT, CpuWorld, run_ranks
+    R = 3
+    w = CpuWorld(R, 16)
+
+    def body(rk):
+        rk.bump()
+        if rk.rank != 1:                          # rank 1 "forgets" collective 5
+            rk.put_all(5, np.ones(4, np.float32))
+        a = rk.reduce(5, 4)
+        t0 = time.monotonic()
+        b = rk.reduce(6, 4)                       # nobody pushed 6: must return at once because the error word is set
+        return a, b, time.monotonic() - t0
+    t0 = time.monotonic()
+    res = run_ranks(w, body, spin_seconds=0.3)
+    assert time.monotonic() - t0 < 3.0
+    for r in range(R):
+        a, b, dt = res[r]
+        assert a is None and b is None and dt < 0.1
+        assert w.err[r].code == ERR_WAIT_TIMEOUT
+        assert (w.err[r].detail >> 24) & 0x3F == 1 and w.err[r].detail & 0xFFFFFF == 5      # waiting for rank 1, collective 5
+
+
+def test_dead_rank_is_noticed_by_its_peers():
+    from qwb200.parallel.cpu_protocol import CpuWorld, run_ranks
+    w = CpuWorld(2, 8)
+
+    def body(rk):
+        rk.bump()
+        if rk.rank == 0:
+            raise RuntimeError("rank 0 died before its push")
+        rk.put_all(1, np.ones(2, np.float32))
+        return rk.reduce(1, 2)
+    res = run_ranks(w, body, spin_seconds=0.2)
+    assert isinstance(res[0], RuntimeError) and res[1] is None and w.err[1].code != 0 and (w.err[1].detail >> 24) & 0x3F == 0
+
+
+def _hb_worker(rank, world, port, q):
+    from torch.distributed import TCPStore
+    from qwb200.parallel.heartbeat import Heartbeat
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=20))
+    hb = Heartbeat(store, rank, world, interval=0.05, limit=0.6)
+    hb.start()
+    store.set(f"ready/{rank}", "1")
+    for r in range(world):
+        store.wait([f"ready/{r}"])
+    steps = 0
+    try:
+        for step in range(200):
+            hb.check()                            # before every launch
+            steps += 1
+            if rank == 2 and step == 3:
+                hb.leave("shutting down")         # between steps, nothing in flight
+                q.put((rank, steps, "left"))
+                time.sleep(1.0)                   # keep the store's clients alive while the others notice
+                return
+            if rank == 1 and step == 3:
+                hb.stop_flag.set()                # rank 1 stops beating without saying anything
+                time.sleep(3.0)
+                q.put((rank, steps, "silent"))
+                return
+            time.sleep(0.05)
+        q.put((rank, steps, "never noticed"))
+    except RuntimeError as ex:
+        q.put((rank, steps, str(ex)))
+        time.sleep(3.5 if rank == 0 else 0.0)     # the store's server outlives its clients
+
+
+def test_heartbeat_across_processes():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650
+    ps = [ctx.Process(target=_hb_worker, args=(r, 3, port, q)) for r in range(3)]
+    for p in ps:
+        p.start()
+    got = {}
+    for _ in range(3):
+        r, steps, msg = q.get(timeout=60)
+        got[r] = (steps, msg)
+    for p in ps:
+        p.join(timeout=30)
+    assert got[2] == (4, "left")
+    assert "peer failure" in got[0][1] and ("rank 2: shutting down" in got[0][1] or "rank 1: silent" in got[0][1])
+    assert 1 <= got[0][0] < 60                     # noticed within a few steps, long before the loop's end

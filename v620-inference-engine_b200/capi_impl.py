@@ -213,6 +213,24 @@ def open(options_json: str) -> CApi:
     from .models.config import ModelConfig
     from .session.session import Session
     o = json.loads(options_json or "{}")
+    from .utils import settings as _settings
+    st = _settings.Settings.from_env(prefill_chunk=o.get("prefill_chunk"), prefill_piece=o.get("prefill_piece"),
+                                     host_cache_gb=o.get("host_cache_gb"), disk_cache_dir=o.get("disk_cache_dir"),
+                                     disk_cache_gb=o.get("disk_cache_gb"), vision_cache_gb=o.get("vision_cache_gb"),
+                                     weight_cache_dir=o.get("weight_cache_dir"), ple_dir=o.get("ple_dir"))
+    _settings.set_current(st)
+    import sys
+    print(st.describe(), file=sys.stderr, flush=True)
+    if st.no_mtp:
+        o["mtp"] = False
+    if st.no_vision:
+        o["vision"] = False
+    o.setdefault("prefill_chunk", st.prefill_chunk)
+    o.setdefault("prefill_piece", st.prefill_piece)
+    if "host_cache_gb" not in o and "QW_HOST_CACHE_GB" in os.environ:
+        o["host_cache_gb"] = st.host_cache_gb
+    if st.disk_cache_dir and not o.get("disk_cache_dir"):
+        o["disk_cache_dir"], o["disk_cache_gb"] = st.disk_cache_dir, st.disk_cache_gb
     slots = o.get("slots", [8192])
     if isinstance(slots, int):
         slots = [8192] * slots
@@ -221,7 +239,7 @@ def open(options_json: str) -> CApi:
     dev = f"cuda:{devices[0]}"
     opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
                          save_gdn=bool(o.get("mtp", True)), host_pages=int(o.get("host_pages", 0)),
-                         dev_pages=o.get("dev_pages"))
+                         dev_pages=o.get("dev_pages"), use_graphs=not st.nograph)
     if "model_dir" in o and o["model_dir"]:
         from .models.config import check_hf_config
         from .models.ple import PleTable

@@ -58,6 +58,11 @@ class Engine:
         self.merge_argmax = None        # set by the NCCL backend: merges the ranks' (max, argmax) after a step
         self.prefiller = None           # token-major prefill, built on first use (one GPU)
         self.vision_lookup = None       # vision token ids -> embeddings [n, hidden] (set by the vision front end)
+        from ..utils import settings as _settings
+        from ..utils.trace import ChunkProfile, StepTrace
+        st = _settings.get()
+        self.step_trace = StepTrace(st.trace)          # QW_TRACE: host preparation / launch / wait per row count
+        self.chunk_profile = ChunkProfile(st.profile)  # QW_PROFILE: device time per prefill chunk
         self.steps = 0
 
     # ---- construction
@@ -255,7 +260,9 @@ class Engine:
             vis = [j for j, t in enumerate(chunk) if t < 0]
             if vis:         # rows that carry vision tokens take the tower's output as their embedding
                 embeds = (torch.tensor(vis, dtype=torch.long, device=self.dm.dev), self.vision_lookup([chunk[j] for j in vis]))
+            ev = self.chunk_profile.begin()
             out = self.prefiller.run(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last, embeds=embeds)
+            self.chunk_profile.end(ev, len(chunk))
             if self.mtp:
                 # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
                 sl = self.slot[slot]
@@ -272,6 +279,7 @@ class Engine:
                 sl.mtp_hidden = keep
             self.slot[slot].tokens.extend(chunk)
         self.steps += 1
+        self.chunk_profile.summary(f"prefill slot {slot}")
         self.last_prefill_row = 0           # logits / argmax of the last token sit in row 0
         return out
 
@@ -280,6 +288,7 @@ class Engine:
         """One batched step: row i appends tokens[i] to slots[i] (rows of a slot consecutive).
         Returns the greedy next token of every row (host ints)."""
         M = len(tokens)
+        self.step_trace.begin()
         pos, c3 = [], []
         seen: Dict[int, int] = {}
         for s, t in zip(slots, tokens):
@@ -300,7 +309,9 @@ class Engine:
         track = self.mtp and self.opts.mtp_track
         if track:
             flags |= DM.FLAG_KEEP_HIDDEN
+        self.step_trace.launched()
         self.dm.step(list(tokens), list(slots), pos, rows3, flags=flags, graph=self.opts.use_graphs)
+        self.step_trace.enqueued()
         if track:
             # plain steps leave the MTP layer one row behind per token: remember the newest hidden per slot; the rows in
             # between are caught up by _mtp_rows the next time drafts are wanted (here: simply dropped for rows > 1 back)
@@ -314,6 +325,7 @@ class Engine:
         self.out_host[:M].copy_(self.dm.buf["amax_idx"][:M], non_blocking=True)
         if sync:
             torch.cuda.current_stream(self.dm.dev).synchronize()
+            self.step_trace.end(M)
             return self.out_host[:M].tolist()
         return []
 

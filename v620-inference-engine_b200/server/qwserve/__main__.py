@@ -53,13 +53,23 @@ def main(argv=None):
     if not a.no_vision and eng.has_vision:
         from .vision import Preprocessor
         pre = Preprocessor(a.model_dir)
-    sched = Scheduler(eng, drafts=a.mtp, prefill_piece=min(2048, a.prefill_chunk), log=logging.info)
+    # server-side switches that deployments set through the environment (QW_STUCK_SECONDS, QW_EXIT_GRACE, QW_DECODE_SHARE, ...)
+    import os
+
+    def envf(name, default):
+        try:
+            return float(os.environ.get(name, default))
+        except ValueError:
+            raise SystemExit(f"{name} must be a number")
+    sched = Scheduler(eng, drafts=a.mtp, prefill_piece=min(int(envf("QW_PREFILL_PIECE", 2048)), a.prefill_chunk),
+                      decode_share=envf("QW_DECODE_SHARE", 0.25), stuck_seconds=envf("QW_STUCK_SECONDS", 300),
+                      exit_grace=envf("QW_EXIT_GRACE", 30), log_interval=envf("QW_LOG_INTERVAL", 30), log=logging.info)
     srv = Server(eng, prompter, sched, a.served_model_name, preprocessor=pre, default_effort=a.reasoning_effort,
                  default_budget=a.thinking_budget)
     im_end = prompter.token_id("<|im_end|>")
     if im_end is not None:
         eng.set_boundary_token(im_end)
-    sched.start()
+    sched.start(watchdog=os.environ.get("QW_WATCHDOG_EXIT", "1") != "0")
     web.run_app(make_app(srv, dashboard=not a.no_dashboard), host=a.host, port=a.port, access_log=None)
     eng.close()
     return 0

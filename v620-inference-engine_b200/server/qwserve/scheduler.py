@@ -67,10 +67,11 @@ class Request:
 
 class Scheduler:
     def __init__(self, engine, drafts: int = 0, prefill_piece: int = 2048, decode_share: float = 0.25, max_step: int = 16,
-                 stuck_seconds: float = 300.0, exit_grace: float = 30.0, log=print):
+                 stuck_seconds: float = 300.0, exit_grace: float = 30.0, log_interval: float = 30.0, log=print):
         self.e, self.k = engine, drafts if getattr(engine, "has_mtp", False) else 0
         self.piece, self.decode_share, self.max_step = prefill_piece, decode_share, max_step
         self.stuck_seconds, self.exit_grace, self.log = stuck_seconds, exit_grace, log
+        self.log_interval, self._logged_at, self._logged_tokens = log_interval, time.time(), 0
         self.inbox: "queue.Queue[Request]" = queue.Queue()
         self.waiting: Deque[Request] = collections.deque()
         self.prefilling: List[Request] = []
@@ -155,6 +156,7 @@ class Scheduler:
                     self._cache_stats = self.e.cache_stats()
                 except Exception:
                     pass
+                self._stats_line()
             busy = self._drain_inbox()
             busy |= self._admit()
             t0 = time.time()
@@ -173,6 +175,21 @@ class Scheduler:
                     self.waiting.append(self.inbox.get(timeout=0.05))
                 except queue.Empty:
                     pass
+
+    def _stats_line(self):
+        """Every ``log_interval`` seconds while there is work: queue depth, throughput, prefix-cache reuse."""
+        now = time.time()
+        if self.log_interval <= 0 or now - self._logged_at < self.log_interval:
+            return
+        c = self.counts()
+        tok = c["tokens"] + sum(r.emitted for r in self.running)
+        if tok != self._logged_tokens or c["waiting"] or c["prefilling"] or c["running"]:
+            cs = self._cache_stats or {}
+            reuse = 100.0 * cs.get("reused_tokens", 0) / max(1, cs.get("prompt_tokens", 0))
+            self.log(f"stats: {c['running']} running, {c['prefilling']} prefilling, {c['waiting']} waiting; "
+                     f"{(tok - self._logged_tokens) / (now - self._logged_at):.1f} tok/s; {c['completed']} done, {c['failed']} failed; "
+                     f"step {c['step_ms']:.1f} ms; prompt tokens from cache {reuse:.0f}%")
+        self._logged_at, self._logged_tokens = now, tok
 
     def _drain_inbox(self) -> bool:
         got = False

@@ -79,6 +79,9 @@ class Session:
                  disk_cache_bytes: int = 0, prefill_piece: int = 2048, seed: int = 0):
         self.e = engine
         self.cfg = engine.cfg
+        from ..utils import settings as _settings
+        from ..utils.trace import PhaseTrace
+        self.gen_trace = PhaseTrace(_settings.get().trace, "generate")     # QW_TRACE: per-phase milliseconds of generate()
         self.io = StateIO(engine.dm)
         n = engine.opts.slots
         self.slots = [SlotInfo() for _ in range(n)]
@@ -271,6 +274,8 @@ class Session:
         outs: List[StepOut] = []
         all_rows = []
         row0 = 0
+        tr = self.gen_trace
+        tr.start()
         for r in reqs:
             si, sl = self.slots[r.slot], self.e.slot[r.slot]
             kk = min(k, r.budget - 1) if self.e.mtp else 0
@@ -278,23 +283,29 @@ class Session:
             if kk > 0 and sl.mtp_hidden is None:
                 kk = 0
             drafts = self.e.draft(r.slot, r.pending, kk) if kk > 0 else []
+            tr.mark("draft")
             rows = [r.pending] + drafts
             logits = self.e.verify(r.slot, rows) if (drafts or self.e.mtp) else None
             if logits is None:
                 self.e.decode([r.slot], [r.pending], sync=False)
                 logits = self.e.dm.buf["logits"][:1]
             logits = logits.clone()
+            tr.mark("verify")
             n = len(rows)
             base = sl.n
             hist = sl.tokens + rows
             toks, lps = self.sampler.sample(logits, [r.sampling] * n, [r.slot] * n, [base + i + 1 for i in range(n)],
                                             hists=[(hist[:base + i + 1], si.prompt_end) for i in range(n)])
+            tr.mark("sample")
             n_acc = 1
             while n_acc <= len(drafts) and toks[n_acc - 1] == drafts[n_acc - 1] and toks[n_acc - 1] not in si.stop:
                 n_acc += 1
             if drafts or self.e.mtp:
                 self.e.accept(r.slot, rows, n_acc)
             self.sampler.note_tokens(r.slot, rows[:n_acc], generated=True)
+            tr.mark("accept")
+            tr.count("drafts", len(drafts))
+            tr.count("accepted", n_acc - 1)
             if drafts:
                 si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(drafts))
             emitted = toks[:n_acc][:r.budget]
@@ -304,6 +315,7 @@ class Session:
             row0 += n_acc
         self.last_rows = torch.cat(all_rows) if all_rows else None
         self.last_row_slots = [r.slot for r, o in zip(reqs, outs) for _ in o.tokens]
+        tr.finish()
         return outs
 
     # ---- stats / persistence
