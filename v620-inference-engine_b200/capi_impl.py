@@ -246,9 +246,10 @@ def open(options_json: str) -> CApi:
         from .models.weights import load_checkpoint
         cfg = ModelConfig.full()
         check_hf_config(cfg, o["model_dir"])
-        w = load_checkpoint(cfg, o["model_dir"])
         table = PleTable.load(cfg, o["ple_dir"], pin=True) if o.get("ple_dir") else None
-        eng = Engine.from_weights(cfg, w, table, opts, device=dev)
+        eng = Engine.from_checkpoint(cfg, o["model_dir"], table, opts, device=dev,
+                                     weight_cache_dir=o.get("weight_cache_dir") or st.weight_cache_dir or None,
+                                     log=lambda m: print(m, file=sys.stderr, flush=True))
     else:
         kind = o.get("synthetic", "tiny")
         cfg = {"full": ModelConfig.full, "slice2": ModelConfig.slice2, "tiny": ModelConfig.tiny}[kind]()

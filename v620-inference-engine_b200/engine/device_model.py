@@ -64,6 +64,15 @@ class DeviceModel:
         qlib.check(self.lib.qwk_rope_init(C.c_double(cfg.rope_theta), cfg.rope_dim), "rope_init")
         # error word for kernels with bounded waits: (code, detail), 0 = ok
         self.err_word = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        from ..utils import settings as _settings
+        self.guard_on = bool(_settings.get().guard)
+        self.guards: Dict[str, torch.Tensor] = {}
+        self._guard_raw = []
+        self.steps_run = 0
+        self.moe_stats = None
+        if _settings.get().moe_stats:           # QW_MOE_STATS: per-layer count of expert pairs computed on this rank
+            self.moe_stats = torch.zeros(cfg.n_layers + 1, dtype=torch.int32, device=self.dev)
+            self.lib.qwrt_set_moe_stats(C.c_void_p(self.moe_stats.data_ptr()))
         self.lib.qwk_set_error_word(C.c_void_p(self.err_word.data_ptr()))
         self._init_ngram()
         self.comm_cb = None
@@ -175,7 +184,7 @@ class DeviceModel:
         for name in S.BUFFER_FIELDS:
             if name in shapes:
                 shp, dt = shapes[name]
-                self.buf[name] = torch.zeros(shp, dtype=dt, device=dv)
+                self.buf[name] = self._zeros(name, shp, dt)
                 setattr(self.model.b, name, self.buf[name].data_ptr())
             else:
                 setattr(self.model.b, name, None)
@@ -214,9 +223,20 @@ class DeviceModel:
         s.w1, s.Wd, s.Wu, s.n_inj = hc["w1"].data_ptr(), hc["Wd"].data_ptr(), hc["Wu"].data_ptr(), int(hc["n_inj"])
         return s
 
-    def set_layer(self, L: int, w: Weights):
-        """Install decoder layer ``L`` from checkpoint-named tensors (any device)."""
-        lw = WP.prep_layer(self.cfg, w, L, self.sc, self.dev)
+    def _cached(self, name: str, make):
+        """The converted tensors of one loading step: from the weight cache when it is replaying, else made now (and
+        recorded when a cache is attached).  ``self.weight_cache`` is set by ``Engine.from_checkpoint``."""
+        wc = getattr(self, "weight_cache", None)
+        if wc is not None and wc.replaying:
+            return wc.get(name, self.dev)
+        obj = make()
+        if wc is not None:
+            wc.put(name, obj)
+        return obj
+
+    def set_layer(self, L: int, w: Optional[Weights]):
+        """Install decoder layer ``L`` from checkpoint-named tensors (any device; None when the weight cache replays)."""
+        lw = self._cached(f"layer{L}", lambda: WP.prep_layer(self.cfg, w, L, self.sc, self.dev))
         self.layers_w.append(lw)
         st = self._layers_arr[L]
         st.is_qsa = 1 if lw["is_qsa"] else 0
@@ -226,8 +246,11 @@ class DeviceModel:
             setattr(st, k, lw[k].data_ptr())
         for k in ("cw", "A_log", "dt_bias", "gdn_norm", "qn1", "kn1", "iqn1", "ikn1"):
             setattr(st, k, lw[k].data_ptr() if k in lw else None)
-        if L == self.cfg.ple_layer and f"layers.{L}.ple.key_proj.weight" in w:
-            pw = WP.prep_ple(self.cfg, w, self.sc, self.dev)
+        if L == self.cfg.ple_layer:
+            has = w is not None and f"layers.{L}.ple.key_proj.weight" in w
+            pw = self._cached("ple", lambda: WP.prep_ple(self.cfg, w, self.sc, self.dev) if has else {})
+            if not pw:
+                return
             self.ple_w = pw
             p = self.model.ple
             for k in ("Wkv", "nk1", "nq1", "nc1", "cw"):
@@ -247,16 +270,18 @@ class DeviceModel:
         c, sc, dv = self.cfg, self.sc, self.dev
         if sc.ranks != 1:
             raise NotImplementedError("the MTP head runs on one GPU")
-        lw = WP.prep_layer(c, w, c.n_layers, sc, dv, prefix="mtp.layers.0.", qsa=True)
-        fin = WP.prep_hc(w, "mtp.hyper_connection_mixer.", sc, False, dv)
-        R = self.max_rows
-        m = self.model.mtp
-        self.mtp_w = {
-            "layer": lw, "final_hc": fin,
+        conv = self._cached("mtp", lambda: {
+            "layer": WP.prep_layer(c, w, c.n_layers, sc, dv, prefix="mtp.layers.0.", qsa=True),
+            "final_hc": WP.prep_hc(w, "mtp.hyper_connection_mixer.", sc, False, dv),
             "fc_h": w["mtp.fc_hidden.weight"].to(dv).to(torch.bfloat16).contiguous(),
             "fc_e": w["mtp.fc_embedding.weight"].to(dv).to(torch.bfloat16).contiguous(),
             "nh1": (1.0 + w["mtp.pre_fc_norm_hidden.weight"].to(dv).float()).contiguous(),
-            "ne1": (1.0 + w["mtp.pre_fc_norm_embedding.weight"].to(dv).float()).contiguous(),
+            "ne1": (1.0 + w["mtp.pre_fc_norm_embedding.weight"].to(dv).float()).contiguous()})
+        lw, fin = conv["layer"], conv["final_hc"]
+        R = self.max_rows
+        m = self.model.mtp
+        self.mtp_w = {
+            **conv,
             "hn": torch.zeros((R * c.hc, c.hidden), dtype=torch.bfloat16, device=dv),
             "en": torch.zeros((R, c.hidden), dtype=torch.bfloat16, device=dv),
             "fh": torch.zeros((R * c.hc, c.hidden), dtype=torch.float32, device=dv),
@@ -294,7 +319,7 @@ class DeviceModel:
         g.replay()
 
     def set_globals(self, w: Weights):
-        g = WP.prep_globals(self.cfg, w, self.sc, self.dev)
+        g = self._cached("globals", lambda: WP.prep_globals(self.cfg, w, self.sc, self.dev))
         self.globals_w = g
         self.model.embed = g["embed"].data_ptr()
         self.model.lm_head = g["lm_head"].data_ptr()
@@ -399,6 +424,9 @@ class DeviceModel:
     def step(self, tokens, slots, pos, ctx3=None, flags: int = 0, graph: bool = False, n_layers: int = -1):
         """Run one batched step.  Returns nothing; results are in ``self.buf``."""
         self.stage_rows(tokens, slots, pos, ctx3)
+        if self.guard_on and self.steps_run:
+            self.check_guards()              # of the previous step (synchronises: a debugging mode)
+        self.steps_run += 1
         if not graph:
             self.launch(flags, n_layers)
             return
@@ -416,6 +444,49 @@ class DeviceModel:
             # the warm-up executed the step once for real; the capture only records it
             return
         g.replay()
+
+    # ---- guard zones (QW_GUARD): 64 KB of 0xA5 behind every step buffer, looked at after a step
+    GUARD_BYTES = 64 * 1024
+
+    def _zeros(self, name: str, shape, dtype) -> torch.Tensor:
+        """A zeroed step buffer; with guard zones on, followed by a guard region that no kernel may touch
+        (reference: src/engine/device_mem.hpp:26-58)."""
+        if not self.guard_on:
+            return torch.zeros(shape, dtype=dtype, device=self.dev)
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        pad = (-nbytes) % 256
+        raw = torch.zeros(nbytes + pad + self.GUARD_BYTES, dtype=torch.uint8, device=self.dev)
+        raw[nbytes:].fill_(0xA5)
+        self.guards[name] = raw[nbytes:]
+        self._guard_raw.append(raw)
+        return raw[:nbytes].view(dtype).view(shape)
+
+    def moe_balance(self, group=None, reset: bool = True):
+        """Per layer: (pairs on the busiest rank, mean over ranks) since the last call - the imbalance expert parallelism
+        pays at every layer (reference: src/engine/moe_balance.cpp:14-59).  None when the statistics are off."""
+        if self.moe_stats is None:
+            return None
+        mine = self.moe_stats.clone()
+        if reset:
+            self.moe_stats.zero_()
+        if self.sc.ranks > 1:
+            import torch.distributed as dist
+            allr = [torch.empty_like(mine) for _ in range(self.sc.ranks)]
+            dist.all_gather(allr, mine, group=group)
+            st = torch.stack(allr).float()
+        else:
+            st = mine.float()[None]
+        return [(int(st[:, l].max()), float(st[:, l].mean())) for l in range(st.shape[1])]
+
+    def check_guards(self) -> None:
+        """Raise with the buffer's name if anything wrote behind a step buffer."""
+        for name, g in self.guards.items():
+            if not bool((g == 0xA5).all()):
+                first = int((g != 0xA5).nonzero()[0])
+                raise RuntimeError(f"guard zone behind buffer '{name}' was overwritten (first byte at +{first})")
 
     def check_error(self):
         """Raise if a kernel gave up on a bounded wait or failed a bounds check."""

@@ -101,6 +101,39 @@ class Engine:
             e.dm.set_mtp(w)
         return e
 
+    @staticmethod
+    def from_checkpoint(cfg: ModelConfig, model_dir: str, table: Optional[PleTable], opts: EngineOptions = EngineOptions(),
+                        ranks: int = 1, rank: int = 0, device: str = "cuda:0", weight_cache_dir: Optional[str] = None,
+                        log=None) -> "Engine":
+        """Load a checkpoint directory.  With ``weight_cache_dir`` the converted per-rank tensors are written to
+        ``rank<r>.qww`` the first time and read back on later starts without touching the checkpoint
+        (reference: src/engine/weights.hip:33-176)."""
+        from ..models.weights import load_checkpoint
+        from .weight_cache import WeightCache, cache_key
+        e = Engine(cfg, opts, ranks, rank, device)
+        wc = None
+        if weight_cache_dir:
+            shapes = repr(sorted((k, v) for k, v in cfg.__dict__.items() if isinstance(v, (int, float, bool, tuple))))
+            wc = WeightCache(weight_cache_dir, rank, cache_key(model_dir, rank, ranks, shapes))
+            e.dm.weight_cache = wc
+            if log:
+                log(f"weight cache {wc.path}: {'replaying' if wc.replaying else 'recording'}")
+        w = None if (wc is not None and wc.replaying) else load_checkpoint(cfg, model_dir)
+        e.dm.set_globals(w)
+        for L in range(cfg.n_layers):
+            e.dm.set_layer(L, w)
+        has_mtp = cfg.mtp and ranks == 1
+        if has_mtp:
+            present = e.dm._cached("mtp_present", lambda: {"present": bool(w is not None and "mtp.fc_hidden.weight" in w)})
+            if present["present"]:
+                e.dm.set_mtp(w)
+        if wc is not None:
+            wc.close()
+            e.dm.weight_cache = None
+        if table is not None:
+            e.dm.set_ple_table(table)
+        return e
+
     # ---- slots
     def reset(self, slot: int):
         self.slot[slot] = Slot()

@@ -39,6 +39,7 @@ __device__ __forceinline__ void report(ErrorWord *e, unsigned int code, unsigned
 // Device address of the error word every launcher hands to its kernel (set once by the host through
 // qwk_set_error_word; null until then, in which case kernels only give up silently).
 extern ErrorWord *g_err_ptr;
+extern int *g_moe_stats;     // host side: where the next routing launch adds its count of local pairs (null = nowhere)
 
 // Row tables of a batched step.  Row i appends one token to slot[i] at position pos[i]; rows of
 // one slot are consecutive and run_start[i] is the first row of that slot's run.

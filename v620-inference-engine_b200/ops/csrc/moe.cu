@@ -17,7 +17,7 @@ namespace qw {
 // Routing of row m from rs[m] = [ router logits (E) | shared gate logit | shared gate rows (F) | shared up rows (F) ].
 // One warp per row.
 __device__ __forceinline__ void route_row(const float *l, int E, int top_k, int e_first, int e_local, int *pair_expert,
-                                          float *pair_w, int lane) {
+                                          float *pair_w, int lane, int *stats) {
     float v[32];     // E <= 1024
     float mx = -INFINITY;
 #pragma unroll
@@ -56,6 +56,7 @@ __device__ __forceinline__ void route_row(const float *l, int E, int top_k, int 
         const int loc = mine_e - e_first;
         const bool local = loc >= 0 && loc < e_local;
         pair_expert[lane] = local ? loc : -1;
+        if (stats && local) atomicAdd(stats, 1);          // balance counter: pairs this rank computes in this layer
         pair_w[lane] = mine_w / topsum;
     }
 }
@@ -70,13 +71,14 @@ struct RouteArgs {
     const char *w13, *w2;
     unsigned long long w13_bytes, w2_bytes;     // per expert
     int prefetch_rows;                           // rows (from 0) whose experts are prefetched
+    int *stats;                                  // optional counter of local pairs (MoE balance statistics)
 };
 
 __device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, const RouteArgs &r) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int m = warp; m < M; m += nw)
         route_row(rs + (long long)m * ld_rs, r.E, r.top_k, r.e_first, r.e_local, r.pair_expert + m * r.top_k,
-                  r.pair_w + m * r.top_k, lane);
+                  r.pair_w + m * r.top_k, lane, r.stats);
     if (r.sh_h) {
         for (int i = threadIdx.x; i < M * r.F; i += blockDim.x) {
             const int m = i / r.F, f = i % r.F;
@@ -302,6 +304,8 @@ static RouteArgs make_route(int E, int top_k, int F, int e_first, int e_local, i
     r.E = E; r.top_k = top_k; r.F = F; r.e_first = e_first; r.e_local = e_local;
     r.pair_expert = pair_expert; r.pair_w = pair_w; r.sh_h = (bf16 *)sh_h; r.ticket = ticket;
     r.w13 = r.w2 = nullptr; r.w13_bytes = r.w2_bytes = 0; r.prefetch_rows = 0;
+    r.stats = qw::g_moe_stats;
+    qw::g_moe_stats = nullptr;
     return r;
 }
 

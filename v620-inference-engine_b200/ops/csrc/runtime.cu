@@ -19,6 +19,7 @@
 namespace qw {
 ErrorWord *g_err_ptr = nullptr;
 PfArgs g_pf = {};
+int *g_moe_stats = nullptr;
 FuseOut g_fo = {};
 FuseIn g_fi = {};
 }
@@ -26,6 +27,13 @@ FuseIn g_fi = {};
 // 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels;
 // 2: timing diagnostic - nothing is sent or waited for, so a step costs what its kernels alone cost (results are wrong)
 static int g_fuse = 1;
+// MoE balance statistics (QW_MOE_STATS): a device array of one counter per layer (+ one for the MTP layer); every
+// routing launch adds the number of expert pairs that fall on this rank.  Null = off.
+static int *g_moe_stats_base = nullptr;
+extern "C" __attribute__((visibility("default"))) int qwrt_set_moe_stats(int *base) {
+    g_moe_stats_base = base;
+    return 0;
+}
 static int g_fuse_kinds = 7;    // timing diagnostic: bit k clear = collectives of kind k (0 all-reduce, 1 all-gather, 2 reduce-scatter) are skipped
 extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse_kinds(int mask) {
     g_fuse_kinds = mask & 7;
@@ -264,13 +272,14 @@ void qsa_block(Ctx &c, const QwLayer &L) {
     QW_OP(1, L.Wout, (size_t)d.H * K * 2, qwk_gemv_bf16(L.Wout, b.o, b.partial, nullptr, d.H, K, M, K, K, d.H, 0, 1, 0, 0, 0, c.s));
 }
 
-void moe_block(Ctx &c, const QwLayer &L, bool fuse_out = true) {
+void moe_block(Ctx &c, const QwLayer &L, bool fuse_out = true, int stats_index = -1) {
     const QwModel &md = *c.md;
     const QwDims &d = md.d;
     const QwBuffers &b = md.b;
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
     await_bin(c);
+    if (!c.dry && g_moe_stats_base && stats_index >= 0) qw::g_moe_stats = g_moe_stats_base + stats_index;
     QW_OP(1, L.Wrs, (size_t)nrs * d.H * 2, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
                               b.pair_w, b.sh_h, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
     QW_OP(1, nullptr, 0, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
@@ -356,7 +365,7 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
         mix(c, L.mlp_hc, out_attn, inj_attn, inj_mlp);
         // the layer before the n-gram embedding layer hands its output to hc_pre, which reads a plain buffer
         const bool fuse_out = !(l + 1 == d.ple_layer && c.md->ple.enabled);
-        moe_block(c, L, fuse_out);
+        moe_block(c, L, fuse_out, l);
         // The MoE output stays pending: the next mixer's hc_pre (or the final one) folds it into X
         // before anything overwrites `partial`, so with one rank it can be used in place.
         pend = scatter(c, b.out_b, fuse_out);
@@ -406,7 +415,7 @@ static void walk_mtp(Ctx &c, int flags) {
     qsa_block(c, t.layer);
     const float *out_attn = scatter(c, b.out_a);
     mix(c, t.layer.mlp_hc, out_attn, inj_attn, inj_mlp);
-    moe_block(c, t.layer);
+    moe_block(c, t.layer, true, d.n_layers);
     const float *pend = scatter(c, b.out_b);
     mix(c, t.final_hc, pend, inj_mlp, nullptr);
     if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
