@@ -141,3 +141,38 @@ def test_chunker_tiles_and_is_position_independent():
     # content-defined: the same text after a different prefix soon falls back into the same chunks
     ch2 = H.chunk_prompt(rng.integers(0, 50000, size=333).tolist() + toks, 99999)
     assert len({c[2] for c in ch} & {c[2] for c in ch2}) >= len(ch) - 3
+
+
+def test_pinned_pool_units_reserve_retire_and_wait_accounting():
+    import threading
+    import time
+    from qwb200.native import host as H
+    unit = 1 << 20
+    pool = H.PinnedPool(unit, arena_bytes=4 << 20, standing_units=2, policy="preferred", node=0)
+    assert pool.unit_bytes == unit and H.numa_nodes() >= 1
+    held = [pool.get() for _ in range(6)]                  # more than one arena of 4 units
+    for i, a in enumerate(held):
+        a[:] = i                                           # units are distinct, writable memory
+    assert [int(a[0]) for a in held] == list(range(6)) and [int(a[-1]) for a in held] == list(range(6))
+    st = pool.stats()
+    assert st["arenas"] >= 2 and st["gets"] == 6 and st["units_total"] == 4 * st["arenas"]
+    for a in held:
+        pool.put(a)
+    time.sleep(0.3)                                        # the worker retires arenas beyond the standing reserve
+    st2 = pool.stats()
+    assert 1 <= st2["arenas"] <= st["arenas"] and st2["units_free"] >= 2
+    # a consumer blocked on an empty pool is served when a unit comes back
+    small = H.PinnedPool(4096, arena_bytes=4096, standing_units=1)
+    a = small.get()
+    got = []
+    t = threading.Thread(target=lambda: got.append(small.get()))
+    t.start()
+    t.join(timeout=5)                                      # a second arena is made for it (pool grows on demand)
+    assert got and got[0].ctypes.data != a.ctypes.data
+    assert small.stats()["waits"] >= 1
+    small.put(a)
+    small.put(got[0])
+    with pytest.raises(KeyError):
+        small.put(np.zeros(4096, np.uint8))                # not one of this pool's units
+    pool.close()
+    small.close()

@@ -47,6 +47,9 @@ def lib() -> C.CDLL:
             "qwh_rng_new": (P, [ULL]), "qwh_rng_free": (None, [P]), "qwh_sample": (I, [P, I, P, P, LL, LL, P, P]),
             "qwh_top_logprobs": (I, [P, I, I, P, P]), "qwh_lse": (C.c_float, [P, I]),
             "qwh_chunk": (I, [P, LL, I, P, P, P, I]),
+            "qwh_pinned_new": (P, [ULL, ULL, I, I, I, I]), "qwh_pinned_free": (None, [P]), "qwh_pinned_reserve": (None, [P, I]),
+            "qwh_pinned_get": (P, [P]), "qwh_pinned_put": (I, [P, P]), "qwh_pinned_unit_bytes": (ULL, [P]),
+            "qwh_pinned_stats": (None, [P, P, P, P]), "qwh_numa_nodes": (I, []),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
@@ -216,3 +219,51 @@ def chunk_prompt(tokens: Sequence[int], boundary: int):
     st, ln, hs = np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.uint64)
     n = lib().qwh_chunk(t.ctypes.data, len(t), boundary, st.ctypes.data, ln.ctypes.data, hs.ctypes.data, cap)
     return [(int(st[i]), int(ln[i]), int(hs[i])) for i in range(min(n, cap))]
+
+
+class PinnedPool:
+    """Pinned host memory in fixed units from background-pinned arenas (``native/src/pinned_pool.hpp``).  ``get()`` returns
+    a uint8 numpy view of one unit; give it back with ``put``.  With ``use_cuda`` the arenas are also registered with the
+    CUDA runtime when it is loaded in the process, so copies from / to the units are asynchronous."""
+    POLICIES = {"process": 0, "bind": 1, "preferred": 2, "interleave": 3, "auto": 0}
+
+    def __init__(self, unit_bytes: int, arena_bytes: int = 256 << 20, standing_units: int = 2, use_cuda: bool = False,
+                 policy: str = "process", node: int = -1):
+        self.p = lib().qwh_pinned_new(unit_bytes, arena_bytes, standing_units, int(use_cuda), self.POLICIES[policy], node)
+        if not self.p:
+            raise RuntimeError(_err())
+        self.unit_bytes = int(lib().qwh_pinned_unit_bytes(self.p))
+        self._out = {}
+
+    def reserve(self, n: int) -> None:
+        lib().qwh_pinned_reserve(self.p, n)
+
+    def get(self) -> np.ndarray:
+        addr = lib().qwh_pinned_get(self.p)
+        if not addr:
+            raise RuntimeError(_err())
+        a = np.ctypeslib.as_array(C.cast(addr, C.POINTER(C.c_uint8)), shape=(self.unit_bytes,))
+        self._out[a.ctypes.data] = addr
+        return a
+
+    def put(self, a: np.ndarray) -> None:
+        addr = self._out.pop(a.ctypes.data)
+        if lib().qwh_pinned_put(self.p, addr) != 0:
+            raise RuntimeError(_err())
+
+    def stats(self) -> dict:
+        i5, d2, x2 = (C.c_longlong * 5)(), (C.c_double * 2)(), (C.c_int * 2)()
+        lib().qwh_pinned_stats(self.p, i5, d2, x2)
+        return {"arenas": i5[0], "units_total": i5[1], "units_free": i5[2], "gets": i5[3], "waits": i5[4], "wait_seconds": d2[0],
+                "pin_seconds": d2[1], "cuda_registered": bool(x2[0]), "numa_node": x2[1]}
+
+    def close(self) -> None:
+        if getattr(self, "p", None) and lib is not None:
+            lib().qwh_pinned_free(self.p)
+            self.p = None
+
+    __del__ = close
+
+
+def numa_nodes() -> int:
+    return int(lib().qwh_numa_nodes())

@@ -13,6 +13,7 @@
 using namespace qwh;
 
 static thread_local std::string g_err;
+#include "pinned_pool.hpp"
 #define API extern "C" __attribute__((visibility("default")))
 #define GUARD(body, bad)                              \
     try { body } catch (const std::exception &e) {    \
@@ -138,3 +139,21 @@ API int qwh_chunk(const int32_t *tok, long long n, int boundary, long long *star
     for (int i = 0; i < m; ++i) { starts[i] = c[size_t(i)].start; lens[i] = c[size_t(i)].len; hashes[i] = c[size_t(i)].hash; }
     return int(c.size());
 }
+
+// ---- pinned pool (+ NUMA placement)
+API void *qwh_pinned_new(unsigned long long unit_bytes, unsigned long long arena_bytes, int standing_units, int use_cuda, int policy,
+                         int node) {
+    GUARD(return new PinnedPool(size_t(unit_bytes), size_t(arena_bytes), standing_units, use_cuda != 0, NumaPolicy(policy), node);, nullptr)
+}
+API void qwh_pinned_free(void *p) { delete static_cast<PinnedPool *>(p); }
+API void qwh_pinned_reserve(void *p, int n) { static_cast<PinnedPool *>(p)->reserve(n); }
+API void *qwh_pinned_get(void *p) { GUARD(return static_cast<PinnedPool *>(p)->get();, nullptr) }
+API int qwh_pinned_put(void *p, void *unit) { GUARD(static_cast<PinnedPool *>(p)->put(unit); return 0;, -1) }
+API unsigned long long qwh_pinned_unit_bytes(void *p) { return static_cast<PinnedPool *>(p)->unit_bytes(); }
+API void qwh_pinned_stats(void *p, long long *i5, double *d2, int *x2) {
+    const PoolStats s = static_cast<PinnedPool *>(p)->stats();
+    i5[0] = s.arenas; i5[1] = s.units_total; i5[2] = s.units_free; i5[3] = s.gets; i5[4] = s.waits;
+    d2[0] = s.wait_seconds; d2[1] = s.pin_seconds;
+    x2[0] = s.cuda_registered; x2[1] = s.numa_node;
+}
+API int qwh_numa_nodes() { return numa_nodes(); }
