@@ -57,6 +57,11 @@ class DeviceModel:
         self.model = S.QwModel()
         self._layers_arr = (S.QwLayer * cfg.n_layers)()
         self.model.layers = C.cast(self._layers_arr, C.POINTER(S.QwLayer))
+        from ..utils import settings as _settings
+        self.guard_on = bool(_settings.get().guard)
+        self.guards: Dict[str, torch.Tensor] = {}
+        self._guard_raw = []
+        self.steps_run = 0
         self._fill_dims()
         self._alloc_state()
         self._alloc_buffers(save_gdn)
@@ -64,11 +69,6 @@ class DeviceModel:
         qlib.check(self.lib.qwk_rope_init(C.c_double(cfg.rope_theta), cfg.rope_dim), "rope_init")
         # error word for kernels with bounded waits: (code, detail), 0 = ok
         self.err_word = torch.zeros(2, dtype=torch.int32, device=self.dev)
-        from ..utils import settings as _settings
-        self.guard_on = bool(_settings.get().guard)
-        self.guards: Dict[str, torch.Tensor] = {}
-        self._guard_raw = []
-        self.steps_run = 0
         self.moe_stats = None
         if _settings.get().moe_stats:           # QW_MOE_STATS: per-layer count of expert pairs computed on this rank
             self.moe_stats = torch.zeros(cfg.n_layers + 1, dtype=torch.int32, device=self.dev)
