@@ -221,6 +221,25 @@ class Engine:
         assert self.mtp and sl.mtp_hidden is not None
         dm.buf["hidden_out"][0] = sl.mtp_hidden
         pos = sl.n - 1
+        if self.opts.use_graphs and k > 1:
+            # chained: the graph of one MTP pass ends by feeding its token, position and hidden state to the next pass
+            # on the device, so k drafts are k graph replays and one read-back
+            flags = DM.FLAG_CHAIN
+            key = ("mtp", 1, flags)
+            got = torch.zeros(k, dtype=torch.int32, device=dm.dev)
+            if key not in dm.graphs:
+                dm.mtp_step([pending], [slot], [pos], flags=flags, graph=True)       # captures; the warm-up is the first pass
+                got[0:1].copy_(dm.buf["amax_idx"][0:1])
+                done = 1
+            else:
+                dm.stage_rows([pending], [slot], [pos], None)
+                done = 0
+            g = dm.graphs[key]
+            for j in range(done, k):
+                g.replay()
+                got[j:j + 1].copy_(dm.buf["amax_idx"][0:1], non_blocking=True)
+            torch.cuda.current_stream(dm.dev).synchronize()
+            return got.tolist()
         out, tok = [], pending
         for j in range(k):
             dm.mtp_step([tok], [slot], [pos + j], graph=self.opts.use_graphs)
