@@ -39,6 +39,20 @@ __device__ __forceinline__ void report(ErrorWord *e, unsigned int code, unsigned
 // Device address of the error word every launcher hands to its kernel (set once by the host through
 // qwk_set_error_word; null until then, in which case kernels only give up silently).
 extern ErrorWord *g_err_ptr;
+// host side: asks the next expert gate/up launch to also form the shared expert's activation from the router's outputs
+// (a few extra blocks of that launch, in parallel with the routed experts) instead of the router's last block doing it
+// in its serial tail.  rs == null: nothing extra.
+struct SharedAct {
+    const float *rs;     // [M][ld_rs]: router logits (E) | shared gate logit | shared gate rows (SF) | shared up rows (SF)
+    int ld_rs, E, SF;
+    void *sh_h;          // out: [M][SF] bf16
+};
+extern SharedAct g_shared_act;
+inline SharedAct take_shared_act() {
+    SharedAct r = g_shared_act;
+    g_shared_act = SharedAct{nullptr, 0, 0, 0, nullptr};
+    return r;
+}
 extern int *g_moe_stats;     // host side: where the next routing launch adds its count of local pairs (null = nowhere)
 
 // Row tables of a batched step.  Row i appends one token to slot[i] at position pos[i]; rows of

@@ -82,9 +82,18 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
     pf_issue(pf);
     pdl_wait();
     pdl_trigger();
+    // this lane's residual values times the norm weight: needed only at the very end, fetched now so that their L2
+    // round trip overlaps the staging of the reduced vector
+    float xw[UP_ROWS];
+    {
+        const float w1v = c < SH ? w1[s * SH + c] : 0.f;
+#pragma unroll
+        for (int mm = 0; mm < UP_ROWS; ++mm)
+            xw[mm] = (c < SH && mm < nrow) ? __ldcg(X + ((long long)(m0 + mm) * hc + s) * SH + c) * w1v : 0.f;
+    }
     // element i of the reduced vector: the local buffer, or (fused all-reduce) the ranks' words added in rank
-    // order - gathered once per block into shared memory, with every thread's loads in flight together
-    float *reds = rs + UP_ROWS * hc;       // [UP_ROWS][ld_red] (fused only)
+    // order - staged once per block into shared memory, with every thread's loads in flight together
+    float *reds = rs + UP_ROWS * hc;       // [UP_ROWS][ld_red]
     if constexpr (FUSED) {
         const unsigned int seq_in = fuse_seq(fi);
         // what this mixer's down projection wrote of each row (an even count), as pairs of words; a thread has
@@ -106,7 +115,27 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
         }
         __syncthreads();
     }
-    auto red_at = [&](long long i) -> float { return FUSED ? reds[i - (long long)m0 * ld_red] : red[i]; };
+    if constexpr (!FUSED) {
+        // the same staging from the local buffer: every thread's loads in flight together (one L2 round trip per batch)
+        const int used = hc + hc * hc_down, total = nrow * used;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 2048) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * 256;
+                const int mm = i / used, j = i - mm * used;
+                v[u] = i < total ? __ldcg(red + (long long)(m0 + mm) * ld_red + j) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * 256;
+                const int mm = i / used, j = i - mm * used;
+                if (i < total) reds[mm * ld_red + j] = v[u];
+            }
+        }
+        __syncthreads();
+    }
+    auto red_at = [&](long long i) -> float { return reds[i - (long long)m0 * ld_red]; };
     for (int i = threadIdx.x; i < nrow * hc; i += 256) {
         const int mm = i / hc, ss = i % hc;
         rs[mm * hc + ss] = rsqrtf(red_at((long long)(m0 + mm) * ld_red + ss) * inv_H + eps);
@@ -150,8 +179,7 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
         g += __shfl_xor_sync(0xffffffffu, g, 4);
         float v = 0.f;
         if (mm < nrow) {
-            const float xv = X[((long long)(m0 + mm) * hc + s) * SH + c] * w1[s * SH + c];
-            const float yv = __bfloat162float(__float2bfloat16(xv));
+            const float yv = __bfloat162float(__float2bfloat16(xw[mm]));
             v = sigmoidf_(g) * yv * rs[mm * hc + s];
         }
         v += __shfl_xor_sync(0xffffffffu, v, 8);
@@ -174,6 +202,8 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
 // to a second buffer because other blocks still read the old one.
 // grid (ceil(down/rpb), hc, ceil(M/8)), 256 threads, dynamic smem 8*SH bf16.
 // ------------------------------------------------------------------------------------------
+constexpr int DN_CP = 3;      // column pieces of 1024 handled per pass of hc_down's row builder (SH <= 3072 in one pass)
+
 struct HcDownArgs {
     const float *Xin;
     float *Xout;            // null: no combine, X stays where it is
@@ -223,25 +253,39 @@ __global__ void __launch_bounds__(256, 3) hc_down_kernel(HcDownArgs a) {
         float coef = 0.f;
         if (a.pend) coef = 2.f * sigmoidf_(a.inj_prev[(long long)m * a.hc + s] / float(a.hc));
         float ss = 0.f;
-        for (int c = threadIdx.x * 4; c < a.SH; c += 1024) {
-            float4 v = *reinterpret_cast<const float4 *>(xin + c);
-            if (a.pend) {
-                float4 p;
-                if (FUSED && a.fi.active) {          // fused reduce-scatter: the ranks' parts of the block output, added in rank order
-                    p = fuse_sum4(a.fi, seq_in, (long long)m * a.ld_pend + c);
-                } else {
-                    p = *reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c);
+        // up to DN_CP pieces of 1024 columns per pass, every load of the pass issued before the first use (the residual,
+        // the pending block output and the norm weight all come from L2: one round trip per pass instead of one per piece)
+        constexpr int CP = FUSED ? 1 : DN_CP;          // the fused form keeps the ranks' words in flight instead (SH is a shard there)
+        for (int c0 = threadIdx.x * 4; c0 < a.SH; c0 += 1024 * CP) {
+            float4 xv[CP], pv[CP], wv[CP];
+#pragma unroll
+            for (int q = 0; q < CP; ++q) {
+                const int c = c0 + q * 1024;
+                if (c < a.SH) {
+                    xv[q] = __ldcg(reinterpret_cast<const float4 *>(xin + c));
+                    wv[q] = __ldg(reinterpret_cast<const float4 *>(a.w1 + s * a.SH + c));
+                    if (a.pend && !(FUSED && a.fi.active)) pv[q] = __ldcg(reinterpret_cast<const float4 *>(a.pend + (long long)m * a.ld_pend + c));
                 }
-                v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
-                v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
-                if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.Xout + ((long long)m * a.hc + s) * a.SH + c) = v;
             }
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            const float4 ww = *reinterpret_cast<const float4 *>(a.w1 + s * a.SH + c);
-            uint2 pk;
-            pk.x = pack_bf16(v.x * ww.x, v.y * ww.y);
-            pk.y = pack_bf16(v.z * ww.z, v.w * ww.w);
-            *reinterpret_cast<uint2 *>(ybuf + r * a.SH + c) = pk;
+#pragma unroll
+            for (int q = 0; q < CP; ++q) {
+                const int c = c0 + q * 1024;
+                if (c < a.SH) {
+                    float4 v = xv[q];
+                    if (a.pend) {
+                        // fused reduce-scatter: the ranks' parts of the block output, added in rank order
+                        const float4 p = (FUSED && a.fi.active) ? fuse_sum4(a.fi, seq_in, (long long)m * a.ld_pend + c) : pv[q];
+                        v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
+                        v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
+                        if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.Xout + ((long long)m * a.hc + s) * a.SH + c) = v;
+                    }
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                    uint2 pk;
+                    pk.x = pack_bf16(v.x * wv[q].x, v.y * wv[q].y);
+                    pk.y = pack_bf16(v.z * wv[q].z, v.w * wv[q].w);
+                    *reinterpret_cast<uint2 *>(ybuf + r * a.SH + c) = pk;
+                }
+            }
         }
         if (blockIdx.x == 0) {                 // block-uniform: only these blocks need the sum of squares
             ss = block_sum<256>(ss, scratch);
@@ -324,7 +368,7 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
     if (hc != 4 || (R & 7) || R > 8 * 8 * UP_MAXI) return -1;
     dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
     const FuseIn fi = take_fi();
-    const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc + (fi.active ? UP_ROWS * ld_red : 0));
+    const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc + UP_ROWS * ld_red);
     if (smem > 48 * 1024) return -1;
     const FuseOut fo = take_fo();
     if ((fi.active != 0) != (fo.mode != 0)) return -1;          // the fused mixer both receives and sends

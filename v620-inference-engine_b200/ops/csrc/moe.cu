@@ -161,10 +161,15 @@ constexpr int DN_T = 8;      // pieces per lane over top_k down rows: top_k * F/
 
 // h[p][f] = silu(gate_e[f] . x_m) * (up_e[f] . x_m) for pair p = (m, j).  grid (ceil(F/8), pairs).
 __global__ void __launch_bounds__(256) moe_gate_up_pair_kernel(const uint32_t *w13, const bf16 *s13, const bf16 *x, int ldx,
-                                                               const int *pair_expert, int top_k, int F, int K, bf16 *h, PfArgs pf) {
+                                                               const int *pair_expert, int top_k, int F, int K, bf16 *h, PfArgs pf,
+                                                               SharedAct sa, int npairs) {
     pf_issue(pf);
     pdl_wait();
     pdl_trigger();
+    if ((int)blockIdx.y >= npairs) {          // the extra rows of the grid: the shared expert's activation
+        if (blockIdx.x == 0) shared_act_row(sa, blockIdx.y - npairs);
+        return;
+    }
     const int p = blockIdx.y;
     const int e = pair_expert[p];
     if (e < 0) return;
@@ -337,17 +342,19 @@ QW_API int qwk_moe_route(const float *rs, int ld_rs, int M, int E, int top_k, in
 QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x, int ldx, const int *pair_expert, int M,
                                 int top_k, int F, int K, void *h, cudaStream_t s) {
     if ((K & 127) || (ldx & 7)) return -1;
+    const SharedAct sa = take_shared_act();
+    const int extra = sa.rs ? M : 0;          // one extra grid row per token for the shared expert's activation
     if ((moe_mma_mask() & 1) && (F & 15) == 0 && (K >> 7) <= MM_WARPS * GU_NG) {
         // tensor-core form: 16 rows of gate and of up per block
         const size_t smem = (size_t)K * 2 + MM_WARPS * 2 * 16 * sizeof(float);
-        cudaError_t e = launch_pdl(moe_gate_up_mma_kernel, dim3(F / 16, M * top_k), dim3(128), smem, s, (const uint32_t *)w13,
-                                   (const bf16 *)s13, (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf());
+        cudaError_t e = launch_pdl(moe_gate_up_mma_kernel, dim3(F / 16, M * top_k + extra), dim3(128), smem, s, (const uint32_t *)w13,
+                                   (const bf16 *)s13, (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf(), sa, M * top_k);
         return e == cudaSuccess ? 0 : -2;
     }
     if (2 * (K >> 5) > 32 * GU_T) return -1;
-    dim3 grid((F + 7) / 8, M * top_k);
+    dim3 grid((F + 7) / 8, M * top_k + extra);
     cudaError_t e = launch_pdl(moe_gate_up_pair_kernel, grid, dim3(256), 0, s, (const uint32_t *)w13, (const bf16 *)s13,
-                               (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf());
+                               (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, take_pf(), sa, M * top_k);
     return e == cudaSuccess ? 0 : -2;
 }
 

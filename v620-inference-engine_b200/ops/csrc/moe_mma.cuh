@@ -44,6 +44,27 @@ __device__ __forceinline__ void mma_bf16_chunk(float (&c)[4], const uint4 &wr, c
     mma_bf16(c, wr.z, wr8.z, wr.w, wr8.w, xv.z, xv.w);
 }
 
+// Shared expert's activation of row m: sh_h[m][f] = bf16(silu(gate_f) * up_f * sigmoid(shared gate logit)), by one block.
+__device__ __forceinline__ void shared_act_row(const SharedAct &sa, int m) {
+    const float *l = sa.rs + (long long)m * sa.ld_rs + sa.E;
+    const float sg = sigmoidf_(__ldcg(l));
+    bf16 *o = reinterpret_cast<bf16 *>(sa.sh_h) + (long long)m * sa.SF;
+    for (int f0 = threadIdx.x; f0 < sa.SF; f0 += 4 * blockDim.x) {          // four independent loads of each kind in flight
+        float g[4], u[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int f = f0 + k * blockDim.x;
+            g[k] = f < sa.SF ? __ldcg(l + 1 + f) : 0.f;
+            u[k] = f < sa.SF ? __ldcg(l + 1 + sa.SF + f) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int f = f0 + k * blockDim.x;
+            if (f < sa.SF) o[f] = __float2bfloat16(siluf_(g[k]) * u[k] * sg);
+        }
+    }
+}
+
 constexpr int MM_WARPS = 4;          // warps per block (128 threads: three blocks per SM stay resident, so 400 tiles are one wave)
 constexpr int GU_NG = 5;             // k groups of 128 per warp in the gate/up kernel: K <= 4 * 5 * 128
 constexpr int DN_NI = 13;            // (expert, k group) items per warp in the down kernel: top_k * F / 128 <= 52
@@ -53,13 +74,18 @@ constexpr int DN_NS = 5;             // quad-steps of the shared expert per warp
 // Warp w takes the k groups g = w, w + 4, ...; every weight load of the block is issued before the first
 // one is used, and the four partial tiles are added in warp order.
 __global__ void __launch_bounds__(128) moe_gate_up_mma_kernel(const uint32_t *w13, const bf16 *s13, const bf16 *x, int ldx,
-                                                              const int *pair_expert, int top_k, int F, int K, bf16 *h, PfArgs pf) {
+                                                              const int *pair_expert, int top_k, int F, int K, bf16 *h, PfArgs pf,
+                                                              SharedAct sa, int npairs) {
     extern __shared__ __align__(16) unsigned char mm_smem[];
     uint4 *xs = reinterpret_cast<uint4 *>(mm_smem);                       // [K / 8] activation words
     float *red = reinterpret_cast<float *>(mm_smem + (size_t)K * 2);     // [4 warps][2][16]
     pf_issue(pf);
     pdl_wait();
     pdl_trigger();
+    if ((int)blockIdx.y >= npairs) {          // the extra rows of the grid: the shared expert's activation
+        if (blockIdx.x == 0) shared_act_row(sa, blockIdx.y - npairs);
+        return;
+    }
     const int p = blockIdx.y;
     const int e = pair_expert[p];
     if (e < 0) return;

@@ -20,6 +20,7 @@ namespace qw {
 ErrorWord *g_err_ptr = nullptr;
 PfArgs g_pf = {};
 int *g_moe_stats = nullptr;
+SharedAct g_shared_act = {nullptr, 0, 0, 0, nullptr};
 FuseOut g_fo = {};
 FuseIn g_fi = {};
 }
@@ -138,6 +139,7 @@ int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the 
             qw::g_pf = qw::PfArgs{};                                              \
             qw::g_fo = qw::FuseOut{};                                             \
             qw::g_fi = qw::FuseIn{};                                              \
+            qw::g_shared_act = qw::SharedAct{nullptr, 0, 0, 0, nullptr};          \
         }                                                                         \
     } while (0)
 
@@ -280,8 +282,10 @@ void moe_block(Ctx &c, const QwLayer &L, bool fuse_out = true, int stats_index =
     const int nrs = d.E + 1 + 2 * d.SF;
     await_bin(c);
     if (!c.dry && g_moe_stats_base && stats_index >= 0) qw::g_moe_stats = g_moe_stats_base + stats_index;
+    // the shared expert's activation is formed by extra blocks of the gate/up launch, not by the router's last block
     QW_OP(1, L.Wrs, (size_t)nrs * d.H * 2, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
-                              b.pair_w, b.sh_h, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
+                              b.pair_w, nullptr, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
+    if (!c.dry) qw::g_shared_act = qw::SharedAct{b.rs, nrs, d.E, d.SF, b.sh_h};
     QW_OP(1, nullptr, 0, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
     send_partial(c, fuse_out);
     QW_OP(1, L.Wsd, (size_t)d.H * d.SF * 2, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,

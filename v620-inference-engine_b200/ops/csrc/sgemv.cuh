@@ -56,12 +56,23 @@ struct SGemvSmem {
 struct XFillCopy {
     const SGemvArgs &a;
     __device__ __forceinline__ void operator()(int /*split*/, int /*row0*/, int m0, int nm, const SGemvSmem &sm, int tid) const {
-        const int nchunk = a.K >> 3;
-        for (int i = tid; i < (nm + 1) * nchunk; i += 256) {
-            const int m = i / nchunk, c = i - m * nchunk;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < nm) v = __ldcg(reinterpret_cast<const uint4 *>(a.x + (long long)(m0 + m) * a.ldx) + c);
-            *reinterpret_cast<uint4 *>(sm.xs + (size_t)m * sm.xrow + (size_t)c * 16) = v;
+        const int nchunk = a.K >> 3, total = (nm + 1) * nchunk;
+        // four loads per thread in flight: the fill is on the kernel's critical path (one L2 round trip per batch)
+        for (int i0 = tid; i0 < total; i0 += 1024) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * 256;
+                const int m = i / nchunk, c = i - m * nchunk;
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < total && m < nm) v[u] = __ldcg(reinterpret_cast<const uint4 *>(a.x + (long long)(m0 + m) * a.ldx) + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * 256;
+                const int m = i / nchunk, c = i - m * nchunk;
+                if (i < total) *reinterpret_cast<uint4 *>(sm.xs + (size_t)m * sm.xrow + (size_t)c * 16) = v[u];
+            }
         }
     }
 };

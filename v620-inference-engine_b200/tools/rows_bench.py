@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--slots", default="1")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--profile", action="store_true", help="bracket one extra step per row count with cudaProfilerStart/Stop")
     a = ap.parse_args()
     rows = [int(x) for x in a.rows.split(",")]
     cfg = ModelConfig.full()
@@ -59,6 +60,11 @@ def main():
                 step()
             e1.record()
             torch.cuda.synchronize()
+            if a.profile and name == "plain":
+                torch.cuda.profiler.start()
+                step()
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
             out[f"{name}_{M}"] = round(e0.elapsed_time(e1) / a.reps, 3)
             print(f"rows={M:2d} {name:6s}: {out[f'{name}_{M}']:.3f} ms per step, {M / out[f'{name}_{M}'] * 1e3:.0f} tok/s", flush=True)
     eng.dm.check_error()
