@@ -189,8 +189,8 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
         for (int k = 0; k < 4; ++k) tap[k] = a.cw[ch * 4 + k];
     }
     pf_issue(a.pf);
-    pdl_wait();
-    pdl_trigger();
+    // The row table was written before the step began and the recurrent state only by this kernel in the previous step:
+    // neither depends on the predecessor, so the state (64 KB per head, from HBM) is fetched before waiting for it.
     if (a.rows.run_start[m0] != m0) return;
     const int len = a.rows.run_len[m0], slot = a.rows.slot[m0];
     float *ring = a.ring + (long long)slot * GDN_RING * qkv_l;
@@ -198,6 +198,8 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
     float S[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) S[i] = Sg[(kg * 32 + i) * GD + c];
+    pdl_wait();
+    pdl_trigger();
     for (int r = 0; r < len; ++r) {
         const int m = m0 + r, pos = a.rows.pos[m];
         // conv + silu for q / k / v channels

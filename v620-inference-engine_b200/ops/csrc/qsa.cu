@@ -95,6 +95,8 @@ __device__ __forceinline__ void fill_cs(float *cs, int pos) {
 
 // grid (M, QL + 2*KVL + IH + 1), 256 threads.
 __global__ void __launch_bounds__(256) qsa_prep_kernel(QsaPrepArgs a) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     __shared__ float sm[HD];
     __shared__ float scratch[32];
     __shared__ float cs[2 * MAX_HALF];
@@ -146,6 +148,8 @@ __global__ void __launch_bounds__(256) qsa_prep_kernel(QsaPrepArgs a) {
 
 // grid M, 128 threads: raw-key ring store for long batches (runs after qsa_prep_kernel).
 __global__ void qsa_raw_ring_kernel(const float *proj, int ld_proj, int off_raw, float *raw_ring, Rows rows) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     const int m = blockIdx.x, d = threadIdx.x;
     const int rs = rows.run_start[m], len = rows.run_len[rs];
     if ((m - rs) < len - RAW_RING) return;
@@ -158,6 +162,8 @@ __global__ void qsa_raw_ring_kernel(const float *proj, int ld_proj, int off_raw,
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) qsa_scores_kernel(const float *iq, int IH, const bf16 *ck, int ck_cap, Rows rows,
                                                          int ratio, int topk_blocks, float *scores, int ld_scores) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     __shared__ float q[8 * ID];          // IH <= 8
     const int m = blockIdx.y;
     const int slot = rows.slot[m], pos = rows.pos[m];
@@ -222,6 +228,8 @@ __device__ __forceinline__ int block_exscan_1024(int v, int *wsum, int &total) {
 
 __global__ void __launch_bounds__(1024) qsa_select_kernel(const float *scores, int ld_scores, Rows rows, int ratio,
                                                           int topk, int *sel, int *sel_n) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     __shared__ int hist[256];
     __shared__ int wsum[32];
     __shared__ unsigned int s_prefix;
@@ -246,14 +254,34 @@ __global__ void __launch_bounds__(1024) qsa_select_kernel(const float *scores, i
             if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xff], 1);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int need = s_need, b = 255;
-            for (; b > 0; --b) {
-                if (hist[b] >= need) break;
-                need -= hist[b];
+        if (threadIdx.x < 32) {
+            // the highest bin b whose count from the top reaches `need` (0 if none does), found by one warp: lane l owns
+            // bins 8 l .. 8 l + 7, a suffix sum over the lanes locates the lane, a scan of its 8 bins the bin
+            const int lane = threadIdx.x, need = s_need;
+            int loc[8], own = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { loc[j] = hist[8 * lane + j]; own += loc[j]; }
+            int suf = own;                                   // bins of this lane and of all higher lanes
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, suf, off);
+                if (lane + off < 32) suf += t;
             }
-            s_need = need;
-            s_prefix = prefix | ((unsigned int)b << shift);
+            const int above = suf - own;
+            const bool mine = above < need && need <= suf;
+            const unsigned int who = __ballot_sync(0xffffffffu, mine);
+            if (who == 0u) {                                 // fewer than `need` entries in all bins above 0: bin 0 takes the rest
+                const int tot = __shfl_sync(0xffffffffu, suf, 0);
+                if (lane == 0) { s_need = need - (tot - loc[0]); s_prefix = prefix; }
+            } else if (mine) {
+                int rem = need - above, b = 7;
+                for (; b > 0; --b) {
+                    if (loc[b] >= rem) break;
+                    rem -= loc[b];
+                }
+                s_need = rem;
+                s_prefix = prefix | ((unsigned int)(8 * lane + b) << shift);
+            }
         }
         __syncthreads();
     }
@@ -301,6 +329,8 @@ __device__ __forceinline__ int list_token(int t, int dense, const int *sel, int 
 
 template <int HT>
 __global__ void __launch_bounds__(256) qsa_attend_kernel(QsaAttendArgs a) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     __shared__ float s_acc[8][HT][HD];
     __shared__ float s_m[8][HT], s_l[8][HT];
     const int sp = blockIdx.x, m = blockIdx.y, h0 = blockIdx.z * HT;
@@ -379,6 +409,8 @@ __global__ void __launch_bounds__(256) qsa_attend_kernel(QsaAttendArgs a) {
 // grid (M, QL), 256 threads: merge the splits, apply sigmoid(gate), write bf16.
 __global__ void __launch_bounds__(256) qsa_combine_kernel(const float *pm, const float *pl, const float *pacc, int nsplit,
                                                           const float *proj, int ld_proj, int QL, bf16 *o) {
+    pdl_wait();          // launched with programmatic dependent launch: the predecessor's results are needed from here on
+    pdl_trigger();
     const int m = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const long long b = ((long long)m * QL + h) * nsplit;
     float M = -INFINITY;
@@ -431,9 +463,9 @@ QW_API int qwk_qsa_prep(const float *proj, int ld_proj, int QL, int KVL, int IH,
     a.q = q; a.iq = iq; a.raw_ring = raw_ring; a.ck = (bf16 *)ck; a.ck_cap = ck_cap; a.ratio = ratio; a.eps = eps;
     a.ring_inline = M <= RAW_RING - ratio ? 1 : 0;
     dim3 grid(M, QL + 2 * KVL + IH + 1);
-    qsa_prep_kernel<<<grid, 256, 0, s>>>(a);
+    launch_pdl(qsa_prep_kernel, grid, dim3(256), 0, s, a);
     if (!a.ring_inline)
-        qsa_raw_ring_kernel<<<M, ID, 0, s>>>(proj, ld_proj, QL * 2 * HD + 2 * KVL * HD + IH * ID, raw_ring, a.rows);
+        launch_pdl(qsa_raw_ring_kernel, dim3(M), dim3(ID), 0, s, proj, ld_proj, QL * 2 * HD + 2 * KVL * HD + IH * ID, raw_ring, a.rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -441,15 +473,15 @@ QW_API int qwk_qsa_scores(const float *iq, int IH, const void *ck, int ck_cap, i
                           int ratio, int topk_blocks, float *scores, int ld_scores, int max_groups, cudaStream_t s) {
     if (max_groups <= topk_blocks) return 0;
     dim3 grid((max_groups + 63) / 64, M);
-    qsa_scores_kernel<<<grid, 256, 0, s>>>(iq, IH, (const bf16 *)ck, ck_cap, Rows{M, slot, pos, nullptr, nullptr}, ratio,
-                                           topk_blocks, scores, ld_scores);
+    launch_pdl(qsa_scores_kernel, grid, dim3(256), 0, s, iq, IH, (const bf16 *)ck, ck_cap, Rows{M, slot, pos, nullptr, nullptr}, ratio,
+               topk_blocks, scores, ld_scores);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 QW_API int qwk_qsa_select(const float *scores, int ld_scores, int M, const int *pos, int ratio, int topk, int *sel,
                           int *sel_n, cudaStream_t s) {
-    qsa_select_kernel<<<M, 1024, 0, s>>>(scores, ld_scores, Rows{M, nullptr, pos, nullptr, nullptr}, ratio, topk, sel,
-                                         sel_n);
+    launch_pdl(qsa_select_kernel, dim3(M), dim3(1024), 0, s, scores, ld_scores, Rows{M, nullptr, pos, nullptr, nullptr}, ratio, topk, sel,
+               sel_n);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -465,11 +497,11 @@ QW_API int qwk_qsa_attend(const float *q, int QL, int KVL, int M, const int *slo
     const int per_kv = QL / KVL;
     int ht = per_kv % 4 == 0 ? 4 : (per_kv % 3 == 0 ? 3 : (per_kv % 2 == 0 ? 2 : 1));
     dim3 grid(nsplit, M, QL / ht);
-    if (ht == 4) qsa_attend_kernel<4><<<grid, 256, 0, s>>>(a);
-    else if (ht == 3) qsa_attend_kernel<3><<<grid, 256, 0, s>>>(a);
-    else if (ht == 2) qsa_attend_kernel<2><<<grid, 256, 0, s>>>(a);
-    else qsa_attend_kernel<1><<<grid, 256, 0, s>>>(a);
+    if (ht == 4) launch_pdl(qsa_attend_kernel<4>, grid, dim3(256), 0, s, a);
+    else if (ht == 3) launch_pdl(qsa_attend_kernel<3>, grid, dim3(256), 0, s, a);
+    else if (ht == 2) launch_pdl(qsa_attend_kernel<2>, grid, dim3(256), 0, s, a);
+    else launch_pdl(qsa_attend_kernel<1>, grid, dim3(256), 0, s, a);
     dim3 g2(M, QL);
-    qsa_combine_kernel<<<g2, 256, 0, s>>>(pm, pl, pacc, nsplit, proj, ld_proj, QL, (bf16 *)o);
+    launch_pdl(qsa_combine_kernel, g2, dim3(256), 0, s, (const float *)pm, (const float *)pl, (const float *)pacc, nsplit, proj, ld_proj, QL, (bf16 *)o);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
