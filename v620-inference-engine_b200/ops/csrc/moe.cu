@@ -8,6 +8,7 @@
 //                weighted combine and the shared expert's down projection fused into the second.
 // (Roles of the reference's src/kernels/moe_route.hip:65-224 and src/kernels/moe_experts.hip:189-246.)
 #include <cstdlib>
+#include <cstring>
 
 #include "sgemv.cuh"
 #include "moe_mma.cuh"
@@ -18,38 +19,44 @@ namespace qw {
 // One warp per row.
 __device__ __forceinline__ void route_row(const float *l, int E, int top_k, int e_first, int e_local, int *pair_expert,
                                           float *pair_w, int lane, int *stats) {
+    // The ranking is done on the logits (the softmax is monotonic); only the chosen ones are exponentiated:
+    // w_j = exp(l_j - l_top) / sum over the chosen.  Every lane keeps the best of its own elements cached, so a round
+    // is one warp arg-max (5 shuffle steps) plus a rescan by the one lane that lost its best.
     float v[32];     // E <= 1024
-    float mx = -INFINITY;
+    const int ni = (E + 31) >> 5;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         const int e = lane + 32 * i;
-        v[i] = e < E ? __ldcg(l + e) : -INFINITY;
-        mx = fmaxf(mx, v[i]);
+        v[i] = (i < ni && e < E) ? __ldcg(l + e) : -INFINITY;
     }
-    mx = warp_max(mx);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;
-    float topsum = 0.f, mine_w = 0.f;
+    for (int i = 0; i < 32; ++i)          // ascending index: strict > keeps the lowest index
+        if (v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
+    float topsum = 0.f, mine_w = 0.f, top0 = 0.f;
     int mine_e = -1;
     for (int j = 0; j < top_k; ++j) {
-        float bv = -1.f;
-        int bi = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {      // ascending index: strict > keeps the lowest index
-            if (v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
-        }
+        float wv = bv;
+        int wi = bi;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+            if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
         }
-        topsum += bv;
-        if (lane == j) { mine_e = bi; mine_w = bv; }
-        if ((bi & 31) == lane) {
+        if (j == 0) top0 = wv;
+        const float p = __expf(wv - top0);
+        topsum += p;
+        if (lane == j) { mine_e = wi; mine_w = p; }
+        if ((wi & 31) == lane) {          // the winner's lane drops it and looks for its next best
+            bv = -INFINITY;
+            bi = 0x7fffffff;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (i == (bi >> 5)) v[i] = -1.f;
+            for (int i = 0; i < 32; ++i) {
+                if (i == (wi >> 5)) v[i] = -INFINITY;
+                if (v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
+            }
         }
     }
     if (lane < top_k) {
@@ -74,11 +81,14 @@ struct RouteArgs {
     int *stats;                                  // optional counter of local pairs (MoE balance statistics)
 };
 
-__device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, const RouteArgs &r) {
+// `scratch`: 1056 floats of shared memory the caller does not need any more.
+__device__ __forceinline__ void route_all(const float *rs, int ld_rs, int M, const RouteArgs &r, float *scratch) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    float *s_log = scratch, *s_top = scratch + 1024;
     for (int m = warp; m < M; m += nw)
         route_row(rs + (long long)m * ld_rs, r.E, r.top_k, r.e_first, r.e_local, r.pair_expert + m * r.top_k,
                   r.pair_w + m * r.top_k, lane, r.stats);
+    (void)s_log; (void)s_top;
     if (r.sh_h) {
         for (int i = threadIdx.x; i < M * r.F; i += blockDim.x) {
             const int m = i / r.F, f = i % r.F;
@@ -101,7 +111,11 @@ __global__ void __launch_bounds__(SG_THREADS, 1) moe_router_kernel(SGemvArgs a, 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    route_all(a.y, a.ldy, a.M, r);
+    if (r.prefetch_rows < 0) {          // timing diagnostic (QW_SKIP=route_tail): leave the routing tables as they are
+        if (threadIdx.x == 0) *r.ticket = 0u;
+        return;
+    }
+    route_all(a.y, a.ldy, a.M, r, reinterpret_cast<float *>(sg_smem + SG_HDR));      // the weight stages are free now
     if (threadIdx.x == 0) *r.ticket = 0u;
 }
 
@@ -138,7 +152,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *rs, int ld_
     q.pair_expert += m0 * r.top_k;
     q.pair_w += m0 * r.top_k;
     if (q.sh_h) q.sh_h += (long long)m0 * r.F;
-    route_all(rs + (long long)m0 * ld_rs, ld_rs, nm, q);
+    __shared__ float s_route[1056];
+    route_all(rs + (long long)m0 * ld_rs, ld_rs, nm, q, s_route);
 }
 
 // 32 q4 values (one 16-byte load, engine order) dot 32 bf16 activations.
@@ -327,6 +342,11 @@ QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, in
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
     r.w13 = (const char *)w13; r.w2 = (const char *)w2; r.w13_bytes = w13_bytes; r.w2_bytes = w2_bytes;
     r.prefetch_rows = 0;       // one block cannot pull 24 MB through its copy engine fast enough: measured 2x slower; kept off
+    {
+        static int skip_tail = -1;
+        if (skip_tail < 0) { const char *e = getenv("QW_SKIP"); skip_tail = e && strstr(e, "route_tail") ? 1 : 0; }
+        if (skip_tail) r.prefetch_rows = -1;
+    }
     const cudaError_t e = launch_router(a, r, s);
     return e == cudaSuccess ? 0 : -2;
 }
