@@ -94,10 +94,10 @@ def test_moe_pair_kernels_match_oracle():
     from qwb200.ops import lib as qlib
     L = qlib.load(True)
     try:
-        for mask in (0, 1, 3):          # scalar kernels, tensor-core gate/up, tensor-core gate/up and down
+        for mask in (0, 1, 3, 12):      # scalar kernels, tensor-core gate/up, + tensor-core down, bulk-copy-fed tensor-core forms
             L.qwk_set_moe_mma(mask)
             out = K_.moe_experts_pair(mw["w13"], mw["s13"], mw["w2"], mw["s2"], xd, pe, pw, cfg.ffn, cfg.hidden, mw["Wsd"], sh)
             err = (out.cpu() - want).abs().max() / want.abs().max()
             assert err < 2e-2, (mask, float(err))
     finally:
-        L.qwk_set_moe_mma(1)
+        L.qwk_set_moe_mma(12)

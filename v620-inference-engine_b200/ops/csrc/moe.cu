@@ -301,20 +301,20 @@ __global__ void __launch_bounds__(256) moe_down_combine_kernel(const uint32_t *w
 
 using namespace qw;
 
-// Which routed-expert kernels run on the tensor cores: bit 0 = gate/up, bit 1 = down.  Default 1: inside the decode
-// graph the tensor-core gate/up kernel costs the same 15 us as the scalar one (the time is the router -> expert id ->
-// weights dependency chain, not the arithmetic) with a third of the instructions; the tensor-core down kernel's longer
-// per-warp chain made the step 0.3 ms slower, so the scalar one stays the default.  QW_MOE_MMA overrides at start-up.
+// Which form of the routed-expert kernels runs: bit 0 / 1 = gate-up / down on the tensor cores with direct loads,
+// bit 2 / 3 = gate-up / down on the tensor cores fed by bulk-async row copies (wins over bits 0 / 1), 0 = scalar kernels.
+// Default 12, measured inside the decode graph on the full model: scalar 5.37 ms per step, direct-load tensor-core forms
+// 5.37 / 5.7, bulk-copy-fed forms 4.85.  QW_MOE_MMA overrides at start-up, qwk_set_moe_mma at run time.
 static int g_moe_mma = -1;
 static int moe_mma_mask() {
     if (g_moe_mma < 0) {
         const char *e = getenv("QW_MOE_MMA");
-        g_moe_mma = e ? atoi(e) & 3 : 1;
+        g_moe_mma = e ? atoi(e) & 15 : 12;
     }
     return g_moe_mma;
 }
 QW_API int qwk_set_moe_mma(int mask) {
-    g_moe_mma = mask & 3;
+    g_moe_mma = mask & 15;
     return 0;
 }
 
@@ -364,6 +364,21 @@ QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x,
     if ((K & 127) || (ldx & 7)) return -1;
     const SharedAct sa = take_shared_act();
     const int extra = sa.rs ? M : 0;          // one extra grid row per token for the shared expert's activation
+    if ((moe_mma_mask() & 4) && (F & 15) == 0 && (K & 127) == 0) {
+        // bulk-copy-fed tensor-core form
+        const int ks = K >> 7;
+        const size_t smem = 128 + 2 * 16 * ((size_t)(K >> 1) + TM_PAD) + 2 * 16 * ks * 2 + 16 + (size_t)(K >> 3) * 16 + 16 * 2 * 16 * sizeof(float);
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(moe_gate_up_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            attr = true;
+        }
+        if (smem <= 100 * 1024) {
+            cudaError_t e = launch_pdl(moe_gate_up_tma_kernel, dim3(F / 16, M * top_k + extra), dim3(512), smem, s, (const uint32_t *)w13,
+                                       (const bf16 *)s13, (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, g_err_ptr, sa, M * top_k);
+            return e == cudaSuccess ? 0 : -2;
+        }
+    }
     if ((moe_mma_mask() & 1) && (F & 15) == 0 && (K >> 7) <= MM_WARPS * GU_NG) {
         // tensor-core form: 16 rows of gate and of up per block
         const size_t smem = (size_t)K * 2 + MM_WARPS * 2 * 16 * sizeof(float);
@@ -383,6 +398,28 @@ QW_API int qwk_moe_down_combine(const void *w2, const void *s2, const void *h, c
                                 const void *sh_h, int SF, float *out, int ldo, cudaStream_t s) {
     if ((F & 127) || (SF & 7)) return -1;
     const FuseOut fo = take_fo();
+    if ((moe_mma_mask() & 8) && (H & 15) == 0 && (F & 127) == 0 && (SF & 7) == 0 && (ld_sd & 7) == 0 && top_k <= 32) {
+        // bulk-copy-fed tensor-core form
+        const int ks = F >> 7;
+        const size_t smem = 128 + (size_t)top_k * 16 * ((F >> 1) + TM_PAD) + (shared_down ? 16 * ((size_t)SF * 2 + TM_PAD) : 0) +
+                            (size_t)top_k * (((16 * ks * 2) + 15) & ~15) + ((size_t)top_k * (F >> 3) + (SF >> 3)) * 16 + 16 * 16 * 4 + 32 * 4 + 32 * 4;
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(moe_down_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+            cudaFuncSetAttribute(moe_down_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+            attr = true;
+        }
+        if (smem <= 110 * 1024) {
+            const dim3 g2(H / 16, M);
+            cudaError_t e = fo.mode ? launch_pdl(moe_down_tma_kernel<true>, g2, dim3(512), smem, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                                 (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                                 (const bf16 *)sh_h, SF, out, ldo, g_err_ptr, fo)
+                                    : launch_pdl(moe_down_tma_kernel<false>, g2, dim3(512), smem, s, (const uint32_t *)w2, (const bf16 *)s2,
+                                                 (const bf16 *)h, pair_expert, pair_w, top_k, F, H, (const bf16 *)shared_down, ld_sd,
+                                                 (const bf16 *)sh_h, SF, out, ldo, g_err_ptr, fo);
+            return e == cudaSuccess ? 0 : -2;
+        }
+    }
     if ((moe_mma_mask() & 2) && (H & 15) == 0 && top_k * (F >> 7) <= MM_WARPS * DN_NI && (SF >> 5) <= MM_WARPS * DN_NS && (ld_sd & 7) == 0) {
         // tensor-core form: 16 output columns per block
         const size_t smem = ((size_t)top_k * (F >> 3) + (SF >> 3)) * 16 + MM_WARPS * 16 * sizeof(float);
