@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
 // to a second buffer because other blocks still read the old one.
 // grid (ceil(down/rpb), hc, ceil(M/8)), 256 threads, dynamic smem 8*SH bf16.
 // ------------------------------------------------------------------------------------------
+constexpr int DN_PF = 5;      // 16-byte weight pieces per lane fetched before the dependency wait (2560 columns / 2 warps / 32 lanes / 8)
 constexpr int DN_CP = 3;      // column pieces of 1024 handled per pass of hc_down's row builder (SH <= 3072 in one pass)
 
 struct HcDownArgs {
@@ -233,11 +234,11 @@ __global__ void __launch_bounds__(256, 3) hc_down_kernel(HcDownArgs a) {
     const int nchunk = a.SH >> 3;
     const bf16 *wrow = a.Wd + ((long long)j * a.hc + s) * a.SH;
     // weights first: prefetch this warp's share of its row into registers / L2
-    uint4 w0[4];
+    uint4 w0[DN_PF];          // this warp's share of its weight row: all of it for the model's shapes, so no load is issued late
     const int stride = wpr * 32;
     if (j < a.down) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < DN_PF; ++u) {
             const int c = kw * 32 + lane + u * stride;
             if (c < nchunk) w0[u] = ld_stream(reinterpret_cast<const uint4 *>(wrow) + c);
         }
@@ -300,15 +301,15 @@ __global__ void __launch_bounds__(256, 3) hc_down_kernel(HcDownArgs a) {
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m] = 0.f;
     if (j < a.down) {
-        for (int c0 = kw * 32 + lane, first = 1; c0 < nchunk; c0 += 4 * stride, first = 0) {
-            uint4 w[4];
+        for (int c0 = kw * 32 + lane, first = 1; c0 < nchunk; c0 += DN_PF * stride, first = 0) {
+            uint4 w[DN_PF];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < DN_PF; ++u) {
                 const int c = c0 + u * stride;
                 if (c < nchunk) w[u] = first ? w0[u] : ld_stream(reinterpret_cast<const uint4 *>(wrow) + c);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < DN_PF; ++u) {
                 const int c = c0 + u * stride;
                 if (c < nchunk) {
 #pragma unroll
