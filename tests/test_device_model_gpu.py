@@ -302,3 +302,52 @@ def test_engine_from_checkpoint_with_weight_cache(tmp_path):
     b = Engine.from_checkpoint(cfg, d, table, opts, weight_cache_dir=cdir)
     assert torch.equal(b.prefill(0, toks), la)
     shutil.rmtree(cdir)
+
+
+@pytest.mark.gpu
+def test_calibration_hessians(tmp_path):
+    """X^T X of every block's input rows, accumulated over two prompts, symmetric, and equal to what the captured inputs give."""
+    from qwb200.engine.calibrate import Calibrator
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    cfg = ModelConfig.tiny()
+    eng = Engine.synthetic(cfg, EngineOptions(slots=1, slot_tokens=1024, use_graphs=False, prefill_chunk=128), device="cuda:0",
+                           exact=True, ple_rows=4096)
+    cal = Calibrator(eng)
+    seen = {}
+    orig = cal._hook
+
+    def spy(layer, kind, x):
+        seen.setdefault((layer, kind), []).append(x.float().clone())
+        orig(layer, kind, x)
+    cal._hook = spy
+    cal.run(0, [(i * 3 + 1) % 900 + 5 for i in range(200)])
+    cal.run(0, [(i * 5 + 2) % 900 + 5 for i in range(150)])
+    assert len(cal.H) == 2 * cfg.n_layers and all(n == 350 for n in cal.rows.values())
+    for k, h in cal.H.items():
+        x = torch.cat(seen[k])
+        assert torch.allclose(h, x.t() @ x, rtol=1e-4, atol=1e-3) and torch.allclose(h, h.t())
+    cal.dump(str(tmp_path))
+    from safetensors.torch import load_file
+    d = load_file(str(tmp_path / "hessians.safetensors"))
+    assert d["layers.0.attn.hessian"].shape == (cfg.hidden, cfg.hidden) and int(d["layers.3.mlp.rows"]) == 350
+
+
+@pytest.mark.gpu
+def test_warmup_captures_graphs_and_memory_plan():
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    eng = Engine.synthetic(ModelConfig.tiny(), EngineOptions(slots=2, slot_tokens=512, use_graphs=True, save_gdn=True), device="cuda:0",
+                           exact=True, ple_rows=4096)
+    plan = eng.memory_plan()
+    assert plan["weights_gb"] > 0 and plan["state_gb"] > 0 and plan["device_free_gb"] > 2
+    n = eng.warmup(max_rows=4)
+    assert n >= 8 + 1                       # 4 plain + 4 verification graphs + the chained step (+ MTP passes)
+    assert eng.slot[0].n == 0
+    before = len(eng.dm.graphs)
+    ref = Engine.synthetic(ModelConfig.tiny(), EngineOptions(slots=1, slot_tokens=512, use_graphs=False), device="cuda:0", exact=True,
+                           ple_rows=4096)
+    toks = [(i * 9 + 2) % 900 + 5 for i in range(30)]
+    a = [eng.decode([0], [t])[0] for t in toks]
+    b = [ref.decode([0], [t])[0] for t in toks]
+    assert a == b and len(eng.dm.graphs) == before          # no capture in front of the "user", same tokens as without graphs

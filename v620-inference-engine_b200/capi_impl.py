@@ -4,7 +4,8 @@ Every method takes the C call's scalars and the *addresses* of its buffers, read
 ctypes and forwards to the :class:`~qwb200.session.session.Session`.  ``open`` builds the engine from
 the options JSON: ``model_dir`` (a checkpoint) or ``synthetic`` (``"full" | "slice2" | "tiny"``, random
 weights), ``ple_dir`` or a synthetic table, ``slots`` (a list of capacities; the largest is used for all
-slots), ``prefill_chunk``, ``host_cache_gb``, ``disk_cache_dir``, ``disk_cache_gb``, ``devices``.
+slots), ``prefill_chunk``, ``host_cache_gb``, ``disk_cache_dir``, ``disk_cache_gb``, ``devices``, ``weight_cache_dir``,
+``warmup`` (capture every graph at start, default on), ``vision``.
 """
 from __future__ import annotations
 
@@ -255,6 +256,9 @@ def open(options_json: str) -> CApi:
         cfg = {"full": ModelConfig.full, "slice2": ModelConfig.slice2, "tiny": ModelConfig.tiny}[kind]()
         eng = Engine.synthetic(cfg, opts, device=dev, exact=(kind != "full"), ple_rows=int(o.get("ple_rows", 1 << 16)),
                                ple_pinned=torch.cuda.is_available())
+    if o.get("warmup", True) and torch.cuda.is_available():
+        n_graphs = eng.warmup(max_rows=int(o.get("warmup_rows", 8)))
+        print(f"engine: {n_graphs} graphs captured; memory plan {eng.memory_plan()}", file=sys.stderr, flush=True)
     ses = Session(eng, host_cache_bytes=int(float(o.get("host_cache_gb", 8)) * (1 << 30)),
                   disk_cache_dir=o.get("disk_cache_dir") or None,
                   disk_cache_bytes=int(float(o.get("disk_cache_gb", 0)) * (1 << 30)),

@@ -134,6 +134,49 @@ class Engine:
             e.dm.set_ple_table(table)
         return e
 
+    # ---- start-up: memory plan and graph warm-up
+    def memory_plan(self) -> Dict[str, float]:
+        """GB this rank holds (weights, KV + recurrent state, step buffers) and what the device has; raises when the plan
+        does not fit with 2 GB to spare (the reference checks its VRAM plan before loading: src/engine/engine.hip:125-163)."""
+        dm = self.dm
+        gb = lambda ts: sum(t.numel() * t.element_size() for t in ts) / 2**30
+        state = gb(dm.k_dev + dm.v_dev + dm.ck + dm.raw_ring + dm.gdn_S + dm.gdn_ring + [dm.ple_ring])
+        plan = {"weights_gb": dm.weight_bytes() / 2**30, "state_gb": state, "buffers_gb": gb(list(dm.buf.values())),
+                "host_kv_gb": gb((dm.k_host or []) + (dm.v_host or []))}
+        free, total = torch.cuda.mem_get_info(dm.dev)
+        plan["device_total_gb"], plan["device_free_gb"] = total / 2**30, free / 2**30
+        if free < 2 * 2**30:
+            raise RuntimeError(f"memory plan leaves {free / 2**30:.1f} GB free on {dm.dev}: {plan}")
+        return plan
+
+    def warmup(self, max_rows: int = 8, spec: bool = True) -> int:
+        """Capture every graph a request can need before the first request arrives: plain steps of 1..max_rows rows, the
+        verification form of the same (GDN state saves, hidden states kept) and the chained MTP pass; returns the number of
+        graphs held.  Runs on slot 0, which is reset afterwards (reference: src/engine/engine.hip:276-312 captures every
+        graph at start for the same reason: a capture in front of a user costs tens of milliseconds)."""
+        if not self.opts.use_graphs:
+            return 0
+        self.reset(0)
+        kinds = [0]
+        if spec and self.opts.save_gdn:
+            kinds.append(DM.FLAG_SAVE_GDN | DM.FLAG_KEEP_HIDDEN)
+        for flags in kinds:
+            for m in range(1, max_rows + 1):
+                base = self.slot[0].n
+                toks = [5 + i for i in range(m)]
+                for _ in range(2):          # first call captures (and runs once), second call replays
+                    self.dm.step(toks, [0] * m, list(range(base, base + m)), self._ctx3(0, toks), flags=flags, graph=True)
+        if self.merge_argmax is None:
+            self.decode_chain(0, 5, 2)
+        if spec and self.mtp and self.opts.save_gdn:
+            self.reset(0)
+            self.prefill(0, [5, 6, 7, 8])
+            self.generate_greedy(0, 9, 4, k=2)
+        torch.cuda.synchronize(self.dm.dev)
+        self.dm.check_error()
+        self.reset(0)
+        return len(self.dm.graphs)
+
     # ---- slots
     def reset(self, slot: int):
         self.slot[slot] = Slot()

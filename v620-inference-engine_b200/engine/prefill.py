@@ -33,6 +33,7 @@ class Prefiller:
         if dm.sc.ranks != 1:
             raise NotImplementedError("token-major prefill runs on one GPU; multi-rank prefill uses the row-batched path")
         self.dm, self.T, self.attn_rows = dm, chunk, attn_rows
+        self.on_block_input = None      # optional hook(layer, "attn" | "mlp", block input [T, hidden] bf16): calibration
         self.lib = dm.lib
         c, sc, dev = dm.cfg, dm.sc, dm.dev
         T = chunk
@@ -145,8 +146,12 @@ class Prefiller:
                                          c.ple_dilation, _p(b["ple_gv"]), _p(b["ple_nc"]), _p(dm.ple_ring), _p(b["X"]), T,
                                          rp("slot"), rp("pos"), rp("run_start"), rp("run_len"), s), "ple_apply")
             self.mix(lw["attn_hc"], T, pend, inj_prev, inj_attn, c.hc)
+            if self.on_block_input is not None:
+                self.on_block_input(li, "attn", b["bin"][:T])
             self.attn_block(lw, T, rp, max_groups, c.qsa_index(li) if lw["is_qsa"] else c.gdn_index(li))
             self.mix(lw["mlp_hc"], T, b["out_a"], inj_attn, inj_mlp, c.hc)
+            if self.on_block_input is not None:
+                self.on_block_input(li, "mlp", b["bin"][:T])
             self.moe(lw, T)
             pend, inj_prev = b["out_b"], inj_mlp
         gw = dm.globals_w
