@@ -34,6 +34,7 @@ class Prefiller:
             raise NotImplementedError("token-major prefill runs on one GPU; multi-rank prefill uses the row-batched path")
         self.dm, self.T, self.attn_rows = dm, chunk, attn_rows
         self.on_block_input = None      # optional hook(layer, "attn" | "mlp", block input [T, hidden] bf16): calibration
+        self.layer_limit = None         # run only the first n layers, then the final mixer (depth diagnostics)
         self.lib = dm.lib
         c, sc, dev = dm.cfg, dm.sc, dm.dev
         T = chunk
@@ -126,7 +127,7 @@ class Prefiller:
         pend, inj_prev = None, None
         inj_attn, inj_mlp = b["inj_a"], b["inj_b"]
         max_groups = (base + T) // c.idx_ratio
-        for li in range(c.n_layers):
+        for li in range(c.n_layers if self.layer_limit is None else min(c.n_layers, int(self.layer_limit))):
             lw = dm.layers_w[li]
             if li == c.ple_layer and dm.model.ple.enabled:
                 if pend is not None:

@@ -85,3 +85,58 @@ def random_q4(out: int, inn: int, *, std: float = 0.02, generator=None, device="
     # uniform nibble 0..15 -> value -8..7 has std sqrt((16^2-1)/12) = 4.61
     scale = torch.full((out, inn // QGROUP), std / 4.61, dtype=scale_dtype, device=device)
     return packed, scale
+
+
+def _pack_q4(q: torch.Tensor) -> torch.Tensor:
+    """int values in [-8, 7] ``[out, in]`` -> checkpoint-order words ``[out, in/8]``."""
+    out, inn = q.shape
+    n = (q.to(torch.int64) + 8).reshape(out, inn // 8, 8)
+    shifts = torch.arange(8, dtype=torch.int64, device=q.device) * 4
+    packed = (n << shifts).sum(dim=-1)
+    return torch.where(packed >= 2**31, packed - 2**32, packed).to(torch.int32)
+
+
+def quantize_q4_gptq(w: torch.Tensor, hessian: torch.Tensor, group: int = QGROUP, *, damp: float = 0.01, block: int = 128,
+                     scale_dtype=torch.float16):
+    """GPTQ form of :func:`quantize_q4`: the same format (amax/7 group scales, values -8..7), but every column's rounding
+    error is pushed onto the columns not yet quantised through the inverse of ``hessian`` = X^T X of the matrix's input
+    (as accumulated by ``engine.calibrate.Calibrator``), so that ``||X W^T - X Wq^T||`` shrinks instead of ``||W - Wq||``.
+    A group's scale is taken when its first column is reached, from the weights as updated so far.
+    (The reference's tools/gptq_int8.py:60-125 does this for its int8 g32 decode copies; here it targets the q4 g128
+    expert / MTP format the kernels read.)  Returns (packed, scale) like ``quantize_q4``."""
+    out, inn = w.shape
+    assert inn % group == 0 and hessian.shape == (inn, inn)
+    W = w.double().clone()
+    H = hessian.double().clone()
+    dead = torch.diagonal(H) <= 0
+    H[dead, dead] = 1.0
+    W[:, dead] = 0.0
+    H += torch.eye(inn, dtype=H.dtype, device=H.device) * (damp * torch.diagonal(H).mean())
+    L = torch.linalg.cholesky(H)
+    U = torch.linalg.cholesky(torch.cholesky_inverse(L), upper=True)       # upper factor of H^-1: row i drives columns >= i
+    Q = torch.zeros(out, inn, dtype=torch.int32, device=w.device)
+    scale = torch.zeros(out, inn // group, dtype=scale_dtype, device=w.device)
+    sc = inv = None
+    for b0 in range(0, inn, block):
+        b1 = min(inn, b0 + block)
+        Wb = W[:, b0:b1].clone()
+        Eb = torch.zeros_like(Wb)
+        Ub = U[b0:b1, b0:b1]
+        for i in range(b1 - b0):
+            col = b0 + i
+            if col % group == 0:
+                # the columns of this group inside the block carry the updates of everything before them
+                g1 = min(col + group, b1)
+                cur = torch.cat([Wb[:, i:i + (g1 - col)], W[:, g1:col + group]], dim=1) if g1 < col + group else Wb[:, i:i + group]
+                s = (cur.abs().amax(dim=1) / 7.0).to(scale_dtype)
+                scale[:, col // group] = s
+                sc = s.double()
+                inv = torch.where(sc > 0, 1.0 / sc, torch.zeros_like(sc))
+            x = Wb[:, i]
+            q = torch.round(x * inv).clamp_(-8, 7)
+            Q[:, col] = q.to(torch.int32)
+            e = (x - q * sc) / Ub[i, i]
+            Wb[:, i:] -= e.unsqueeze(1) * Ub[i, i:].unsqueeze(0)
+            Eb[:, i] = e
+        W[:, b1:] -= Eb @ U[b0:b1, b1:]
+    return _pack_q4(Q), scale
