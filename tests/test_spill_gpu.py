@@ -29,3 +29,66 @@ def test_spilled_slot_equals_resident_slot():
     assert int((spilled.page_table_host[0, :3] >= spilled.n_dev_pages).sum()) >= 2      # pages 1 and 2 of the slot sit in host memory
     assert torch.equal(outs[0][0], outs[1][0])
     assert outs[0][1] == outs[1][1]
+
+
+def _run(opts, toks, n_new, seed=3):
+    from qwb200.engine.engine import Engine
+    from qwb200.models.config import ModelConfig
+    eng = Engine.synthetic(ModelConfig.tiny(), opts, device="cuda:0", exact=True, ple_rows=4096, seed=seed)
+    out = []
+    for prompt in toks:                              # several prompts one after the other in slot 0: the slot is reused
+        eng.reset(0)
+        lg = eng.prefill(0, prompt).clone()
+        t = int(lg.argmax())
+        seq = [t]
+        for _ in range(n_new):
+            t = eng.decode([0], [t])[0]
+            seq.append(t)
+        out.append((lg, seq))
+    torch.cuda.synchronize()
+    eng.dm.check_error()
+    return eng, out
+
+
+@pytest.mark.parametrize("cache_mb,graphs", [(256, False), (256, True), (0, False)])
+def test_spill_cache_hits_and_stays_exact(cache_mb, graphs):
+    """The device cache in front of the host pages serves repeated reads (hits counted), leaves the results bit-exact,
+    and a slot that is filled again with other tokens does not see rows of the earlier request."""
+    from qwb200.engine.engine import EngineOptions
+    from qwb200.utils import settings
+    prompts = [[(i * 13 + 7) % 900 + 5 for i in range(700)], [(i * 29 + 3) % 900 + 5 for i in range(650)]]
+    old = settings.get()
+    try:
+        settings.set_current(settings.Settings.from_env({}, spill_cache_mb=cache_mb, spill_cache_stats=True))
+        res, want = _run(EngineOptions(slots=1, slot_tokens=1024, use_graphs=graphs, prefill_chunk=0), prompts, 12)
+        assert res.dm.spill_cache is None
+        sp, got = _run(EngineOptions(slots=1, slot_tokens=1024, use_graphs=graphs, prefill_chunk=0, dev_pages=1, host_pages=3), prompts, 12)
+    finally:
+        settings.set_current(old)
+    for (lw, sw), (lg, sg) in zip(want, got):
+        assert torch.equal(lw, lg) and sw == sg
+    st = sp.dm.spill_cache_stats()
+    if cache_mb == 0:
+        assert sp.dm.spill_cache is None and st is None
+        return
+    hits, misses = st
+    assert misses > 0 and hits > 0                      # later steps re-read rows that earlier steps fetched
+    assert int(sp.dm.spill_cache["ctl"][0]) == 0        # the fill kernel emptied the miss list
+    sp.dm.spill_cache_clear()
+    assert int(sp.dm.spill_cache["tags"].abs().sum()) == 0
+
+
+def test_spill_cache_with_conflicts_stays_exact():
+    """A cache far smaller than the working set (entries evict each other all the time) changes nothing but speed."""
+    from qwb200.engine.engine import EngineOptions
+    from qwb200.utils import settings
+    prompts = [[(i * 17 + 1) % 900 + 5 for i in range(700)]]
+    old = settings.get()
+    try:
+        settings.set_current(settings.Settings.from_env({}, spill_cache_mb=1, spill_cache_stats=True))
+        _, want = _run(EngineOptions(slots=1, slot_tokens=1024, use_graphs=False, prefill_chunk=0), prompts, 8)
+        sp, got = _run(EngineOptions(slots=1, slot_tokens=1024, use_graphs=False, prefill_chunk=0, dev_pages=1, host_pages=3), prompts, 8)
+        assert sp.dm.spill_cache["entries"] >= 64
+    finally:
+        settings.set_current(old)
+    assert torch.equal(want[0][0], got[0][0]) and want[0][1] == got[0][1]

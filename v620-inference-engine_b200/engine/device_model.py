@@ -27,6 +27,7 @@ RAW_RING = 16
 GDN_RING = 16
 PLE_RING = 32
 MAX_ROWS = 32
+_SPILL_KEEPALIVE: list = []      # spill-cache buffers of every model made in this process (see _alloc_spill_cache)
 PLE_LAYOUT_ID = {"f8": 0, "bf16": 1, "int8": 2, "int4": 3}
 
 FLAG_SAVE_GDN = 1
@@ -64,6 +65,7 @@ class DeviceModel:
         self.steps_run = 0
         self._fill_dims()
         self._alloc_state()
+        self._alloc_spill_cache(int(_settings.get().spill_cache_mb), bool(_settings.get().spill_cache_stats))
         self._alloc_buffers(save_gdn)
         self._alloc_rows()
         qlib.check(self.lib.qwk_rope_init(C.c_double(cfg.rope_theta), cfg.rope_dim), "rope_init")
@@ -152,6 +154,43 @@ class DeviceModel:
         for t in self.gdn_S + self.gdn_ring + self.raw_ring:
             t[slot].zero_()
         self.ple_ring[slot].zero_()
+
+    # ------------------------------------------------------------------ cache of host KV rows
+    def _alloc_spill_cache(self, mb: int, stats: bool):
+        """Direct-mapped device cache in front of the pinned host KV pages (one entry = K row + V row of one token of
+        one layer; reference: SpillCache in src/kernels/types.hpp:48-70, sized by QW_SPILL_CACHE_MB).  The kernels
+        find it through a process-wide pointer set, so the newest model with host pages owns it; the buffers of
+        earlier models stay referenced, because captured graphs of theirs may still name them."""
+        self.spill_cache = None
+        if not self.n_host_pages or mb <= 0:
+            self.lib.qwk_set_spill_cache(None, None, None, None, None, 0, 0)
+            return
+        row = self.sc.kvh_l * self.cfg.head_dim
+        entries = 1
+        while entries * 2 * (4 * row + 8) <= mb << 20:
+            entries *= 2
+        z = lambda n, dt: torch.zeros(n, dtype=dt, device=self.dev)
+        sc_ = {"tags": z(entries, torch.int64), "rows": z(entries * 2 * row, torch.bfloat16), "miss": z(1 << 16, torch.int64),
+               "ctl": z(2, torch.int32), "stats": z(2, torch.int64) if stats else None, "entries": entries}
+        rc = self.lib.qwk_set_spill_cache(sc_["tags"].data_ptr(), sc_["rows"].data_ptr(), sc_["miss"].data_ptr(), sc_["ctl"].data_ptr(),
+                                          sc_["stats"].data_ptr() if stats else None, entries, 1 << 16)
+        if rc != 0:
+            raise RuntimeError(f"qwk_set_spill_cache failed: {rc}")
+        self.spill_cache = sc_
+        _SPILL_KEEPALIVE.append(sc_)
+
+    def spill_cache_clear(self):
+        """Forget every cached row: for writers of host pages that are not kernels of the step (state import, slot copy)."""
+        if self.spill_cache is not None:
+            self.spill_cache["tags"].zero_()
+            self.spill_cache["ctl"].zero_()
+
+    def spill_cache_stats(self):
+        """(hits, misses) of host-row reads since the model was made; None without QW_SPILL_CACHE_STATS."""
+        if self.spill_cache is None or self.spill_cache["stats"] is None:
+            return None
+        h, m = self.spill_cache["stats"].tolist()
+        return int(h), int(m)
 
     # ------------------------------------------------------------------ buffers
     def _alloc_buffers(self, save_gdn: bool):

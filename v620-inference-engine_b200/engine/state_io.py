@@ -72,6 +72,7 @@ class StateIO:
                 n = dst.numel()
                 dst.copy_(t[off:off + n].view(dst.shape).to(dst.device))
                 off += n
+        self.dm.spill_cache_clear()         # the page may live in host memory: cached copies of its rows are stale now
 
     # ---- recurrent state
     def _recurrent_tensors(self, slot: int) -> List[torch.Tensor]:
@@ -113,5 +114,6 @@ class StateIO:
                 kd.copy_(ks)
                 vd.copy_(vs)
                 cd.copy_(cs)
+        dm.spill_cache_clear()
         for d, s in zip(self._recurrent_tensors(dst), self._recurrent_tensors(src)):
             d.copy_(s)

@@ -47,7 +47,99 @@ __device__ __forceinline__ bf16 *v_row(const KvPool &kv, int slot, int pos) {
     return (host ? kv.v_host : kv.v_dev) + o;
 }
 
+// Device-memory cache in front of the host KV pages: direct mapped, one entry = the K row and the V row of one
+// token of one layer, tagged with the host address of the K row.  The attention kernel looks a host row up, reads the
+// cached copy on a hit and the host row itself on a miss (then also lists the row); the fill kernel that runs right
+// after the attention kernels copies the listed rows in.  A kernel that writes a host row drops its entry.
+// (Role of the reference's SpillCache, src/kernels/types.hpp:48-70, and spill_cache_fill, src/kernels/qsa.hip:247-273.)
+struct SpillCache {
+    unsigned long long *tags;    // [mask + 1]: host address of the cached K row; 0 = empty, 1 = being filled
+    bf16 *rows;                  // [mask + 1][2][row]
+    unsigned long long *miss;    // [miss_cap] K-row addresses that missed since the last fill
+    unsigned *ctl;               // [0] number of misses listed (may run past miss_cap), [1] fill ticket
+    unsigned long long *stats;   // [0] hits, [1] misses; nullptr = not counted
+    unsigned mask;
+    int miss_cap;
+};
+__device__ __forceinline__ unsigned spill_index(unsigned long long key, unsigned mask) {
+    return (unsigned)(((key >> 9) * 0x9E3779B97F4A7C15ull) >> 40) & mask;
+}
+
+// K and V row of (slot, pos) for reading.  `record`: this thread lists a miss (one thread per token).
+__device__ __forceinline__ void kv_rows_read(const KvPool &kv, const SpillCache &sc, int slot, int pos, bool record,
+                                             const bf16 *&kp, const bf16 *&vp) {
+    bool host;
+    const long long o = kv_off(kv, slot, pos, host);
+    if (!host) {
+        kp = kv.k_dev + o;
+        vp = kv.v_dev + o;
+        return;
+    }
+    kp = kv.k_host + o;
+    vp = kv.v_host + o;
+    if (sc.tags == nullptr) return;
+    const unsigned long long key = reinterpret_cast<unsigned long long>(kp);
+    const unsigned idx = spill_index(key, sc.mask);
+    const bool hit = __ldcg(sc.tags + idx) == key;
+    if (hit) {
+        kp = sc.rows + (long long)idx * 2 * kv.row;
+        vp = kp + kv.row;
+    } else if (record) {
+        const unsigned n = atomicAdd(sc.ctl, 1u);
+        if (n < (unsigned)sc.miss_cap) sc.miss[n] = key;
+    }
+    if (record && sc.stats) atomicAdd(sc.stats + (hit ? 0 : 1), 1ull);
+}
+// A host row is about to be rewritten: its cached copy is dropped.
+__device__ __forceinline__ void spill_drop(const KvPool &kv, const SpillCache &sc, int slot, int pos) {
+    if (sc.tags == nullptr) return;
+    bool host;
+    const long long o = kv_off(kv, slot, pos, host);
+    if (!host) return;
+    const unsigned long long key = reinterpret_cast<unsigned long long>(kv.k_host + o);
+    const unsigned idx = spill_index(key, sc.mask);
+    if (__ldcg(sc.tags + idx) == key) sc.tags[idx] = 0ull;
+}
+
+// One warp per listed miss.  The entry is claimed by exchanging its tag with 1: a warp that finds 1 there leaves the
+// entry to the warp that is filling it, a warp that finds its own key puts it back.  The last block resets the list.
+__global__ void __launch_bounds__(256) spill_cache_fill_kernel(SpillCache sc, const bf16 *k_host, const bf16 *v_host, int row) {
+    const int lane = threadIdx.x & 31;
+    const unsigned n = min(__ldcg(sc.ctl), (unsigned)sc.miss_cap);
+    const unsigned nw = gridDim.x * (blockDim.x >> 5);
+    for (unsigned i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += nw) {
+        const unsigned long long key = __ldcg(sc.miss + i);
+        const unsigned idx = spill_index(key, sc.mask);
+        unsigned long long prev = 0ull;
+        if (lane == 0) prev = atomicExch(sc.tags + idx, 1ull);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == 1ull) continue;
+        if (prev != key) {
+            const uint4 *ks = reinterpret_cast<const uint4 *>(key);
+            const uint4 *vs = reinterpret_cast<const uint4 *>(v_host + (reinterpret_cast<const bf16 *>(key) - k_host));
+            uint4 *dst = reinterpret_cast<uint4 *>(sc.rows + (long long)idx * 2 * row);
+            const int n16 = row >> 3;
+            for (int j = lane; j < n16; j += 32) {
+                dst[j] = ks[j];
+                dst[n16 + j] = vs[j];
+            }
+            __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) atomicExch(sc.tags + idx, key);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(sc.ctl + 1, 1u) == gridDim.x - 1) {
+            sc.ctl[0] = 0u;
+            sc.ctl[1] = 0u;
+        }
+    }
+}
+
 struct QsaPrepArgs {
+    SpillCache sc;
     const float *proj;
     int ld_proj;
     int QL, KVL, IH;
@@ -112,6 +204,7 @@ __global__ void __launch_bounds__(256) qsa_prep_kernel(QsaPrepArgs a) {
         const int j = hb - a.QL;
         fill_cs(cs, pos);
         const float v = norm_rope<HD>(row[off_k + j * HD + d], sm, scratch, cs, a.kn1, a.eps, d);
+        if (j == 0 && d == 0) spill_drop(a.kv, a.sc, slot, pos);
         k_row(a.kv, slot, pos)[j * HD + d] = __float2bfloat16(v);
     } else if (hb < a.QL + 2 * a.KVL) {                // value head
         const int j = hb - a.QL - a.KVL;
@@ -310,6 +403,7 @@ __global__ void __launch_bounds__(1024) qsa_select_kernel(const float *scores, i
 // list entries for HT query heads that share one KV head.
 // ------------------------------------------------------------------------------------------
 struct QsaAttendArgs {
+    SpillCache sc;
     const float *q;          // [M][QL][256]
     int QL, KVL;
     Rows rows;
@@ -357,8 +451,10 @@ __global__ void __launch_bounds__(256) qsa_attend_kernel(QsaAttendArgs a) {
         const int t = sp * 64 + it * 8 + warp;
         if (t >= count) break;                 // warp-uniform
         const int tok = list_token(t, dense, sel, a.ratio, a.topk, nb);
-        const uint4 kk = *(reinterpret_cast<const uint4 *>(k_row(a.kv, slot, tok) + kvh * HD) + lane);
-        const uint4 vv = *(reinterpret_cast<const uint4 *>(v_row(a.kv, slot, tok) + kvh * HD) + lane);
+        const bf16 *kp, *vp;
+        kv_rows_read(a.kv, a.sc, slot, tok, blockIdx.z == 0 && lane == 0, kp, vp);
+        const uint4 kk = *(reinterpret_cast<const uint4 *>(kp + kvh * HD) + lane);
+        const uint4 vv = *(reinterpret_cast<const uint4 *>(vp + kvh * HD) + lane);
         const float kf[8] = {bf16_lo(kk.x), bf16_hi(kk.x), bf16_lo(kk.y), bf16_hi(kk.y),
                              bf16_lo(kk.z), bf16_hi(kk.z), bf16_lo(kk.w), bf16_hi(kk.w)};
         const float vf[8] = {bf16_lo(vv.x), bf16_hi(vv.x), bf16_lo(vv.y), bf16_hi(vv.y),
@@ -441,6 +537,8 @@ QW_API int qwk_rope_init(double theta, int rope_dim) {
     return 0;
 }
 
+static SpillCache g_spill{};          // process-wide; all-null = no cache
+
 static KvPool make_pool(void *k_dev, void *v_dev, void *k_host, void *v_host, int n_dev_pages, const int *page_table,
                         int max_pages, int row) {
     KvPool p;
@@ -460,6 +558,7 @@ QW_API int qwk_qsa_prep(const float *proj, int ld_proj, int QL, int KVL, int IH,
     a.qn1 = qn1; a.kn1 = kn1; a.iqn1 = iqn1; a.ikn1 = ikn1;
     a.rows = Rows{M, slot, pos, run_start, run_len};
     a.kv = make_pool(k_dev, v_dev, k_host, v_host, n_dev_pages, page_table, max_pages, KVL * HD);
+    a.sc = k_host ? g_spill : SpillCache{};
     a.q = q; a.iq = iq; a.raw_ring = raw_ring; a.ck = (bf16 *)ck; a.ck_cap = ck_cap; a.ratio = ratio; a.eps = eps;
     a.ring_inline = M <= RAW_RING - ratio ? 1 : 0;
     dim3 grid(M, QL + 2 * KVL + IH + 1);
@@ -492,6 +591,7 @@ QW_API int qwk_qsa_attend(const float *q, int QL, int KVL, int M, const int *slo
     QsaAttendArgs a;
     a.q = q; a.QL = QL; a.KVL = KVL; a.rows = Rows{M, slot, pos, nullptr, nullptr};
     a.kv = make_pool(k_dev, v_dev, k_host, v_host, n_dev_pages, page_table, max_pages, KVL * HD);
+    a.sc = k_host ? g_spill : SpillCache{};
     a.sel = sel; a.sel_n = sel_n; a.topk = topk; a.ratio = ratio; a.nsplit = nsplit;
     a.pm = pm; a.pl = pl; a.pacc = pacc;
     const int per_kv = QL / KVL;
@@ -503,5 +603,23 @@ QW_API int qwk_qsa_attend(const float *q, int QL, int KVL, int M, const int *slo
     else launch_pdl(qsa_attend_kernel<1>, grid, dim3(256), 0, s, a);
     dim3 g2(M, QL);
     launch_pdl(qsa_combine_kernel, g2, dim3(256), 0, s, (const float *)pm, (const float *)pl, (const float *)pacc, nsplit, proj, ld_proj, QL, (bf16 *)o);
+    // plain launch: it starts when both kernels above have finished, so nothing reads the cache while entries change
+    if (a.sc.tags) spill_cache_fill_kernel<<<64, 256, 0, s>>>(a.sc, (const bf16 *)k_host, (const bf16 *)v_host, KVL * HD);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// Installs (entries > 0, a power of two) or removes (entries == 0) the cache of host KV rows.  tags: entries x u64,
+// zeroed; rows: entries x 2 x row bf16; miss: miss_cap x u64; ctl: 2 x u32, zeroed; stats: 2 x u64 or null.
+QW_API int qwk_set_spill_cache(void *tags, void *rows, void *miss, void *ctl, void *stats, int entries, int miss_cap) {
+    if (entries == 0) {
+        g_spill = SpillCache{};
+        return 0;
+    }
+    if (entries < 0 || (entries & (entries - 1)) || !tags || !rows || !miss || !ctl || miss_cap <= 0) return -1;
+    g_spill.tags = (unsigned long long *)tags; g_spill.rows = (bf16 *)rows; g_spill.miss = (unsigned long long *)miss;
+    g_spill.ctl = (unsigned *)ctl; g_spill.stats = (unsigned long long *)stats; g_spill.mask = (unsigned)entries - 1u;
+    g_spill.miss_cap = miss_cap;
+    return 0;
+}
+// 1 when launches that get host pages also launch the fill kernel (launch accounting).
+QW_API int qwk_spill_cache_active(int unused) { return (void)unused, g_spill.tags ? 1 : 0; }

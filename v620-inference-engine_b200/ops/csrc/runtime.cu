@@ -265,7 +265,7 @@ void qsa_block(Ctx &c, const QwLayer &L) {
     QW_TRYN((r.max_groups > d.idx_topk ? 1 : 0), qwk_qsa_scores(b.iq, d.IH, st.ck[qi], d.ck_cap, M, r.slot, r.pos, d.idx_ratio, d.idx_topk, b.scores,
                           d.score_cap, r.max_groups, c.s));
     QW_TRYN(1, qwk_qsa_select(b.scores, d.score_cap, M, r.pos, d.idx_ratio, d.idx_topk, b.sel, b.sel_n, c.s));
-    QW_TRYN(2, qwk_qsa_attend(b.q, d.QL, d.KVL, M, r.slot, r.pos, st.k_dev[qi], st.v_dev[qi],
+    QW_TRYN(2 + (st.k_host ? qwk_spill_cache_active(0) : 0), qwk_qsa_attend(b.q, d.QL, d.KVL, M, r.slot, r.pos, st.k_dev[qi], st.v_dev[qi],
                           st.k_host ? st.k_host[qi] : nullptr, st.v_host ? st.v_host[qi] : nullptr, d.n_dev_pages,
                           st.page_table, d.max_pages, b.sel, b.sel_n, d.idx_topk, d.idx_ratio, d.nsplit, b.pm, b.pl,
                           b.pacc, b.proj, d.proj_qsa, b.o, c.s));

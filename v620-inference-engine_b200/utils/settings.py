@@ -45,7 +45,8 @@ class Settings:
     slots: List[int] = field(default_factory=lambda: [131072, 32768, 32768, 32768])      # QW_SLOTS
     slot_max_tokens: int = 0            # QW_SLOT_MAX_TOKENS (with spill)
     kv_spill: bool = False              # QW_KV_SPILL / QW_SPILL / QW_SLOT_SPILL
-    spill_cache_mb: int = 256           # QW_SPILL_CACHE_MB
+    spill_cache_mb: int = 256           # QW_SPILL_CACHE_MB: device cache in front of the host KV pages (0 = none)
+    spill_cache_stats: bool = False     # QW_SPILL_CACHE_STATS: count hits and misses
     spill_policy: str = "auto"          # QW_SPILL_POLICY: auto | bind | preferred | interleave | process
     prefill_chunk: int = 4096           # QW_PREFILL_CHUNK
     prefill_piece: int = 2048           # QW_PREFILL_PIECE
@@ -85,7 +86,7 @@ class Settings:
                "QW_INT8_DIR", "QW_INT8_DUMP", "QW_INT8_EXPERTS", "QW_INT8_SKIP", "QW_KV_PAIRS", "QW_KV_PAIR_CHECK", "QW_LOAD_SERIAL",
                "QW_MOE_PAIR_MAX", "QW_NO_SPLIT", "QW_POOL_ARENA", "QW_POOL_PREPIN", "QW_POOL_SERIAL", "QW_PREFILL_BATCH",
                "QW_PREFILL_PIPELINE", "QW_RESERVE_AHEAD", "QW_SHARE_MIN", "QW_SHARE_WAIT", "QW_SLOT_MOVE_IDLE_S", "QW_SNAP_SYSTEM_MIN",
-               "QW_SPEC_BASE", "QW_SPEC_COST", "QW_SPEC_MIXED", "QW_SPILL_CACHE_STATS", "QW_SPILL_LOCALITY", "QW_SPILL_MARGIN_GB",
+               "QW_SPEC_BASE", "QW_SPEC_COST", "QW_SPEC_MIXED", "QW_SPILL_LOCALITY", "QW_SPILL_MARGIN_GB",
                "QW_SPILL_NC", "QW_SPILL_NUMA", "QW_SPILL_STAGE", "QW_VIT_GEMM_ATTN", "QW_MOE_MMA", "QW_SKIP"}
 
     def validate(self) -> "Settings":
