@@ -9,6 +9,10 @@ def _dev():
     return torch.device("cuda:0")
 
 
+def rel(a, b):
+    return (a - b).abs().max() / b.abs().max()
+
+
 @pytest.mark.parametrize("N,K", [(324, 2560), (512 + 1281, 2560), (2560, 6144), (16444, 2560), (40, 64)])
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 16, 32])
 def test_gemv_bf16_matches_fp32_and_rows_are_batch_invariant(N, K, M):
@@ -101,3 +105,62 @@ def test_moe_pair_kernels_match_oracle():
             assert err < 2e-2, (mask, float(err))
     finally:
         L.qwk_set_moe_mma(12)
+
+
+@pytest.mark.parametrize("M", [64, 200, 1000])
+def test_gdn_chunked_scan_matches_sequential_fp32(M):
+    """The chunked (tensor-core) delta-rule scan against the token-by-token recurrence in PyTorch fp32 and
+    against the row-by-row kernel: outputs, and the state it leaves in the slot."""
+    import ctypes as C
+    from qwb200.models.gdn_chunked import scan_sequential
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    dev = _dev()
+    g = torch.Generator(device="cuda").manual_seed(M)
+    KL, VL, D, slots, slot = 2, 4, 128, 3, 1
+    qkv_l = (2 * KL + VL) * D
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    q = torch.nn.functional.normalize(rn(M, KL, D), dim=-1) * D ** -0.5
+    k = torch.nn.functional.normalize(rn(M, KL, D), dim=-1)
+    v = rn(M, VL, D)
+    qkv = torch.cat([q.reshape(M, -1), k.reshape(M, -1), v.reshape(M, -1)], 1).contiguous()
+    decay = torch.exp(-torch.rand(M, VL, generator=g, device=dev) * 0.2).contiguous()
+    beta = torch.sigmoid(rn(M, VL)).contiguous()
+    ld = qkv_l + VL * D + 2 * VL
+    proj = rn(M, ld).contiguous()
+    S0 = (rn(slots, VL, D, D) * 0.1).contiguous()
+    nw = (1 + 0.1 * rn(D)).contiguous()
+    eps = 1e-6
+    # fp32 oracle
+    want_o = torch.empty(M, VL, D, device=dev)
+    want_S = S0.clone()
+    for h in range(VL):
+        kh = h // (VL // KL)
+        o, S = scan_sequential(q[:, kh].cpu(), k[:, kh].cpu(), v[:, h].cpu(), decay[:, h].cpu(), beta[:, h].cpu(), S0[slot, h].cpu())
+        z = proj[:, qkv_l + h * D: qkv_l + (h + 1) * D].cpu()
+        want_o[:, h] = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * nw.cpu() * torch.sigmoid(z)).to(dev)
+        want_S[slot, h] = S.to(dev)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rows = torch.zeros(4, M, dtype=torch.int32, device=dev)
+    rows[0] = slot
+    rows[1] = torch.arange(M, device=dev)
+    rows[3, 0] = M
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    nch = (M + 63) // 64
+    scratch = torch.zeros(nch * VL * (2 * 64 * 128 + 64 * 64 + 64) + M * VL * 128, device=dev)
+    S_c = S0.clone()
+    o_c = torch.zeros(M, VL * D, dtype=torch.bfloat16, device=dev)
+    rc = L.qwk_gdn_scan_chunked(P(qkv), P(decay), P(beta), P(proj), ld, P(S_c), P(nw), KL, VL, M, P(rows[0]), P(scratch),
+                                P(o_c), C.c_float(eps), s)
+    assert rc == 0
+    S_s = S0.clone()
+    o_s = torch.zeros(M, VL * D, dtype=torch.bfloat16, device=dev)
+    rc = L.qwk_gdn_scan(P(qkv), P(decay), P(beta), P(proj), ld, P(S_s), None, P(nw), KL, VL, M, P(rows[0]), P(rows[1]),
+                        P(rows[2]), P(rows[3]), P(o_s), C.c_float(eps), s)
+    assert rc == 0
+    torch.cuda.synchronize()
+    w = want_o.reshape(M, -1)
+    assert rel(o_s.float(), w) < 1e-2                   # the row-by-row kernel (bf16 output rounding)
+    assert rel(o_c.float(), w) < 1e-2, float(rel(o_c.float(), w))
+    assert rel(S_c[slot], want_S[slot]) < 5e-3, float(rel(S_c[slot], want_S[slot]))
+    assert torch.equal(S_c[0], S0[0]) and torch.equal(S_c[2], S0[2])      # other slots untouched

@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from ..ops import lib as qlib
+from ..utils import settings
 from .device_model import DeviceModel
 
 P = C.c_void_p
@@ -64,6 +65,11 @@ class Prefiller:
             "ple_gv": z((T, sc.xw), f32), "ple_nc": z((T, sc.xw), f32),
             "rows": z((8 * T,), i32),
         }
+        # the GDN scan of a chunk runs in its chunked (tensor-core) form; QW_GDN_SEQUENTIAL=1 keeps the row-by-row scan
+        self.gdn_chunked = not settings.get().gdn_sequential
+        if self.gdn_chunked:
+            nch = (T + 63) // 64
+            self.b["gdn_scratch"] = z((nch * sc.gdn_vl * (2 * 64 * 128 + 64 * 64 + 64) + T * sc.gdn_vl * 128,), f32)
         self.rows_host = torch.zeros(8 * T, dtype=torch.int32).pin_memory()
         self.max_tiles = Pn // 128 + sc.exp_l
 
@@ -209,9 +215,15 @@ class Prefiller:
                                     P(lw["dt_bias"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
                                     rp("run_start"), rp("run_len"), _p(b["qkv"]), _p(b["decay"]), _p(b["beta"]),
                                     C.c_float(c.eps), s), "gdn_conv")
-            self._ck(L.qwk_gdn_scan(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp, _p(dm.gdn_S[gi]), None,
-                                    P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
-                                    rp("run_start"), rp("run_len"), _p(b["o"]), C.c_float(c.eps), s), "gdn_scan")
+            if self.gdn_chunked:
+                self._ck(L.qwk_gdn_scan_chunked(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp,
+                                                _p(dm.gdn_S[gi]), P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T,
+                                                rp("slot"), _p(b["gdn_scratch"]), _p(b["o"]), C.c_float(c.eps), s),
+                         "gdn_scan_chunked")
+            else:
+                self._ck(L.qwk_gdn_scan(_p(b["qkv"]), _p(b["decay"]), _p(b["beta"]), _p(b["proj"]), ldp, _p(dm.gdn_S[gi]), None,
+                                        P(lw["gdn_norm"].data_ptr()), sc.gdn_kl, sc.gdn_vl, T, rp("slot"), rp("pos"),
+                                        rp("run_start"), rp("run_len"), _p(b["o"]), C.c_float(c.eps), s), "gdn_scan")
             ow = sc.gdn_vl * c.gdn_dim
             # gdn_scan writes o rows densely ([T][VL*128])
             self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,

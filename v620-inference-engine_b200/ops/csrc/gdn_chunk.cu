@@ -1,0 +1,381 @@
+// Chunked (WY) gated delta rule for token-major prefill: the recurrent scan of a run of M tokens done as
+// dense 64-token chunk products on the tensor cores, with the state in fp32.
+//
+// The reference only has the token-by-token scan (gdn_scan_T, src/kernels/gdn.hip:229-309) and lists the
+// chunked form as future work (docs/DESIGN.md:512).  Math (per value head, state S [128 k][128 v], chunk of
+// C = 64 rows, entry state S0, g_t = sum_{s<=t} log decay_s):
+//
+//     A[t,s] = beta_t exp(g_t - g_s) (k_t . k_s)       s <  t
+//     (I + A) Wv = diag(beta) V      (I + A) Wk = diag(beta exp(g)) K
+//     P[t,s] = exp(g_t - g_s) (q_t . k_s)              s <= t
+//     U  = Wv - Wk S0
+//     O  = diag(exp(g)) Q S0 + P U
+//     S1 = exp(g_C) S0 + (diag(exp(g_C - g)) K)^T U
+//
+// Three launches per layer:
+//   1. gdn_chunk_prep_kernel   grid (chunks, VL): everything that does not depend on the state (A, Wv, Wk, P, g),
+//      all chunks in parallel.  K K^T and Q K^T on mma.sync tf32; the two triangular solves by forward
+//      substitution in fp32, one column of [Wv | Wk] per thread.
+//   2. gdn_chunk_apply_kernel  grid (2, VL): walks the chunks in order with the state of one head's 64 value
+//      columns in shared memory; three tf32 products per chunk.  The value columns of a head are independent in
+//      every state-dependent product, so a head is split over two blocks.
+//   3. gdn_chunk_norm_kernel   grid (M, VL): gated RMS norm over the head's 128 outputs -> bf16.
+//
+// The run must be one slot's: rows 0..M-1 of the batch are consecutive positions of slot[0].  Rows past M in
+// the last chunk are masked (beta = 0, decay = 1, q = k = 0), which leaves the state untouched.
+#include "common.cuh"
+
+namespace qw {
+
+constexpr int CD = 128;          // head dim (keys and values)
+constexpr int CC = 64;           // rows per chunk
+constexpr int LDA = CD + 4;      // row stride of a [64][128] A-operand tile: 4 mod 32 words -> fragment loads hit 32 banks
+constexpr int LDT = CD + 8;      // row stride of a [64][128] tile read transposed (8 mod 32)
+constexpr int LDP = CC + 4;      // [64][64] A-operand tile
+constexpr int LDS = 64 + 8;      // [.][64] B-operand tile (state half, U)
+
+__device__ __forceinline__ uint32_t tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// A fragment of a 16 x 8 tile at (r0, k0) of a row-major matrix: lane (g = lane / 4, t = lane % 4) holds
+// (r0+g, k0+t), (r0+g+8, k0+t), (r0+g, k0+t+4), (r0+g+8, k0+t+4).
+__device__ __forceinline__ void lda_frag(uint32_t (&a)[4], const float *m, int ld, int r0, int k0, int g, int t) {
+    const float *p = m + (r0 + g) * ld + k0 + t;
+    a[0] = tf32(p[0]);
+    a[1] = tf32(p[8 * ld]);
+    a[2] = tf32(p[4]);
+    a[3] = tf32(p[8 * ld + 4]);
+}
+
+struct GdnChunkArgs {
+    const float *qkv;            // [M][qkv_l]  q (KL heads) | k (KL heads) | v (VL heads), after conv / norm
+    const float *decay, *beta;   // [M][VL]
+    const float *proj;           // z gate: proj[m][qkv_l + h*128 + d]
+    int ld_proj;
+    float *S;                    // [slots][VL][128 k][128 v]
+    const float *norm_w;         // [128]
+    int KL, VL, M;
+    const int *slot;             // slot[0] = the run's slot
+    float *Wk, *Wv;              // scratch [chunks][VL][64][128]
+    float *P;                    // scratch [chunks][VL][64][64]
+    float *G;                    // scratch [chunks][VL][64]   cumulative log decay
+    float *Oraw;                 // scratch [M][VL*128]
+    bf16 *o;                     // [M][VL*128]
+    float eps;
+};
+
+// Loads rows [m0, m0+64) x 128 floats at column offset col of the qkv rows into a shared tile of stride ld;
+// rows >= M are zero.  256 threads.
+__device__ __forceinline__ void load_tile(float *dst, int ld, const float *qkv, int qkv_l, int col, int m0, int M, int tid) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * 256;          // float4 index: 64 rows x 32
+        const int r = idx >> 5, c4 = idx & 31;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m0 + r < M) v = *reinterpret_cast<const float4 *>(qkv + (long long)(m0 + r) * qkv_l + col + c4 * 4);
+        *reinterpret_cast<float4 *>(dst + r * ld + c4 * 4) = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 1. state-independent part of every chunk
+// ------------------------------------------------------------------------------------------------
+constexpr int PREP_SMEM = (2 * CC * LDA + CC * LDP + 2 * CC) * 4;
+
+__global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(GdnChunkArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    float *Ks = sm;                      // [64][LDA]
+    float *Qs = Ks + CC * LDA;           // [64][LDA]
+    float *As = Qs + CC * LDA;           // [64][LDP]
+    float *gs = As + CC * LDP;           // [64] cumulative log decay
+    float *bs = gs + CC;                 // [64] beta
+    const int ch = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int qkv_l = (2 * a.KL + a.VL) * CD;
+    const int kh = h / (a.VL / a.KL);
+    const int m0 = ch * CC;
+    load_tile(Ks, LDA, a.qkv, qkv_l, (a.KL + kh) * CD, m0, a.M, tid);
+    load_tile(Qs, LDA, a.qkv, qkv_l, kh * CD, m0, a.M, tid);
+    if (w == 0) {
+        const int r0 = 2 * lane, r1 = r0 + 1;
+        float x0 = 0.f, x1 = 0.f, b0 = 0.f, b1 = 0.f;
+        if (m0 + r0 < a.M) {
+            x0 = fmaxf(__logf(a.decay[(long long)(m0 + r0) * a.VL + h]), -87.f);
+            b0 = a.beta[(long long)(m0 + r0) * a.VL + h];
+        }
+        if (m0 + r1 < a.M) {
+            x1 = fmaxf(__logf(a.decay[(long long)(m0 + r1) * a.VL + h]), -87.f);
+            b1 = a.beta[(long long)(m0 + r1) * a.VL + h];
+        }
+        float s = x0 + x1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n = __shfl_up_sync(0xffffffffu, s, o);
+            if (lane >= o) s += n;
+        }
+        gs[r0] = s - x1;
+        gs[r1] = s;
+        bs[r0] = b0;
+        bs[r1] = b1;
+    }
+    __syncthreads();
+    // K K^T and Q K^T: warp tile 16 rows x 32 columns
+    const int r0 = (w & 3) * 16, c0 = (w >> 2) * 32;
+    float akk[4][4], aqk[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) akk[n][i] = aqk[n][i] = 0.f;
+#pragma unroll 4
+    for (int k0 = 0; k0 < CD; k0 += 8) {
+        uint32_t fk[4], fq[4];
+        lda_frag(fk, Ks, LDA, r0, k0, g, t);
+        lda_frag(fq, Qs, LDA, r0, k0, g, t);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const float *p = Ks + (c0 + n * 8 + g) * LDA + k0 + t;      // B[k][n] = K[n][k]
+            const uint32_t b0 = tf32(p[0]), b1 = tf32(p[4]);
+            mma_tf32(akk[n], fk, b0, b1);
+            mma_tf32(aqk[n], fq, b0, b1);
+        }
+    }
+    float *Pg = a.P + ((long long)ch * a.VL + h) * CC * CC;
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = r0 + g + (i >> 1) * 8, c = c0 + n * 8 + 2 * t + (i & 1);
+            const float d = __expf(gs[r] - gs[c]);
+            As[r * LDP + c] = c < r ? bs[r] * d * akk[n][i] : 0.f;
+            Pg[r * CC + c] = c <= r ? d * aqk[n][i] : 0.f;
+        }
+    if (tid < CC) a.G[((long long)ch * a.VL + h) * CC + tid] = gs[tid];
+    __syncthreads();
+    // forward substitution: thread j owns column j of [Wv | Wk]
+    const int j = tid & 127;
+    const bool isk = tid >= 128;
+    float wcol[CC];
+#pragma unroll
+    for (int r = 0; r < CC; ++r) {
+        float b;
+        if (isk) b = bs[r] * __expf(gs[r]) * Ks[r * LDA + j];
+        else b = (m0 + r < a.M) ? bs[r] * a.qkv[(long long)(m0 + r) * qkv_l + (2 * a.KL + h) * CD + j] : 0.f;
+        wcol[r] = b;
+    }
+#pragma unroll
+    for (int r = 1; r < CC; ++r) {
+        float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+        for (int s4 = 0; s4 < r; s4 += 4) {
+            const float4 av = *reinterpret_cast<const float4 *>(As + r * LDP + s4);     // zero at s >= r
+            acc0 = fmaf(av.x, wcol[s4], acc0);
+            if (s4 + 1 < r) acc1 = fmaf(av.y, wcol[s4 + 1], acc1);
+            if (s4 + 2 < r) acc0 = fmaf(av.z, wcol[s4 + 2], acc0);
+            if (s4 + 3 < r) acc1 = fmaf(av.w, wcol[s4 + 3], acc1);
+        }
+        wcol[r] -= acc0 + acc1;
+    }
+    float *Wg = (isk ? a.Wk : a.Wv) + ((long long)ch * a.VL + h) * CC * CD;
+#pragma unroll
+    for (int r = 0; r < CC; ++r) Wg[r * CD + j] = wcol[r];
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. state-dependent part: one block per (half of the value columns, head) walks the chunks
+// ------------------------------------------------------------------------------------------------
+constexpr int APPLY_FLOATS = CD * LDS + 2 * CC * LDA + CC * LDT + CC * LDP + CC * LDS + 2 * CC;
+constexpr int APPLY_SMEM = APPLY_FLOATS * 4;
+
+__global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    float *Ss = sm;                      // [128 k][LDS]   state, this block's 64 value columns
+    float *Wks = Ss + CD * LDS;          // [64][LDA]
+    float *Qs = Wks + CC * LDA;          // [64][LDA]
+    float *Ks = Qs + CC * LDA;           // [64][LDT]      read transposed in the state update
+    float *Ps = Ks + CC * LDT;           // [64][LDP]
+    float *Us = Ps + CC * LDP;           // [64][LDS]
+    float *eg = Us + CC * LDS;           // [64] exp(g_t)
+    float *ek = eg + CC;                 // [64] exp(g_C - g_t)
+    const int vh = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int qkv_l = (2 * a.KL + a.VL) * CD;
+    const int kh = h / (a.VL / a.KL);
+    const int slot = a.slot[0];
+    float *Sg = a.S + ((long long)slot * a.VL + h) * CD * CD + vh * 64;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * 256;              // float4 index: 128 rows x 16
+        const int r = idx >> 4, c4 = idx & 15;
+        *reinterpret_cast<float4 *>(Ss + r * LDS + c4 * 4) = *reinterpret_cast<const float4 *>(Sg + r * CD + c4 * 4);
+    }
+    const int nch = (a.M + CC - 1) / CC;
+    const int r0 = (w & 3) * 16, c0 = (w >> 2) * 32;
+    for (int ch = 0; ch < nch; ++ch) {
+        const int m0 = ch * CC;
+        const long long cb = (long long)ch * a.VL + h;
+        load_tile(Qs, LDA, a.qkv, qkv_l, kh * CD, m0, a.M, tid);
+        load_tile(Ks, LDT, a.qkv, qkv_l, (a.KL + kh) * CD, m0, a.M, tid);
+        load_tile(Wks, LDA, a.Wk + cb * CC * CD, CD, 0, 0, CC, tid);
+        {
+            const float *Pg = a.P + cb * CC * CC;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * 256;      // float4 index: 64 rows x 16
+                const int r = idx >> 4, c4 = idx & 15;
+                *reinterpret_cast<float4 *>(Ps + r * LDP + c4 * 4) = *reinterpret_cast<const float4 *>(Pg + r * CC + c4 * 4);
+            }
+        }
+        if (tid < CC) {
+            const float *Gg = a.G + cb * CC;
+            const float gt = Gg[tid], gC = Gg[CC - 1];
+            eg[tid] = __expf(gt);
+            ek[tid] = __expf(gC - gt);
+        }
+        __syncthreads();
+        // U = Wv - Wk S0 and Q S0: warp tile 16 rows x 32 value columns
+        float accW[4][4], accO[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) accW[n][i] = accO[n][i] = 0.f;
+#pragma unroll 4
+        for (int k0 = 0; k0 < CD; k0 += 8) {
+            uint32_t fw[4], fq[4];
+            lda_frag(fw, Wks, LDA, r0, k0, g, t);
+            lda_frag(fq, Qs, LDA, r0, k0, g, t);
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const float *p = Ss + (k0 + t) * LDS + c0 + n * 8 + g;
+                const uint32_t b0 = tf32(p[0]), b1 = tf32(p[4 * LDS]);
+                mma_tf32(accW[n], fw, b0, b1);
+                mma_tf32(accO[n], fq, b0, b1);
+            }
+        }
+        {
+            const float *Wvg = a.Wv + cb * CC * CD + vh * 64;
+            const float e0 = eg[r0 + g], e1 = eg[r0 + g + 8];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int c = c0 + n * 8 + 2 * t;
+                const float2 v0 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g) * CD + c);
+                const float2 v1 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g + 8) * CD + c);
+                *reinterpret_cast<float2 *>(Us + (r0 + g) * LDS + c) = make_float2(v0.x - accW[n][0], v0.y - accW[n][1]);
+                *reinterpret_cast<float2 *>(Us + (r0 + g + 8) * LDS + c) = make_float2(v1.x - accW[n][2], v1.y - accW[n][3]);
+                accO[n][0] *= e0; accO[n][1] *= e0;
+                accO[n][2] *= e1; accO[n][3] *= e1;
+            }
+        }
+        __syncthreads();
+        // O += P U (P is zero above the diagonal: k tiles past the warp's rows are skipped)
+        for (int k0 = 0; k0 < r0 + 16; k0 += 8) {
+            uint32_t fp[4];
+            lda_frag(fp, Ps, LDP, r0, k0, g, t);
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const float *p = Us + (k0 + t) * LDS + c0 + n * 8 + g;
+                mma_tf32(accO[n], fp, tf32(p[0]), tf32(p[4 * LDS]));
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int c = h * CD + vh * 64 + c0 + n * 8 + 2 * t;
+            const int ra = m0 + r0 + g, rb = ra + 8;
+            if (ra < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)ra * a.VL * CD + c) = make_float2(accO[n][0], accO[n][1]);
+            if (rb < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)rb * a.VL * CD + c) = make_float2(accO[n][2], accO[n][3]);
+        }
+        // S1 = exp(g_C) S0 + (diag(ek) K)^T U: warp w owns state rows 16w .. 16w+15, all 64 columns
+        {
+            const int i0 = w * 16;
+            const float eC = eg[CC - 1];
+            float accS[8][4];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float2 s0 = *reinterpret_cast<const float2 *>(Ss + (i0 + g) * LDS + n * 8 + 2 * t);
+                const float2 s1 = *reinterpret_cast<const float2 *>(Ss + (i0 + g + 8) * LDS + n * 8 + 2 * t);
+                accS[n][0] = s0.x * eC; accS[n][1] = s0.y * eC;
+                accS[n][2] = s1.x * eC; accS[n][3] = s1.y * eC;
+            }
+#pragma unroll 2
+            for (int k0 = 0; k0 < CC; k0 += 8) {
+                const float ea = ek[k0 + t], eb = ek[k0 + t + 4];
+                const float *p = Ks + (k0 + t) * LDT + i0 + g;      // A[i][s] = K[s][i] ek[s]
+                uint32_t fa[4];
+                fa[0] = tf32(p[0] * ea);
+                fa[1] = tf32(p[8] * ea);
+                fa[2] = tf32(p[4 * LDT] * eb);
+                fa[3] = tf32(p[4 * LDT + 8] * eb);
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    const float *q = Us + (k0 + t) * LDS + n * 8 + g;
+                    mma_tf32(accS[n], fa, tf32(q[0]), tf32(q[4 * LDS]));
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                *reinterpret_cast<float2 *>(Ss + (i0 + g) * LDS + n * 8 + 2 * t) = make_float2(accS[n][0], accS[n][1]);
+                *reinterpret_cast<float2 *>(Ss + (i0 + g + 8) * LDS + n * 8 + 2 * t) = make_float2(accS[n][2], accS[n][3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * 256;
+        const int r = idx >> 4, c4 = idx & 15;
+        *reinterpret_cast<float4 *>(Sg + r * CD + c4 * 4) = *reinterpret_cast<const float4 *>(Ss + r * LDS + c4 * 4);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. gated RMS norm over each head's 128 outputs
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gdn_chunk_norm_kernel(GdnChunkArgs a) {
+    __shared__ float scratch[32];
+    const int m = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+    const int qkv_l = (2 * a.KL + a.VL) * CD;
+    const long long oi = (long long)m * a.VL * CD + h * CD + c;
+    const float ov = a.Oraw[oi];
+    const float ss = block_sum<128>(ov * ov, scratch);
+    const float z = a.proj[(long long)m * a.ld_proj + qkv_l + h * CD + c];
+    a.o[oi] = __float2bfloat16(ov * rsqrtf(ss / float(CD) + a.eps) * a.norm_w[c] * sigmoidf_(z));
+}
+
+}  // namespace qw
+
+using namespace qw;
+
+// The scan of one slot's run of M rows (rows 0..M-1 consecutive positions of slot[0]): same inputs and outputs
+// as qwk_gdn_scan without the per-row state saves.  `scratch` holds
+// 4 * (ceil(M / 64) * VL * (2 * 64 * 128 + 64 * 64 + 64) + M * VL * 128) bytes.
+QW_API int qwk_gdn_scan_chunked(const float *qkv, const float *decay, const float *beta, const float *proj, int ld_proj,
+                                float *S, const float *norm_w, int KL, int VL, int M, const int *slot, float *scratch,
+                                void *o, float eps, cudaStream_t s) {
+    if (M < 1 || KL < 1 || VL % KL != 0) return -1;
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, APPLY_SMEM) != cudaSuccess)
+            return -3;
+        attr_done = true;
+    }
+    const long long nch = (M + CC - 1) / CC;
+    GdnChunkArgs a;
+    a.qkv = qkv; a.decay = decay; a.beta = beta; a.proj = proj; a.ld_proj = ld_proj; a.S = S; a.norm_w = norm_w;
+    a.KL = KL; a.VL = VL; a.M = M; a.slot = slot; a.eps = eps; a.o = (bf16 *)o;
+    a.Wk = scratch;
+    a.Wv = a.Wk + nch * VL * CC * CD;
+    a.P = a.Wv + nch * VL * CC * CD;
+    a.G = a.P + nch * VL * CC * CC;
+    a.Oraw = a.G + nch * VL * CC;
+    gdn_chunk_prep_kernel<<<dim3((unsigned)nch, VL), 256, PREP_SMEM, s>>>(a);
+    gdn_chunk_apply_kernel<<<dim3(2, VL), 256, APPLY_SMEM, s>>>(a);
+    gdn_chunk_norm_kernel<<<dim3(M, VL), 128, 0, s>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
