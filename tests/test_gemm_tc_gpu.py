@@ -22,3 +22,46 @@ def test_gemm_tc_matches_fp32(T, N, K, out_dtype):
     tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
     err = float((out[:, :N].float() - ref).abs().max() / ref.abs().max())
     assert err < tol, err
+
+
+@pytest.mark.parametrize("Nw,K,counts", [(256, 256, [5, 0, 130, 128, 1, 300]), (1280, 2560, [80, 200, 0, 33]),
+                                         (2560, 640, [77, 129, 64])])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_grouped_q4_gemm_matches_fp32(Nw, K, counts, out_dtype):
+    """Grouped tcgen05 GEMM whose W operand is dequantised from q4 inside the kernel: every group's rows against
+    A @ dequant(W_group)^T in fp32, rows of unused tile entries and guard rows untouched."""
+    import ctypes as C
+    from qwb200.models.quant import dequantize_q4, quantize_q4, to_engine_order
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(Nw + K)
+    E = len(counts)
+    W = torch.randn(E * Nw, K, generator=g, device=dev) * 0.05
+    packed, scale = quantize_q4(W, scale_dtype=torch.bfloat16)
+    Wd = dequantize_q4(packed, scale).to(torch.bfloat16).float()       # the kernel rounds value * scale to bf16
+    words = to_engine_order(packed).contiguous()
+    rows = sum(counts)
+    A = torch.randn(rows + 128, K, generator=g, device=dev).to(torch.bfloat16)
+    tiles, r0 = [], 0
+    for e, n in enumerate(counts):
+        for t in range(0, n, 128):
+            tiles.append([r0 + t, min(128, n - t), e * Nw, 0])
+        r0 += n
+    tiles.append([0, 0, 0, 0])                                   # an unused entry
+    tt = torch.tensor(tiles, dtype=torch.int32, device=dev)
+    out = torch.full((rows + 128, Nw), 768.0, dtype=out_dtype, device=dev)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rc = L.qwk_gemm_q4_tc_grouped(P(A), P(words), P(scale), P(out), P(tt), len(tiles), rows, E * Nw, Nw, K, K, Nw,
+                                  1 if out_dtype == torch.bfloat16 else 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.all(out[rows:].float() == 768.0)
+    r0 = 0
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    for e, n in enumerate(counts):
+        if n:
+            ref = A[r0:r0 + n].float() @ Wd[e * Nw:(e + 1) * Nw].float().T
+            err = float((out[r0:r0 + n].float() - ref).abs().max() / ref.abs().max())
+            assert err < tol, (e, err)
+        r0 += n

@@ -164,3 +164,68 @@ def test_gdn_chunked_scan_matches_sequential_fp32(M):
     assert rel(o_c.float(), w) < 1e-2, float(rel(o_c.float(), w))
     assert rel(S_c[slot], want_S[slot]) < 5e-3, float(rel(S_c[slot], want_S[slot]))
     assert torch.equal(S_c[0], S0[0]) and torch.equal(S_c[2], S0[2])      # other slots untouched
+
+
+@pytest.mark.parametrize("QL,KVL", [(24, 2), (8, 2), (3, 1)])
+def test_qsa_attend_mma_matches_fp32_and_decode_kernel(QL, KVL):
+    """Tensor-core prefill attention over the paged KV against PyTorch fp32 and against the decode attention kernel:
+    dense rows (below the budget), sparse rows (selected groups + open tail), a shuffled page table."""
+    import ctypes as C
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    dev = _dev()
+    g = torch.Generator(device="cuda").manual_seed(QL)
+    HD, topk, ratio, page = 256, 512, 4, 256
+    n_pages = 14
+    positions = [0, 1, 62, 63, 64, 200, 2047, 2048, 2049, 2050, 2051, 2500, 3001, 3583]
+    M = len(positions)
+    kpool = (torch.randn(n_pages, page, KVL * HD, generator=g, device=dev)).to(torch.bfloat16)
+    vpool = (torch.randn(n_pages, page, KVL * HD, generator=g, device=dev)).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    page_table = perm.to(dev).contiguous()
+    q = torch.randn(M, QL, HD, generator=g, device=dev).contiguous()
+    ldp = QL * 2 * HD + 40
+    proj = torch.randn(M, ldp, generator=g, device=dev).contiguous()
+    pos = torch.tensor(positions, dtype=torch.int32, device=dev)
+    slot = torch.zeros(M, dtype=torch.int32, device=dev)
+    sel = torch.zeros(M, topk, dtype=torch.int32, device=dev)
+    sel_n = torch.full((M,), -1, dtype=torch.int32, device=dev)
+    lists = []
+    for m, p in enumerate(positions):
+        nb = (p + 1) // ratio
+        if nb > topk:
+            ch = torch.sort(torch.randperm(nb, generator=torch.Generator().manual_seed(m))[:topk]).values
+            sel[m] = ch.to(dev, torch.int32)
+            sel_n[m] = topk
+            toks = (ch[:, None] * ratio + torch.arange(ratio)[None]).reshape(-1).tolist() + list(range(nb * ratio, p + 1))
+        else:
+            toks = list(range(p + 1))
+        lists.append(torch.tensor(toks, dtype=torch.long, device=dev))
+    kf = kpool.float()[page_table.long()].reshape(-1, KVL, HD)        # token-major view through the page table
+    vf = vpool.float()[page_table.long()].reshape(-1, KVL, HD)
+    per = QL // KVL
+    want = torch.empty(M, QL, HD, device=dev)
+    for m in range(M):
+        for h in range(QL):
+            kv = h // per
+            sc = (kf[lists[m], kv] @ q[m, h]) / 16.0
+            w = torch.softmax(sc, 0)
+            gate = proj[m, h * 2 * HD + HD: h * 2 * HD + 2 * HD]
+            want[m, h] = (w @ vf[lists[m], kv]) * torch.sigmoid(gate)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    o = torch.zeros(M, QL, HD, dtype=torch.bfloat16, device=dev)
+    rc = L.qwk_qsa_attend_mma(P(q), QL, KVL, M, P(slot), P(pos), P(kpool), P(vpool), None, None, n_pages, P(page_table), n_pages,
+                              P(sel), P(sel_n), topk, ratio, P(proj), ldp, P(o), s)
+    assert rc == 0
+    nsplit = (topk * ratio + 8 + 63) // 64 + 24
+    pm = torch.zeros(M, QL, nsplit, device=dev)
+    pl = torch.zeros(M, QL, nsplit, device=dev)
+    pacc = torch.zeros(M, QL, nsplit, HD, device=dev)
+    o2 = torch.zeros(M, QL, HD, dtype=torch.bfloat16, device=dev)
+    rc = L.qwk_qsa_attend(P(q), QL, KVL, M, P(slot), P(pos), P(kpool), P(vpool), None, None, n_pages, P(page_table), n_pages,
+                          P(sel), P(sel_n), topk, ratio, nsplit, P(pm), P(pl), P(pacc), P(proj), ldp, P(o2), s)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert rel(o2.float(), want) < 1e-2
+    assert rel(o.float(), want) < 2e-2, rel(o.float(), want)

@@ -60,16 +60,22 @@ class Prefiller:
             "sh_h": z((T, sc.sffn_l), bf), "sd": z((T, c.hidden), f32),
             "xperm": z((Pn + 128, c.hidden), bf), "h13": z((Pn, 2 * c.ffn), bf), "h": z((Pn + 128, c.ffn), bf),
             "y": z((Pn, c.hidden), f32),
-            "w13dq": z((sc.exp_l * 2 * c.ffn, c.hidden), bf), "w2dq": z((sc.exp_l * c.hidden, c.ffn), bf),
             "ple_e": z((T, c.hidden), bf), "ple_kv": z((T, (sc.ple_kv + 7) // 8 * 8), f32), "ple_send": z((T, 16), f32),
             "ple_gv": z((T, sc.xw), f32), "ple_nc": z((T, sc.xw), f32),
             "rows": z((8 * T,), i32),
         }
         # the GDN scan of a chunk runs in its chunked (tensor-core) form; QW_GDN_SEQUENTIAL=1 keeps the row-by-row scan
         self.gdn_chunked = not settings.get().gdn_sequential
+        # QSA attention of a chunk: one tensor-core launch over all rows; QW_QSA_ATTEND_ROWS=1 keeps the decode kernels
+        self.qsa_mma = not settings.get().qsa_attend_rows and sc.qh_l // sc.kvh_l <= 16
         if self.gdn_chunked:
             nch = (T + 63) // 64
             self.b["gdn_scratch"] = z((nch * sc.gdn_vl * (2 * 64 * 128 + 64 * 64 + 64) + T * sc.gdn_vl * 128,), f32)
+        # expert GEMMs read the q4 words themselves; QW_MOE_DEQUANT_SCRATCH=1 converts a layer's experts to bf16 first
+        self.q4_fused = not settings.get().moe_dequant_scratch and c.hidden % 128 == 0 and c.ffn % 128 == 0
+        if not self.q4_fused:
+            self.b["w13dq"] = z((sc.exp_l * 2 * c.ffn, c.hidden), bf)
+            self.b["w2dq"] = z((sc.exp_l * c.hidden, c.ffn), bf)
         self.rows_host = torch.zeros(8 * T, dtype=torch.int32).pin_memory()
         self.max_tiles = Pn // 128 + sc.exp_l
 
@@ -193,17 +199,23 @@ class Prefiller:
                                       c.idx_ratio, c.idx_topk_blocks, _p(b["scores"]), d.score_cap, max_groups, s), "scores")
             self._ck(L.qwk_qsa_select(_p(b["scores"]), d.score_cap, T, rp("pos"), c.idx_ratio, c.idx_topk_blocks,
                                       _p(b["sel"]), _p(b["sel_n"]), s), "select")
-            A = self.attn_rows
             ow = sc.qh_l * c.head_dim
-            for r0 in range(0, T, A):
-                n = min(A, T - r0)
-                self._ck(L.qwk_qsa_attend(P(b["q"].data_ptr() + 4 * r0 * ow), sc.qh_l, sc.kvh_l, n, rp("slot", r0),
-                                          rp("pos", r0), P(kd), P(vd), P(kh) if kh else None, P(vh) if vh else None,
-                                          d.n_dev_pages, _p(dm.page_table), d.max_pages,
-                                          P(b["sel"].data_ptr() + 4 * r0 * c.idx_topk_blocks),
-                                          P(b["sel_n"].data_ptr() + 4 * r0), c.idx_topk_blocks, c.idx_ratio, d.nsplit,
-                                          _p(b["pm"]), _p(b["pl"]), _p(b["pacc"]), P(b["proj"].data_ptr() + 4 * r0 * ldp),
-                                          ldp, P(b["o"].data_ptr() + 2 * r0 * ow), s), "attend")
+            if self.qsa_mma:
+                self._ck(L.qwk_qsa_attend_mma(_p(b["q"]), sc.qh_l, sc.kvh_l, T, rp("slot"), rp("pos"), P(kd), P(vd),
+                                              P(kh) if kh else None, P(vh) if vh else None, d.n_dev_pages, _p(dm.page_table),
+                                              d.max_pages, _p(b["sel"]), _p(b["sel_n"]), c.idx_topk_blocks, c.idx_ratio,
+                                              _p(b["proj"]), ldp, _p(b["o"]), s), "attend_mma")
+            else:
+                A = self.attn_rows
+                for r0 in range(0, T, A):
+                    n = min(A, T - r0)
+                    self._ck(L.qwk_qsa_attend(P(b["q"].data_ptr() + 4 * r0 * ow), sc.qh_l, sc.kvh_l, n, rp("slot", r0),
+                                              rp("pos", r0), P(kd), P(vd), P(kh) if kh else None, P(vh) if vh else None,
+                                              d.n_dev_pages, _p(dm.page_table), d.max_pages,
+                                              P(b["sel"].data_ptr() + 4 * r0 * c.idx_topk_blocks),
+                                              P(b["sel_n"].data_ptr() + 4 * r0), c.idx_topk_blocks, c.idx_ratio, d.nsplit,
+                                              _p(b["pm"]), _p(b["pl"]), _p(b["pacc"]), P(b["proj"].data_ptr() + 4 * r0 * ldp),
+                                              ldp, P(b["o"].data_ptr() + 2 * r0 * ow), s), "attend")
             # the attention kernels write o rows densely ([T][QL*256])
             self._ck(L.qwk_gemm_bf16_tc(_p(b["o"]), P(lw["Wout"].data_ptr()), _p(b["out_a"]), T, c.hidden, ow, ow, ow,
                                         c.hidden, 0, s), "o_proj")
@@ -287,13 +299,20 @@ class Prefiller:
         zero = torch.zeros_like(row0)
         t13 = torch.stack([row0, valid, e * (2 * F), zero], 1).to(torch.int32).contiguous()
         t2 = torch.stack([row0, valid, e * H, zero], 1).to(torch.int32).contiguous()
-        # ---- weights of this layer: q4 -> bf16 scratch
-        self._ck(L.qwk_q4_dequant(P(lw["w13"].data_ptr()), P(lw["s13"].data_ptr()), E * 2 * F, H, _p(b["w13dq"]), s), "dequant13")
-        self._ck(L.qwk_q4_dequant(P(lw["w2"].data_ptr()), P(lw["s2"].data_ptr()), E * H, F, _p(b["w2dq"]), s), "dequant2")
-        self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["xperm"]), _p(b["w13dq"]), _p(b["h13"]), _p(t13), self.max_tiles, Pn,
-                                            E * 2 * F, 2 * F, H, H, H, 2 * F, 1, s), "experts13")
-        self._ck(L.qwk_swiglu_T(_p(b["h13"]), F, _p(b["h"]), Pn, s), "swiglu")
-        self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["h"]), _p(b["w2dq"]), _p(b["y"]), _p(t2), self.max_tiles, Pn, E * H, H, F, F,
-                                            F, H, 0, s), "experts2")
+        if self.q4_fused:
+            # q4 words converted inside the GEMM's W-operand producer warps: no bf16 copy of the layer's experts
+            self._ck(L.qwk_gemm_q4_tc_grouped(_p(b["xperm"]), P(lw["w13"].data_ptr()), P(lw["s13"].data_ptr()), _p(b["h13"]),
+                                              _p(t13), self.max_tiles, Pn, E * 2 * F, 2 * F, H, H, 2 * F, 1, s), "experts13")
+            self._ck(L.qwk_swiglu_T(_p(b["h13"]), F, _p(b["h"]), Pn, s), "swiglu")
+            self._ck(L.qwk_gemm_q4_tc_grouped(_p(b["h"]), P(lw["w2"].data_ptr()), P(lw["s2"].data_ptr()), _p(b["y"]), _p(t2),
+                                              self.max_tiles, Pn, E * H, H, F, F, H, 0, s), "experts2")
+        else:
+            self._ck(L.qwk_q4_dequant(P(lw["w13"].data_ptr()), P(lw["s13"].data_ptr()), E * 2 * F, H, _p(b["w13dq"]), s), "dequant13")
+            self._ck(L.qwk_q4_dequant(P(lw["w2"].data_ptr()), P(lw["s2"].data_ptr()), E * H, F, _p(b["w2dq"]), s), "dequant2")
+            self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["xperm"]), _p(b["w13dq"]), _p(b["h13"]), _p(t13), self.max_tiles, Pn,
+                                                E * 2 * F, 2 * F, H, H, H, 2 * F, 1, s), "experts13")
+            self._ck(L.qwk_swiglu_T(_p(b["h13"]), F, _p(b["h"]), Pn, s), "swiglu")
+            self._ck(L.qwk_gemm_bf16_tc_grouped(_p(b["h"]), _p(b["w2dq"]), _p(b["y"]), _p(t2), self.max_tiles, Pn, E * H, H, F, F,
+                                                F, H, 0, s), "experts2")
         self.gemm(b["sh_h"][:T], lw["Wsd"].data_ptr(), H, sc.sffn_l, b["sd"][:T])
         self._ck(L.qwk_moe_combine_T(_p(b["y"]), H, _p(inv), _p(b["pw"]), k, _p(b["sd"]), H, _p(b["out_b"]), T, s), "combine")

@@ -4,13 +4,15 @@
 //
 // One CTA computes a 128 x 128 output tile.  Warp roles:
 //   warp 0   : TMA producer - one thread issues cp.async.bulk.tensor loads (no multicast) of the
-//              128 x 64 A tile and the 128 x 64 W tile of each k block into a 6-stage ring of
+//              128 x 64 A tile and the 128 x 64 W tile of each k block into a 3-stage ring of
 //              128B-swizzled shared-memory tiles, completing on the stage's "full" mbarrier;
 //   warp 1   : allocates 128 TMEM columns, and one thread issues tcgen05.mma (M=128, N=128, K=16, four per
 //              k block) reading both operands straight from shared memory through matrix descriptors;
 //              tcgen05.commit releases a stage ("empty" mbarrier) and finally signals the epilogue;
 //   warps 2-5: epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32 output rows),
 //              convert and store.
+// Two CTAs share an SM (3 stages x 32 KB and 128 of the 512 TMEM columns each), so the prologue and the epilogue of
+// one tile run under the main loop of the other; with 10-40 k blocks per tile that matters more than ring depth.
 // Every mbarrier wait is bounded; a wait that runs out records an error, the pipeline drains and the
 // TMEM allocation is released before the kernel returns.
 #include <cuda.h>
@@ -19,7 +21,7 @@
 
 namespace qw {
 
-constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 6;
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;     // 16 KB each
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -61,7 +63,7 @@ struct GemmTcArgs {
     const int4 *tiles;
 };
 
-__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+__global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                          const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
     extern __shared__ unsigned char raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -130,6 +132,181 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         }
     } else {
         // epilogue warps 2..5: TMEM lane quarter = warp % 4
+        const bool ok = mbar_wait(done, 0, a.err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3;
+        const int row = t0 + q * 32 + lane;
+        const bool row_ok = row < a.T && q * 32 + lane < rows_valid;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+                    const int nmax = a.N - (n0 + c0);
+                    if (a.C32) {
+                        float *o = a.C32 + (long long)row * a.ldc + n0 + c0;
+                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        } else {
+                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
+                        }
+                    } else {
+                        bf16 *o = a.C16 + (long long)row * a.ldc + n0 + c0;
+                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pk;
+                                pk.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                                pk.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                                pk.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                                pk.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                                *reinterpret_cast<uint4 *>(o + j) = pk;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __float2bfloat16(__uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Grouped GEMM with the weights in q4 (group 128, bf16 scales): the expert products of token-major prefill without a
+// bf16 copy of the layer's experts.  Same tile, pipeline and epilogue as gemm_tc_kernel; the W operand of a stage is
+// not loaded by TMA but produced by four extra warps: thread r of them owns row r of the 128 x 64 W tile, fetches its
+// 8 q4 words (32 bytes, one sector) four k blocks ahead, converts them to the eight 16-byte bf16 chunks of the row
+// with the row's scale (the same rounding as the stand-alone dequantisation) and stores them where the 128-byte
+// swizzle puts them (chunk c of row r at chunk c ^ (r & 7)); a proxy fence makes the stores visible to the tensor
+// core's reads, and the thread arrives on the stage's "full" barrier (1 TMA arrival + 128 producer arrivals).
+// (Role of the reference's moe_gate_up_T / moe_down_T, src/kernels/moe_experts.hip:17-27.)
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int Q4_AHEAD = 4;
+
+__global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constant__ CUtensorMap mapA, GemmTcArgs a,
+                                                            const uint32_t *Wq, const bf16 *scale, long long w_rows) {
+    extern __shared__ unsigned char raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);
+    uint64_t *empty = full + TC_STAGES;
+    uint64_t *done = empty + TC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BN;
+    const int4 tl = a.tiles[blockIdx.y];
+    const int t0 = tl.x, rows_valid = tl.y, w0 = tl.z + n0;
+    if (rows_valid <= 0) return;              // unused entry of the tile table (uniform for the CTA, before any barrier)
+    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full + s, 1 + 128);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) break;
+                mbar_expect_tx(full + s, TC_A_BYTES);
+                tma_load_2d(smem + s * TC_STAGE_BYTES, &mapA, kb * TC_BK, t0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                ok = mbar_wait(full + s, (unsigned)(kb / TC_STAGES) & 1u, a.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
+                    umma_bf16(tmem, da, db, idesc, (kb | k) ? 1u : 0u);
+                }
+                umma_commit(empty + s);
+            }
+            umma_commit(done);
+        }
+    } else if (warp >= 6) {
+        // W producers: thread r = row r of the tile
+        const int r = threadIdx.x - 192;
+        const long long wrow = (long long)w0 + r;
+        const bool row_ok = n0 + r < a.N && wrow < w_rows;
+        const int wpr = a.K >> 3, spr = a.K >> 7;
+        const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr);
+        const bf16 *sc_row = scale + (row_ok ? wrow : 0) * spr;
+        uint4 ring[Q4_AHEAD][2];
+#pragma unroll
+        for (int i = 0; i < Q4_AHEAD; ++i) {
+            ring[i][0] = ring[i][1] = make_uint4(0u, 0u, 0u, 0u);
+            if (row_ok && i < kblocks) { ring[i][0] = __ldg(src + 2 * i); ring[i][1] = __ldg(src + 2 * i + 1); }
+        }
+        bool ok = true;
+        for (int kb0 = 0; kb0 < kblocks && ok; kb0 += Q4_AHEAD) {
+#pragma unroll
+            for (int i = 0; i < Q4_AHEAD; ++i) {
+                const int kb = kb0 + i;
+                if (kb >= kblocks) break;
+                const int s = kb % TC_STAGES;
+                const uint4 q0 = ring[i][0], q1 = ring[i][1];
+                if (row_ok && kb + Q4_AHEAD < kblocks) {
+                    ring[i][0] = __ldg(src + 2 * (kb + Q4_AHEAD));
+                    ring[i][1] = __ldg(src + 2 * (kb + Q4_AHEAD) + 1);
+                }
+                const float sc = row_ok ? __bfloat162float(sc_row[kb >> 1]) : 0.f;
+                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
+                unsigned char *dst = smem + s * TC_STAGE_BYTES + TC_A_BYTES + r * 128;
+                const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float e0, e1;
+                    uint4 o;
+                    q4_pair(words[c], 0, e0, e1); o.x = pack_bf16(e0 * sc, e1 * sc);
+                    q4_pair(words[c], 1, e0, e1); o.y = pack_bf16(e0 * sc, e1 * sc);
+                    q4_pair(words[c], 2, e0, e1); o.z = pack_bf16(e0 * sc, e1 * sc);
+                    q4_pair(words[c], 3, e0, e1); o.w = pack_bf16(e0 * sc, e1 * sc);
+                    *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(full + s);
+            }
+        }
+    } else {
         const bool ok = mbar_wait(done, 0, a.err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int q = warp & 3;
@@ -260,5 +437,27 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
     dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
     gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Grouped form with q4 weights: Wq uint32 [w_rows][K/8] (engine nibble order), scale bf16 [w_rows][K/128]; otherwise
+// as qwk_gemm_bf16_tc_grouped.  K a multiple of 128.
+QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *scale, void *C, const void *tiles, int max_tiles,
+                                  int rows, long long w_rows, int Nw, int K, int lda, int ldc, int out_bf16, cudaStream_t s) {
+    if (rows <= 0 || max_tiles <= 0) return 0;
+    if ((K & 127) || (lda & 7) || ((uintptr_t)A & 15) || ((uintptr_t)Wq & 15)) return -1;
+    CUtensorMap mA;
+    if (!make_map(&mA, A, rows, K, lda, TC_BM)) return -3;
+    GemmTcArgs a;
+    a.C32 = out_bf16 ? nullptr : (float *)C;
+    a.C16 = out_bf16 ? (bf16 *)C : nullptr;
+    a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return -3;
+        configured = true;
+    }
+    dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
+    gemm_tc_q4_kernel<<<grid, 320, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

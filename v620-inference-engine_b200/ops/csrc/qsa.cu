@@ -11,6 +11,7 @@
 // live in the device pool, the rest in the host pool (pinned, mapped: the kernels read host RAM
 // directly).  page_table[slot][i] is the page of tokens i*KV_PAGE ...
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace qw {
 
@@ -523,6 +524,8 @@ __global__ void __launch_bounds__(256) qsa_combine_kernel(const float *pm, const
     o[((long long)m * QL + h) * HD + d] = __float2bfloat16(A / L * sigmoidf_(gate));
 }
 
+#include "qsa_mma.cuh"
+
 }  // namespace qw
 
 using namespace qw;
@@ -604,6 +607,30 @@ QW_API int qwk_qsa_attend(const float *q, int QL, int KVL, int M, const int *slo
     dim3 g2(M, QL);
     launch_pdl(qsa_combine_kernel, g2, dim3(256), 0, s, (const float *)pm, (const float *)pl, (const float *)pacc, nsplit, proj, ld_proj, QL, (bf16 *)o);
     // plain launch: it starts when both kernels above have finished, so nothing reads the cache while entries change
+    if (a.sc.tags) spill_cache_fill_kernel<<<64, 256, 0, s>>>(a.sc, (const bf16 *)k_host, (const bf16 *)v_host, KVL * HD);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// The same attention for the rows of a token-major prefill chunk, on the tensor cores: one launch for all M rows, no
+// partial buffers.  Needs QL / KVL <= 16 query heads per KV head.
+QW_API int qwk_qsa_attend_mma(const float *q, int QL, int KVL, int M, const int *slot, const int *pos, void *k_dev,
+                              void *v_dev, void *k_host, void *v_host, int n_dev_pages, const int *page_table,
+                              int max_pages, const int *sel, const int *sel_n, int topk, int ratio, const float *proj,
+                              int ld_proj, void *o, cudaStream_t s) {
+    if (KVL < 1 || QL % KVL != 0 || QL / KVL > 16 || M < 1 || M > 65535) return -1;
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(qsa_attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
+            return -3;
+        attr_done = true;
+    }
+    QsaAttendArgs a;
+    a.q = q; a.QL = QL; a.KVL = KVL; a.rows = Rows{M, slot, pos, nullptr, nullptr};
+    a.kv = make_pool(k_dev, v_dev, k_host, v_host, n_dev_pages, page_table, max_pages, KVL * HD);
+    a.sc = k_host ? g_spill : SpillCache{};
+    a.sel = sel; a.sel_n = sel_n; a.topk = topk; a.ratio = ratio; a.nsplit = 0;
+    a.pm = nullptr; a.pl = nullptr; a.pacc = nullptr;
+    qsa_attend_mma_kernel<<<dim3(KVL, M), 128, ATT_SMEM, s>>>(a, proj, ld_proj, (bf16 *)o);
     if (a.sc.tags) spill_cache_fill_kernel<<<64, 256, 0, s>>>(a.sc, (const bf16 *)k_host, (const bf16 *)v_host, KVL * HD);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=4096)
     ap.add_argument("--ctx", type=int, default=0, help="tokens already in the slot before the measured prompt")
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--by-kernel", action="store_true", help="a third pass that times every launcher call of the library by name")
     a = ap.parse_args()
     cfg = ModelConfig.full()
     if a.layers:
@@ -78,6 +79,41 @@ def main():
     for k, v in sorted(acc.items(), key=lambda kv: -kv[1]):
         print(f"  {k:46s} {v:8.1f} ms  {100 * v / total:5.1f} %")
     print(json.dumps({"tokens": a.tokens, "ctx": a.ctx, "ms": round(ms, 1), "tok_s": round(a.tokens / ms * 1e3), "split_ms": {k: round(v, 1) for k, v in acc.items()}}))
+    if a.by_kernel:
+        by = collections.defaultdict(float)
+        n_calls = collections.Counter()
+
+        class TimedLib:
+            """Every ``qwk_*`` launcher of the library, bracketed by CUDA events and a synchronize."""
+            def __init__(self, lib):
+                self._lib = lib
+
+            def __getattr__(self, name):
+                fn = getattr(self._lib, name)
+                if not name.startswith("qwk_"):
+                    return fn
+
+                def timed(*args):
+                    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s0.record()
+                    r = fn(*args)
+                    s1.record()
+                    torch.cuda.synchronize()
+                    by[name] += s0.elapsed_time(s1)
+                    n_calls[name] += 1
+                    return r
+                return timed
+        real = P.lib
+        P.lib = TimedLib(real)
+        eng.reset(0)
+        if a.ctx:
+            eng.prefill(0, toks[:a.ctx], want_logits=False)
+            by.clear()
+            n_calls.clear()
+        eng.prefill(0, toks[a.ctx:], want_logits=True)
+        P.lib = real
+        for k, v in sorted(by.items(), key=lambda kv: -kv[1]):
+            print(f"  {k:34s} {n_calls[k]:5d} calls {v:8.1f} ms")
 
 
 if __name__ == "__main__":

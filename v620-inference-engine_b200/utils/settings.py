@@ -50,6 +50,8 @@ class Settings:
     spill_policy: str = "auto"          # QW_SPILL_POLICY: auto | bind | preferred | interleave | process
     prefill_chunk: int = 4096           # QW_PREFILL_CHUNK
     prefill_piece: int = 2048           # QW_PREFILL_PIECE
+    qsa_attend_rows: bool = False       # QW_QSA_ATTEND_ROWS: token-major prefill attends with the decode kernels (CUDA cores)
+    moe_dequant_scratch: bool = False   # QW_MOE_DEQUANT_SCRATCH: token-major prefill converts a layer's q4 experts to bf16 before its GEMMs
     gdn_sequential: bool = False        # QW_GDN_SEQUENTIAL: token-major prefill scans GDN layers row by row (not chunked)
     spec_max_rows: int = 8              # QW_SPEC_MAX_ROWS: rows of one verification step
     weight_cache_dir: str = ""          # QW_WEIGHT_CACHE_DIR
