@@ -72,10 +72,12 @@ __global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__
     uint64_t *done = empty + TC_STAGES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BN;
-    int t0 = blockIdx.y * TC_BM, rows_valid = TC_BM, w0 = n0;
+    // Plain mode: blockIdx.x walks the row tiles of one column panel, so the CTAs in flight share one W panel and the
+    // (smaller) activation matrix stays in L2 while W streams through once.  Grouped mode: x walks the group's columns.
+    int n0 = blockIdx.y * TC_BN, t0 = blockIdx.x * TC_BM, rows_valid = TC_BM, w0 = n0;
     if (a.tiles) {
         const int4 tl = a.tiles[blockIdx.y];
+        n0 = blockIdx.x * TC_BN;
         t0 = tl.x;
         rows_valid = tl.y;
         w0 = tl.z + n0;
@@ -414,7 +416,7 @@ QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N,
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
         configured = true;
     }
-    dim3 grid((N + TC_BN - 1) / TC_BN, (T + TC_BM - 1) / TC_BM);
+    dim3 grid((T + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
     gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
