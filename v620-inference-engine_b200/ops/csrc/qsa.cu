@@ -630,7 +630,7 @@ QW_API int qwk_qsa_attend_mma(const float *q, int QL, int KVL, int M, const int 
     a.sc = k_host ? g_spill : SpillCache{};
     a.sel = sel; a.sel_n = sel_n; a.topk = topk; a.ratio = ratio; a.nsplit = 0;
     a.pm = nullptr; a.pl = nullptr; a.pacc = nullptr;
-    qsa_attend_mma_kernel<<<dim3(KVL, M), 128, ATT_SMEM, s>>>(a, proj, ld_proj, (bf16 *)o);
+    qsa_attend_mma_kernel<<<dim3(KVL, M), 128, ATT_SMEM, s>>>(a, proj, ld_proj, (bf16 *)o, g_err_ptr);
     if (a.sc.tags) spill_cache_fill_kernel<<<64, 256, 0, s>>>(a.sc, (const bf16 *)k_host, (const bf16 *)v_host, KVL * HD);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

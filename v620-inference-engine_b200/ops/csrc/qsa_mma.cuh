@@ -3,10 +3,12 @@
 // One block per (query row, local KV head): the query heads that share the KV head (<= 16; 12 in the full model at
 // one rank) are the 16 rows of the MMA tile, so the gathered K and V rows of a token are fetched once for all of
 // them.  The row's token list (every visible token below the budget, else the selected groups plus the open tail) is
-// walked in tiles of 64 tokens: rows gathered into padded shared memory by 16-byte async copies straight from the
-// paged pool (device pages, host pages or the spill cache), S = Q K^T and O += P V on mma.sync m16n8k16 bf16 with
+// walked in tiles of 64 tokens: rows gathered into padded shared memory by one 512-byte bulk-async copy per row
+// straight from the paged pool (device pages or the spill cache; rows that live in host pages are copied by their
+// thread with plain loads), completing on an mbarrier per tile, S = Q K^T and O += P V on mma.sync m16n8k16 bf16 with
 // fp32 accumulation, online softmax in fp32 with one running maximum per query head shared by the four warps.
-// The copies of the next tile's K overlap P V of this tile and the copies of its V overlap the next S.
+// The copies of the next tile's K overlap P V of this tile and the copies of its V overlap the next S.  Every wait on
+// a tile's mbarrier is bounded.
 // Output: o = softmax(..) V * sigmoid(gate) in bf16, with no partial buffers and no merge kernel
 // (role of the reference's qsa_attend_T + combine, src/kernels/qsa.hip:136-243).
 #pragma once
@@ -14,48 +16,60 @@
 constexpr int AT = 64;               // tokens per tile
 constexpr int KV_LD = HD + 8;        // shared row stride (bf16): 528 bytes keeps the 8 rows of an ldmatrix in distinct banks
 constexpr int P_LD = AT + 8;
-constexpr int ATT_SMEM = (2 * AT * KV_LD + 16 * P_LD) * 2 + (4 * 16 * 2) * 4;
+constexpr int ATT_SMEM = (2 * AT * KV_LD + 16 * P_LD) * 2 + (4 * 16 * 2) * 4 + 16;
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t saddr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(saddr));
 }
 
-// Issues the copies of one tile of K rows (which = 0) or V rows (which = 1).  Two threads per token; 16 chunks each.
-// Tokens past the list's end are zero-filled by plain stores.
-__device__ __forceinline__ void att_issue(const QsaAttendArgs &a, uint32_t dst_base, bf16 *dst_ptr, int which, int tile,
+// Starts the copies of one tile of K rows (which = 0) or V rows (which = 1): thread r < 64 owns token r of the tile
+// and arrives once on `bar` (64 arrivals complete a tile).  Device rows: one bulk-async copy of the head's 512 bytes.
+// Rows in host pages: copied here with plain loads.  Tokens past the list's end: zero-filled.
+__device__ __forceinline__ void att_issue(const QsaAttendArgs &a, bf16 *dst_tile, uint64_t *bar, int which, int tile,
                                           int count, int dense, const int *sel, int nb, int slot, int kvh, bool record) {
-    const int tid = threadIdx.x, r = tid >> 1, half = tid & 1;
+    const int r = threadIdx.x;
+    if (r >= AT) return;
+    bf16 *dst = dst_tile + r * KV_LD;
     const int t = tile * AT + r;
     if (t < count) {
         const int tok = list_token(t, dense, sel, a.ratio, a.topk, nb);
-        const bf16 *kp, *vp;
-        kv_rows_read(a.kv, a.sc, slot, tok, record && which == 0 && half == 0, kp, vp);
-        const char *src = reinterpret_cast<const char *>((which ? vp : kp) + kvh * HD) + half * 256;
-        const uint32_t d = dst_base + (uint32_t)(r * KV_LD * 2 + half * 256);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) cp_async16(d + i * 16, src + i * 16);
+        bool host;
+        const long long off = kv_off(a.kv, slot, tok, host);
+        const bf16 *kp = a.kv.k_dev + off, *vp = a.kv.v_dev + off;
+        bool from_host = false;
+        if (host) {
+            kv_rows_read(a.kv, a.sc, slot, tok, record && which == 0, kp, vp);
+            from_host = kp == a.kv.k_host + off;           // not in the spill cache
+        }
+        const bf16 *src = (which ? vp : kp) + kvh * HD;
+        if (!from_host) {
+            mbar_expect_tx(bar, HD * 2);
+            bulk_g2s(dst, src, HD * 2, bar);
+            return;
+        }
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+        uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll 8
+        for (int i = 0; i < HD * 2 / 16; ++i) d4[i] = s4[i];
     } else {
-        uint4 *d = reinterpret_cast<uint4 *>(reinterpret_cast<char *>(dst_ptr) + r * KV_LD * 2 + half * 256);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) d[i] = make_uint4(0u, 0u, 0u, 0u);
+        uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll 8
+        for (int i = 0; i < HD * 2 / 16; ++i) d4[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+    mbar_arrive(bar);
 }
 
 // grid (KVL, M), 128 threads.
-__global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a, const float *proj, int ld_proj, bf16 *o) {
+__global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a, const float *proj, int ld_proj, bf16 *o,
+                                                                ErrorWord *g_err) {
     extern __shared__ __align__(16) unsigned char att_sm[];
     bf16 *Ks = reinterpret_cast<bf16 *>(att_sm);             // [64][KV_LD]   (first: the 16 query rows, staged once)
     bf16 *Vs = Ks + AT * KV_LD;                              // [64][KV_LD]
     bf16 *Ps = Vs + AT * KV_LD;                              // [16][P_LD]
     float *s_max = reinterpret_cast<float *>(Ps + 16 * P_LD);    // [4][16]
     float *s_l = s_max + 64;                                 // [4][16]
+    uint64_t *kbar = reinterpret_cast<uint64_t *>(s_l + 64), *vbar = kbar + 1;     // one phase per tile
     const int kvh = blockIdx.x, m = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3;
     const int per_kv = a.QL / a.KVL, h0 = kvh * per_kv;
@@ -66,6 +80,11 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
     const int ntiles = (count + AT - 1) / AT;
     const int *sel = a.sel + (long long)m * a.topk;
     const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
+    if (tid == 0) {
+        mbar_init(kbar, AT);
+        mbar_init(vbar, AT);
+        mbar_fence_init();
+    }
     const uint32_t ps_base = (uint32_t)__cvta_generic_to_shared(Ps);
     // ---- the query rows -> bf16 in shared memory -> A fragments held in registers for the whole walk
     for (int i = tid; i < 16 * (HD / 2); i += 128) {
@@ -80,10 +99,8 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
     for (int ks = 0; ks < 16; ++ks)
         ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], a_tile_addr(ks_base, KV_LD * 2, ks * 16, lane));
     __syncthreads();
-    att_issue(a, ks_base, Ks, 0, 0, count, dense, sel, nb, slot, kvh, kvh == 0);
-    cp_commit();
-    att_issue(a, vs_base, Vs, 1, 0, count, dense, sel, nb, slot, kvh, false);
-    cp_commit();
+    att_issue(a, Ks, kbar, 0, 0, count, dense, sel, nb, slot, kvh, kvh == 0);
+    att_issue(a, Vs, vbar, 1, 0, count, dense, sel, nb, slot, kvh, false);
     float acc[8][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n)
@@ -91,8 +108,7 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     for (int tile = 0; tile < ntiles; ++tile) {
-        cp_wait<1>();            // this tile's K rows have landed (its V rows may still be in flight)
-        __syncthreads();
+        mbar_wait(kbar, (unsigned)tile & 1u, g_err);        // this tile's K rows have landed (bounded; a time-out is recorded)
         // ---- S = Q K^T for this warp's 16 tokens
         float s[2][4];
 #pragma unroll
@@ -126,8 +142,7 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
         tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
         if (t4 == 0) { s_max[w * 16 + g] = tm0; s_max[w * 16 + g + 8] = tm1; }
         __syncthreads();         // every warp is past its reads of the K tile, too
-        if (tile + 1 < ntiles) att_issue(a, ks_base, Ks, 0, tile + 1, count, dense, sel, nb, slot, kvh, kvh == 0);
-        cp_commit();
+        if (tile + 1 < ntiles) att_issue(a, Ks, kbar, 0, tile + 1, count, dense, sel, nb, slot, kvh, kvh == 0);
         const float n0 = fmaxf(fmaxf(fmaxf(s_max[g], s_max[16 + g]), fmaxf(s_max[32 + g], s_max[48 + g])), mx0);
         const float n1 = fmaxf(fmaxf(fmaxf(s_max[g + 8], s_max[24 + g]), fmaxf(s_max[40 + g], s_max[56 + g])), mx1);
         // the first tile always holds a visible token, so n0 / n1 are finite
@@ -149,8 +164,8 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
             acc[n][0] *= c0; acc[n][1] *= c0;
             acc[n][2] *= c1; acc[n][3] *= c1;
         }
-        cp_wait<1>();            // this tile's V rows have landed (the next K tile may be in flight)
-        __syncthreads();         // P and V visible
+        __syncthreads();         // P visible
+        mbar_wait(vbar, (unsigned)tile & 1u, g_err);        // this tile's V rows have landed
         // ---- O += P V for this warp's 64 output dims
         {
             const int mid = lane >> 3;
@@ -169,10 +184,8 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
             }
         }
         __syncthreads();         // V, P and the maxima are free again
-        if (tile + 1 < ntiles) att_issue(a, vs_base, Vs, 1, tile + 1, count, dense, sel, nb, slot, kvh, false);
-        cp_commit();
+        if (tile + 1 < ntiles) att_issue(a, Vs, vbar, 1, tile + 1, count, dense, sel, nb, slot, kvh, false);
     }
-    cp_wait<0>();
     // ---- normalise, gate, store
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
