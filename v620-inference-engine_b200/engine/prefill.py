@@ -63,6 +63,8 @@ class Prefiller:
             "ple_e": z((T, c.hidden), bf), "ple_kv": z((T, (sc.ple_kv + 7) // 8 * 8), f32), "ple_send": z((T, 16), f32),
             "ple_gv": z((T, sc.xw), f32), "ple_nc": z((T, sc.xw), f32),
             "rows": z((8 * T,), i32),
+            "inv": z((Pn,), i32), "src_token": z((Pn,), i32),
+            "t13": z((Pn // 128 + sc.exp_l, 4), i32), "t2": z((Pn // 128 + sc.exp_l, 4), i32),
         }
         # the GDN scan of a chunk runs in its chunked (tensor-core) form; QW_GDN_SEQUENTIAL=1 keeps the row-by-row scan
         self.gdn_chunked = not settings.get().gdn_sequential
@@ -278,27 +280,11 @@ class Prefiller:
         self.gemm(b["bin"][:T], lw["Wrs"].data_ptr(), nrs, H, b["rs"][:T])
         self._ck(L.qwk_moe_route(_p(b["rs"]), self.nrs_ld, T, c.n_experts, k, sc.sffn_l, 0, E, _p(b["pe"]), _p(b["pw"]),
                                  _p(b["sh_h"]), s), "route")
-        # ---- expert sort (index arithmetic only)
-        flat = b["pe"][:T].reshape(-1).long()
-        Pn = flat.numel()
-        order = torch.sort(flat, stable=True).indices
-        counts = torch.bincount(flat, minlength=E)
-        ends = torch.cumsum(counts, 0)
-        offsets = ends - counts
-        inv = torch.empty(Pn, dtype=torch.int32, device=flat.device)
-        inv[order] = torch.arange(Pn, dtype=torch.int32, device=flat.device)
-        torch.index_select(b["bin"][:T], 0, order // k, out=b["xperm"][:Pn])
-        nt = (counts + 127) // 128
-        tend = torch.cumsum(nt, 0)
-        idx = torch.arange(self.max_tiles, device=flat.device)
-        e = torch.searchsorted(tend, idx, right=True).clamp(max=E - 1)
-        local = idx - (tend[e] - nt[e])
-        valid = (counts[e] - local * 128).clamp(0, 128)
-        valid = torch.where(idx < tend[-1], valid, torch.zeros_like(valid))
-        row0 = offsets[e] + local * 128
-        zero = torch.zeros_like(row0)
-        t13 = torch.stack([row0, valid, e * (2 * F), zero], 1).to(torch.int32).contiguous()
-        t2 = torch.stack([row0, valid, e * H, zero], 1).to(torch.int32).contiguous()
+        # ---- expert sort: pairs of one expert become consecutive rows; tile tables for the grouped GEMMs; row gather
+        Pn = T * k
+        inv, t13, t2 = b["inv"], b["t13"], b["t2"]
+        self._ck(L.qwk_moe_sort_T(_p(b["pe"]), T, k, E, 2 * F, H, self.max_tiles, _p(inv), _p(b["src_token"]), _p(t13), _p(t2),
+                                  _p(b["bin"]), b["bin"].stride(0), H, _p(b["xperm"]), s), "moe_sort")
         if self.q4_fused:
             # q4 words converted inside the GEMM's W-operand producer warps: no bf16 copy of the layer's experts
             self._ck(L.qwk_gemm_q4_tc_grouped(_p(b["xperm"]), P(lw["w13"].data_ptr()), P(lw["s13"].data_ptr()), _p(b["h13"]),

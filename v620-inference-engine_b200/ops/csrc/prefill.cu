@@ -76,6 +76,76 @@ __global__ void q4_dequant_kernel(const uint32_t *w, const bf16 *scale, int K, b
     *reinterpret_cast<uint4 *>(out + i * 8) = o;
 }
 
+// Expert sort of a chunk's (token, choice) pairs in one block: rows of one expert become consecutive.
+// pair_expert [P] (local expert id, or < 0 / >= E: not on this rank) -> inv [P] (pair -> sorted row, -1 = none),
+// src_token [P] (sorted row -> token), and the two tile tables of the grouped GEMMs ({first row, valid rows, first W row of
+// the expert, 0} per 128-row tile; unused entries zero).  The order of an expert's rows among themselves follows the
+// atomics and may differ between runs; every row's result is independent of where it sits, so outputs do not.
+// One block of 1024 threads; E <= 1024.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int *pair_expert, int P, int top_k, int E, int Nw13, int Nw2,
+                                                        int max_tiles, int *inv, int *src_token, int4 *t13, int4 *t2) {
+    __shared__ int cnt[1024], off[1024], tb[1024], cur[1024];
+    __shared__ int warp_tot[2][32];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    cnt[tid] = 0;
+    cur[tid] = 0;
+    for (int i = tid; i < max_tiles; i += 1024) t13[i] = t2[i] = make_int4(0, 0, 0, 0);
+    __syncthreads();
+    for (int i = tid; i < P; i += 1024) {
+        const int e = pair_expert[i];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    // exclusive scans of the counts (row offsets) and of the tile counts (tile-table offsets)
+    const int c = tid < E ? cnt[tid] : 0, nt = (c + 127) >> 7;
+    int sc = c, st = nt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, st, o);
+        if (lane >= o) { sc += a; st += b; }
+    }
+    if (lane == 31) { warp_tot[0][wid] = sc; warp_tot[1][wid] = st; }
+    __syncthreads();
+    if (wid == 0) {
+        int a = warp_tot[0][lane], b = warp_tot[1][lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b, o);
+            if (lane >= o) { a += x; b += y; }
+        }
+        warp_tot[0][lane] = a;
+        warp_tot[1][lane] = b;
+    }
+    __syncthreads();
+    const int row0 = sc - c + (wid ? warp_tot[0][wid - 1] : 0), tile0 = st - nt + (wid ? warp_tot[1][wid - 1] : 0);
+    off[tid] = row0;
+    tb[tid] = tile0;
+    if (tid < E)
+        for (int j = 0; j < nt && tile0 + j < max_tiles; ++j) {
+            const int valid = min(128, c - j * 128);
+            t13[tile0 + j] = make_int4(row0 + j * 128, valid, tid * Nw13, 0);
+            t2[tile0 + j] = make_int4(row0 + j * 128, valid, tid * Nw2, 0);
+        }
+    __syncthreads();
+    for (int i = tid; i < P; i += 1024) {
+        const int e = pair_expert[i];
+        int r = -1;
+        if (e >= 0 && e < E) {
+            r = off[e] + atomicAdd(&cur[e], 1);
+            src_token[r] = i / top_k;
+        }
+        inv[i] = r;
+    }
+}
+
+// xperm[r][:] = x[src_token[r]][:] for the first n_rows sorted rows (bf16 rows of H elements, H % 8 == 0).  grid n_rows.
+__global__ void moe_gather_rows_kernel(const bf16 *x, int ldx, const int *src_token, int H, bf16 *xperm) {
+    const int r = blockIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + (long long)src_token[r] * ldx);
+    uint4 *dst = reinterpret_cast<uint4 *>(xperm + (long long)r * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 // h13 [P][2F] bf16 (gate | up) -> h [P][F] = silu(gate) * up.
 __global__ void swiglu_T_kernel(const bf16 *h13, int F, bf16 *h, long long total) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -139,5 +209,18 @@ QW_API int qwk_moe_combine_T(const float *y, int ld_y, const int *inv, const flo
                              int H, float *out, int T, cudaStream_t s) {
     const long long total = (long long)T * H;
     moe_combine_T_kernel<<<blocks_for(total, 256), 256, 0, s>>>(y, ld_y, inv, pair_w, top_k, shared, H, out, total);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Expert sort + row gather of a prefill chunk (see moe_sort_kernel).  pair_expert [T*top_k]; x bf16 [T][ldx];
+// outputs inv [T*top_k], src_token [T*top_k] (scratch), t13 / t2 [max_tiles] int4, xperm bf16 [T*top_k][H].  With all pairs
+// local, xperm holds T*top_k rows; rows past the last local pair are left as they were.
+QW_API int qwk_moe_sort_T(const int *pair_expert, int T, int top_k, int E, int Nw13, int Nw2, int max_tiles, int *inv,
+                          int *src_token, void *t13, void *t2, const void *x, int ldx, int H, void *xperm, cudaStream_t s) {
+    if (E > 1024 || (H & 7) || (ldx & 7)) return -1;
+    const int P = T * top_k;
+    cudaMemsetAsync(src_token, 0, sizeof(int) * (size_t)P, s);
+    moe_sort_kernel<<<1, 1024, 0, s>>>(pair_expert, P, top_k, E, Nw13, Nw2, max_tiles, inv, src_token, (int4 *)t13, (int4 *)t2);
+    moe_gather_rows_kernel<<<P, 256, 0, s>>>((const bf16 *)x, ldx, src_token, H, (bf16 *)xperm);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
