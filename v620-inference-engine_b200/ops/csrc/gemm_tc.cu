@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__
 // Grouped GEMM with the weights in q4 (group 128, bf16 scales): the expert products of token-major prefill without a
 // bf16 copy of the layer's experts.  Same tile, pipeline and epilogue as gemm_tc_kernel; the W operand of a stage is
 // not loaded by TMA but produced by four extra warps: thread r of them owns row r of the 128 x 64 W tile, fetches its
-// 8 q4 words (32 bytes, one sector) four k blocks ahead, converts them to the eight 16-byte bf16 chunks of the row
+// 8 q4 words (32 bytes, one sector) and the block's scale four k blocks ahead, converts them to the eight 16-byte bf16 chunks of the row
 // with the row's scale (the same rounding as the stand-alone dequantisation) and stores them where the 128-byte
 // swizzle puts them (chunk c of row r at chunk c ^ (r & 7)); a proxy fence makes the stores visible to the tensor
 // core's reads, and the thread arrives on the stage's "full" barrier (1 TMA arrival + 128 producer arrivals).
@@ -272,11 +272,18 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constan
         const int wpr = a.K >> 3, spr = a.K >> 7;
         const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr);
         const bf16 *sc_row = scale + (row_ok ? wrow : 0) * spr;
+        const unsigned short *sc_bits = reinterpret_cast<const unsigned short *>(sc_row);
         uint4 ring[Q4_AHEAD][2];
+        unsigned short sring[Q4_AHEAD];          // the k block's scale travels with its words: no dependent load in the loop
 #pragma unroll
         for (int i = 0; i < Q4_AHEAD; ++i) {
             ring[i][0] = ring[i][1] = make_uint4(0u, 0u, 0u, 0u);
-            if (row_ok && i < kblocks) { ring[i][0] = __ldg(src + 2 * i); ring[i][1] = __ldg(src + 2 * i + 1); }
+            sring[i] = 0;
+            if (row_ok && i < kblocks) {
+                ring[i][0] = __ldg(src + 2 * i);
+                ring[i][1] = __ldg(src + 2 * i + 1);
+                sring[i] = __ldg(sc_bits + (i >> 1));
+            }
         }
         bool ok = true;
         for (int kb0 = 0; kb0 < kblocks && ok; kb0 += Q4_AHEAD) {
@@ -286,11 +293,12 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constan
                 if (kb >= kblocks) break;
                 const int s = kb % TC_STAGES;
                 const uint4 q0 = ring[i][0], q1 = ring[i][1];
+                const float sc = __uint_as_float((uint32_t)sring[i] << 16);       // bf16 bits -> fp32 (0 for rows outside)
                 if (row_ok && kb + Q4_AHEAD < kblocks) {
                     ring[i][0] = __ldg(src + 2 * (kb + Q4_AHEAD));
                     ring[i][1] = __ldg(src + 2 * (kb + Q4_AHEAD) + 1);
+                    sring[i] = __ldg(sc_bits + ((kb + Q4_AHEAD) >> 1));
                 }
-                const float sc = row_ok ? __bfloat162float(sc_row[kb >> 1]) : 0.f;
                 if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
                 unsigned char *dst = smem + s * TC_STAGE_BYTES + TC_A_BYTES + r * 128;
                 const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};

@@ -7,30 +7,48 @@
 namespace qw {
 
 // grid (T, hc), 256 threads.  X[t][s][:] (+= pend[t][:] * 2*sigmoid(inj[t][s]/hc)); xn = bf16(X * w1 * rsqrt(mean X^2 + eps)).
+// SH % 4 == 0, SH <= 4096: a thread keeps its (up to four) float4 pieces of the row in registers between the two passes.
 __global__ void __launch_bounds__(256) hc_prenorm_T_kernel(float *X, const float *pend, int ld_pend, const float *inj,
                                                            const float *w1, int SH, int hc, float eps, bf16 *xn) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, s = blockIdx.y;
-    float *x = X + ((long long)t * hc + s) * SH;
-    float coef = 0.f;
-    if (pend) coef = 2.f * sigmoidf_(inj[(long long)t * hc + s] / float(hc));
-    float v[16];            // SH <= 4096
-    float ss = 0.f;
-    int n = 0;
-    for (int c = threadIdx.x; c < SH; c += 256, ++n) {
-        float a = x[c];
-        if (pend) {
-            a = fmaf(pend[(long long)t * ld_pend + c], coef, a);
-            x[c] = a;
-        }
-        v[n] = a;
-        ss = fmaf(a, a, ss);
+    float4 *x = reinterpret_cast<float4 *>(X + ((long long)t * hc + s) * SH);
+    const float4 *pe = reinterpret_cast<const float4 *>(pend + (pend ? (long long)t * ld_pend : 0));
+    const int n4 = SH >> 2;
+    float4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        v[i] = c < n4 ? x[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    float ss = 0.f;
+    if (pend) {
+        const float coef = 2.f * sigmoidf_(inj[(long long)t * hc + s] / float(hc));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < n4) {
+                const float4 p = pe[c];
+                v[i].x = fmaf(p.x, coef, v[i].x); v[i].y = fmaf(p.y, coef, v[i].y);
+                v[i].z = fmaf(p.z, coef, v[i].z); v[i].w = fmaf(p.w, coef, v[i].w);
+                x[c] = v[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     ss = block_sum<256>(ss, scratch);
     const float r = rsqrtf(ss / float(SH) + eps);
-    n = 0;
-    for (int c = threadIdx.x; c < SH; c += 256, ++n)
-        xn[((long long)t * hc + s) * SH + c] = __float2bfloat16(v[n] * w1[s * SH + c] * r);
+    const float4 *w4 = reinterpret_cast<const float4 *>(w1 + (long long)s * SH);
+    uint2 *o = reinterpret_cast<uint2 *>(xn + ((long long)t * hc + s) * SH);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < n4) {
+            const float4 w = w4[c];
+            o[c] = make_uint2(pack_bf16(v[i].x * w.x * r, v[i].y * w.y * r), pack_bf16(v[i].z * w.z * r, v[i].w * w.w * r));
+        }
+    }
 }
 
 // d [T][ld_d] fp32 (R + n_inj columns) -> u bf16 [T][R] = silu(d/hc), inj fp32 [T][n_inj].
@@ -45,17 +63,24 @@ __global__ void hc_mid_T_kernel(const float *d, int ld_d, int R, int n_inj, int 
     else inj[t * n_inj + (j - R)] = v;
 }
 
-// g [T][SH*hc] fp32 with columns ordered (c, s); bin[t][c] = mean_s sigmoid(g[t][c][s]) * xn[t][s][c].  hc == 4.
-__global__ void hc_mix_T_kernel(const float *g, const bf16 *xn, int SH, bf16 *bin, int ld_bin, long long total) {
+// g [T][SH*hc] fp32 with columns ordered (c, s); bin[t][c] = mean_s sigmoid(g[t][c][s]) * xn[t][s][c].  hc == 4, SH even,
+// ld_bin even.  One thread per two neighbouring columns.
+__global__ void hc_mix_T_kernel(const float *g, const bf16 *xn, int SH, bf16 *bin, int ld_bin, long long total2) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const long long t = i / SH;
-    const int c = (int)(i - t * SH);
-    const float4 gg = *reinterpret_cast<const float4 *>(g + (t * SH + c) * 4);
+    if (i >= total2) return;
+    const int h2 = SH >> 1;
+    const long long t = i / h2;
+    const int c = (int)(i - t * h2) * 2;
+    const float4 g0 = *reinterpret_cast<const float4 *>(g + (t * SH + c) * 4);
+    const float4 g1 = *reinterpret_cast<const float4 *>(g + (t * SH + c + 1) * 4);
     const bf16 *x = xn + t * 4 * SH + c;
-    const float v = sigmoidf_(gg.x) * __bfloat162float(x[0]) + sigmoidf_(gg.y) * __bfloat162float(x[SH]) +
-                    sigmoidf_(gg.z) * __bfloat162float(x[2 * SH]) + sigmoidf_(gg.w) * __bfloat162float(x[3 * SH]);
-    bin[t * ld_bin + c] = __float2bfloat16(v * 0.25f);
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const bf162 *>(x));
+    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const bf162 *>(x + SH));
+    const float2 x2 = __bfloat1622float2(*reinterpret_cast<const bf162 *>(x + 2 * SH));
+    const float2 x3 = __bfloat1622float2(*reinterpret_cast<const bf162 *>(x + 3 * SH));
+    const float v0 = sigmoidf_(g0.x) * x0.x + sigmoidf_(g0.y) * x1.x + sigmoidf_(g0.z) * x2.x + sigmoidf_(g0.w) * x3.x;
+    const float v1 = sigmoidf_(g1.x) * x0.y + sigmoidf_(g1.y) * x1.y + sigmoidf_(g1.z) * x2.y + sigmoidf_(g1.w) * x3.y;
+    *reinterpret_cast<bf162 *>(bin + t * ld_bin + c) = __floats2bfloat162_rn(v0 * 0.25f, v1 * 0.25f);
 }
 
 // q4 (engine order) rows -> bf16 rows.  One thread per word (8 values).
@@ -180,7 +205,7 @@ static inline unsigned blocks_for(long long n, int per) { return (unsigned)((n +
 
 QW_API int qwk_hc_prenorm_T(float *X, const float *pend, int ld_pend, const float *inj, const float *w1, int SH, int hc,
                             float eps, void *xn, int T, cudaStream_t s) {
-    if (SH > 4096) return -1;
+    if (SH > 4096 || (SH & 3) || (ld_pend & 3)) return -1;
     hc_prenorm_T_kernel<<<dim3(T, hc), 256, 0, s>>>(X, pend, ld_pend, inj, w1, SH, hc, eps, (bf16 *)xn);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -190,7 +215,8 @@ QW_API int qwk_hc_mid_T(const float *d, int ld_d, int R, int n_inj, int hc, void
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 QW_API int qwk_hc_mix_T(const float *g, const void *xn, int SH, void *bin, int ld_bin, int T, cudaStream_t s) {
-    const long long total = (long long)T * SH;
+    if ((SH & 1) || (ld_bin & 1)) return -1;
+    const long long total = (long long)T * (SH >> 1);
     hc_mix_T_kernel<<<blocks_for(total, 256), 256, 0, s>>>(g, (const bf16 *)xn, SH, (bf16 *)bin, ld_bin, total);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
