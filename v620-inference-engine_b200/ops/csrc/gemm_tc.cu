@@ -196,16 +196,18 @@ __global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__
 // ------------------------------------------------------------------------------------------------------------------
 // Grouped GEMM with the weights in q4 (group 128, bf16 scales): the expert products of token-major prefill without a
 // bf16 copy of the layer's experts.  Same tile, pipeline and epilogue as gemm_tc_kernel; the W operand of a stage is
-// not loaded by TMA but produced by four extra warps: thread r of them owns row r of the 128 x 64 W tile, fetches its
-// 8 q4 words (32 bytes, one sector) and the block's scale four k blocks ahead, converts them to the eight 16-byte bf16 chunks of the row
-// with the row's scale (the same rounding as the stand-alone dequantisation) and stores them where the 128-byte
+// not loaded by TMA but produced by eight extra warps: two threads own row r of the 128 x 64 W tile, each fetches 4 q4
+// words (16 bytes) and the block's scale four k blocks ahead, converts them to four 16-byte bf16 chunks of the row with
+// packed bf16 arithmetic (the same values as the stand-alone dequantisation) and stores them where the 128-byte
 // swizzle puts them (chunk c of row r at chunk c ^ (r & 7)); a proxy fence makes the stores visible to the tensor
-// core's reads, and the thread arrives on the stage's "full" barrier (1 TMA arrival + 128 producer arrivals).
+// core's reads, and the thread arrives on the stage's "full" barrier (1 TMA arrival + 256 producer arrivals).  What
+// bounds the kernel is how fast the producer warps turn words into tiles (~150 instructions per thread and k block),
+// hence eight of them and two-wide arithmetic.
 // (Role of the reference's moe_gate_up_T / moe_down_T, src/kernels/moe_experts.hip:17-27.)
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int Q4_AHEAD = 4;
 
-__global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constant__ CUtensorMap mapA, GemmTcArgs a,
+__global__ void __launch_bounds__(448, 2) gemm_tc_q4_kernel(const __grid_constant__ CUtensorMap mapA, GemmTcArgs a,
                                                             const uint32_t *Wq, const bf16 *scale, long long w_rows) {
     extern __shared__ unsigned char raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constan
     const int kblocks = (a.K + TC_BK - 1) / TC_BK;
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(full + s, 1 + 128);
+            mbar_init(full + s, 1 + 256);
             mbar_init(empty + s, 1);
         }
         mbar_init(done, 1);
@@ -265,26 +267,25 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constan
             umma_commit(done);
         }
     } else if (warp >= 6) {
-        // W producers: thread r = row r of the tile
-        const int r = threadIdx.x - 192;
+        // W producers: two threads per row of the tile, 32 k values (4 words, 4 chunks) each
+        const int p = threadIdx.x - 192, r = p >> 1, hf = p & 1;
         const long long wrow = (long long)w0 + r;
         const bool row_ok = n0 + r < a.N && wrow < w_rows;
         const int wpr = a.K >> 3, spr = a.K >> 7;
-        const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr);
-        const bf16 *sc_row = scale + (row_ok ? wrow : 0) * spr;
-        const unsigned short *sc_bits = reinterpret_cast<const unsigned short *>(sc_row);
-        uint4 ring[Q4_AHEAD][2];
+        const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr) + hf;
+        const unsigned short *sc_bits = reinterpret_cast<const unsigned short *>(scale + (row_ok ? wrow : 0) * spr);
+        uint4 ring[Q4_AHEAD];
         unsigned short sring[Q4_AHEAD];          // the k block's scale travels with its words: no dependent load in the loop
 #pragma unroll
         for (int i = 0; i < Q4_AHEAD; ++i) {
-            ring[i][0] = ring[i][1] = make_uint4(0u, 0u, 0u, 0u);
+            ring[i] = make_uint4(0u, 0u, 0u, 0u);
             sring[i] = 0;
             if (row_ok && i < kblocks) {
-                ring[i][0] = __ldg(src + 2 * i);
-                ring[i][1] = __ldg(src + 2 * i + 1);
+                ring[i] = __ldg(src + 2 * i);
                 sring[i] = __ldg(sc_bits + (i >> 1));
             }
         }
+        const bf162 off2 = __floats2bfloat162_rn(136.f, 136.f);
         bool ok = true;
         for (int kb0 = 0; kb0 < kblocks && ok; kb0 += Q4_AHEAD) {
 #pragma unroll
@@ -292,25 +293,28 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_q4_kernel(const __grid_constan
                 const int kb = kb0 + i;
                 if (kb >= kblocks) break;
                 const int s = kb % TC_STAGES;
-                const uint4 q0 = ring[i][0], q1 = ring[i][1];
-                const float sc = __uint_as_float((uint32_t)sring[i] << 16);       // bf16 bits -> fp32 (0 for rows outside)
+                const uint4 q = ring[i];
+                // scale as a bf16 pair; (nibble - 8) is exact in bf16 and its product with a bf16 scale, rounded once to bf16,
+                // equals the fp32 product rounded to bf16: the stand-alone conversion's values bit for bit
+                const uint32_t sb = (uint32_t)sring[i] | ((uint32_t)sring[i] << 16);
+                const bf162 sc2 = *reinterpret_cast<const bf162 *>(&sb);
                 if (row_ok && kb + Q4_AHEAD < kblocks) {
-                    ring[i][0] = __ldg(src + 2 * (kb + Q4_AHEAD));
-                    ring[i][1] = __ldg(src + 2 * (kb + Q4_AHEAD) + 1);
+                    ring[i] = __ldg(src + 2 * (kb + Q4_AHEAD));
                     sring[i] = __ldg(sc_bits + ((kb + Q4_AHEAD) >> 1));
                 }
                 if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
                 unsigned char *dst = smem + s * TC_STAGE_BYTES + TC_A_BYTES + r * 128;
-                const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float e0, e1;
-                    uint4 o;
-                    q4_pair(words[c], 0, e0, e1); o.x = pack_bf16(e0 * sc, e1 * sc);
-                    q4_pair(words[c], 1, e0, e1); o.y = pack_bf16(e0 * sc, e1 * sc);
-                    q4_pair(words[c], 2, e0, e1); o.z = pack_bf16(e0 * sc, e1 * sc);
-                    q4_pair(words[c], 3, e0, e1); o.w = pack_bf16(e0 * sc, e1 * sc);
-                    *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o;
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t bits = ((words[c] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+                        const bf162 v = __hmul2(__hsub2(*reinterpret_cast<bf162 *>(&bits), off2), sc2);
+                        o[j] = *reinterpret_cast<const uint32_t *>(&v);
+                    }
+                    *reinterpret_cast<uint4 *>(dst + (((hf * 4 + c) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(full + s);
@@ -468,6 +472,6 @@ QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *sca
         configured = true;
     }
     dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
-    gemm_tc_q4_kernel<<<grid, 320, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
+    gemm_tc_q4_kernel<<<grid, 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
