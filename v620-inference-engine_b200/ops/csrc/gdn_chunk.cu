@@ -87,14 +87,14 @@ __device__ __forceinline__ void load_tile(float *dst, int ld, const float *qkv, 
 // ------------------------------------------------------------------------------------------------
 // 1. state-independent part of every chunk
 // ------------------------------------------------------------------------------------------------
-constexpr int PREP_SMEM = (2 * CC * LDA + CC * LDP + 2 * CC) * 4;
+constexpr int PREP_SMEM = (2 * CC * LDA + 2 * CC) * 4;      // 68 KB: three blocks per SM
 
-__global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(GdnChunkArgs a) {
+__global__ void __launch_bounds__(256, 3) gdn_chunk_prep_kernel(GdnChunkArgs a) {
     extern __shared__ __align__(16) float sm[];
     float *Ks = sm;                      // [64][LDA]
     float *Qs = Ks + CC * LDA;           // [64][LDA]
-    float *As = Qs + CC * LDA;           // [64][LDP]
-    float *gs = As + CC * LDP;           // [64] cumulative log decay
+    float *As = Qs;                      // [64][LDP]  takes Q's place once Q K^T is done
+    float *gs = Qs + CC * LDA;           // [64] cumulative log decay
     float *bs = gs + CC;                 // [64] beta
     const int ch = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(GdnChunkArgs a) {
             mma_tf32(aqk[n], fq, b0, b1);
         }
     }
+    __syncthreads();                     // every warp is done reading Q before A overwrites it
     float *Pg = a.P + ((long long)ch * a.VL + h) * CC * CC;
 #pragma unroll
     for (int n = 0; n < 4; ++n)

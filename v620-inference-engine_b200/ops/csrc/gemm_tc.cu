@@ -9,8 +9,8 @@
 //   warp 1   : allocates 128 TMEM columns, and one thread issues tcgen05.mma (M=128, N=128, K=16, four per
 //              k block) reading both operands straight from shared memory through matrix descriptors;
 //              tcgen05.commit releases a stage ("empty" mbarrier) and finally signals the epilogue;
-//   warps 2-5: epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32 output rows),
-//              convert and store.
+//   warps 2-9: epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32 output rows; warps 2-5 the
+//              first 64 columns, warps 6-9 the other 64), convert and store.
 // Two CTAs share an SM (3 stages x 32 KB and 128 of the 512 TMEM columns each), so the prologue and the epilogue of
 // one tile run under the main loop of the other; with 10-40 k blocks per tile that matters more than ring depth.
 // Every mbarrier wait is bounded; a wait that runs out records an error, the pipeline drains and the
@@ -63,7 +63,7 @@ struct GemmTcArgs {
     const int4 *tiles;
 };
 
-__global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+__global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                          const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
     extern __shared__ unsigned char raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -139,9 +139,10 @@ __global__ void __launch_bounds__(192, 2) gemm_tc_kernel(const __grid_constant__
         const int q = warp & 3;
         const int row = t0 + q * 32 + lane;
         const bool row_ok = row < a.T && q * 32 + lane < rows_valid;
+        const int cbeg = warp < 6 ? 0 : TC_BN / 2;          // two warps per lane quarter, half of the columns each
         if (ok) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+            for (int c0 = cbeg; c0 < cbeg + TC_BN / 2; c0 += 32) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
                 asm volatile(
@@ -429,7 +430,7 @@ QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N,
         configured = true;
     }
     dim3 grid((T + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
-    gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
+    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -450,7 +451,7 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
     dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
-    gemm_tc_kernel<<<grid, 192, TC_SMEM, s>>>(mA, mW, a);
+    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
