@@ -2,18 +2,22 @@
 // tensor memory, fp32 or bf16 output (prefill path: projections, mixers, router with fp32 output,
 // lm_head; role of the reference's rocBLAS call sites, src/kernels/gemm.hip:10-18).
 //
-// One CTA computes a 128 x 128 output tile.  Warp roles:
+// Persistent CTAs (two per SM) walk the 128 x 128 output tiles round-robin.  Warp roles:
 //   warp 0   : TMA producer - one thread issues cp.async.bulk.tensor loads (no multicast) of the
 //              128 x 64 A tile and the 128 x 64 W tile of each k block into a 3-stage ring of
 //              128B-swizzled shared-memory tiles, completing on the stage's "full" mbarrier;
-//   warp 1   : allocates 128 TMEM columns, and one thread issues tcgen05.mma (M=128, N=128, K=16, four per
-//              k block) reading both operands straight from shared memory through matrix descriptors;
-//              tcgen05.commit releases a stage ("empty" mbarrier) and finally signals the epilogue;
+//   warp 1   : allocates 256 TMEM columns (two accumulators), and one thread issues tcgen05.mma (M=128, N=128, K=16,
+//              four per k block) reading both operands straight from shared memory through matrix descriptors;
+//              tcgen05.commit releases a stage ("empty" mbarrier) and, after a tile's last k block, signals that
+//              tile's accumulator ("done" mbarrier of the buffer);
 //   warps 2-9: epilogue - tcgen05.ld the accumulator (each warp its 32 TMEM lanes = 32 output rows; warps 2-5 the
-//              first 64 columns, warps 6-9 the other 64), convert and store.
-// Two CTAs share an SM (3 stages x 32 KB and 128 of the 512 TMEM columns each), so the prologue and the epilogue of
-// one tile run under the main loop of the other; with 10-40 k blocks per tile that matters more than ring depth.
-// Every mbarrier wait is bounded; a wait that runs out records an error, the pipeline drains and the
+//              first 64 columns, warps 6-9 the other 64), convert and store, then hand the buffer back
+//              ("acc_empty" mbarrier, one arrival per warp).
+// The ring and the barriers' phases run on across tiles, so the loads and MMAs of the next tile start while the
+// epilogue of this one drains the other accumulator; barrier set-up, the TMEM allocation and the tensor-map fetch are
+// paid once per CTA, not once per tile (what weighed on the products with 5-10 k blocks per tile).  Two CTAs share
+// an SM: 3 stages x 32 KB and 256 of the 512 TMEM columns each.
+// Every mbarrier wait is bounded; a wait that runs out records an error, the roles leave their loops and the
 // TMEM allocation is released before the kernel returns.
 #include <cuda.h>
 
@@ -25,6 +29,7 @@ constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;     // 16 KB each
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int TC_TMEM_COLS = 2 * TC_BN;          // two accumulators
 
 __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
     // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
@@ -59,139 +64,209 @@ struct GemmTcArgs {
     bf16 *C16;
     int T, N, K, ldc;
     ErrorWord *err;
-    // grouped mode (expert-sorted rows): tiles[blockIdx.y] = {first A row, valid rows, first W row of the group, -}
+    // grouped mode (expert-sorted rows): tiles[entry] = {first A row, valid rows, first W row of the group, -}
     const int4 *tiles;
+    int total, tiles_t, tiles_n;     // linear tile ids 0..total-1; plain: id = n * tiles_t + t; grouped: id = entry * tiles_n + n
 };
 
-__global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
-                                                         const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
-    extern __shared__ unsigned char raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);
-    uint64_t *empty = full + TC_STAGES;
-    uint64_t *done = empty + TC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Plain mode: blockIdx.x walks the row tiles of one column panel, so the CTAs in flight share one W panel and the
-    // (smaller) activation matrix stays in L2 while W streams through once.  Grouped mode: x walks the group's columns.
-    int n0 = blockIdx.y * TC_BN, t0 = blockIdx.x * TC_BM, rows_valid = TC_BM, w0 = n0;
+struct TileAt {
+    int t0, rows_valid, n0, w0;
+};
+// Tile `id` of the launch; false for an unused entry of the tile table (every role skips it alike).
+__device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) {
     if (a.tiles) {
-        const int4 tl = a.tiles[blockIdx.y];
-        n0 = blockIdx.x * TC_BN;
-        t0 = tl.x;
-        rows_valid = tl.y;
-        w0 = tl.z + n0;
-        if (rows_valid <= 0) return;          // unused entry of the tile table (uniform for the CTA, before any barrier)
+        const int4 tl = __ldg(a.tiles + id / a.tiles_n);
+        t.n0 = (id % a.tiles_n) * TC_BN;
+        t.t0 = tl.x;
+        t.rows_valid = tl.y;
+        t.w0 = tl.z + t.n0;
+        return tl.y > 0;
     }
-    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    // plain: the row tiles of one column panel are neighbours, so the CTAs in flight share a W panel and the (smaller)
+    // activation matrix stays in L2 while W streams through once
+    t.n0 = (id / a.tiles_t) * TC_BN;
+    t.t0 = (id % a.tiles_t) * TC_BM;
+    t.rows_valid = TC_BM;
+    t.w0 = t.n0;
+    return true;
+}
+
+// One 32-column piece of an accumulator row -> C.
+__device__ __forceinline__ void store_piece(const GemmTcArgs &a, int row, int col0, const uint32_t (&v)[32]) {
+    const int nmax = a.N - col0;
+    if (a.C32) {
+        float *o = a.C32 + (long long)row * a.ldc + col0;
+        if (nmax >= 32 && ((a.ldc | col0) & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        } else {
+            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
+        }
+    } else {
+        bf16 *o = a.C16 + (long long)row * a.ldc + col0;
+        if (nmax >= 32 && ((a.ldc | col0) & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                pk.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                pk.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                pk.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                pk.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                *reinterpret_cast<uint4 *>(o + j) = pk;
+            }
+        } else {
+            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __float2bfloat16(__uint_as_float(v[j]));
+        }
+    }
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// The epilogue role of both kernels: warps `first_warp` .. `first_warp + n_warps - 1` (n_warps = 4: all 128 columns per warp;
+// 8: half of them), for every tile of this CTA in order.
+__device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem, uint64_t *done, uint64_t *acc_empty,
+                                              int warp, int lane, int first_warp, int n_warps) {
+    const int q = warp & 3;
+    const int cbeg = (n_warps == 8 && warp >= first_warp + 4) ? TC_BN / 2 : 0;
+    const int cend = n_warps == 8 ? cbeg + TC_BN / 2 : TC_BN;
+    int j = 0;
+    for (int id = blockIdx.x; id < a.total; id += gridDim.x) {
+        TileAt t;
+        if (!tile_at(a, id, t)) continue;
+        const int b = j & 1;
+        if (!mbar_wait(done + b, (unsigned)(j >> 1) & 1u, a.err)) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = t.t0 + q * 32 + lane;
+        const bool row_ok = row < a.T && q * 32 + lane < t.rows_valid;
+#pragma unroll 1
+        for (int c0 = cbeg; c0 < cend; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_BN + c0), v);
+            if (row_ok) store_piece(a, row, t.n0 + c0, v);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + b);
+        ++j;
+    }
+}
+
+// The MMA role of both kernels (one thread).
+__device__ __forceinline__ void mma_role(const GemmTcArgs &a, unsigned char *smem, uint32_t tmem, uint64_t *full, uint64_t *empty,
+                                         uint64_t *done, uint64_t *acc_empty, int kblocks) {
+    // instruction descriptor: D fp32, A/B bf16, both K-major, N and M of the tile
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    int j = 0;
+    unsigned it = 0;
+    for (int id = blockIdx.x; id < a.total; id += gridDim.x) {
+        TileAt t;
+        if (!tile_at(a, id, t)) continue;
+        const int b = j & 1;
+        if (j >= 2 && !mbar_wait(acc_empty + b, (unsigned)((j >> 1) - 1) & 1u, a.err)) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            const unsigned s = it % TC_STAGES;
+            if (!mbar_wait(full + s, (it / TC_STAGES) & 1u, a.err)) return;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k) {
+                const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
+                umma_bf16(tmem + (uint32_t)(b * TC_BN), da, db, idesc, (kb | k) ? 1u : 0u);
+            }
+            umma_commit(empty + s);          // the stage is free once these MMAs have read it
+        }
+        umma_commit(done + b);               // this tile's accumulator is complete
+        ++j;
+    }
+}
+
+// Shared set-up of both kernels: barriers, TMEM allocation (warp 1), and the pointers into shared memory.
+struct TcShared {
+    unsigned char *smem;
+    uint64_t *full, *empty, *done, *acc_empty;
+    uint32_t tmem;
+};
+__device__ __forceinline__ TcShared tc_setup(unsigned char *raw, int warp, unsigned full_count, unsigned acc_empty_count) {
+    TcShared t;
+    t.smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    t.full = reinterpret_cast<uint64_t *>(t.smem + TC_STAGES * TC_STAGE_BYTES);
+    t.empty = t.full + TC_STAGES;
+    t.done = t.empty + TC_STAGES;
+    t.acc_empty = t.done + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t.acc_empty + 2);
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, 1);
+            mbar_init(t.full + s, full_count);
+            mbar_init(t.empty + s, 1);
         }
-        mbar_init(done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(t.done + b, 1);
+            mbar_init(t.acc_empty + b, acc_empty_count);
+        }
         mbar_fence_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = *tmem_slot;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % TC_STAGES;
-                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) break;
-                mbar_expect_tx(full + s, TC_STAGE_BYTES);
-                unsigned char *st = smem + s * TC_STAGE_BYTES;
-                tma_load_2d(st, &mapA, kb * TC_BK, t0, full + s);
-                tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, w0, full + s);
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // instruction descriptor: D fp32, A/B bf16, both K-major, N and M of the tile
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            bool ok = true;
-            for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                ok = mbar_wait(full + s, (unsigned)(kb / TC_STAGES) & 1u, a.err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {
-                    const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
-                    umma_bf16(tmem, da, db, idesc, (kb | k) ? 1u : 0u);
-                }
-                umma_commit(empty + s);          // the stage is free once these MMAs have read it
-            }
-            umma_commit(done);                   // accumulator complete (arrives even after a failed wait)
-        }
-    } else {
-        // epilogue warps 2..5: TMEM lane quarter = warp % 4
-        const bool ok = mbar_wait(done, 0, a.err);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int q = warp & 3;
-        const int row = t0 + q * 32 + lane;
-        const bool row_ok = row < a.T && q * 32 + lane < rows_valid;
-        const int cbeg = warp < 6 ? 0 : TC_BN / 2;          // two warps per lane quarter, half of the columns each
-        if (ok) {
-#pragma unroll 1
-            for (int c0 = cbeg; c0 < cbeg + TC_BN / 2; c0 += 32) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
-                    const int nmax = a.N - (n0 + c0);
-                    if (a.C32) {
-                        float *o = a.C32 + (long long)row * a.ldc + n0 + c0;
-                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        } else {
-                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
-                        }
-                    } else {
-                        bf16 *o = a.C16 + (long long)row * a.ldc + n0 + c0;
-                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 7) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pk;
-                                pk.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                                pk.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                                pk.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                                pk.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                                *reinterpret_cast<uint4 *>(o + j) = pk;
-                            }
-                        } else {
-                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __float2bfloat16(__uint_as_float(v[j]));
-                        }
-                    }
-                }
-            }
-        }
-    }
+    t.tmem = *tmem_slot;
+    return t;
+}
+__device__ __forceinline__ void tc_teardown(const TcShared &t, int warp) {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(t.tmem), "r"(TC_TMEM_COLS) : "memory");
     }
+}
+
+// grid: min(tiles, 2 x SMs) CTAs of 320 threads.
+__global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                         const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
+    extern __shared__ unsigned char raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TcShared sh = tc_setup(raw, warp, 1, 8);
+    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
+                TileAt t;
+                if (!tile_at(a, id, t)) continue;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const unsigned s = it % TC_STAGES;
+                    if (it >= TC_STAGES && !mbar_wait(sh.empty + s, (it / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
+                    mbar_expect_tx(sh.full + s, TC_STAGE_BYTES);
+                    unsigned char *st = sh.smem + s * TC_STAGE_BYTES;
+                    tma_load_2d(st, &mapA, kb * TC_BK, t.t0, sh.full + s);
+                    tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, t.w0, sh.full + s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) mma_role(a, sh.smem, sh.tmem, sh.full, sh.empty, sh.done, sh.acc_empty, kblocks);
+    } else {
+        epilogue_role(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 8);
+    }
+    tc_teardown(sh, warp);
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -208,177 +283,94 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int Q4_AHEAD = 4;
 
+// grid: min(tiles, 2 x SMs) CTAs of 448 threads: warp 0 TMA (A), warp 1 MMA, warps 2-5 epilogue, warps 6-13 W producers.
 __global__ void __launch_bounds__(448, 2) gemm_tc_q4_kernel(const __grid_constant__ CUtensorMap mapA, GemmTcArgs a,
                                                             const uint32_t *Wq, const bf16 *scale, long long w_rows) {
     extern __shared__ unsigned char raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + TC_STAGES * TC_STAGE_BYTES);
-    uint64_t *empty = full + TC_STAGES;
-    uint64_t *done = empty + TC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(done + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BN;
-    const int4 tl = a.tiles[blockIdx.y];
-    const int t0 = tl.x, rows_valid = tl.y, w0 = tl.z + n0;
-    if (rows_valid <= 0) return;              // unused entry of the tile table (uniform for the CTA, before any barrier)
+    const TcShared sh = tc_setup(raw, warp, 1 + 256, 4);
     const int kblocks = (a.K + TC_BK - 1) / TC_BK;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(full + s, 1 + 256);
-            mbar_init(empty + s, 1);
-        }
-        mbar_init(done, 1);
-        mbar_fence_init();
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_BN) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = *tmem_slot;
-
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % TC_STAGES;
-                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) break;
-                mbar_expect_tx(full + s, TC_A_BYTES);
-                tma_load_2d(smem + s * TC_STAGE_BYTES, &mapA, kb * TC_BK, t0, full + s);
+            unsigned it = 0;
+            bool ok = true;
+            for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
+                TileAt t;
+                if (!tile_at(a, id, t)) continue;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const unsigned s = it % TC_STAGES;
+                    if (it >= TC_STAGES && !mbar_wait(sh.empty + s, (it / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
+                    mbar_expect_tx(sh.full + s, TC_A_BYTES);
+                    tma_load_2d(sh.smem + s * TC_STAGE_BYTES, &mapA, kb * TC_BK, t.t0, sh.full + s);
+                }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            bool ok = true;
-            for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                ok = mbar_wait(full + s, (unsigned)(kb / TC_STAGES) & 1u, a.err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {
-                    const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
-                    umma_bf16(tmem, da, db, idesc, (kb | k) ? 1u : 0u);
-                }
-                umma_commit(empty + s);
-            }
-            umma_commit(done);
-        }
+        if (lane == 0) mma_role(a, sh.smem, sh.tmem, sh.full, sh.empty, sh.done, sh.acc_empty, kblocks);
     } else if (warp >= 6) {
         // W producers: two threads per row of the tile, 32 k values (4 words, 4 chunks) each
         const int p = threadIdx.x - 192, r = p >> 1, hf = p & 1;
-        const long long wrow = (long long)w0 + r;
-        const bool row_ok = n0 + r < a.N && wrow < w_rows;
         const int wpr = a.K >> 3, spr = a.K >> 7;
-        const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr) + hf;
-        const unsigned short *sc_bits = reinterpret_cast<const unsigned short *>(scale + (row_ok ? wrow : 0) * spr);
-        uint4 ring[Q4_AHEAD];
-        unsigned short sring[Q4_AHEAD];          // the k block's scale travels with its words: no dependent load in the loop
-#pragma unroll
-        for (int i = 0; i < Q4_AHEAD; ++i) {
-            ring[i] = make_uint4(0u, 0u, 0u, 0u);
-            sring[i] = 0;
-            if (row_ok && i < kblocks) {
-                ring[i] = __ldg(src + 2 * i);
-                sring[i] = __ldg(sc_bits + (i >> 1));
-            }
-        }
         const bf162 off2 = __floats2bfloat162_rn(136.f, 136.f);
+        unsigned it0 = 0;                        // k blocks of the tiles before this one
         bool ok = true;
-        for (int kb0 = 0; kb0 < kblocks && ok; kb0 += Q4_AHEAD) {
+        for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
+            TileAt t;
+            if (!tile_at(a, id, t)) continue;
+            const long long wrow = (long long)t.w0 + r;
+            const bool row_ok = t.n0 + r < a.N && wrow < w_rows;
+            const uint4 *src = reinterpret_cast<const uint4 *>(Wq + (row_ok ? wrow : 0) * wpr) + hf;
+            const unsigned short *sc_bits = reinterpret_cast<const unsigned short *>(scale + (row_ok ? wrow : 0) * spr);
+            uint4 ring[Q4_AHEAD];
+            unsigned short sring[Q4_AHEAD];      // the k block's scale travels with its words: no dependent load in the loop
 #pragma unroll
             for (int i = 0; i < Q4_AHEAD; ++i) {
-                const int kb = kb0 + i;
-                if (kb >= kblocks) break;
-                const int s = kb % TC_STAGES;
-                const uint4 q = ring[i];
-                // scale as a bf16 pair; (nibble - 8) is exact in bf16 and its product with a bf16 scale, rounded once to bf16,
-                // equals the fp32 product rounded to bf16: the stand-alone conversion's values bit for bit
-                const uint32_t sb = (uint32_t)sring[i] | ((uint32_t)sring[i] << 16);
-                const bf162 sc2 = *reinterpret_cast<const bf162 *>(&sb);
-                if (row_ok && kb + Q4_AHEAD < kblocks) {
-                    ring[i] = __ldg(src + 2 * (kb + Q4_AHEAD));
-                    sring[i] = __ldg(sc_bits + ((kb + Q4_AHEAD) >> 1));
+                ring[i] = make_uint4(0u, 0u, 0u, 0u);
+                sring[i] = 0;
+                if (row_ok && i < kblocks) {
+                    ring[i] = __ldg(src + 2 * i);
+                    sring[i] = __ldg(sc_bits + (i >> 1));
                 }
-                if (kb >= TC_STAGES && !mbar_wait(empty + s, (unsigned)(kb / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
-                unsigned char *dst = smem + s * TC_STAGE_BYTES + TC_A_BYTES + r * 128;
-                const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t bits = ((words[c] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
-                        const bf162 v = __hmul2(__hsub2(*reinterpret_cast<bf162 *>(&bits), off2), sc2);
-                        o[j] = *reinterpret_cast<const uint32_t *>(&v);
-                    }
-                    *reinterpret_cast<uint4 *>(dst + (((hf * 4 + c) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(full + s);
             }
+            for (int kb0 = 0; kb0 < kblocks && ok; kb0 += Q4_AHEAD) {
+#pragma unroll
+                for (int i = 0; i < Q4_AHEAD; ++i) {
+                    const int kb = kb0 + i;
+                    if (kb >= kblocks) break;
+                    const unsigned it = it0 + (unsigned)kb, s = it % TC_STAGES;
+                    const uint4 q = ring[i];
+                    // scale as a bf16 pair; (nibble - 8) is exact in bf16 and its product with a bf16 scale, rounded once to
+                    // bf16, equals the fp32 product rounded to bf16: the stand-alone conversion's values bit for bit
+                    const uint32_t sb = (uint32_t)sring[i] | ((uint32_t)sring[i] << 16);
+                    const bf162 sc2 = *reinterpret_cast<const bf162 *>(&sb);
+                    if (row_ok && kb + Q4_AHEAD < kblocks) {
+                        ring[i] = __ldg(src + 2 * (kb + Q4_AHEAD));
+                        sring[i] = __ldg(sc_bits + ((kb + Q4_AHEAD) >> 1));
+                    }
+                    if (it >= TC_STAGES && !mbar_wait(sh.empty + s, (it / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
+                    unsigned char *dst = sh.smem + s * TC_STAGE_BYTES + TC_A_BYTES + r * 128;
+                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t bits = ((words[c] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+                            const bf162 v = __hmul2(__hsub2(*reinterpret_cast<bf162 *>(&bits), off2), sc2);
+                            o[j] = *reinterpret_cast<const uint32_t *>(&v);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + (((hf * 4 + c) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive(sh.full + s);
+                }
+            }
+            it0 += (unsigned)kblocks;
         }
     } else {
-        const bool ok = mbar_wait(done, 0, a.err);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int q = warp & 3;
-        const int row = t0 + q * 32 + lane;
-        const bool row_ok = row < a.T && q * 32 + lane < rows_valid;
-        if (ok) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
-                    const int nmax = a.N - (n0 + c0);
-                    if (a.C32) {
-                        float *o = a.C32 + (long long)row * a.ldc + n0 + c0;
-                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        } else {
-                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
-                        }
-                    } else {
-                        bf16 *o = a.C16 + (long long)row * a.ldc + n0 + c0;
-                        if (nmax >= 32 && ((a.ldc | (n0 + c0)) & 7) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pk;
-                                pk.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                                pk.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                                pk.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                                pk.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                                *reinterpret_cast<uint4 *>(o + j) = pk;
-                            }
-                        } else {
-                            for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __float2bfloat16(__uint_as_float(v[j]));
-                        }
-                    }
-                }
-            }
-        }
+        epilogue_role(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 4);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
-    }
+    tc_teardown(sh, warp);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -408,6 +400,21 @@ static bool make_map(CUtensorMap *m, const void *base, long long rows, long long
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Two persistent CTAs per SM of the current device, or one CTA per tile when there are fewer tiles.
+static unsigned persistent_grid(int total) {
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    const int cap = 2 * sms[dev];
+    return (unsigned)(total < cap ? total : cap);
+}
+
 }  // namespace qw
 
 using namespace qw;
@@ -424,13 +431,13 @@ QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N,
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
+    a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
         configured = true;
     }
-    dim3 grid((T + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
-    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
+    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -449,9 +456,9 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
+    a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-    dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
-    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
+    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -467,12 +474,12 @@ QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *sca
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
+    a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return -3;
         configured = true;
     }
-    dim3 grid((Nw + TC_BN - 1) / TC_BN, max_tiles);
-    gemm_tc_q4_kernel<<<grid, 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
+    gemm_tc_q4_kernel<<<persistent_grid(a.total), 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
