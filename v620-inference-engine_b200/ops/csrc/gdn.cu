@@ -23,46 +23,64 @@ struct GdnConvArgs {
     float eps;
 };
 
-// grid (M, 2*KL+VL), 128 threads: one head per block.
+// Pre-conv value of channel c at `back` rows before row m: from this batch while that row belongs to m's run, else from
+// the slot's ring (positions before the run), else zero (before the sequence's start).
+__device__ __forceinline__ float gdn_preconv(const GdnConvArgs &a, const float *ring, int qkv_l, int m, int rs, int pos,
+                                             int back, int c) {
+    if (m - back >= rs) return a.proj[(long long)(m - back) * a.ld_proj + c];
+    const int q = pos - back;
+    return q >= 0 ? ring[(q % GDN_RING) * qkv_l + c] : 0.f;
+}
+
+constexpr int CONV_ROWS = 8;     // rows of the batch per block
+
+// grid (ceil(M / 8), 2*KL+VL), 128 threads: one head and eight consecutive rows per block.  The four-tap window slides
+// down the rows in registers (one new load per row while the rows stay in one run).
 __global__ void __launch_bounds__(128) gdn_conv_kernel(GdnConvArgs a) {
     __shared__ float scratch[32];
-    const int m = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int m_first = blockIdx.x * CONV_ROWS, head = blockIdx.y, d = threadIdx.x;
     const int qkv_l = (2 * a.KL + a.VL) * GD;
     const int c = head * GD + d;
-    const int slot = a.rows.slot[m], pos = a.rows.pos[m], rs = a.rows.run_start[m];
-    float *ring = a.ring + (long long)slot * GDN_RING * qkv_l;
-    // value of the pre-conv row at position q: from this batch when q belongs to the run, else the ring
-    float acc = 0.f;
+    float tap[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int q = pos - 3 + k;
-        const int back = pos - q;            // rows back within the run
-        float v;
-        if (m - back >= rs) v = a.proj[(long long)(m - back) * a.ld_proj + c];
-        else if (q >= 0) v = ring[(q % GDN_RING) * qkv_l + c];
-        else v = 0.f;
-        acc = fmaf(a.cw[c * 4 + k], v, acc);
-    }
-    float v = siluf_(acc);
-    if (head < 2 * a.KL) {
-        const float ss = block_sum<128>(v * v, scratch);
-        v = v / sqrtf(ss + a.eps);
-        if (head < a.KL) v *= 0.08838834764831845f;    // 1/sqrt(128)
-    }
-    a.qkv[(long long)m * qkv_l + c] = v;
-    if (head == 0 && d < a.VL) {
-        const float *row = a.proj + (long long)m * a.ld_proj + qkv_l + a.VL * GD;
-        const float bb = row[d], aa = row[a.VL + d];
-        const float g = -__expf(a.A_log[d]) * softplusf_(aa + a.dt_bias[d]);
-        a.decay[m * a.VL + d] = __expf(g);
-        a.beta[m * a.VL + d] = sigmoidf_(bb);
+    for (int k = 0; k < 4; ++k) tap[k] = a.cw[c * 4 + k];
+    float w0 = 0.f, w1 = 0.f, w2 = 0.f;      // values 3, 2, 1 rows back
+    int prev_rs = -1;
+    for (int i = 0; i < CONV_ROWS; ++i) {
+        const int m = m_first + i;
+        if (m >= a.rows.M) break;                // uniform for the block
+        const int slot = a.rows.slot[m], pos = a.rows.pos[m], rs = a.rows.run_start[m];
+        const float *ring = a.ring + (long long)slot * GDN_RING * qkv_l;
+        if (i == 0 || rs != prev_rs || m == rs) {
+            w0 = gdn_preconv(a, ring, qkv_l, m, rs, pos, 3, c);
+            w1 = gdn_preconv(a, ring, qkv_l, m, rs, pos, 2, c);
+            w2 = gdn_preconv(a, ring, qkv_l, m, rs, pos, 1, c);
+        }
+        prev_rs = rs;
+        const float cur = a.proj[(long long)m * a.ld_proj + c];
+        const float acc = fmaf(tap[3], cur, fmaf(tap[2], w2, fmaf(tap[1], w1, tap[0] * w0)));
+        w0 = w1; w1 = w2; w2 = cur;
+        float v = siluf_(acc);
+        if (head < 2 * a.KL) {
+            const float ss = block_sum<128>(v * v, scratch);
+            v = v / sqrtf(ss + a.eps);
+            if (head < a.KL) v *= 0.08838834764831845f;    // 1/sqrt(128)
+        }
+        a.qkv[(long long)m * qkv_l + c] = v;
+        if (head == 0 && d < a.VL) {
+            const float *row = a.proj + (long long)m * a.ld_proj + qkv_l + a.VL * GD;
+            const float bb = row[d], aa = row[a.VL + d];
+            const float g = -__expf(a.A_log[d]) * softplusf_(aa + a.dt_bias[d]);
+            a.decay[m * a.VL + d] = __expf(g);
+            a.beta[m * a.VL + d] = sigmoidf_(bb);
+        }
     }
 }
 
 // Stores the batch's pre-conv rows into the ring (after gdn_conv has read the old entries).
 // grid (M, ceil(qkv_l/256)).
-__global__ void gdn_ring_kernel(const float *proj, int ld_proj, float *ring, int qkv_l, Rows rows) {
-    const int m = blockIdx.x;
+__global__ void gdn_ring_kernel(const float *proj, int ld_proj, float *ring, int qkv_l, Rows rows, int m_first) {
+    const int m = m_first + blockIdx.x;
     const int c = blockIdx.y * 256 + threadIdx.x;
     if (c >= qkv_l) return;
     const int slot = rows.slot[m], pos = rows.pos[m];
@@ -292,11 +310,13 @@ QW_API int qwk_gdn_conv(const float *proj, int ld_proj, float *ring, const float
     a.KL = KL; a.VL = VL; a.rows = Rows{M, slot, pos, run_start, run_len};
     a.qkv = qkv; a.decay = decay; a.beta = beta; a.eps = eps;
     if (VL > 128) return -1;
-    dim3 grid(M, 2 * KL + VL);
+    dim3 grid((M + CONV_ROWS - 1) / CONV_ROWS, 2 * KL + VL);
     gdn_conv_kernel<<<grid, 128, 0, s>>>(a);
     const int qkv_l = (2 * KL + VL) * GD;
-    dim3 g2(M, (qkv_l + 255) / 256);
-    gdn_ring_kernel<<<g2, 256, 0, s>>>(proj, ld_proj, ring, qkv_l, a.rows);
+    // A batch of more than MAX_ROWS rows is one run of one slot (a prefill chunk): only its last GDN_RING rows stay in the ring.
+    const int m_first = M > MAX_ROWS ? M - GDN_RING : 0;
+    dim3 g2(M - m_first, (qkv_l + 255) / 256);
+    gdn_ring_kernel<<<g2, 256, 0, s>>>(proj, ld_proj, ring, qkv_l, a.rows, m_first);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
