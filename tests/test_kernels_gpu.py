@@ -229,3 +229,34 @@ def test_qsa_attend_mma_matches_fp32_and_decode_kernel(QL, KVL):
     torch.cuda.synchronize()
     assert rel(o2.float(), want) < 1e-2
     assert rel(o.float(), want) < 2e-2, rel(o.float(), want)
+
+
+@pytest.mark.parametrize("base,M", [(2040, 70), (9000, 100)])
+def test_qsa_scores_tensor_core_form_matches_fp32(base, M):
+    """Indexer scores of a prefill chunk (more rows than a decode batch: the tensor-core kernel) against PyTorch fp32:
+    rows at and around the budget boundary, groups past a row's visible range untouched."""
+    import ctypes as C
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    dev = _dev()
+    g = torch.Generator(device="cuda").manual_seed(base)
+    IH, ID, ratio, topk, cap = 4, 128, 4, 512, 4096
+    ck = torch.randn(2, cap, ID, generator=g, device=dev).to(torch.bfloat16)
+    iq = torch.randn(M, IH, ID, generator=g, device=dev).contiguous()
+    slot = torch.ones(M, dtype=torch.int32, device=dev)
+    pos = torch.arange(base, base + M, dtype=torch.int32, device=dev)
+    scores = torch.full((M, cap), -7.0, device=dev)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rc = L.qwk_qsa_scores(P(iq), IH, P(ck), cap, M, P(slot), P(pos), ratio, topk, P(scores), cap, (base + M) // ratio,
+                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    want = torch.relu(torch.einsum("mhd,cd->mhc", iq, ck[1].float())).sum(1) / ID ** 0.5
+    for m in range(M):
+        nb = (base + m + 1) // ratio
+        if nb <= topk:
+            assert torch.all(scores[m] == -7.0)
+        else:
+            assert torch.all(scores[m, nb:] == -7.0)
+            err = (scores[m, :nb] - want[m, :nb]).abs().max() / want[m, :nb].abs().max()
+            assert err < 1e-3, (m, float(err))

@@ -574,6 +574,13 @@ QW_API int qwk_qsa_prep(const float *proj, int ld_proj, int QL, int KVL, int IH,
 QW_API int qwk_qsa_scores(const float *iq, int IH, const void *ck, int ck_cap, int M, const int *slot, const int *pos,
                           int ratio, int topk_blocks, float *scores, int ld_scores, int max_groups, cudaStream_t s) {
     if (max_groups <= topk_blocks) return 0;
+    if (M > MAX_ROWS && IH == 4) {
+        // a batch of more than MAX_ROWS rows is one run of one slot (a prefill chunk): tensor-core form
+        qsa_scores_mma_kernel<<<dim3((M + 15) / 16, SC_SPLIT), 128, 0, s>>>(iq, (const bf16 *)ck, ck_cap,
+                                                                            Rows{M, slot, pos, nullptr, nullptr}, ratio, topk_blocks,
+                                                                            scores, ld_scores);
+        return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    }
     dim3 grid((max_groups + 63) / 64, M);
     launch_pdl(qsa_scores_kernel, grid, dim3(256), 0, s, iq, IH, (const bf16 *)ck, ck_cap, Rows{M, slot, pos, nullptr, nullptr}, ratio,
                topk_blocks, scores, ld_scores);

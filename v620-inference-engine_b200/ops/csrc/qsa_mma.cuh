@@ -211,3 +211,108 @@ __global__ void __launch_bounds__(128, 3) qsa_attend_mma_kernel(QsaAttendArgs a,
         }
     }
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Indexer scores of a prefill chunk on the tensor cores: score[m][c] = sum_h relu(iq[m][h] . ck[c]) / sqrt(128) for the
+// groups c visible to row m, for rows whose visible groups exceed the budget (the others attend densely).
+// A block takes 16 consecutive rows of the chunk (one slot, ascending positions): the MMA rows of a warp are its 4
+// query rows x 4 indexer heads, the fp32 queries split into a bf16 high and low part (two MMAs per step) so that the
+// ranking keeps fp32-like resolution against the bf16 keys; key tiles of 64 groups go through shared memory and are
+// shared by the four warps.  The sum over the heads is two lane shuffles on the accumulator fragment.
+// grid (ceil(M / 16), SC_SPLIT), 128 threads; block y takes key tiles y, y + SC_SPLIT, ...   IH == 4.
+// (Role of the reference's score GEMM + score_reduce, src/kernels/qsa.hip and docs/MODEL.md:150-160.)
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int SC_SPLIT = 4;
+constexpr int SC_LD = ID + 8;        // shared row stride of a key tile (bf16)
+
+__global__ void __launch_bounds__(128) qsa_scores_mma_kernel(const float *iq, const bf16 *ck, int ck_cap, Rows rows, int ratio,
+                                                             int topk_blocks, float *scores, int ld_scores) {
+    __shared__ __align__(16) bf16 tile[64 * SC_LD];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    const int m0 = blockIdx.x * 16;
+    const int m_last = min(m0 + 15, rows.M - 1);
+    const int nb_max = (rows.pos[m_last] + 1) / ratio;
+    if (nb_max <= topk_blocks) return;                       // every row of the block attends densely (uniform)
+    const int slot = rows.slot[m0];
+    const bf16 *keys = ck + (long long)slot * ck_cap * ID;
+    // ---- A fragments: MMA row i = 4 * (query row within the warp) + head; rows g and g + 8 of this lane
+    uint32_t ahi[8][4], alo[8][4];
+    int nb_row[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int i = g + hh * 8, m = m0 + w * 4 + (i >> 2), h = i & 3;
+        const bool ok = m < rows.M;
+        nb_row[hh] = ok ? (rows.pos[m] + 1) / ratio : 0;
+        const float *q = iq + ((long long)(ok ? m : m0) * 4 + h) * ID;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float2 v = *reinterpret_cast<const float2 *>(q + ks * 16 + half * 8 + 2 * t4);
+                if (!ok) v = make_float2(0.f, 0.f);
+                const bf162 hi = __floats2bfloat162_rn(v.x, v.y);
+                const float2 hf = __bfloat1622float2(hi);
+                const bf162 lo = __floats2bfloat162_rn(v.x - hf.x, v.y - hf.y);
+                ahi[ks][hh + 2 * half] = *reinterpret_cast<const uint32_t *>(&hi);
+                alo[ks][hh + 2 * half] = *reinterpret_cast<const uint32_t *>(&lo);
+            }
+    }
+    const uint32_t tile_base = (uint32_t)__cvta_generic_to_shared(tile);
+    const int ntiles = (nb_max + 63) / 64;
+    for (int kt = blockIdx.y; kt < ntiles; kt += SC_SPLIT) {
+        const int c0 = kt * 64;
+        __syncthreads();                                     // the previous tile has been read
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = tid + i * 128;                   // 16-byte piece: 64 groups x 16
+            const int r = idx >> 4, p = idx & 15;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c0 + r < nb_max) v = __ldg(reinterpret_cast<const uint4 *>(keys + (long long)(c0 + r) * ID) + p);
+            *reinterpret_cast<uint4 *>(tile + r * SC_LD + p * 8) = v;
+        }
+        __syncthreads();
+        float acc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+        const int mid = lane >> 3;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, tile_base + (uint32_t)(((n2 * 16 + (mid >> 1) * 8 + (lane & 7)) * SC_LD + ks * 16 + (mid & 1) * 8) * 2));
+                mma_bf16(acc[2 * n2], ahi[ks][0], ahi[ks][1], ahi[ks][2], ahi[ks][3], b0, b1);
+                mma_bf16(acc[2 * n2], alo[ks][0], alo[ks][1], alo[ks][2], alo[ks][3], b0, b1);
+                mma_bf16(acc[2 * n2 + 1], ahi[ks][0], ahi[ks][1], ahi[ks][2], ahi[ks][3], b2, b3);
+                mma_bf16(acc[2 * n2 + 1], alo[ks][0], alo[ks][1], alo[ks][2], alo[ks][3], b2, b3);
+            }
+        // relu, sum over the 4 heads (lanes that differ in the low two bits of g), store
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            float s[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = fmaxf(acc[n][i], 0.f);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                s[i] = v * 0.08838834764831845f;
+            }
+            if ((g & 3) == 0) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int m = m0 + w * 4 + ((g + hh * 8) >> 2);
+                    const int nb = nb_row[hh];
+                    if (m < rows.M && nb > topk_blocks) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int c = c0 + n * 8 + 2 * t4 + j;
+                            if (c < nb) scores[(long long)m * ld_scores + c] = s[hh * 2 + j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
