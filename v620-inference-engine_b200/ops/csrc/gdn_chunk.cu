@@ -2,7 +2,7 @@
 // dense 64-token chunk products on the tensor cores, with the state in fp32.
 //
 // The reference only has the token-by-token scan (gdn_scan_T, src/kernels/gdn.hip:229-309) and lists the
-// chunked form as future work (docs/DESIGN.md:512).  Math (per value head, state S [128 k][128 v], chunk of
+// chunked form as future work (its design document under docs/, line 512).  Math (per value head, state S [128 k][128 v], chunk of
 // C = 64 rows, entry state S0, g_t = sum_{s<=t} log decay_s):
 //
 //     A[t,s] = beta_t exp(g_t - g_s) (k_t . k_s)       s <  t

@@ -6,7 +6,7 @@
 Measures the stand-alone peer-memory kernels (all-reduce of the 1,300-float mixer vector = 5.2 KB, reduce-scatter of a
 [rows][hidden] fp32 block output, all-gather of the bf16 block input) and the same collectives through NCCL.  The fused
 forms have no launch of their own; their cost is the difference between `bench.py --comm p2p` and `--comm p2p-mute`.
-(The reference's figure for the chained 5.2 KB all-reduce on PCIe: 45.7 -> 15.7 us, docs/DESIGN.md:238,1586.)"""
+(The reference's figure for the chained 5.2 KB all-reduce on PCIe: 45.7 -> 15.7 us, its design document under docs/, lines 238 and 1586.)"""
 import argparse
 import ctypes as C
 import json
