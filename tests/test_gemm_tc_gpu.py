@@ -65,3 +65,26 @@ def test_grouped_q4_gemm_matches_fp32(Nw, K, counts, out_dtype):
             err = float((out[r0:r0 + n].float() - ref).abs().max() / ref.abs().max())
             assert err < tol, (e, err)
         r0 += n
+
+
+@pytest.mark.parametrize("T,N,K,ks", [(200, 324, 10240, 3), (128, 128, 256, 2), (77, 40, 640, 1)])
+def test_gemm_tc_split_k_partials_add_up(T, N, K, ks):
+    """Split-K form: the partial products of the shares of K, added in order, equal the full product."""
+    import ctypes as C
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    g = torch.Generator(device="cuda").manual_seed(T + N + K)
+    A = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    ldc = (N + 7) // 8 * 8
+    out = torch.full((ks, T + 3, ldc), 768.0, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rc = L.qwk_gemm_bf16_tc_splitk(P(A), P(W), P(out), T, N, K, K, K, ldc, ks, (T + 3) * ldc,
+                                   C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.all(out[:, T:] == 768.0) and torch.all(out[:, :, N:] == 768.0)
+    ref = A.float() @ W.float().T
+    got = out[:, :T, :N].sum(0)
+    err = float((got - ref).abs().max() / ref.abs().max())
+    assert err < 2e-3, err

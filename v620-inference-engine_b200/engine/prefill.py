@@ -42,12 +42,16 @@ class Prefiller:
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
         z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
         self.hc_ld = (c.hc_down + 7) // 8 * 8
+        kblocks = (c.hch + 63) // 64
+        self.hc_ksplit = 3 if kblocks >= 48 else 1          # split-K shares of the mixers' down projection
+        if (kblocks + self.hc_ksplit - 1) // self.hc_ksplit * (self.hc_ksplit - 1) >= kblocks:
+            self.hc_ksplit = 1
         nrs = c.n_experts + 1 + 2 * sc.sffn_l
         self.nrs_ld = (nrs + 7) // 8 * 8
         self.proj_ld = (max(sc.gdn_proj_l, sc.qsa_proj_l) + 7) // 8 * 8
         Pn = T * c.top_k
         self.b = {
-            "X": z((T, c.hc, sc.sh), f32), "xn": z((T, c.hch), bf), "d": z((T, self.hc_ld), f32), "u": z((T, c.hc_rank), bf),
+            "X": z((T, c.hc, sc.sh), f32), "xn": z((T, c.hch), bf), "d": z((self.hc_ksplit, T, self.hc_ld), f32), "u": z((T, c.hc_rank), bf),
             "inj_a": z((T, c.hc), f32), "inj_b": z((T, c.hc), f32), "g": z((T, c.hch), f32), "bin": z((T, c.hidden), bf),
             "proj": z((T, self.proj_ld), f32), "o": z((T, max(sc.gdn_vl * c.gdn_dim, sc.qh_l * c.head_dim)), bf),
             "out_a": z((T, c.hidden), f32), "out_b": z((T, c.hidden), f32),
@@ -116,8 +120,12 @@ class Prefiller:
         self._ck(L.qwk_hc_prenorm_T(_p(b["X"]), _p(pend), c.hidden, _p(inj_prev), P(hc["w1"].data_ptr()), sc.sh, c.hc,
                                     C.c_float(c.eps), _p(b["xn"]), T, s), "hc_prenorm")
         down = c.hc_rank + n_inj
-        self.gemm(b["xn"][:T], hc["Wd"].data_ptr(), down, c.hch, b["d"][:T])
-        self._ck(L.qwk_hc_mid_T(_p(b["d"]), self.hc_ld, c.hc_rank, n_inj, c.hc, _p(b["u"]), _p(inj_out), T, s), "hc_mid")
+        # few output tiles and a long K: the down projection runs split-K; hc_mid adds the partial sums in order
+        ks = self.hc_ksplit
+        self._ck(L.qwk_gemm_bf16_tc_splitk(_p(b["xn"]), P(hc["Wd"].data_ptr()), _p(b["d"]), T, down, c.hch, c.hch, c.hch,
+                                           self.hc_ld, ks, self.T * self.hc_ld, s), "hc_down")
+        self._ck(L.qwk_hc_mid_T(_p(b["d"]), self.hc_ld, c.hc_rank, n_inj, c.hc, _p(b["u"]), _p(inj_out), T, ks,
+                                self.T * self.hc_ld, s), "hc_mid")
         self.gemm(b["u"][:T], hc["Wu"].data_ptr(), c.hch, c.hc_rank, b["g"][:T])
         self._ck(L.qwk_hc_mix_T(_p(b["g"]), _p(b["xn"]), sc.sh, _p(b["bin"]), c.hidden, T, s), "hc_mix")
 

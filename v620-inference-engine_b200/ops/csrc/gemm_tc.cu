@@ -66,14 +66,24 @@ struct GemmTcArgs {
     ErrorWord *err;
     // grouped mode (expert-sorted rows): tiles[entry] = {first A row, valid rows, first W row of the group, -}
     const int4 *tiles;
-    int total, tiles_t, tiles_n;     // linear tile ids 0..total-1; plain: id = n * tiles_t + t; grouped: id = entry * tiles_n + n
+    int total, tiles_t, tiles_n;     // linear tile ids 0..total-1; plain: id = (split * tiles_n + n) * tiles_t + t; grouped: id = entry * tiles_n + n
+    // split-K (plain mode, fp32 output): split s covers k blocks [s * kb_per, (s + 1) * kb_per) and writes its partial sums
+    // to C + s * c_split (the consumer adds the splits in order); ksplit == 1: the whole K, c_split unused
+    int ksplit, kb_per;
+    long long c_split;
 };
 
 struct TileAt {
     int t0, rows_valid, n0, w0;
+    int kb0, kbn;                    // first k block and number of k blocks of this tile's share of K
+    long long c_off;                 // element offset of its output within C
 };
 // Tile `id` of the launch; false for an unused entry of the tile table (every role skips it alike).
 __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) {
+    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    t.kb0 = 0;
+    t.kbn = kblocks;
+    t.c_off = 0;
     if (a.tiles) {
         const int4 tl = __ldg(a.tiles + id / a.tiles_n);
         t.n0 = (id % a.tiles_n) * TC_BN;
@@ -84,6 +94,13 @@ __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) 
     }
     // plain: the row tiles of one column panel are neighbours, so the CTAs in flight share a W panel and the (smaller)
     // activation matrix stays in L2 while W streams through once
+    if (a.ksplit > 1) {
+        const int per = a.tiles_t * a.tiles_n, sp = id / per;
+        id -= sp * per;
+        t.kb0 = sp * a.kb_per;
+        t.kbn = min(a.kb_per, kblocks - t.kb0);
+        t.c_off = sp * a.c_split;
+    }
     t.n0 = (id / a.tiles_t) * TC_BN;
     t.t0 = (id % a.tiles_t) * TC_BM;
     t.rows_valid = TC_BM;
@@ -92,10 +109,10 @@ __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) 
 }
 
 // One 32-column piece of an accumulator row -> C.
-__device__ __forceinline__ void store_piece(const GemmTcArgs &a, int row, int col0, const uint32_t (&v)[32]) {
+__device__ __forceinline__ void store_piece(const GemmTcArgs &a, long long c_off, int row, int col0, const uint32_t (&v)[32]) {
     const int nmax = a.N - col0;
     if (a.C32) {
-        float *o = a.C32 + (long long)row * a.ldc + col0;
+        float *o = a.C32 + c_off + (long long)row * a.ldc + col0;
         if (nmax >= 32 && ((a.ldc | col0) & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
@@ -154,7 +171,7 @@ __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem
         for (int c0 = cbeg; c0 < cend; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_BN + c0), v);
-            if (row_ok) store_piece(a, row, t.n0 + c0, v);
+            if (row_ok) store_piece(a, t.c_off, row, t.n0 + c0, v);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
@@ -176,7 +193,7 @@ __device__ __forceinline__ void mma_role(const GemmTcArgs &a, unsigned char *sme
         const int b = j & 1;
         if (j >= 2 && !mbar_wait(acc_empty + b, (unsigned)((j >> 1) - 1) & 1u, a.err)) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = 0; kb < t.kbn; ++kb, ++it) {
             const unsigned s = it % TC_STAGES;
             if (!mbar_wait(full + s, (it / TC_STAGES) & 1u, a.err)) return;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -251,13 +268,13 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__
             for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
                 TileAt t;
                 if (!tile_at(a, id, t)) continue;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = 0; kb < t.kbn; ++kb, ++it) {
                     const unsigned s = it % TC_STAGES;
                     if (it >= TC_STAGES && !mbar_wait(sh.empty + s, (it / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
                     mbar_expect_tx(sh.full + s, TC_STAGE_BYTES);
                     unsigned char *st = sh.smem + s * TC_STAGE_BYTES;
-                    tma_load_2d(st, &mapA, kb * TC_BK, t.t0, sh.full + s);
-                    tma_load_2d(st + TC_A_BYTES, &mapW, kb * TC_BK, t.w0, sh.full + s);
+                    tma_load_2d(st, &mapA, (t.kb0 + kb) * TC_BK, t.t0, sh.full + s);
+                    tma_load_2d(st + TC_A_BYTES, &mapW, (t.kb0 + kb) * TC_BK, t.w0, sh.full + s);
                 }
             }
         }
@@ -432,6 +449,7 @@ QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N,
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
+    a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
@@ -457,6 +475,7 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
+    a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
     cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
     gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -475,11 +494,40 @@ QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *sca
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
+    a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return -3;
         configured = true;
     }
     gemm_tc_q4_kernel<<<persistent_grid(a.total), 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Split-K form for products with few output tiles and a long K (the mixers' down projection): C_s = A[:, K_s] . W[:, K_s]^T
+// for ksplit shares of K, partial s written as fp32 to C + s * c_split (elements); the consumer adds the partials in
+// order, so the sum does not depend on timing.  ksplit <= number of k blocks.
+QW_API int qwk_gemm_bf16_tc_splitk(const void *A, const void *W, float *C, int T, int N, int K, int lda, int ldw, int ldc,
+                                   int ksplit, long long c_split, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ksplit < 1 || ksplit > kblocks) return -1;
+    CUtensorMap mA, mW;
+    if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_BN)) return -3;
+    GemmTcArgs a;
+    a.C32 = C; a.C16 = nullptr;
+    a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
+    a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN;
+    a.kb_per = (kblocks + ksplit - 1) / ksplit;
+    a.ksplit = (kblocks + a.kb_per - 1) / a.kb_per;          // every share holds at least one k block
+    if (a.ksplit != ksplit) return -1;
+    a.c_split = c_split;
+    a.total = a.tiles_t * a.tiles_n * a.ksplit;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        configured = true;
+    }
+    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -51,14 +51,17 @@ __global__ void __launch_bounds__(256) hc_prenorm_T_kernel(float *X, const float
     }
 }
 
-// d [T][ld_d] fp32 (R + n_inj columns) -> u bf16 [T][R] = silu(d/hc), inj fp32 [T][n_inj].
-__global__ void hc_mid_T_kernel(const float *d, int ld_d, int R, int n_inj, int hc, bf16 *u, float *inj, long long total) {
+// d [nsplit][T][ld_d] fp32 (R + n_inj columns; the split-K partial sums of the down projection, added here in order)
+// -> u bf16 [T][R] = silu(d/hc), inj fp32 [T][n_inj].
+__global__ void hc_mid_T_kernel(const float *d, int ld_d, int R, int n_inj, int hc, bf16 *u, float *inj, long long total,
+                                int nsplit, long long split_stride) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int w = R + n_inj;
     const long long t = i / w;
     const int j = (int)(i - t * w);
-    const float v = d[t * ld_d + j];
+    float v = d[t * ld_d + j];
+    for (int s = 1; s < nsplit; ++s) v += d[s * split_stride + t * ld_d + j];
     if (j < R) u[t * R + j] = __float2bfloat16(siluf_(v / float(hc)));
     else inj[t * n_inj + (j - R)] = v;
 }
@@ -209,9 +212,11 @@ QW_API int qwk_hc_prenorm_T(float *X, const float *pend, int ld_pend, const floa
     hc_prenorm_T_kernel<<<dim3(T, hc), 256, 0, s>>>(X, pend, ld_pend, inj, w1, SH, hc, eps, (bf16 *)xn);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
-QW_API int qwk_hc_mid_T(const float *d, int ld_d, int R, int n_inj, int hc, void *u, float *inj, int T, cudaStream_t s) {
+QW_API int qwk_hc_mid_T(const float *d, int ld_d, int R, int n_inj, int hc, void *u, float *inj, int T, int nsplit,
+                        long long split_stride, cudaStream_t s) {
     const long long total = (long long)T * (R + n_inj);
-    hc_mid_T_kernel<<<blocks_for(total, 256), 256, 0, s>>>(d, ld_d, R, n_inj, hc, (bf16 *)u, inj, total);
+    hc_mid_T_kernel<<<blocks_for(total, 256), 256, 0, s>>>(d, ld_d, R, n_inj, hc, (bf16 *)u, inj, total, nsplit < 1 ? 1 : nsplit,
+                                                           split_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 QW_API int qwk_hc_mix_T(const float *g, const void *xn, int SH, void *bin, int ld_bin, int T, cudaStream_t s) {
