@@ -307,13 +307,12 @@ class DeviceModel:
     def set_mtp(self, w: Weights):
         """Install the MTP head (a QSA decoder layer with its own mixer, the two fc matrices and norms)."""
         c, sc, dv = self.cfg, self.sc, self.dev
-        if sc.ranks != 1:
-            raise NotImplementedError("the MTP head runs on one GPU")
+        cols = sc.cols()          # the fc matrices are sliced by output rows: their products are this rank's residual columns
         conv = self._cached("mtp", lambda: {
             "layer": WP.prep_layer(c, w, c.n_layers, sc, dv, prefix="mtp.layers.0.", qsa=True),
             "final_hc": WP.prep_hc(w, "mtp.hyper_connection_mixer.", sc, False, dv),
-            "fc_h": w["mtp.fc_hidden.weight"].to(dv).to(torch.bfloat16).contiguous(),
-            "fc_e": w["mtp.fc_embedding.weight"].to(dv).to(torch.bfloat16).contiguous(),
+            "fc_h": w["mtp.fc_hidden.weight"].to(dv)[cols].to(torch.bfloat16).contiguous(),
+            "fc_e": w["mtp.fc_embedding.weight"].to(dv)[cols].to(torch.bfloat16).contiguous(),
             "nh1": (1.0 + w["mtp.pre_fc_norm_hidden.weight"].to(dv).float()).contiguous(),
             "ne1": (1.0 + w["mtp.pre_fc_norm_embedding.weight"].to(dv).float()).contiguous()})
         lw, fin = conv["layer"], conv["final_hc"]
@@ -323,8 +322,8 @@ class DeviceModel:
             **conv,
             "hn": torch.zeros((R * c.hc, c.hidden), dtype=torch.bfloat16, device=dv),
             "en": torch.zeros((R, c.hidden), dtype=torch.bfloat16, device=dv),
-            "fh": torch.zeros((R * c.hc, c.hidden), dtype=torch.float32, device=dv),
-            "fe": torch.zeros((R, c.hidden), dtype=torch.float32, device=dv),
+            "fh": torch.zeros((R * c.hc, sc.sh), dtype=torch.float32, device=dv),
+            "fe": torch.zeros((R, sc.sh), dtype=torch.float32, device=dv),
         }
         self._layer_struct(m.layer, lw, c.n_qsa)
         m.final_hc = self._hc_struct(fin)

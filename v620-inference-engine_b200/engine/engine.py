@@ -56,7 +56,8 @@ class Engine:
         self.slot = [Slot() for _ in range(opts.slots)]
         self.out_host = torch.zeros(opts.max_rows, dtype=torch.int32).pin_memory()
         self.merge_argmax = None        # set by the NCCL backend: merges the ranks' (max, argmax) after a step
-        self.prefiller = None           # token-major prefill, built on first use (one GPU)
+        self.prefiller = None           # token-major prefill, built on first use
+        self.tp_channels = None         # several ranks: the prefill channels, one per micro-batch lane (parallel.tp_channel)
         self.vision_lookup = None       # vision token ids -> embeddings [n, hidden] (set by the vision front end)
         from ..utils import settings as _settings
         from ..utils.trace import ChunkProfile, StepTrace
@@ -81,7 +82,7 @@ class Engine:
                 log(f"layer {L + 1}/{cfg.n_layers} ready, {e.dm.weight_bytes() / 1e9:.1f} GB, {time.time() - t0:.0f} s")
         table = PleTable.synthetic(cfg, rows=ple_rows, layout="f8", seed=seed, pin=ple_pinned)
         e.dm.set_ple_table(table)
-        if cfg.mtp and ranks == 1:
+        if cfg.mtp:
             g = synth_globals(cfg, seed, device=device)
             g.update(synth_layer(cfg, cfg.n_layers, seed, device=device, exact=exact, prefix="mtp.layers.0.", qsa=True))
             e.dm.set_mtp(g)
@@ -97,7 +98,7 @@ class Engine:
             e.dm.set_layer(L, w)
         if table is not None:
             e.dm.set_ple_table(table)
-        if cfg.mtp and ranks == 1 and "mtp.fc_hidden.weight" in w:
+        if cfg.mtp and "mtp.fc_hidden.weight" in w:
             e.dm.set_mtp(w)
         return e
 
@@ -122,7 +123,7 @@ class Engine:
         e.dm.set_globals(w)
         for L in range(cfg.n_layers):
             e.dm.set_layer(L, w)
-        has_mtp = cfg.mtp and ranks == 1
+        has_mtp = cfg.mtp
         if has_mtp:
             present = e.dm._cached("mtp_present", lambda: {"present": bool(w is not None and "mtp.fc_hidden.weight" in w)})
             if present["present"]:
@@ -202,9 +203,10 @@ class Engine:
         toks = [int(t) for t in tokens]
         n = len(toks)
         has_media = any(t < 0 for t in toks)
-        if has_media and (self.vision_lookup is None or self.dm.sc.ranks != 1 or self.opts.prefill_chunk <= 0):
+        token_major = self.opts.prefill_chunk > 0 and (self.dm.sc.ranks == 1 or self.tp_channels is not None)
+        if has_media and (self.vision_lookup is None or not token_major):
             raise ValueError("vision tokens need a vision tower and the token-major prefill path")
-        if self.dm.sc.ranks == 1 and self.opts.prefill_chunk > 0 and (n >= self.opts.prefill_min or has_media):
+        if token_major and (n >= self.opts.prefill_min or has_media):
             return self._prefill_token_major(slot, toks, want_logits)
         step = max(1, min(self.opts.prefill_rows, self.opts.max_rows))
         i = 0
@@ -339,44 +341,62 @@ class Engine:
             self.spec_accepted += n_acc - 1
         return out[:n_new]
 
-    def _prefill_token_major(self, slot: int, toks: List[int], want_logits: bool):
+    def _get_prefiller(self):
         from .prefill import Prefiller
+        if self.prefiller is None:
+            self.prefiller = Prefiller(self.dm, chunk=min(self.opts.prefill_chunk, max(256, self.dm.slot_tokens)),
+                                       channels=self.tp_channels)
+        return self.prefiller
+
+    def prefill_jobs(self, slot: int, toks: List[int], want_logits: bool):
+        """The token-major prefill of ``toks`` as a generator: yields the job of each chunk (``QwPrefillJob``), which the
+        caller launches before resuming.  One process per GPU launches each job by itself (``_prefill_token_major``); a
+        process that emulates several ranks on one GPU launches the ranks' jobs of a chunk together."""
         if self.slot[slot].n + len(toks) > self.dm.slot_tokens:
             raise ValueError("slot capacity exceeded")
-        if self.prefiller is None:
-            self.prefiller = Prefiller(self.dm, chunk=min(self.opts.prefill_chunk, max(256, self.dm.slot_tokens)))
-        T = self.prefiller.T
-        out = None
+        pf = self._get_prefiller()
+        T = pf.T
         for i in range(0, len(toks), T):
             chunk = toks[i:i + T]
             last = i + T >= len(toks)
-            base = self.slot[slot].n
+            sl = self.slot[slot]
+            base = sl.n
             embeds = None
             vis = [j for j, t in enumerate(chunk) if t < 0]
             if vis:         # rows that carry vision tokens take the tower's output as their embedding
                 embeds = (torch.tensor(vis, dtype=torch.long, device=self.dm.dev), self.vision_lookup([chunk[j] for j in vis]))
             ev = self.chunk_profile.begin()
-            out = self.prefiller.run(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last, embeds=embeds)
+            if pf.native:
+                yield pf.make_job(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last, embeds, mtp=self.mtp,
+                                  pending=sl.mtp_hidden)
+                if self.mtp:
+                    sl.mtp_hidden = pf.b["hid_out"].clone()
+            else:
+                pf.run_py(slot, base, chunk, self._ctx3(slot, chunk), want_logits and last, embeds=embeds)
+                if self.mtp:
+                    # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
+                    keep = pf.b["X"][len(chunk) - 1].clone()
+                    if want_logits and last:             # the MTP rows below reuse the logits / argmax buffers
+                        saved = (self.dm.buf["logits"][:1].clone(), self.dm.buf["amax_idx"][:1].clone())
+                    if sl.mtp_hidden is not None and base > 0:
+                        self.dm.buf["hidden_out"][0] = sl.mtp_hidden
+                        self.dm.mtp_step([chunk[0]], [slot], [base - 1])
+                    pf.mtp_pass(slot, base, len(chunk), chunk[1:])
+                    if want_logits and last:
+                        self.dm.buf["logits"][:1].copy_(saved[0])
+                        self.dm.buf["amax_idx"][:1].copy_(saved[1])
+                    sl.mtp_hidden = keep
             self.chunk_profile.end(ev, len(chunk))
-            if self.mtp:
-                # the chunk's hidden states are in the prefiller's X: MTP rows for every position whose next token is known
-                sl = self.slot[slot]
-                keep = self.prefiller.b["X"][len(chunk) - 1].clone()
-                if want_logits and last:             # the MTP rows below reuse the logits / argmax buffers
-                    saved = (self.dm.buf["logits"][:1].clone(), self.dm.buf["amax_idx"][:1].clone())
-                if sl.mtp_hidden is not None and base > 0:
-                    self.dm.buf["hidden_out"][0] = sl.mtp_hidden
-                    self.dm.mtp_step([chunk[0]], [slot], [base - 1])
-                self.prefiller.mtp_pass(slot, base, len(chunk), chunk[1:])
-                if want_logits and last:
-                    self.dm.buf["logits"][:1].copy_(saved[0])
-                    self.dm.buf["amax_idx"][:1].copy_(saved[1])
-                sl.mtp_hidden = keep
-            self.slot[slot].tokens.extend(chunk)
+            sl.tokens.extend(chunk)
         self.steps += 1
         self.chunk_profile.summary(f"prefill slot {slot}")
         self.last_prefill_row = 0           # logits / argmax of the last token sit in row 0
-        return out
+
+    def _prefill_token_major(self, slot: int, toks: List[int], want_logits: bool):
+        from .prefill import Prefiller
+        for job in self.prefill_jobs(slot, toks, want_logits):
+            Prefiller.launch(self.dm.lib, [job])
+        return self.dm.buf["logits"][0] if want_logits else None
 
     # ---- decode
     def decode(self, slots: Sequence[int], tokens: Sequence[int], flags: int = 0, sync: bool = True) -> List[int]:

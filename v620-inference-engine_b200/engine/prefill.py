@@ -1,24 +1,27 @@
-"""Token-major prefill of one slot on one GPU.
+"""Token-major prefill of one slot: a chunk of T prompt tokens through the whole model.
 
-A chunk of T prompt tokens goes through the model with every dense product on the tcgen05 GEMM
-(``qwk_gemm_bf16_tc``), the routed experts as one grouped tcgen05 GEMM per projection over
-expert-sorted rows (weights of the layer dequantised q4 -> bf16 into a scratch first), and the
-stateful pieces (GDN conv + scan, QSA prep / indexer / selection / attention over the paged KV, PLE)
-on the same row-batch kernels the decode path uses, so the slot state a prefill leaves behind is the
-state the decode kernels expect (reference: ``run_prefill_rank``, src/engine/prefill.hip:46-496).
+Every dense product runs on the tcgen05 GEMM (``qwk_gemm_bf16_tc``), the routed experts as one grouped tcgen05
+GEMM per projection over expert-sorted rows with the q4 words converted inside the kernel, and the stateful
+pieces (GDN conv + chunked scan, QSA prep / indexer / selection / attention over the paged KV, PLE) on kernels
+that leave the slot state exactly as the decode kernels expect it (reference: ``run_prefill_rank``,
+src/engine/prefill.hip:46-496).
 
-PyTorch only does the bookkeeping here (buffers, the expert sort's index arithmetic); everything that
-touches activations or weights is one of this library's kernels.
+The chunk's launch sequence lives in the native runtime (``ops/csrc/prefill_rt.cu``, one call per chunk): one rank
+or several (tensor + expert parallel with the collectives inside the kernels, ``ops/csrc/tp.cuh``), one or two
+micro-batches on two streams.  This module owns the buffers (PyTorch allocations), the row tables and the job
+struct.  ``run_py`` keeps the same schedule spelled out in Python, kernel by kernel, for one GPU: the cross-check
+of the runtime in the tests, and ``QW_PREFILL_PY=1``.
 """
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from ..ops import lib as qlib
+from ..ops import structs as S
 from ..utils import settings
 from .device_model import DeviceModel
 
@@ -30,60 +33,110 @@ def _p(t):
 
 
 class Prefiller:
-    def __init__(self, dm: DeviceModel, chunk: int = 4096, attn_rows: int = 256):
-        if dm.sc.ranks != 1:
-            raise NotImplementedError("token-major prefill runs on one GPU; multi-rank prefill uses the row-batched path")
+    def __init__(self, dm: DeviceModel, chunk: int = 4096, attn_rows: int = 256, channels=None, lanes: int = 0):
+        """``channels``: with several ranks, one ``TpChannel`` per micro-batch lane (``parallel/tp_channel.py``)."""
+        st = settings.get()
         self.dm, self.T, self.attn_rows = dm, chunk, attn_rows
-        self.on_block_input = None      # optional hook(layer, "attn" | "mlp", block input [T, hidden] bf16): calibration
+        self.on_block_input = None      # optional hook(layer, "attn" | "mlp", block input [n, hidden] bf16): calibration
         self.layer_limit = None         # run only the first n layers, then the final mixer (depth diagnostics)
         self.lib = dm.lib
+        self.channels = list(channels or [])
+        self.tp = dm.sc.ranks > 1
+        if self.tp and not self.channels:
+            raise ValueError("token-major prefill on several ranks needs a channel per lane (parallel.tp_channel)")
+        self.lanes = lanes or st.prefill_lanes or (2 if self.tp else 1)
+        self.lanes = max(1, min(self.lanes, len(self.channels))) if self.tp else self.lanes
+        S.check_prefill_structs(self.lib)
+        self.lib.qwrt_prefill.argtypes = [C.POINTER(C.POINTER(S.QwPrefillJob)), C.c_int]
+        self.lib.qwrt_prefill.restype = C.c_int
+        self.lib.qwrt_prefill_last_launches.restype = C.c_longlong
         c, sc, dev = dm.cfg, dm.sc, dm.dev
         T = chunk
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
         z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
         self.hc_ld = (c.hc_down + 7) // 8 * 8
-        kblocks = (c.hch + 63) // 64
-        self.hc_ksplit = 3 if kblocks >= 48 else 1          # split-K shares of the mixers' down projection
+        K_down = c.hc * sc.sh
+        kblocks = (K_down + 63) // 64
+        self.hc_ksplit = 3 if (kblocks >= 48 and not self.tp) else 1          # split-K shares of the mixers' down projection
         if (kblocks + self.hc_ksplit - 1) // self.hc_ksplit * (self.hc_ksplit - 1) >= kblocks:
             self.hc_ksplit = 1
         nrs = c.n_experts + 1 + 2 * sc.sffn_l
         self.nrs_ld = (nrs + 7) // 8 * 8
         self.proj_ld = (max(sc.gdn_proj_l, sc.qsa_proj_l) + 7) // 8 * 8
+        self.o_ld = max(sc.gdn_vl * c.gdn_dim, sc.qh_l * c.head_dim)
+        self.ple_ld = (sc.ple_kv + 7) // 8 * 8
         Pn = T * c.top_k
+        self.max_tiles = Pn // 128 + sc.exp_l
+        nch = (T + 63) // 64 + 1
+        self.gdn_scratch_lane = nch * sc.gdn_vl * (2 * 64 * 128 + 64 * 64 + 64) + T * sc.gdn_vl * 128
+        one = not self.tp
         self.b = {
-            "X": z((T, c.hc, sc.sh), f32), "xn": z((T, c.hch), bf), "d": z((self.hc_ksplit, T, self.hc_ld), f32), "u": z((T, c.hc_rank), bf),
-            "inj_a": z((T, c.hc), f32), "inj_b": z((T, c.hc), f32), "g": z((T, c.hch), f32), "bin": z((T, c.hidden), bf),
-            "proj": z((T, self.proj_ld), f32), "o": z((T, max(sc.gdn_vl * c.gdn_dim, sc.qh_l * c.head_dim)), bf),
-            "out_a": z((T, c.hidden), f32), "out_b": z((T, c.hidden), f32),
+            "X": z((T, c.hc, sc.sh), f32), "xn": z((T, c.hc * sc.sh), bf), "d": z((self.hc_ksplit, T, self.hc_ld), f32) if one else None,
+            "u": z((T, c.hc_rank), bf), "inj_a": z((T, c.hc), f32), "inj_b": z((T, c.hc), f32), "g": z((T, c.hc * sc.sh), f32),
+            "bin": z((T, c.hidden), bf) if one else None,
+            "proj": z((T, self.proj_ld), f32), "o": z((T, self.o_ld), bf),
+            "out_a": z((T, c.hidden), f32) if one else None, "out_b": z((T, c.hidden if one else sc.sh), f32),
             "qkv": z((T, sc.gdn_qkv_l), f32), "decay": z((T, sc.gdn_vl), f32), "beta": z((T, sc.gdn_vl), f32),
             "q": z((T, sc.qh_l, c.head_dim), f32), "iq": z((T, c.idx_heads, c.idx_dim), f32),
             "scores": z((T, dm.model.d.score_cap), f32), "sel": z((T, c.idx_topk_blocks), i32), "sel_n": z((T,), i32),
-            "pm": z((attn_rows, sc.qh_l, dm.model.d.nsplit), f32), "pl": z((attn_rows, sc.qh_l, dm.model.d.nsplit), f32),
-            "pacc": z((attn_rows, sc.qh_l, dm.model.d.nsplit, c.head_dim), f32),
             "rs": z((T, self.nrs_ld), f32), "pe": z((T, c.top_k), i32), "pw": z((T, c.top_k), f32),
             "sh_h": z((T, sc.sffn_l), bf), "sd": z((T, c.hidden), f32),
             "xperm": z((Pn + 128, c.hidden), bf), "h13": z((Pn, 2 * c.ffn), bf), "h": z((Pn + 128, c.ffn), bf),
             "y": z((Pn, c.hidden), f32),
-            "ple_e": z((T, c.hidden), bf), "ple_kv": z((T, (sc.ple_kv + 7) // 8 * 8), f32), "ple_send": z((T, 16), f32),
+            "ple_e": z((T, c.hidden), bf), "ple_kv": z((T, self.ple_ld), f32), "ple_send": z((T, 16), f32), "ple_red": z((T, 16), f32),
             "ple_gv": z((T, sc.xw), f32), "ple_nc": z((T, sc.xw), f32),
-            "rows": z((8 * T,), i32),
+            "rows": z((11 * T,), i32),
             "inv": z((Pn,), i32), "src_token": z((Pn,), i32),
-            "t13": z((Pn // 128 + sc.exp_l, 4), i32), "t2": z((Pn // 128 + sc.exp_l, 4), i32),
+            "t13": z((2 * self.max_tiles, 4), i32), "t2": z((2 * self.max_tiles, 4), i32),
+            "gdn_scratch": z((2 * self.gdn_scratch_lane,), f32),
+            "hid_out": z((c.hc, sc.sh), f32), "amax16": z((16,), f32),
         }
-        # the GDN scan of a chunk runs in its chunked (tensor-core) form; QW_GDN_SEQUENTIAL=1 keeps the row-by-row scan
-        self.gdn_chunked = not settings.get().gdn_sequential
-        # QSA attention of a chunk: one tensor-core launch over all rows; QW_QSA_ATTEND_ROWS=1 keeps the decode kernels
-        self.qsa_mma = not settings.get().qsa_attend_rows and sc.qh_l // sc.kvh_l <= 16
-        if self.gdn_chunked:
-            nch = (T + 63) // 64
-            self.b["gdn_scratch"] = z((nch * sc.gdn_vl * (2 * 64 * 128 + 64 * 64 + 64) + T * sc.gdn_vl * 128,), f32)
-        # expert GEMMs read the q4 words themselves; QW_MOE_DEQUANT_SCRATCH=1 converts a layer's experts to bf16 first
-        self.q4_fused = not settings.get().moe_dequant_scratch and c.hidden % 128 == 0 and c.ffn % 128 == 0
-        if not self.q4_fused:
-            self.b["w13dq"] = z((sc.exp_l * 2 * c.ffn, c.hidden), bf)
-            self.b["w2dq"] = z((sc.exp_l * c.hidden, c.ffn), bf)
-        self.rows_host = torch.zeros(8 * T, dtype=torch.int32).pin_memory()
-        self.max_tiles = Pn // 128 + sc.exp_l
+        # the run_py path keeps the decode kernels' attention scratch
+        self.gdn_chunked = not st.gdn_sequential
+        self.qsa_mma = not st.qsa_attend_rows and sc.qh_l // sc.kvh_l <= 16
+        self.q4_fused = not st.moe_dequant_scratch and c.hidden % 128 == 0 and c.ffn % 128 == 0
+        # the native runtime covers the default forms of the kernels; the diagnostic forms run from Python
+        self.native = (not st.prefill_py and self.gdn_chunked and self.qsa_mma and self.q4_fused) or self.tp
+        if self.tp and not (self.gdn_chunked and self.qsa_mma and self.q4_fused):
+            raise ValueError("QW_GDN_SEQUENTIAL / QW_QSA_ATTEND_ROWS / QW_MOE_DEQUANT_SCRATCH are one-GPU diagnostics")
+        if not self.native:
+            if not self.qsa_mma:
+                nsp = dm.model.d.nsplit
+                self.b["pm"], self.b["pl"] = z((attn_rows, sc.qh_l, nsp), f32), z((attn_rows, sc.qh_l, nsp), f32)
+                self.b["pacc"] = z((attn_rows, sc.qh_l, nsp, c.head_dim), f32)
+            if not self.q4_fused:
+                self.b["w13dq"] = z((sc.exp_l * 2 * c.ffn, c.hidden), bf)
+                self.b["w2dq"] = z((sc.exp_l * c.hidden, c.ffn), bf)
+        self.rows_host = torch.zeros(11 * T, dtype=torch.int32).pin_memory()
+        self.side_stream = torch.cuda.Stream(device=dev) if self.lanes == 2 else None
+        self.bufs = S.QwPrefillBufs()
+        self._hook_cb = None
+        self._over = None
+        self._fill_struct()
+
+    def _ensure_mtp_buffers(self):
+        """Buffers of the MTP pass, made when a model with an MTP head first prefills."""
+        if "Xm" in self.b:
+            return
+        dm, c, sc, T = self.dm, self.dm.cfg, self.dm.sc, self.T
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dm.dev)
+        self.b["Xm"] = z((T, c.hc, sc.sh), torch.float32)
+        self.b["hn"] = z((T * c.hc, c.hidden), torch.bfloat16) if not self.tp else None
+        self.b["en"] = z((T, c.hidden), torch.bfloat16)
+        self.b["fh"], self.b["fe"] = z((T * c.hc, sc.sh), torch.float32), z((T, sc.sh), torch.float32)
+        self.b["mtp_ssq"] = z((2, T), torch.float32)
+        self._fill_struct()
+
+    def _fill_struct(self):
+        b, s, T = self.b, self.bufs, self.T
+        for name in S.PREFILL_PTR_FIELDS:
+            t = b.get(name)
+            setattr(s, name, None if t is None else t.data_ptr())
+        r = b["rows"].data_ptr()
+        s.tokens, s.slot, s.pos, s.run_start, s.run_len, s.ctx3 = r, r + 4 * T, r + 8 * T, r + 12 * T, r + 16 * T, r + 20 * T
+        s.m_slot, s.m_pos, s.m_run_start, s.m_run_len, s.mtp_tok = r + 4 * T, r + 32 * T, r + 12 * T, r + 36 * T, r + 40 * T
+        s.cap, s.hc_ld, s.hc_ksplit, s.nrs_ld, s.proj_ld = T, self.hc_ld, self.hc_ksplit, self.nrs_ld, self.proj_ld
+        s.o_ld, s.ple_ld, s.max_tiles, s.gdn_scratch_lane = self.o_ld, self.ple_ld, self.max_tiles, self.gdn_scratch_lane
 
     # ---- helpers
     def _s(self):
@@ -99,7 +152,16 @@ class Prefiller:
         self._ck(self.lib.qwk_gemm_bf16_tc(_p(A), P(W_ptr), _p(out), T, N, K, A.stride(0), ldw or K, out.stride(0),
                                            1 if out.dtype == torch.bfloat16 else 0, self._s()), "gemm")
 
-    def _rows(self, slot, base, T, toks, ctx3):
+    def lane_split(self, T: int):
+        """Rows of lane 0 when a chunk of T rows runs as two micro-batches (a multiple of the GDN scan's 64-row chunk)."""
+        if self.lanes < 2 or T < 2:
+            return T
+        n0 = (T // 2 + 63) // 64 * 64
+        return n0 if n0 < T else T // 2
+
+    def _rows(self, slot, base, T, toks, ctx3, mtp_tokens=(), mtp_base=0, n0=None):
+        """Row tables of a chunk (pinned host memory -> device, one copy): tokens | slot | pos | run_start | run_len | ctx3 |
+        MTP positions | MTP run_len | MTP next tokens.  Run tables are relative to a lane's first row."""
         Tm = self.T
         h = self.rows_host.numpy()
         h[0:T] = toks
@@ -107,12 +169,92 @@ class Prefiller:
         h[2 * Tm:2 * Tm + T] = np.arange(base, base + T, dtype=np.int32)
         h[3 * Tm:3 * Tm + T] = 0
         h[4 * Tm:4 * Tm + T] = 0
-        h[4 * Tm] = T
+        n0 = T if n0 is None else n0
+        h[4 * Tm] = n0
+        if n0 < T:
+            h[4 * Tm + n0] = T - n0
         h[5 * Tm:5 * Tm + 3 * T] = ctx3.reshape(-1)
+        nm = len(mtp_tokens)
+        if nm:
+            h[8 * Tm:8 * Tm + nm] = np.arange(mtp_base, mtp_base + nm, dtype=np.int32)
+            h[9 * Tm:9 * Tm + nm] = 0
+            h[9 * Tm] = nm
+            h[10 * Tm:10 * Tm + nm] = mtp_tokens
         self.b["rows"].copy_(self.rows_host, non_blocking=True)
         r = self.b["rows"].data_ptr()
         return {"tokens": r, "slot": r + 4 * Tm, "pos": r + 8 * Tm, "run_start": r + 12 * Tm, "run_len": r + 16 * Tm,
                 "ctx3": r + 20 * Tm}
+
+    # ---- one chunk through the native runtime
+    def make_job(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True, embeds=None,
+                 mtp: bool = False, pending: Optional[torch.Tensor] = None) -> S.QwPrefillJob:
+        """Stage the chunk's row tables and describe it for ``qwrt_prefill``.  ``mtp``: also run the MTP head over the rows
+        whose next token is known, preceded by the row of ``pending`` (the hidden state of the position before the chunk)."""
+        dm, c = self.dm, self.dm.cfg
+        T = len(tokens)
+        assert 1 <= T <= self.T
+        toks = [c.real_token(int(t)) for t in tokens]
+        mtp_tokens, mtp_base = [], base
+        if mtp:
+            self._ensure_mtp_buffers()
+            if pending is not None and base > 0:
+                dm.buf["hidden_out"][0].copy_(pending)
+                mtp_tokens, mtp_base = toks[:T], base - 1
+            else:
+                pending = None
+                mtp_tokens = toks[1:T]
+        lanes = self.lanes if T >= 128 else 1          # a short chunk runs as one lane
+        n0 = self.lane_split(T) if lanes == 2 else T
+        self._rows(slot, base, T, toks, np.asarray(ctx3, dtype=np.int32), mtp_tokens, mtp_base, n0)
+        j = S.QwPrefillJob()
+        j.md, j.b = C.pointer(dm.model), C.pointer(self.bufs)
+        cur = torch.cuda.current_stream(dm.dev)
+        j.stream[0] = cur.cuda_stream
+        j.stream[1] = self.side_stream.cuda_stream if self.side_stream is not None else cur.cuda_stream
+        for l in range(2):
+            j.tp[l] = self.channels[min(l, len(self.channels) - 1)].ptr if self.tp else None
+        j.T, j.lanes, j.base, j.want_logits = T, lanes, base, int(bool(want_logits))
+        j.n0 = n0
+        j.layer_limit = -1 if self.layer_limit is None else int(self.layer_limit)
+        j.mtp_rows, j.mtp_base, j.has_pending = len(mtp_tokens), mtp_base, int(pending is not None)
+        j.n_over = 0
+        if embeds is not None:          # (row indices, [n, hidden] fp32): these rows' embedding replaces the table's
+            rows_i, emb = embeds
+            self._over = (rows_i.to(dm.dev, torch.int32).contiguous(), emb.to(dm.dev, torch.float32).contiguous())
+            self.bufs.over_rows, self.bufs.over_emb = self._over[0].data_ptr(), self._over[1].data_ptr()
+            j.n_over = int(self._over[0].numel())
+        if self.on_block_input is not None:
+            def hook(user, layer, which, bin_ptr, ld, r0, n):
+                self.on_block_input(layer, "attn" if which == 0 else "mlp", self.block_input(0 if r0 == 0 else 1, r0, n))
+            self._hook_cb = S.PREFILL_HOOK(hook)
+            j.hook = self._hook_cb
+        return j
+
+    def block_input(self, lane: int, r0: int, n: int) -> torch.Tensor:
+        """The block-input rows of a lane as a tensor [n, hidden] (bf16)."""
+        H = self.dm.cfg.hidden
+        if self.tp:
+            return self.channels[lane].view(S.TP_BIN, n * H * 2, torch.bfloat16).view(n, H)
+        return self.b["bin"][r0:r0 + n]
+
+    @staticmethod
+    def launch(lib, jobs: List[S.QwPrefillJob]) -> None:
+        """Enqueue the chunk of every job (several jobs: emulated ranks of one process, all on one stream)."""
+        arr = (C.POINTER(S.QwPrefillJob) * len(jobs))(*[C.pointer(j) for j in jobs])
+        rc = lib.qwrt_prefill(arr, len(jobs))
+        if rc != 0:
+            raise RuntimeError(f"qwrt_prefill failed: {rc}")
+
+    @torch.no_grad()
+    def run(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True, embeds=None,
+            mtp: bool = False, pending: Optional[torch.Tensor] = None):
+        """One chunk.  Returns the logits of the last token (this rank's vocabulary shard; the argmax over all ranks is in
+        ``dm.buf['amax_idx'][0]``).  After a chunk with ``mtp``, ``self.b['hid_out']`` holds the next call's pending row."""
+        if not self.native:
+            return self.run_py(slot, base, tokens, ctx3, want_logits, embeds)
+        job = self.make_job(slot, base, tokens, ctx3, want_logits, embeds, mtp, pending)
+        self.launch(self.lib, [job])
+        return self.dm.buf["logits"][0] if want_logits else None
 
     def mix(self, hc, T, pend, inj_prev, inj_out, n_inj):
         dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
@@ -129,12 +271,12 @@ class Prefiller:
         self.gemm(b["u"][:T], hc["Wu"].data_ptr(), c.hch, c.hc_rank, b["g"][:T])
         self._ck(L.qwk_hc_mix_T(_p(b["g"]), _p(b["xn"]), sc.sh, _p(b["bin"]), c.hidden, T, s), "hc_mix")
 
-    # ---- one chunk
+    # ---- one chunk, scheduled from Python (one GPU, one lane)
     @torch.no_grad()
-    def run(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True, embeds=None):
+    def run_py(self, slot: int, base: int, tokens: Sequence[int], ctx3: np.ndarray, want_logits: bool = True, embeds=None):
         dm, b, c, sc, L = self.dm, self.b, self.dm.cfg, self.dm.sc, self.lib
         T = len(tokens)
-        assert 1 <= T <= self.T
+        assert 1 <= T <= self.T and not self.tp
         s = self._s()
         rows = self._rows(slot, base, T, [c.real_token(int(t)) for t in tokens], np.asarray(ctx3, dtype=np.int32))
         self._last_rows = rows
@@ -260,15 +402,13 @@ class Prefiller:
         if n == 0:
             return
         s = self._s()
-        if "hn" not in b:
-            z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dm.dev)
-            b["hn"], b["en"] = z((self.T * c.hc, c.hidden), torch.bfloat16), z((self.T, c.hidden), torch.bfloat16)
-            b["fh"], b["fe"] = z((self.T * c.hc, c.hidden), torch.float32), z((self.T, c.hidden), torch.float32)
-            b["mtp_tok"] = z((self.T,), torch.int32)
-        b["mtp_tok"][:n].copy_(torch.as_tensor([c.real_token(int(t)) for t in next_tokens], dtype=torch.int32), non_blocking=True)
+        self._ensure_mtp_buffers()
+        if "mtp_tok_py" not in b:
+            b["mtp_tok_py"] = torch.zeros((self.T,), dtype=torch.int32, device=dm.dev)
+        b["mtp_tok_py"][:n].copy_(torch.as_tensor([c.real_token(int(t)) for t in next_tokens], dtype=torch.int32), non_blocking=True)
         rows = self._last_rows
         rp = lambda k, off=0: P(rows[k] + 4 * off)
-        self._ck(L.qwk_mtp_norm(_p(b["X"]), _p(b["mtp_tok"]), P(dm.globals_w["embed"].data_ptr()), c.vocab, P(w["nh1"].data_ptr()),
+        self._ck(L.qwk_mtp_norm(_p(b["X"]), _p(b["mtp_tok_py"]), P(dm.globals_w["embed"].data_ptr()), c.vocab, P(w["nh1"].data_ptr()),
                                 P(w["ne1"].data_ptr()), c.hidden, c.hc, C.c_float(c.eps), _p(b["hn"]), _p(b["en"]), n, s), "mtp_norm")
         self.gemm(b["hn"][:n * c.hc], w["fc_h"].data_ptr(), c.hidden, c.hidden, b["fh"][:n * c.hc])
         self.gemm(b["en"][:n], w["fc_e"].data_ptr(), c.hidden, c.hidden, b["fe"][:n])

@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include "stream.cuh"
+#include "tp.cuh"
 
 namespace qw {
 
@@ -71,6 +72,10 @@ struct GemmTcArgs {
     // to C + s * c_split (the consumer adds the splits in order); ksplit == 1: the whole K, c_split unused
     int ksplit, kb_per;
     long long c_split;
+    // tensor-parallel prefill (tp.cuh): the producer thread waits for a gathered A operand before its first load; the
+    // epilogue sends fp32 tiles to other ranks' receive buffers instead of (mode != 0) storing them to C
+    TpWait wait;
+    TpEpilogue epi;
 };
 
 struct TileAt {
@@ -111,6 +116,26 @@ __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) 
 // One 32-column piece of an accumulator row -> C.
 __device__ __forceinline__ void store_piece(const GemmTcArgs &a, long long c_off, int row, int col0, const uint32_t (&v)[32]) {
     const int nmax = a.N - col0;
+    if (a.epi.mode) {
+        // fp32 pieces to the receive buffers: every rank's (parts of an all-reduce) or the column owner's (reduce-scatter)
+        const int owner = a.epi.mode == 2 ? col0 / a.epi.cols_per_rank : 0;
+        const long long off = (long long)row * a.epi.ld + (col0 - owner * a.epi.cols_per_rank * (a.epi.mode == 2));
+        const bool vec = nmax >= 32 && ((a.epi.ld | col0) & 3) == 0;
+#pragma unroll
+        for (int d = 0; d < TP_MAX_RANKS; ++d) {
+            if (d >= a.epi.ranks || (a.epi.mode == 2 && d != owner)) continue;
+            float *o = a.epi.dst[d] + off;
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            } else {
+                for (int j = 0; j < 32 && j < nmax; ++j) o[j] = __uint_as_float(v[j]);
+            }
+        }
+        return;
+    }
     if (a.C32) {
         float *o = a.C32 + c_off + (long long)row * a.ldc + col0;
         if (nmax >= 32 && ((a.ldc | col0) & 3) == 0) {
@@ -264,7 +289,7 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__
     if (warp == 0) {
         if (lane == 0) {
             unsigned it = 0;
-            bool ok = true;
+            bool ok = tp_wait_thread(a.wait);
             for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
                 TileAt t;
                 if (!tile_at(a, id, t)) continue;
@@ -284,6 +309,7 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__
         epilogue_role(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 8);
     }
     tc_teardown(sh, warp);
+    tp_signal(a.epi.sig);
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -436,27 +462,84 @@ static unsigned persistent_grid(int total) {
 
 using namespace qw;
 
-// C = A . W^T.  A bf16 [T][lda], W bf16 [N][ldw], C fp32 (out_bf16 = 0) or bf16 [T][ldc].
-// Base addresses 16-byte aligned, lda/ldw multiples of 8 elements, K a multiple of 8.
-QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
-                            int out_bf16, cudaStream_t s) {
-    if (T <= 0 || N <= 0) return 0;
+// One-time (per device) opt-in to the kernels' dynamic shared memory.
+static bool configure_once(const void *kernel) {
+    static bool done[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    const int which = kernel == (const void *)gemm_tc_q4_kernel ? 1 : 0;
+    if (!done[which][dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return false;
+        done[which][dev] = true;
+    }
+    return true;
+}
+
+static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
+                      int out_bf16, cudaStream_t s) {
     if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -1;
     CUtensorMap mA, mW;
     if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_BN)) return -3;
-    GemmTcArgs a;
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        configured = true;
-    }
-    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
+    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
+    const unsigned grid = persistent_grid(a.total);
+    if (a.epi.sig.ticket) a.epi.sig.nblocks = grid;
+    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// C = A . W^T.  A bf16 [T][lda], W bf16 [N][ldw], C fp32 (out_bf16 = 0) or bf16 [T][ldc].
+// Base addresses 16-byte aligned, lda/ldw multiples of 8 elements, K a multiple of 8.
+QW_API int qwk_gemm_bf16_tc(const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
+                            int out_bf16, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    GemmTcArgs a{};
+    return gemm_plain(a, A, W, C, T, N, K, lda, ldw, ldc, out_bf16, s);
+}
+
+// Tensor-parallel forms of the same product (tp.cuh); `tp` is the rank's QwTp channel.
+//   wait_kind >= 0 : A lies in the receive buffer of that all-gather kind; the kernel waits for the kind's latest
+//                    collective before its first load of A.
+//   epi_mode 0     : C as above.
+//   epi_mode 1     : the fp32 result goes to every rank's receive buffer of kind `epi_kind` as this rank's part of an
+//                    all-reduce (rows of ld_epi floats); C is not written.
+//   epi_mode 2     : N = ranks * cols_per_rank; columns go to the rank that owns them, as this rank's part of a
+//                    reduce-scatter (rows of cols_per_rank floats, cols_per_rank a multiple of 32); C is not written.
+// In modes 1 and 2 the kernel publishes the collective when its last CTA has stored its tiles.
+QW_API int qwk_gemm_bf16_tc_tp(void *tp_, const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
+                               int out_bf16, int wait_kind, int epi_mode, int epi_kind, int ld_epi, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    QwTp *tp = (QwTp *)tp_;
+    GemmTcArgs a{};
+    if (!tp || tp->ranks < 1 || tp->ranks > TP_MAX_RANKS) return -1;
+    if (wait_kind >= 0) {
+        if (wait_kind >= TP_KINDS) return -1;
+        a.wait = tp_make_wait(tp, wait_kind);
+    }
+    if (epi_mode) {
+        if (epi_kind < 0 || epi_kind >= TP_KINDS || out_bf16) return -1;
+        a.epi.mode = epi_mode;
+        a.epi.ranks = tp->ranks;
+        if (epi_mode == 2) {
+            if (N % tp->ranks) return -1;
+            a.epi.cols_per_rank = N / tp->ranks;
+            if (a.epi.cols_per_rank & 31) return -1;
+            a.epi.ld = a.epi.cols_per_rank;
+        } else {
+            a.epi.cols_per_rank = 0;
+            a.epi.ld = ld_epi;
+            if (ld_epi < N) return -1;
+        }
+        if ((long long)T * a.epi.ld * 4 > tp->part_bytes[epi_kind]) return -1;
+        for (int d = 0; d < tp->ranks; ++d) a.epi.dst[d] = (float *)tp_part_on(tp, epi_kind, d);
+        a.epi.sig = tp_make_signal(tp, epi_kind, 1);
+    }
+    return gemm_plain(a, A, W, C, T, N, K, lda, ldw, ldc, out_bf16, s);
 }
 
 // Grouped form for expert-sorted rows: A bf16 [rows][lda] holds the rows of group after group, W bf16
@@ -470,13 +553,13 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -1;
     CUtensorMap mA, mW;
     if (!make_map(&mA, A, rows, K, lda, TC_BM) || !make_map(&mW, W, w_rows, K, ldw, TC_BN)) return -3;
-    GemmTcArgs a;
+    GemmTcArgs a{};
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
     gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -489,17 +572,13 @@ QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *sca
     if ((K & 127) || (lda & 7) || ((uintptr_t)A & 15) || ((uintptr_t)Wq & 15)) return -1;
     CUtensorMap mA;
     if (!make_map(&mA, A, rows, K, lda, TC_BM)) return -3;
-    GemmTcArgs a;
+    GemmTcArgs a{};
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return -3;
-        configured = true;
-    }
+    if (!configure_once((const void *)gemm_tc_q4_kernel)) return -3;
     gemm_tc_q4_kernel<<<persistent_grid(a.total), 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -514,7 +593,7 @@ QW_API int qwk_gemm_bf16_tc_splitk(const void *A, const void *W, float *C, int T
     if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ksplit < 1 || ksplit > kblocks) return -1;
     CUtensorMap mA, mW;
     if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_BN)) return -3;
-    GemmTcArgs a;
+    GemmTcArgs a{};
     a.C32 = C; a.C16 = nullptr;
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN;
@@ -523,11 +602,7 @@ QW_API int qwk_gemm_bf16_tc_splitk(const void *A, const void *W, float *C, int T
     if (a.ksplit != ksplit) return -1;
     a.c_split = c_split;
     a.total = a.tiles_t * a.tiles_n * a.ksplit;
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        configured = true;
-    }
+    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
     gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

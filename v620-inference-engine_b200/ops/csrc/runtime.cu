@@ -337,6 +337,32 @@ void ple_block(Ctx &c) {
 
 }  // namespace
 
+// lm_head over the gathered block input, per-row reductions, the vocabulary-parallel argmax merge, and (chained
+// steps) the rows' advance to their sampled tokens.
+static void head(Ctx &c, int flags) {
+    const QwModel *md = c.md;
+    const QwDims &d = md->d;
+    const QwBuffers &b = md->b;
+    const int M = c.rows->M;
+    await_bin(c);
+    QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
+                         c.s));
+    QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
+                          b.lse_sum, c.s));
+    if (d.ranks > 1 && md->p2p && md->amax_pairs) {
+        // vocabulary-parallel argmax: gather every rank's (value, index) and merge on the device
+        QW_TRYN(1, qwk_amax_pack(b.amax_val, b.amax_idx, md->amax_pairs, M, d.rank, d.ranks, c.s));
+        ++c.site;
+        if (!c.dry) {
+            QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_amax, M, 2, 4, c.s));
+        }
+        QW_TRYN(1, qwk_amax_merge(md->amax_pairs, M, d.ranks, b.amax_idx, b.amax_val, c.s));
+    }
+    if ((flags & QWRT_CHAIN) && (d.ranks == 1 || md->p2p))
+        QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
+                                const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
+}
+
 // The launch sequence of one step.  With c.dry it only records the weights of the prefetch-capable
 // launches; otherwise it enqueues the kernels.
 static void walk(Ctx &c, int flags, int n_layers_run) {
@@ -377,25 +403,7 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     mix(c, c.md->final_hc, pend, inj_mlp, nullptr);
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
         if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
-    if (!(flags & QWRT_NO_HEAD)) {
-        await_bin(c);
-        QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
-                             c.s));
-        QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
-                              b.lse_sum, c.s));
-        if (d.ranks > 1 && md->p2p && md->amax_pairs) {
-            // vocabulary-parallel argmax: gather every rank's (value, index) and merge on the device
-            QW_TRYN(1, qwk_amax_pack(b.amax_val, b.amax_idx, md->amax_pairs, M, d.rank, d.ranks, c.s));
-            ++c.site;
-            if (!c.dry) {
-                QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_amax, M, 2, 4, c.s));
-            }
-            QW_TRYN(1, qwk_amax_merge(md->amax_pairs, M, d.ranks, b.amax_idx, b.amax_val, c.s));
-        }
-        if ((flags & QWRT_CHAIN) && (d.ranks == 1 || md->p2p))
-            QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
-                                    const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
-    }
+    if (!(flags & QWRT_NO_HEAD)) head(c, flags);
 }
 
 // The MTP pass (see runtime.h).
@@ -409,11 +417,28 @@ static void walk_mtp(Ctx &c, int flags) {
     c.Xalt = b.X2;
     c.site = 0;
     c.op = 0;
-    QW_TRYN(1, qwk_mtp_norm(b.hidden_out, c.rows->tokens, md->embed, d.vocab, t.nh1, t.ne1, d.H, d.hc, d.eps, t.hn, t.en, M, c.s));
-    QW_OP(1, t.fc_h, (size_t)d.H * d.H * 2,
-          qwk_gemv_bf16(t.fc_h, t.hn, t.fh, nullptr, d.H, d.H, M * d.hc, d.H, d.H, d.H, 0, 1, 0, 0, 0, c.s));
-    QW_OP(1, t.fc_e, (size_t)d.H * d.H * 2, qwk_gemv_bf16(t.fc_e, t.en, t.fe, nullptr, d.H, d.H, M, d.H, d.H, d.H, 0, 1, 0, 0, 0, c.s));
-    QW_TRYN(1, qwk_mtp_add(t.fh, t.fe, d.H, d.hc, c.X, M, c.s));
+    c.fuse = d.ranks > 1 && md->p2p && g_fuse;
+    c.mute = g_fuse == 2;
+    c.bin_pending = c.pend_fused = false;
+    const float *hidden = b.hidden_out;
+    if (d.ranks > 1) {
+        // The input norm is one RMS over all hc * H values of a row and the fc products take whole rows: gather the ranks'
+        // column slices of the hidden states into a [M*hc][H] matrix inside the symmetric region.  The fc matrices are
+        // sliced by output rows, so their products are this rank's columns of the new residual: no collective after them.
+        QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
+        if (!c.dry) {
+            cudaMemcpy2DAsync(md->mtp_hid + (size_t)d.rank * d.SH, sizeof(float) * (size_t)d.H, b.hidden_out, sizeof(float) * (size_t)d.SH,
+                              sizeof(float) * (size_t)d.SH, (size_t)M * d.hc, cudaMemcpyDeviceToDevice, c.s);
+        }
+        ++c.site;
+        if (!c.dry) QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_mtp_hid, M * d.hc, d.SH, 4, c.s));
+        hidden = md->mtp_hid;
+    }
+    QW_TRYN(1, qwk_mtp_norm(hidden, c.rows->tokens, md->embed, d.vocab, t.nh1, t.ne1, d.H, d.hc, d.eps, t.hn, t.en, M, c.s));
+    QW_OP(1, t.fc_h, (size_t)d.SH * d.H * 2,
+          qwk_gemv_bf16(t.fc_h, t.hn, t.fh, nullptr, d.SH, d.H, M * d.hc, d.H, d.H, d.SH, 0, 1, 0, 0, 0, c.s));
+    QW_OP(1, t.fc_e, (size_t)d.SH * d.H * 2, qwk_gemv_bf16(t.fc_e, t.en, t.fe, nullptr, d.SH, d.H, M, d.H, d.H, d.SH, 0, 1, 0, 0, 0, c.s));
+    QW_TRYN(1, qwk_mtp_add(t.fh, t.fe, d.SH, d.hc, c.X, M, c.s));
     float *inj_attn = b.inj_a, *inj_mlp = b.inj_b;
     mix(c, t.layer.attn_hc, nullptr, inj_mlp, inj_attn);
     qsa_block(c, t.layer);
@@ -423,12 +448,7 @@ static void walk_mtp(Ctx &c, int flags) {
     const float *pend = scatter(c, b.out_b);
     mix(c, t.final_hc, pend, inj_mlp, nullptr);
     if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
-    QW_OP(1, md->lm_head, (size_t)d.vocab_l * d.H * 2,
-          qwk_gemv_bf16(md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0, c.s));
-    QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, 0, M, b.amax_val, b.amax_idx, b.lse_max, b.lse_sum, c.s));
-    if (flags & QWRT_CHAIN)
-        QW_TRYN(1, qwk_advance_rows(const_cast<int *>(c.rows->tokens), const_cast<int *>(c.rows->pos),
-                                    const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
+    head(c, flags);
 }
 
 // Ranges of later kernels' weights that launch k asks the L2 to fetch: the plan keeps the prefetch
@@ -496,7 +516,7 @@ extern "C" __attribute__((visibility("default"))) long long qwrt_last_launches()
 
 extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md, const QwRows *rows, int flags,
                                                                 cudaStream_t stream) {
-    if (!md->mtp.enabled || md->d.ranks != 1) return -1;
+    if (!md->mtp.enabled || (md->d.ranks != 1 && (!md->p2p || !md->mtp_hid))) return -1;
     const int M = rows->M;
     if (M < 1 || M * md->d.hc > md->d.max_rows * md->d.hc) return -1;
     Ctx c{};

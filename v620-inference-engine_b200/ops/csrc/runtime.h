@@ -64,11 +64,11 @@ typedef struct QwMtp {
     int enabled, pad_;
     QwLayer layer;             // a QSA decoder layer (its KV lives at state index n_qsa)
     QwHc final_hc;
-    const void *fc_h, *fc_e;   // bf16 [H][H]
+    const void *fc_h, *fc_e;   // bf16 [SH][H]: this rank's output rows
     const float *nh1;          // (1+w) [hc*H]: pre_fc_norm_hidden
     const float *ne1;          // (1+w) [H]: pre_fc_norm_embedding
     void *hn, *en;             // bf16 [rows*hc][H], [rows][H]
-    float *fh, *fe;            // fp32 [rows*hc][H], [rows][H]
+    float *fh, *fe;            // fp32 [rows*hc][SH], [rows][SH]
 } QwMtp;
 
 typedef struct QwState {
@@ -146,6 +146,8 @@ typedef struct QwModel {
     long long off_amax;        // its offset inside the region
     long long off_bin;         // offset of b.bin inside the region
     QwMtp mtp;
+    float *mtp_hid;            // several ranks: [rows*hc][H] fp32 inside the symmetric region, the gathered hidden states of an MTP pass
+    long long off_mtp_hid;     // its offset inside the region
 } QwModel;
 
 // flags of qwrt_decode
@@ -158,7 +160,7 @@ int qwrt_decode(const QwModel *md, const QwRows *rows, int flags, int n_layers_r
 
 // One MTP pass over the rows: input b.hidden_out (the pre-final-mixer state of each row's position) and
 // rows->tokens (the token AFTER that position); output logits / argmax of the position after that, and the MTP's
-// own pre-final-mixer state back in b.hidden_out (the input of a chained next draft).  One GPU only.
+// own pre-final-mixer state back in b.hidden_out (the input of a chained next draft).  Several ranks: peer-memory collectives only.
 int qwrt_mtp(const QwModel *md, const QwRows *rows, int flags, cudaStream_t stream);
 
 }  // extern "C"

@@ -61,10 +61,57 @@ COMM_FN = C.CFUNCTYPE(None, P, C.c_int, C.c_int, P, P, C.c_int, C.c_int, P)
 class QwModel(C.Structure):
     _fields_ = [("d", QwDims), ("layers", C.POINTER(QwLayer)), ("final_hc", QwHc), ("ple", QwPle), ("embed", P),
                 ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P),
-                ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong), ("mtp", QwMtp)]
+                ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong), ("mtp", QwMtp),
+                ("mtp_hid", P), ("off_mtp_hid", C.c_longlong)]
 
 
 class QwP2P(C.Structure):
     _fields_ = [("peer", P * 8), ("ranks", C.c_int), ("rank", C.c_int), ("base", P), ("off_flags", C.c_longlong * 4),
                 ("off_recv", C.c_longlong * 4), ("slot_bytes", C.c_longlong * 4), ("off_bin", C.c_longlong),
                 ("off_amax", C.c_longlong)]
+
+
+# ---- token-major prefill runtime (csrc/prefill_rt.h, csrc/tp.cuh) -------------------------------------------------
+TP_KINDS = 6
+TP_SSQ, TP_DOWN, TP_BIN, TP_RS, TP_SMALL, TP_WIDE = range(6)
+
+
+class QwTp(C.Structure):
+    _fields_ = [("peer", P * 8), ("ranks", C.c_int), ("rank", C.c_int), ("off_flags", C.c_longlong),
+                ("off_buf", C.c_longlong * 6), ("part_bytes", C.c_longlong * 6), ("ticket", P), ("seq", C.c_uint * 6),
+                ("spin_limit", C.c_uint), ("pad_", C.c_int)]
+
+
+PREFILL_PTR_FIELDS = (
+    "X", "xn", "d", "u", "inj_a", "inj_b", "g", "bin", "proj", "o", "out_a", "out_b", "qkv", "decay", "beta",
+    "q", "iq", "scores", "sel", "sel_n", "rs", "pe", "pw", "sh_h", "sd", "xperm", "h13", "h", "y", "inv", "src_token",
+    "t13", "t2", "gdn_scratch", "ple_e", "ple_kv", "ple_send", "ple_red", "ple_gv", "ple_nc",
+    "Xm", "hn", "en", "fh", "fe", "mtp_ssq", "mtp_tok", "hid_out", "amax16",
+    "tokens", "slot", "pos", "run_start", "run_len", "ctx3", "m_slot", "m_pos", "m_run_start", "m_run_len",
+    "over_rows", "over_emb")
+PREFILL_INT_FIELDS = ("cap", "hc_ld", "hc_ksplit", "nrs_ld", "proj_ld", "o_ld", "ple_ld", "max_tiles")
+
+
+class QwPrefillBufs(C.Structure):
+    _fields_ = [(n, P) for n in PREFILL_PTR_FIELDS] + [(n, C.c_int) for n in PREFILL_INT_FIELDS] + \
+               [("gdn_scratch_lane", C.c_longlong)]
+
+
+PREFILL_HOOK = C.CFUNCTYPE(None, P, C.c_int, C.c_int, P, C.c_int, C.c_int, C.c_int)
+
+
+class QwPrefillJob(C.Structure):
+    _fields_ = [("md", C.POINTER(QwModel)), ("b", C.POINTER(QwPrefillBufs)), ("tp", P * 2), ("stream", P * 2),
+                ("T", C.c_int), ("lanes", C.c_int), ("base", C.c_int), ("want_logits", C.c_int), ("layer_limit", C.c_int),
+                ("mtp_rows", C.c_int), ("mtp_base", C.c_int), ("has_pending", C.c_int), ("n_over", C.c_int), ("n0", C.c_int),
+                ("hook", PREFILL_HOOK), ("hook_user", P)]
+
+
+def check_prefill_structs(lib) -> None:
+    """The C side's struct sizes must equal the mirrors' (a mismatch means the two field lists have drifted apart)."""
+    lib.qwrt_prefill_sizes.restype = C.c_longlong
+    lib.qwrt_prefill_sizes.argtypes = [C.c_int]
+    for which, cls in ((0, QwPrefillBufs), (1, QwPrefillJob), (2, QwTp)):
+        want, have = int(lib.qwrt_prefill_sizes(which)), C.sizeof(cls)
+        if want != have:
+            raise RuntimeError(f"{cls.__name__}: ctypes mirror is {have} bytes, the library's struct {want}")

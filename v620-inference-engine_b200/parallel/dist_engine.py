@@ -74,6 +74,7 @@ def attach_p2p(eng: Engine, group=None) -> None:
     take("recv2", 2 * R * slot2)
     take("bin", rows * c.hidden * 2)
     take("amax", rows * R * 2 * 4)
+    take("mtp_hid", rows * c.hc * c.hidden * 4)
     region = SymmetricRegion(off, dm.dev, group)
     p = S.QwP2P()
     for i in range(8):
@@ -99,7 +100,23 @@ def attach_p2p(eng: Engine, group=None) -> None:
     dm.model.amax_pairs = base + lay["amax"]
     dm.model.off_amax = lay["amax"]
     dm.model.off_bin = lay["bin"]
+    dm.model.mtp_hid = base + lay["mtp_hid"]
+    dm.model.off_mtp_hid = lay["mtp_hid"]
     dm.graphs.clear()
+
+
+def attach_tp(eng: Engine, group=None, lanes: int = 0) -> None:
+    """Channels of the token-major prefill (``ops/csrc/tp.cuh``): one symmetric region per micro-batch lane, sized for
+    the engine's prefill chunk.  Without them a multi-rank engine prefills with the row-batched decode kernels."""
+    from ..utils import settings
+    from . import tp_channel
+    dm = eng.dm
+    if eng.opts.prefill_chunk <= 0 or dm.sc.ranks == 1:
+        return
+    lanes = lanes or settings.get().prefill_lanes or 2
+    rows = min(eng.opts.prefill_chunk, max(256, dm.slot_tokens))
+    eng.tp_channels = [tp_channel.make_symmetric(dm.cfg, dm.sc, rows, dm.dev, bool(dm.cfg.mtp), group) for _ in range(lanes)]
+    eng.prefiller = None
 
 
 def set_fused(on: bool) -> None:
@@ -135,6 +152,7 @@ def attach_nccl(eng: Engine, group=None) -> None:
 
     dm.set_comm(cb)
     dm.model.p2p = None
+    dm.model.mtp.enabled = 0             # the MTP pass gathers hidden states through the peer-memory backend only
     eng.opts.use_graphs = False          # the collectives are enqueued from a host callback: steps are not graph-captured
 
     def merge_argmax(M):
@@ -161,6 +179,7 @@ def make_engine(cfg: ModelConfig, opts: EngineOptions, world: int, rank: int, de
         if comm in ("p2p", "p2p-unfused", "p2p-mute"):
             attach_p2p(eng)
             set_fused({"p2p": 1, "p2p-unfused": 0, "p2p-mute": 2}[comm])
+            attach_tp(eng)
         else:
             attach_nccl(eng)
     return eng

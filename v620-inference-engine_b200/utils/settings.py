@@ -53,6 +53,8 @@ class Settings:
     qsa_attend_rows: bool = False       # QW_QSA_ATTEND_ROWS: token-major prefill attends with the decode kernels (CUDA cores)
     moe_dequant_scratch: bool = False   # QW_MOE_DEQUANT_SCRATCH: token-major prefill converts a layer's q4 experts to bf16 before its GEMMs
     gdn_sequential: bool = False        # QW_GDN_SEQUENTIAL: token-major prefill scans GDN layers row by row (not chunked)
+    prefill_py: bool = False            # QW_PREFILL_PY: token-major prefill scheduled from Python, kernel by kernel (one GPU; the native runtime is the default)
+    prefill_lanes: int = 0              # QW_PREFILL_LANES: micro-batches per chunk, 1 or 2 (0 = two on several GPUs, one on one)
     spec_max_rows: int = 8              # QW_SPEC_MAX_ROWS: rows of one verification step
     weight_cache_dir: str = ""          # QW_WEIGHT_CACHE_DIR
     ple_dir: str = ""                   # QW_PLE_DIR
@@ -99,6 +101,7 @@ class Settings:
         need(self.prefill_chunk >= 0 and self.prefill_chunk % 256 == 0, "prefill_chunk must be a multiple of 256")
         need(self.prefill_piece > 0 and self.prefill_piece % 256 == 0, "prefill_piece must be a positive multiple of 256")
         need(0.0 < self.decode_share <= 1.0, "decode_share must be in (0, 1]")
+        need(self.prefill_lanes in (0, 1, 2), "prefill_lanes must be 0, 1 or 2")
         need(1 <= self.spec_max_rows <= 32, "spec_max_rows must be in 1..32")
         need(len(self.slots) >= 1 and all(s >= 256 for s in self.slots), "slots: at least one slot of >= 256 tokens")
         need(self.spill_policy in ("auto", "bind", "preferred", "interleave", "process"), "spill_policy")
