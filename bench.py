@@ -82,7 +82,7 @@ def main():
         cfg = ModelConfig(**{**cfg.__dict__, "n_layers": args.layers})
     e2e_steps = args.e2e_steps or K
     need = args.context + 2 * (W + K) + 2 * (W + e2e_steps) + 64
-    opts = EngineOptions(slots=1, slot_tokens=need, use_graphs=True, save_gdn=(world == 1))      # GDN state saves: speculative steps on one GPU
+    opts = EngineOptions(slots=1, slot_tokens=need, use_graphs=True, save_gdn=True)      # GDN state saves after every row: speculative verification
     t0 = time.time()
     if world > 1:
         from qwb200.parallel.dist_engine import make_engine
@@ -97,8 +97,9 @@ def main():
     # ---- context: 4,096 random tokens through the prefill path (untimed)
     g = torch.Generator().manual_seed(1234)
     ctx = torch.randint(0, cfg.vocab, (args.context,), generator=g).tolist()
-    if world == 1 and eng.opts.prefill_chunk:
-        eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, tensor maps), then start over
+    token_major = bool(eng.opts.prefill_chunk) and (world == 1 or eng.tp_channels is not None)
+    if token_major:
+        eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, kernel attributes), then start over
         torch.cuda.synchronize()
         eng.reset(0)
     t0 = time.time()
@@ -108,6 +109,7 @@ def main():
     pe1.record()
     torch.cuda.synchronize()
     prefill_ms = pe0.elapsed_time(pe1)
+    eng.dm.check_error()
     first = int(eng.dm.buf["amax_idx"][eng.last_prefill_row])
     log(f"context of {args.context} tokens in {time.time() - t0:.2f} s")
 
@@ -219,7 +221,8 @@ def main():
                     "h2d_bytes_per_step": int(eng.dm.rows_host.numel() * 4), "d2h_bytes_per_step": 4,
                     "api": "Engine.decode"},
             "prefill": {"tokens": args.context, "ms": round(prefill_ms, 2), "tok_s": round(args.context / (prefill_ms / 1e3), 1),
-                        "path": "token-major tcgen05 GEMM" if (world == 1 and eng.opts.prefill_chunk) else "row-batched"},
+                        "path": "token-major" if token_major else "row-batched",
+                        "lanes": (eng.prefiller.lanes if eng.prefiller is not None else 0)},
             "mtp": mtp,
             "gpu_launches": launches * K,
             "gpu_launches_per_step": launches,

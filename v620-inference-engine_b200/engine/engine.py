@@ -329,8 +329,8 @@ class Engine:
                 continue
             drafts = self.draft(slot, pending, k)
             rows = [pending] + drafts
-            logits = self.verify(slot, rows)
-            picks = torch.argmax(logits, dim=-1).tolist()
+            self.verify(slot, rows)
+            picks = self.dm.buf["amax_idx"][:len(rows)].tolist()          # merged over the vocabulary shards on the device
             n_acc = 1
             while n_acc <= k and picks[n_acc - 1] == drafts[n_acc - 1]:
                 n_acc += 1

@@ -83,6 +83,18 @@ struct Builder {
 
     void add(Op op) { ops.push_back(std::move(op)); }
 
+    // Two lanes on several ranks: a kernel that spins inside can fill the GPU and keep the other lane's kernels - which
+    // another rank may be waiting for - from being scheduled, and two ranks doing that to each other never finish.  So
+    // with two lanes every collective is first awaited by a one-block kernel on the consumer's stream; the consumer
+    // then finds its flags set.  (With one lane a spinning kernel only ever waits for kernels that peers can run.)
+    void guard(int l, int kind) {
+        if (!tp || lanes < 2) return;
+        add([=](PCtx &c) {
+            const Lane &L = c.lane[l];
+            PF_TRY(1, qwk_tp_wait(L.tp, kind, L.s));
+        });
+    }
+
     // One mixer of lane l: X (+= pending block output) -> block input + injection logits.
     //   hc_sel: 0 attention mixer of layer li, 1 MoE mixer of layer li, 2 the model's final mixer, 3 / 4 / 5 the same of the MTP layer
     void mix(int l, int li, int hc_sel, int pend, int inj_prev, int inj_out) {
@@ -133,12 +145,14 @@ struct Builder {
             return;
         }
         // several ranks: the pending block output is the reduce-scatter (kind 3) that the previous block sent
+        if (pend != PEND_NONE) guard(l, 3);
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_hc_prenorm_tp(L.tp, f_at(b.X, L.r0, hc * SH), nullptr, SH, pend == PEND_NONE ? -1 : 3,
                                         inj_of(b, inj_prev, L.r0, hc), SH, hc, L.n, L.s));
         });
+        guard(l, 0);
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -151,6 +165,7 @@ struct Builder {
             PF_TRY(1, qwk_gemm_bf16_tc_tp(L.tp, h_at(b.xn, L.r0, hc * SH), w.Wd, nullptr, L.n, R + w.n_inj, hc * SH, hc * SH, hc * SH,
                                           b.hc_ld, 0, -1, 1, 1, b.hc_ld, L.s));
         });
+        guard(l, 1);
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -200,6 +215,7 @@ struct Builder {
             return RowsAt{b.slot + L.r0, b.pos + L.r0, b.run_start + L.r0, b.run_len + L.r0};
         };
         // projection: reads the gathered block input first
+        guard(l, 2);
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -302,6 +318,7 @@ struct Builder {
         auto layer_of = [li, mtp](const PCtx &c) -> const QwLayer & { return mtp ? c.md->mtp.layer : c.md->layers[li]; };
         const int H = d.H, F = d.F, k = d.top_k, E = d.E_l;
         const int nrs = d.E + 1 + 2 * d.SF;
+        guard(l, 2);
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -372,6 +389,7 @@ struct Builder {
         if (pend != PEND_NONE) {
             if (tp) {
                 // fold the pending reduce-scatter into X: reduce its parts to a local matrix first
+                guard(l, 3);
                 add([=](PCtx &c) {
                     const Lane &L = c.lane[l];
                     PF_TRY(1, qwk_tp_reduce(L.tp, 3, f_at(c.b->out_b, L.r0, SH), (long long)L.n * SH, L.s));
@@ -412,6 +430,7 @@ struct Builder {
                 const Lane &L = c.lane[l];
                 PF_TRY(1, qwk_tp_push(L.tp, 4, f_at(c.b->ple_send, L.r0, 16), 64, L.n, 64, 0, L.s));
             });
+            guard(l, 4);
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 PF_TRY(1, qwk_tp_reduce(L.tp, 4, f_at(c.b->ple_red, L.r0, 16), (long long)L.n * 16, L.s));

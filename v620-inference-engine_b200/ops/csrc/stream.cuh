@@ -48,6 +48,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, ErrorW
             : "r"(a), "r"(parity)
             : "memory");
         if (ok) return true;
+        // another waiter already gave up (e.g. the role that feeds this barrier): do not sit out the whole limit
+        if (err && (i & 255u) == 255u && *reinterpret_cast<volatile unsigned int *>(&err->code)) return false;
     }
     report(err, ERR_WAIT_TIMEOUT, __LINE__);
     return false;

@@ -38,6 +38,10 @@ def main():
         want_tok.append(single.decode([0], [t])[0])
         want_logits.append(single.dm.buf["logits"][0].clone())
     want_logits = torch.stack(want_logits)
+    def near_tie0(row, frac=0.02):
+        top2 = torch.topk(row.float(), 2).values
+        return float(top2[0] - top2[1]) < frac * float(row.abs().max())
+
     ok = True
     for backend in ("p2p", "p2p-unfused", "nccl"):
         eng = Engine.from_weights(cfg, w, table, opts, ranks=world, rank=rank, device=dev)
@@ -69,27 +73,68 @@ def main():
         if rank == 0:
             print(f"[selftest] backend={backend} ranks={world}: rel logits err {rel:.3e}, greedy agreement {agree:.3f}, "
                   f"bit-identical block input {same}", flush=True)
-        ok = ok and rel < 3e-2 and agree > 0.9 and same
+        # greedy tokens may differ from the one-GPU run only where its two best logits are a near-tie
+        bad = [i for i, (x, y) in enumerate(zip(got_tok, want_tok)) if x != y and not near_tie0(want_logits[i])]
+        ok = ok and rel < 3e-2 and not bad and same
         del eng
-    # chained, graph-captured decode on the p2p backend equals step-by-step decode
-    eng = Engine.from_weights(cfg, w, table, EngineOptions(slots=1, slot_tokens=512, use_graphs=True), ranks=world,
-                              rank=rank, device=dev)
+    def near_tie(logits_row, frac=0.02):
+        top2 = torch.topk(logits_row.float(), 2).values
+        return float(top2[0] - top2[1]) < frac * float(logits_row.abs().max())
+
+    # chained, graph-captured decode on the p2p backend equals step-by-step decode; token-major prefill on all ranks
+    # (collectives inside the kernels, two micro-batches) equals the one-GPU prefill
+    from qwb200.parallel.dist_engine import attach_tp
+    popts = EngineOptions(slots=1, slot_tokens=512, use_graphs=True, prefill_chunk=256, save_gdn=True)
+    eng = Engine.from_weights(cfg, w, table, popts, ranks=world, rank=rank, device=dev)
     attach_p2p(eng)
     set_fused(True)
-    eng.prefill(0, toks[:40])
+    attach_tp(eng)
+    single = Engine.from_weights(cfg, w, table, popts, device=dev)
+    prompt = torch.randint(0, cfg.vocab, (300,), generator=torch.Generator().manual_seed(9)).tolist()
+    lg = eng.prefill(0, prompt).clone()
     torch.cuda.synchronize()
-    a = eng.decode_chain(0, toks[40], 12)
-    single.reset(0)
-    single.prefill(0, toks[:40])
-    t, b = toks[40], []
+    eng.dm.check_error()
+    path = "token-major" if (eng.prefiller is not None and eng.prefiller.tp) else "row-batched"
+    ls = single.prefill(0, prompt).clone()
+    full = [torch.empty_like(lg) for _ in range(world)]
+    dist.all_gather(full, lg)
+    full = torch.cat(full)
+    relp = float((full - ls).abs().max() / ls.abs().max())
+    t_multi, t_single = int(eng.dm.buf["amax_idx"][0]), int(single.dm.buf["amax_idx"][single.last_prefill_row])
+    tok_ok = t_multi == t_single or near_tie(ls)
+    if rank == 0:
+        print(f"[selftest] prefill ({path}, {eng.prefiller.lanes if eng.prefiller else 0} lanes) vs single GPU: rel logits err {relp:.3e}, "
+              f"token {t_multi} vs {t_single}", flush=True)
+    ok = ok and path == "token-major" and relp < 3e-2 and tok_ok
+    a = eng.decode_chain(0, t_single, 12)
+    t, b = t_single, []
     for _ in range(12):
         t = single.decode([0], [t])[0]
         b.append(t)
     eng.dm.check_error()
-    match = sum(int(x == y) for x, y in zip(a, b)) / 12
+    first_diff = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), 12)
     if rank == 0:
-        print(f"[selftest] chained p2p decode vs single GPU: agreement {match:.2f}", flush=True)
-    ok = ok and match >= 0.75
+        print(f"[selftest] chained p2p decode vs single GPU: first difference at step {first_diff} of 12", flush=True)
+    ok = ok and first_diff >= 6
+    # speculative decoding on all ranks: MTP drafts (chained graphs) + verification give exactly the plain greedy tokens
+    if eng.mtp:
+        plain = Engine.from_weights(cfg, w, table, popts, ranks=world, rank=rank, device=dev)
+        attach_p2p(plain)
+        attach_tp(plain)
+        plain.prefill(0, prompt[:200])
+        f0 = int(plain.dm.buf["amax_idx"][0])
+        want = plain.generate_greedy(0, f0, 20, k=0)
+        spec = Engine.from_weights(cfg, w, table, popts, ranks=world, rank=rank, device=dev)
+        attach_p2p(spec)
+        attach_tp(spec)
+        spec.prefill(0, prompt[:200])
+        got = spec.generate_greedy(0, int(spec.dm.buf["amax_idx"][0]), 20, k=3)
+        spec.dm.check_error()
+        same = got == want
+        if rank == 0:
+            print(f"[selftest] speculative (3 drafts) on {world} ranks == plain greedy: {same}; accepted {spec.spec_accepted} drafts in "
+                  f"{spec.spec_steps} steps", flush=True)
+        ok = ok and same
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
