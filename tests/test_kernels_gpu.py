@@ -107,8 +107,8 @@ def test_moe_pair_kernels_match_oracle():
         L.qwk_set_moe_mma(12)
 
 
-@pytest.mark.parametrize("M", [64, 200, 1000])
-def test_gdn_chunked_scan_matches_sequential_fp32(M):
+@pytest.mark.parametrize("M,KL,VL", [(64, 2, 4), (200, 2, 4), (1000, 2, 4), (200, 4, 16), (200, 8, 32)])
+def test_gdn_chunked_scan_matches_sequential_fp32(M, KL, VL):
     """The chunked (tensor-core) delta-rule scan against the token-by-token recurrence in PyTorch fp32 and
     against the row-by-row kernel: outputs, and the state it leaves in the slot."""
     import ctypes as C
@@ -117,7 +117,7 @@ def test_gdn_chunked_scan_matches_sequential_fp32(M):
     L = qlib.load(True)
     dev = _dev()
     g = torch.Generator(device="cuda").manual_seed(M)
-    KL, VL, D, slots, slot = 2, 4, 128, 3, 1
+    D, slots, slot = 128, 3, 1          # VL < 16, < 32, >= 32: the three column splits of the sequential walk
     qkv_l = (2 * KL + VL) * D
     rn = lambda *s: torch.randn(*s, generator=g, device=dev)
     q = torch.nn.functional.normalize(rn(M, KL, D), dim=-1) * D ** -0.5

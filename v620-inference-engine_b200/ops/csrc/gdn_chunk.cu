@@ -191,12 +191,21 @@ __global__ void __launch_bounds__(256, 3) gdn_chunk_prep_kernel(GdnChunkArgs a) 
 // ------------------------------------------------------------------------------------------------
 // 2. state-dependent part: one block per (half of the value columns, head) walks the chunks
 // ------------------------------------------------------------------------------------------------
-constexpr int APPLY_FLOATS = CD * LDS + 2 * CC * LDA + CC * LDT + CC * LDP + CC * LDS + 2 * CC;
-constexpr int APPLY_SMEM = APPLY_FLOATS * 4;
+// NC = value columns of the state per block (64, 32 or 16): the value columns of a head are independent in every
+// state-dependent product, so a head is split over 128 / NC blocks; with few heads per rank (tensor parallel) a finer
+// split keeps the number of blocks up.  Every output element's sum runs over k in the same order whatever NC is.
+template <int NC>
+constexpr int apply_smem() {
+    return (CD * (NC + 8) + 2 * CC * LDA + CC * LDT + CC * LDP + CC * (NC + 8) + 2 * CC) * 4;
+}
 
+template <int NC>
 __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
+    constexpr int LDS = NC + 8;          // [.][NC] B-operand tile (state slice, U)
+    constexpr int NT = NC / 16;          // 8-column tiles of a warp in the row-tiled products
+    constexpr int NS = NC / 8;           // 8-column tiles of a warp in the state update
     extern __shared__ __align__(16) float sm[];
-    float *Ss = sm;                      // [128 k][LDS]   state, this block's 64 value columns
+    float *Ss = sm;                      // [128 k][LDS]   state, this block's NC value columns
     float *Wks = Ss + CD * LDS;          // [64][LDA]
     float *Qs = Wks + CC * LDA;          // [64][LDA]
     float *Ks = Qs + CC * LDA;           // [64][LDT]      read transposed in the state update
@@ -209,15 +218,13 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
     const int qkv_l = (2 * a.KL + a.VL) * CD;
     const int kh = h / (a.VL / a.KL);
     const int slot = a.slot[0];
-    float *Sg = a.S + ((long long)slot * a.VL + h) * CD * CD + vh * 64;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int idx = tid + i * 256;              // float4 index: 128 rows x 16
-        const int r = idx >> 4, c4 = idx & 15;
+    float *Sg = a.S + ((long long)slot * a.VL + h) * CD * CD + vh * NC;
+    for (int idx = tid; idx < CD * (NC / 4); idx += 256) {      // float4 index: 128 rows x NC / 4
+        const int r = idx / (NC / 4), c4 = idx % (NC / 4);
         *reinterpret_cast<float4 *>(Ss + r * LDS + c4 * 4) = *reinterpret_cast<const float4 *>(Sg + r * CD + c4 * 4);
     }
     const int nch = (a.M + CC - 1) / CC;
-    const int r0 = (w & 3) * 16, c0 = (w >> 2) * 32;
+    const int r0 = (w & 3) * 16, c0 = (w >> 2) * (NC / 2);
     for (int ch = 0; ch < nch; ++ch) {
         const int m0 = ch * CC;
         const long long cb = (long long)ch * a.VL + h;
@@ -240,10 +247,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             ek[tid] = __expf(gC - gt);
         }
         __syncthreads();
-        // U = Wv - Wk S0 and Q S0: warp tile 16 rows x 32 value columns
-        float accW[4][4], accO[4][4];
+        // U = Wv - Wk S0 and Q S0: warp tile 16 rows x NC / 2 value columns
+        float accW[NT][4], accO[NT][4];
 #pragma unroll
-        for (int n = 0; n < 4; ++n)
+        for (int n = 0; n < NT; ++n)
 #pragma unroll
             for (int i = 0; i < 4; ++i) accW[n][i] = accO[n][i] = 0.f;
 #pragma unroll 4
@@ -252,7 +259,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             lda_frag(fw, Wks, LDA, r0, k0, g, t);
             lda_frag(fq, Qs, LDA, r0, k0, g, t);
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < NT; ++n) {
                 const float *p = Ss + (k0 + t) * LDS + c0 + n * 8 + g;
                 const uint32_t b0 = tf32(p[0]), b1 = tf32(p[4 * LDS]);
                 mma_tf32(accW[n], fw, b0, b1);
@@ -260,10 +267,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             }
         }
         {
-            const float *Wvg = a.Wv + cb * CC * CD + vh * 64;
+            const float *Wvg = a.Wv + cb * CC * CD + vh * NC;
             const float e0 = eg[r0 + g], e1 = eg[r0 + g + 8];
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < NT; ++n) {
                 const int c = c0 + n * 8 + 2 * t;
                 const float2 v0 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g) * CD + c);
                 const float2 v1 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g + 8) * CD + c);
@@ -279,25 +286,25 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             uint32_t fp[4];
             lda_frag(fp, Ps, LDP, r0, k0, g, t);
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
+            for (int n = 0; n < NT; ++n) {
                 const float *p = Us + (k0 + t) * LDS + c0 + n * 8 + g;
                 mma_tf32(accO[n], fp, tf32(p[0]), tf32(p[4 * LDS]));
             }
         }
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int c = h * CD + vh * 64 + c0 + n * 8 + 2 * t;
+        for (int n = 0; n < NT; ++n) {
+            const int c = h * CD + vh * NC + c0 + n * 8 + 2 * t;
             const int ra = m0 + r0 + g, rb = ra + 8;
             if (ra < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)ra * a.VL * CD + c) = make_float2(accO[n][0], accO[n][1]);
             if (rb < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)rb * a.VL * CD + c) = make_float2(accO[n][2], accO[n][3]);
         }
-        // S1 = exp(g_C) S0 + (diag(ek) K)^T U: warp w owns state rows 16w .. 16w+15, all 64 columns
+        // S1 = exp(g_C) S0 + (diag(ek) K)^T U: warp w owns state rows 16w .. 16w+15, all NC columns
         {
             const int i0 = w * 16;
             const float eC = eg[CC - 1];
-            float accS[8][4];
+            float accS[NS][4];
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
+            for (int n = 0; n < NS; ++n) {
                 const float2 s0 = *reinterpret_cast<const float2 *>(Ss + (i0 + g) * LDS + n * 8 + 2 * t);
                 const float2 s1 = *reinterpret_cast<const float2 *>(Ss + (i0 + g + 8) * LDS + n * 8 + 2 * t);
                 accS[n][0] = s0.x * eC; accS[n][1] = s0.y * eC;
@@ -313,23 +320,21 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
                 fa[2] = tf32(p[4 * LDT] * eb);
                 fa[3] = tf32(p[4 * LDT + 8] * eb);
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
+                for (int n = 0; n < NS; ++n) {
                     const float *q = Us + (k0 + t) * LDS + n * 8 + g;
                     mma_tf32(accS[n], fa, tf32(q[0]), tf32(q[4 * LDS]));
                 }
             }
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
+            for (int n = 0; n < NS; ++n) {
                 *reinterpret_cast<float2 *>(Ss + (i0 + g) * LDS + n * 8 + 2 * t) = make_float2(accS[n][0], accS[n][1]);
                 *reinterpret_cast<float2 *>(Ss + (i0 + g + 8) * LDS + n * 8 + 2 * t) = make_float2(accS[n][2], accS[n][3]);
             }
         }
         __syncthreads();
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int idx = tid + i * 256;
-        const int r = idx >> 4, c4 = idx & 15;
+    for (int idx = tid; idx < CD * (NC / 4); idx += 256) {
+        const int r = idx / (NC / 4), c4 = idx % (NC / 4);
         *reinterpret_cast<float4 *>(Sg + r * CD + c4 * 4) = *reinterpret_cast<const float4 *>(Ss + r * LDS + c4 * 4);
     }
 }
@@ -359,12 +364,17 @@ QW_API int qwk_gdn_scan_chunked(const float *qkv, const float *decay, const floa
                                 float *S, const float *norm_w, int KL, int VL, int M, const int *slot, float *scratch,
                                 void *o, float eps, cudaStream_t s) {
     if (M < 1 || KL < 1 || VL % KL != 0) return -1;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_done[dev]) {
         if (cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(gdn_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, APPLY_SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(gdn_chunk_apply_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, apply_smem<64>()) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_chunk_apply_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, apply_smem<32>()) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_chunk_apply_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, apply_smem<16>()) != cudaSuccess)
             return -3;
-        attr_done = true;
+        attr_done[dev] = true;
     }
     const long long nch = (M + CC - 1) / CC;
     GdnChunkArgs a;
@@ -376,7 +386,10 @@ QW_API int qwk_gdn_scan_chunked(const float *qkv, const float *decay, const floa
     a.G = a.P + nch * VL * CC * CC;
     a.Oraw = a.G + nch * VL * CC;
     gdn_chunk_prep_kernel<<<dim3((unsigned)nch, VL), 256, PREP_SMEM, s>>>(a);
-    gdn_chunk_apply_kernel<<<dim3(2, VL), 256, APPLY_SMEM, s>>>(a);
+    // blocks of the sequential walk: 128 / NC per head, NC chosen so that about a hundred blocks run
+    if (VL >= 32) gdn_chunk_apply_kernel<64><<<dim3(2, VL), 256, apply_smem<64>(), s>>>(a);
+    else if (VL >= 16) gdn_chunk_apply_kernel<32><<<dim3(4, VL), 256, apply_smem<32>(), s>>>(a);
+    else gdn_chunk_apply_kernel<16><<<dim3(8, VL), 256, apply_smem<16>(), s>>>(a);
     gdn_chunk_norm_kernel<<<dim3(M, VL), 128, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -46,6 +46,9 @@ struct PCtx {
 typedef std::function<void(PCtx &)> Op;
 
 long long g_prefill_launches = 0;
+int g_profile = 0;
+std::vector<cudaEvent_t> g_prof_ev;
+double g_prof_ms[16] = {};
 
 #define PF_TRY(n_, expr)                                                   \
     do {                                                                   \
@@ -74,14 +77,24 @@ inline const void *bin_of(const PCtx &c, int l) {
     return h_at(c.b->bin, L.r0, c.md->d.H);
 }
 
+// Profile categories of a step (qwrt_prefill_profile).
+enum Cat { CAT_MIX_GLUE = 0, CAT_MIX_GEMM, CAT_PROJ, CAT_GDN, CAT_QSA, CAT_OUT, CAT_ROUTE, CAT_EXPERTS, CAT_COMBINE, CAT_PLE, CAT_OTHER,
+           CAT_MTP, CAT_GUARD, CAT_COUNT };
+
+struct Step {
+    Op fn;
+    int cat, lane;
+};
+
 struct Builder {
-    std::vector<Op> ops;
+    std::vector<Step> ops;
+    int cur_cat = CAT_OTHER, cur_lane = 0;
     const QwDims d;
     const bool tp;          // several ranks
     const int lanes;
     explicit Builder(const QwPrefillJob &j) : d(j.md->d), tp(j.tp[0] != nullptr), lanes(j.lanes) {}
 
-    void add(Op op) { ops.push_back(std::move(op)); }
+    void add(Op op) { ops.push_back(Step{std::move(op), cur_cat, cur_lane}); }
 
     // Two lanes on several ranks: a kernel that spins inside can fill the GPU and keep the other lane's kernels - which
     // another rank may be waiting for - from being scheduled, and two ranks doing that to each other never finish.  So
@@ -89,15 +102,20 @@ struct Builder {
     // then finds its flags set.  (With one lane a spinning kernel only ever waits for kernels that peers can run.)
     void guard(int l, int kind) {
         if (!tp || lanes < 2) return;
+        const int keep = cur_cat;
+        cur_cat = CAT_GUARD;
+        cur_lane = l;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             PF_TRY(1, qwk_tp_wait(L.tp, kind, L.s));
         });
+        cur_cat = keep;
     }
 
     // One mixer of lane l: X (+= pending block output) -> block input + injection logits.
     //   hc_sel: 0 attention mixer of layer li, 1 MoE mixer of layer li, 2 the model's final mixer, 3 / 4 / 5 the same of the MTP layer
     void mix(int l, int li, int hc_sel, int pend, int inj_prev, int inj_out) {
+        cur_lane = l;
         auto hc_of = [li, hc_sel](const PCtx &c) -> const QwHc & {
             const QwModel &m = *c.md;
             switch (hc_sel) {
@@ -111,6 +129,7 @@ struct Builder {
         };
         const int hc = d.hc, SH = d.SH, R = d.hc_rank, H = d.H;
         if (!tp) {
+            cur_cat = CAT_MIX_GLUE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -118,6 +137,7 @@ struct Builder {
                 PF_TRY(1, qwk_hc_prenorm_T(f_at(b.X, L.r0, hc * SH), pe, H, inj_of(b, inj_prev, L.r0, hc), hc_of(c).w1, SH, hc, d.eps,
                                            h_at(b.xn, L.r0, hc * SH), L.n, L.s));
             });
+            cur_cat = CAT_MIX_GEMM;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -125,6 +145,7 @@ struct Builder {
                 PF_TRY(1, qwk_gemm_bf16_tc_splitk(h_at(b.xn, L.r0, hc * SH), w.Wd, f_at(b.d, L.r0, b.hc_ld), L.n, R + w.n_inj, hc * SH,
                                                   hc * SH, hc * SH, b.hc_ld, b.hc_ksplit, (long long)b.cap * b.hc_ld, L.s));
             });
+            cur_cat = CAT_MIX_GLUE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -132,11 +153,13 @@ struct Builder {
                 PF_TRY(1, qwk_hc_mid_T(f_at(b.d, L.r0, b.hc_ld), b.hc_ld, R, w.n_inj, hc, h_at(b.u, L.r0, R), inj_of(b, inj_out, L.r0, hc),
                                        L.n, b.hc_ksplit, (long long)b.cap * b.hc_ld, L.s));
             });
+            cur_cat = CAT_MIX_GEMM;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
                 PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.u, L.r0, R), hc_of(c).Wu, f_at(b.g, L.r0, hc * SH), L.n, hc * SH, R, R, R, hc * SH, 0, L.s));
             });
+            cur_cat = CAT_MIX_GLUE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -146,6 +169,7 @@ struct Builder {
         }
         // several ranks: the pending block output is the reduce-scatter (kind 3) that the previous block sent
         if (pend != PEND_NONE) guard(l, 3);
+        cur_cat = CAT_MIX_GLUE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -153,11 +177,13 @@ struct Builder {
                                         inj_of(b, inj_prev, L.r0, hc), SH, hc, L.n, L.s));
         });
         guard(l, 0);
+        cur_cat = CAT_MIX_GLUE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_hc_norm_tp(L.tp, f_at(b.X, L.r0, hc * SH), hc_of(c).w1, SH, hc, H, d.eps, h_at(b.xn, L.r0, hc * SH), L.n, L.s));
         });
+        cur_cat = CAT_MIX_GEMM;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -166,17 +192,20 @@ struct Builder {
                                           b.hc_ld, 0, -1, 1, 1, b.hc_ld, L.s));
         });
         guard(l, 1);
+        cur_cat = CAT_MIX_GLUE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             const QwHc &w = hc_of(c);
             PF_TRY(1, qwk_hc_mid_tp(L.tp, b.hc_ld, R, w.n_inj, hc, h_at(b.u, L.r0, R), inj_of(b, inj_out, L.r0, hc), L.n, L.s));
         });
+        cur_cat = CAT_MIX_GEMM;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.u, L.r0, R), hc_of(c).Wu, f_at(b.g, L.r0, hc * SH), L.n, hc * SH, R, R, R, hc * SH, 0, L.s));
         });
+        cur_cat = CAT_MIX_GLUE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -185,6 +214,7 @@ struct Builder {
     }
 
     void hook(int l, int li, int which) {
+        cur_lane = l;
         add([=](PCtx &c) {
             if (!c.job->hook) return;
             const Lane &L = c.lane[l];
@@ -195,15 +225,20 @@ struct Builder {
     // Lane 1 touches a layer's sequential state after lane 0; lane 0 of the next chunk after lane 1 (the join at the chunk's end).
     void state_begin(int l, int slot_ev) {
         if (lanes < 2 || l != 1) return;
+        cur_cat = CAT_PROJ;
+        cur_cat = CAT_OTHER;
         add([=](PCtx &c) { cudaStreamWaitEvent(c.lane[1].s, c.ev[2 + slot_ev], 0); });
     }
     void state_end(int l, int slot_ev) {
         if (lanes < 2 || l != 0) return;
+        cur_cat = CAT_PROJ;
+        cur_cat = CAT_OTHER;
         add([=](PCtx &c) { cudaEventRecord(c.ev[2 + slot_ev], c.lane[0].s); });
     }
 
     // The attention block of a layer for lane l.  mtp: the MTP head's layer with the MTP row tables.
     void attn_block(int l, int li, bool mtp, int ev_slot) {
+        cur_lane = l;
         auto layer_of = [li, mtp](const PCtx &c) -> const QwLayer & { return mtp ? c.md->mtp.layer : c.md->layers[li]; };
         const int H = d.H;
         struct RowsAt {
@@ -216,6 +251,7 @@ struct Builder {
         };
         // projection: reads the gathered block input first
         guard(l, 2);
+        cur_cat = CAT_PROJ;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -229,6 +265,7 @@ struct Builder {
         });
         state_begin(l, ev_slot);
         // stateful part 1 (writes the layer's state)
+        cur_cat = CAT_GDN;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -250,6 +287,7 @@ struct Builder {
             }
         });
         // stateful part 2 (GDN: the scan; QSA: nothing else writes state)
+        cur_cat = CAT_GDN;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -265,6 +303,7 @@ struct Builder {
         });
         state_end(l, ev_slot);
         // QSA: indexer scores, selection, attention (read-only on the state)
+        cur_cat = CAT_QSA;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -278,6 +317,7 @@ struct Builder {
             PF_TRY(1, qwk_qsa_scores(f_at(b.iq, L.r0, d.IH * 128), d.IH, st.ck[qi], d.ck_cap, L.n, r.slot, r.pos, d.idx_ratio, d.idx_topk,
                                      f_at(b.scores, L.r0, d.score_cap), d.score_cap, max_groups, L.s));
         });
+        cur_cat = CAT_QSA;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -287,6 +327,7 @@ struct Builder {
             PF_TRY(1, qwk_qsa_select(f_at(b.scores, L.r0, d.score_cap), d.score_cap, L.n, r.pos, d.idx_ratio, d.idx_topk,
                                      i_at(b.sel, L.r0, d.idx_topk), b.sel_n + L.r0, L.s));
         });
+        cur_cat = CAT_QSA;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -301,6 +342,7 @@ struct Builder {
                                          f_at(b.proj, L.r0, b.proj_ld), b.proj_ld, h_at(b.o, L.r0, b.o_ld), L.s));
         });
         // out projection (K depends on the layer kind, which every rank knows alike: resolve when run)
+        cur_cat = CAT_OUT;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -315,10 +357,12 @@ struct Builder {
     }
 
     void moe(int l, int li, bool mtp) {
+        cur_lane = l;
         auto layer_of = [li, mtp](const PCtx &c) -> const QwLayer & { return mtp ? c.md->mtp.layer : c.md->layers[li]; };
         const int H = d.H, F = d.F, k = d.top_k, E = d.E_l;
         const int nrs = d.E + 1 + 2 * d.SF;
         guard(l, 2);
+        cur_cat = CAT_ROUTE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -328,12 +372,14 @@ struct Builder {
             else
                 PF_TRY(1, qwk_gemm_bf16_tc(bin_of(c, l), w.Wrs, f_at(b.rs, L.r0, b.nrs_ld), L.n, nrs, H, H, H, b.nrs_ld, 0, L.s));
         });
+        cur_cat = CAT_ROUTE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_moe_route(f_at(b.rs, L.r0, b.nrs_ld), b.nrs_ld, L.n, d.E, k, d.SF, c.md->d.e_first, E, i_at(b.pe, L.r0, k),
                                     f_at(b.pw, L.r0, k), h_at(b.sh_h, L.r0, d.SF), L.s));
         });
+        cur_cat = CAT_ROUTE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -342,6 +388,7 @@ struct Builder {
                                      (char *)b.t13 + (long long)(l == 1) * b.max_tiles * 16, (char *)b.t2 + (long long)(l == 1) * b.max_tiles * 16, bin_of(c, l), H,
                                      H, h_at(b.xperm, p0, H), L.s));
         });
+        cur_cat = CAT_EXPERTS;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -351,12 +398,14 @@ struct Builder {
                                              (char *)b.t13 + (long long)(l == 1) * b.max_tiles * 16, b.max_tiles, L.n * k, (long long)E * 2 * F, 2 * F, H, H,
                                              2 * F, 1, L.s));
         });
+        cur_cat = CAT_EXPERTS;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             const long long p0 = (long long)L.r0 * k;
             PF_TRY(1, qwk_swiglu_T(h_at(b.h13, p0, 2 * F), F, h_at(b.h, p0, F), (long long)L.n * k, L.s));
         });
+        cur_cat = CAT_EXPERTS;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -366,11 +415,13 @@ struct Builder {
                                              (char *)b.t2 + (long long)(l == 1) * b.max_tiles * 16, b.max_tiles, L.n * k, (long long)E * H, H, F, F, H, 0,
                                              L.s));
         });
+        cur_cat = CAT_COMBINE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.sh_h, L.r0, d.SF), layer_of(c).Wsd, f_at(b.sd, L.r0, H), L.n, H, d.SF, d.SF, d.SF, H, 0, L.s));
         });
+        cur_cat = CAT_COMBINE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -385,16 +436,19 @@ struct Builder {
 
     // The n-gram embedding layer's extra input, applied to X before the layer's first mixer.
     void ple(int l, int pend, int inj_prev) {
+        cur_lane = l;
         const int H = d.H, hc = d.hc, SH = d.SH;
         if (pend != PEND_NONE) {
             if (tp) {
                 // fold the pending reduce-scatter into X: reduce its parts to a local matrix first
                 guard(l, 3);
+                cur_cat = CAT_PLE;
                 add([=](PCtx &c) {
                     const Lane &L = c.lane[l];
                     PF_TRY(1, qwk_tp_reduce(L.tp, 3, f_at(c.b->out_b, L.r0, SH), (long long)L.n * SH, L.s));
                 });
             }
+            cur_cat = CAT_PLE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -404,6 +458,7 @@ struct Builder {
                                      L.n, L.s));
             });
         }
+        cur_cat = CAT_PLE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -411,12 +466,14 @@ struct Builder {
             PF_TRY(1, qwk_ple_gather(b.ctx3 + 3 * L.r0, p.shards, p.scales, p.rows_per_shard, p.rows, p.layout, d.ngram_dim, d.ngram_heads,
                                      h_at(b.ple_e, L.r0, H), nullptr, L.n, L.s));
         });
+        cur_cat = CAT_PLE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.ple_e, L.r0, H), c.md->ple.Wkv, f_at(b.ple_kv, L.r0, b.ple_ld), L.n, d.ple_kv, H, H, H, b.ple_ld, 0,
                                        L.s));
         });
+        cur_cat = CAT_PLE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -426,17 +483,20 @@ struct Builder {
         });
         if (tp) {
             // all-reduce of the 16 statistics per row, as two steps: every rank sends before any rank adds
+            cur_cat = CAT_PLE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 PF_TRY(1, qwk_tp_push(L.tp, 4, f_at(c.b->ple_send, L.r0, 16), 64, L.n, 64, 0, L.s));
             });
             guard(l, 4);
+            cur_cat = CAT_PLE;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 PF_TRY(1, qwk_tp_reduce(L.tp, 4, f_at(c.b->ple_red, L.r0, 16), (long long)L.n * 16, L.s));
             });
         }
         state_begin(l, 0);
+        cur_cat = CAT_PLE;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -488,12 +548,16 @@ void build(Builder &B, const QwPrefillJob &j) {
     }
     for (int l = 0; l < lanes; ++l) B.mix(l, 0, 2, pend, inj_prev, INJ_NONE);
     // join: everything after this runs on the caller's stream
+    B.cur_cat = CAT_OTHER;
+    B.cur_lane = 0;
     if (lanes == 2) {
         B.add([](PCtx &c) {
             cudaEventRecord(c.ev[1], c.lane[1].s);
             cudaStreamWaitEvent(c.lane[0].s, c.ev[1], 0);
         });
     }
+    B.cur_cat = CAT_OTHER;
+    B.cur_lane = 0;
     if (j.want_logits) {
         const int ll = lanes - 1;          // the lane that holds the chunk's last row
         if (B.tp) B.add([=](PCtx &c) { PF_TRY(1, qwk_tp_wait(c.lane[ll].tp, 2, c.lane[0].s)); });
@@ -520,6 +584,7 @@ void build(Builder &B, const QwPrefillJob &j) {
     if (j.mtp_rows > 0 && md.mtp.enabled) {
         const int n = j.mtp_rows, hp = j.has_pending ? 1 : 0;
         // the hidden state of the chunk's last position is the next call's pending row
+        B.cur_cat = CAT_MTP;
         B.add([=](PCtx &c) {
             const QwPrefillBufs &b = *c.b;
             cudaStream_t s = c.lane[0].s;
@@ -529,34 +594,41 @@ void build(Builder &B, const QwPrefillJob &j) {
             if (n - hp > 0) cudaMemcpyAsync(b.Xm + (size_t)hp * hc * SH, b.X, row * (size_t)(n - hp), cudaMemcpyDeviceToDevice, s);
         });
         if (!B.tp) {
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 const QwMtp &t = c.md->mtp;
                 PF_TRY(1, qwk_mtp_norm(b.Xm, b.mtp_tok, c.md->embed, d.vocab, t.nh1, t.ne1, H, hc, d.eps, b.hn, b.en, n, c.lane[0].s));
             });
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 PF_TRY(1, qwk_gemm_bf16_tc(b.hn, c.md->mtp.fc_h, b.fh, n * hc, H, H, H, H, H, 0, c.lane[0].s));
             });
         } else {
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 PF_TRY(1, qwk_mtp_ssq(b.Xm, hc * SH, b.mtp_ssq, n, c.lane[0].s));
             });
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const int n4 = (n + 3) & ~3;
                 PF_TRY(1, qwk_tp_push(c.lane[0].tp, 4, c.b->mtp_ssq, (long long)n4 * 4, 1, n4 * 4, 0, c.lane[0].s));
             });
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 PF_TRY(1, qwk_tp_reduce(c.lane[0].tp, 4, b.mtp_ssq + b.cap, (long long)((n + 3) & ~3), c.lane[0].s));
             });
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 const QwMtp &t = c.md->mtp;
                 PF_TRY(1, qwk_mtp_norm_tp(c.lane[0].tp, b.Xm, b.mtp_ssq + b.cap, b.mtp_tok, c.md->embed, d.vocab, t.nh1, t.ne1, H, hc, d.eps, b.en,
                                           n, c.lane[0].s));
             });
+            B.cur_cat = CAT_MTP;
             B.add([=](PCtx &c) {
                 const QwPrefillBufs &b = *c.b;
                 QwTp *tp = c.lane[0].tp;
@@ -564,10 +636,12 @@ void build(Builder &B, const QwPrefillJob &j) {
                 PF_TRY(1, qwk_gemm_bf16_tc_tp(tp, hn, c.md->mtp.fc_h, b.fh, n * hc, SH, H, H, H, SH, 0, 5, 0, 0, 0, c.lane[0].s));
             });
         }
+        B.cur_cat = CAT_MTP;
         B.add([=](PCtx &c) {
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_gemm_bf16_tc(b.en, c.md->mtp.fc_e, b.fe, n, SH, H, H, H, SH, 0, c.lane[0].s));
         });
+        B.cur_cat = CAT_MTP;
         B.add([=](PCtx &c) {
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_mtp_add(b.fh, b.fe, SH, hc, b.X, n, c.lane[0].s));
@@ -620,8 +694,30 @@ extern "C" __attribute__((visibility("default"))) int qwrt_prefill(const QwPrefi
     }
     Builder B(j0);
     build(B, j0);
-    for (size_t k = 0; k < B.ops.size(); ++k)
-        for (int i = 0; i < njobs; ++i) B.ops[k](ctx[i]);
+    if (g_profile && njobs == 1) {
+        // every step between two events on its stream; read back after the chunk (the streams are synchronised: a diagnostic)
+        const size_t n = B.ops.size();
+        if (g_prof_ev.size() < 2 * n) {
+            const size_t old = g_prof_ev.size();
+            g_prof_ev.resize(2 * n);
+            for (size_t k = old; k < 2 * n; ++k) cudaEventCreate(&g_prof_ev[k]);
+        }
+        for (size_t k = 0; k < n; ++k) {
+            cudaStream_t s = ctx[0].lane[B.ops[k].lane].s;
+            cudaEventRecord(g_prof_ev[2 * k], s);
+            B.ops[k].fn(ctx[0]);
+            cudaEventRecord(g_prof_ev[2 * k + 1], s);
+        }
+        cudaStreamSynchronize(ctx[0].lane[0].s);
+        cudaStreamSynchronize(ctx[0].lane[1].s);
+        for (size_t k = 0; k < n; ++k) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, g_prof_ev[2 * k], g_prof_ev[2 * k + 1]) == cudaSuccess) g_prof_ms[B.ops[k].cat] += ms;
+        }
+    } else {
+        for (size_t k = 0; k < B.ops.size(); ++k)
+            for (int i = 0; i < njobs; ++i) B.ops[k].fn(ctx[i]);
+    }
     long long launches = 0;
     int err = 0;
     for (auto &c : ctx) {
@@ -637,3 +733,18 @@ extern "C" __attribute__((visibility("default"))) long long qwrt_prefill_sizes(i
 }
 
 extern "C" __attribute__((visibility("default"))) long long qwrt_prefill_last_launches(void) { return g_prefill_launches; }
+
+// Profiling of the chunks that follow (one job per call): device time of every step, added up per category
+// (mixer glue, mixer GEMMs, projection, GDN, QSA, out projection, routing, expert GEMMs, shared down + combine, PLE, other,
+// MTP pass, guard waits).  qwrt_prefill_profile_read copies the sums (milliseconds) out and clears them.
+extern "C" __attribute__((visibility("default"))) int qwrt_prefill_profile(int on) {
+    g_profile = on;
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int qwrt_prefill_profile_read(double *out, int n) {
+    for (int i = 0; i < n && i < 16; ++i) {
+        out[i] = g_prof_ms[i];
+        g_prof_ms[i] = 0.0;
+    }
+    return CAT_COUNT;
+}

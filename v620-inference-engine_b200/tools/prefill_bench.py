@@ -1,19 +1,29 @@
-"""Prefill throughput and where the time goes: tokens per second of one prompt through the token-major path, and the
-share of the mixers, attention blocks (GDN / QSA), MoE blocks and the rest, measured with CUDA events around the
-Prefiller's phases (a second, instrumented pass; the throughput figure comes from the plain pass).
+"""Prefill throughput and where the time goes, on one GPU or on N (one process per GPU under torchrun):
 
-    python -m qwb200.tools.prefill_bench [--tokens 4096] [--chunk 4096] [--ctx 0] [--layers 0]
+    python -m qwb200.tools.prefill_bench [--tokens 4096] [--chunk 4096] [--ctx 0] [--layers 0] [--lanes 0] [--by-step]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m qwb200.tools.prefill_bench ...
+
+Tokens per second of one prompt through the token-major path (CUDA events on the launching stream, max over ranks), then,
+with ``--by-step``, a second pass in which the native runtime brackets every step of a chunk with events and adds the
+device time up per category (mixer glue / mixer GEMMs / projections / GDN / QSA / out projection (+ reduce-scatter) /
+routing / expert GEMMs / shared down + combine / PLE / MTP pass / guard waits).  On several ranks a step's time
+includes what it waits for inside the kernel, which is the point.
 
 (The reference's tool: bench/prefill_bench with --ctx / --tokens-file.)"""
 import argparse
-import collections
+import ctypes as C
+import dataclasses
 import json
+import os
 
 import torch
 
 from ..engine.engine import Engine, EngineOptions
-from ..engine.prefill import Prefiller
 from ..models.config import ModelConfig
+
+CATS = ["mixer glue", "mixer GEMMs", "projection GEMM", "GDN conv + scan", "QSA prep / scores / select / attend", "out projection",
+        "router GEMM + routing + sort", "expert GEMMs + swiglu", "shared down + combine", "PLE", "other", "MTP pass", "guard waits"]
 
 
 def main():
@@ -22,98 +32,82 @@ def main():
     ap.add_argument("--chunk", type=int, default=4096)
     ap.add_argument("--ctx", type=int, default=0, help="tokens already in the slot before the measured prompt")
     ap.add_argument("--layers", type=int, default=0)
-    ap.add_argument("--by-kernel", action="store_true", help="a third pass that times every launcher call of the library by name")
+    ap.add_argument("--lanes", type=int, default=0, help="micro-batches per chunk (0: the default of the rank count)")
+    ap.add_argument("--by-step", action="store_true", help="a second pass with the runtime's per-category step timing")
+    ap.add_argument("--repeat", type=int, default=2, help="timed repetitions (the best is reported)")
     a = ap.parse_args()
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(dev))
     cfg = ModelConfig.full()
     if a.layers:
-        import dataclasses
         cfg = dataclasses.replace(cfg, n_layers=a.layers)
-    eng = Engine.synthetic(cfg, EngineOptions(slots=1, slot_tokens=a.ctx + 2 * a.tokens + 512, use_graphs=False, prefill_chunk=a.chunk),
-                           device="cuda:0", ple_rows=1 << 20)
+    if a.lanes:
+        from ..utils import settings
+        settings.set_current(settings.Settings.from_env(prefill_lanes=a.lanes))
+    opts = EngineOptions(slots=1, slot_tokens=a.ctx + a.tokens + 512, use_graphs=False, prefill_chunk=a.chunk)
+    if world > 1:
+        from ..parallel.dist_engine import make_engine
+        eng = make_engine(cfg, opts, world, rank, dev, ple_rows=1 << 20)
+    else:
+        eng = Engine.synthetic(cfg, opts, device=dev, ple_rows=1 << 20)
     g = torch.Generator().manual_seed(3)
     toks = torch.randint(0, cfg.vocab, (a.ctx + a.tokens,), generator=g).tolist()
-    eng.prefill(0, toks[:512], want_logits=False)          # warm-up
-    torch.cuda.synchronize()
-    eng.reset(0)
-    if a.ctx:
-        eng.prefill(0, toks[:a.ctx], want_logits=False)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    eng.prefill(0, toks[a.ctx:], want_logits=True)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    print(f"prefill of {a.tokens} tokens after {a.ctx}: {ms:.1f} ms, {a.tokens / ms * 1e3:.0f} tok/s", flush=True)
-    # instrumented pass
-    acc = collections.defaultdict(float)
-    P = eng.prefiller
 
-    def wrap(name, key_of=lambda *args: None):
-        fn = getattr(P, name)
+    def sync():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
 
-        def timed(*args, **kw):
-            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
-            r = fn(*args, **kw)
-            s1.record()
-            torch.cuda.synchronize()
-            acc[key_of(*args) or name] += s0.elapsed_time(s1)
-            return r
-        setattr(P, name, timed)
-    wrap("mix")
-    wrap("attn_block", lambda lw, *rest: "attn_qsa" if lw["is_qsa"] else "attn_gdn")
-    wrap("moe")
-    if hasattr(P, "mtp_pass"):
-        wrap("mtp_pass")
-    eng.reset(0)
-    if a.ctx:
-        eng.prefill(0, toks[:a.ctx], want_logits=False)
-        acc.clear()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    eng.prefill(0, toks[a.ctx:], want_logits=True)
-    t1.record()
-    torch.cuda.synchronize()
-    total = t0.elapsed_time(t1)
-    acc["other (embed, PLE, final mix, lm_head, host)"] = total - sum(acc.values())
-    for k, v in sorted(acc.items(), key=lambda kv: -kv[1]):
-        print(f"  {k:46s} {v:8.1f} ms  {100 * v / total:5.1f} %")
-    print(json.dumps({"tokens": a.tokens, "ctx": a.ctx, "ms": round(ms, 1), "tok_s": round(a.tokens / ms * 1e3), "split_ms": {k: round(v, 1) for k, v in acc.items()}}))
-    if a.by_kernel:
-        by = collections.defaultdict(float)
-        n_calls = collections.Counter()
-
-        class TimedLib:
-            """Every ``qwk_*`` launcher of the library, bracketed by CUDA events and a synchronize."""
-            def __init__(self, lib):
-                self._lib = lib
-
-            def __getattr__(self, name):
-                fn = getattr(self._lib, name)
-                if not name.startswith("qwk_"):
-                    return fn
-
-                def timed(*args):
-                    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    s0.record()
-                    r = fn(*args)
-                    s1.record()
-                    torch.cuda.synchronize()
-                    by[name] += s0.elapsed_time(s1)
-                    n_calls[name] += 1
-                    return r
-                return timed
-        real = P.lib
-        P.lib = TimedLib(real)
+    def fresh():
         eng.reset(0)
         if a.ctx:
             eng.prefill(0, toks[:a.ctx], want_logits=False)
-            by.clear()
-            n_calls.clear()
+        sync()
+
+    eng.prefill(0, toks[:min(512, a.tokens)], want_logits=False)          # warm-up
+    best = None
+    for _ in range(max(1, a.repeat)):
+        fresh()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         eng.prefill(0, toks[a.ctx:], want_logits=True)
-        P.lib = real
-        for k, v in sorted(by.items(), key=lambda kv: -kv[1]):
-            print(f"  {k:34s} {n_calls[k]:5d} calls {v:8.1f} ms")
+        e1.record()
+        sync()
+        eng.dm.check_error()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        best = float(t) if best is None else min(best, float(t))
+    pf = eng.prefiller
+    out = {"tokens": a.tokens, "ctx": a.ctx, "ranks": world, "lanes": pf.lanes, "chunk": pf.T, "ms": round(best, 2),
+           "tok_s": round(a.tokens / best * 1e3), "launches_per_chunk": int(eng.dm.lib.qwrt_prefill_last_launches())}
+    if a.by_step:
+        lib = eng.dm.lib
+        lib.qwrt_prefill_profile.argtypes = [C.c_int]
+        lib.qwrt_prefill_profile_read.argtypes = [C.POINTER(C.c_double), C.c_int]
+        fresh()
+        lib.qwrt_prefill_profile(1)
+        eng.prefill(0, toks[a.ctx:], want_logits=True)
+        lib.qwrt_prefill_profile(0)
+        sync()
+        buf = (C.c_double * 16)()
+        n = lib.qwrt_prefill_profile_read(buf, 16)
+        split = {CATS[i]: round(buf[i], 2) for i in range(min(n, len(CATS)))}
+        out["split_ms"] = split
+        if rank == 0:
+            tot = sum(split.values()) or 1.0
+            for k, v in sorted(split.items(), key=lambda kv: -kv[1]):
+                print(f"  {k:40s} {v:8.2f} ms  {100 * v / tot:5.1f} %", flush=True)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
