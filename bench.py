@@ -51,6 +51,9 @@ def main():
     ap.add_argument("--fuse-kinds", type=int, default=7,
                     help="timing diagnostic (results are wrong unless 7): bit mask of the fused collective kinds that run "
                          "(1 all-reduce, 2 all-gather, 4 reduce-scatter)")
+    ap.add_argument("--prefill-long", type=int, default=32768, help="tokens of the long-prompt prefill run (4,096-token chunks); 0 = skip")
+    ap.add_argument("--mtp-context", type=int, default=8192, help="context of the speculative-decoding runs; 0 = skip them")
+    ap.add_argument("--mtp-steps", type=int, default=12, help="timed speculative steps per forced-acceptance value")
     ap.add_argument("--profile-step", action="store_true",
                     help="bracket one extra chained decode step with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -81,8 +84,9 @@ def main():
     if args.layers:
         cfg = ModelConfig(**{**cfg.__dict__, "n_layers": args.layers})
     e2e_steps = args.e2e_steps or K
-    need = args.context + 2 * (W + K) + 2 * (W + e2e_steps) + 64
-    opts = EngineOptions(slots=1, slot_tokens=need, use_graphs=True, save_gdn=True)      # GDN state saves after every row: speculative verification
+    need = max(args.context + 2 * (W + K) + 2 * (W + e2e_steps) + 64, args.prefill_long + 256, args.mtp_context + 1024)
+    # four slots (the concurrent-stream runs); GDN state saved after every row of a step: speculative verification
+    opts = EngineOptions(slots=4, slot_tokens=need, use_graphs=True, save_gdn=True)
     t0 = time.time()
     if world > 1:
         from qwb200.parallel.dist_engine import make_engine
@@ -160,44 +164,72 @@ def main():
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     sampler.stop()
-    # ---- speculative decoding (one GPU): cost of a step with 3 drafts.  Random weights accept almost nothing, so the
-    # throughput the reference quotes (which rests on 2.35-3.53 accepted tokens per step with real weights) is given
-    # as a derived figure at its published 2.5 tokens per step, next to what was actually measured here.
+    # ---- long prompt: 32,768 tokens in 4,096-token chunks through the token-major path
+    prefill_long = None
+    if args.prefill_long and token_major:
+        lg = torch.Generator().manual_seed(77)
+        long_toks = torch.randint(0, cfg.vocab, (args.prefill_long,), generator=lg).tolist()
+        eng.reset(1)
+        barrier()
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        eng.prefill(1, long_toks, want_logits=True)
+        q1.record()
+        barrier()
+        eng.dm.check_error()
+        tl = torch.tensor([q0.elapsed_time(q1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+        prefill_long = {"tokens": args.prefill_long, "chunk": eng.prefiller.T, "lanes": eng.prefiller.lanes, "ms": round(float(tl), 1),
+                        "tok_s": round(args.prefill_long / (float(tl) / 1e3), 1)}
+        log(f"long prefill: {prefill_long}")
+        eng.reset(1)
+    # ---- speculative decoding through Session.generate: 5 drafts per step, sampling (T 1.0, top-k 20, top-p 0.95), 1 and 4
+    # concurrent streams of 8,192-token context.  Random weights accept next to nothing, so acceptance is forced: for
+    # a = 0..5 exactly `a` drafts are accepted per stream and step, and every figure is a timed run of real steps
+    # (drafts, one verification step over all streams' rows, sampling of every row, accept / rollback).
     mtp = None
-    if world == 1 and eng.mtp:
-        kd = 3
-        eng.reset(0)
-        eng.prefill(0, ctx[:512])
-        tk = int(eng.dm.buf["amax_idx"][eng.last_prefill_row])
-        got = eng.generate_greedy(0, tk, 8, k=kd)            # warm-up: captures the draft / verify graphs
+    if args.mtp_context and eng.mtp and (world == 1 or args.comm == "p2p"):
+        from qwb200.engine.sampling import SamplingParams
+        from qwb200.session.session import Session, StepReq
+        ses = Session(eng, host_cache_bytes=0)
+        kd, steps_m = 5, max(3, args.mtp_steps)
+        sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
+        mg = torch.Generator().manual_seed(99)
+        for sl_ in range(4):
+            eng.reset(sl_)
+            ses.sampler.reset_slot(sl_)
+            eng.prefill(sl_, torch.randint(0, cfg.vocab, (args.mtp_context,), generator=mg).tolist(), want_logits=True)
         torch.cuda.synchronize()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        got = eng.generate_greedy(0, got[-1], 48, k=kd)
-        s1.record()
-        torch.cuda.synchronize()
-        spec_ms = s0.elapsed_time(s1)
-        steps_, acc_ = max(1, eng.spec_steps), eng.spec_accepted
-        # phase split (host-timed with a synchronise after each phase)
-        ph = {"draft": 0.0, "verify": 0.0, "accept": 0.0}
-        pend = got[-1]
-        for _ in range(16):
-            torch.cuda.synchronize(); a0 = time.perf_counter()
-            dr = eng.draft(0, pend, kd)
-            torch.cuda.synchronize(); a1 = time.perf_counter()
-            lg = eng.verify(0, [pend] + dr)
-            torch.cuda.synchronize(); a2 = time.perf_counter()
-            pend = int(lg[0].argmax())
-            a2b = time.perf_counter()
-            eng.accept(0, [pend] + dr, 1)
-            torch.cuda.synchronize(); a3 = time.perf_counter()
-            ph["draft"] += (a1 - a0) * 1e3 / 16; ph["verify"] += (a2 - a1) * 1e3 / 16; ph["accept"] += (a3 - a2b) * 1e3 / 16
-        per_step = spec_ms / steps_
-        mtp = {"drafts": kd, "ms_per_spec_step": round(per_step, 3), "spec_steps": steps_, "accepted_drafts": acc_,
-               "phase_ms": {k_: round(v_, 3) for k_, v_ in ph.items()},
-               "tokens_per_step_measured": round(48 / steps_, 3), "tok_s_measured_random_weights": round(48 / (spec_ms / 1e3), 1),
-               "tok_s_at_2.5_tokens_per_step": round(2.5 / (per_step / 1e3), 1),
-               "note": "derived: measured step cost x the reference's published acceptance; random weights cannot show acceptance"}
+        eng.dm.check_error()
+        mtp = {"drafts": kd, "context": args.mtp_context, "sampling": {"temperature": 1.0, "top_k": 20, "top_p": 0.95},
+               "timed_steps_per_point": steps_m, "note": "measured: forced acceptance of a drafts per stream and step"}
+        for streams in (1, 4):
+            pend = [7 + i for i in range(streams)]
+            res = []
+            for acc in range(kd + 1):
+                def one_step():
+                    outs = ses.generate([StepReq(i, pend[i], 64, 0, sp) for i in range(streams)], kd, force_accept=acc)
+                    for i, o in enumerate(outs):
+                        pend[i] = o.tokens[-1]
+                    return sum(len(o.tokens) for o in outs)
+                for _ in range(3):
+                    one_step()
+                barrier()
+                m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                m0.record()
+                emitted = 0
+                for _ in range(steps_m):
+                    emitted += one_step()
+                m1.record()
+                barrier()
+                tm = torch.tensor([m0.elapsed_time(m1)], device=dev)
+                if dist is not None:
+                    dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+                res.append({"accepted": acc, "ms_per_step": round(float(tm) / steps_m, 3), "tok_s": round(emitted / (float(tm) / 1e3), 1)})
+            eng.dm.check_error()
+            mtp[f"streams_{streams}"] = res
+            log(f"speculative, {streams} stream(s): {res}")
     if dist is not None:
         tt = torch.tensor([ms, ms_e2e], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -223,6 +255,7 @@ def main():
             "prefill": {"tokens": args.context, "ms": round(prefill_ms, 2), "tok_s": round(args.context / (prefill_ms / 1e3), 1),
                         "path": "token-major" if token_major else "row-batched",
                         "lanes": (eng.prefiller.lanes if eng.prefiller is not None else 0)},
+            "prefill_long": prefill_long,
             "mtp": mtp,
             "gpu_launches": launches * K,
             "gpu_launches_per_step": launches,

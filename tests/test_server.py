@@ -230,6 +230,30 @@ def test_generate_error_fails_only_the_culprit():
     sched.shutdown()
 
 
+def test_failure_after_state_change_is_not_retried():
+    """A step that failed after the engine had advanced some slots fails the whole batch: stepping the others again
+    would decode their pending tokens twice."""
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(512, 512), step_seconds=0.005)
+    eng.reply = lambda prompt: [66] * 30
+    res, evs, reqs = {}, [], []
+    for i in range(2):
+        ev = threading.Event()
+        evs.append(ev)
+        reqs.append(Request(tokens=Tokens([65] * 8), max_new=50, sampling=Sampling(), stop_ids=[eng.eos],
+                            on_done=lambda reason, i=i, ev=ev: (res.__setitem__(i, reason), ev.set())))
+    for r in reqs:
+        sched.submit(r)
+    while not all(r.slot >= 0 and r.prefill_done for r in reqs):
+        time.sleep(0.002)
+    calls_before = eng.generate_calls if hasattr(eng, "generate_calls") else None
+    eng.generate_error[reqs[1].slot] = "step failed after slot state changed: device error"
+    assert all(ev.wait(10) for ev in evs)
+    assert res[0].startswith("error: step failed after slot state changed") and res[1].startswith("error: step failed")
+    sched.shutdown()
+
+
 def test_hung_engine_call_is_unhealthy():
     srv, sched, eng, pr = make_server("ok", stuck_seconds=0.2)
     eng.generate_block = threading.Event()

@@ -97,3 +97,84 @@ def test_generate_greedy_matches_engine_and_sampling_runs():
     assert all(0 <= x < cfg.vocab for x in outs[0].tokens) and all(lp <= 1e-4 for lp in outs[0].logprobs)
     ids, lps = ses.top_logprobs(0, 5)
     assert len(ids) == 5 and lps[0] >= lps[-1]
+
+
+def _ready(ses, cfg, slot_prompt):
+    for p in slot_prompt:
+        s = ses.acquire(p, 64)
+        ses.begin_prompt(s, p)
+        while not ses.prefill_some(s, 4096):
+            pass
+        ses.set_stop_tokens(s, [])
+        yield s
+
+
+def test_generate_batches_requests_into_one_step():
+    """Three requests through one generate() call per step (one draft chain, one verification step, one sampler call, one
+    accept launch) emit token for token what each request emits alone."""
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session.session import StepReq
+    cfg, eng, ses = make(None, slots=3)
+    prompts = [prompt_of(cfg, 70 + 9 * i, 30 + i) for i in range(3)]
+    slots = list(_ready(ses, cfg, prompts))
+    firsts = [ses.sample_prompt(s, SamplingParams())[0] for s in slots]
+    want = []
+    for p, f in zip(prompts, firsts):
+        _, e1, s1 = make(None, slots=1)
+        e1.prefill(0, p)
+        want.append(e1.generate_greedy(0, f, 12, k=0))
+    got, pend = [[] for _ in slots], list(firsts)
+    launches = []
+    while min(len(g) for g in got) < 12:
+        outs = ses.generate([StepReq(s, pend[i], 12, 0, SamplingParams()) for i, s in enumerate(slots)], k=3)
+        for i, o in enumerate(outs):
+            got[i] += o.tokens
+            pend[i] = o.tokens[-1]
+        assert ses.last_rows.shape[0] == sum(len(o.tokens) for o in outs)
+    for g, w in zip(got, want):
+        assert g[:12] == w
+    eng.dm.check_error()
+
+
+def test_penalties_with_drafts_equal_plain_decoding():
+    """Presence / frequency / repetition penalties see the pending token and the drafts before a row: generate() with
+    drafts emits token for token what it emits without, at a fixed seed."""
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session.session import StepReq
+    sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.9, presence_penalty=0.7, frequency_penalty=0.3,
+                        repetition_penalty=1.2, seed=11)
+    runs = []
+    for k in (0, 3):
+        cfg, eng, ses = make(None, slots=1)
+        p = prompt_of(cfg, 90, 8)
+        (s,) = _ready(ses, cfg, [p])
+        t, _ = ses.sample_prompt(s, sp)
+        out, pending = [], t
+        while len(out) < 16:
+            o = ses.generate([StepReq(s, pending, 16 - len(out), 0, sp)], k=k, force_accept=None)[0]
+            out += o.tokens
+            pending = o.tokens[-1]
+        runs.append([t] + out[:16])
+    assert runs[0] == runs[1]
+
+
+def test_forced_acceptance_keeps_the_slot_consistent():
+    """Accepting drafts by decree (the benchmark mode) leaves a slot whose state is that of its token list: the next
+    greedy token equals that of an engine that simply prefilled those tokens."""
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session.session import StepReq
+    cfg, eng, ses = make(None, slots=2)
+    prompts = [prompt_of(cfg, 75, 41), prompt_of(cfg, 66, 42)]
+    slots = list(_ready(ses, cfg, prompts))
+    pend = [ses.sample_prompt(s, SamplingParams())[0] for s in slots]
+    for step in range(4):
+        outs = ses.generate([StepReq(s, pend[i], 32, 0, SamplingParams()) for i, s in enumerate(slots)], k=3, force_accept=2)
+        for i, o in enumerate(outs):
+            assert len(o.tokens) == 3
+            pend[i] = o.tokens[-1]
+    for i, s in enumerate(slots):
+        _, e1, _ = make(None, slots=1)
+        e1.prefill(0, eng.slot[s].tokens)
+        want = e1.decode([0], [pend[i]])[0]
+        got = eng.decode([s], [pend[i]])[0]
+        assert got == want, (i, got, want)

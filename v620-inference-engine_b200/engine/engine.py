@@ -318,6 +318,116 @@ class Engine:
             dm.mtp_step([rows[n_acc - 1]], [slot], [base + n_acc - 2])
         sl.tokens.extend(int(t) for t in rows[:n_acc])
 
+    # ---- the same for several requests at once (one draft chain, one verification step, one accept launch)
+    MAX_DRAFTS = min(DM.GDN_RING, DM.RAW_RING) - 4      # a verification run longer than this would wrap the rings a rollback needs
+
+    def full_logits(self, n: int) -> torch.Tensor:
+        """Rows 0..n-1 of the last step's logits over the whole vocabulary [n, vocab] (device).  With several ranks the
+        vocabulary shards are gathered into every rank's copy first (one collective outside the step's graph)."""
+        dm = self.dm
+        if dm.sc.ranks == 1 or getattr(dm, "logits_full", None) is None:
+            return dm.buf["logits"][:n]
+        s = torch.cuda.current_stream(dm.dev).cuda_stream
+        import ctypes as C
+        rc = dm.lib.qwrt_gather_logits(C.byref(dm.model), n, 4000, C.c_void_p(s))
+        if rc != 0:
+            raise RuntimeError(f"qwrt_gather_logits failed: {rc}")
+        return dm.logits_full[:n]
+
+    def draft_batch(self, slots: Sequence[int], pendings: Sequence[int], k: int) -> List[List[int]]:
+        """k greedy draft tokens for every request (row i: slot ``slots[i]``, not yet decoded token ``pendings[i]``): one
+        MTP pass over all requests, chained k times on the device, one read-back."""
+        dm = self.dm
+        M = len(slots)
+        if M == 0 or k <= 0:
+            return [[] for _ in slots]
+        k = min(k, self.MAX_DRAFTS)
+        hid = dm.buf["hidden_out"]
+        for i, s_ in enumerate(slots):
+            assert self.slot[s_].mtp_hidden is not None
+            hid[i].copy_(self.slot[s_].mtp_hidden)
+        pos = [self.slot[s_].n - 1 for s_ in slots]
+        got = torch.zeros((k, M), dtype=torch.int32, device=dm.dev)
+        if self.opts.use_graphs:
+            flags = DM.FLAG_CHAIN
+            key = ("mtp", M, flags)
+            if key not in dm.graphs:
+                dm.mtp_step(list(pendings), list(slots), pos, flags=flags, graph=True)       # captures; the warm-up is the first pass
+                got[0].copy_(dm.buf["amax_idx"][:M])
+                done = 1
+            else:
+                dm.stage_rows(list(pendings), list(slots), pos, None)
+                done = 0
+            g = dm.graphs[key]
+            for j in range(done, k):
+                g.replay()
+                got[j].copy_(dm.buf["amax_idx"][:M], non_blocking=True)
+        else:
+            toks = list(pendings)
+            for j in range(k):
+                dm.mtp_step(toks, list(slots), [p + j for p in pos])
+                got[j].copy_(dm.buf["amax_idx"][:M])
+                toks = got[j].tolist()
+        torch.cuda.current_stream(dm.dev).synchronize()
+        cols = got.t().tolist()
+        return [list(c) for c in cols]
+
+    def verify_batch(self, slots: Sequence[int], runs: Sequence[List[int]]) -> int:
+        """One step over the runs of all requests (``runs[i]`` = [pending, draft 1, ...] appended to ``slots[i]``), keeping
+        the GDN state after every row and the hidden states.  Returns the number of rows; logits / argmax are in the
+        step buffers, the rows of a request consecutive and in request order."""
+        row_slots, row_toks, row_pos = [], [], []
+        c3 = []
+        for s_, run in zip(slots, runs):
+            base = self.slot[s_].n
+            if base + len(run) > self.dm.slot_tokens:
+                raise ValueError("slot capacity exceeded")
+            row_slots += [s_] * len(run)
+            row_toks += [int(t) for t in run]
+            row_pos += list(range(base, base + len(run)))
+            c3.append(self._ctx3(s_, run))
+        n = len(row_toks)
+        if n > self.dm.max_rows:
+            raise ValueError("too many rows in one verification step")
+        self.dm.step(row_toks, row_slots, row_pos, np.concatenate(c3), flags=DM.FLAG_SAVE_GDN | DM.FLAG_KEEP_HIDDEN,
+                     graph=self.opts.use_graphs)
+        return n
+
+    def accept_batch(self, slots: Sequence[int], runs: Sequence[List[int]], n_acc: Sequence[int]) -> None:
+        """Keep the first ``n_acc[i]`` rows of request i of the last ``verify_batch``: one launch copies the saved GDN states
+        of all requests and layers; requests whose drafts were all accepted get the MTP row they still lack."""
+        import ctypes as C
+        dm = self.dm
+        if not hasattr(self, "_accept_pairs"):
+            self._accept_pairs_host = torch.zeros(2 * dm.max_rows, dtype=torch.int32).pin_memory()
+            self._accept_pairs = torch.zeros(2 * dm.max_rows, dtype=torch.int32, device=dm.dev)
+            self._gdn_ptrs = torch.tensor([t.data_ptr() for t in dm.gdn_S] or [0], dtype=torch.int64, device=dm.dev)
+        h = self._accept_pairs_host.numpy()
+        row0, catch = 0, []
+        hid = dm.buf["hidden_out"]
+        for i, (s_, run, na) in enumerate(zip(slots, runs, n_acc)):
+            h[2 * i], h[2 * i + 1] = s_, (row0 + na - 1) if na < len(run) else -1
+            sl = self.slot[s_]
+            sl.mtp_hidden = hid[row0 + na - 1].clone()
+            if na == len(run) and na >= 2:
+                catch.append((s_, row0 + na - 2, run[na - 1], sl.n + na - 2))
+            row0 += len(run)
+        if self.cfg.n_gdn and "gdn_save" in dm.buf and any(h[2 * i + 1] >= 0 for i in range(len(slots))):
+            self._accept_pairs.copy_(self._accept_pairs_host, non_blocking=True)
+            st = C.c_void_p(torch.cuda.current_stream(dm.dev).cuda_stream)
+            state = dm.sc.gdn_vl * self.cfg.gdn_dim * self.cfg.gdn_dim
+            rc = dm.lib.qwk_gdn_accept(C.c_void_p(self._gdn_ptrs.data_ptr()), C.c_void_p(dm.buf["gdn_save"].data_ptr()), self.cfg.n_gdn,
+                                       dm.max_rows, state, C.c_void_p(self._accept_pairs.data_ptr()), len(slots), st)
+            if rc != 0:
+                raise RuntimeError(f"qwk_gdn_accept failed: {rc}")
+        if catch and self.mtp:
+            # every draft was accepted: the MTP layer has no row yet for the position of the last-but-one row
+            rows_h = torch.stack([hid[r].clone() for _, r, _, _ in catch])
+            hid[:len(catch)].copy_(rows_h)
+            dm.mtp_step([t for _, _, t, _ in catch], [s_ for s_, _, _, _ in catch], [p for _, _, _, p in catch])
+        for s_, run, na in zip(slots, runs, n_acc):
+            self.slot[s_].tokens.extend(int(t) for t in run[:na])
+
     def generate_greedy(self, slot: int, pending: int, n_new: int, k: int = 0) -> List[int]:
         """Greedy continuation of ``n_new`` tokens; with k > 0 drafts are verified (the result equals k = 0)."""
         out: List[int] = []

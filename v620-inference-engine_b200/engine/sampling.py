@@ -66,8 +66,11 @@ class GpuSampler:
             self.gen[slot].index_add_(0, t, torch.ones_like(t, dtype=torch.int16))
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], slots: Sequence[int], positions: Sequence[int],
-               hists: Optional[Sequence[Tuple[Sequence[int], int]]] = None) -> Tuple[List[int], List[float]]:
-        """logits fp32 [M, V] on the device.  ``hists[i] = (tokens so far, prompt_end)`` is only needed for a host fallback."""
+               hists: Optional[Sequence[Tuple[Sequence[int], int]]] = None,
+               force_host: Optional[Sequence[bool]] = None) -> Tuple[List[int], List[float]]:
+        """logits fp32 [M, V] on the device.  ``hists[i] = (tokens so far, prompt_end)`` is only needed for a host fallback;
+        ``force_host[i]``: draw row i on the host from ``hists[i]`` (rows whose penalty counts must include tokens that
+        are not in the slot's count tables yet)."""
         M = len(params)
         arr = np.zeros(M, dtype=_PARAM_DT)
         for i, (p, s, pos) in enumerate(zip(params, slots, positions)):
@@ -87,7 +90,7 @@ class GpuSampler:
         out = self.out_host[:M * 16].numpy().view(_OUT_DT)
         toks, lps = [int(x) for x in out["token"]], [float(x) for x in out["logprob"]]
         for i in range(M):
-            if out["fallback"][i]:
+            if out["fallback"][i] or (force_host is not None and force_host[i]):
                 self.fallbacks += 1
                 hist, pend = hists[i] if hists else ((), 0)
                 toks[i], lps[i] = self.host.sample(logits[i].float().cpu().numpy(), params[i].to_host(), hist, pend)

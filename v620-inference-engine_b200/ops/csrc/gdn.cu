@@ -297,6 +297,19 @@ __global__ void __launch_bounds__(512) gdn_fused_kernel(GdnFusedArgs a) {
     for (int i = 0; i < 32; ++i) Sg[(kg * 32 + i) * GD + c] = S[i];
 }
 
+
+// Speculative acceptance: for every (slot, row) pair and every GDN layer, the state saved after `row` of the last
+// verification step becomes the slot's state.  grid (blocks, pairs, layers); S_ptrs[layer] = [slots][state] fp32,
+// save = [layers][max_rows][state].  state % 4 == 0.
+__global__ void __launch_bounds__(256) gdn_accept_kernel(float *const *S_ptrs, const float *save, int max_rows, long long state,
+                                                         const int *pairs) {
+    const int layer = blockIdx.z, slot = pairs[2 * blockIdx.y], row = pairs[2 * blockIdx.y + 1];
+    if (row < 0) return;
+    const float4 *src = reinterpret_cast<const float4 *>(save + ((long long)layer * max_rows + row) * state);
+    float4 *dst = reinterpret_cast<float4 *>(S_ptrs[layer] + (long long)slot * state);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (state >> 2); i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace qw
 
 using namespace qw;
@@ -352,3 +365,12 @@ QW_API int qwk_gdn_step(const float *proj, int ld_proj, float *ring, const float
                         eps, s);
 }
 
+
+// S_ptrs: device array of n_layers state pointers; pairs: device [n_pairs][2] = {slot, saved row (-1: keep)}.
+QW_API int qwk_gdn_accept(const void *S_ptrs, const float *save, int n_layers, int max_rows, long long state, const int *pairs,
+                          int n_pairs, cudaStream_t s) {
+    if (n_pairs <= 0 || n_layers <= 0) return 0;
+    if (state & 3) return -1;
+    gdn_accept_kernel<<<dim3(8, n_pairs, n_layers), 256, 0, s>>>((float *const *)S_ptrs, save, max_rows, state, pairs);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

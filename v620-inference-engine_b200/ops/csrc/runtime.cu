@@ -345,9 +345,10 @@ static void head(Ctx &c, int flags) {
     const QwBuffers &b = md->b;
     const int M = c.rows->M;
     await_bin(c);
-    QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, d.vocab_l, 0, 1, 0, 0, 0,
+    const int ldl = md->logits_ld > 0 ? md->logits_ld : d.vocab_l;      // rows of the logits buffer (a slice of the all-rank matrix, or dense)
+    QW_OP(1, c.md->lm_head, (size_t)d.vocab_l * d.H * 2, qwk_gemv_bf16(c.md->lm_head, b.bin, b.logits, nullptr, d.vocab_l, d.H, M, d.H, d.H, ldl, 0, 1, 0, 0, 0,
                          c.s));
-    QW_TRYN(1, qwk_row_reduce(b.logits, d.vocab_l, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
+    QW_TRYN(1, qwk_row_reduce(b.logits, ldl, d.vocab_l, d.rank * d.vocab_l, M, b.amax_val, b.amax_idx, b.lse_max,
                           b.lse_sum, c.s));
     if (d.ranks > 1 && md->p2p && md->amax_pairs) {
         // vocabulary-parallel argmax: gather every rank's (value, index) and merge on the device
@@ -533,4 +534,13 @@ extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md
     walk_mtp(c, flags);
     g_last_launches = c.launches;
     return c.err;
+}
+
+// All ranks' logits of the last step side by side: with several ranks the logits buffer is this rank's column slice of a
+// [rows][vocab] matrix inside the symmetric region (logits_ld = vocab); this gathers the other ranks' slices of rows
+// 0..M-1 into it.  Outside the step's graph; `k` must differ from the step's own collective indices (use >= 4000).
+extern "C" __attribute__((visibility("default"))) int qwrt_gather_logits(const QwModel *md, int M, unsigned int k, cudaStream_t s) {
+    if (md->d.ranks == 1) return 0;
+    if (!md->p2p || md->logits_ld <= 0) return -1;
+    return qwk_p2p_allgather(md->p2p, k, 3, md->off_logits, M, md->d.vocab_l, 4, s);
 }

@@ -148,6 +148,9 @@ typedef struct QwModel {
     QwMtp mtp;
     float *mtp_hid;            // several ranks: [rows*hc][H] fp32 inside the symmetric region, the gathered hidden states of an MTP pass
     long long off_mtp_hid;     // its offset inside the region
+    long long off_logits;      // several ranks: offset of the [rows][vocab] fp32 logits matrix inside the region (b.logits = this rank's column slice)
+    int logits_ld;             // row stride of b.logits in floats (0: vocab_l, dense)
+    int pad2_;
 } QwModel;
 
 // flags of qwrt_decode

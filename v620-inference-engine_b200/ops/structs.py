@@ -62,7 +62,8 @@ class QwModel(C.Structure):
     _fields_ = [("d", QwDims), ("layers", C.POINTER(QwLayer)), ("final_hc", QwHc), ("ple", QwPle), ("embed", P),
                 ("lm_head", P), ("st", QwState), ("b", QwBuffers), ("comm", COMM_FN), ("comm_user", P),
                 ("p2p", P), ("amax_pairs", P), ("off_amax", C.c_longlong), ("off_bin", C.c_longlong), ("mtp", QwMtp),
-                ("mtp_hid", P), ("off_mtp_hid", C.c_longlong)]
+                ("mtp_hid", P), ("off_mtp_hid", C.c_longlong), ("off_logits", C.c_longlong), ("logits_ld", C.c_int),
+                ("pad2_", C.c_int)]
 
 
 class QwP2P(C.Structure):

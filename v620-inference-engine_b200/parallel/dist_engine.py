@@ -75,6 +75,7 @@ def attach_p2p(eng: Engine, group=None) -> None:
     take("bin", rows * c.hidden * 2)
     take("amax", rows * R * 2 * 4)
     take("mtp_hid", rows * c.hc * c.hidden * 4)
+    take("logits", rows * c.vocab * 4)
     region = SymmetricRegion(off, dm.dev, group)
     p = S.QwP2P()
     for i in range(8):
@@ -102,6 +103,13 @@ def attach_p2p(eng: Engine, group=None) -> None:
     dm.model.off_bin = lay["bin"]
     dm.model.mtp_hid = base + lay["mtp_hid"]
     dm.model.off_mtp_hid = lay["mtp_hid"]
+    # the logits buffer becomes this rank's column slice of the [rows][vocab] matrix all ranks' slices are gathered into
+    full = raw[lay["logits"]: lay["logits"] + rows * c.vocab * 4].view(torch.float32).view(rows, c.vocab)
+    dm.logits_full = full
+    dm.buf["logits"] = full[:, sc.rank * sc.vocab_l:(sc.rank + 1) * sc.vocab_l]
+    dm.model.b.logits = base + lay["logits"] + sc.rank * sc.vocab_l * 4
+    dm.model.off_logits = lay["logits"]
+    dm.model.logits_ld = c.vocab
     dm.graphs.clear()
 
 

@@ -362,10 +362,13 @@ class Scheduler:
         try:
             outs = self._call(self.e.generate, reqs, self.k)
         except Exception as ex:
-            if len(batch) == 1:
-                self.running.remove(batch[0])
-                self._fail(batch[0], str(ex))
-            else:                                          # find the culprit by stepping the requests one by one
+            if len(batch) == 1 or "step failed after slot state changed" in str(ex):
+                # a refusal of a single request, or a failure after the engine had already advanced some of the slots: repeating
+                # the step for the others would decode their pending token twice, so the whole batch fails
+                for r in batch:
+                    self.running.remove(r)
+                    self._fail(r, str(ex))
+            else:                                          # the step was refused before anything ran: find the culprit one by one
                 for r in batch:
                     try:
                         o = self._call(self.e.generate, [(r.slot, r.pending, max(1, r.max_new - r.emitted), 0, r.sampling)], self.k)

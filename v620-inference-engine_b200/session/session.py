@@ -89,7 +89,7 @@ class Session:
         self.boundary = -1
         self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
         self.store = H.BlockStore(self.io.state_layout_id(), engine.dm.sc.ranks, host_cache_bytes, disk_cache_dir, disk_cache_bytes)
-        self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.dm.sc.vocab_l, n, engine.opts.max_rows, seed)
+        self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.cfg.vocab, n, engine.opts.max_rows, seed)
         self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
         self.seen_chunks = set()
         self.last_rows: Optional[torch.Tensor] = None        # logits of the last decode / generate rows
@@ -206,10 +206,11 @@ class Session:
             end = end // BLOCK * BLOCK            # pieces end on block boundaries so a snapshot can be stored there
         piece = si.prompt[done:end]
         last = end >= len(si.prompt)
-        logits = self.e.prefill(slot, piece, want_logits=last)
+        self.e.prefill(slot, piece, want_logits=last)
         self.sampler.note_tokens(slot, piece, generated=False)
-        if last:
-            si.logits = logits.clone()
+        if last:          # the last row's logits over the whole vocabulary (gathered from the ranks' shards)
+            row = self.e.last_prefill_row
+            si.logits = self.e.full_logits(row + 1)[row].clone()
         si.timing["prefill_s"] += time.time() - t0
         self._save_blocks(slot, snapshot=(end % BLOCK == 0))
         return last
@@ -246,7 +247,7 @@ class Session:
         self.e.decode(slots, tokens, sync=False)
         for s, t in zip(slots, tokens):
             self.sampler.note_tokens(s, [int(t)], generated=True)
-        self.last_rows = self.e.dm.buf["logits"][:len(tokens)]
+        self.last_rows = self.e.full_logits(len(tokens))
         self.last_row_slots = list(slots)
 
     def sample_row(self, row: int, p: SamplingParams) -> Tuple[int, float]:
@@ -269,51 +270,111 @@ class Session:
         rate, k = best_rate(self.slots[slot].accept, k_max)
         return k if rate >= 1.0 else 0
 
-    def generate(self, reqs: Sequence[StepReq], k: int) -> List[StepOut]:
-        """One step for every request: decode its pending token plus up to k drafts, emit 1..k+1 tokens."""
-        outs: List[StepOut] = []
-        all_rows = []
-        row0 = 0
+    def generate(self, reqs: Sequence[StepReq], k: int, force_accept: Optional[int] = None) -> List[StepOut]:
+        """One step for every request: its pending token plus up to k drafts are decoded, 1..k+1 tokens are emitted.
+
+        All requests share one draft chain (the MTP pass over one row per request, chained on the device), ONE
+        verification step (the runs of all requests as consecutive rows), one sampler call over all rows and one accept
+        launch (reference: src/session/generate.cpp:119-313).  Everything that can be refused - budgets, slot capacity,
+        row limits - is checked before the first launch, so a ``ValueError`` leaves every slot as it was.
+        ``force_accept`` (benchmarks): accept exactly that many drafts per request whatever was sampled."""
         tr = self.gen_trace
         tr.start()
+        e = self.e
+        # ---- plan (no state is touched here)
+        max_rows = min(e.dm.max_rows, 32)
+        want = []
         for r in reqs:
-            si, sl = self.slots[r.slot], self.e.slot[r.slot]
-            kk = min(k, r.budget - 1) if self.e.mtp else 0
-            kk = self.draft_count(r.slot, kk) if kk > 0 else 0
-            if kk > 0 and sl.mtp_hidden is None:
-                kk = 0
-            drafts = self.e.draft(r.slot, r.pending, kk) if kk > 0 else []
-            tr.mark("draft")
-            rows = [r.pending] + drafts
-            logits = self.e.verify(r.slot, rows) if (drafts or self.e.mtp) else None
-            if logits is None:
-                self.e.decode([r.slot], [r.pending], sync=False)
-                logits = self.e.dm.buf["logits"][:1]
-            logits = logits.clone()
-            tr.mark("verify")
-            n = len(rows)
-            base = sl.n
-            hist = sl.tokens + rows
-            toks, lps = self.sampler.sample(logits, [r.sampling] * n, [r.slot] * n, [base + i + 1 for i in range(n)],
-                                            hists=[(hist[:base + i + 1], si.prompt_end) for i in range(n)])
-            tr.mark("sample")
-            n_acc = 1
-            while n_acc <= len(drafts) and toks[n_acc - 1] == drafts[n_acc - 1] and toks[n_acc - 1] not in si.stop:
-                n_acc += 1
-            if drafts or self.e.mtp:
-                self.e.accept(r.slot, rows, n_acc)
-            self.sampler.note_tokens(r.slot, rows[:n_acc], generated=True)
-            tr.mark("accept")
-            tr.count("drafts", len(drafts))
+            sl = e.slot[r.slot]
+            if r.budget < 1:
+                raise ValueError("a request needs a budget of at least one token")
+            kk = min(k, r.budget - 1, e.MAX_DRAFTS) if (e.mtp and sl.mtp_hidden is not None) else 0
+            if kk > 0 and force_accept is None:
+                kk = self.draft_count(r.slot, kk)
+            if sl.n + kk + 1 > e.dm.slot_tokens:
+                kk = e.dm.slot_tokens - sl.n - 1
+                if kk < 0:
+                    raise ValueError(f"slot {r.slot} is full")
+            want.append(kk)
+        if len(reqs) > max_rows:
+            raise ValueError("more requests than rows in a step")
+        while sum(want) + len(reqs) > max_rows:          # trim the longest draft runs first
+            want[want.index(max(want))] -= 1
+        spec = e.mtp and "gdn_save" in e.dm.buf
+        try:
+            return self._generate_planned(reqs, want, spec, force_accept)
+        except Exception as ex:
+            # from here on slots may have advanced: the caller must not repeat the step for any of these requests
+            raise RuntimeError(f"{self.STATE_CHANGED}: {ex}") from ex
+
+    STATE_CHANGED = "step failed after slot state changed"
+
+    def _generate_planned(self, reqs, want, spec, force_accept):
+        tr, e = self.gen_trace, self.e
+        # ---- drafts: one chain over the requests that draft
+        drafting = [i for i, kk in enumerate(want) if kk > 0]
+        drafts: List[List[int]] = [[] for _ in reqs]
+        if drafting:
+            got = e.draft_batch([reqs[i].slot for i in drafting], [reqs[i].pending for i in drafting], max(want))
+            for i, d in zip(drafting, got):
+                drafts[i] = d[:want[i]]
+        tr.mark("draft")
+        # ---- one verification step
+        slots = [r.slot for r in reqs]
+        runs = [[r.pending] + drafts[i] for i, r in enumerate(reqs)]
+        if spec:
+            n_rows = e.verify_batch(slots, runs)
+        else:
+            e.decode(slots, [r.pending for r in reqs], sync=False)
+            n_rows = len(reqs)
+        logits = e.full_logits(n_rows).clone()
+        tr.mark("verify")
+        # ---- one sampler call; the pending token joins the counts first, and a row behind drafts of a request with
+        # penalties is drawn on the host from the history that includes those drafts
+        params, row_slots, positions, hists, force_host = [], [], [], [], []
+        for i, r in enumerate(reqs):
+            si, sl = self.slots[r.slot], e.slot[r.slot]
+            self.sampler.note_tokens(r.slot, [r.pending], generated=True)
+            base = sl.n if spec else sl.n - 1          # a plain decode step has already appended the pending token
+            hist = sl.tokens[:base] + runs[i]
+            for j in range(len(runs[i])):
+                params.append(r.sampling)
+                row_slots.append(r.slot)
+                positions.append(base + j + 1)
+                hists.append((hist[:base + j + 1], si.prompt_end))
+                force_host.append(j > 0 and r.sampling.has_penalties())
+        toks, lps = self.sampler.sample(logits, params, row_slots, positions, hists=hists, force_host=force_host)
+        tr.mark("sample")
+        # ---- accept per request, one launch
+        outs: List[StepOut] = []
+        n_acc_all, row0, keep_rows = [], 0, []
+        for i, r in enumerate(reqs):
+            si = self.slots[r.slot]
+            d = drafts[i]
+            t = toks[row0:row0 + len(runs[i])]
+            if force_accept is not None:
+                n_acc = min(force_accept, len(d)) + 1
+                emitted = (d[:n_acc - 1] + [t[n_acc - 1]])[:r.budget]
+            else:
+                n_acc = 1
+                while n_acc <= len(d) and t[n_acc - 1] == d[n_acc - 1] and t[n_acc - 1] not in si.stop:
+                    n_acc += 1
+                emitted = t[:n_acc][:r.budget]
+            n_acc_all.append(n_acc)
+            if d:
+                si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(d))
+            tr.count("drafts", len(d))
             tr.count("accepted", n_acc - 1)
-            if drafts:
-                si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(drafts))
-            emitted = toks[:n_acc][:r.budget]
             stopped = bool(emitted) and emitted[-1] in si.stop
-            outs.append(StepOut(emitted, lps[:len(emitted)], row0, stopped))
-            all_rows.append(logits[:n_acc])
-            row0 += n_acc
-        self.last_rows = torch.cat(all_rows) if all_rows else None
+            outs.append(StepOut(emitted, lps[row0:row0 + len(emitted)], sum(n_acc_all[:-1]), stopped))
+            keep_rows.append(logits[row0:row0 + n_acc])
+            row0 += len(runs[i])
+        if spec:
+            e.accept_batch(slots, runs, n_acc_all)
+        for i, r in enumerate(reqs):
+            self.sampler.note_tokens(r.slot, runs[i][1:n_acc_all[i]], generated=True)
+        tr.mark("accept")
+        self.last_rows = torch.cat(keep_rows) if keep_rows else None
         self.last_row_slots = [r.slot for r, o in zip(reqs, outs) for _ in o.tokens]
         tr.finish()
         return outs
