@@ -160,7 +160,7 @@ def test_penalties_with_drafts_equal_plain_decoding():
 
 def test_forced_acceptance_keeps_the_slot_consistent():
     """Accepting drafts by decree (the benchmark mode) leaves a slot whose state is that of its token list: the next
-    greedy token equals that of an engine that simply prefilled those tokens."""
+    step's logits equal those of an engine that simply prefilled those tokens."""
     from qwb200.engine.sampling import SamplingParams
     from qwb200.session.session import StepReq
     cfg, eng, ses = make(None, slots=2)
@@ -175,6 +175,8 @@ def test_forced_acceptance_keeps_the_slot_consistent():
     for i, s in enumerate(slots):
         _, e1, _ = make(None, slots=1)
         e1.prefill(0, eng.slot[s].tokens)
-        want = e1.decode([0], [pend[i]])[0]
-        got = eng.decode([s], [pend[i]])[0]
-        assert got == want, (i, got, want)
+        e1.decode([0], [pend[i]])
+        want = e1.dm.buf["logits"][0].clone()
+        eng.decode([s], [pend[i]])
+        got = eng.dm.buf["logits"][0]
+        assert float((got - want).abs().max() / want.abs().max()) < 3e-2, i

@@ -107,7 +107,12 @@ class Prefiller:
             if not self.q4_fused:
                 self.b["w13dq"] = z((sc.exp_l * 2 * c.ffn, c.hidden), bf)
                 self.b["w2dq"] = z((sc.exp_l * c.hidden, c.ffn), bf)
-        self.rows_host = torch.zeros(11 * T, dtype=torch.int32).pin_memory()
+        # ring of pinned staging buffers: a chunk's row tables are copied when the stream gets to them, which can be long after
+        # the next chunk's tables are written on the host, so a buffer is refilled only once the copy that read it has run
+        self.rows_ring = [torch.zeros(11 * T, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self.rows_events = [None] * 3
+        self.rows_turn = 0
+        self.rows_host = self.rows_ring[0]
         self.side_stream = torch.cuda.Stream(device=dev) if self.lanes == 2 else None
         self.bufs = S.QwPrefillBufs()
         self._hook_cb = None
@@ -163,6 +168,10 @@ class Prefiller:
         """Row tables of a chunk (pinned host memory -> device, one copy): tokens | slot | pos | run_start | run_len | ctx3 |
         MTP positions | MTP run_len | MTP next tokens.  Run tables are relative to a lane's first row."""
         Tm = self.T
+        turn = self.rows_turn = (self.rows_turn + 1) % len(self.rows_ring)
+        if self.rows_events[turn] is not None:
+            self.rows_events[turn].synchronize()
+        self.rows_host = self.rows_ring[turn]
         h = self.rows_host.numpy()
         h[0:T] = toks
         h[Tm:Tm + T] = slot
@@ -181,6 +190,9 @@ class Prefiller:
             h[9 * Tm] = nm
             h[10 * Tm:10 * Tm + nm] = mtp_tokens
         self.b["rows"].copy_(self.rows_host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.dm.dev))
+        self.rows_events[turn] = ev
         r = self.b["rows"].data_ptr()
         return {"tokens": r, "slot": r + 4 * Tm, "pos": r + 8 * Tm, "run_start": r + 12 * Tm, "run_len": r + 16 * Tm,
                 "ctx3": r + 20 * Tm}

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float *logits, int l
     __shared__ float s_red[32];
     __shared__ int s_redi[32];
     __shared__ unsigned int s_prefix;
-    __shared__ int s_need, s_count;
+    __shared__ int s_need, s_count, s_ties;
     __shared__ float c_val[CAND];
     __shared__ int c_idx[CAND];
     __shared__ float scratch[32];
@@ -184,13 +184,29 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float *logits, int l
     __syncthreads();
     const int above = min(s_count, CAND);
     __syncthreads();
-    if (tid == 0) {           // ties at T are rare (equal floats): take them in index order, serially
-        int o = above;
-        for (int i = 0; i < V && o < want; ++i) {
-            const float v = penalised(l, i, p, g, sn);
-            if (order_key(v) == T) { c_val[o] = v; c_idx[o] = i; ++o; }
+    // ---- the entries equal to T (at least the want-th best itself): all threads look for them; if there are more than
+    // are needed (equal floats straddling the cut: rare) one thread takes the lowest indices serially instead
+    if (tid == 0) s_ties = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += 1024) {
+        const float v = penalised(l, i, p, g, sn);
+        if (order_key(v) == T) {
+            const int o = above + atomicAdd(&s_ties, 1);
+            if (o < CAND) { c_val[o] = v; c_idx[o] = i; }
         }
-        s_count = o;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (above + s_ties <= want) {
+            s_count = above + s_ties;
+        } else {
+            int o = above;
+            for (int i = 0; i < V && o < want; ++i) {
+                const float v = penalised(l, i, p, g, sn);
+                if (order_key(v) == T) { c_val[o] = v; c_idx[o] = i; ++o; }
+            }
+            s_count = o;
+        }
     }
     __syncthreads();
     const int n = s_count;
