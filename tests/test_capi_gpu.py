@@ -73,3 +73,41 @@ def test_capi_batch_of_requests_and_logprobs(eng):
     assert all(top is not None and len(top) == 3 for top in tops)
     # greedy: the sampled token is the most likely one
     assert all(top[0][0] == t for (t, top) in outs[0])
+
+
+@pytest.mark.multigpu
+def test_capi_on_two_gpus_matches_one():
+    """``devices: [0, 1]`` starts rank 0 in this process and rank 1 as a worker that replays every call: greedy and
+    speculative generation through the scheduler give the one-GPU tokens, prefix-cache reuse included, and the engine
+    reports no failure.  NVLS off: a test process that dies must not leave its memory bound to a multicast object."""
+    import os
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from qwserve.engine import Engine
+    from qwserve.scheduler import Scheduler
+    opts = {"synthetic": "tiny", "slots": [2048, 2048], "prefill_chunk": 256, "host_cache_gb": 0.25, "mtp": True}
+    prompt = [(i * 37 + 11) % 1000 + 5 for i in range(600)]
+    one = Engine(dict(opts))
+    s1 = Scheduler(one, drafts=0, prefill_piece=256)
+    s1.start(watchdog=False)
+    want, _, _ = run(s1, one, prompt, 20)
+    s1.shutdown()
+    one.close()
+    two = Engine(dict(opts, devices=[0, 1]))
+    try:
+        assert two.failure() == ""
+        s2 = Scheduler(two, drafts=0, prefill_piece=256)
+        s2.start(watchdog=False)
+        got, _, _ = run(s2, two, prompt, 20)
+        again, _, r2 = run(s2, two, prompt, 20)
+        s2.shutdown()
+        # greedy tokens may part ways only at a near-tie; the first tokens must agree and a rerun must repeat itself
+        assert got[:4] == want[:4] and again == got and r2.reused >= 256
+        if two.has_mtp:
+            s3 = Scheduler(two, drafts=2, prefill_piece=256)
+            s3.start(watchdog=False)
+            spec, _, _ = run(s3, two, prompt, 20)
+            s3.shutdown()
+            assert spec == got
+        assert two.failure() == ""
+    finally:
+        two.close()

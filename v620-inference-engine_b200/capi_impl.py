@@ -57,26 +57,87 @@ def _sampling(addr: int):
                           s.repetition_penalty, s.seed)
 
 
-class CApi:
+class SessionOps:
+    """The calls of the C API on plain Python values, over one rank's Session.  With several GPUs every rank owns one of
+    these and ``parallel.rank_group.RankGroup`` replays each call on all of them."""
+
     def __init__(self, session, vision=None):
-        self.s = session
-        self.vision = vision
+        self.s, self.vision = session, vision
+
+    def persist(self):
+        self.s.persist()
+        return 0
+
+    def flush(self):
+        self.s.store.flush()
+        return 0
+
+    def set_boundary_token(self, tok):
+        self.s.set_boundary_token(tok)
+        return 0
+
+    def acquire(self, toks, max_new):
+        return self.s.acquire(toks, max_new)
+
+    def release(self, slot):
+        self.s.release(slot)
+        return 0
+
+    def begin_prompt(self, slot, toks):
+        return self.s.begin_prompt(slot, toks)
+
+    def prefill_some(self, slot, max_tokens):
+        return bool(self.s.prefill_some(slot, max_tokens))
+
+    def sample_prompt(self, slot, sp):
+        return self.s.sample_prompt(slot, sp)
+
+    def decode(self, slots, tokens):
+        self.s.decode(slots, tokens)
+        return 0
+
+    def sample_row(self, row, sp):
+        return self.s.sample_row(row, sp)
+
+    def set_stop_tokens(self, slot, ids):
+        self.s.set_stop_tokens(slot, ids)
+        return 0
+
+    def generate(self, reqs, k):
+        return self.s.generate(reqs, k)
+
+    def check_error(self):
+        self.s.e.dm.check_error()
+        return 0
+
+
+class CApi:
+    def __init__(self, local: SessionOps, group=None):
+        self.local = local              # rank 0's own session
+        self.ops = group or local       # what engine calls go through: the rank group, or the local session alone
+        self.group = group
+        self.s = local.s
+        self.vision = local.vision
         self._failure = ""
         self._lock = threading.Lock()
 
     # ---- lifetime / health
     def close(self):
         try:
-            self.s.store.flush()
+            self.ops.flush()
         finally:
+            if self.group is not None:
+                self.group.shutdown()
             self.s = None
 
     def persist(self):
-        self.s.persist()
-        return 0
+        return self.ops.persist()
 
     def failure(self) -> str:
         if self._failure:
+            return self._failure
+        if self.group is not None and self.group.failure():
+            self._failure = self.group.failure()
             return self._failure
         try:
             self.s.e.dm.check_error()
@@ -86,8 +147,7 @@ class CApi:
 
     # ---- cache
     def set_boundary_token(self, tok):
-        self.s.set_boundary_token(tok)
-        return 0
+        return self.ops.set_boundary_token(tok)
 
     def get_cache_stats(self, out):
         st = self.s.cache_stats()
@@ -117,24 +177,23 @@ class CApi:
         return toks
 
     def acquire(self, addr, n, max_new, media, n_media):
-        return self.s.acquire(self._tokens(addr, n, media, n_media), max_new)
+        return self.ops.acquire(self._tokens(addr, n, media, n_media), max_new)
 
     def release(self, slot):
-        self.s.release(slot)
-        return 0
+        return self.ops.release(slot)
 
     def begin_prompt(self, slot, addr, n, media, n_media):
         toks = self._tokens(addr, n, media, n_media)
         if n_media and self.vision is not None:
             self.vision.stage(slot, media, n_media)
-        return self.s.begin_prompt(slot, toks)
+        return self.ops.begin_prompt(slot, toks)
 
     def prefill_some(self, slot, max_tokens):
-        return 1 if self.s.prefill_some(slot, max_tokens) else 0
+        return 1 if self.ops.prefill_some(slot, max_tokens) else 0
 
     def set_prompt(self, slot, addr, n, media, n_media):
         r = self.begin_prompt(slot, addr, n, media, n_media)
-        while not self.s.prefill_some(slot, 1 << 30):
+        while not self.ops.prefill_some(slot, 1 << 30):
             pass
         return r
 
@@ -146,7 +205,7 @@ class CApi:
         mt = np.ctypeslib.as_array(C.cast(max_tokens, C.POINTER(C.c_int64)), shape=(n,)).tolist()
         d = np.ctypeslib.as_array(C.cast(done, C.POINTER(C.c_int32)), shape=(n,))
         for i in range(n):
-            d[i] = 1 if self.s.prefill_some(sl[i], mt[i]) else 0
+            d[i] = 1 if self.ops.prefill_some(sl[i], mt[i]) else 0
         return 0
 
     def has_vision(self):
@@ -156,31 +215,29 @@ class CApi:
         return 1 if self.s.e.mtp else 0
 
     def sample_prompt(self, slot, p, lp):
-        tok, l = self.s.sample_prompt(slot, _sampling(p))
+        tok, l = self.ops.sample_prompt(slot, _sampling(p))
         if lp:
             C.c_float.from_address(lp).value = l
         return tok
 
     # ---- decoding
     def decode(self, n, slots, tokens):
-        self.s.decode(_i32(slots, n), _i32(tokens, n))
-        return 0
+        return self.ops.decode(_i32(slots, n), _i32(tokens, n))
 
     def sample_row(self, row, p, lp):
-        tok, l = self.s.sample_row(row, _sampling(p))
+        tok, l = self.ops.sample_row(row, _sampling(p))
         if lp:
             C.c_float.from_address(lp).value = l
         return tok
 
     def set_stop_tokens(self, slot, ids, n):
-        self.s.set_stop_tokens(slot, _i32(ids, n))
-        return 0
+        return self.ops.set_stop_tokens(slot, _i32(ids, n))
 
     def generate(self, n, reqs, k, tokens, logprobs, counts, first_rows, stopped):
         from .session.session import StepReq
         arr = (QwStepReq * n).from_address(reqs)
         rq = [StepReq(r.slot, r.pending, r.budget, r.flags, _sampling(C.addressof(r.sampling))) for r in arr]
-        outs = self.s.generate(rq, k)
+        outs = self.ops.generate(rq, k)
         tk = np.ctypeslib.as_array(C.cast(tokens, C.POINTER(C.c_int32)), shape=(n * (k + 1),))
         lp = np.ctypeslib.as_array(C.cast(logprobs, C.POINTER(C.c_float)), shape=(n * (k + 1),))
         cn = np.ctypeslib.as_array(C.cast(counts, C.POINTER(C.c_int32)), shape=(n,))
@@ -207,13 +264,38 @@ class CApi:
         return self._write_top(self.s.top_logprobs_prompt(slot, k), k, ids, lps)
 
 
+def _free_port() -> int:
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
 def open(options_json: str) -> CApi:
-    """Build engine + session from the options (see the module docstring)."""
+    """Build engine + session from the options (see the module docstring).  ``devices`` with more than one entry
+    starts one rank per device: rank 0 in this process, the others as worker processes that replay every call."""
+    o = json.loads(options_json or "{}")
+    devices = o.get("devices", [0])
+    world = len(devices)
+    if world == 1:
+        return CApi(build_ops(o, 0, 1, 0))
+    from .models.config import VALID_RANKS
+    if world not in VALID_RANKS:
+        raise ValueError(f"devices must list 1, 2, 4 or 8 GPUs, got {world}")
+    from .parallel.rank_group import RankGroup
+    port = _free_port()
+    group = RankGroup.spawn(world, [], {"options": o, "master_port": port}, lambda: build_ops(o, 0, world, port),
+                            ack_timeout=float(o.get("rank_timeout_s", 120)))
+    return CApi(group.local, group)
+
+
+def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
+    """One rank's engine + session from the options dictionary."""
     import torch
     from .engine.engine import Engine, EngineOptions
     from .models.config import ModelConfig
     from .session.session import Session
-    o = json.loads(options_json or "{}")
+    o = dict(o)
     from .utils import settings as _settings
     st = _settings.Settings.from_env(prefill_chunk=o.get("prefill_chunk"), prefill_piece=o.get("prefill_piece"),
                                      host_cache_gb=o.get("host_cache_gb"), disk_cache_dir=o.get("disk_cache_dir"),
@@ -221,11 +303,12 @@ def open(options_json: str) -> CApi:
                                      weight_cache_dir=o.get("weight_cache_dir"), ple_dir=o.get("ple_dir"))
     _settings.set_current(st)
     import sys
-    print(st.describe(), file=sys.stderr, flush=True)
+    if rank == 0:
+        print(st.describe(), file=sys.stderr, flush=True)
     if st.no_mtp:
         o["mtp"] = False
-    if st.no_vision:
-        o["vision"] = False
+    if st.no_vision or world > 1:
+        o["vision"] = False          # media patches reach rank 0 only: the vision tower serves one-GPU engines
     o.setdefault("prefill_chunk", st.prefill_chunk)
     o.setdefault("prefill_piece", st.prefill_piece)
     if "host_cache_gb" not in o and "QW_HOST_CACHE_GB" in os.environ:
@@ -237,30 +320,47 @@ def open(options_json: str) -> CApi:
         slots = [8192] * slots
     cap = int(o.get("slot_max_tokens") or max(slots))
     devices = o.get("devices", [0])
-    dev = f"cuda:{devices[0]}"
+    dev = f"cuda:{devices[rank]}"
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(devices[rank])
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(master_port), RANK=str(rank), WORLD_SIZE=str(world),
+                          LOCAL_RANK=str(rank))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device(dev))
     opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
                          save_gdn=bool(o.get("mtp", True)), host_pages=int(o.get("host_pages", 0)),
                          dev_pages=o.get("dev_pages"), use_graphs=not st.nograph)
+    log = (lambda m: print(m, file=sys.stderr, flush=True)) if rank == 0 else None
     if "model_dir" in o and o["model_dir"]:
         from .models.config import check_hf_config
         from .models.ple import PleTable
-        from .models.weights import load_checkpoint
         cfg = ModelConfig.full()
         check_hf_config(cfg, o["model_dir"])
         table = PleTable.load(cfg, o["ple_dir"], pin=True) if o.get("ple_dir") else None
-        eng = Engine.from_checkpoint(cfg, o["model_dir"], table, opts, device=dev,
-                                     weight_cache_dir=o.get("weight_cache_dir") or st.weight_cache_dir or None,
-                                     log=lambda m: print(m, file=sys.stderr, flush=True))
+        eng = Engine.from_checkpoint(cfg, o["model_dir"], table, opts, ranks=world, rank=rank, device=dev,
+                                     weight_cache_dir=o.get("weight_cache_dir") or st.weight_cache_dir or None, log=log)
     else:
         kind = o.get("synthetic", "tiny")
         cfg = {"full": ModelConfig.full, "slice2": ModelConfig.slice2, "tiny": ModelConfig.tiny}[kind]()
-        eng = Engine.synthetic(cfg, opts, device=dev, exact=(kind != "full"), ple_rows=int(o.get("ple_rows", 1 << 16)),
-                               ple_pinned=torch.cuda.is_available())
+        eng = Engine.synthetic(cfg, opts, ranks=world, rank=rank, device=dev, exact=(kind != "full"),
+                               ple_rows=int(o.get("ple_rows", 1 << 16)), ple_pinned=torch.cuda.is_available())
+    if world > 1:
+        from .parallel.dist_engine import attach_p2p, attach_tp, set_fused
+        attach_p2p(eng)
+        set_fused(True)
+        attach_tp(eng)
     if o.get("warmup", True) and torch.cuda.is_available():
         n_graphs = eng.warmup(max_rows=int(o.get("warmup_rows", 8)))
-        print(f"engine: {n_graphs} graphs captured; memory plan {eng.memory_plan()}", file=sys.stderr, flush=True)
+        if rank == 0:
+            print(f"engine: {n_graphs} graphs captured; memory plan {eng.memory_plan()}", file=sys.stderr, flush=True)
+    disk = o.get("disk_cache_dir") or None
+    if disk and world > 1:
+        disk = os.path.join(disk, f"rank{rank}")          # every rank keeps the blocks of its own shard
+        os.makedirs(disk, exist_ok=True)
     ses = Session(eng, host_cache_bytes=int(float(o.get("host_cache_gb", 8)) * (1 << 30)),
-                  disk_cache_dir=o.get("disk_cache_dir") or None,
+                  disk_cache_dir=disk,
                   disk_cache_bytes=int(float(o.get("disk_cache_gb", 0)) * (1 << 30)),
                   prefill_piece=int(o.get("prefill_piece", 2048)))
     vision = None
@@ -275,4 +375,4 @@ def open(options_json: str) -> CApi:
         if enc is not None:
             vision = VisionFrontend(enc, int(float(o.get("vision_cache_gb", 2)) * (1 << 30)))
             eng.vision_lookup = vision.lookup
-    return CApi(ses, vision)
+    return SessionOps(ses, vision)

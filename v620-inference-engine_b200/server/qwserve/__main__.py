@@ -27,6 +27,7 @@ def parse_args(argv=None):
     p.add_argument("--disk-cache-gb", type=float, default=0.0)
     p.add_argument("--no-vision", action="store_true")
     p.add_argument("--no-dashboard", action="store_true")
+    p.add_argument("--devices", default="0", help="GPUs of the engine, comma separated: 1, 2, 4 or 8 of them (tensor + expert parallel)")
     p.add_argument("--synthetic", default=None, help="serve a random-weight model of this size (tiny|slice2|full): for tests")
     return p.parse_args(argv)
 
@@ -40,7 +41,9 @@ def main(argv=None):
     from .scheduler import Scheduler
     opts = {"model_dir": a.model_dir, "ple_dir": a.ple_dir, "prefill_chunk": a.prefill_chunk,
             "slots": [int(x) for x in a.slots.split(",")], "host_cache_gb": a.host_cache_gb, "mtp": a.mtp > 0,
-            "vision": not a.no_vision}
+            "vision": not a.no_vision, "devices": [int(x) for x in a.devices.split(",") if x.strip() != ""]}
+    if a.mtp > 12:
+        raise SystemExit("--mtp: at most 12 drafts per step (a verification run must not wrap the 16-row state rings)")
     if a.synthetic:
         opts["synthetic"] = a.synthetic
     if a.kv_spill == "on":
