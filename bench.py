@@ -46,11 +46,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: run a model with fewer layers (marks the result invalid)")
     ap.add_argument("--ple-rows", type=int, default=1 << 22)
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end loop (default: --steps)")
-    ap.add_argument("--comm", default="p2p", choices=["p2p", "p2p-unfused", "p2p-mute", "nccl"],
-                    help="multi-GPU collectives: this library's peer-memory kernels, or the NCCL baseline")
-    ap.add_argument("--fuse-kinds", type=int, default=7,
-                    help="timing diagnostic (results are wrong unless 7): bit mask of the fused collective kinds that run "
-                         "(1 all-reduce, 2 all-gather, 4 reduce-scatter)")
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "p2p-unfused", "nccl"],
+                    help="multi-GPU collectives: this library's peer-memory kernels (inside the compute kernels, or as kernels "
+                         "of their own), or the NCCL baseline")
     ap.add_argument("--prefill-long", type=int, default=32768, help="tokens of the long-prompt prefill run (4,096-token chunks); 0 = skip")
     ap.add_argument("--mtp-context", type=int, default=8192, help="context of the speculative-decoding runs; 0 = skip them")
     ap.add_argument("--mtp-steps", type=int, default=12, help="timed speculative steps per forced-acceptance value")
@@ -91,9 +89,6 @@ def main():
     if world > 1:
         from qwb200.parallel.dist_engine import make_engine
         eng = make_engine(cfg, opts, world, rank, dev, ple_rows=args.ple_rows, log=log, comm=args.comm)
-        if args.fuse_kinds != 7:
-            from qwb200.ops import lib as qlib
-            qlib.load(True).qwrt_set_fuse_kinds(args.fuse_kinds)
     else:
         eng = Engine.synthetic(cfg, opts, device=dev, ple_rows=args.ple_rows, log=log)
     log(f"model ready in {time.time() - t0:.1f} s: {eng.dm.weight_bytes() / 1e9:.1f} GB of weights on rank {rank}")

@@ -84,5 +84,8 @@ def test_router_static_refuses_what_does_not_fit():
     assert L.qwk_moe_router_static(*args(33, nrs)) == -4
     assert L.qwk_moe_router_static(*args(4, 4097)) == -4
     assert L.qwk_moe_router_static(*args(0, nrs)) == -4
+    # fewer outputs per row than the routing reads (512 logits + gate + 2 x 640 shared rows): refused as an unsupported shape
+    assert L.qwk_moe_router_static(*args(4, 512 + 2 * 640)) == -1
+    assert L.qwk_moe_router_static(*args(4, 511)) == -1
     torch.cuda.synchronize()
     assert int((pe == -7).sum()) == pe.numel()            # nothing was launched

@@ -120,13 +120,20 @@ __global__ void __launch_bounds__(SG_THREADS, 1) moe_router_kernel(SGemvArgs a, 
 }
 
 template <int NT>
-static cudaError_t launch_router_nt(SGemvArgs &a, const RouteArgs &r, size_t smem, int grid, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
+static void configure_router_nt() {          // once per device: the kernels' dynamic shared memory opt-in
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaFuncSetAttribute(moe_router_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         cudaFuncSetAttribute(moe_router_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-        configured = true;
+        configured[dev] = true;
     }
+}
+template <int NT>
+static cudaError_t launch_router_nt(SGemvArgs &a, const RouteArgs &r, size_t smem, int grid, cudaStream_t s) {
+    configure_router_nt<NT>();
     if (a.fi.active) return launch_pdl(moe_router_kernel<NT, true>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
     return launch_pdl(moe_router_kernel<NT, false>, dim3(grid), dim3(SG_THREADS), smem, s, a, r);
 }
@@ -341,12 +348,14 @@ QW_API int qwk_moe_router(const void *Wrs, const void *x, float *rs, int nrs, in
     a.fi = take_fi();
     RouteArgs r = make_route(E, top_k, F, e_first, e_local, pair_expert, pair_w, sh_h, ticket);
     r.w13 = (const char *)w13; r.w2 = (const char *)w2; r.w13_bytes = w13_bytes; r.w2_bytes = w2_bytes;
-    r.prefetch_rows = 0;       // one block cannot pull 24 MB through its copy engine fast enough: measured 2x slower; kept off
-    {
+    r.prefetch_rows = 0;
+#ifdef QW_DIAG
+    {          // timing instrument: QW_SKIP=route_tail leaves the routing tables as they are
         static int skip_tail = -1;
         if (skip_tail < 0) { const char *e = getenv("QW_SKIP"); skip_tail = e && strstr(e, "route_tail") ? 1 : 0; }
         if (skip_tail) r.prefetch_rows = -1;
     }
+#endif
     const cudaError_t e = launch_router(a, r, s);
     return e == cudaSuccess ? 0 : -2;
 }
@@ -463,6 +472,8 @@ extern "C" __attribute__((visibility("default"))) int qwk_moe_router_static_setu
     const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_router_static_scratch);
     if (e != cudaSuccess || p == nullptr) return -3;
     g_router_static_ptr[dev] = p;
+    configure_router_nt<1>();          // the kernels' attributes too, so that a first call inside a capture has nothing left to set up
+    configure_router_nt<2>();
     return 0;
 }
 
@@ -470,6 +481,8 @@ extern "C" __attribute__((visibility("default"))) int qwk_moe_router_static(cons
                                  int e_first, int e_local, int *pair_expert, float *pair_w, void *sh_h, cudaStream_t s) {
     if (E > 1024 || top_k > 32 || (K & 15) || (ldx & 7)) return -1;
     if (M < 1 || M > QWK_ROUTER_STATIC_MAX_ROWS || nrs < 1 || nrs > QWK_ROUTER_STATIC_MAX_OUTPUTS) return -4;
+    // the routing reads E logits of a row and, for the shared activation, the gate logit and 2 F more outputs behind them
+    if (nrs < E + (sh_h ? 1 + 2 * F : 0)) return -1;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= QWK_ROUTER_STATIC_MAX_DEVICES) return -3;
     if (!g_router_static_ptr[dev] && qwk_moe_router_static_setup() != 0) return -3;

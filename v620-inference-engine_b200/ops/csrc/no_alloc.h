@@ -31,7 +31,11 @@
 // before the launch and the kernel leaves it at zero, the rest of the scratch is written before it is
 // read.  The results are in the caller's own buffers, so they stay valid after the next call.
 //
-// Return values: 0 enqueued; -1 unsupported shape (as qwk_moe_router); -2 launch error; -3 set-up failed
+// Like qwk_moe_router, a call takes the library's one-shot launch options that a caller of the step runtime may
+// have armed for "the next launch" (weight prefetch ranges, balance counters); callers of this entry point alone
+// never arm any.
+//
+// Return values: 0 enqueued; -1 unsupported shape (as qwk_moe_router; also nrs < E, or < E + 1 + 2 F with sh_h); -2 launch error; -3 set-up failed
 // (no current device, device index >= QWK_ROUTER_STATIC_MAX_DEVICES, or the symbol lookup failed);
 // -4 M or nrs beyond the limits above.
 #pragma once

@@ -25,8 +25,10 @@ FuseOut g_fo = {};
 FuseIn g_fi = {};
 }
 
-// 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels;
-// 2: timing diagnostic - nothing is sent or waited for, so a step costs what its kernels alone cost (results are wrong)
+// 1: collectives ride in the producer / consumer kernels; 0: stand-alone collective kernels.
+// Builds with -DQW_DIAG add timing instruments that make a step compute garbage on purpose: mode 2 (nothing is sent or
+// waited for, so a step costs what its kernels alone cost), a mask of collective kinds to leave out, and QW_SKIP=name,...
+// which leaves out every launch whose launcher call contains one of the names.  None of it is in the shipped library.
 static int g_fuse = 1;
 // MoE balance statistics (QW_MOE_STATS): a device array of one counter per layer (+ one for the MTP layer); every
 // routing launch adds the number of expert pairs that fall on this rank.  Null = off.
@@ -35,11 +37,17 @@ extern "C" __attribute__((visibility("default"))) int qwrt_set_moe_stats(int *ba
     g_moe_stats_base = base;
     return 0;
 }
-static int g_fuse_kinds = 7;    // timing diagnostic: bit k clear = collectives of kind k (0 all-reduce, 1 all-gather, 2 reduce-scatter) are skipped
+#ifdef QW_DIAG
+static int g_fuse_kinds = 7;    // bit k clear = collectives of kind k (0 all-reduce, 1 all-gather, 2 reduce-scatter) are skipped
 extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse_kinds(int mask) {
     g_fuse_kinds = mask & 7;
     return 0;
 }
+constexpr int FUSE_MODE_MAX = 2;
+#else
+constexpr int g_fuse_kinds = 7;
+constexpr int FUSE_MODE_MAX = 1;
+#endif
 static qw::FuseOut fuse_out_of(const void *p2p, int kind, unsigned k, int mode, int n) {
     return (g_fuse_kinds >> kind) & 1 ? qw::make_fuse_out(p2p, kind, k, mode, n) : qw::FuseOut{};
 }
@@ -47,7 +55,7 @@ static qw::FuseIn fuse_in_of(const void *p2p, int kind, unsigned k, int n) {
     return (g_fuse_kinds >> kind) & 1 ? qw::make_fuse_in(p2p, kind, k, n) : qw::FuseIn{};
 }
 extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int mode) {
-    g_fuse = mode < 0 || mode > 2 ? 1 : mode;
+    g_fuse = mode < 0 || mode > FUSE_MODE_MAX ? 1 : mode;
     return 0;
 }
 
@@ -58,11 +66,6 @@ extern "C" __attribute__((visibility("default"))) int qwk_set_error_word(void *p
 }
 
 namespace {
-
-struct WRange {
-    const char *p;
-    size_t n;
-};
 
 struct Ctx {
     const QwModel *md;
@@ -77,14 +80,9 @@ struct Ctx {
     bool fuse, mute;
     bool bin_pending, pend_fused;
     int bin_site, pend_site;
-    // L2 prefetch planning: a dry walk records the weights of every prefetch-capable launch in
-    // order; the real walk hands launch k the ranges plan[k]
-    bool dry;
-    int op;
-    std::vector<WRange> *ops;
-    const std::vector<qw::PfArgs> *plan;
 };
 
+#ifdef QW_DIAG
 // Timing diagnostic: QW_SKIP=name[,name...] leaves out every launch whose launcher call contains one of the names
 // (e.g. QW_SKIP=qwk_hc_down).  The step's results are then wrong; the step time shows what the kernels cost in place.
 bool skipped(const char *expr) {
@@ -109,38 +107,36 @@ bool skipped(const char *expr) {
         if (strstr(expr, n.c_str())) return true;
     return false;
 }
+#else
+inline bool skipped(const char *) { return false; }
+#endif
 
-long long g_last_launches = 0;
-int g_lookahead_mb = 0;         // how far ahead (MB) of the running kernel the L2 prefetch front is kept; 0 = off (measured: no gain on B200)   // kernels enqueued by the most recent qwrt_decode call
+long long g_last_launches = 0;      // kernels enqueued by the most recent qwrt_decode / qwrt_mtp call
 
 // Runs a launcher that enqueues `n` kernels; remembers the first failure and counts the launches.
 #define QW_TRYN(n, expr)                   \
     do {                                   \
-        if (!c.dry && !skipped(#expr)) {   \
+        if (!skipped(#expr)) {             \
             int rc__ = (expr);             \
             c.launches += (n);             \
             if (rc__ != 0 && c.err == 0) c.err = rc__ * 1000 - __LINE__; \
         }                                  \
     } while (0)
 
-// A launch whose kernel issues L2 prefetches for later kernels; `wptr`/`wbytes` are the weights it reads.
+// A launch that takes the one-shot options armed just before it (fused collective ends, the shared expert's activation);
+// they are cleared afterwards whether or not the launcher took them.  `wptr` / `wbytes` name the weights it streams.
 #define QW_OP(n, wptr, wbytes, expr)                                              \
     do {                                                                          \
-        if (c.dry) {                                                              \
-            c.ops->push_back(WRange{(const char *)(wptr), (size_t)(wbytes)});     \
-        } else {                                                                  \
-            if (c.mute) {                                                         \
-                qw::g_fo = qw::FuseOut{};                                         \
-                qw::g_fi = qw::FuseIn{};                                          \
-            }                                                                     \
-            if (c.plan && c.op < (int)c.plan->size()) qw::g_pf = (*c.plan)[c.op]; \
-            ++c.op;                                                               \
-            QW_TRYN(n, expr);                                                     \
-            qw::g_pf = qw::PfArgs{};                                              \
+        (void)(wptr);                                                             \
+        (void)(wbytes);                                                           \
+        if (c.mute) {                                                             \
             qw::g_fo = qw::FuseOut{};                                             \
             qw::g_fi = qw::FuseIn{};                                              \
-            qw::g_shared_act = qw::SharedAct{nullptr, 0, 0, 0, nullptr};          \
         }                                                                         \
+        QW_TRYN(n, expr);                                                         \
+        qw::g_fo = qw::FuseOut{};                                                 \
+        qw::g_fi = qw::FuseIn{};                                                  \
+        qw::g_shared_act = qw::SharedAct{nullptr, 0, 0, 0, nullptr};              \
     } while (0)
 
 inline int hc_send(const QwDims &d) { return d.hc + d.hc * (d.hc_rank + d.hc); }
@@ -148,7 +144,6 @@ inline int hc_send(const QwDims &d) { return d.hc + d.hc * (d.hc_rank + d.hc); }
 void comm(Ctx &c, int kind, const void *src, void *dst, int rows, int n) {
     const QwModel &md = *c.md;
     ++c.site;
-    if (c.dry) return;
     if (md.d.ranks > 1 && md.p2p) {
         int rc = 0;
         if (kind == 0) rc = qwk_p2p_allreduce(md.p2p, (unsigned)c.site, (const float *)src, (float *)dst, rows, n, c.s);
@@ -168,7 +163,7 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const QwBuffers &b = md.b;
     const int M = c.rows->M, ld = hc_send(d);
     const int down = d.hc_rank + w.n_inj;
-    if (c.fuse && !c.dry) {
+    if (c.fuse) {
         // the down projection consumes the pending block output's reduce-scatter and sends the all-reduce
         if (pend && c.pend_fused) qw::g_fi = fuse_in_of(md.p2p, 2, (unsigned)c.pend_site, d.SH);
         qw::g_fo = fuse_out_of(md.p2p, 0, (unsigned)(c.site + 1), 1, ld);
@@ -184,11 +179,9 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
     const float *red = b.send;
     if (c.fuse) {
         ++c.site;
-        if (!c.dry) {
-            // the up projection consumes that all-reduce and sends its columns of the block input (all-gather)
-            qw::g_fi = fuse_in_of(md.p2p, 0, (unsigned)c.site, ld);
-            qw::g_fo = fuse_out_of(md.p2p, 1, (unsigned)(c.site + 1), 1, d.SH);
-        }
+        // the up projection consumes that all-reduce and sends its columns of the block input (all-gather)
+        qw::g_fi = fuse_in_of(md.p2p, 0, (unsigned)c.site, ld);
+        qw::g_fo = fuse_out_of(md.p2p, 1, (unsigned)(c.site + 1), 1, d.SH);
     } else if (d.ranks > 1) {
         comm(c, 0, b.send, b.red, M, ld);
         red = b.red;
@@ -209,14 +202,14 @@ void mix(Ctx &c, const QwHc &w, const float *pend, const float *inj_prev, float 
 
 // Before the first kernel that reads the gathered block input.
 inline void await_bin(Ctx &c) {
-    if (c.bin_pending && !c.dry) qw::g_fi = fuse_in_of(c.md->p2p, 1, (unsigned)c.bin_site, c.md->d.SH);
+    if (c.bin_pending) qw::g_fi = fuse_in_of(c.md->p2p, 1, (unsigned)c.bin_site, c.md->d.SH);
     c.bin_pending = false;
 }
 
 // Before the kernel that writes the block output `partial`: it also sends the reduce-scatter.
 inline void send_partial(Ctx &c, bool fused) {
     const QwDims &d = c.md->d;
-    if (fused && c.fuse && !c.dry)
+    if (fused && c.fuse)
         qw::g_fo = fuse_out_of(c.md->p2p, 2, (unsigned)(c.site + 1), 2, d.SH);
 }
 
@@ -281,11 +274,11 @@ void moe_block(Ctx &c, const QwLayer &L, bool fuse_out = true, int stats_index =
     const int M = c.rows->M;
     const int nrs = d.E + 1 + 2 * d.SF;
     await_bin(c);
-    if (!c.dry && g_moe_stats_base && stats_index >= 0) qw::g_moe_stats = g_moe_stats_base + stats_index;
+    if (g_moe_stats_base && stats_index >= 0) qw::g_moe_stats = g_moe_stats_base + stats_index;
     // the shared expert's activation is formed by extra blocks of the gate/up launch, not by the router's last block
     QW_OP(1, L.Wrs, (size_t)nrs * d.H * 2, qwk_moe_router(L.Wrs, b.bin, b.rs, nrs, d.H, M, d.H, d.E, d.top_k, d.SF, d.e_first, d.E_l, b.pair_expert,
                               b.pair_w, nullptr, b.ticket, L.w13, L.w2, (long long)2 * d.F * d.H / 2, (long long)d.H * d.F / 2, c.s));
-    if (!c.dry) qw::g_shared_act = qw::SharedAct{b.rs, nrs, d.E, d.SF, b.sh_h};
+    qw::g_shared_act = qw::SharedAct{b.rs, nrs, d.E, d.SF, b.sh_h};
     QW_OP(1, nullptr, 0, qwk_moe_gate_up_pair(L.w13, L.s13, b.bin, d.H, b.pair_expert, M, d.top_k, d.F, d.H, b.moe_h, c.s));
     send_partial(c, fuse_out);
     QW_OP(1, L.Wsd, (size_t)d.H * d.SF * 2, qwk_moe_down_combine(L.w2, L.s2, b.moe_h, b.pair_expert, b.pair_w, M, d.top_k, d.F, d.H, L.Wsd, d.SF, b.sh_h,
@@ -354,9 +347,7 @@ static void head(Ctx &c, int flags) {
         // vocabulary-parallel argmax: gather every rank's (value, index) and merge on the device
         QW_TRYN(1, qwk_amax_pack(b.amax_val, b.amax_idx, md->amax_pairs, M, d.rank, d.ranks, c.s));
         ++c.site;
-        if (!c.dry) {
-            QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_amax, M, 2, 4, c.s));
-        }
+        QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_amax, M, 2, 4, c.s));
         QW_TRYN(1, qwk_amax_merge(md->amax_pairs, M, d.ranks, b.amax_idx, b.amax_val, c.s));
     }
     if ((flags & QWRT_CHAIN) && (d.ranks == 1 || md->p2p))
@@ -364,8 +355,7 @@ static void head(Ctx &c, int flags) {
                                 const_cast<int *>(c.rows->ctx3), b.amax_idx, M, c.s));
 }
 
-// The launch sequence of one step.  With c.dry it only records the weights of the prefetch-capable
-// launches; otherwise it enqueues the kernels.
+// The launch sequence of one step.
 static void walk(Ctx &c, int flags, int n_layers_run) {
     const QwModel *md = c.md;
     const QwDims &d = md->d;
@@ -374,9 +364,8 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     c.X = b.X;
     c.Xalt = b.X2;
     c.site = 0;
-    c.op = 0;
     c.fuse = d.ranks > 1 && md->p2p && g_fuse;
-    c.mute = g_fuse == 2;
+    c.mute = FUSE_MODE_MAX > 1 && g_fuse == 2;
     c.bin_pending = c.pend_fused = false;
     if (d.ranks > 1 && md->p2p) QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
     QW_TRYN(1, qwk_embed_rows(c.rows->tokens, c.md->embed, d.H, d.rank * d.SH, d.SH, d.hc, d.vocab, b.X, M, c.s));
@@ -403,7 +392,7 @@ static void walk(Ctx &c, int flags, int n_layers_run) {
     }
     mix(c, c.md->final_hc, pend, inj_mlp, nullptr);
     if ((flags & QWRT_KEEP_HIDDEN) && b.hidden_out)
-        if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
+        cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
     if (!(flags & QWRT_NO_HEAD)) head(c, flags);
 }
 
@@ -417,9 +406,8 @@ static void walk_mtp(Ctx &c, int flags) {
     c.X = b.X;
     c.Xalt = b.X2;
     c.site = 0;
-    c.op = 0;
     c.fuse = d.ranks > 1 && md->p2p && g_fuse;
-    c.mute = g_fuse == 2;
+    c.mute = FUSE_MODE_MAX > 1 && g_fuse == 2;
     c.bin_pending = c.pend_fused = false;
     const float *hidden = b.hidden_out;
     if (d.ranks > 1) {
@@ -427,12 +415,12 @@ static void walk_mtp(Ctx &c, int flags) {
         // column slices of the hidden states into a [M*hc][H] matrix inside the symmetric region.  The fc matrices are
         // sliced by output rows, so their products are this rank's columns of the new residual: no collective after them.
         QW_TRYN(1, qwk_p2p_bump_base(md->p2p, 4096u, c.s));
-        if (!c.dry) {
+        {
             cudaMemcpy2DAsync(md->mtp_hid + (size_t)d.rank * d.SH, sizeof(float) * (size_t)d.H, b.hidden_out, sizeof(float) * (size_t)d.SH,
                               sizeof(float) * (size_t)d.SH, (size_t)M * d.hc, cudaMemcpyDeviceToDevice, c.s);
         }
         ++c.site;
-        if (!c.dry) QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_mtp_hid, M * d.hc, d.SH, 4, c.s));
+        QW_TRYN(1, qwk_p2p_allgather(md->p2p, (unsigned)c.site, 3, md->off_mtp_hid, M * d.hc, d.SH, 4, c.s));
         hidden = md->mtp_hid;
     }
     QW_TRYN(1, qwk_mtp_norm(hidden, c.rows->tokens, md->embed, d.vocab, t.nh1, t.ne1, d.H, d.hc, d.eps, t.hn, t.en, M, c.s));
@@ -448,37 +436,8 @@ static void walk_mtp(Ctx &c, int flags) {
     moe_block(c, t.layer, true, d.n_layers);
     const float *pend = scatter(c, b.out_b);
     mix(c, t.final_hc, pend, inj_mlp, nullptr);
-    if (!c.dry) cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
+    cudaMemcpyAsync(b.hidden_out, c.X, sizeof(float) * (size_t)M * d.hc * d.SH, cudaMemcpyDeviceToDevice, c.s);
     head(c, flags);
-}
-
-// Ranges of later kernels' weights that launch k asks the L2 to fetch: the plan keeps the prefetch
-// front `lookahead` bytes past the end of launch k's own weights.
-static void make_plan(const std::vector<WRange> &ops, size_t lookahead, std::vector<qw::PfArgs> &plan) {
-    const int n = (int)ops.size();
-    std::vector<size_t> cum(n + 1, 0);
-    for (int k = 0; k < n; ++k) cum[k + 1] = cum[k] + ops[k].n;
-    plan.assign(n, qw::PfArgs{});
-    size_t issued = n ? cum[1] : 0;
-    for (int k = 0; k < n; ++k) {
-        if (issued < cum[k + 1]) issued = cum[k + 1];
-        const size_t target = cum[k + 1] + lookahead < cum[n] ? cum[k + 1] + lookahead : cum[n];
-        int r = 0;
-        while (issued < target && r < 3) {
-            int j = k + 1;
-            while (j < n && cum[j + 1] <= issued) ++j;      // the launch whose weights contain `issued`
-            if (j >= n) break;
-            const size_t off = issued - cum[j];
-            size_t len = ops[j].n - off;
-            if (issued + len > target) len = target - issued;
-            len &= ~(size_t)15;
-            if (!len) { issued = cum[j + 1]; continue; }
-            plan[k].p[r] = ops[j].p + off;
-            plan[k].n[r] = len;
-            issued += len;
-            ++r;
-        }
-    }
 }
 
 extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel *md, const QwRows *rows, int flags,
@@ -490,29 +449,13 @@ extern "C" __attribute__((visibility("default"))) int qwrt_decode(const QwModel 
     const int M = rows->M;
     if (M < 1 || M > d.max_rows) return -1;
     if (n_layers_run < 0 || n_layers_run > d.n_layers) n_layers_run = d.n_layers;
-    // dry walk -> weight list -> prefetch plan -> real walk
-    std::vector<WRange> ops;
-    std::vector<qw::PfArgs> plan;
-    ops.reserve(1024);
-    c.dry = true;
-    c.ops = &ops;
-    walk(c, flags, n_layers_run);
-    make_plan(ops, (size_t)g_lookahead_mb << 20, plan);
-    c.dry = false;
-    c.plan = &plan;
     c.launches = 0;
     walk(c, flags, n_layers_run);
     g_last_launches = c.launches;
     return c.err;
 }
 
-// Kernels enqueued by the most recent qwrt_decode call (what one replay of its graph launches).
-// Sets the prefetch distance in MB (0 disables L2 prefetching).
-extern "C" __attribute__((visibility("default"))) int qwrt_set_lookahead_mb(int mb) {
-    g_lookahead_mb = mb < 0 ? 0 : mb;
-    return 0;
-}
-
+// Kernels enqueued by the most recent qwrt_decode / qwrt_mtp call (what one replay of its graph launches).
 extern "C" __attribute__((visibility("default"))) long long qwrt_last_launches() { return g_last_launches; }
 
 extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md, const QwRows *rows, int flags,
@@ -522,14 +465,6 @@ extern "C" __attribute__((visibility("default"))) int qwrt_mtp(const QwModel *md
     if (M < 1 || M * md->d.hc > md->d.max_rows * md->d.hc) return -1;
     Ctx c{};
     c.md = md; c.rows = rows; c.s = stream; c.X = md->b.X; c.Xalt = md->b.X2;
-    std::vector<WRange> ops;
-    std::vector<qw::PfArgs> plan;
-    c.dry = true;
-    c.ops = &ops;
-    walk_mtp(c, flags);
-    make_plan(ops, (size_t)g_lookahead_mb << 20, plan);
-    c.dry = false;
-    c.plan = &plan;
     c.launches = 0;
     walk_mtp(c, flags);
     g_last_launches = c.launches;

@@ -131,7 +131,7 @@ def set_fused(on: bool) -> None:
     """Peer-memory backend: send every collective from the kernel that produces its payload and wait for it in
     the kernel that consumes it (default), or run each collective as a kernel of its own."""
     from ..ops import lib as qlib
-    qlib.load(True).qwrt_set_fuse(int(on))          # 2 = timing diagnostic without any exchange (wrong results)
+    qlib.load(True).qwrt_set_fuse(int(on))
 
 
 def attach_nccl(eng: Engine, group=None) -> None:
@@ -184,9 +184,9 @@ def make_engine(cfg: ModelConfig, opts: EngineOptions, world: int, rank: int, de
     eng = Engine.synthetic(cfg, opts, ranks=world, rank=rank, device=device, seed=seed, exact=exact,
                            ple_rows=ple_rows, log=log)
     if world > 1:
-        if comm in ("p2p", "p2p-unfused", "p2p-mute"):
+        if comm in ("p2p", "p2p-unfused"):
             attach_p2p(eng)
-            set_fused({"p2p": 1, "p2p-unfused": 0, "p2p-mute": 2}[comm])
+            set_fused(comm == "p2p")
             attach_tp(eng)
         else:
             attach_nccl(eng)
