@@ -8,6 +8,7 @@ from .ops import lib as qlib
 def build_all(force: bool = False, verbose: bool = False) -> None:
     path = qlib.build(force=force, verbose=verbose)
     print("built", path)
+    print("built", qlib.build(force=force, verbose=verbose, checked=True))
     try:
         from .native import build as nbuild
         nbuild.build(force=force, verbose=verbose)

@@ -36,6 +36,33 @@ enum ErrCode : unsigned int {
 __device__ __forceinline__ void report(ErrorWord *e, unsigned int code, unsigned int detail) {
     if (e && atomicCAS(&e->code, 0u, code) == 0u) e->detail = detail;
 }
+// Checked builds (-DQW_DEVICE_CHECKS, the library libqw_kernels_checked.so): indices that come from data - token ids,
+// positions, page numbers - are validated where they are used.  A violation records ERR_BOUNDS with `detail` in the
+// error word and the kernel skips the access and returns; nothing traps, so the context stays usable and the host reads
+// the word like any other kernel failure.  Without the flag the checks compile to nothing.  A translation unit that uses
+// QW_DCHECK registers itself with QW_DCHECK_TU(name); qwk_set_error_word then hands the word's address to every one of
+// them (each unit keeps its own copy: the library is built without relocatable device code).
+// (Role of the reference's QW_DCHECK, src/kernels/common.cuh:13-24, which traps instead.)
+#ifdef QW_DEVICE_CHECKS
+static __device__ __attribute__((unused)) ErrorWord *s_dcheck_word = nullptr;
+#define QW_DCHECK(cond, detail)                                             \
+    do {                                                                    \
+        if (!(cond)) {                                                      \
+            report(s_dcheck_word, ERR_BOUNDS, (unsigned int)(detail));      \
+            return;                                                         \
+        }                                                                   \
+    } while (0)
+#define QW_DCHECK_TU(name)                                                                                  \
+    extern "C" __attribute__((visibility("default"))) int qw_dcheck_set_##name(void *p) {                   \
+        return cudaMemcpyToSymbol(qw::s_dcheck_word, &p, sizeof(p)) == cudaSuccess ? 0 : -2;                \
+    }
+#else
+#define QW_DCHECK(cond, detail) \
+    do {                        \
+    } while (0)
+#define QW_DCHECK_TU(name)
+#endif
+
 // Device address of the error word every launcher hands to its kernel (set once by the host through
 // qwk_set_error_word; null until then, in which case kernels only give up silently).
 extern ErrorWord *g_err_ptr;

@@ -19,6 +19,7 @@ __global__ void embed_rows_kernel(const int *tokens, const bf16 *table, int ld_t
                                   int vocab, float *X) {
     const int m = blockIdx.x;
     int t = tokens[m];
+    QW_DCHECK(t >= 0 && t < vocab, 0x01000000u | (unsigned)(m & 0xffffff));          // token id outside the vocabulary (row m)
     if (t < 0 || t >= vocab) t = 0;
     const bf16 *row = table + (long long)t * ld_table + col0;
     for (int c = threadIdx.x; c < SH; c += blockDim.x) {
@@ -52,21 +53,21 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(float *X, const float *pend
     }
 }
 
-constexpr int UP_ROWS = 4;     // rows per block of hc_up_mix
+constexpr int UP_ROWS = 4;     // rows per block of hc_up_mix (8 in steps of more than four rows: the weights are read once per block)
 constexpr int UP_MAXI = 5;     // 16-byte weight pieces per lane: covers mixer ranks up to 320
 
-// grid (ceil(SH/8), ceil(M/UP_ROWS)), 256 threads.  hc must be 4 (one 8-lane group per stream).
+// grid (ceil(SH/8), ceil(M/UPR)), 256 threads.  hc must be 4 (one 8-lane group per stream).
 // y[s][c] = bf16(X[s][c] * w1[s][c]) is recomputed here exactly as hc_down_kernel computed it.
-template <bool FUSED>
+template <bool FUSED, int UPR>
 __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int ld_red, const bf16 *Wu /* [SH][hc][R] */,
                                                         const float *X, const float *w1, int SH, int hc, int R, int hc_down,
                                                         float inv_H, float eps, int M, float *inj, int ld_inj, bf16 *bin,
                                                         int ld_bin, int bin_col0, PfArgs pf, FuseIn fi, FuseOut fo) {
     extern __shared__ float sm[];
-    float *u = sm;                         // [UP_ROWS][R]
-    float *rs = sm + UP_ROWS * R;          // [UP_ROWS][hc]
-    const int m0 = blockIdx.y * UP_ROWS;
-    const int nrow = min(UP_ROWS, M - m0);
+    float *u = sm;                         // [UPR][R]
+    float *rs = sm + UPR * R;          // [UPR][hc]
+    const int m0 = blockIdx.y * UPR;
+    const int nrow = min(UPR, M - m0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * 8 + warp;
     const int s = lane >> 3, li = lane & 7;
@@ -84,16 +85,16 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
     pdl_trigger();
     // this lane's residual values times the norm weight: needed only at the very end, fetched now so that their L2
     // round trip overlaps the staging of the reduced vector
-    float xw[UP_ROWS];
+    float xw[UPR];
     {
         const float w1v = c < SH ? w1[s * SH + c] : 0.f;
 #pragma unroll
-        for (int mm = 0; mm < UP_ROWS; ++mm)
+        for (int mm = 0; mm < UPR; ++mm)
             xw[mm] = (c < SH && mm < nrow) ? __ldcg(X + ((long long)(m0 + mm) * hc + s) * SH + c) * w1v : 0.f;
     }
     // element i of the reduced vector: the local buffer, or (fused all-reduce) the ranks' words added in rank
     // order - staged once per block into shared memory, with every thread's loads in flight together
-    float *reds = rs + UP_ROWS * hc;       // [UP_ROWS][ld_red]
+    float *reds = rs + UPR * hc;       // [UPR][ld_red]
     if constexpr (FUSED) {
         const unsigned int seq_in = fuse_seq(fi);
         // what this mixer's down projection wrote of each row (an even count), as pairs of words; a thread has
@@ -152,9 +153,9 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
     __syncthreads();
     if (c >= SH) return;
     const unsigned int seq_out = FUSED ? fuse_seq(fo) : 0u;
-    float acc[UP_ROWS];
+    float acc[UPR];
 #pragma unroll
-    for (int mm = 0; mm < UP_ROWS; ++mm) acc[mm] = 0.f;
+    for (int mm = 0; mm < UPR; ++mm) acc[mm] = 0.f;
 #pragma unroll
     for (int i = 0; i < UP_MAXI; ++i) {
         const int ch = li + 8 * i;
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
             const float wf[8] = {bf16_lo(w[i].x), bf16_hi(w[i].x), bf16_lo(w[i].y), bf16_hi(w[i].y),
                                  bf16_lo(w[i].z), bf16_hi(w[i].z), bf16_lo(w[i].w), bf16_hi(w[i].w)};
 #pragma unroll
-            for (int mm = 0; mm < UP_ROWS; ++mm) {
+            for (int mm = 0; mm < UPR; ++mm) {
                 if (mm < nrow) {
                     const float *uu = u + mm * R + ch * 8;
 #pragma unroll
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(256, 3) hc_up_mix_kernel(const float *red, int
         }
     }
 #pragma unroll
-    for (int mm = 0; mm < UP_ROWS; ++mm) {
+    for (int mm = 0; mm < UPR; ++mm) {
         float g = acc[mm];
         g += __shfl_xor_sync(0xffffffffu, g, 1);
         g += __shfl_xor_sync(0xffffffffu, g, 2);
@@ -350,6 +351,8 @@ __global__ void __launch_bounds__(256, 3) hc_down_kernel(HcDownArgs a) {
 
 using namespace qw;
 
+QW_DCHECK_TU(hc)
+
 QW_API int qwk_embed_rows(const int *tokens, const void *table, int ld_table, int col0, int SH, int hc, int vocab,
                           float *X, int M, cudaStream_t s) {
     embed_rows_kernel<<<M, 256, 0, s>>>(tokens, (const bf16 *)table, ld_table, col0, SH, hc, vocab, X);
@@ -367,19 +370,32 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
                          int R, int n_inj, int H, float eps, int M, float *inj, int ld_inj, void *bin, int ld_bin,
                          int bin_col0, cudaStream_t s) {
     if (hc != 4 || (R & 7) || R > 8 * 8 * UP_MAXI) return -1;
-    dim3 grid((SH + 7) / 8, (M + UP_ROWS - 1) / UP_ROWS);
+    const int upr = M > UP_ROWS ? 2 * UP_ROWS : UP_ROWS;
+    dim3 grid((SH + 7) / 8, (M + upr - 1) / upr);
     const FuseIn fi = take_fi();
-    const size_t smem = sizeof(float) * (UP_ROWS * R + UP_ROWS * hc + UP_ROWS * ld_red);
-    if (smem > 48 * 1024) return -1;
+    const size_t smem = sizeof(float) * ((size_t)upr * R + upr * hc + (size_t)upr * ld_red);
+    if (smem > 96 * 1024) return -1;
+    {
+        static bool attr[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64) dev = 0;
+        if (!attr[dev]) {
+            cudaFuncSetAttribute(hc_up_mix_kernel<true, 2 * UP_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            cudaFuncSetAttribute(hc_up_mix_kernel<false, 2 * UP_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            attr[dev] = true;
+        }
+    }
+    if (upr == UP_ROWS && smem > 48 * 1024) return -1;
     const FuseOut fo = take_fo();
     if ((fi.active != 0) != (fo.mode != 0)) return -1;          // the fused mixer both receives and sends
     cudaError_t e;
-    if (fi.active)
-        e = launch_pdl(hc_up_mix_kernel<true>, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                       R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, fo);
-    else
-        e = launch_pdl(hc_up_mix_kernel<false>, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R,
-                       R + n_inj, 1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, fo);
+#define QW_UPMIX(F_, R_)                                                                                                        \
+    launch_pdl(hc_up_mix_kernel<F_, R_>, grid, dim3(256), smem, s, red, ld_red, (const bf16 *)Wu, X, w1, SH, hc, R, R + n_inj, \
+               1.f / float(H), eps, M, inj, ld_inj, (bf16 *)bin, ld_bin, bin_col0, take_pf(), fi, fo)
+    if (fi.active) e = upr == UP_ROWS ? QW_UPMIX(true, UP_ROWS) : QW_UPMIX(true, 2 * UP_ROWS);
+    else e = upr == UP_ROWS ? QW_UPMIX(false, UP_ROWS) : QW_UPMIX(false, 2 * UP_ROWS);
+#undef QW_UPMIX
     return e == cudaSuccess ? 0 : -2;
 }
 

@@ -195,6 +195,9 @@ __global__ void __launch_bounds__(256) qsa_prep_kernel(QsaPrepArgs a) {
     __shared__ float cs[2 * MAX_HALF];
     const int m = blockIdx.x, hb = blockIdx.y, d = threadIdx.x;
     const int slot = a.rows.slot[m], pos = a.rows.pos[m];
+    // a position beyond the slot's page table, or a page entry that is not a page (row m)
+    QW_DCHECK(slot >= 0 && pos >= 0 && pos / KV_PAGE < a.kv.max_pages, 0x02000000u | (unsigned)(m & 0xffffff));
+    QW_DCHECK(a.kv.page_table[(long long)slot * a.kv.max_pages + pos / KV_PAGE] >= 0, 0x03000000u | (unsigned)(m & 0xffffff));
     const float *row = a.proj + (long long)m * a.ld_proj;
     const int off_k = a.QL * 2 * HD, off_v = off_k + a.KVL * HD, off_iq = off_v + a.KVL * HD, off_raw = off_iq + a.IH * ID;
     if (hb < a.QL) {                                   // query head
@@ -529,6 +532,8 @@ __global__ void __launch_bounds__(256) qsa_combine_kernel(const float *pm, const
 }  // namespace qw
 
 using namespace qw;
+
+QW_DCHECK_TU(qsa)
 
 QW_API int qwk_rope_init(double theta, int rope_dim) {
     double inv[MAX_HALF];

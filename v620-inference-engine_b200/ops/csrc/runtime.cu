@@ -60,9 +60,24 @@ extern "C" __attribute__((visibility("default"))) int qwrt_set_fuse(int mode) {
 }
 
 // Registers the device error word (8 bytes, zeroed by the caller) that kernels with bounded waits report to.
+#ifdef QW_DEVICE_CHECKS
+extern "C" int qw_dcheck_set_hc(void *p);
+extern "C" int qw_dcheck_set_qsa(void *p);
+#endif
 extern "C" __attribute__((visibility("default"))) int qwk_set_error_word(void *p) {
     qw::g_err_ptr = (qw::ErrorWord *)p;
+#ifdef QW_DEVICE_CHECKS
+    if (qw_dcheck_set_hc(p) || qw_dcheck_set_qsa(p)) return -2;      // the checked kernels report to the same word
+#endif
     return 0;
+}
+// 1 in the checked build of the library (-DQW_DEVICE_CHECKS), 0 otherwise.
+extern "C" __attribute__((visibility("default"))) int qwk_device_checks(void) {
+#ifdef QW_DEVICE_CHECKS
+    return 1;
+#else
+    return 0;
+#endif
 }
 
 namespace {

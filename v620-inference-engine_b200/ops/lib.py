@@ -19,6 +19,7 @@ from typing import Dict, List, Optional
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libqw_kernels.so")
+CHECKED_LIB_PATH = os.path.join(HERE, "libqw_kernels_checked.so")      # the same sources with -DQW_DEVICE_CHECKS
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -35,23 +36,30 @@ def sources() -> List[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def want_checked() -> bool:
+    """QW_DEVICE_CHECKS=1 selects the bounds-checked build of the kernels."""
+    return os.environ.get("QW_DEVICE_CHECKS", "0").strip().lower() in ("1", "true", "on", "yes")
+
+
+def _stale(path: str = LIB_PATH) -> bool:
+    if not os.path.exists(path):
         return True
-    t = os.path.getmtime(LIB_PATH)
+    t = os.path.getmtime(path)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, jobs: int = 8) -> str:
-    """Compile every ``.cu`` to an object (in parallel) and link the shared library."""
-    if not force and not _stale():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, jobs: int = 8, checked: bool = False) -> str:
+    """Compile every ``.cu`` to an object (in parallel) and link the shared library (``checked``: the bounds-checked
+    variant, ``libqw_kernels_checked.so``)."""
+    out_path = CHECKED_LIB_PATH if checked else LIB_PATH
+    if not force and not _stale(out_path):
+        return out_path
     nvcc = nvcc_path()
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_checked" if checked else "build")
     os.makedirs(objdir, exist_ok=True)
     common = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
-                           "--expt-relaxed-constexpr", "-I", CSRC]
+                           "--expt-relaxed-constexpr", "-I", CSRC] + (["-DQW_DEVICE_CHECKS"] if checked else [])
     if verbose:
         common += ["-Xptxas", "-v"]
     procs, objs = [], []
@@ -71,13 +79,13 @@ def build(force: bool = False, verbose: bool = False, jobs: int = 8) -> str:
         log.append(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src}:\n{out}")
-    link = [nvcc] + ARCH_FLAGS + ["-shared", "-o", LIB_PATH] + objs
+    link = [nvcc] + ARCH_FLAGS + ["-shared", "-o", out_path] + objs
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout)
     if verbose:
         print("\n".join(log))
-    return LIB_PATH
+    return out_path
 
 
 _CTYPE = {
@@ -114,12 +122,13 @@ def load(required: Optional[bool] = None) -> Optional[ctypes.CDLL]:
             required = torch.cuda.is_available()
         except Exception:
             required = False
-    if not os.path.exists(LIB_PATH):
+    path = CHECKED_LIB_PATH if want_checked() else LIB_PATH
+    if not os.path.exists(path):
         if required:
-            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m qwb200.build` (the CUDA ops have no fallback)")
+            raise RuntimeError(f"{path} is missing: run `python -m qwb200.build` (the CUDA ops have no fallback)")
         return None
     try:
-        lib = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
     except OSError:
         if required:
             raise
