@@ -74,6 +74,76 @@ class StateIO:
                 off += n
         self.dm.spill_cache_clear()         # the page may live in host memory: cached copies of its rows are stale now
 
+    # ---- KV pages through pinned units: one gather launch + one asynchronous copy per block
+    MAX_BATCH = 8          # blocks moved per call (a 2,048-token prefill piece)
+
+    def _ensure_staging(self):
+        if getattr(self, "stage", None) is not None:
+            return
+        dm = self.dm
+        nseg = self.MAX_BATCH * 3 * len(dm.k_dev)
+        self.stage = torch.zeros(self.MAX_BATCH * self.kv_block_bytes, dtype=torch.uint8, device=dm.dev)
+        self.tab_host = torch.zeros(3 * nseg, dtype=torch.int64).pin_memory()       # src | dst | bytes
+        self.tab_dev = torch.zeros(3 * nseg, dtype=torch.int64, device=dm.dev)
+        self.nseg_max = nseg
+
+    def _segments(self, slot: int, page_indices, to_stage: bool):
+        """Fill the segment tables for moving the given pages between the slot state and the staging buffer."""
+        import ctypes as C
+        self._ensure_staging()
+        assert len(page_indices) <= self.MAX_BATCH
+        if getattr(self, "tab_event", None) is not None:
+            self.tab_event.synchronize()          # the previous call's copy of the tables has run
+        tab = self.tab_host.numpy()
+        n, base = 0, self.stage.data_ptr()
+        for b, pi in enumerate(page_indices):
+            off = b * self.kv_block_bytes
+            for k, v, ck in self._page_views(slot, pi):
+                for t in (k, v, ck):
+                    nb = t.numel() * 2
+                    state, st = t.data_ptr(), base + off
+                    tab[n], tab[self.nseg_max + n], tab[2 * self.nseg_max + n] = (state, st, nb) if to_stage else (st, state, nb)
+                    off += nb
+                    n += 1
+        self.tab_dev.copy_(self.tab_host, non_blocking=True)
+        self.tab_event = torch.cuda.Event()
+        self.tab_event.record(torch.cuda.current_stream(self.dm.dev))
+        s = C.c_void_p(torch.cuda.current_stream(self.dm.dev).cuda_stream)
+        p = self.tab_dev.data_ptr()
+        return n, C.c_void_p(p), C.c_void_p(p + 8 * self.nseg_max), C.c_void_p(p + 16 * self.nseg_max), s
+
+    def export_kv_units(self, slot: int, page_indices, units) -> None:
+        """Enqueue the export of the given pages, block i into ``units[i]`` (uint8 arrays over pinned host memory of at
+        least ``kv_block_bytes``).  Asynchronous: ``sync()`` before the units are read."""
+        import ctypes as C
+        n, src, dst, nb, s = self._segments(slot, page_indices, True)
+        L = self.dm.lib
+        if L.qwk_segments_copy(src, dst, nb, n, s) != 0:
+            raise RuntimeError("qwk_segments_copy failed")
+        for b, u in enumerate(units):
+            if L.qwk_memcpy_async(C.c_void_p(u.ctypes.data), C.c_void_p(self.stage.data_ptr() + b * self.kv_block_bytes),
+                                  self.kv_block_bytes, 2, s) != 0:
+                raise RuntimeError("qwk_memcpy_async failed")
+
+    def import_kv_units(self, slot: int, page_indices, units) -> None:
+        """The reverse: ``units[i]`` holds the payload of page ``page_indices[i]``.  Asynchronous on the current stream (the
+        units must stay untouched until ``sync()``)."""
+        import ctypes as C
+        L = self.dm.lib
+        s = C.c_void_p(torch.cuda.current_stream(self.dm.dev).cuda_stream)
+        self._ensure_staging()
+        for b, u in enumerate(units):
+            if L.qwk_memcpy_async(C.c_void_p(self.stage.data_ptr() + b * self.kv_block_bytes), C.c_void_p(u.ctypes.data),
+                                  self.kv_block_bytes, 1, s) != 0:
+                raise RuntimeError("qwk_memcpy_async failed")
+        n, src, dst, nb, s = self._segments(slot, page_indices, False)
+        if L.qwk_segments_copy(src, dst, nb, n, s) != 0:
+            raise RuntimeError("qwk_segments_copy failed")
+        self.dm.spill_cache_clear()
+
+    def sync(self) -> None:
+        torch.cuda.current_stream(self.dm.dev).synchronize()
+
     # ---- recurrent state
     def _recurrent_tensors(self, slot: int) -> List[torch.Tensor]:
         dm = self.dm

@@ -142,6 +142,20 @@ class BlockStore:
         buf = (C.c_char * len(kv)).from_buffer_copy(kv)
         return lib().qwh_store_save_block(self.s, parent, start, t.ctypes.data, len(t), C.addressof(buf), len(kv))
 
+    def save_block_from(self, parent: int, start: int, tokens: Sequence[int], addr: int, nbytes: int) -> int:
+        """``save_block`` with the payload given by address (a pinned unit the engine exported into): no intermediate copy."""
+        t = _i32(tokens)
+        return lib().qwh_store_save_block(self.s, parent, start, t.ctypes.data, len(t), addr, nbytes)
+
+    def get_into(self, key: int, out: np.ndarray) -> int:
+        """Copy a block's KV payload into ``out`` (uint8, e.g. a pinned unit).  Returns its size, or -1 when it is gone."""
+        nl = C.c_int(0)
+        size = lib().qwh_store_get(self.s, key, 0, None, 0, None, 0, C.byref(nl))
+        if size < 0 or size > out.nbytes:
+            return -1
+        lib().qwh_store_get(self.s, key, 0, out.ctypes.data, size, None, 0, C.byref(nl))
+        return int(size)
+
     def save_snapshot(self, key: int, snap: bytes, logits: Optional[np.ndarray] = None, anchor: bool = False) -> bool:
         buf = (C.c_char * len(snap)).from_buffer_copy(snap)
         lg = None if logits is None else np.ascontiguousarray(logits, dtype=np.float32)

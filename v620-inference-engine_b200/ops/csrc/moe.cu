@@ -383,19 +383,7 @@ QW_API int qwk_moe_gate_up_pair(const void *w13, const void *s13, const void *x,
         if (dev < 0 || dev >= 64) dev = 0;
         if (!attr[dev]) {
             cudaFuncSetAttribute(moe_gate_up_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-            cudaFuncSetAttribute(moe_gate_up_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
             attr[dev] = true;
-        }
-        // many pairs (several rows): blocks keep their column tile and walk the pairs through a two-stage ring
-        const size_t stage = 2 * 16 * ((size_t)(K >> 1) + TM_PAD) + 2 * 16 * ks * 2 + 16 + (size_t)(K >> 3) * 16;
-        const size_t ring_smem = 128 + 16 * 2 * 16 * sizeof(float) + 2 * stage;
-        if (M * top_k >= 30 && ring_smem <= 112 * 1024) {
-            int groups = (2 * NUM_SMS + F / 16 - 1) / (F / 16);
-            if (groups > M * top_k) groups = M * top_k;
-            cudaError_t e = launch_pdl(moe_gate_up_ring_kernel, dim3(F / 16, groups + extra), dim3(512), ring_smem, s, (const uint32_t *)w13,
-                                       (const bf16 *)s13, (const bf16 *)x, ldx, pair_expert, top_k, F, K, (bf16 *)h, g_err_ptr, sa, M * top_k,
-                                       groups);
-            return e == cudaSuccess ? 0 : -2;
         }
         if (smem <= 100 * 1024) {
             cudaError_t e = launch_pdl(moe_gate_up_tma_kernel, dim3(F / 16, M * top_k + extra), dim3(512), smem, s, (const uint32_t *)w13,

@@ -361,114 +361,6 @@ __global__ void __launch_bounds__(512) moe_gate_up_tma_kernel(const uint32_t *w1
     }
 }
 
-// The same product for steps with many pairs (several rows: speculative verification, concurrent streams): instead of
-// one block per (16-column tile, pair) - whose copy, wait and product run one after the other, wave after wave - a
-// block keeps its column tile and walks the pairs p = blockIdx.y, blockIdx.y + groups, ... through a two-stage ring: the
-// copies of the next pair's weight rows are in flight while the tensor cores work on the current one.
-// grid (F / 16, groups [+ M extra rows for the shared activation]), 512 threads; pairs of other ranks' experts are skipped.
-__global__ void __launch_bounds__(512) moe_gate_up_ring_kernel(const uint32_t *w13, const bf16 *s13, const bf16 *x, int ldx,
-                                                               const int *pair_expert, int top_k, int F, int K, bf16 *h, ErrorWord *err,
-                                                               SharedAct sa, int npairs, int groups) {
-    extern __shared__ __align__(128) unsigned char tm_smem[];
-    const int rowb = K >> 1, srow = rowb + TM_PAD, ks = K >> 7, wpr = K >> 3;
-    uint64_t *bar = reinterpret_cast<uint64_t *>(tm_smem);                      // [2]
-    float *red = reinterpret_cast<float *>(tm_smem + 128);                      // [16 warps][2][16]
-    const size_t stage_bytes = (size_t)2 * 16 * srow + (size_t)2 * 16 * ks * 2 + 16 + (size_t)wpr * 16;
-    unsigned char *stages = tm_smem + 128 + 16 * 2 * 16 * sizeof(float);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) {
-        mbar_init(bar, 1);
-        mbar_init(bar + 1, 1);
-        mbar_fence_init();
-    }
-    pdl_wait();
-    pdl_trigger();
-    if ((int)blockIdx.y >= groups) {          // the extra rows of the grid: the shared expert's activation
-        if (blockIdx.x == 0) shared_act_row(sa, blockIdx.y - groups);
-        return;
-    }
-    const int f0 = blockIdx.x * 16;
-    auto next_local = [&](int p) {            // the first pair at or after p (in steps of `groups`) whose expert is on this rank
-        while (p < npairs && pair_expert[p] < 0) p += groups;
-        return p;
-    };
-    // stage s holds: gate rows [16][srow] | up rows [16][srow] | gate scales | up scales | the token's activations
-    auto issue = [&](int p, int st) {
-        unsigned char *wg = stages + st * stage_bytes, *wu = wg + 16 * srow;
-        bf16 *sg = reinterpret_cast<bf16 *>(wu + 16 * srow), *su = sg + 16 * ks;
-        uint4 *xs = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(su + 16 * ks) + ((-(16 * ks * 4)) & 15));
-        const int e = pair_expert[p];
-        const long long row_g = (long long)e * 2 * F + f0, row_u = row_g + F;
-        if (warp == 0) {
-            if (lane == 0) mbar_expect_tx(bar + st, (unsigned)(32 * rowb + 2 * 16 * ks * 2));
-            __syncwarp();
-            if (lane < 16) bulk_g2s(wg + lane * srow, w13 + (row_g + lane) * wpr, (unsigned)rowb, bar + st);
-            else bulk_g2s(wu + (lane - 16) * srow, w13 + (row_u + lane - 16) * wpr, (unsigned)rowb, bar + st);
-            if (lane == 0) bulk_g2s(sg, s13 + row_g * ks, (unsigned)(16 * ks * 2), bar + st);
-            if (lane == 1) bulk_g2s(su, s13 + row_u * ks, (unsigned)(16 * ks * 2), bar + st);
-        }
-        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (long long)(p / top_k) * ldx);
-        for (int i = tid; i < wpr; i += 512) xs[i] = __ldcg(xr + i);
-    };
-    __syncthreads();                          // the barriers are initialised
-    int p = next_local(blockIdx.y);
-    if (p >= npairs) return;
-    issue(p, 0);
-    const int r = lane >> 2, q = lane & 3;
-    for (int it = 0; p < npairs; ++it) {
-        const int st = it & 1;
-        const int pn = next_local(p + groups);
-        // the other stage was read in the previous round, which ended with a block-wide barrier: refill it
-        if (pn < npairs) issue(pn, st ^ 1);
-        __syncthreads();                      // this stage's activations (plain stores of round it - 1 or of the prologue)
-        const bool ok = mbar_wait(bar + st, (unsigned)(it >> 1) & 1u, err);
-        unsigned char *wg = stages + st * stage_bytes, *wu = wg + 16 * srow;
-        bf16 *sg = reinterpret_cast<bf16 *>(wu + 16 * srow), *su = sg + 16 * ks;
-        const uint4 *xs = reinterpret_cast<const uint4 *>(reinterpret_cast<unsigned char *>(su + 16 * ks) + ((-(16 * ks * 4)) & 15));
-        float ag = 0.f, ag8 = 0.f, au = 0.f, au8 = 0.f;
-        if (ok) {
-            for (int g = warp; g < ks; g += 16) {
-                float cg[4] = {0.f, 0.f, 0.f, 0.f}, cu[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int ds = 0; ds < 2; ++ds) {
-                    const int wi = g * 16 + ds * 8 + 2 * q;
-                    const uint2 a0 = *reinterpret_cast<const uint2 *>(wg + r * srow + wi * 4), a8 = *reinterpret_cast<const uint2 *>(wg + (r + 8) * srow + wi * 4);
-                    const uint2 b0 = *reinterpret_cast<const uint2 *>(wu + r * srow + wi * 4), b8 = *reinterpret_cast<const uint2 *>(wu + (r + 8) * srow + wi * 4);
-                    uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
-                    if (r == 0) {                                               // column 0 of the narrow operand is the token
-                        x0 = xs[wi];
-                        x1 = xs[wi + 1];
-                    }
-                    mma_q4_word(cg, a0.x, a8.x, x0);
-                    mma_q4_word(cg, a0.y, a8.y, x1);
-                    mma_q4_word(cu, b0.x, b8.x, x0);
-                    mma_q4_word(cu, b0.y, b8.y, x1);
-                }
-                if (q == 0) {
-                    ag = fmaf(__bfloat162float(sg[r * ks + g]), cg[0], ag);
-                    ag8 = fmaf(__bfloat162float(sg[(r + 8) * ks + g]), cg[2], ag8);
-                    au = fmaf(__bfloat162float(su[r * ks + g]), cu[0], au);
-                    au8 = fmaf(__bfloat162float(su[(r + 8) * ks + g]), cu[2], au8);
-                }
-            }
-        }
-        if (q == 0) {
-            red[(warp * 2 + 0) * 16 + r] = ag; red[(warp * 2 + 0) * 16 + r + 8] = ag8;
-            red[(warp * 2 + 1) * 16 + r] = au; red[(warp * 2 + 1) * 16 + r + 8] = au8;
-        }
-        __syncthreads();
-        if (tid < 16) {
-            float gs = 0.f, us = 0.f;
-#pragma unroll
-            for (int w = 0; w < 16; ++w) { gs += red[(w * 2) * 16 + tid]; us += red[(w * 2 + 1) * 16 + tid]; }
-            h[(long long)p * F + f0 + tid] = __float2bfloat16(siluf_(gs) * us);
-        }
-        __syncthreads();                      // `red` and this stage are free again
-        if (!ok) return;
-        p = pn;
-    }
-}
-
 // grid (H / 16, M), 512 threads.  Shared memory: barrier(s) | top_k expert tiles [16][F/2 + pad] | shared tile
 // [16][SF*2 + pad] | scales [top_k][16][F/128] | h vectors | shared activation | reduction scratch.
 template <bool FUSED>

@@ -89,6 +89,14 @@ class Session:
         self.boundary = -1
         self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
         self.store = H.BlockStore(self.io.state_layout_id(), engine.dm.sc.ranks, host_cache_bytes, disk_cache_dir, disk_cache_bytes)
+        # pinned units for the blocks on their way between the engine and the store (one block per unit)
+        self.pool = None
+        if torch.cuda.is_available():
+            try:
+                self.pool = H.PinnedPool(self.io.kv_block_bytes, arena_bytes=max(64 << 20, 16 * self.io.kv_block_bytes), standing_units=2,
+                                         use_cuda=True)
+            except Exception:
+                self.pool = None          # no pinned memory to be had: blocks take the pageable path
         self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.cfg.vocab, n, engine.opts.max_rows, seed)
         self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
         self.seen_chunks = set()
@@ -167,12 +175,30 @@ class Session:
         if depth == 0:
             return 0
         ok = True
-        for bi, key in enumerate(path[:depth]):
-            kv = self.store.get(key)
-            if kv is None or len(kv) != self.io.kv_block_bytes:
-                ok = False
-                break
-            self.io.import_kv(slot, bi, kv)
+        if self.pool is not None:
+            # blocks travel through pinned units, eight at a time: one copy and one scatter launch per block, one wait per batch
+            for b0 in range(0, depth, self.io.MAX_BATCH):
+                idx = list(range(b0, min(depth, b0 + self.io.MAX_BATCH)))
+                units = [self.pool.get() for _ in idx]
+                try:
+                    for u, bi in zip(units, idx):
+                        if self.store.get_into(path[bi], u) != self.io.kv_block_bytes:
+                            ok = False
+                    if ok:
+                        self.io.import_kv_units(slot, idx, units)
+                        self.io.sync()
+                finally:
+                    for u in units:
+                        self.pool.put(u)
+                if not ok:
+                    break
+        else:
+            for bi, key in enumerate(path[:depth]):
+                kv = self.store.get(key)
+                if kv is None or len(kv) != self.io.kv_block_bytes:
+                    ok = False
+                    break
+                self.io.import_kv(slot, bi, kv)
         snap = self.store.get(path[depth - 1], snapshot=True) if ok else None
         if not ok or snap is None or len(snap[0]) != self.io.recurrent_bytes():
             self.e.reset(slot)           # a payload vanished (budget) or does not fit: recompute
@@ -222,13 +248,38 @@ class Session:
         t0 = time.time()
         full = sl.n // BLOCK
         parent = si.block_keys[-1] if si.block_keys else self.store.root
-        for bi in range(len(si.block_keys), full):
-            toks = sl.tokens[bi * BLOCK:(bi + 1) * BLOCK]
-            key = self.store.save_block(parent, bi * BLOCK, toks, self.io.export_kv(slot, bi))
-            if key == 0:
-                break
-            si.block_keys.append(key)
-            parent = key
+        first = len(si.block_keys)
+        if self.pool is not None:
+            stop = False
+            for b0 in range(first, full, self.io.MAX_BATCH):
+                idx = list(range(b0, min(full, b0 + self.io.MAX_BATCH)))
+                tw = time.time()
+                units = [self.pool.get() for _ in idx]
+                si.timing["pin_wait_s"] += time.time() - tw
+                try:
+                    self.io.export_kv_units(slot, idx, units)
+                    self.io.sync()
+                    for u, bi in zip(units, idx):
+                        key = self.store.save_block_from(parent, bi * BLOCK, sl.tokens[bi * BLOCK:(bi + 1) * BLOCK], u.ctypes.data,
+                                                         self.io.kv_block_bytes)
+                        if key == 0:
+                            stop = True
+                            break
+                        si.block_keys.append(key)
+                        parent = key
+                finally:
+                    for u in units:
+                        self.pool.put(u)
+                if stop:
+                    break
+        else:
+            for bi in range(first, full):
+                toks = sl.tokens[bi * BLOCK:(bi + 1) * BLOCK]
+                key = self.store.save_block(parent, bi * BLOCK, toks, self.io.export_kv(slot, bi))
+                if key == 0:
+                    break
+                si.block_keys.append(key)
+                parent = key
         if snapshot and si.block_keys and len(si.block_keys) * BLOCK == sl.n:
             anchor = sl.n < len(si.prompt) and si.prompt[sl.n] == self.boundary
             self.store.save_snapshot(si.block_keys[-1], self.io.export_recurrent(slot), None, anchor)
