@@ -160,7 +160,8 @@ class FakeEngine:
 
 
 def make_server(reply_text=None, reply=None, **kw):
-    """(server, scheduler, engine, prompter); the scheduler thread is started, the watchdog is not."""
+    """(server, scheduler, engine, prompter); the scheduler thread is started (unless ``start=False``: the test drives the
+    scheduler's steps by hand), the watchdog is not."""
     from qwserve.api import Server
     from qwserve.scheduler import Scheduler
     pr = make_prompter()
@@ -171,5 +172,6 @@ def make_server(reply_text=None, reply=None, **kw):
     sched = Scheduler(eng, drafts=kw.get("drafts", 0), prefill_piece=kw.get("piece", 2048), stuck_seconds=kw.get("stuck_seconds", 300.0),
                       log=kw.get("log", lambda *_: None))
     srv = Server(eng, pr, sched, "qw-test", default_budget=kw.get("default_budget", 0))
-    sched.start(watchdog=False)
+    if kw.get("start", True):
+        sched.start(watchdog=False)
     return srv, sched, eng, pr

@@ -176,3 +176,28 @@ def test_pinned_pool_units_reserve_retire_and_wait_accounting():
         small.put(np.zeros(4096, np.uint8))                # not one of this pool's units
     pool.close()
     small.close()
+
+
+def test_block_store_prefetch_loads_disk_blocks_in_the_background(tmp_path):
+    """After a restart the index knows the blocks but their payloads are only on disk; ``prefetch`` queues reads on the
+    loader thread and ``loads_pending`` drops to zero with the payloads (and the last snapshot) back in RAM."""
+    import time
+    st = H.BlockStore(1, 1, 64 << 20, str(tmp_path), 1 << 30)
+    toks = list(range(768))
+    keys, parent = [], st.root
+    for b in range(3):
+        parent = st.save_block(parent, b * 256, toks[b * 256:(b + 1) * 256], bytes([65 + b]) * 8192)
+        keys.append(parent)
+    assert st.save_snapshot(keys[-1], b"s" * 256)
+    st.flush()
+    del st
+    st = H.BlockStore(1, 1, 64 << 20, str(tmp_path), 1 << 30)
+    path, depth = st.lookup(toks + [5])
+    assert depth == 3 and not any(st.info(k)["in_ram"] for k in path[:3])
+    assert st.prefetch(path[:depth]) == 4                  # three KV payloads and the last block's snapshot
+    t0 = time.time()
+    while st.loads_pending() and time.time() - t0 < 10:
+        time.sleep(0.01)
+    assert st.loads_pending() == 0 and all(st.info(k)["in_ram"] for k in path[:3])
+    assert st.prefetch(path[:depth]) == 0                  # nothing left to read
+    assert st.get(path[1]) == bytes([66]) * 8192

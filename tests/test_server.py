@@ -329,3 +329,28 @@ def test_metrics_rings_and_fake_nvml():
         def nvmlDeviceGetClockInfo(self, h, k): return 1900
     g = Gpus(Nv()).sample()
     assert len(g) == 2 and g[1]["power_w"] == 700.0 and g[0]["mem_used_gb"] == 2.0
+
+
+def test_request_sharing_a_long_prefix_waits_for_the_one_in_flight():
+    """Two prompts with the same first 1,024 tokens: the second is not admitted while the first is still prefilling, so it
+    finds the shared part in the prefix cache; an unrelated prompt is admitted at once."""
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(8192, 8192, 8192), step_seconds=0.002, start=False)
+    shared = [65 + (i % 20) for i in range(1500)]
+    a = Request(tokens=Tokens(shared + [70] * 3000), max_new=4, sampling=Sampling(), stop_ids=[eng.eos])
+    b = Request(tokens=Tokens(shared + [71] * 10), max_new=4, sampling=Sampling(), stop_ids=[eng.eos])
+    c = Request(tokens=Tokens([90] * 1200), max_new=4, sampling=Sampling(), stop_ids=[eng.eos])
+    for r in (a, b, c):
+        r.in_think = False
+        sched.waiting.append(r)
+    sched._admit()
+    assert a.slot >= 0 and c.slot >= 0 and b.slot < 0 and list(sched.waiting) == [b]
+    sched._prefill()                                   # one piece of each: `a` is still not in
+    assert not a.prefill_done
+    sched._admit()
+    assert b.slot < 0
+    while sched.prefilling:
+        sched._prefill()
+    sched._admit()
+    assert b.slot >= 0

@@ -86,6 +86,9 @@ class SessionOps:
     def begin_prompt(self, slot, toks):
         return self.s.begin_prompt(slot, toks)
 
+    def prefetch(self, toks):
+        return self.s.prefetch(toks)
+
     def prefill_some(self, slot, max_tokens):
         return bool(self.s.prefill_some(slot, max_tokens))
 
@@ -198,7 +201,9 @@ class CApi:
         return r
 
     def prefetch(self, slot, addr, n, media, n_media):
-        return 0            # the block store reads disk entries on demand during begin_prompt
+        """Queue background disk reads for the prompt's stored prefix; returns the number of reads still pending."""
+        self.ops.prefetch(self._tokens(addr, n, media, n_media))
+        return self.s.loads_pending()
 
     def prefill_batch(self, n, slots, max_tokens, done):
         sl = _i32(slots, n)

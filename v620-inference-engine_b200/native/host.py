@@ -43,7 +43,7 @@ def lib() -> C.CDLL:
             "qwh_store_save_snapshot": (I, [P, ULL, P, ULL, P, I, I]), "qwh_store_lookup": (I, [P, P, LL, P, I, P]),
             "qwh_store_get": (LL, [P, ULL, I, P, ULL, P, I, P]), "qwh_store_block_info": (I, [P, ULL, P, P, P, P, P]),
             "qwh_store_note_restore": (None, [P, ULL, LL]), "qwh_store_flush": (None, [P]), "qwh_store_thin": (I, [P, LL]),
-            "qwh_store_stats": (None, [P, P]),
+            "qwh_store_stats": (None, [P, P]), "qwh_store_prefetch": (I, [P, P, I, I]), "qwh_store_loads_pending": (I, [P]),
             "qwh_rng_new": (P, [ULL]), "qwh_rng_free": (None, [P]), "qwh_sample": (I, [P, I, P, P, LL, LL, P, P]),
             "qwh_top_logprobs": (I, [P, I, I, P, P]), "qwh_lse": (C.c_float, [P, I]),
             "qwh_chunk": (I, [P, LL, I, P, P, P, I]),
@@ -155,6 +155,17 @@ class BlockStore:
             return -1
         lib().qwh_store_get(self.s, key, 0, out.ctypes.data, size, None, 0, C.byref(nl))
         return int(size)
+
+    def prefetch(self, keys: Sequence[int], last_snapshot: bool = True) -> int:
+        """Queue background reads of the blocks' payloads that are only on disk (and of the last block's snapshot).  Returns
+        the number of reads queued; ``loads_pending()`` tells when they are done."""
+        if not keys:
+            return 0
+        arr = (C.c_ulonglong * len(keys))(*[int(k) for k in keys])
+        return int(lib().qwh_store_prefetch(self.s, arr, len(keys), int(last_snapshot)))
+
+    def loads_pending(self) -> int:
+        return int(lib().qwh_store_loads_pending(self.s))
 
     def save_snapshot(self, key: int, snap: bytes, logits: Optional[np.ndarray] = None, anchor: bool = False) -> bool:
         buf = (C.c_char * len(snap)).from_buffer_copy(snap)

@@ -94,6 +94,12 @@ public:
         }
         qcv_.notify_all();
         if (writer_.joinable()) writer_.join();
+        {
+            std::lock_guard<std::mutex> lk(lmu_);          // stop_ is read under either queue's mutex
+            loads_.clear();
+        }
+        lcv_.notify_all();
+        if (loader_.joinable()) loader_.join();
     }
 
     // Stores tokens [start, start+n) after `parent` with their KV payload; returns the block's key.
@@ -201,6 +207,32 @@ public:
         for (auto &kv : nodes_) s.snapshots += kv.second.has_snap ? 1 : 0;
         return s;
     }
+    // Background loads: the payloads (KV, and the snapshot when asked) of blocks that are only on disk are read into RAM
+    // by a loader thread, so that a later restore finds them there.  Returns how many reads were queued.
+    int prefetch(const uint64_t *keys, int n, bool last_snapshot) {
+        int queued = 0;
+        std::lock_guard<std::mutex> lk(lmu_);
+        for (int i = 0; i < n; ++i) {
+            bool kv_need = false, snap_need = false;
+            {
+                std::lock_guard<std::mutex> lk2(mu_);
+                auto it = nodes_.find(keys[i]);
+                if (it == nodes_.end()) continue;
+                const Node &nd = it->second;
+                kv_need = nd.kv.empty() && nd.kv_disk;
+                snap_need = last_snapshot && i == n - 1 && nd.snap.empty() && nd.snap_disk;
+            }
+            if (kv_need) { loads_.push_back({keys[i], false}); ++queued; }
+            if (snap_need) { loads_.push_back({keys[i], true}); ++queued; }
+        }
+        if (queued && !loader_.joinable()) loader_ = std::thread([this] { load_loop(); });
+        lcv_.notify_all();
+        return queued;
+    }
+    int loads_pending() {
+        std::lock_guard<std::mutex> lk(lmu_);
+        return int(loads_.size()) + (loading_ ? 1 : 0);
+    }
     // Waits until every queued disk write has been done.
     void flush() {
         std::unique_lock<std::mutex> lk(qmu_);
@@ -235,6 +267,26 @@ private:
         std::lock_guard<std::mutex> lk(qmu_);
         queue_.push_back({key, snap});
         qcv_.notify_all();
+    }
+    void load_loop() {
+        for (;;) {
+            std::pair<uint64_t, bool> job;
+            {
+                std::unique_lock<std::mutex> lk(lmu_);
+                lcv_.wait(lk, [&] { return stop_ || !loads_.empty(); });
+                if (stop_) return;
+                job = loads_.front();
+                loads_.pop_front();
+                loading_ = true;
+            }
+            std::vector<uint8_t> tmp;
+            std::vector<float> lg;
+            get(job.first, job.second, tmp, &lg);          // leaves the payload in RAM (subject to the budget)
+            {
+                std::lock_guard<std::mutex> lk(lmu_);
+                loading_ = false;
+            }
+        }
     }
     void write_loop() {
         for (;;) {
@@ -471,6 +523,12 @@ private:
     std::deque<std::pair<uint64_t, bool>> queue_;
     bool stop_ = false, writing_ = false;
     std::thread writer_;
+    // background loader
+    std::mutex lmu_;
+    std::condition_variable lcv_;
+    std::deque<std::pair<uint64_t, bool>> loads_;
+    bool loading_ = false;
+    std::thread loader_;
 };
 
 }  // namespace qwh

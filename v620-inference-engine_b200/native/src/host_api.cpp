@@ -105,6 +105,10 @@ API int qwh_store_block_info(void *s, unsigned long long key, long long *start, 
     return 0;
 }
 API void qwh_store_note_restore(void *s, unsigned long long key, long long tokens) { static_cast<BlockStore *>(s)->note_restore(key, tokens); }
+API int qwh_store_prefetch(void *s, const unsigned long long *keys, int n, int last_snapshot) {
+    return static_cast<BlockStore *>(s)->prefetch(reinterpret_cast<const uint64_t *>(keys), n, last_snapshot != 0);
+}
+API int qwh_store_loads_pending(void *s) { return static_cast<BlockStore *>(s)->loads_pending(); }
 API void qwh_store_flush(void *s) { static_cast<BlockStore *>(s)->flush(); }
 API int qwh_store_thin(void *s, long long gap) { return static_cast<BlockStore *>(s)->thin(gap); }
 API void qwh_store_stats(void *s, unsigned long long *out7) {

@@ -48,6 +48,7 @@ class Request:
     cancelled: bool = False
     no_slot: bool = False
     t_submit: float = field(default_factory=time.time)
+    load_deadline: float = 0.0          # until when the request waits for its stored prefix to be read from disk
     t_admit: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
@@ -67,11 +68,18 @@ class Request:
 
 class Scheduler:
     def __init__(self, engine, drafts: int = 0, prefill_piece: int = 2048, decode_share: float = 0.25, max_step: int = 16,
-                 stuck_seconds: float = 300.0, exit_grace: float = 30.0, log_interval: float = 30.0, log=print):
+                 stuck_seconds: float = 300.0, exit_grace: float = 30.0, log_interval: float = 30.0, log=print,
+                 share_min: int = 1024, share_wait: float = 30.0, load_wait: float = 30.0):
         self.e, self.k = engine, drafts if getattr(engine, "has_mtp", False) else 0
         self.piece, self.decode_share, self.max_step = prefill_piece, decode_share, max_step
         self.stuck_seconds, self.exit_grace, self.log = stuck_seconds, exit_grace, log
         self.log_interval, self._logged_at, self._logged_tokens = log_interval, time.time(), 0
+        # A request whose prompt shares at least `share_min` tokens with one that is being prefilled waits (at most `share_wait`
+        # seconds) until that one is in, so that it restores the shared part from the prefix cache instead of computing it
+        # a second time; blocks that are only on disk are read in the background for at most `load_wait` seconds before the
+        # prompt begins (QW_SHARE_MIN / QW_SHARE_WAIT of the reference's scheduler, server/qwserve/scheduler.py:315-398).
+        self.share_min, self.share_wait, self.load_wait = share_min, share_wait, load_wait
+        self.loading: List[Request] = []
         self.inbox: "queue.Queue[Request]" = queue.Queue()
         self.waiting: Deque[Request] = collections.deque()
         self.prefilling: List[Request] = []
@@ -107,7 +115,7 @@ class Scheduler:
         return self._cache_stats
 
     def counts(self) -> dict:
-        return {"waiting": len(self.waiting) + self.inbox.qsize(), "prefilling": len(self.prefilling), "running": len(self.running),
+        return {"waiting": len(self.waiting) + self.inbox.qsize(), "prefilling": len(self.prefilling) + len(self.loading), "running": len(self.running),
                 **{k: self.stats[k] for k in ("completed", "failed", "tokens", "steps")}, "step_ms": 1e3 * self.stats.get("step_s", 0.0)}
 
     def shutdown(self):
@@ -159,6 +167,7 @@ class Scheduler:
                 self._stats_line()
             busy = self._drain_inbox()
             busy |= self._admit()
+            busy |= self._poll_loads()
             t0 = time.time()
             busy |= self._prefill()
             spent = time.time() - t0
@@ -229,6 +238,9 @@ class Scheduler:
             if r.no_slot and not retry:                   # it found no slot before and none was released since
                 keep.append(r)
                 continue
+            if self._shares_prefix_in_flight(r):
+                keep.append(r)
+                continue
             try:
                 slot = self._call(self.e.acquire, r.tokens, r.max_new, r.media)
             except Exception as ex:                       # this request fails alone
@@ -239,16 +251,66 @@ class Scheduler:
                 keep.append(r)                            # no slot for it now: later arrivals may still fit
                 continue
             r.slot, r.t_admit = slot, time.time()
-            try:
-                r.reused = self._call(self.e.begin_prompt, slot, r.tokens, r.media)
-                self._call(self.e.set_stop_tokens, slot, r.stop_ids)
-            except Exception as ex:
-                self._fail(r, str(ex))
+            pending = False
+            if hasattr(self.e, "prefetch"):
+                try:
+                    pending = bool(self._call(self.e.prefetch, slot, r.tokens, r.media))
+                except Exception:
+                    pending = False                       # a failed read-ahead only costs the time it would have saved
+            if pending:
+                r.load_deadline = time.time() + self.load_wait
+                self.loading.append(r)
+                admitted = True
                 continue
-            self.prefilling.append(r)
-            admitted = True
+            admitted = self._begin(r) or admitted
         self.waiting = keep
         return admitted
+
+    def _begin(self, r: "Request") -> bool:
+        try:
+            r.reused = self._call(self.e.begin_prompt, r.slot, r.tokens, r.media)
+            self._call(self.e.set_stop_tokens, r.slot, r.stop_ids)
+        except Exception as ex:
+            self._fail(r, str(ex))
+            return False
+        self.prefilling.append(r)
+        return True
+
+    def _poll_loads(self) -> bool:
+        """Requests whose stored prefix is being read from disk begin once the reads are done (or took too long)."""
+        if not self.loading:
+            return False
+        still, began = [], False
+        for r in self.loading:
+            if r.cancelled:
+                self._call(self.e.release, r.slot)
+                self.released = True
+                r.finish = "abort"
+                if r.on_done:
+                    r.on_done("abort")
+                continue
+            try:
+                pending = bool(self._call(self.e.prefetch, r.slot, r.tokens, r.media)) and time.time() < r.load_deadline
+            except Exception:
+                pending = False
+            if pending:
+                still.append(r)
+            else:
+                began = self._begin(r) or began
+        self.loading = still
+        return began
+
+    def _shares_prefix_in_flight(self, r: "Request") -> bool:
+        if self.share_min <= 0 or not self.prefilling or time.time() - r.t_submit > self.share_wait:
+            return False
+        n = len(r.tokens)
+        if n < self.share_min:
+            return False
+        for p in self.prefilling:
+            m = min(n, len(p.tokens))
+            if m >= self.share_min and r.tokens[:self.share_min] == p.tokens[:self.share_min]:
+                return True
+        return False
 
     def _prefill(self) -> bool:
         if not self.prefilling:

@@ -213,6 +213,17 @@ class Session:
         self.sampler.note_tokens(slot, toks[:stored], generated=False)
         return stored
 
+    def prefetch(self, tokens: Sequence[int]) -> int:
+        """Start reading, in the background, the stored blocks on the prompt's path that are only on disk, so that
+        ``begin_prompt`` finds them in memory (reference: Session::prefetch, src/session/prefix_cache.cpp:34-39 and the
+        load workers of src/session/block_store.cpp:312-339).  Returns the number of reads queued."""
+        toks = [int(t) for t in tokens]
+        path, depth = self.store.lookup(toks[:max(0, len(toks) - 1)])
+        return self.store.prefetch(path[:depth], last_snapshot=True) if depth else 0
+
+    def loads_pending(self) -> int:
+        return self.store.loads_pending()
+
     def sampler_sync(self, slot: int, tokens: Sequence[int], prompt_end: int) -> None:
         self.sampler.reset_slot(slot)
         self.sampler.note_tokens(slot, tokens[:prompt_end], generated=False)
