@@ -180,3 +180,46 @@ def test_forced_acceptance_keeps_the_slot_consistent():
         eng.decode([s], [pend[i]])
         got = eng.dm.buf["logits"][0]
         assert float((got - want).abs().max() / want.abs().max()) < 3e-2, i
+
+
+def test_device_snapshots_at_prompt_end_and_message_boundaries():
+    """A slot that has generated past its prompt goes back to the device snapshot taken at the prompt's end when the same
+    prompt comes again (regenerate) or comes with a different last message: the reused length is the snapshot's position,
+    not the last stored block's, and what follows equals a computation from scratch."""
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session.session import StepReq
+    cfg, eng, ses = make(None, slots=1)
+    ses.snap_min_gap = 256
+    boundary = 999
+    ses.set_boundary_token(boundary)
+    sys_msg = [t if t != boundary else 5 for t in prompt_of(cfg, 330, 51)]
+    msg1 = [boundary] + [t if t != boundary else 6 for t in prompt_of(cfg, 90, 52)]
+    p1 = sys_msg + msg1
+    s = ses.acquire(p1, 32)
+    assert ses.begin_prompt(s, p1) == 0
+    while not ses.prefill_some(s, 4096):
+        pass
+    # captures: at the message boundary (position 330, not a block boundary) and at the prompt's end
+    assert sorted(v.n for v in ses.vram_snaps) == [330, len(p1)]
+    first, _ = ses.sample_prompt(s, SamplingParams())
+    pending = first
+    for _ in range(3):
+        pending = ses.generate([StepReq(s, pending, 8, 0, SamplingParams())], k=2)[0].tokens[-1]
+    ses.release(s)
+    # the same prompt again: everything is reused, the first token is the same
+    assert ses.acquire(p1, 32) == s and ses.begin_prompt(s, p1) == len(p1)
+    assert ses.prefill_some(s, 4096)
+    again, _ = ses.sample_prompt(s, SamplingParams())
+    assert again == first
+    ses.release(s)
+    # the system prompt with a different message: back to the boundary snapshot (330 > the 256 tokens the store holds)
+    msg2 = [boundary] + [t if t != boundary else 7 for t in prompt_of(cfg, 70, 53)]
+    p2 = sys_msg + msg2
+    assert ses.acquire(p2, 32) == s and ses.begin_prompt(s, p2) == 330
+    while not ses.prefill_some(s, 4096):
+        pass
+    got = ses.slots[s].logits.clone()
+    _, e2, s2 = make(None, slots=1)
+    e2.prefill(0, p2)
+    want = e2.dm.buf["logits"][0]
+    assert float((got - want).abs().max() / want.abs().max()) < 3e-2

@@ -29,6 +29,20 @@ from ..native import host as H
 
 BLOCK = 256
 SPEC_BASE, SPEC_BETA = 1.25, 0.25
+VRAM_SNAPSHOTS = 8          # recurrent-state snapshots kept on the device, least recently used first out
+
+
+@dataclass
+class VramSnap:
+    """The recurrent state of a slot as it was after its first ``n`` tokens, kept on the device.  The slot's KV rows of
+    those tokens stay where they are, so going back to the snapshot costs a few device copies (reference: the snapshot
+    table of src/session/session.cpp:37-54 and src/engine/snapshot.hip:19-71)."""
+    slot: int
+    n: int
+    tensors: list
+    mtp_hidden: Optional[torch.Tensor]
+    logits: Optional[torch.Tensor]
+    used: int = 0
 
 
 @dataclass
@@ -43,6 +57,7 @@ class SlotInfo:
     drafts: List[int] = field(default_factory=list)
     drafts_for: int = -1
     block_keys: List[int] = field(default_factory=list)   # store keys of the slot's full blocks, in order
+    last_capture: int = 0                                 # position of the newest device snapshot taken during this prompt
     timing: Dict[str, float] = field(default_factory=lambda: {"restore_s": 0.0, "prefill_s": 0.0, "save_s": 0.0, "pin_wait_s": 0.0})
 
 
@@ -98,6 +113,8 @@ class Session:
             except Exception:
                 self.pool = None          # no pinned memory to be had: blocks take the pageable path
         self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.cfg.vocab, n, engine.opts.max_rows, seed)
+        self.vram_snaps: List[VramSnap] = []
+        self.snap_min_gap = max(BLOCK, int(_settings.get().snap_min_gap))
         self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
         self.seen_chunks = set()
         self.last_rows: Optional[torch.Tensor] = None        # logits of the last decode / generate rows
@@ -161,14 +178,25 @@ class Session:
             if hs in self.seen_chunks:
                 self.blend_candidate_tokens += ln
             self.seen_chunks.add(hs)
+        # four ways to start (reference: begin_keys, src/session/session.cpp:214-312): continue what the slot holds, go back to
+        # a device snapshot of this slot, restore the longest stored prefix, or start from nothing - whichever keeps most
         keep = self.reusable(slot, toks)
         t0 = time.time()
         path, depth = self.store.lookup(toks[:max(0, len(toks) - 1)])      # at least one token is left to prefill
         stored = depth * BLOCK
+        snap = self._best_vram_snapshot(slot, toks)
+        si.last_capture = 0
+        if snap is not None and snap.n > max(keep, stored):
+            self._restore_vram_snapshot(slot, snap, toks)
+            self.reused_tokens += snap.n
+            si.last_capture = snap.n
+            return snap.n
         if keep >= stored and keep > 0:
             self.reused_tokens += keep
             self.sampler_sync(slot, toks[:keep], keep)
+            si.last_capture = keep
             return keep
+        self._drop_vram_snapshots(slot)
         self.e.reset(slot)
         si.block_keys = []
         self.sampler.reset_slot(slot)
@@ -213,6 +241,59 @@ class Session:
         self.sampler.note_tokens(slot, toks[:stored], generated=False)
         return stored
 
+    # ---- device snapshots
+    def _drop_vram_snapshots(self, slot: int) -> None:
+        self.vram_snaps = [v for v in self.vram_snaps if v.slot != slot]
+
+    def _take_vram_snapshot(self, slot: int, logits: Optional[torch.Tensor] = None) -> None:
+        sl = self.e.slot[slot]
+        self.vram_snaps = [v for v in self.vram_snaps if not (v.slot == slot and v.n == sl.n)]
+        if len(self.vram_snaps) >= VRAM_SNAPSHOTS:
+            self.vram_snaps.remove(min(self.vram_snaps, key=lambda v: v.used))
+        self.clock += 1
+        self.vram_snaps.append(VramSnap(slot, sl.n, self.io.snapshot_save(slot), None if sl.mtp_hidden is None else sl.mtp_hidden.clone(),
+                                        None if logits is None else logits.clone(), self.clock))
+
+    def _best_vram_snapshot(self, slot: int, toks: Sequence[int]) -> Optional[VramSnap]:
+        """The deepest snapshot of this slot that lies inside what the slot and the prompt have in common (at least one
+        prompt token must remain to be prefilled unless the snapshot carries the logits of its position)."""
+        common = self._common(slot, toks)
+        best = None
+        for v in self.vram_snaps:
+            if v.slot != slot or v.n > common or v.n < 1:
+                continue
+            if v.n >= len(toks) and not (v.n == len(toks) and v.logits is not None):
+                continue
+            if best is None or v.n > best.n:
+                best = v
+        return best
+
+    def _restore_vram_snapshot(self, slot: int, snap: VramSnap, toks: Sequence[int]) -> None:
+        si, sl = self.slots[slot], self.e.slot[slot]
+        self.io.snapshot_restore(slot, snap.tensors)
+        sl.tokens = list(toks[:snap.n])
+        sl.mtp_hidden = None if snap.mtp_hidden is None else snap.mtp_hidden.clone()
+        si.block_keys = si.block_keys[:snap.n // BLOCK]
+        self.clock += 1
+        snap.used = self.clock
+        # snapshots of later positions describe a continuation that is being abandoned
+        self.vram_snaps = [v for v in self.vram_snaps if not (v.slot == slot and v.n > snap.n)]
+        self.sampler_sync(slot, toks[:snap.n], snap.n)
+        if snap.n == len(toks) and snap.logits is not None:
+            si.logits = snap.logits.clone()
+
+    def _capture_point(self, prompt: Sequence[int], done: int, end: int, last_capture: int) -> int:
+        """Where a piece [done, end) should end so that a device snapshot can be taken at a message boundary: the last
+        boundary token in the piece that lies at least ``snap_min_gap`` tokens after the previous capture (reference:
+        plan_captures, src/session/prefix_cache.cpp:41-78).  ``end`` when there is none."""
+        if self.boundary < 0:
+            return end
+        lo = max(done + 1, last_capture + self.snap_min_gap)
+        for p in range(min(end, len(prompt) - 1), lo - 1, -1):
+            if prompt[p] == self.boundary:
+                return p
+        return end
+
     def prefetch(self, tokens: Sequence[int]) -> int:
         """Start reading, in the background, the stored blocks on the prompt's path that are only on disk, so that
         ``begin_prompt`` finds them in memory (reference: Session::prefetch, src/session/prefix_cache.cpp:34-39 and the
@@ -241,6 +322,9 @@ class Session:
         end = done + n
         if end < len(si.prompt) and end // BLOCK * BLOCK > done:
             end = end // BLOCK * BLOCK            # pieces end on block boundaries so a snapshot can be stored there
+        cap = self._capture_point(si.prompt, done, end, si.last_capture) if end < len(si.prompt) else end
+        at_boundary = cap < end or (cap < len(si.prompt) and si.prompt[cap] == self.boundary and cap - si.last_capture >= self.snap_min_gap)
+        end = cap
         piece = si.prompt[done:end]
         last = end >= len(si.prompt)
         self.e.prefill(slot, piece, want_logits=last)
@@ -248,6 +332,11 @@ class Session:
         if last:          # the last row's logits over the whole vocabulary (gathered from the ranks' shards)
             row = self.e.last_prefill_row
             si.logits = self.e.full_logits(row + 1)[row].clone()
+        if last or at_boundary:
+            # the state before the next message (or before generation) stays on the device: a request that shares the prompt up to
+            # here and then differs - an edited last message, a regenerated answer - goes back to it
+            self._take_vram_snapshot(slot, si.logits if last else None)
+            si.last_capture = end
         si.timing["prefill_s"] += time.time() - t0
         self._save_blocks(slot, snapshot=(end % BLOCK == 0))
         return last
