@@ -370,7 +370,7 @@ QW_API int qwk_hc_up_mix(const float *red, int ld_red, const void *Wu, const flo
                          int R, int n_inj, int H, float eps, int M, float *inj, int ld_inj, void *bin, int ld_bin,
                          int bin_col0, cudaStream_t s) {
     if (hc != 4 || (R & 7) || R > 8 * 8 * UP_MAXI) return -1;
-    const int upr = M > UP_ROWS ? 2 * UP_ROWS : UP_ROWS;
+    const int upr = UP_ROWS;          // eight rows per block (weights read once for up to eight rows) measured slower at 6 and 8 rows
     dim3 grid((SH + 7) / 8, (M + upr - 1) / upr);
     const FuseIn fi = take_fi();
     const size_t smem = sizeof(float) * ((size_t)upr * R + upr * hc + (size_t)upr * ld_red);

@@ -322,7 +322,7 @@ class Session:
         end = done + n
         if end < len(si.prompt) and end // BLOCK * BLOCK > done:
             end = end // BLOCK * BLOCK            # pieces end on block boundaries so a snapshot can be stored there
-        cap = self._capture_point(si.prompt, done, end, si.last_capture) if end < len(si.prompt) else end
+        cap = self._capture_point(si.prompt, done, end, si.last_capture)
         at_boundary = cap < end or (cap < len(si.prompt) and si.prompt[cap] == self.boundary and cap - si.last_capture >= self.snap_min_gap)
         end = cap
         piece = si.prompt[done:end]
