@@ -6,7 +6,9 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("T,N,K", [(128, 128, 64), (128, 128, 256), (256, 384, 2560), (200, 324, 2560), (4096, 512, 2560),
-                                   (77, 130, 328)])
+                                   (77, 130, 328),
+                                   # wide enough (N >= 1024, >= 74 tiles) for the 128 x 256 tile form, with ragged edges
+                                   (1024, 2560, 320), (2000, 1536, 640), (4096, 1200, 128), (1111, 10240, 64)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tc_matches_fp32(T, N, K, out_dtype):
     from qwb200.ops import kernels as K_
@@ -88,3 +90,36 @@ def test_gemm_tc_split_k_partials_add_up(T, N, K, ks):
     got = out[:, :T, :N].sum(0)
     err = float((got - ref).abs().max() / ref.abs().max())
     assert err < 2e-3, err
+
+
+@pytest.mark.parametrize("T,N,K", [(1024, 2048, 256), (1500, 512, 192)])
+def test_gemm_tc_reduce_scatter_epilogue_on_emulated_ranks(T, N, K):
+    """The tensor-parallel forms of the product on four ranks emulated on one GPU: with the reduce-scatter epilogue every
+    rank's tiles land in the column owner's receive buffer and the owners' rank-order sums equal the sum of the full
+    products; with the all-reduce epilogue every rank receives every part.  (2048 columns: the 256-wide tile form.)"""
+    import ctypes as C
+    from qwb200.models.config import ModelConfig
+    from qwb200.ops import lib as qlib, structs as S
+    from qwb200.parallel import tp_channel
+    L = qlib.load(True)
+    dev = torch.device("cuda:0")
+    R = 4
+    cfg = ModelConfig.tiny(hidden=N)
+    chans = tp_channel.make_emulated(cfg, R, T, dev, mtp=False)
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator(device="cuda").manual_seed(N + K)
+    A = [torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16) for _ in range(R)]
+    W = [(torch.randn(N, K, generator=g, device=dev) * 0.05).to(torch.bfloat16) for _ in range(R)]
+    full = [a.float() @ w.float().T for a, w in zip(A, W)]
+    for r in range(R):
+        assert L.qwk_gemm_bf16_tc_tp(chans[r].ptr, P(A[r]), P(W[r]), None, T, N, K, K, K, N, 0, -1, 2, S.TP_RS, 0, s) == 0
+    SH = N // R
+    outs = [torch.zeros(T, SH, device=dev) for _ in range(R)]
+    for r in range(R):
+        assert L.qwk_tp_reduce(chans[r].ptr, S.TP_RS, P(outs[r]), T * SH, s) == 0
+    torch.cuda.synchronize()
+    want = sum(full)
+    for r in range(R):
+        err = float((outs[r] - want[:, r * SH:(r + 1) * SH]).abs().max() / want.abs().max())
+        assert err < 2e-3, (r, err)

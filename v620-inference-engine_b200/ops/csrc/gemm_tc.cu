@@ -31,6 +31,13 @@ constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;   
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr int TC_TMEM_COLS = 2 * TC_BN;          // two accumulators
+// The wide form of the dense kernel: 128 x 256 tiles (the widest MMA: per k block 48 KB of operands feed twice the
+// math of a 128 x 128 tile's 32 KB), four stages, one CTA per SM holding all 512 TMEM columns for its two accumulators.
+constexpr int TC_WIDE_BN = 256, TC_WIDE_STAGES = 4;
+template <int BN>
+constexpr int tc_stage_bytes() { return TC_A_BYTES + BN * TC_BK * 2; }
+template <int BN, int ST>
+constexpr int tc_smem_bytes() { return ST * tc_stage_bytes<BN>() + 1024 /*alignment*/ + 256 /*barriers*/; }
 
 __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
     // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
@@ -84,6 +91,7 @@ struct TileAt {
     long long c_off;                 // element offset of its output within C
 };
 // Tile `id` of the launch; false for an unused entry of the tile table (every role skips it alike).
+template <int BN = TC_BN>
 __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) {
     const int kblocks = (a.K + TC_BK - 1) / TC_BK;
     t.kb0 = 0;
@@ -91,7 +99,7 @@ __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) 
     t.c_off = 0;
     if (a.tiles) {
         const int4 tl = __ldg(a.tiles + id / a.tiles_n);
-        t.n0 = (id % a.tiles_n) * TC_BN;
+        t.n0 = (id % a.tiles_n) * BN;
         t.t0 = tl.x;
         t.rows_valid = tl.y;
         t.w0 = tl.z + t.n0;
@@ -106,7 +114,7 @@ __device__ __forceinline__ bool tile_at(const GemmTcArgs &a, int id, TileAt &t) 
         t.kbn = min(a.kb_per, kblocks - t.kb0);
         t.c_off = sp * a.c_split;
     }
-    t.n0 = (id / a.tiles_t) * TC_BN;
+    t.n0 = (id / a.tiles_t) * BN;
     t.t0 = (id % a.tiles_t) * TC_BM;
     t.rows_valid = TC_BM;
     t.w0 = t.n0;
@@ -178,15 +186,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 // The epilogue role of both kernels: warps `first_warp` .. `first_warp + n_warps - 1` (n_warps = 4: all 128 columns per warp;
 // 8: half of them), for every tile of this CTA in order.
+template <int BN = TC_BN>
 __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem, uint64_t *done, uint64_t *acc_empty,
                                               int warp, int lane, int first_warp, int n_warps) {
     const int q = warp & 3;
-    const int cbeg = (n_warps == 8 && warp >= first_warp + 4) ? TC_BN / 2 : 0;
-    const int cend = n_warps == 8 ? cbeg + TC_BN / 2 : TC_BN;
+    const int cbeg = (n_warps == 8 && warp >= first_warp + 4) ? BN / 2 : 0;
+    const int cend = n_warps == 8 ? cbeg + BN / 2 : BN;
     int j = 0;
     for (int id = blockIdx.x; id < a.total; id += gridDim.x) {
         TileAt t;
-        if (!tile_at(a, id, t)) continue;
+        if (!tile_at<BN>(a, id, t)) continue;
         const int b = j & 1;
         if (!mbar_wait(done + b, (unsigned)(j >> 1) & 1u, a.err)) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -195,7 +204,7 @@ __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem
 #pragma unroll 1
         for (int c0 = cbeg; c0 < cend; c0 += 32) {
             uint32_t v[32];
-            tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_BN + c0), v);
+            tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c0), v);
             if (row_ok) store_piece(a, t.c_off, row, t.n0 + c0, v);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -206,27 +215,28 @@ __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem
 }
 
 // The MMA role of both kernels (one thread).
+template <int BN = TC_BN, int ST = TC_STAGES>
 __device__ __forceinline__ void mma_role(const GemmTcArgs &a, unsigned char *smem, uint32_t tmem, uint64_t *full, uint64_t *empty,
                                          uint64_t *done, uint64_t *acc_empty, int kblocks) {
     // instruction descriptor: D fp32, A/B bf16, both K-major, N and M of the tile
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
     int j = 0;
     unsigned it = 0;
     for (int id = blockIdx.x; id < a.total; id += gridDim.x) {
         TileAt t;
-        if (!tile_at(a, id, t)) continue;
+        if (!tile_at<BN>(a, id, t)) continue;
         const int b = j & 1;
         if (j >= 2 && !mbar_wait(acc_empty + b, (unsigned)((j >> 1) - 1) & 1u, a.err)) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < t.kbn; ++kb, ++it) {
-            const unsigned s = it % TC_STAGES;
-            if (!mbar_wait(full + s, (it / TC_STAGES) & 1u, a.err)) return;
+            const unsigned s = it % ST;
+            if (!mbar_wait(full + s, (it / ST) & 1u, a.err)) return;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sa = smem_u32(smem + s * TC_STAGE_BYTES), sb = sa + TC_A_BYTES;
+            const uint32_t sa = smem_u32(smem + s * tc_stage_bytes<BN>()), sb = sa + TC_A_BYTES;
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; ++k) {
                 const uint64_t da = make_sw128_desc(sa + k * 32), db = make_sw128_desc(sb + k * 32);
-                umma_bf16(tmem + (uint32_t)(b * TC_BN), da, db, idesc, (kb | k) ? 1u : 0u);
+                umma_bf16(tmem + (uint32_t)(b * BN), da, db, idesc, (kb | k) ? 1u : 0u);
             }
             umma_commit(empty + s);          // the stage is free once these MMAs have read it
         }
@@ -241,16 +251,17 @@ struct TcShared {
     uint64_t *full, *empty, *done, *acc_empty;
     uint32_t tmem;
 };
+template <int BN = TC_BN, int ST = TC_STAGES>
 __device__ __forceinline__ TcShared tc_setup(unsigned char *raw, int warp, unsigned full_count, unsigned acc_empty_count) {
     TcShared t;
     t.smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
-    t.full = reinterpret_cast<uint64_t *>(t.smem + TC_STAGES * TC_STAGE_BYTES);
-    t.empty = t.full + TC_STAGES;
-    t.done = t.empty + TC_STAGES;
+    t.full = reinterpret_cast<uint64_t *>(t.smem + ST * tc_stage_bytes<BN>());
+    t.empty = t.full + ST;
+    t.done = t.empty + ST;
     t.acc_empty = t.done + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t.acc_empty + 2);
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < ST; ++s) {
             mbar_init(t.full + s, full_count);
             mbar_init(t.empty + s, 1);
         }
@@ -261,7 +272,7 @@ __device__ __forceinline__ TcShared tc_setup(unsigned char *raw, int warp, unsig
         mbar_fence_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -270,21 +281,23 @@ __device__ __forceinline__ TcShared tc_setup(unsigned char *raw, int warp, unsig
     t.tmem = *tmem_slot;
     return t;
 }
+template <int BN = TC_BN>
 __device__ __forceinline__ void tc_teardown(const TcShared &t, int warp) {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(t.tmem), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(t.tmem), "r"(2 * BN) : "memory");
     }
 }
 
-// grid: min(tiles, 2 x SMs) CTAs of 320 threads.
-__global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+// grid: min(tiles, CTAs per SM x SMs) CTAs of 320 threads (two per SM with 128-wide tiles, one with 256-wide tiles).
+template <int BN, int ST>
+__global__ void __launch_bounds__(320, BN == TC_BN ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                          const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
     extern __shared__ unsigned char raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TcShared sh = tc_setup(raw, warp, 1, 8);
+    const TcShared sh = tc_setup<BN, ST>(raw, warp, 1, 8);
     const int kblocks = (a.K + TC_BK - 1) / TC_BK;
     if (warp == 0) {
         if (lane == 0) {
@@ -292,23 +305,23 @@ __global__ void __launch_bounds__(320, 2) gemm_tc_kernel(const __grid_constant__
             bool ok = tp_wait_thread(a.wait);
             for (int id = blockIdx.x; id < a.total && ok; id += gridDim.x) {
                 TileAt t;
-                if (!tile_at(a, id, t)) continue;
+                if (!tile_at<BN>(a, id, t)) continue;
                 for (int kb = 0; kb < t.kbn; ++kb, ++it) {
-                    const unsigned s = it % TC_STAGES;
-                    if (it >= TC_STAGES && !mbar_wait(sh.empty + s, (it / TC_STAGES - 1) & 1u, a.err)) { ok = false; break; }
-                    mbar_expect_tx(sh.full + s, TC_STAGE_BYTES);
-                    unsigned char *st = sh.smem + s * TC_STAGE_BYTES;
+                    const unsigned s = it % ST;
+                    if (it >= ST && !mbar_wait(sh.empty + s, (it / ST - 1) & 1u, a.err)) { ok = false; break; }
+                    mbar_expect_tx(sh.full + s, tc_stage_bytes<BN>());
+                    unsigned char *st = sh.smem + s * tc_stage_bytes<BN>();
                     tma_load_2d(st, &mapA, (t.kb0 + kb) * TC_BK, t.t0, sh.full + s);
                     tma_load_2d(st + TC_A_BYTES, &mapW, (t.kb0 + kb) * TC_BK, t.w0, sh.full + s);
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) mma_role(a, sh.smem, sh.tmem, sh.full, sh.empty, sh.done, sh.acc_empty, kblocks);
+        if (lane == 0) mma_role<BN, ST>(a, sh.smem, sh.tmem, sh.full, sh.empty, sh.done, sh.acc_empty, kblocks);
     } else {
-        epilogue_role(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 8);
+        epilogue_role<BN>(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 8);
     }
-    tc_teardown(sh, warp);
+    tc_teardown<BN>(sh, warp);
     tp_signal(a.epi.sig);
 }
 
@@ -443,8 +456,8 @@ static bool make_map(CUtensorMap *m, const void *base, long long rows, long long
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Two persistent CTAs per SM of the current device, or one CTA per tile when there are fewer tiles.
-static unsigned persistent_grid(int total) {
+// `per_sm` persistent CTAs per SM of the current device, or one CTA per tile when there are fewer tiles.
+static unsigned persistent_grid(int total, int per_sm = 2) {
     static int sms[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -454,7 +467,7 @@ static unsigned persistent_grid(int total) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
         sms[dev] = n;
     }
-    const int cap = 2 * sms[dev];
+    const int cap = per_sm * sms[dev];
     return (unsigned)(total < cap ? total : cap);
 }
 
@@ -463,34 +476,53 @@ static unsigned persistent_grid(int total) {
 using namespace qw;
 
 // One-time (per device) opt-in to the kernels' dynamic shared memory.
-static bool configure_once(const void *kernel) {
-    static bool done[2][64] = {};
+static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 grouped, 2 dense 256-wide
+    static bool done[3][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    const int which = kernel == (const void *)gemm_tc_q4_kernel ? 1 : 0;
     if (!done[which][dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return false;
+        cudaError_t e;
+        if (which == 0) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN, TC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        else if (which == 1) e = cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        else e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>());
+        if (e != cudaSuccess) return false;
         done[which][dev] = true;
     }
     return true;
 }
 
+static int g_wide_min_n = 1024;          // products at least this wide use the 128 x 256 tile form (0: never)
+
 static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
                       int out_bf16, cudaStream_t s) {
     if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return -1;
+    // wide tiles pay when there are enough of them to fill the SMs and the last column tile is not mostly padding
+    const int tiles_t = (T + TC_BM - 1) / TC_BM;
+    const bool wide = g_wide_min_n > 0 && N >= g_wide_min_n && (N % TC_WIDE_BN == 0 || N % TC_WIDE_BN > TC_BN) &&
+                      tiles_t * ((N + TC_WIDE_BN - 1) / TC_WIDE_BN) >= NUM_SMS / 2;
+    const int BN = wide ? TC_WIDE_BN : TC_BN;
     CUtensorMap mA, mW;
-    if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_BN)) return -3;
+    if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, BN)) return -3;
     a.C32 = out_bf16 ? nullptr : (float *)C;
     a.C16 = out_bf16 ? (bf16 *)C : nullptr;
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
-    a.tiles_t = (T + TC_BM - 1) / TC_BM; a.tiles_n = (N + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
+    a.tiles_t = tiles_t; a.tiles_n = (N + BN - 1) / BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
-    const unsigned grid = persistent_grid(a.total);
+    if (!configure_once(wide ? 2 : 0)) return -3;
+    const unsigned grid = persistent_grid(a.total, wide ? 1 : 2);
     if (a.epi.sig.ticket) a.epi.sig.nblocks = grid;
-    gemm_tc_kernel<<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
+    if (wide) gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES><<<grid, 320, tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>(), s>>>(mA, mW, a);
+    else gemm_tc_kernel<TC_BN, TC_STAGES><<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Products at least `min_n` columns wide use the 128 x 256 tile form (0 switches it off; measurements and tests).
+QW_API int qwk_gemm_tc_wide_min_n(int min_n) {
+    const int old = g_wide_min_n;
+    g_wide_min_n = min_n;
+    return old;
 }
 
 // C = A . W^T.  A bf16 [T][lda], W bf16 [N][ldw], C fp32 (out_bf16 = 0) or bf16 [T][ldc].
@@ -559,8 +591,8 @@ QW_API int qwk_gemm_bf16_tc_grouped(const void *A, const void *W, void *C, const
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
-    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
+    if (!configure_once(0)) return -3;
+    gemm_tc_kernel<TC_BN, TC_STAGES><<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -578,7 +610,7 @@ QW_API int qwk_gemm_q4_tc_grouped(const void *A, const void *Wq, const void *sca
     a.T = rows; a.N = Nw; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = (const int4 *)tiles;
     a.tiles_t = max_tiles; a.tiles_n = (Nw + TC_BN - 1) / TC_BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    if (!configure_once((const void *)gemm_tc_q4_kernel)) return -3;
+    if (!configure_once(1)) return -3;
     gemm_tc_q4_kernel<<<persistent_grid(a.total), 448, TC_SMEM, s>>>(mA, a, (const uint32_t *)Wq, (const bf16 *)scale, w_rows);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -602,7 +634,7 @@ QW_API int qwk_gemm_bf16_tc_splitk(const void *A, const void *W, float *C, int T
     if (a.ksplit != ksplit) return -1;
     a.c_split = c_split;
     a.total = a.tiles_t * a.tiles_n * a.ksplit;
-    if (!configure_once((const void *)gemm_tc_kernel)) return -3;
-    gemm_tc_kernel<<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
+    if (!configure_once(0)) return -3;
+    gemm_tc_kernel<TC_BN, TC_STAGES><<<persistent_grid(a.total), 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
