@@ -36,8 +36,14 @@ constexpr int TC_TMEM_COLS = 2 * TC_BN;          // two accumulators
 constexpr int TC_WIDE_BN = 256, TC_WIDE_STAGES = 4;
 template <int BN>
 constexpr int tc_stage_bytes() { return TC_A_BYTES + BN * TC_BK * 2; }
-template <int BN, int ST>
-constexpr int tc_smem_bytes() { return ST * tc_stage_bytes<BN>() + 1024 /*alignment*/ + 256 /*barriers*/; }
+// Staged epilogue (the tensor-parallel forms): 4 KB per epilogue warp behind the barriers, where a 32 x 32 fp32 piece is
+// turned from "a thread owns a row" into "eight lanes own 128 contiguous bytes of a row" before it leaves for a peer.
+constexpr int TC_EPI_WARPS = 8, TC_STG_BYTES = 4096;
+constexpr int TC_STG_STAGES = 5;                 // k-block ring of the staged 128-wide form (one CTA per SM)
+template <int BN, int ST, bool STG = false>
+constexpr int tc_smem_bytes() {
+    return ST * tc_stage_bytes<BN>() + 1024 /*alignment*/ + 256 /*barriers*/ + (STG ? TC_EPI_WARPS * TC_STG_BYTES : 0);
+}
 
 __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
     // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
@@ -172,6 +178,44 @@ __device__ __forceinline__ void store_piece(const GemmTcArgs &a, long long c_off
     }
 }
 
+// The same piece on its way to other ranks, through the warp's staging buffer: lane r writes its row as eight 16-byte
+// chunks (chunk k at position k ^ (r & 7): no bank conflicts either way), then lanes 8i..8i+7 read row 4j + i back and
+// store its 128 bytes as one contiguous line - a peer store of whole 128-byte lines instead of 32 scattered 16-byte ones,
+// which is what NVLink carries at full rate.  `row0` is the output row of lane 0, `rows_ok` how many of the 32 rows exist.
+__device__ __forceinline__ void send_piece(const GemmTcArgs &a, float *stg, int lane, int row0, int rows_ok, int col0,
+                                           const uint32_t (&v)[32]) {
+    float4 *s4 = reinterpret_cast<float4 *>(stg);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        s4[lane * 8 + (k ^ (lane & 7))] = make_float4(__uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
+                                                      __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
+    __syncwarp();
+    const int owner = a.epi.mode == 2 ? col0 / a.epi.cols_per_rank : 0;
+    const int ch = lane & 7, rsub = lane >> 3;
+    const int col = col0 + ch * 4;                                   // first of this lane's four columns
+    const int ccol = col - (a.epi.mode == 2 ? owner * a.epi.cols_per_rank : 0);
+    const bool vec = ((a.epi.ld | col0) & 3) == 0 && col + 4 <= a.N;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + rsub;
+        const float4 val = s4[r * 8 + (ch ^ (r & 7))];
+        if (r >= rows_ok || col >= a.N) continue;
+        const long long off = (long long)(row0 + r) * a.epi.ld + ccol;
+#pragma unroll
+        for (int d = 0; d < TP_MAX_RANKS; ++d) {
+            if (d >= a.epi.ranks || (a.epi.mode == 2 && d != owner)) continue;
+            float *o = a.epi.dst[d] + off;
+            if (vec) {
+                *reinterpret_cast<float4 *>(o) = val;
+            } else {
+                const float e[4] = {val.x, val.y, val.z, val.w};
+                for (int j = 0; j < 4 && col + j < a.N; ++j) o[j] = e[j];
+            }
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -186,9 +230,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 // The epilogue role of both kernels: warps `first_warp` .. `first_warp + n_warps - 1` (n_warps = 4: all 128 columns per warp;
 // 8: half of them), for every tile of this CTA in order.
-template <int BN = TC_BN>
+template <int BN = TC_BN, bool STG = false>
 __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem, uint64_t *done, uint64_t *acc_empty,
-                                              int warp, int lane, int first_warp, int n_warps) {
+                                              int warp, int lane, int first_warp, int n_warps, float *stg = nullptr) {
     const int q = warp & 3;
     const int cbeg = (n_warps == 8 && warp >= first_warp + 4) ? BN / 2 : 0;
     const int cend = n_warps == 8 ? cbeg + BN / 2 : BN;
@@ -205,6 +249,13 @@ __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem
         for (int c0 = cbeg; c0 < cend; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c0), v);
+            if constexpr (STG) {
+                if (a.epi.mode) {
+                    const int r0 = t.t0 + q * 32;
+                    send_piece(a, stg, lane, r0, min(32, min(a.T - r0, t.rows_valid - q * 32)), t.n0 + c0, v);
+                    continue;
+                }
+            }
             if (row_ok) store_piece(a, t.c_off, row, t.n0 + c0, v);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -292,8 +343,8 @@ __device__ __forceinline__ void tc_teardown(const TcShared &t, int warp) {
 }
 
 // grid: min(tiles, CTAs per SM x SMs) CTAs of 320 threads (two per SM with 128-wide tiles, one with 256-wide tiles).
-template <int BN, int ST>
-__global__ void __launch_bounds__(320, BN == TC_BN ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+template <int BN, int ST, bool STG = false>
+__global__ void __launch_bounds__(320, (BN == TC_BN && !STG) ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                          const __grid_constant__ CUtensorMap mapW, GemmTcArgs a) {
     extern __shared__ unsigned char raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,7 +370,10 @@ __global__ void __launch_bounds__(320, BN == TC_BN ? 2 : 1) gemm_tc_kernel(const
     } else if (warp == 1) {
         if (lane == 0) mma_role<BN, ST>(a, sh.smem, sh.tmem, sh.full, sh.empty, sh.done, sh.acc_empty, kblocks);
     } else {
-        epilogue_role<BN>(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, 8);
+        float *stg = nullptr;
+        if constexpr (STG)
+            stg = reinterpret_cast<float *>(sh.smem + ST * tc_stage_bytes<BN>() + 256 + (warp - 2) * TC_STG_BYTES);
+        epilogue_role<BN, STG>(a, sh.tmem, sh.done, sh.acc_empty, warp, lane, 2, TC_EPI_WARPS, stg);
     }
     tc_teardown<BN>(sh, warp);
     tp_signal(a.epi.sig);
@@ -476,8 +530,8 @@ static unsigned persistent_grid(int total, int per_sm = 2) {
 using namespace qw;
 
 // One-time (per device) opt-in to the kernels' dynamic shared memory.
-static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 grouped, 2 dense 256-wide
-    static bool done[3][64] = {};
+static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 grouped, 2 dense 256-wide, 3 / 4 the two with a staged epilogue
+    static bool done[5][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
@@ -485,8 +539,12 @@ static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 group
         cudaError_t e;
         if (which == 0) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN, TC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
         else if (which == 1) e = cudaFuncSetAttribute(gemm_tc_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        else e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>());
+        else if (which == 2) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>());
+        else if (which == 3) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN, TC_STG_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      tc_smem_bytes<TC_BN, TC_STG_STAGES, true>());
+        else e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES, true>());
         if (e != cudaSuccess) return false;
         done[which][dev] = true;
     }
@@ -510,10 +568,15 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     a.tiles_t = tiles_t; a.tiles_n = (N + BN - 1) / BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    if (!configure_once(wide ? 2 : 0)) return -3;
-    const unsigned grid = persistent_grid(a.total, wide ? 1 : 2);
+    const bool staged = a.epi.mode != 0;          // tiles that leave for other ranks go out as whole 128-byte lines
+    if (!configure_once(staged ? (wide ? 4 : 3) : (wide ? 2 : 0))) return -3;
+    const unsigned grid = persistent_grid(a.total, (wide || staged) ? 1 : 2);
     if (a.epi.sig.ticket) a.epi.sig.nblocks = grid;
-    if (wide) gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES><<<grid, 320, tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>(), s>>>(mA, mW, a);
+    if (staged && wide)
+        gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES, true><<<grid, 320, tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES, true>(), s>>>(mA, mW, a);
+    else if (staged)
+        gemm_tc_kernel<TC_BN, TC_STG_STAGES, true><<<grid, 320, tc_smem_bytes<TC_BN, TC_STG_STAGES, true>(), s>>>(mA, mW, a);
+    else if (wide) gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES><<<grid, 320, tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>(), s>>>(mA, mW, a);
     else gemm_tc_kernel<TC_BN, TC_STAGES><<<grid, 320, TC_SMEM, s>>>(mA, mW, a);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
