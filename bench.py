@@ -97,18 +97,38 @@ def main():
     g = torch.Generator().manual_seed(1234)
     ctx = torch.randint(0, cfg.vocab, (args.context,), generator=g).tolist()
     token_major = bool(eng.opts.prefill_chunk) and (world == 1 or eng.tp_channels is not None)
-    if token_major:
-        eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, kernel attributes), then start over
-        torch.cuda.synchronize()
-        eng.reset(0)
     t0 = time.time()
     pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    pe0.record()
-    eng.prefill(0, ctx, want_logits=True)
-    pe1.record()
-    torch.cuda.synchronize()
+    prefill_note = None
+    try:
+        if token_major:
+            eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, kernel attributes), then start over
+            torch.cuda.synchronize()
+            eng.dm.check_error()
+            eng.reset(0)
+        pe0.record()
+        eng.prefill(0, ctx, want_logits=True)
+        pe1.record()
+        torch.cuda.synchronize()
+        eng.dm.check_error()
+    except RuntimeError as ex:
+        if not token_major:
+            raise
+        # the headline is the decode step: fill the context through the row-batched path instead and say so
+        prefill_note = f"token-major prefill failed ({str(ex)[:160]}); context filled by the row-batched path"
+        log(prefill_note)
+        torch.cuda.synchronize()
+        eng.dm.err_word.zero_()
+        eng.tp_channels = None
+        eng.opts.prefill_chunk = 0
+        token_major = False
+        eng.reset(0)
+        pe0.record()
+        eng.prefill(0, ctx, want_logits=True)
+        pe1.record()
+        torch.cuda.synchronize()
+        eng.dm.check_error()
     prefill_ms = pe0.elapsed_time(pe1)
-    eng.dm.check_error()
     first = int(eng.dm.buf["amax_idx"][eng.last_prefill_row])
     log(f"context of {args.context} tokens in {time.time() - t0:.2f} s")
 
@@ -159,72 +179,95 @@ def main():
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     sampler.stop()
-    # ---- long prompt: 32,768 tokens in 4,096-token chunks through the token-major path
-    prefill_long = None
-    if args.prefill_long and token_major:
-        lg = torch.Generator().manual_seed(77)
-        long_toks = torch.randint(0, cfg.vocab, (args.prefill_long,), generator=lg).tolist()
-        eng.reset(1)
-        barrier()
-        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        q0.record()
-        eng.prefill(1, long_toks, want_logits=True)
-        q1.record()
-        barrier()
-        eng.dm.check_error()
-        tl = torch.tensor([q0.elapsed_time(q1)], device=dev)
-        if dist is not None:
-            dist.all_reduce(tl, op=dist.ReduceOp.MAX)
-        prefill_long = {"tokens": args.prefill_long, "chunk": eng.prefiller.T, "lanes": eng.prefiller.lanes, "ms": round(float(tl), 1),
-                        "tok_s": round(args.prefill_long / (float(tl) / 1e3), 1)}
-        log(f"long prefill: {prefill_long}")
-        eng.reset(1)
-    # ---- speculative decoding through Session.generate: 5 drafts per step, sampling (T 1.0, top-k 20, top-p 0.95), 1 and 4
-    # concurrent streams of 8,192-token context.  Random weights accept next to nothing, so acceptance is forced: for
-    # a = 0..5 exactly `a` drafts are accepted per stream and step, and every figure is a timed run of real steps
-    # (drafts, one verification step over all streams' rows, sampling of every row, accept / rollback).
-    mtp = None
-    if args.mtp_context and eng.mtp and (world == 1 or args.comm == "p2p"):
-        from qwb200.engine.sampling import SamplingParams
-        from qwb200.session.session import Session, StepReq
-        ses = Session(eng, host_cache_bytes=0)
-        kd, steps_m = 5, max(3, args.mtp_steps)
-        sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
-        mg = torch.Generator().manual_seed(99)
-        for sl_ in range(4):
-            eng.reset(sl_)
-            ses.sampler.reset_slot(sl_)
-            eng.prefill(sl_, torch.randint(0, cfg.vocab, (args.mtp_context,), generator=mg).tolist(), want_logits=True)
-        torch.cuda.synchronize()
-        eng.dm.check_error()
-        mtp = {"drafts": kd, "context": args.mtp_context, "sampling": {"temperature": 1.0, "top_k": 20, "top_p": 0.95},
-               "timed_steps_per_point": steps_m, "note": "measured: forced acceptance of a drafts per stream and step"}
-        for streams in (1, 4):
-            pend = [7 + i for i in range(streams)]
-            res = []
-            for acc in range(kd + 1):
-                def one_step():
-                    outs = ses.generate([StepReq(i, pend[i], 64, 0, sp) for i in range(streams)], kd, force_accept=acc)
-                    for i, o in enumerate(outs):
-                        pend[i] = o.tokens[-1]
-                    return sum(len(o.tokens) for o in outs)
-                for _ in range(3):
-                    one_step()
-                barrier()
-                m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                m0.record()
-                emitted = 0
-                for _ in range(steps_m):
-                    emitted += one_step()
-                m1.record()
-                barrier()
-                tm = torch.tensor([m0.elapsed_time(m1)], device=dev)
-                if dist is not None:
-                    dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-                res.append({"accepted": acc, "ms_per_step": round(float(tm) / steps_m, 3), "tok_s": round(emitted / (float(tm) / 1e3), 1)})
+    def run_long_prefill():
+        # ---- long prompt: 32,768 tokens in 4,096-token chunks through the token-major path
+        prefill_long = None
+        if args.prefill_long and token_major:
+            lg = torch.Generator().manual_seed(77)
+            long_toks = torch.randint(0, cfg.vocab, (args.prefill_long,), generator=lg).tolist()
+            eng.reset(1)
+            barrier()
+            q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            q0.record()
+            eng.prefill(1, long_toks, want_logits=True)
+            q1.record()
+            barrier()
             eng.dm.check_error()
-            mtp[f"streams_{streams}"] = res
-            log(f"speculative, {streams} stream(s): {res}")
+            tl = torch.tensor([q0.elapsed_time(q1)], device=dev)
+            if dist is not None:
+                dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+            prefill_long = {"tokens": args.prefill_long, "chunk": eng.prefiller.T, "lanes": eng.prefiller.lanes, "ms": round(float(tl), 1),
+                            "tok_s": round(args.prefill_long / (float(tl) / 1e3), 1)}
+            log(f"long prefill: {prefill_long}")
+            eng.reset(1)
+        return prefill_long
+    def run_mtp():
+        # ---- speculative decoding through Session.generate: 5 drafts per step, sampling (T 1.0, top-k 20, top-p 0.95), 1 and 4
+        # concurrent streams of 8,192-token context.  Random weights accept next to nothing, so acceptance is forced: for
+        # a = 0..5 exactly `a` drafts are accepted per stream and step, and every figure is a timed run of real steps
+        # (drafts, one verification step over all streams' rows, sampling of every row, accept / rollback).
+        mtp = None
+        if args.mtp_context and eng.mtp and (world == 1 or args.comm == "p2p"):
+            from qwb200.engine.sampling import SamplingParams
+            from qwb200.session.session import Session, StepReq
+            ses = Session(eng, host_cache_bytes=0)
+            kd, steps_m = 5, max(3, args.mtp_steps)
+            sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
+            mg = torch.Generator().manual_seed(99)
+            for sl_ in range(4):
+                eng.reset(sl_)
+                ses.sampler.reset_slot(sl_)
+                eng.prefill(sl_, torch.randint(0, cfg.vocab, (args.mtp_context,), generator=mg).tolist(), want_logits=True)
+            torch.cuda.synchronize()
+            eng.dm.check_error()
+            mtp = {"drafts": kd, "context": args.mtp_context, "sampling": {"temperature": 1.0, "top_k": 20, "top_p": 0.95},
+                   "timed_steps_per_point": steps_m, "note": "measured: forced acceptance of a drafts per stream and step"}
+            for streams in (1, 4):
+                pend = [7 + i for i in range(streams)]
+                res = []
+                for acc in range(kd + 1):
+                    def one_step():
+                        outs = ses.generate([StepReq(i, pend[i], 64, 0, sp) for i in range(streams)], kd, force_accept=acc)
+                        for i, o in enumerate(outs):
+                            pend[i] = o.tokens[-1]
+                        return sum(len(o.tokens) for o in outs)
+                    for _ in range(3):
+                        one_step()
+                    barrier()
+                    m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    m0.record()
+                    emitted = 0
+                    for _ in range(steps_m):
+                        emitted += one_step()
+                    m1.record()
+                    barrier()
+                    tm = torch.tensor([m0.elapsed_time(m1)], device=dev)
+                    if dist is not None:
+                        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+                    res.append({"accepted": acc, "ms_per_step": round(float(tm) / steps_m, 3), "tok_s": round(emitted / (float(tm) / 1e3), 1)})
+                eng.dm.check_error()
+                mtp[f"streams_{streams}"] = res
+                log(f"speculative, {streams} stream(s): {res}")
+        return mtp
+    # the extras must not take the headline with them: a failure is recorded in their place
+    extras_failed = {}
+    prefill_long = mtp = None
+    for name, fn in (("prefill_long", run_long_prefill), ("mtp", run_mtp)):
+        try:
+            r = fn()
+        except Exception as ex:          # noqa: BLE001 - reported in the JSON line
+            r = None
+            extras_failed[name] = f"{type(ex).__name__}: {str(ex)[:200]}"
+            log(f"{name} failed: {extras_failed[name]}")
+            try:
+                torch.cuda.synchronize()
+                eng.dm.err_word.zero_()
+            except Exception:
+                pass
+        if name == "prefill_long":
+            prefill_long = r
+        else:
+            mtp = r
     if dist is not None:
         tt = torch.tensor([ms, ms_e2e], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -256,6 +299,10 @@ def main():
             "gpu_launches_per_step": launches,
             "impl": "ours",
         }
+        if prefill_note:
+            out["prefill"]["note"] = prefill_note
+        if extras_failed:
+            out["extras_failed"] = extras_failed
         print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()

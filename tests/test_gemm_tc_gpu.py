@@ -123,3 +123,43 @@ def test_gemm_tc_reduce_scatter_epilogue_on_emulated_ranks(T, N, K):
     for r in range(R):
         err = float((outs[r] - want[:, r * SH:(r + 1) * SH]).abs().max() / want.abs().max())
         assert err < 2e-3, (r, err)
+
+
+@pytest.fixture
+def pair_form():
+    """Switch the CTA-pair form of the dense kernel on for products at least 256 columns wide, and off again."""
+    import ctypes as C
+    from qwb200.ops import lib as qlib
+    L = qlib.load(True)
+    old = L.qwk_gemm_tc_pair_min_n(256)
+    word = torch.zeros(2, dtype=torch.int32, device="cuda")           # bounded waits that run out report here
+    L.qwk_set_error_word(C.c_void_p(word.data_ptr()))
+    yield word
+    torch.cuda.synchronize()
+    L.qwk_set_error_word(None)
+    L.qwk_gemm_tc_pair_min_n(old)
+
+
+@pytest.mark.parametrize("T,N,K", [(256, 256, 64), (512, 512, 256), (4096, 2560, 640), (300, 700, 192), (1111, 1536, 128), (2048, 13952, 320)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tc_pair_form_matches_fp32(pair_form, T, N, K, out_dtype):
+    """256 x 256 tiles computed by two CTAs with tcgen05.mma.cta_group::2, ragged rows and columns included; a run whose
+    barriers did not meet would end with the error word set, which is checked too."""
+    from qwb200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(T + N + K + 1)
+    A = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    ldc = (N + 7) // 8 * 8 + 8
+    out = torch.full((T + 3, ldc), 768.0, dtype=out_dtype, device="cuda")      # guard columns and rows detect stray writes
+    K_.gemm_bf16_tc(A, W, out=out[:T, :N])
+    torch.cuda.synchronize()
+    assert pair_form.tolist() == [0, 0]
+    ref = A.float() @ W.float().T
+    assert torch.all(out[:, N:].float() == 768.0) and torch.all(out[T:].float() == 768.0)
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    err = float((out[:T, :N].float() - ref).abs().max() / ref.abs().max())
+    assert err < tol, err
+
+
+def test_gemm_tc_pair_form_reduce_scatter_on_emulated_ranks(pair_form):
+    test_gemm_tc_reduce_scatter_epilogue_on_emulated_ranks(1024, 2048, 256)

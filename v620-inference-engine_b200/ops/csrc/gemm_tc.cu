@@ -380,6 +380,198 @@ __global__ void __launch_bounds__(320, (BN == TC_BN && !STG) ? 2 : 1) gemm_tc_ke
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// The pair form of the dense kernel: two CTAs of a cluster (two neighbouring SMs) compute one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and ONE HALF of the tile's W rows (128 of 256) per k
+// block - 32 KB for 128 x 256 x 64 multiply-adds per SM, where the single-CTA forms need 48 KB (128 x 256 tile) or 64 KB
+// (two 128 x 128 tiles) for the same math: those stop at what an SM can pull out of L2 (~64 bytes per cycle), this one
+// does not.  The tensor cores of both SMs read both CTAs' shared memory; each SM accumulates its 128 rows x 256 columns
+// in its own tensor memory (two accumulators = all 512 columns).
+//   producer (warp 0, one thread, both CTAs): waits for its own "empty" barrier of the stage, loads its A tile and its W
+//       half with cp.async.bulk.tensor.cta_group::2 (no multicast), both completing on the LEADER's "full" barrier, on
+//       which the leader's producer has announced the 64 KB of the pair;
+//   MMA (warp 1, one thread, leader CTA only): four cta_group::2 MMAs per k block; tcgen05.commit (to both CTAs of the
+//       pair) frees the stage in both CTAs and, after a tile's last k block, publishes the accumulator to both CTAs'
+//       epilogue warps;
+//   epilogue (warps 2-9, both CTAs): as in the single-CTA kernel, on the CTA's own 128 rows; hands the accumulator back
+//       by arriving on the leader's "acc_empty" barrier (16 arrivals: 8 warps of 2 CTAs).
+// Barriers are initialised before a cluster-wide barrier and nobody leaves before another one, so no signal is ever
+// sent to a CTA that is not there; every wait is bounded as elsewhere.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int TC_PAIR_BN = 256, TC_PAIR_BM = 256, TC_PAIR_STAGES = 6, TC_PAIR_STG_STAGES = 5;
+constexpr int TC_PAIR_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;          // per CTA: 128 x 64 of A and 128 x 64 of W
+template <int ST, bool STG>
+constexpr int tc_pair_smem_bytes() { return ST * TC_PAIR_STAGE_BYTES + 1024 + 256 + (STG ? TC_EPI_WARPS * TC_STG_BYTES : 0); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {          // the same offset in CTA `rank` of the cluster
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3)
+                 : "memory");
+}
+
+struct PairTile {
+    int t0, n0, w0, rows_valid;          // this CTA's first A row / the tile's first column / this CTA's first W row
+};
+__device__ __forceinline__ PairTile pair_tile_at(const GemmTcArgs &a, int id, uint32_t rank) {
+    PairTile t;
+    // the row tiles of one column panel are neighbours (W streams once, A stays in L2)
+    t.n0 = (id / a.tiles_t) * TC_PAIR_BN;
+    t.t0 = (id % a.tiles_t) * TC_PAIR_BM + (int)rank * TC_BM;
+    t.w0 = t.n0 + (int)rank * (TC_PAIR_BN / 2);
+    t.rows_valid = TC_BM;
+    return t;
+}
+
+// grid: 2 x min(pair tiles, SMs / 2) CTAs of 320 threads in clusters of two.  a.tiles_t / a.total count 256 x 256 tiles.
+template <int ST, bool STG>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                                                        const __grid_constant__ CUtensorMap mapW,
+                                                                                        GemmTcArgs a) {
+    extern __shared__ unsigned char raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + ST * TC_PAIR_STAGE_BYTES);
+    uint64_t *empty = full + ST, *done = empty + ST, *acc_empty = done + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST; ++s) {
+            mbar_init(full + s, 1);          // the leader's: one arrival (its producer's expect_tx) + the pair's bytes
+            mbar_init(empty + s, 1);         // one commit arrival
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(done + b, 1);
+            mbar_init(acc_empty + b, 2 * TC_EPI_WARPS);          // the leader's: the epilogue warps of both CTAs
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                      // both CTAs' barriers exist before anything is sent to them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = tp_wait_thread(a.wait);
+            for (int id = cluster_id; id < a.total && ok; id += n_clusters) {
+                const PairTile t = pair_tile_at(a, id, rank);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const unsigned s = it % ST;
+                    if (it >= ST && !mbar_wait(empty + s, (it / ST - 1) & 1u, a.err)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(full + s, 2 * TC_PAIR_STAGE_BYTES);
+                    const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                    unsigned char *st = smem + s * TC_PAIR_STAGE_BYTES;
+                    tma_load_2d_pair(st, &mapA, kb * TC_BK, t.t0, bar);
+                    tma_load_2d_pair(st + TC_A_BYTES, &mapW, kb * TC_BK, t.w0, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // instruction descriptor: D fp32, A/B bf16, both K-major, N = 256, M = 256 (the pair's rows)
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_PAIR_BN >> 3) << 17) | ((uint32_t)(TC_PAIR_BM >> 4) << 24);
+            int j = 0;
+            unsigned it = 0;
+            bool ok = true;
+            for (int id = cluster_id; id < a.total && ok; id += n_clusters) {
+                const int b = j & 1;
+                if (j >= 2 && !mbar_wait(acc_empty + b, (unsigned)((j >> 1) - 1) & 1u, a.err)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const unsigned s = it % ST;
+                    if (!mbar_wait(full + s, (it / ST) & 1u, a.err)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + s * TC_PAIR_STAGE_BYTES), sb = sa + TC_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_pair(tmem + (uint32_t)(b * TC_PAIR_BN), make_sw128_desc(sa + k * 32), make_sw128_desc(sb + k * 32), idesc,
+                                       (kb | k) ? 1u : 0u);
+                    umma_commit_pair(empty + s);
+                }
+                if (ok) umma_commit_pair(done + b);
+                ++j;
+            }
+        }
+    } else {
+        float *stg = nullptr;
+        if constexpr (STG) stg = reinterpret_cast<float *>(smem + ST * TC_PAIR_STAGE_BYTES + 256 + (warp - 2) * TC_STG_BYTES);
+        const int q = warp & 3;
+        const int cbeg = warp >= 6 ? TC_PAIR_BN / 2 : 0, cend = cbeg + TC_PAIR_BN / 2;
+        const uint32_t acc_bar = map_to_cta(smem_u32(acc_empty), 0);
+        int j = 0;
+        for (int id = cluster_id; id < a.total; id += n_clusters) {
+            const PairTile t = pair_tile_at(a, id, rank);
+            const int b = j & 1;
+            if (!mbar_wait(done + b, (unsigned)(j >> 1) & 1u, a.err)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = t.t0 + q * 32 + lane;
+            const bool row_ok = row < a.T;
+#pragma unroll 1
+            for (int c0 = cbeg; c0 < cend; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_PAIR_BN + c0), v);
+                if (t.n0 + c0 >= a.N) continue;
+                if constexpr (STG) {
+                    if (a.epi.mode) {
+                        const int r0 = t.t0 + q * 32;
+                        send_piece(a, stg, lane, r0, min(32, a.T - r0), t.n0 + c0, v);
+                        continue;
+                    }
+                }
+                if (row_ok) store_piece(a, 0, row, t.n0 + c0, v);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_bar + (uint32_t)(b * 8));
+            ++j;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                      // nothing is in flight towards either CTA any more
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    tp_signal(a.epi.sig);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // Grouped GEMM with the weights in q4 (group 128, bf16 scales): the expert products of token-major prefill without a
 // bf16 copy of the layer's experts.  Same tile, pipeline and epilogue as gemm_tc_kernel; the W operand of a stage is
 // not loaded by TMA but produced by eight extra warps: two threads own row r of the 128 x 64 W tile, each fetches 4 q4
@@ -530,8 +722,8 @@ static unsigned persistent_grid(int total, int per_sm = 2) {
 using namespace qw;
 
 // One-time (per device) opt-in to the kernels' dynamic shared memory.
-static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 grouped, 2 dense 256-wide, 3 / 4 the two with a staged epilogue
-    static bool done[5][64] = {};
+static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 grouped, 2 dense 256-wide, 3 / 4 the two with a staged epilogue, 5 / 6 the pair form
+    static bool done[7][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
@@ -543,8 +735,12 @@ static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 group
                                                       tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES>());
         else if (which == 3) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN, TC_STG_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                       tc_smem_bytes<TC_BN, TC_STG_STAGES, true>());
-        else e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES, true>());
+        else if (which == 4) e = cudaFuncSetAttribute(gemm_tc_kernel<TC_WIDE_BN, TC_WIDE_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      tc_smem_bytes<TC_WIDE_BN, TC_WIDE_STAGES, true>());
+        else if (which == 5) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TC_PAIR_STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      tc_pair_smem_bytes<TC_PAIR_STAGES, false>());
+        else e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TC_PAIR_STG_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      tc_pair_smem_bytes<TC_PAIR_STG_STAGES, true>());
         if (e != cudaSuccess) return false;
         done[which][dev] = true;
     }
@@ -552,6 +748,7 @@ static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 group
 }
 
 static int g_wide_min_n = 1024;          // products at least this wide use the 128 x 256 tile form (0: never)
+static int g_pair_min_n = 0;             // products at least this wide (and 256 rows tall) use CTA pairs (0: never)
 
 static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
                       int out_bf16, cudaStream_t s) {
@@ -560,6 +757,26 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
     const int tiles_t = (T + TC_BM - 1) / TC_BM;
     const bool wide = g_wide_min_n > 0 && N >= g_wide_min_n && (N % TC_WIDE_BN == 0 || N % TC_WIDE_BN > TC_BN) &&
                       tiles_t * ((N + TC_WIDE_BN - 1) / TC_WIDE_BN) >= NUM_SMS / 2;
+    const bool pair = g_pair_min_n > 0 && N >= g_pair_min_n && T >= TC_PAIR_BM && (N % TC_PAIR_BN == 0 || N % TC_PAIR_BN > TC_BN) &&
+                      ((T + TC_PAIR_BM - 1) / TC_PAIR_BM) * ((N + TC_PAIR_BN - 1) / TC_PAIR_BN) >= NUM_SMS / 4;
+    if (pair) {
+        CUtensorMap mA, mW;
+        if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_PAIR_BN / 2)) return -3;
+        a.C32 = out_bf16 ? nullptr : (float *)C;
+        a.C16 = out_bf16 ? (bf16 *)C : nullptr;
+        a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
+        a.tiles_t = (T + TC_PAIR_BM - 1) / TC_PAIR_BM; a.tiles_n = (N + TC_PAIR_BN - 1) / TC_PAIR_BN; a.total = a.tiles_t * a.tiles_n;
+        a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
+        const bool staged = a.epi.mode != 0;
+        if (!configure_once(staged ? 6 : 5)) return -3;
+        const unsigned sm_pairs = persistent_grid(1 << 30, 1) / 2;          // SMs / 2
+        const unsigned clusters = (unsigned)a.total < sm_pairs ? (unsigned)a.total : sm_pairs;
+        const unsigned ctas = 2 * clusters;
+        if (a.epi.sig.ticket) a.epi.sig.nblocks = ctas;
+        if (staged) gemm_tc_pair_kernel<TC_PAIR_STG_STAGES, true><<<ctas, 320, tc_pair_smem_bytes<TC_PAIR_STG_STAGES, true>(), s>>>(mA, mW, a);
+        else gemm_tc_pair_kernel<TC_PAIR_STAGES, false><<<ctas, 320, tc_pair_smem_bytes<TC_PAIR_STAGES, false>(), s>>>(mA, mW, a);
+        return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    }
     const int BN = wide ? TC_WIDE_BN : TC_BN;
     CUtensorMap mA, mW;
     if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, BN)) return -3;
@@ -585,6 +802,13 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
 QW_API int qwk_gemm_tc_wide_min_n(int min_n) {
     const int old = g_wide_min_n;
     g_wide_min_n = min_n;
+    return old;
+}
+
+// Products at least `min_n` columns wide (and 256 rows tall) use the CTA-pair form (0 switches it off).
+QW_API int qwk_gemm_tc_pair_min_n(int min_n) {
+    const int old = g_pair_min_n;
+    g_pair_min_n = min_n;
     return old;
 }
 
