@@ -182,17 +182,37 @@ __device__ __forceinline__ void store_piece(const GemmTcArgs &a, long long c_off
 // chunks (chunk k at position k ^ (r & 7): no bank conflicts either way), then lanes 8i..8i+7 read row 4j + i back and
 // store its 128 bytes as one contiguous line - a peer store of whole 128-byte lines instead of 32 scattered 16-byte ones,
 // which is what NVLink carries at full rate.  `row0` is the output row of lane 0, `rows_ok` how many of the 32 rows exist.
+template <bool LOCAL = false>
 __device__ __forceinline__ void send_piece(const GemmTcArgs &a, float *stg, int lane, int row0, int rows_ok, int col0,
-                                           const uint32_t (&v)[32]) {
+                                           const uint32_t (&v)[32], long long c_off = 0) {
     float4 *s4 = reinterpret_cast<float4 *>(stg);
 #pragma unroll
     for (int k = 0; k < 8; ++k)
         s4[lane * 8 + (k ^ (lane & 7))] = make_float4(__uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
                                                       __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
     __syncwarp();
-    const int owner = a.epi.mode == 2 ? col0 / a.epi.cols_per_rank : 0;
     const int ch = lane & 7, rsub = lane >> 3;
     const int col = col0 + ch * 4;                                   // first of this lane's four columns
+    if constexpr (LOCAL) {
+        // the same transposition for this GPU's own fp32 output: whole lines instead of 16-byte pieces of 32 rows
+        const bool vec = ((a.ldc | col0) & 3) == 0 && col + 4 <= a.N;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + rsub;
+            const float4 val = s4[r * 8 + (ch ^ (r & 7))];
+            if (r >= rows_ok || col >= a.N) continue;
+            float *o = a.C32 + c_off + (long long)(row0 + r) * a.ldc + col;
+            if (vec) {
+                *reinterpret_cast<float4 *>(o) = val;
+            } else {
+                const float e[4] = {val.x, val.y, val.z, val.w};
+                for (int j = 0; j < 4 && col + j < a.N; ++j) o[j] = e[j];
+            }
+        }
+        __syncwarp();
+        return;
+    }
+    const int owner = a.epi.mode == 2 ? col0 / a.epi.cols_per_rank : 0;
     const int ccol = col - (a.epi.mode == 2 ? owner * a.epi.cols_per_rank : 0);
     const bool vec = ((a.epi.ld | col0) & 3) == 0 && col + 4 <= a.N;
 #pragma unroll
@@ -250,9 +270,13 @@ __device__ __forceinline__ void epilogue_role(const GemmTcArgs &a, uint32_t tmem
             uint32_t v[32];
             tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c0), v);
             if constexpr (STG) {
+                const int r0 = t.t0 + q * 32, rows_ok = min(32, min(a.T - r0, t.rows_valid - q * 32));
                 if (a.epi.mode) {
-                    const int r0 = t.t0 + q * 32;
-                    send_piece(a, stg, lane, r0, min(32, min(a.T - r0, t.rows_valid - q * 32)), t.n0 + c0, v);
+                    send_piece(a, stg, lane, r0, rows_ok, t.n0 + c0, v);
+                    continue;
+                }
+                if (a.C32) {
+                    send_piece<true>(a, stg, lane, r0, rows_ok, t.n0 + c0, v, t.c_off);
                     continue;
                 }
             }
@@ -547,9 +571,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1) gemm_tc_pair
                 tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TC_PAIR_BN + c0), v);
                 if (t.n0 + c0 >= a.N) continue;
                 if constexpr (STG) {
+                    const int r0 = t.t0 + q * 32;
                     if (a.epi.mode) {
-                        const int r0 = t.t0 + q * 32;
                         send_piece(a, stg, lane, r0, min(32, a.T - r0), t.n0 + c0, v);
+                        continue;
+                    }
+                    if (a.C32) {
+                        send_piece<true>(a, stg, lane, r0, min(32, a.T - r0), t.n0 + c0, v);
                         continue;
                     }
                 }
@@ -748,7 +776,8 @@ static bool configure_once(int which) {          // 0 dense 128-wide, 1 q4 group
 }
 
 static int g_wide_min_n = 1024;          // products at least this wide use the 128 x 256 tile form (0: never)
-static int g_pair_min_n = 0;             // products at least this wide (and 256 rows tall) use CTA pairs (0: never)
+static int g_pair_min_n = 1024;          // products at least this wide (and 256 rows tall) use CTA pairs (0: never)
+static int g_stage_local = 1;            // 1: fp32 output of the wide and pair forms also leaves through the staging buffers
 
 static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int T, int N, int K, int lda, int ldw, int ldc,
                       int out_bf16, cudaStream_t s) {
@@ -757,8 +786,10 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
     const int tiles_t = (T + TC_BM - 1) / TC_BM;
     const bool wide = g_wide_min_n > 0 && N >= g_wide_min_n && (N % TC_WIDE_BN == 0 || N % TC_WIDE_BN > TC_BN) &&
                       tiles_t * ((N + TC_WIDE_BN - 1) / TC_WIDE_BN) >= NUM_SMS / 2;
-    const bool pair = g_pair_min_n > 0 && N >= g_pair_min_n && T >= TC_PAIR_BM && (N % TC_PAIR_BN == 0 || N % TC_PAIR_BN > TC_BN) &&
-                      ((T + TC_PAIR_BM - 1) / TC_PAIR_BM) * ((N + TC_PAIR_BN - 1) / TC_PAIR_BN) >= NUM_SMS / 4;
+    // pairs pay when the padding of the 256 x 256 tiles stays under ~6 % of the work and there are tiles for every pair of SMs
+    const long long pad_t = (long long)((T + TC_PAIR_BM - 1) / TC_PAIR_BM) * TC_PAIR_BM, pad_n = (long long)((N + TC_PAIR_BN - 1) / TC_PAIR_BN) * TC_PAIR_BN;
+    const bool pair = g_pair_min_n > 0 && N >= g_pair_min_n && T >= TC_PAIR_BM && pad_t * pad_n * 100 <= (long long)T * N * 106 &&
+                      (pad_t / TC_PAIR_BM) * (pad_n / TC_PAIR_BN) >= NUM_SMS / 4;
     if (pair) {
         CUtensorMap mA, mW;
         if (!make_map(&mA, A, T, K, lda, TC_BM) || !make_map(&mW, W, N, K, ldw, TC_PAIR_BN / 2)) return -3;
@@ -767,7 +798,7 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
         a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
         a.tiles_t = (T + TC_PAIR_BM - 1) / TC_PAIR_BM; a.tiles_n = (N + TC_PAIR_BN - 1) / TC_PAIR_BN; a.total = a.tiles_t * a.tiles_n;
         a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-        const bool staged = a.epi.mode != 0;
+        const bool staged = a.epi.mode != 0 || (g_stage_local && !out_bf16);
         if (!configure_once(staged ? 6 : 5)) return -3;
         const unsigned sm_pairs = persistent_grid(1 << 30, 1) / 2;          // SMs / 2
         const unsigned clusters = (unsigned)a.total < sm_pairs ? (unsigned)a.total : sm_pairs;
@@ -785,7 +816,8 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
     a.T = T; a.N = N; a.K = K; a.ldc = ldc; a.err = g_err_ptr; a.tiles = nullptr;
     a.tiles_t = tiles_t; a.tiles_n = (N + BN - 1) / BN; a.total = a.tiles_t * a.tiles_n;
     a.ksplit = 1; a.kb_per = 0; a.c_split = 0;
-    const bool staged = a.epi.mode != 0;          // tiles that leave for other ranks go out as whole 128-byte lines
+    // tiles that leave for other ranks go out as whole 128-byte lines (optionally this GPU's own fp32 tiles of the wide form too)
+    const bool staged = a.epi.mode != 0 || (g_stage_local && wide && !out_bf16);
     if (!configure_once(staged ? (wide ? 4 : 3) : (wide ? 2 : 0))) return -3;
     const unsigned grid = persistent_grid(a.total, (wide || staged) ? 1 : 2);
     if (a.epi.sig.ticket) a.epi.sig.nblocks = grid;
@@ -802,6 +834,13 @@ static int gemm_plain(GemmTcArgs &a, const void *A, const void *W, void *C, int 
 QW_API int qwk_gemm_tc_wide_min_n(int min_n) {
     const int old = g_wide_min_n;
     g_wide_min_n = min_n;
+    return old;
+}
+
+// 1: the wide and pair forms write fp32 output through the staging buffers as well (whole lines per store instruction).
+QW_API int qwk_gemm_tc_stage_local(int on) {
+    const int old = g_stage_local;
+    g_stage_local = on;
     return old;
 }
 
