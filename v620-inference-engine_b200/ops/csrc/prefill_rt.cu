@@ -79,7 +79,7 @@ inline const void *bin_of(const PCtx &c, int l) {
 
 // Profile categories of a step (qwrt_prefill_profile).
 enum Cat { CAT_MIX_GLUE = 0, CAT_MIX_GEMM, CAT_PROJ, CAT_GDN, CAT_QSA, CAT_OUT, CAT_ROUTE, CAT_EXPERTS, CAT_COMBINE, CAT_PLE, CAT_OTHER,
-           CAT_MTP, CAT_GUARD, CAT_COUNT };
+           CAT_MTP, CAT_GUARD, CAT_GLUE_NORM, CAT_GLUE_MID, CAT_GLUE_MIX, CAT_COUNT };
 
 struct Step {
     Op fn;
@@ -145,7 +145,7 @@ struct Builder {
                 PF_TRY(1, qwk_gemm_bf16_tc_splitk(h_at(b.xn, L.r0, hc * SH), w.Wd, f_at(b.d, L.r0, b.hc_ld), L.n, R + w.n_inj, hc * SH,
                                                   hc * SH, hc * SH, b.hc_ld, b.hc_ksplit, (long long)b.cap * b.hc_ld, L.s));
             });
-            cur_cat = CAT_MIX_GLUE;
+            cur_cat = CAT_GLUE_MID;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -159,7 +159,7 @@ struct Builder {
                 const QwPrefillBufs &b = *c.b;
                 PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.u, L.r0, R), hc_of(c).Wu, f_at(b.g, L.r0, hc * SH), L.n, hc * SH, R, R, R, hc * SH, 0, L.s));
             });
-            cur_cat = CAT_MIX_GLUE;
+            cur_cat = CAT_GLUE_MIX;
             add([=](PCtx &c) {
                 const Lane &L = c.lane[l];
                 const QwPrefillBufs &b = *c.b;
@@ -177,7 +177,7 @@ struct Builder {
                                         inj_of(b, inj_prev, L.r0, hc), SH, hc, L.n, L.s));
         });
         guard(l, 0);
-        cur_cat = CAT_MIX_GLUE;
+        cur_cat = CAT_GLUE_NORM;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -192,7 +192,7 @@ struct Builder {
                                           b.hc_ld, 0, -1, 1, 1, b.hc_ld, L.s));
         });
         guard(l, 1);
-        cur_cat = CAT_MIX_GLUE;
+        cur_cat = CAT_GLUE_MID;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;
@@ -205,7 +205,7 @@ struct Builder {
             const QwPrefillBufs &b = *c.b;
             PF_TRY(1, qwk_gemm_bf16_tc(h_at(b.u, L.r0, R), hc_of(c).Wu, f_at(b.g, L.r0, hc * SH), L.n, hc * SH, R, R, R, hc * SH, 0, L.s));
         });
-        cur_cat = CAT_MIX_GLUE;
+        cur_cat = CAT_GLUE_MIX;
         add([=](PCtx &c) {
             const Lane &L = c.lane[l];
             const QwPrefillBufs &b = *c.b;

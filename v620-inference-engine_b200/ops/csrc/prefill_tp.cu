@@ -18,33 +18,45 @@ struct Peers {
     char *p[TP_MAX_RANKS];
 };
 
-// grid (T, hc), 256 threads.  X[t][s][:] += coef(t, s) * sum_r part_r[t][:] (parts added in rank order), then the row's
-// sum of squares goes to every rank.  SH % 4 == 0, SH <= 4096.
+// Kernels of this file that wait for or publish a collective run as a few fat CTAs (TP_CTAS_PER_SM per SM) that walk
+// their share of the rows: the wait (an acquire poll) and the publication (a system-wide fence and a ticket) are paid
+// once per CTA, not once per row - with one CTA per row a 4,096-token chunk paid 16,384 fences per launch, which cost
+// more than the kernel's work.
+constexpr int TP_CTAS_PER_SM = 8;
+constexpr int TP_PRENORM_ITEMS = 64;          // (row, stream) items per CTA of hc_prenorm_tp, at most
+
+// grid: CTAs that each own a contiguous range of `per` (row, stream) items, 256 threads.  X[t][s][:] += coef(t, s) *
+// sum_r part_r[t][:] (parts added in rank order), then the items' sums of squares go to every rank in one coalesced
+// store per CTA.  SH % 4 == 0, SH <= 4096, per <= TP_PRENORM_ITEMS.
 __global__ void __launch_bounds__(256) hc_prenorm_tp_kernel(float *X, const float *pend, int nparts, long long part_stride,
-                                                            int ld_pend, const float *inj, int SH, int hc, TpWait wait,
-                                                            Peers ssq_dst, int ranks, TpSignal sig) {
+                                                            int ld_pend, const float *inj, int SH, int hc, long long items, int per,
+                                                            TpWait wait, Peers ssq_dst, int ranks, TpSignal sig) {
     __shared__ float scratch[32];
-    const int t = blockIdx.x, s = blockIdx.y;
-    float4 *x = reinterpret_cast<float4 *>(X + ((long long)t * hc + s) * SH);
+    __shared__ float s_ssq[TP_PRENORM_ITEMS];
+    const long long first = (long long)blockIdx.x * per;
+    const int mine = (int)min((long long)per, items - first);
     const int n4 = SH >> 2;
-    float4 v[4];
+    const bool ok = pend ? tp_wait(wait) : true;
+    for (int k = 0; k < mine; ++k) {
+        const long long it = first + k;
+        const long long t = it / hc;
+        const int s = (int)(it - t * hc);
+        float4 *x = reinterpret_cast<float4 *>(X + it * SH);
+        float4 v[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = threadIdx.x + i * 256;
-        v[i] = c < n4 ? x[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    bool ok = true;
-    if (pend) {
-        ok = tp_wait(wait);
-        if (ok) {
-            const float coef = 2.f * sigmoidf_(inj[(long long)t * hc + s] / float(hc));
+        for (int i = 0; i < 4; ++i) {
+            const int c = threadIdx.x + i * 256;
+            v[i] = c < n4 ? x[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (pend && ok) {
+            const float coef = 2.f * sigmoidf_(inj[it] / float(hc));
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int c = threadIdx.x + i * 256;
                 if (c < n4) {
                     float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int r = 0; r < nparts; ++r) {
-                        const float4 q = __ldcg(reinterpret_cast<const float4 *>(pend + r * part_stride + (long long)t * ld_pend) + c);
+                        const float4 q = __ldcg(reinterpret_cast<const float4 *>(pend + r * part_stride + t * ld_pend) + c);
                         p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
                     }
                     v[i].x = fmaf(p.x, coef, v[i].x); v[i].y = fmaf(p.y, coef, v[i].y);
@@ -53,33 +65,38 @@ __global__ void __launch_bounds__(256) hc_prenorm_tp_kernel(float *X, const floa
                 }
             }
         }
-    }
-    float ss = 0.f;
+        float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-    ss = block_sum<256>(ss, scratch);
-    if (threadIdx.x == 0 && ok) {
+        for (int i = 0; i < 4; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        ss = block_sum<256>(ss, scratch);
+        if (threadIdx.x == 0) s_ssq[k] = ss;
+    }
+    __syncthreads();
+    if (ok && (int)threadIdx.x < mine) {
 #pragma unroll
         for (int d = 0; d < TP_MAX_RANKS; ++d)
-            if (d < ranks) reinterpret_cast<float *>(ssq_dst.p[d])[(long long)t * hc + s] = ss;
+            if (d < ranks) reinterpret_cast<float *>(ssq_dst.p[d])[first + threadIdx.x] = s_ssq[threadIdx.x];
     }
     tp_signal(sig);
 }
 
-// grid (T, hc), 256 threads.  xn[t][s][:] = bf16(X * w1 * rsqrt(sum_r ssq_r[t][s] / H + eps)).
+// grid: CTAs that stride over the (row, stream) items, 256 threads.  xn[t][s][:] = bf16(X * w1 * rsqrt(sum_r ssq_r[t][s] / H + eps)).
 __global__ void __launch_bounds__(256) hc_norm_tp_kernel(const float *X, const float *ssq_parts, int nparts, long long part_stride,
-                                                         const float *w1, int SH, int hc, int H, float eps, bf16 *xn, TpWait wait) {
+                                                         const float *w1, int SH, int hc, int H, float eps, bf16 *xn, long long items,
+                                                         TpWait wait) {
     if (!tp_wait(wait)) return;
-    const int t = blockIdx.x, s = blockIdx.y;
-    float tot = 0.f;
-    for (int r = 0; r < nparts; ++r) tot += __ldcg(ssq_parts + r * part_stride + (long long)t * hc + s);
-    const float rn = rsqrtf(tot / float(H) + eps);
-    const float4 *x = reinterpret_cast<const float4 *>(X + ((long long)t * hc + s) * SH);
-    const float4 *w4 = reinterpret_cast<const float4 *>(w1 + (long long)s * SH);
-    uint2 *o = reinterpret_cast<uint2 *>(xn + ((long long)t * hc + s) * SH);
-    for (int c = threadIdx.x; c < (SH >> 2); c += 256) {
-        const float4 v = x[c], w = w4[c];
-        o[c] = make_uint2(pack_bf16(v.x * w.x * rn, v.y * w.y * rn), pack_bf16(v.z * w.z * rn, v.w * w.w * rn));
+    for (long long it = blockIdx.x; it < items; it += gridDim.x) {
+        const int s = (int)(it % hc);
+        float tot = 0.f;
+        for (int r = 0; r < nparts; ++r) tot += __ldcg(ssq_parts + r * part_stride + it);
+        const float rn = rsqrtf(tot / float(H) + eps);
+        const float4 *x = reinterpret_cast<const float4 *>(X + it * SH);
+        const float4 *w4 = reinterpret_cast<const float4 *>(w1 + (long long)s * SH);
+        uint2 *o = reinterpret_cast<uint2 *>(xn + it * SH);
+        for (int c = threadIdx.x; c < (SH >> 2); c += 256) {
+            const float4 v = x[c], w = w4[c];
+            o[c] = make_uint2(pack_bf16(v.x * w.x * rn, v.y * w.y * rn), pack_bf16(v.z * w.z * rn, v.w * w.w * rn));
+        }
     }
 }
 
@@ -88,23 +105,22 @@ __global__ void __launch_bounds__(256) hc_norm_tp_kernel(const float *X, const f
 __global__ void __launch_bounds__(256) hc_mid_tp_kernel(const float *parts, int nparts, long long part_stride, int ld_d, int R,
                                                         int n_inj, int hc, bf16 *u, float *inj, long long total, TpWait wait) {
     if (!tp_wait(wait)) return;
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
     const int w = R + n_inj;
-    const long long t = i / w;
-    const int j = (int)(i - t * w);
-    float v = 0.f;
-    for (int r = 0; r < nparts; ++r) v += __ldcg(parts + r * part_stride + t * ld_d + j);
-    if (j < R) u[t * R + j] = __float2bfloat16(siluf_(v / float(hc)));
-    else inj[t * n_inj + (j - R)] = v;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / w;
+        const int j = (int)(i - t * w);
+        float v = 0.f;
+        for (int r = 0; r < nparts; ++r) v += __ldcg(parts + r * part_stride + t * ld_d + j);
+        if (j < R) u[t * R + j] = __float2bfloat16(siluf_(v / float(hc)));
+        else inj[t * n_inj + (j - R)] = v;
+    }
 }
 
 // g [T][SH*4] fp32 with columns ordered (c, s); this rank's block-input columns bin[t][col0 + c] = mean_s sigmoid(g) * xn
 // go to every rank's block-input matrix.  One thread per eight columns; SH % 8 == 0, col0 % 8 == 0, ld_bin % 8 == 0.
 __global__ void __launch_bounds__(256) hc_mix_tp_kernel(const float *g, const bf16 *xn, int SH, Peers bin_dst, int ranks,
                                                         int ld_bin, int col0, long long total8, TpSignal sig) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < total8) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (long long)gridDim.x * blockDim.x) {
         const int h8 = SH >> 3;
         const long long t = i / h8;
         const int c = (int)(i - t * h8) * 8;
@@ -137,8 +153,7 @@ __global__ void __launch_bounds__(256) hc_mix_tp_kernel(const float *g, const bf
 __global__ void __launch_bounds__(256) moe_combine_tp_kernel(const float *y, int ld_y, const int *inv, const float *pair_w,
                                                              int top_k, const float *shared, int H, int SH, Peers rs_dst,
                                                              long long total4, TpSignal sig) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < total4) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
         const int h4 = H >> 2;
         const long long t = i / h4;
         const int c = (int)(i - t * h4) * 4;
@@ -290,6 +305,11 @@ __global__ void amax_merge16_kernel(const float4 *gathered, int M, int ranks, in
 using namespace qw;
 
 static inline unsigned blocks_for(long long n, int per) { return (unsigned)((n + per - 1) / per); }
+// A grid of at most TP_CTAS_PER_SM CTAs per SM for `n` work items of `per` per CTA pass.
+static inline unsigned fat_grid(long long n, int per) {
+    const long long want = (n + per - 1) / per, cap = (long long)TP_CTAS_PER_SM * NUM_SMS;
+    return (unsigned)(want < 1 ? 1 : want < cap ? want : cap);
+}
 static bool tp_ok(const QwTp *tp) { return tp && tp->ranks >= 1 && tp->ranks <= TP_MAX_RANKS && tp->rank >= 0 && tp->rank < tp->ranks; }
 
 // Mixer step 1.  pend: null, a local [T][ld_pend] matrix (pend_kind < 0), or the reduce-scatter parts of kind pend_kind
@@ -312,8 +332,13 @@ QW_API int qwk_hc_prenorm_tp(void *tp_, float *X, const float *pend_local, int l
     }
     Peers dst{};
     for (int d = 0; d < tp->ranks; ++d) dst.p[d] = tp_part_on(tp, 0, d);
-    const TpSignal sig = tp_make_signal(tp, 0, (unsigned)T * hc);
-    hc_prenorm_tp_kernel<<<dim3(T, hc), 256, 0, s>>>(X, pend, nparts, stride, ld_pend, inj, SH, hc, w, dst, tp->ranks, sig);
+    const long long items = (long long)T * hc;
+    int per = (int)((items + (long long)TP_CTAS_PER_SM * NUM_SMS - 1) / ((long long)TP_CTAS_PER_SM * NUM_SMS));
+    if (per < 1) per = 1;
+    if (per > TP_PRENORM_ITEMS) per = TP_PRENORM_ITEMS;          // more rows than that: more CTAs, each still with one fence
+    const unsigned grid = blocks_for(items, per);
+    const TpSignal sig = tp_make_signal(tp, 0, grid);
+    hc_prenorm_tp_kernel<<<grid, 256, 0, s>>>(X, pend, nparts, stride, ld_pend, inj, SH, hc, items, per, w, dst, tp->ranks, sig);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -322,8 +347,9 @@ QW_API int qwk_hc_norm_tp(void *tp_, const float *X, const float *w1, int SH, in
                           cudaStream_t s) {
     QwTp *tp = (QwTp *)tp_;
     if (!tp_ok(tp) || (SH & 3)) return -1;
-    hc_norm_tp_kernel<<<dim3(T, hc), 256, 0, s>>>(X, (const float *)tp_parts(tp, 0), tp->ranks, tp->part_bytes[0] >> 2, w1, SH, hc, H,
-                                                  eps, (bf16 *)xn, tp_make_wait(tp, 0));
+    const long long items = (long long)T * hc;
+    hc_norm_tp_kernel<<<fat_grid(items, 1), 256, 0, s>>>(X, (const float *)tp_parts(tp, 0), tp->ranks, tp->part_bytes[0] >> 2, w1, SH, hc,
+                                                         H, eps, (bf16 *)xn, items, tp_make_wait(tp, 0));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -332,7 +358,7 @@ QW_API int qwk_hc_mid_tp(void *tp_, int ld_d, int R, int n_inj, int hc, void *u,
     QwTp *tp = (QwTp *)tp_;
     if (!tp_ok(tp)) return -1;
     const long long total = (long long)T * (R + n_inj);
-    hc_mid_tp_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const float *)tp_parts(tp, 1), tp->ranks, tp->part_bytes[1] >> 2, ld_d, R,
+    hc_mid_tp_kernel<<<fat_grid(total, 256), 256, 0, s>>>((const float *)tp_parts(tp, 1), tp->ranks, tp->part_bytes[1] >> 2, ld_d, R,
                                                             n_inj, hc, (bf16 *)u, inj, total, tp_make_wait(tp, 1));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -345,7 +371,7 @@ QW_API int qwk_hc_mix_tp(void *tp_, const float *g, const void *xn, int SH, int 
     Peers dst{};
     for (int d = 0; d < tp->ranks; ++d) dst.p[d] = (char *)tp->peer[d] + tp->off_buf[2];
     const long long total8 = (long long)T * (SH >> 3);
-    const unsigned grid = blocks_for(total8, 256);
+    const unsigned grid = fat_grid(total8, 256);
     const TpSignal sig = tp_make_signal(tp, 2, grid);
     hc_mix_tp_kernel<<<grid, 256, 0, s>>>(g, (const bf16 *)xn, SH, dst, tp->ranks, ld_bin, tp->rank * SH, total8, sig);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -361,7 +387,7 @@ QW_API int qwk_moe_combine_tp(void *tp_, const float *y, int ld_y, const int *in
     Peers dst{};
     for (int d = 0; d < tp->ranks; ++d) dst.p[d] = tp_part_on(tp, 3, d);
     const long long total4 = (long long)T * (H >> 2);
-    const unsigned grid = blocks_for(total4, 256);
+    const unsigned grid = fat_grid(total4, 256);
     const TpSignal sig = tp_make_signal(tp, 3, grid);
     moe_combine_tp_kernel<<<grid, 256, 0, s>>>(y, ld_y, inv, pair_w, top_k, shared, H, SH, dst, total4, sig);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -22,8 +22,9 @@ import torch
 from ..engine.engine import Engine, EngineOptions
 from ..models.config import ModelConfig
 
-CATS = ["mixer glue", "mixer GEMMs", "projection GEMM", "GDN conv + scan", "QSA prep / scores / select / attend", "out projection",
-        "router GEMM + routing + sort", "expert GEMMs + swiglu", "shared down + combine", "PLE", "other", "MTP pass", "guard waits"]
+CATS = ["mixer pre-norm (+ pending block output)", "mixer GEMMs", "projection GEMM", "GDN conv + scan", "QSA prep / scores / select / attend", "out projection",
+        "router GEMM + routing + sort", "expert GEMMs + swiglu", "shared down + combine", "PLE", "other", "MTP pass", "guard waits", "mixer norm (after the sums of squares)", "mixer mid (after the down projection)",
+        "mixer mix (+ block-input all-gather)"]
 
 
 def main():
