@@ -92,3 +92,36 @@ def test_spill_cache_with_conflicts_stays_exact():
     finally:
         settings.set_current(old)
     assert torch.equal(want[0][0], got[0][0]) and want[0][1] == got[0][1]
+
+
+@pytest.mark.parametrize("stage", [True, False])
+def test_token_major_prefill_into_spilled_pages_equals_resident(stage):
+    """Chunked token-major prefill whose later chunks lie in host pages: with the per-layer staging copy (the attention
+    reads the slot's host pages from a device buffer) and without it (the kernel gathers rows from host memory) the logits
+    and the following decode steps equal those of a fully resident slot bit for bit.  Slot 1 of 2, so that the slot's
+    offset into the host pool is not zero."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.utils import settings
+    prompt = [(i * 13 + 7) % 900 + 5 for i in range(700)]
+
+    def run(opts):
+        eng = Engine.synthetic(ModelConfig.tiny(), opts, device="cuda:0", exact=True, ple_rows=4096, seed=3)
+        lg = eng.prefill(1, prompt).clone()
+        t = int(lg.argmax())
+        seq = [t]
+        for _ in range(6):
+            t = eng.decode([1], [t])[0]
+            seq.append(t)
+        torch.cuda.synchronize()
+        eng.dm.check_error()
+        return eng, lg, seq
+    old = settings.get()
+    try:
+        settings.set_current(settings.Settings.from_env({}, spill_stage=stage))
+        _, lw, sw = run(EngineOptions(slots=2, slot_tokens=1024, use_graphs=False, prefill_chunk=128))
+        sp, lg, sg = run(EngineOptions(slots=2, slot_tokens=1024, use_graphs=False, prefill_chunk=128, dev_pages=2, host_pages=6))
+    finally:
+        settings.set_current(old)
+    assert sp.prefiller is not None and (("stage_k" in sp.prefiller.b) == stage)
+    assert torch.equal(lw, lg) and sw == sg

@@ -23,6 +23,7 @@ import torch
 from ..ops import lib as qlib
 from ..ops import structs as S
 from ..utils import settings
+from . import device_model as DM
 from .device_model import DeviceModel
 
 P = C.c_void_p
@@ -113,6 +114,15 @@ class Prefiller:
         self.rows_events = [None] * 3
         self.rows_turn = 0
         self.rows_host = self.rows_ring[0]
+        # KV spill: device copies of one slot's host pages of one layer; the attention of a chunk that reaches into the
+        # spilled part reads them here instead of gathering rows over the host link (one lane only: the copy follows the
+        # chunk's own key / value writes on the same stream)
+        if dm.n_host_pages and st.spill_stage:
+            spill = dm.max_pages - dm.dev_quota
+            row = sc.kvh_l * c.head_dim
+            self.b["stage_k"] = z((spill, DM.KV_PAGE, row), bf)
+            self.b["stage_v"] = z((spill, DM.KV_PAGE, row), bf)
+            self.lanes = 1
         self.side_stream = torch.cuda.Stream(device=dev) if self.lanes == 2 else None
         self.bufs = S.QwPrefillBufs()
         self._hook_cb = None
@@ -226,6 +236,7 @@ class Prefiller:
         for l in range(2):
             j.tp[l] = self.channels[min(l, len(self.channels) - 1)].ptr if self.tp else None
         j.T, j.lanes, j.base, j.want_logits = T, lanes, base, int(bool(want_logits))
+        j.slot = int(slot)
         j.n0 = n0
         j.layer_limit = -1 if self.layer_limit is None else int(self.layer_limit)
         j.mtp_rows, j.mtp_base, j.has_pending = len(mtp_tokens), mtp_base, int(pending is not None)

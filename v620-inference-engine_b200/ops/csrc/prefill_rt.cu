@@ -336,8 +336,29 @@ struct Builder {
             const QwState &st = c.md->st;
             const RowsAt r = rows_of(c, L);
             const int qi = w.state_index;
+            void *kh = st.k_host ? st.k_host[qi] : nullptr, *vh = st.v_host ? st.v_host[qi] : nullptr;
+            // KV spill: the slot's host pages of this layer (the rows this chunk just wrote among them) are copied into
+            // the staging buffers and the attention reads them there: a gather of ~2,000 rows per query over the host
+            // link costs more than one sequential copy of the pages (host pages of slot s are [s * spill, (s + 1) * spill))
+            if (kh && b.stage_k && b.stage_v && c.job->lanes == 1 && d.slots > 0) {
+                const int quota = d.n_dev_pages / d.slots, spill = d.max_pages - quota;
+                const int last_pos = (mtp ? c.job->mtp_base : c.job->base) + L.r0 + L.n;          // one past the last position
+                const int used = (last_pos + 255) / 256 - quota;                                   // host pages in use
+                if (spill > 0 && used > 0) {
+                    const long long page_bytes = 256ll * d.KVL * 256 * 2;
+                    const long long off = (long long)c.job->slot * spill * page_bytes, n = (long long)(used < spill ? used : spill) * page_bytes;
+                    if (cudaMemcpyAsync(b.stage_k, (const char *)kh + off, (size_t)n, cudaMemcpyHostToDevice, L.s) != cudaSuccess ||
+                        cudaMemcpyAsync(b.stage_v, (const char *)vh + off, (size_t)n, cudaMemcpyHostToDevice, L.s) != cudaSuccess) {
+                        if (c.err == 0) c.err = -2000 - __LINE__;
+                        return;
+                    }
+                    c.launches += 2;
+                    kh = (char *)b.stage_k - off;
+                    vh = (char *)b.stage_v - off;
+                }
+            }
             PF_TRY(1, qwk_qsa_attend_mma(f_at(b.q, L.r0, d.QL * 256), d.QL, d.KVL, L.n, r.slot, r.pos, st.k_dev[qi], st.v_dev[qi],
-                                         st.k_host ? st.k_host[qi] : nullptr, st.v_host ? st.v_host[qi] : nullptr, d.n_dev_pages,
+                                         kh, vh, d.n_dev_pages,
                                          st.page_table, d.max_pages, i_at(b.sel, L.r0, d.idx_topk), b.sel_n + L.r0, d.idx_topk, d.idx_ratio,
                                          f_at(b.proj, L.r0, b.proj_ld), b.proj_ld, h_at(b.o, L.r0, b.o_ld), L.s));
         });

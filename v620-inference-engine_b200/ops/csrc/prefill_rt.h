@@ -57,6 +57,9 @@ typedef struct QwPrefillBufs {
     // vision rows: X[over_rows[j]] = over_emb[j] (fp32 [n_over][H])
     const int *over_rows;
     const float *over_emb;
+    // KV spill: device copies of one slot's host pages of one layer (K and V), filled before a QSA layer's attention
+    // so that the attention kernel gathers its rows from device memory (null: the kernels read the host pages directly)
+    void *stage_k, *stage_v;
     int cap, hc_ld, hc_ksplit, nrs_ld, proj_ld, o_ld, ple_ld, max_tiles;
     long long gdn_scratch_lane;
 } QwPrefillBufs;
@@ -80,6 +83,8 @@ typedef struct QwPrefillJob {
     int n0;                    // two lanes: rows of lane 0 (lane 1 takes the rest)
     QwPrefillHook hook;        // optional: called (after the stream work is enqueued) with each block input
     void *hook_user;
+    int slot;                  // the chunk's slot (host copy of the row table's value)
+    int pad_;
 } QwPrefillJob;
 
 // Enqueues the chunk of every job (one job per rank; more than one only when several ranks are emulated in one

@@ -89,7 +89,7 @@ PREFILL_PTR_FIELDS = (
     "t13", "t2", "gdn_scratch", "ple_e", "ple_kv", "ple_send", "ple_red", "ple_gv", "ple_nc",
     "Xm", "hn", "en", "fh", "fe", "mtp_ssq", "mtp_tok", "hid_out", "amax16",
     "tokens", "slot", "pos", "run_start", "run_len", "ctx3", "m_slot", "m_pos", "m_run_start", "m_run_len",
-    "over_rows", "over_emb")
+    "over_rows", "over_emb", "stage_k", "stage_v")
 PREFILL_INT_FIELDS = ("cap", "hc_ld", "hc_ksplit", "nrs_ld", "proj_ld", "o_ld", "ple_ld", "max_tiles")
 
 
@@ -105,7 +105,7 @@ class QwPrefillJob(C.Structure):
     _fields_ = [("md", C.POINTER(QwModel)), ("b", C.POINTER(QwPrefillBufs)), ("tp", P * 2), ("stream", P * 2),
                 ("T", C.c_int), ("lanes", C.c_int), ("base", C.c_int), ("want_logits", C.c_int), ("layer_limit", C.c_int),
                 ("mtp_rows", C.c_int), ("mtp_base", C.c_int), ("has_pending", C.c_int), ("n_over", C.c_int), ("n0", C.c_int),
-                ("hook", PREFILL_HOOK), ("hook_user", P)]
+                ("hook", PREFILL_HOOK), ("hook_user", P), ("slot", C.c_int), ("pad_", C.c_int)]
 
 
 def check_prefill_structs(lib) -> None:

@@ -104,6 +104,7 @@ class Session:
         self.boundary = -1
         self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
         self.store = H.BlockStore(self.io.state_layout_id(), engine.dm.sc.ranks, host_cache_bytes, disk_cache_dir, disk_cache_bytes)
+        self.store_on = host_cache_bytes > 0 or bool(disk_cache_dir)          # no tier to keep blocks in: nothing is exported
         # pinned units for the blocks on their way between the engine and the store (one block per unit)
         self.pool = None
         if torch.cuda.is_available():
@@ -345,6 +346,8 @@ class Session:
         """Store the slot's new full blocks; a snapshot of the recurrent state goes with the last one when the slot
         ends exactly on its boundary."""
         si, sl = self.slots[slot], self.e.slot[slot]
+        if not self.store_on:
+            return
         t0 = time.time()
         full = sl.n // BLOCK
         parent = si.block_keys[-1] if si.block_keys else self.store.root

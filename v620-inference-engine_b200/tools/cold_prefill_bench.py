@@ -61,7 +61,7 @@ def main():
             st = ses.cache_stats()
             rows.append({"config": name, "rep": rep, "seconds": round(dt, 3), "tok_s": round(a.tokens / dt), "save_s": round(tm["save_s"], 3),
                          "pin_wait_s": round(tm["pin_wait_s"], 3), "arenas": pool.get("arenas"), "pin_seconds": round(pool.get("pin_seconds", 0.0), 3),
-                         "unit_waits": pool.get("waits"), "cache_ram_bytes": st.get("ram_bytes"), "cache_disk_bytes": st.get("disk_bytes"), "kilojoules": en.get("kilojoules"),
+                         "unit_waits": pool.get("waits"), "cache_ram_bytes": max(0, int(st.get("ram_bytes") or 0)) if name != "nostore" else 0, "cache_disk_bytes": st.get("disk_bytes"), "kilojoules": en.get("kilojoules"),
                          "avg_w": en.get("avg_w")})
             print(json.dumps(rows[-1]), flush=True)
             ses.slots[0].busy = False

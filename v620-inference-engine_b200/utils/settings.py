@@ -47,6 +47,7 @@ class Settings:
     kv_spill: bool = False              # QW_KV_SPILL / QW_SPILL / QW_SLOT_SPILL
     spill_cache_mb: int = 256           # QW_SPILL_CACHE_MB: device cache in front of the host KV pages (0 = none)
     spill_cache_stats: bool = False     # QW_SPILL_CACHE_STATS: count hits and misses
+    spill_stage: bool = True            # QW_SPILL_STAGE: prefill attention reads spilled pages from a device copy made per layer
     spill_policy: str = "auto"          # QW_SPILL_POLICY: auto | bind | preferred | interleave | process
     prefill_chunk: int = 4096           # QW_PREFILL_CHUNK
     prefill_piece: int = 2048           # QW_PREFILL_PIECE
