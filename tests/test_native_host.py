@@ -201,3 +201,19 @@ def test_block_store_prefetch_loads_disk_blocks_in_the_background(tmp_path):
     assert st.loads_pending() == 0 and all(st.info(k)["in_ram"] for k in path[:3])
     assert st.prefetch(path[:depth]) == 0                  # nothing left to read
     assert st.get(path[1]) == bytes([66]) * 8192
+
+
+def test_block_store_snapshot_by_address_round_trip():
+    """Snapshot payloads given and taken by address (the engine's pinned snapshot buffer): same bytes back, a buffer that is
+    too small is refused, a block without a snapshot answers -1."""
+    st = H.BlockStore(7, 1, 8 << 20)
+    toks = list(range(512))
+    k0 = st.save_block(st.root, 0, toks[:256], b"k" * 64)
+    k1 = st.save_block(k0, 256, toks[256:], b"k" * 64)
+    src = (np.arange(5000, dtype=np.uint32) * 2654435761 % 251).astype(np.uint8)
+    assert st.save_snapshot_from(k1, src.ctypes.data, src.nbytes, anchor=False)
+    out = np.zeros(6000, dtype=np.uint8)
+    assert st.get_snapshot_into(k1, out) == 5000 and bytes(out[:5000]) == bytes(src)
+    assert st.get_snapshot_into(k1, np.zeros(100, dtype=np.uint8)) == -1
+    assert st.get_snapshot_into(k0, out) == -1
+    assert st.get(k1, snapshot=True)[0] == bytes(src)

@@ -153,6 +153,34 @@ class StateIO:
     def recurrent_bytes(self) -> int:
         return sum(t.numel() * 4 for t in self._recurrent_tensors(0))
 
+    def _recurrent_pinned(self) -> torch.Tensor:
+        """One pinned buffer of ``recurrent_bytes`` for snapshots on their way to and from the host store."""
+        if getattr(self, "_rec_pin", None) is None:
+            self._rec_pin = torch.empty(self.recurrent_bytes(), dtype=torch.uint8).pin_memory()
+        return self._rec_pin
+
+    def export_recurrent_pinned(self, slot: int):
+        """The slot's recurrent state in the pinned snapshot buffer (asynchronous copies, then one wait).  Returns
+        (address, bytes); the buffer is reused by the next export or import."""
+        pin = self._recurrent_pinned().view(torch.float32)
+        off = 0
+        for t in self._recurrent_tensors(slot):
+            n = t.numel()
+            pin[off:off + n].view(t.shape).copy_(t, non_blocking=True)
+            off += n
+        self.sync()
+        return pin.data_ptr(), off * 4
+
+    def import_recurrent_pinned(self, slot: int) -> None:
+        """The reverse: the pinned snapshot buffer (filled by the caller) becomes the slot's recurrent state."""
+        pin = self._recurrent_pinned().view(torch.float32)
+        off = 0
+        for dst in self._recurrent_tensors(slot):
+            n = dst.numel()
+            dst.copy_(pin[off:off + n].view(dst.shape), non_blocking=True)
+            off += n
+        self.sync()
+
     def export_recurrent(self, slot: int) -> bytes:
         return torch.cat([t.reshape(-1) for t in self._recurrent_tensors(slot)]).cpu().numpy().tobytes()
 

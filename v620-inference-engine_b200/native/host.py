@@ -173,6 +173,19 @@ class BlockStore:
         return lib().qwh_store_save_snapshot(self.s, key, C.addressof(buf), len(snap), None if lg is None else lg.ctypes.data,
                                              0 if lg is None else lg.size, int(anchor)) == 0
 
+    def save_snapshot_from(self, key: int, addr: int, nbytes: int, anchor: bool = False) -> bool:
+        """``save_snapshot`` with the payload given by address (pinned memory the engine exported into)."""
+        return lib().qwh_store_save_snapshot(self.s, key, addr, nbytes, None, 0, int(anchor)) == 0
+
+    def get_snapshot_into(self, key: int, out: np.ndarray) -> int:
+        """Copy a block's snapshot payload into ``out`` (uint8).  Returns its size, or -1 when there is none or it does not fit."""
+        nl = C.c_int(0)
+        size = lib().qwh_store_get(self.s, key, 1, None, 0, None, 0, C.byref(nl))
+        if size < 0 or size > out.nbytes:
+            return -1
+        lib().qwh_store_get(self.s, key, 1, out.ctypes.data, size, None, 0, C.byref(nl))
+        return int(size)
+
     def lookup(self, tokens: Sequence[int]) -> Tuple[List[int], int]:
         t = _i32(tokens)
         keys = (C.c_ulonglong * (len(t) // self.BLOCK + 2))()

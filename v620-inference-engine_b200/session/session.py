@@ -228,11 +228,18 @@ class Session:
                     ok = False
                     break
                 self.io.import_kv(slot, bi, kv)
-        snap = self.store.get(path[depth - 1], snapshot=True) if ok else None
-        if not ok or snap is None or len(snap[0]) != self.io.recurrent_bytes():
-            self.e.reset(slot)           # a payload vanished (budget) or does not fit: recompute
-            return 0
-        self.io.import_recurrent(slot, snap[0])
+        if ok and self.pool is not None:          # through the pinned snapshot buffer: no pageable copies
+            got = self.store.get_snapshot_into(path[depth - 1], self.io._recurrent_pinned().numpy())
+            if got != self.io.recurrent_bytes():
+                self.e.reset(slot)
+                return 0
+            self.io.import_recurrent_pinned(slot)
+        else:
+            snap = self.store.get(path[depth - 1], snapshot=True) if ok else None
+            if not ok or snap is None or len(snap[0]) != self.io.recurrent_bytes():
+                self.e.reset(slot)           # a payload vanished (budget) or does not fit: recompute
+                return 0
+            self.io.import_recurrent(slot, snap[0])
         self.e.slot[slot].tokens = toks[:stored]
         self.e.slot[slot].mtp_hidden = None
         si.block_keys = list(path[:depth])
@@ -385,7 +392,11 @@ class Session:
                 parent = key
         if snapshot and si.block_keys and len(si.block_keys) * BLOCK == sl.n:
             anchor = sl.n < len(si.prompt) and si.prompt[sl.n] == self.boundary
-            self.store.save_snapshot(si.block_keys[-1], self.io.export_recurrent(slot), None, anchor)
+            if self.pool is not None:
+                addr, nb = self.io.export_recurrent_pinned(slot)
+                self.store.save_snapshot_from(si.block_keys[-1], addr, nb, anchor)
+            else:
+                self.store.save_snapshot(si.block_keys[-1], self.io.export_recurrent(slot), None, anchor)
         si.timing["save_s"] += time.time() - t0
 
     def sample_prompt(self, slot: int, p: SamplingParams) -> Tuple[int, float]:

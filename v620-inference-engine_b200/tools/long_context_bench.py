@@ -113,6 +113,7 @@ def main():
     torch.cuda.synchronize()
     out["prefix_cold_s"] = round(time.time() - t1, 3)
     out["prefix_save_s"] = round(ses.slots[sa].timing["save_s"], 3)
+    out["prefix_pin_wait_s"] = round(ses.slots[sa].timing["pin_wait_s"], 3)
     sb = a.slots - 3 if a.slots >= 4 else short
     eng.reset(sb)
     ses.slots[sb].busy = True
