@@ -196,9 +196,36 @@ __global__ void __launch_bounds__(256, 3) gdn_chunk_prep_kernel(GdnChunkArgs a) 
 // split keeps the number of blocks up.  Every output element's sum runs over k in the same order whatever NC is.
 template <int NC>
 constexpr int apply_smem() {
-    return (CD * (NC + 8) + 2 * CC * LDA + CC * LDT + CC * LDP + CC * (NC + 8) + 2 * CC) * 4;
+    return (CD * (NC + 8) + 2 * CC * LDA + CC * LDT + 2 * CC * LDP + CC * (NC + 8) + 2 * CC) * 4;
 }
 
+// 16-byte asynchronous copy global -> shared; `ok` false: the destination is zero-filled (rows past the run's end).
+__device__ __forceinline__ void cp_async16(float *dst, const float *src, bool ok) {
+    const unsigned int d = (unsigned int)__cvta_generic_to_shared(dst);
+    const int n = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Rows [m0, m0+64) x 128 floats at column offset col of the qkv rows -> shared tile of stride ld, asynchronously; rows
+// >= M become zero.  256 threads.
+__device__ __forceinline__ void load_tile_async(float *dst, int ld, const float *qkv, int qkv_l, int col, int m0, int M, int tid) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * 256;          // float4 index: 64 rows x 32
+        const int r = idx >> 5, c4 = idx & 31;
+        const bool ok = m0 + r < M;
+        cp_async16(dst + r * ld + c4 * 4, qkv + (long long)(ok ? m0 + r : 0) * qkv_l + col + c4 * 4, ok);
+    }
+}
+
+// The kernel walks the chunks in order; what a chunk needs from global memory is in shared memory before its products
+// start: Wk, Q, P and the cumulative log decays of chunk c + 1 are fetched (cp.async) into the tiles that chunk c's first
+// product has finished with, under chunk c's second and third products; K of chunk c, needed only by the third
+// product, is fetched under the first two.  The chain of 64 chunk steps of a 4,096-token run is what bounds the
+// kernel (it does not shorten with fewer heads per rank), so nothing on it waits for a global load.
 template <int NC>
 __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
     constexpr int LDS = NC + 8;          // [.][NC] B-operand tile (state slice, U)
@@ -209,44 +236,55 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
     float *Wks = Ss + CD * LDS;          // [64][LDA]
     float *Qs = Wks + CC * LDA;          // [64][LDA]
     float *Ks = Qs + CC * LDA;           // [64][LDT]      read transposed in the state update
-    float *Ps = Ks + CC * LDT;           // [64][LDP]
-    float *Us = Ps + CC * LDP;           // [64][LDS]
-    float *eg = Us + CC * LDS;           // [64] exp(g_t)
-    float *ek = eg + CC;                 // [64] exp(g_C - g_t)
+    float *Ps = Ks + CC * LDT;           // [2][64][LDP]   chunk c in buffer c & 1
+    float *Us = Ps + 2 * CC * LDP;       // [64][LDS]
+    float *gb = Us + CC * LDS;           // [2][64]        cumulative log decay g_t of the chunk
     const int vh = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int qkv_l = (2 * a.KL + a.VL) * CD;
     const int kh = h / (a.VL / a.KL);
     const int slot = a.slot[0];
     float *Sg = a.S + ((long long)slot * a.VL + h) * CD * CD + vh * NC;
+    const int nch = (a.M + CC - 1) / CC;
+    // what chunk `ch` needs before its first product: Q, Wk, P, g
+    auto fetch_front = [&](int ch) {
+        const long long cb = (long long)ch * a.VL + h;
+        load_tile_async(Qs, LDA, a.qkv, qkv_l, kh * CD, ch * CC, a.M, tid);
+        load_tile_async(Wks, LDA, a.Wk + cb * CC * CD, CD, 0, 0, CC, tid);
+        const float *Pg = a.P + cb * CC * CC;
+        float *Pd = Ps + (ch & 1) * CC * LDP;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256;      // float4 index: 64 rows x 16
+            const int r = idx >> 4, c4 = idx & 15;
+            cp_async16(Pd + r * LDP + c4 * 4, Pg + r * CC + c4 * 4, true);
+        }
+        if (tid < CC / 4) cp_async16(gb + (ch & 1) * CC + tid * 4, a.G + cb * CC + tid * 4, true);
+    };
+    fetch_front(0);
+    cp_async_commit();
     for (int idx = tid; idx < CD * (NC / 4); idx += 256) {      // float4 index: 128 rows x NC / 4
         const int r = idx / (NC / 4), c4 = idx % (NC / 4);
         *reinterpret_cast<float4 *>(Ss + r * LDS + c4 * 4) = *reinterpret_cast<const float4 *>(Sg + r * CD + c4 * 4);
     }
-    const int nch = (a.M + CC - 1) / CC;
     const int r0 = (w & 3) * 16, c0 = (w >> 2) * (NC / 2);
     for (int ch = 0; ch < nch; ++ch) {
         const int m0 = ch * CC;
         const long long cb = (long long)ch * a.VL + h;
-        load_tile(Qs, LDA, a.qkv, qkv_l, kh * CD, m0, a.M, tid);
-        load_tile(Ks, LDT, a.qkv, qkv_l, (a.KL + kh) * CD, m0, a.M, tid);
-        load_tile(Wks, LDA, a.Wk + cb * CC * CD, CD, 0, 0, CC, tid);
-        {
-            const float *Pg = a.P + cb * CC * CC;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int idx = tid + i * 256;      // float4 index: 64 rows x 16
-                const int r = idx >> 4, c4 = idx & 15;
-                *reinterpret_cast<float4 *>(Ps + r * LDP + c4 * 4) = *reinterpret_cast<const float4 *>(Pg + r * CC + c4 * 4);
-            }
-        }
-        if (tid < CC) {
-            const float *Gg = a.G + cb * CC;
-            const float gt = Gg[tid], gC = Gg[CC - 1];
-            eg[tid] = __expf(gt);
-            ek[tid] = __expf(gC - gt);
-        }
+        const float *Pc = Ps + (ch & 1) * CC * LDP, *gc = gb + (ch & 1) * CC;
+        load_tile_async(Ks, LDT, a.qkv, qkv_l, (a.KL + kh) * CD, m0, a.M, tid);      // for the third product
+        cp_async_commit();
+        cp_async_wait<1>();              // everything but K: this chunk's Q, Wk, P, g are in
         __syncthreads();
+        // Wv of this thread's U elements: issued now, used after the first product
+        const float *Wvg = a.Wv + cb * CC * CD + vh * NC;
+        float2 wv0[NT], wv1[NT];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const int c = c0 + n * 8 + 2 * t;
+            wv0[n] = *reinterpret_cast<const float2 *>(Wvg + (r0 + g) * CD + c);
+            wv1[n] = *reinterpret_cast<const float2 *>(Wvg + (r0 + g + 8) * CD + c);
+        }
         // U = Wv - Wk S0 and Q S0: warp tile 16 rows x NC / 2 value columns
         float accW[NT][4], accO[NT][4];
 #pragma unroll
@@ -267,24 +305,26 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             }
         }
         {
-            const float *Wvg = a.Wv + cb * CC * CD + vh * NC;
-            const float e0 = eg[r0 + g], e1 = eg[r0 + g + 8];
+            const float e0 = __expf(gc[r0 + g]), e1 = __expf(gc[r0 + g + 8]);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const int c = c0 + n * 8 + 2 * t;
-                const float2 v0 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g) * CD + c);
-                const float2 v1 = *reinterpret_cast<const float2 *>(Wvg + (r0 + g + 8) * CD + c);
-                *reinterpret_cast<float2 *>(Us + (r0 + g) * LDS + c) = make_float2(v0.x - accW[n][0], v0.y - accW[n][1]);
-                *reinterpret_cast<float2 *>(Us + (r0 + g + 8) * LDS + c) = make_float2(v1.x - accW[n][2], v1.y - accW[n][3]);
+                *reinterpret_cast<float2 *>(Us + (r0 + g) * LDS + c) = make_float2(wv0[n].x - accW[n][0], wv0[n].y - accW[n][1]);
+                *reinterpret_cast<float2 *>(Us + (r0 + g + 8) * LDS + c) = make_float2(wv1[n].x - accW[n][2], wv1[n].y - accW[n][3]);
                 accO[n][0] *= e0; accO[n][1] *= e0;
                 accO[n][2] *= e1; accO[n][3] *= e1;
             }
         }
-        __syncthreads();
+        __syncthreads();                 // U is complete; the Q and Wk tiles are free
+        const bool more = ch + 1 < nch;
+        if (more) {
+            fetch_front(ch + 1);
+            cp_async_commit();
+        }
         // O += P U (P is zero above the diagonal: k tiles past the warp's rows are skipped)
         for (int k0 = 0; k0 < r0 + 16; k0 += 8) {
             uint32_t fp[4];
-            lda_frag(fp, Ps, LDP, r0, k0, g, t);
+            lda_frag(fp, Pc, LDP, r0, k0, g, t);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const float *p = Us + (k0 + t) * LDS + c0 + n * 8 + g;
@@ -298,10 +338,14 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             if (ra < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)ra * a.VL * CD + c) = make_float2(accO[n][0], accO[n][1]);
             if (rb < a.M) *reinterpret_cast<float2 *>(a.Oraw + (long long)rb * a.VL * CD + c) = make_float2(accO[n][2], accO[n][3]);
         }
+        if (more) cp_async_wait<1>();    // K of this chunk (the next chunk's front tiles may still be on their way)
+        else cp_async_wait<0>();
+        __syncthreads();
         // S1 = exp(g_C) S0 + (diag(ek) K)^T U: warp w owns state rows 16w .. 16w+15, all NC columns
         {
             const int i0 = w * 16;
-            const float eC = eg[CC - 1];
+            const float gC = gc[CC - 1];
+            const float eC = __expf(gC);
             float accS[NS][4];
 #pragma unroll
             for (int n = 0; n < NS; ++n) {
@@ -312,7 +356,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_apply_kernel(GdnChunkArgs a) {
             }
 #pragma unroll 2
             for (int k0 = 0; k0 < CC; k0 += 8) {
-                const float ea = ek[k0 + t], eb = ek[k0 + t + 4];
+                const float ea = __expf(gC - gc[k0 + t]), eb = __expf(gC - gc[k0 + t + 4]);
                 const float *p = Ks + (k0 + t) * LDT + i0 + g;      // A[i][s] = K[s][i] ek[s]
                 uint32_t fa[4];
                 fa[0] = tf32(p[0] * ea);
