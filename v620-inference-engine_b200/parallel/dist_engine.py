@@ -121,7 +121,8 @@ def attach_tp(eng: Engine, group=None, lanes: int = 0) -> None:
     dm = eng.dm
     if eng.opts.prefill_chunk <= 0 or dm.sc.ranks == 1:
         return
-    lanes = lanes or settings.get().prefill_lanes or 2
+    # measured per 4,096-token chunk, one lane / two lanes: 132.6 / 142.7 ms on 2 GPUs, 106.9 / 107.1 on 4, 95.9 / 93.2 on 8
+    lanes = lanes or settings.get().prefill_lanes or (2 if dm.sc.ranks >= 8 else 1)
     rows = min(eng.opts.prefill_chunk, max(256, dm.slot_tokens))
     eng.tp_channels = [tp_channel.make_symmetric(dm.cfg, dm.sc, rows, dm.dev, bool(dm.cfg.mtp), group) for _ in range(lanes)]
     eng.prefiller = None

@@ -88,7 +88,7 @@ def main():
     eng = Engine.from_weights(cfg, w, table, popts, ranks=world, rank=rank, device=dev)
     attach_p2p(eng)
     set_fused(True)
-    attach_tp(eng)
+    attach_tp(eng, lanes=2)          # both micro-batch lanes, whatever the default of this rank count is
     single = Engine.from_weights(cfg, w, table, popts, device=dev)
     prompt = torch.randint(0, cfg.vocab, (300,), generator=torch.Generator().manual_seed(9)).tolist()
     lg = eng.prefill(0, prompt).clone()

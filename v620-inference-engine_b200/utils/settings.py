@@ -55,7 +55,7 @@ class Settings:
     moe_dequant_scratch: bool = False   # QW_MOE_DEQUANT_SCRATCH: token-major prefill converts a layer's q4 experts to bf16 before its GEMMs
     gdn_sequential: bool = False        # QW_GDN_SEQUENTIAL: token-major prefill scans GDN layers row by row (not chunked)
     prefill_py: bool = False            # QW_PREFILL_PY: token-major prefill scheduled from Python, kernel by kernel (one GPU; the native runtime is the default)
-    prefill_lanes: int = 0              # QW_PREFILL_LANES: micro-batches per chunk, 1 or 2 (0 = two on several GPUs, one on one)
+    prefill_lanes: int = 0              # QW_PREFILL_LANES: micro-batches per chunk, 1 or 2 (0 = two on eight GPUs, one below)
     spec_max_rows: int = 8              # QW_SPEC_MAX_ROWS: rows of one verification step
     weight_cache_dir: str = ""          # QW_WEIGHT_CACHE_DIR
     ple_dir: str = ""                   # QW_PLE_DIR
