@@ -92,7 +92,7 @@ def test_gemm_tc_split_k_partials_add_up(T, N, K, ks):
     assert err < 2e-3, err
 
 
-@pytest.mark.parametrize("T,N,K", [(1024, 2048, 256), (1500, 512, 192)])
+@pytest.mark.parametrize("T,N,K", [(1024, 2048, 256), (1500, 512, 192), (4096, 2560, 1536)])      # the last: the out projection of a chunk on 4 ranks (CTA-pair form)
 def test_gemm_tc_reduce_scatter_epilogue_on_emulated_ranks(T, N, K):
     """The tensor-parallel forms of the product on four ranks emulated on one GPU: with the reduce-scatter epilogue every
     rank's tiles land in the column owner's receive buffer and the owners' rank-order sums equal the sum of the full

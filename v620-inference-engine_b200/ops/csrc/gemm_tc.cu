@@ -212,28 +212,35 @@ __device__ __forceinline__ void send_piece(const GemmTcArgs &a, float *stg, int 
         __syncwarp();
         return;
     }
-    const int owner = a.epi.mode == 2 ? col0 / a.epi.cols_per_rank : 0;
-    const int ccol = col - (a.epi.mode == 2 ? owner * a.epi.cols_per_rank : 0);
-    const bool vec = ((a.epi.ld | col0) & 3) == 0 && col + 4 <= a.N;
+    // the lane's eight float4 (rows rsub, rsub + 4, ...) come out of shared memory once; the destination is chosen once
+    // per piece (reduce-scatter: the owner of these columns) or per rank (all-reduce), not once per store
+    float4 val[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = 4 * i + rsub;
-        const float4 val = s4[r * 8 + (ch ^ (r & 7))];
-        if (r >= rows_ok || col >= a.N) continue;
-        const long long off = (long long)(row0 + r) * a.epi.ld + ccol;
+        val[i] = s4[r * 8 + (ch ^ (r & 7))];
+    }
+    __syncwarp();
+    if (col >= a.N) return;
+    const bool rs = a.epi.mode == 2;
+    const int owner = rs ? col0 / a.epi.cols_per_rank : 0;
+    const int ccol = col - (rs ? owner * a.epi.cols_per_rank : 0);
+    const bool vec = ((a.epi.ld | col0) & 3) == 0 && col + 4 <= a.N;
+    const long long off0 = (long long)(row0 + rsub) * a.epi.ld + ccol, step = 4ll * a.epi.ld;
+    const int d0 = rs ? owner : 0, d1 = rs ? owner + 1 : a.epi.ranks;
+    for (int d = d0; d < d1; ++d) {
+        float *o = tp_pick(a.epi.dst, d) + off0;
 #pragma unroll
-        for (int d = 0; d < TP_MAX_RANKS; ++d) {
-            if (d >= a.epi.ranks || (a.epi.mode == 2 && d != owner)) continue;
-            float *o = a.epi.dst[d] + off;
+        for (int i = 0; i < 8; ++i) {
+            if (4 * i + rsub >= rows_ok) break;
             if (vec) {
-                *reinterpret_cast<float4 *>(o) = val;
+                *reinterpret_cast<float4 *>(o + i * step) = val[i];
             } else {
-                const float e[4] = {val.x, val.y, val.z, val.w};
-                for (int j = 0; j < 4 && col + j < a.N; ++j) o[j] = e[j];
+                const float e[4] = {val[i].x, val[i].y, val[i].z, val[i].w};
+                for (int j = 0; j < 4 && col + j < a.N; ++j) o[i * step + j] = e[j];
             }
         }
     }
-    __syncwarp();
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
