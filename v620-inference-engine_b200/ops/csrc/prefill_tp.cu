@@ -25,51 +25,43 @@ struct Peers {
 constexpr int TP_CTAS_PER_SM = 8;
 constexpr int TP_PRENORM_ITEMS = 64;          // (row, stream) items per CTA of hc_prenorm_tp, at most
 
-// grid: CTAs that each own a contiguous range of `per` (row, stream) items, 256 threads.  X[t][s][:] += coef(t, s) *
-// sum_r part_r[t][:] (parts added in rank order), then the items' sums of squares go to every rank in one coalesced
-// store per CTA.  SH % 4 == 0, SH <= 4096, per <= TP_PRENORM_ITEMS.
+// grid: CTAs that each own a contiguous range of `per` (row, stream) items, 256 threads = 8 warps, one item per warp at a
+// time (an item is SH floats: a warp has all of its loads in flight at once, and eight items are in flight per CTA; one
+// CTA per item spent its time in the chain load -> reduce -> store).  X[t][s][:] += coef(t, s) * sum_r part_r[t][:]
+// (parts added in rank order), then the items' sums of squares go to every rank in one coalesced store per CTA.
+// SH % 4 == 0, per <= TP_PRENORM_ITEMS.
 __global__ void __launch_bounds__(256) hc_prenorm_tp_kernel(float *X, const float *pend, int nparts, long long part_stride,
                                                             int ld_pend, const float *inj, int SH, int hc, long long items, int per,
                                                             TpWait wait, Peers ssq_dst, int ranks, TpSignal sig) {
-    __shared__ float scratch[32];
     __shared__ float s_ssq[TP_PRENORM_ITEMS];
     const long long first = (long long)blockIdx.x * per;
     const int mine = (int)min((long long)per, items - first);
-    const int n4 = SH >> 2;
+    const int n4 = SH >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool ok = pend ? tp_wait(wait) : true;
-    for (int k = 0; k < mine; ++k) {
+    for (int k = warp; k < mine; k += 8) {
         const long long it = first + k;
         const long long t = it / hc;
-        const int s = (int)(it - t * hc);
         float4 *x = reinterpret_cast<float4 *>(X + it * SH);
-        float4 v[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c = threadIdx.x + i * 256;
-            v[i] = c < n4 ? x[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        if (pend && ok) {
-            const float coef = 2.f * sigmoidf_(inj[it] / float(hc));
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int c = threadIdx.x + i * 256;
-                if (c < n4) {
-                    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int r = 0; r < nparts; ++r) {
-                        const float4 q = __ldcg(reinterpret_cast<const float4 *>(pend + r * part_stride + t * ld_pend) + c);
-                        p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
-                    }
-                    v[i].x = fmaf(p.x, coef, v[i].x); v[i].y = fmaf(p.y, coef, v[i].y);
-                    v[i].z = fmaf(p.z, coef, v[i].z); v[i].w = fmaf(p.w, coef, v[i].w);
-                    x[c] = v[i];
-                }
-            }
-        }
+        const float coef = (pend && ok) ? 2.f * sigmoidf_(inj[it] / float(hc)) : 0.f;
         float ss = 0.f;
+#pragma unroll 4
+        for (int c = lane; c < n4; c += 32) {
+            float4 v = x[c];
+            if (pend && ok) {
+                float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < nparts; ++r) {
+                    const float4 q = __ldcg(reinterpret_cast<const float4 *>(pend + r * part_stride + t * ld_pend) + c);
+                    p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
+                }
+                v.x = fmaf(p.x, coef, v.x); v.y = fmaf(p.y, coef, v.y);
+                v.z = fmaf(p.z, coef, v.z); v.w = fmaf(p.w, coef, v.w);
+                x[c] = v;
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-        ss = block_sum<256>(ss, scratch);
-        if (threadIdx.x == 0) s_ssq[k] = ss;
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_ssq[k] = ss;
     }
     __syncthreads();
     if (ok && (int)threadIdx.x < mine) {
@@ -80,12 +72,14 @@ __global__ void __launch_bounds__(256) hc_prenorm_tp_kernel(float *X, const floa
     tp_signal(sig);
 }
 
-// grid: CTAs that stride over the (row, stream) items, 256 threads.  xn[t][s][:] = bf16(X * w1 * rsqrt(sum_r ssq_r[t][s] / H + eps)).
+// grid: CTAs of 8 warps that stride over the (row, stream) items, one item per warp at a time.
+// xn[t][s][:] = bf16(X * w1 * rsqrt(sum_r ssq_r[t][s] / H + eps)).
 __global__ void __launch_bounds__(256) hc_norm_tp_kernel(const float *X, const float *ssq_parts, int nparts, long long part_stride,
                                                          const float *w1, int SH, int hc, int H, float eps, bf16 *xn, long long items,
                                                          TpWait wait) {
     if (!tp_wait(wait)) return;
-    for (long long it = blockIdx.x; it < items; it += gridDim.x) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n4 = SH >> 2;
+    for (long long it = (long long)blockIdx.x * 8 + warp; it < items; it += (long long)gridDim.x * 8) {
         const int s = (int)(it % hc);
         float tot = 0.f;
         for (int r = 0; r < nparts; ++r) tot += __ldcg(ssq_parts + r * part_stride + it);
@@ -93,7 +87,8 @@ __global__ void __launch_bounds__(256) hc_norm_tp_kernel(const float *X, const f
         const float4 *x = reinterpret_cast<const float4 *>(X + it * SH);
         const float4 *w4 = reinterpret_cast<const float4 *>(w1 + (long long)s * SH);
         uint2 *o = reinterpret_cast<uint2 *>(xn + it * SH);
-        for (int c = threadIdx.x; c < (SH >> 2); c += 256) {
+#pragma unroll 4
+        for (int c = lane; c < n4; c += 32) {
             const float4 v = x[c], w = w4[c];
             o[c] = make_uint2(pack_bf16(v.x * w.x * rn, v.y * w.y * rn), pack_bf16(v.z * w.z * rn, v.w * w.w * rn));
         }
@@ -117,7 +112,9 @@ __global__ void __launch_bounds__(256) hc_mid_tp_kernel(const float *parts, int 
 }
 
 // g [T][SH*4] fp32 with columns ordered (c, s); this rank's block-input columns bin[t][col0 + c] = mean_s sigmoid(g) * xn
-// go to every rank's block-input matrix.  One thread per eight columns; SH % 8 == 0, col0 % 8 == 0, ld_bin % 8 == 0.
+// go to every rank's block-input matrix.  One thread per eight columns (a 16-byte store per destination); a form with one
+// thread per two columns and the stores gathered by shuffles measured slower (5.4 -> 7.7 ms per chunk on 2 GPUs).
+// SH % 8 == 0, col0 % 8 == 0, ld_bin % 8 == 0.
 __global__ void __launch_bounds__(256) hc_mix_tp_kernel(const float *g, const bf16 *xn, int SH, Peers bin_dst, int ranks,
                                                         int ld_bin, int col0, long long total8, TpSignal sig) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (long long)gridDim.x * blockDim.x) {
@@ -348,7 +345,7 @@ QW_API int qwk_hc_norm_tp(void *tp_, const float *X, const float *w1, int SH, in
     QwTp *tp = (QwTp *)tp_;
     if (!tp_ok(tp) || (SH & 3)) return -1;
     const long long items = (long long)T * hc;
-    hc_norm_tp_kernel<<<fat_grid(items, 1), 256, 0, s>>>(X, (const float *)tp_parts(tp, 0), tp->ranks, tp->part_bytes[0] >> 2, w1, SH, hc,
+    hc_norm_tp_kernel<<<fat_grid(items, 8), 256, 0, s>>>(X, (const float *)tp_parts(tp, 0), tp->ranks, tp->part_bytes[0] >> 2, w1, SH, hc,
                                                          H, eps, (bf16 *)xn, items, tp_make_wait(tp, 0));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
