@@ -223,3 +223,38 @@ def test_device_snapshots_at_prompt_end_and_message_boundaries():
     e2.prefill(0, p2)
     want = e2.dm.buf["logits"][0]
     assert float((got - want).abs().max() / want.abs().max()) < 3e-2
+
+
+def test_plain_stretches_and_mtp_catch_up_keep_the_output_exact():
+    """Random weights accept no draft, so the acceptance average falls until drafting stops paying: the session then
+    decodes a stretch of plain steps, catches the skipped MTP rows up in batched passes, probes with drafts again and,
+    failing again, starts a longer stretch.  The tokens equal plain greedy decoding throughout."""
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.session import session as SS
+    cfg, eng, ses = make(None, slots=1)
+    p = prompt_of(cfg, 64, 11)
+    s = ses.acquire(p, 400)
+    ses.begin_prompt(s, p)
+    while not ses.prefill_some(s, 4096):
+        pass
+    ses.set_stop_tokens(s, [])
+    first, _ = ses.sample_prompt(s, SamplingParams())
+    cfg2, eng2, ses2 = make(None, slots=1)
+    eng2.prefill(0, p)
+    n_new = 150
+    want = eng2.generate_greedy(0, first, n_new, k=0)
+    got, pending, drafted, plain, stretches = [], first, 0, 0, []
+    si = ses.slots[s]
+    while len(got) < n_new:
+        before = si.plain_left
+        out = ses.generate([SS.StepReq(s, pending, n_new - len(got), 0, SamplingParams())], k=3)[0]
+        if before == 0 and si.plain_left > 0:
+            stretches.append(si.plain_left + 1 if si.plain_left < si.plain_stretch - SS.PLAIN_GROW else si.plain_left)
+        plain += 1 if (before > 0 or si.plain_left > 0) else 0
+        got += out.tokens
+        pending = out.tokens[-1]
+    eng.dm.check_error()
+    assert got[:n_new] == want
+    assert len(stretches) >= 2 and plain >= SS.PLAIN_FIRST                # drafting stopped, was probed again, stopped again
+    assert si.plain_stretch > SS.PLAIN_FIRST + SS.PLAIN_GROW - 1          # the second stretch is longer than the first
+    assert ses.catch_up_rows >= SS.PLAIN_FIRST - 1                         # the first stretch's MTP rows were run when drafting resumed

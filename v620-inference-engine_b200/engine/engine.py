@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Tuple,  Callable, Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -427,6 +427,22 @@ class Engine:
             dm.mtp_step([t for _, _, t, _ in catch], [s_ for s_, _, _, _ in catch], [p for _, _, _, p in catch])
         for s_, run, na in zip(slots, runs, n_acc):
             self.slot[s_].tokens.extend(int(t) for t in run[:na])
+
+    def mtp_catch_up(self, slot: int, rows: Sequence[Tuple[torch.Tensor, int, int]]) -> int:
+        """MTP rows that were skipped while the slot decoded without drafts: ``rows`` = (backbone hidden state of position
+        p, token of position p + 1, p) in position order.  They run as batched MTP passes (up to ``max_rows`` rows each), so
+        that the MTP layer's own KV / indexer state has no holes when drafting resumes.  Returns the number of passes.
+        (reference: mtp_catch_up, src/engine/speculative.hip:43-66)"""
+        if not self.mtp or not rows:
+            return 0
+        dm, hid = self.dm, self.dm.buf["hidden_out"]
+        step, passes = dm.max_rows, 0
+        for i in range(0, len(rows), step):
+            part = rows[i:i + step]
+            hid[:len(part)].copy_(torch.stack([h for h, _, _ in part]))
+            dm.mtp_step([int(t) for _, t, _ in part], [slot] * len(part), [int(p_) for _, _, p_ in part])
+            passes += 1
+        return passes
 
     def generate_greedy(self, slot: int, pending: int, n_new: int, k: int = 0) -> List[int]:
         """Greedy continuation of ``n_new`` tokens; with k > 0 drafts are verified (the result equals k = 0)."""

@@ -172,16 +172,16 @@ __global__ void __launch_bounds__(256, 3) gdn_chunk_prep_kernel(GdnChunkArgs a) 
     }
 #pragma unroll
     for (int r = 1; r < CC; ++r) {
-        float acc0 = 0.f, acc1 = 0.f;
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;      // four independent chains: a row's sum is r / 4 dependent FMAs deep
 #pragma unroll
         for (int s4 = 0; s4 < r; s4 += 4) {
             const float4 av = *reinterpret_cast<const float4 *>(As + r * LDP + s4);     // zero at s >= r
             acc0 = fmaf(av.x, wcol[s4], acc0);
             if (s4 + 1 < r) acc1 = fmaf(av.y, wcol[s4 + 1], acc1);
-            if (s4 + 2 < r) acc0 = fmaf(av.z, wcol[s4 + 2], acc0);
-            if (s4 + 3 < r) acc1 = fmaf(av.w, wcol[s4 + 3], acc1);
+            if (s4 + 2 < r) acc2 = fmaf(av.z, wcol[s4 + 2], acc2);
+            if (s4 + 3 < r) acc3 = fmaf(av.w, wcol[s4 + 3], acc3);
         }
-        wcol[r] -= acc0 + acc1;
+        wcol[r] -= (acc0 + acc1) + (acc2 + acc3);
     }
     float *Wg = (isk ? a.Wk : a.Wv) + ((long long)ch * a.VL + h) * CC * CD;
 #pragma unroll

@@ -725,16 +725,50 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D bf16 row-major matrix [rows][cols] (row stride ld elements), box = 64 columns x box_rows rows, 128B swizzle.
+// A chunk issues ~800 of these for a few dozen distinct (address, shape) pairs - weights and the engine's fixed buffers -
+// so encoded maps are kept in a small direct-mapped table (per thread: the launchers run on the caller's thread) and an
+// encode is paid only on a miss.  A map depends on nothing but the key: the same address with the same shape encodes to
+// the same map whatever the memory holds.
+struct MapKey {
+    const void *base;
+    long long rows, cols, ld;
+    int box_rows, dev;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && dev == o.dev;
+    }
+};
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int MAP_SLOTS = 256;
+
 static bool make_map(CUtensorMap *m, const void *base, long long rows, long long cols, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
+    static thread_local MapSlot table[MAP_SLOTS] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const MapKey key{base, rows, cols, ld, box_rows, dev};
+    unsigned long long h = (unsigned long long)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= (unsigned long long)rows * 0xC2B2AE3D27D4EB4Full + (unsigned long long)cols * 0x165667B19E3779F9ull + (unsigned long long)ld * 31 + box_rows;
+    MapSlot &slot = table[(h >> 40) % MAP_SLOTS];
+    if (slot.used && slot.key == key) {
+        *m = slot.map;
+        return true;
+    }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    slot.key = key;
+    slot.map = *m;
+    slot.used = true;
+    return true;
 }
 
 // `per_sm` persistent CTAs per SM of the current device, or one CTA per tile when there are fewer tiles.

@@ -29,6 +29,10 @@ from ..native import host as H
 
 BLOCK = 256
 SPEC_BASE, SPEC_BETA = 1.25, 0.25
+# Drafting that does not pay (the acceptance average says a step with drafts emits fewer tokens per unit of time than a
+# plain one) is switched off for a stretch of steps, then tried again from a probing acceptance; stretches that follow
+# one another without a good spell in between grow (reference: plain_step, src/session/generate.cpp:49-86).
+PLAIN_FIRST, PLAIN_GROW, PLAIN_MAX, PROBE_ACCEPT, MISSED_MAX = 32, 48, 176, 0.3, 256
 VRAM_SNAPSHOTS = 8          # recurrent-state snapshots kept on the device, least recently used first out
 
 
@@ -58,6 +62,9 @@ class SlotInfo:
     drafts_for: int = -1
     block_keys: List[int] = field(default_factory=list)   # store keys of the slot's full blocks, in order
     last_capture: int = 0                                 # position of the newest device snapshot taken during this prompt
+    plain_left: int = 0                                   # steps left of a stretch without drafts
+    plain_stretch: int = 32                               # length of the next such stretch (32 -> 80 -> 128 -> 176)
+    missed: list = field(default_factory=list)            # MTP rows skipped during the stretch: (hidden, next token, position)
     timing: Dict[str, float] = field(default_factory=lambda: {"restore_s": 0.0, "prefill_s": 0.0, "save_s": 0.0, "pin_wait_s": 0.0})
 
 
@@ -118,6 +125,7 @@ class Session:
         self.snap_min_gap = max(BLOCK, int(_settings.get().snap_min_gap))
         self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
         self.seen_chunks = set()
+        self.catch_up_rows = 0                    # MTP rows run late, after stretches without drafts
         self.last_rows: Optional[torch.Tensor] = None        # logits of the last decode / generate rows
 
     # ---- slots
@@ -172,6 +180,7 @@ class Session:
         si = self.slots[slot]
         toks = [int(t) for t in tokens]
         si.prompt, si.prompt_end, si.logits, si.drafts = toks, len(toks), None, []
+        si.missed, si.plain_left = [], 0          # the prefill rebuilds the MTP layer's state
         for k in si.timing:
             si.timing[k] = 0.0
         self.prompt_tokens += len(toks)
@@ -455,7 +464,14 @@ class Session:
                 raise ValueError("a request needs a budget of at least one token")
             kk = min(k, r.budget - 1, e.MAX_DRAFTS) if (e.mtp and sl.mtp_hidden is not None) else 0
             if kk > 0 and force_accept is None:
-                kk = self.draft_count(r.slot, kk)
+                si = self.slots[r.slot]
+                if si.plain_left > 0:
+                    kk = 0                                # inside a stretch without drafts
+                else:
+                    kk = self.draft_count(r.slot, kk)
+                    if kk == 0 and k > 1:                 # drafting stopped paying: a stretch of plain steps starts
+                        si.plain_left = si.plain_stretch
+                        si.plain_stretch = min(PLAIN_MAX, si.plain_stretch + PLAIN_GROW)
             if sl.n + kk + 1 > e.dm.slot_tokens:
                 kk = e.dm.slot_tokens - sl.n - 1
                 if kk < 0:
@@ -476,6 +492,22 @@ class Session:
 
     def _generate_planned(self, reqs, want, spec, force_accept):
         tr, e = self.gen_trace, self.e
+        # ---- plain stretches: a request that does not draft leaves an MTP row behind (its hidden state and pending token
+        # are what the first draft row would have consumed); when its drafting resumes the rows are caught up in batches
+        if e.mtp and force_accept is None:
+            for i, r in enumerate(reqs):
+                si, sl = self.slots[r.slot], e.slot[r.slot]
+                if want[i] == 0 and si.plain_left > 0 and sl.mtp_hidden is not None:
+                    si.missed.append((sl.mtp_hidden, int(r.pending), sl.n - 1))
+                    del si.missed[:-MISSED_MAX]
+                    si.plain_left -= 1
+                    if si.plain_left == 0:
+                        si.accept = max(si.accept, PROBE_ACCEPT)          # the next step probes with a short draft run
+                elif want[i] > 0 and si.missed:
+                    self.catch_up_rows += len(si.missed)
+                    e.mtp_catch_up(r.slot, si.missed)
+                    si.missed = []
+                    tr.count("catch_up", 1)
         # ---- drafts: one chain over the requests that draft
         drafting = [i for i, kk in enumerate(want) if kk > 0]
         drafts: List[List[int]] = [[] for _ in reqs]
@@ -528,6 +560,8 @@ class Session:
             n_acc_all.append(n_acc)
             if d:
                 si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(d))
+                if si.accept >= 0.5:
+                    si.plain_stretch = PLAIN_FIRST                        # a good spell: the next stretch starts short again
             tr.count("drafts", len(d))
             tr.count("accepted", n_acc - 1)
             stopped = bool(emitted) and emitted[-1] in si.stop
