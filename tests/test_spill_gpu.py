@@ -125,3 +125,32 @@ def test_token_major_prefill_into_spilled_pages_equals_resident(stage):
         settings.set_current(old)
     assert sp.prefiller is not None and (("stage_k" in sp.prefiller.b) == stage)
     assert torch.equal(lw, lg) and sw == sg
+
+
+def test_spill_pool_reports_its_numa_placement():
+    """The host pages come either from the NUMA-placed arena (policy bind / preferred / interleave; the node they landed on
+    is read back) or from the CUDA allocator (policy process); both are pinned and hold zeros before first use."""
+    from qwb200.engine.engine import Engine, EngineOptions
+    from qwb200.models.config import ModelConfig
+    from qwb200.utils import settings
+    old = settings.get()
+    try:
+        for pol in ("process", "interleave", "auto"):
+            settings.set_current(settings.Settings.from_env({}, spill_policy=pol))
+            eng = Engine.synthetic(ModelConfig.tiny(), EngineOptions(slots=1, slot_tokens=1024, use_graphs=False, prefill_chunk=0,
+                                                                     dev_pages=1, host_pages=3), device="cuda:0", ple_rows=4096)
+            info = eng.dm.spill_numa
+            assert info is not None and info["policy"] in ("process", "bind", "interleave")
+            if pol == "process":
+                assert info["policy"] == "process"
+            if pol == "interleave" and "fallback" not in info:
+                assert info["policy"] == "interleave" and info["node_got"] >= -1
+            assert all(t.is_pinned() or "fallback" not in info for t in eng.dm.k_host)
+            assert float(eng.dm.k_host[0].float().abs().sum()) == 0.0
+            toks = [(i * 13 + 7) % 900 + 5 for i in range(600)]
+            eng.prefill(0, toks)
+            eng.decode([0], [11])
+            torch.cuda.synchronize()
+            eng.dm.check_error()
+    finally:
+        settings.set_current(old)

@@ -27,6 +27,17 @@ RAW_RING = 16
 GDN_RING = 16
 PLE_RING = 32
 MAX_ROWS = 32
+def gpu_numa_node(dev) -> int:
+    """NUMA node of the GPU's PCI function (sysfs), -1 when the system does not say."""
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            return int(f.read().strip())
+    except Exception:          # noqa: BLE001 - no sysfs entry, no CUDA device, a property this torch lacks
+        return -1
+
+
 _SPILL_KEEPALIVE: list = []      # spill-cache buffers of every model made in this process (see _alloc_spill_cache)
 PLE_LAYOUT_ID = {"f8": 0, "bf16": 1, "int8": 2, "int4": 3}
 
@@ -108,10 +119,9 @@ class DeviceModel:
         self.k_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(nkv)]
         self.v_dev = [z(self.n_dev_pages, KV_PAGE, row, dtype=torch.bfloat16) for _ in range(nkv)]
         self.k_host = self.v_host = None
+        self.spill_numa = None
         if self.n_host_pages:
-            hp = lambda: torch.zeros(self.n_host_pages, KV_PAGE, row, dtype=torch.bfloat16).pin_memory()
-            self.k_host = [hp() for _ in range(nkv)]
-            self.v_host = [hp() for _ in range(nkv)]
+            self.k_host, self.v_host = self._alloc_spill_pool(nkv, row)
         self.ck = [z(self.slots, self.slot_tokens // c.idx_ratio, c.idx_dim, dtype=torch.bfloat16) for _ in range(nkv)]
         self.raw_ring = [z(self.slots, RAW_RING, c.idx_dim) for _ in range(nkv)]
         self.gdn_S = [z(self.slots, sc.gdn_vl, c.gdn_dim, c.gdn_dim) for _ in range(c.n_gdn)]
@@ -156,6 +166,45 @@ class DeviceModel:
         self.ple_ring[slot].zero_()
 
     # ------------------------------------------------------------------ cache of host KV rows
+    def _alloc_spill_pool(self, nkv: int, row: int):
+        """Host pages of the KV spill: pinned memory the kernels address directly.  With a NUMA policy other than
+        ``process`` (setting ``spill_policy``: auto = bind to the GPU's node when the machine has several) the pages
+        come from one arena of the pinned pool - mmap, mbind, touch, register - and the node they landed on is read back
+        (``spill_numa``); otherwise, or when that fails, from the CUDA allocator under the process's own policy.
+        (reference: src/engine/spill.cpp:64-164)"""
+        from ..native import host as H
+        from ..utils import settings as _settings
+        per = self.n_host_pages * KV_PAGE * row * 2
+        pol = _settings.get().spill_policy
+        node = gpu_numa_node(self.dev)
+        try:
+            nodes = H.numa_nodes()
+        except Exception:
+            nodes = 1
+        if pol == "auto":
+            pol = "bind" if (nodes > 1 and node >= 0) else "process"
+        if pol != "process":
+            try:
+                unit = (per + 4095) // 4096 * 4096
+                pool = H.PinnedPool(unit_bytes=unit, arena_bytes=unit * 2 * nkv, standing_units=0, use_cuda=True, policy=pol, node=node)
+                pool.reserve(2 * nkv)
+                views = [pool.get() for _ in range(2 * nkv)]
+                ts = [torch.from_numpy(v[:per]).view(torch.bfloat16).view(self.n_host_pages, KV_PAGE, row) for v in views]
+                for t in ts:
+                    t.zero_()
+                st = pool.stats()
+                if not st["cuda_registered"]:
+                    raise RuntimeError("the arena could not be registered with CUDA")
+                self._spill_pool, self._spill_views = pool, views          # the pool owns the memory for the model's lifetime
+                self.spill_numa = {"policy": pol, "node_wanted": node, "node_got": st["numa_node"], "nodes": nodes}
+                return ts[:nkv], ts[nkv:]
+            except Exception as ex:          # noqa: BLE001 - placement is an optimisation: fall back and say so
+                self.spill_numa = {"policy": "process", "fallback": str(ex)[:120]}
+        hp = lambda: torch.zeros(self.n_host_pages, KV_PAGE, row, dtype=torch.bfloat16).pin_memory()
+        if self.spill_numa is None:
+            self.spill_numa = {"policy": "process", "nodes": nodes}
+        return [hp() for _ in range(nkv)], [hp() for _ in range(nkv)]
+
     def _alloc_spill_cache(self, mb: int, stats: bool):
         """Direct-mapped device cache in front of the pinned host KV pages (one entry = K row + V row of one token of
         one layer; reference: SpillCache in src/kernels/types.hpp:48-70, sized by QW_SPILL_CACHE_MB).  The kernels

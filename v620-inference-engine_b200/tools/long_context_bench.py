@@ -69,6 +69,7 @@ def main():
     out = {"slots": a.slots, "tokens": a.tokens, "resident": a.resident, "layers": cfg.n_layers,
            "host_kv_gb": round(sum(t.numel() * 2 for t in (eng.dm.k_host or []) + (eng.dm.v_host or [])) / 2**30, 2),
            "ple_table_gb": round(ple_rows * cfg.ngram_dim / 2**30, 2), "build_s": round(time.time() - t0, 1)}
+    out["spill_numa"] = eng.dm.spill_numa
     g = torch.Generator().manual_seed(5)
     ctx = [torch.randint(0, cfg.vocab, (a.tokens,), generator=g).tolist() for _ in range(a.filled)]
     eng.prefill(0, ctx[0][:512], want_logits=False)          # warm-up

@@ -42,7 +42,7 @@ def main():
     free1, _ = torch.cuda.mem_get_info(0)
     out = {"slots": a.slots, "slot_tokens": cap, "resident_tokens": a.resident or cap, "build_s": round(time.time() - t0, 1),
            "device_total_gb": round(total / 2**30, 1), "device_free_before_gb": round(free0 / 2**30, 1), "device_free_after_gb": round(free1 / 2**30, 1),
-           "memory": eng.memory_plan()}
+           "memory": eng.memory_plan(), "spill_numa": eng.dm.spill_numa}
     g = torch.Generator().manual_seed(1)
     for s in range(a.slots):
         eng.prefill(s, torch.randint(0, cfg.vocab, (a.fill,), generator=g).tolist(), want_logits=True)
