@@ -98,6 +98,7 @@ def test_capi_on_two_gpus_matches_one():
         s2 = Scheduler(two, drafts=0, prefill_piece=256)
         s2.start(watchdog=False)
         got, _, _ = run(s2, two, prompt, 20)
+        assert two.failure() == "", two.failure()
         again, _, r2 = run(s2, two, prompt, 20)
         s2.shutdown()
         # greedy tokens may part ways only at a near-tie; the first tokens must agree and a rerun must repeat itself
@@ -111,3 +112,4 @@ def test_capi_on_two_gpus_matches_one():
         assert two.failure() == ""
     finally:
         two.close()
+

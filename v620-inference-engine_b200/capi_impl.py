@@ -76,6 +76,12 @@ class SessionOps:
         self.s.set_boundary_token(tok)
         return 0
 
+    def map_media(self, toks, media):
+        """Every rank registers the prompt's media with its own vision front end (each runs the tower on the slices its
+        prefill needs: same kernels on the same patches, so the ranks' embeddings are bit-identical) and maps the pad
+        tokens to vision ids; the mapping is a pure function of the arguments, so all ranks return the same list."""
+        return self.vision.map_media(toks, media) if self.vision is not None else list(toks)
+
     def acquire(self, toks, max_new):
         return self.s.acquire(toks, max_new)
 
@@ -176,7 +182,7 @@ class CApi:
     def _tokens(self, addr, n, media_addr, n_media):
         toks = _i32(addr, n)
         if n_media and self.vision is not None:
-            toks = self.vision.map_media_tokens(toks, media_addr, n_media)
+            toks = self.ops.map_media(toks, self.vision.read_media(media_addr, n_media))
         return toks
 
     def acquire(self, addr, n, max_new, media, n_media):
@@ -313,7 +319,9 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
     if st.no_mtp:
         o["mtp"] = False
     if st.no_vision or world > 1:
-        o["vision"] = False          # media patches reach rank 0 only: the vision tower serves one-GPU engines
+        # the media descriptors can travel to the other ranks by value (SessionOps.map_media), but an image prompt on two
+        # ranks has not run to completion yet: until it has, the vision tower serves one-rank engines
+        o["vision"] = False
     o.setdefault("prefill_chunk", st.prefill_chunk)
     o.setdefault("prefill_piece", st.prefill_piece)
     if "host_cache_gb" not in o and "QW_HOST_CACHE_GB" in os.environ:

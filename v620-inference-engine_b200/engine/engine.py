@@ -521,8 +521,23 @@ class Engine:
     def _prefill_token_major(self, slot: int, toks: List[int], want_logits: bool):
         from .prefill import Prefiller
         for job in self.prefill_jobs(slot, toks, want_logits):
+            self._rendezvous()
             Prefiller.launch(self.dm.lib, [job])
         return self.dm.buf["logits"][0] if want_logits else None
+
+    def _rendezvous(self) -> None:
+        """Several ranks, one process each: a one-element all-reduce on the stream before a chunk's kernels.  The kernels'
+        own waits for their peers are bounded (about a second), which covers the ranks' differences in kernel time but not
+        a rank whose host is late by more - a first call that still allocates buffers or loads kernels, a worker process
+        that got its call over a socket; behind the all-reduce both GPUs start the chunk together wherever their hosts are."""
+        if self.dm.sc.ranks == 1:
+            return
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() != self.dm.sc.ranks:
+            return          # ranks emulated in one process are walked in lock step by the runtime
+        if getattr(self, "_rdv", None) is None:
+            self._rdv = torch.zeros(1, device=self.dm.dev)
+        dist.all_reduce(self._rdv)
 
     # ---- decode
     def decode(self, slots: Sequence[int], tokens: Sequence[int], flags: int = 0, sync: bool = True) -> List[int]:

@@ -36,17 +36,29 @@ class VisionFrontend:
                 tokens[s0 + j] = k
                 self.where[k] = (content_hash, sl, j)
 
-    def map_media_tokens(self, tokens: List[int], media_addr: int, n_media: int) -> List[int]:
-        """C API entry: ``media_addr`` points at ``n_media`` qw_media structs."""
+    def read_media(self, media_addr: int, n_media: int) -> list:
+        """The ``n_media`` qw_media structs at ``media_addr`` as plain values (hash, video, t, h, w, patches, starts):
+        copies, so that they can travel to the other ranks' processes."""
         from ..capi_impl import QwMedia
-        out = list(tokens)
         arr = (QwMedia * n_media).from_address(media_addr)
+        out = []
         for m in arr:
             rows = m.t * m.h * m.w
             patches = np.ctypeslib.as_array(m.patches, shape=(rows, self.enc.cfg.patch_in)).copy()
             starts = np.ctypeslib.as_array(m.starts, shape=(m.t,)).copy()
-            self.add_media(out, int(m.hash), bool(m.video), m.t, m.h, m.w, patches, starts)
+            out.append((int(m.hash), bool(m.video), int(m.t), int(m.h), int(m.w), patches, starts))
         return out
+
+    def map_media(self, tokens: List[int], media: list) -> List[int]:
+        """Register the media (values of ``read_media``) and return the prompt with its pad tokens replaced by vision ids."""
+        out = list(tokens)
+        for hsh, video, t, h, w, patches, starts in media:
+            self.add_media(out, hsh, video, t, h, w, patches, starts)
+        return out
+
+    def map_media_tokens(self, tokens: List[int], media_addr: int, n_media: int) -> List[int]:
+        """C API entry: ``media_addr`` points at ``n_media`` qw_media structs."""
+        return self.map_media(tokens, self.read_media(media_addr, n_media))
 
     def stage(self, slot, media_addr, n_media) -> None:
         """Nothing to do ahead of time: slices are encoded when the chunk that holds their tokens is prefilled."""
