@@ -45,7 +45,7 @@ class Prefiller:
         self.tp = dm.sc.ranks > 1
         if self.tp and not self.channels:
             raise ValueError("token-major prefill on several ranks needs a channel per lane (parallel.tp_channel)")
-        self.lanes = lanes or st.prefill_lanes or (2 if dm.sc.ranks >= 8 else 1)
+        self.lanes = lanes or st.prefill_lanes or (len(self.channels) if self.tp else 1)          # attach_tp made one channel per lane
         self.lanes = max(1, min(self.lanes, len(self.channels))) if self.tp else self.lanes
         S.check_prefill_structs(self.lib)
         self.lib.qwrt_prefill.argtypes = [C.POINTER(C.POINTER(S.QwPrefillJob)), C.c_int]
