@@ -211,6 +211,7 @@ def main():
             from qwb200.engine.sampling import SamplingParams
             from qwb200.session.session import Session, StepReq
             ses = Session(eng, host_cache_bytes=0)
+            barrier()          # the ranks' hosts leave the set-up together
             kd, steps_m = 5, max(3, args.mtp_steps)
             sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
             mg = torch.Generator().manual_seed(99)
@@ -253,6 +254,9 @@ def main():
     extras_failed = {}
     prefill_long = mtp = None
     for name, fn in (("prefill_long", run_long_prefill), ("mtp", run_mtp)):
+        if extras_failed:
+            extras_failed[name] = "skipped after an earlier failure"
+            continue
         try:
             r = fn()
         except Exception as ex:          # noqa: BLE001 - reported in the JSON line
@@ -264,6 +268,14 @@ def main():
                 eng.dm.err_word.zero_()
             except Exception:
                 pass
+        if dist is not None:
+            # a failure on any rank ends the extras on every rank: the ranks that did not see it would otherwise go on
+            # into collectives that nobody answers
+            bad = torch.tensor([1.0 if name in extras_failed else 0.0], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if float(bad) > 0 and name not in extras_failed:
+                extras_failed[name] = "failed on another rank"
+                r = None
         if name == "prefill_long":
             prefill_long = r
         else:
@@ -304,6 +316,11 @@ def main():
         if extras_failed:
             out["extras_failed"] = extras_failed
         print(json.dumps(out), flush=True)
+    if extras_failed:
+        # ranks may be out of step after a failure: leave without the collective tear-down (which waits for all of them)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     if dist is not None:
         dist.destroy_process_group()
     return 0

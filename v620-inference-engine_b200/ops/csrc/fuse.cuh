@@ -23,7 +23,7 @@
 namespace qw {
 
 constexpr int FUSE_MAX_RANKS = 8;
-constexpr unsigned FUSE_SPIN_LIMIT = 1u << 22;      // polls of one word before a wait gives up (about a second)
+constexpr unsigned FUSE_SPIN_LIMIT = 1u << 26;      // polls of one word before a wait gives up (~15 s: a rank whose host launches its step a second late is not a failure)
 
 struct FuseOut {
     int mode;                    // 0 off | 1 every word to every rank (all-reduce, all-gather) | 2 column c of a row to rank c / n (reduce-scatter)

@@ -14,7 +14,7 @@
 namespace qw {
 
 constexpr int P2P_MAX_RANKS = 8;
-constexpr unsigned SPIN_LIMIT = 1u << 24;      // polls before a wait gives up (about a second)
+constexpr unsigned SPIN_LIMIT = 1u << 28;      // polls before a wait gives up (~15 s)
 
 struct P2PArgs {
     char *peer[P2P_MAX_RANKS];   // base of every rank's symmetric region (peer[rank] is local)

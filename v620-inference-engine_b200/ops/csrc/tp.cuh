@@ -150,7 +150,9 @@ inline TpWait tp_make_wait(const QwTp *tp, int kind) {
     w.flags = reinterpret_cast<const unsigned int *>((const char *)tp->peer[tp->rank] + tp->off_flags) + kind * 8 * 16;
     w.ranks = tp->ranks;
     w.seq = tp->seq[kind];
-    w.limit = tp->spin_limit ? tp->spin_limit : (1u << 21);
+    // default: ~2^25 polls, tens of seconds.  A peer whose host stalls in the middle of enqueueing a chunk (a page-locking call in
+    // another thread, a collection pause) is late by a second or more; a peer that is gone is found by the host long before
+    w.limit = tp->spin_limit ? tp->spin_limit : (1u << 25);
     w.err = g_err_ptr;
     return w;
 }

@@ -114,7 +114,7 @@ class Session:
         self.store_on = host_cache_bytes > 0 or bool(disk_cache_dir)          # no tier to keep blocks in: nothing is exported
         # pinned units for the blocks on their way between the engine and the store (one block per unit)
         self.pool = None
-        if torch.cuda.is_available():
+        if torch.cuda.is_available() and (host_cache_bytes > 0 or bool(disk_cache_dir)):          # no store tier: nothing to stage, nothing to pin
             try:
                 self.pool = H.PinnedPool(self.io.kv_block_bytes, arena_bytes=max(64 << 20, 16 * self.io.kv_block_bytes), standing_units=2,
                                          use_cuda=True)
