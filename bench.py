@@ -179,6 +179,37 @@ def main():
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     sampler.stop()
+    # The extras run the same program on every rank, and a failure (a bounded wait that ran out sets the device error word,
+    # a launch that was refused raises) may show on some ranks only.  So no rank raises where it notices: it notes the
+    # failure, skips its work up to the next sync point, and there all ranks learn of it together (one all-reduce that every
+    # rank reaches, failed or not) and raise together - the collectives of the ranks never get out of step.
+    trouble = {"msg": ""}
+
+    def attempt(fn, default=None):
+        if trouble["msg"]:
+            return default
+        try:
+            return fn()
+        except Exception as ex:          # noqa: BLE001 - carried to the next sync point
+            trouble["msg"] = f"{type(ex).__name__}: {str(ex)[:200]}"
+            return default
+
+    def sync_point():
+        torch.cuda.synchronize()
+        if not trouble["msg"]:
+            try:
+                eng.dm.check_error()
+            except RuntimeError as ex:
+                trouble["msg"] = str(ex)[:200]
+        bad = 1.0 if trouble["msg"] else 0.0
+        if dist is not None:
+            t_ = torch.tensor([bad], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            bad = float(t_)
+        torch.cuda.synchronize()
+        if bad > 0:
+            raise RuntimeError(trouble["msg"] or "failed on another rank")
+
     def run_long_prefill():
         # ---- long prompt: 32,768 tokens in 4,096-token chunks through the token-major path
         prefill_long = None
@@ -186,13 +217,12 @@ def main():
             lg = torch.Generator().manual_seed(77)
             long_toks = torch.randint(0, cfg.vocab, (args.prefill_long,), generator=lg).tolist()
             eng.reset(1)
-            barrier()
+            sync_point()
             q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             q0.record()
-            eng.prefill(1, long_toks, want_logits=True)
+            attempt(lambda: eng.prefill(1, long_toks, want_logits=True))
             q1.record()
-            barrier()
-            eng.dm.check_error()
+            sync_point()
             tl = torch.tensor([q0.elapsed_time(q1)], device=dev)
             if dist is not None:
                 dist.all_reduce(tl, op=dist.ReduceOp.MAX)
@@ -201,6 +231,7 @@ def main():
             log(f"long prefill: {prefill_long}")
             eng.reset(1)
         return prefill_long
+
     def run_mtp():
         # ---- speculative decoding through Session.generate: 5 drafts per step, sampling (T 1.0, top-k 20, top-p 0.95), 1 and 4
         # concurrent streams of 8,192-token context.  Random weights accept next to nothing, so acceptance is forced: for
@@ -210,17 +241,20 @@ def main():
         if args.mtp_context and eng.mtp and (world == 1 or args.comm == "p2p"):
             from qwb200.engine.sampling import SamplingParams
             from qwb200.session.session import Session, StepReq
-            ses = Session(eng, host_cache_bytes=0)
-            barrier()          # the ranks' hosts leave the set-up together
+            ses = attempt(lambda: Session(eng, host_cache_bytes=0))
+            sync_point()          # the ranks' hosts leave the set-up together
             kd, steps_m = 5, max(3, args.mtp_steps)
             sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
             mg = torch.Generator().manual_seed(99)
             for sl_ in range(4):
-                eng.reset(sl_)
-                ses.sampler.reset_slot(sl_)
-                eng.prefill(sl_, torch.randint(0, cfg.vocab, (args.mtp_context,), generator=mg).tolist(), want_logits=True)
-            torch.cuda.synchronize()
-            eng.dm.check_error()
+                toks_ = torch.randint(0, cfg.vocab, (args.mtp_context,), generator=mg).tolist()
+
+                def fill(sl_=sl_, toks_=toks_):
+                    eng.reset(sl_)
+                    ses.sampler.reset_slot(sl_)
+                    eng.prefill(sl_, toks_, want_logits=True)
+                attempt(fill)
+            sync_point()
             mtp = {"drafts": kd, "context": args.mtp_context, "sampling": {"temperature": 1.0, "top_k": 20, "top_p": 0.95},
                    "timed_steps_per_point": steps_m, "note": "measured: forced acceptance of a drafts per stream and step"}
             for streams in (1, 4):
@@ -233,23 +267,28 @@ def main():
                             pend[i] = o.tokens[-1]
                         return sum(len(o.tokens) for o in outs)
                     for _ in range(3):
-                        one_step()
-                    barrier()
+                        attempt(one_step)
+                    sync_point()
                     m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     m0.record()
                     emitted = 0
                     for _ in range(steps_m):
-                        emitted += one_step()
+                        emitted += attempt(one_step, 0)
                     m1.record()
-                    barrier()
+                    sync_point()
                     tm = torch.tensor([m0.elapsed_time(m1)], device=dev)
                     if dist is not None:
                         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
                     res.append({"accepted": acc, "ms_per_step": round(float(tm) / steps_m, 3), "tok_s": round(emitted / (float(tm) / 1e3), 1)})
-                eng.dm.check_error()
                 mtp[f"streams_{streams}"] = res
                 log(f"speculative, {streams} stream(s): {res}")
         return mtp
+
+    # the headline's times as the maximum over the ranks, taken while the ranks are certainly in step
+    if dist is not None:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(tt[0]), float(tt[1])
     # the extras must not take the headline with them: a failure is recorded in their place
     extras_failed = {}
     prefill_long = mtp = None
@@ -268,22 +307,10 @@ def main():
                 eng.dm.err_word.zero_()
             except Exception:
                 pass
-        if dist is not None:
-            # a failure on any rank ends the extras on every rank: the ranks that did not see it would otherwise go on
-            # into collectives that nobody answers
-            bad = torch.tensor([1.0 if name in extras_failed else 0.0], device=dev)
-            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
-            if float(bad) > 0 and name not in extras_failed:
-                extras_failed[name] = "failed on another rank"
-                r = None
         if name == "prefill_long":
             prefill_long = r
         else:
             mtp = r
-    if dist is not None:
-        tt = torch.tensor([ms, ms_e2e], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(tt[0]), float(tt[1])
     clocks = sampler.summary()
     if rank == 0:
         val = K / (ms / 1e3)
