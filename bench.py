@@ -179,36 +179,11 @@ def main():
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     sampler.stop()
-    # The extras run the same program on every rank, and a failure (a bounded wait that ran out sets the device error word,
-    # a launch that was refused raises) may show on some ranks only.  So no rank raises where it notices: it notes the
-    # failure, skips its work up to the next sync point, and there all ranks learn of it together (one all-reduce that every
-    # rank reaches, failed or not) and raise together - the collectives of the ranks never get out of step.
-    trouble = {"msg": ""}
-
-    def attempt(fn, default=None):
-        if trouble["msg"]:
-            return default
-        try:
-            return fn()
-        except Exception as ex:          # noqa: BLE001 - carried to the next sync point
-            trouble["msg"] = f"{type(ex).__name__}: {str(ex)[:200]}"
-            return default
-
-    def sync_point():
-        torch.cuda.synchronize()
-        if not trouble["msg"]:
-            try:
-                eng.dm.check_error()
-            except RuntimeError as ex:
-                trouble["msg"] = str(ex)[:200]
-        bad = 1.0 if trouble["msg"] else 0.0
-        if dist is not None:
-            t_ = torch.tensor([bad], device=dev)
-            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-            bad = float(t_)
-        torch.cuda.synchronize()
-        if bad > 0:
-            raise RuntimeError(trouble["msg"] or "failed on another rank")
+    # the extras run under a lock-step guard: a failure that shows on some ranks only (a bounded wait that ran out) is
+    # spread to all ranks at the next sync point, so that their collectives never get out of step
+    from qwb200.utils.lockstep import Lockstep
+    guard = Lockstep(dist, dev, check=eng.dm.check_error, sync=torch.cuda.synchronize)
+    attempt, sync_point = guard.attempt, guard.sync_point
 
     def run_long_prefill():
         # ---- long prompt: 32,768 tokens in 4,096-token chunks through the token-major path
