@@ -74,6 +74,10 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # in the product arm NCCL serves rendezvous and timing only: its in-switch (NVLS) transport is left off unless asked for
+        # (NCCL_NVLS_ENABLE=1, e.g. for the --comm nccl baseline), so that a rank that dies does not leave its memory bound to a
+        # multicast object the other ranks still use
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(dev))
 
     W, K = max(3, args.warmup), args.steps

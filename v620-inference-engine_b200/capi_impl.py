@@ -341,6 +341,9 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(master_port), RANK=str(rank), WORLD_SIZE=str(world),
                           LOCAL_RANK=str(rank))
         if not dist.is_initialized():
+            # NCCL serves rendezvous and timing here, never the hot path: its in-switch (NVLS) transport is left off unless asked for,
+            # so that a rank that dies does not leave its memory bound to a multicast object the other ranks still use
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             dist.init_process_group("nccl", device_id=torch.device(dev))
     opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
                          save_gdn=bool(o.get("mtp", True)), host_pages=int(o.get("host_pages", 0)),
