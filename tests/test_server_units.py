@@ -155,3 +155,16 @@ def test_ctypes_structs_match_header(tmp_path):
     want = [C.sizeof(E.Sampling), E.Sampling.seed.offset, C.sizeof(E.CacheStats), C.sizeof(E.SlotTiming), C.sizeof(E.Media),
             E.Media.patches.offset, C.sizeof(E.StepReq), E.StepReq.sampling.offset]
     assert got == want
+
+
+def test_spill_plan_from_serving_options():
+    """--kv-spill on --slot-max-tokens N: N tokens per slot, the first max(slots) resident, the rest in host pages."""
+    from qwb200.capi_impl import spill_plan
+    assert spill_plan([131072, 32768, 32768, 32768], 0, False) == (131072, None, 0)
+    assert spill_plan([8192, 8192], 65536, False) == (65536, None, 0)                       # a larger capacity, all resident
+    cap, dev, host = spill_plan([32768] * 6, 131072, True)
+    assert (cap, dev, host) == (131072, 6 * 128, 6 * 384)
+    cap, dev, host = spill_plan([8192, 4096], 10000, True)                                  # rounded up to whole pages
+    assert cap == 10240 and dev == 2 * 32 and host == 2 * 8
+    assert spill_plan([32768] * 2, 16384, True) == (16384, None, 0)                         # nothing to spill
+    assert spill_plan([1024], 4096, False, dev_pages=2, host_pages=6) == (4096, 2, 6)       # explicit pages win

@@ -300,6 +300,23 @@ def open(options_json: str) -> CApi:
     return CApi(group.local, group)
 
 
+def spill_plan(slots, slot_max_tokens: int, kv_spill: bool, dev_pages=None, host_pages: int = 0, page: int = 256):
+    """(slot capacity in tokens, device pages or None, host pages) from the serving options.  Without spill every slot
+    holds ``slot_max_tokens`` (or the largest entry of ``slots``) tokens in device memory.  With ``kv_spill`` a slot
+    holds ``slot_max_tokens`` tokens of which the first max(slots) stay in device memory and the rest live in pinned host
+    pages (the engine's slots are uniform: the reference's per-slot device capacities become the largest of them).
+    Explicit ``dev_pages`` / ``host_pages`` win."""
+    n = len(slots)
+    resident = max(int(x) for x in slots)
+    cap = int(slot_max_tokens) if slot_max_tokens else resident
+    if dev_pages is not None or host_pages:
+        return cap, dev_pages, int(host_pages)
+    if not kv_spill or cap <= resident:
+        return max(cap, resident) if not kv_spill else cap, None, 0
+    cap_pages, res_pages = (cap + page - 1) // page, (resident + page - 1) // page
+    return cap_pages * page, n * res_pages, n * (cap_pages - res_pages)
+
+
 def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
     """One rank's engine + session from the options dictionary."""
     import torch
@@ -331,7 +348,8 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
     slots = o.get("slots", [8192])
     if isinstance(slots, int):
         slots = [8192] * slots
-    cap = int(o.get("slot_max_tokens") or max(slots))
+    cap, dev_pages, host_pages = spill_plan(slots, int(o.get("slot_max_tokens") or 0), bool(o.get("kv_spill") or st.kv_spill),
+                                            o.get("dev_pages"), int(o.get("host_pages", 0)))
     devices = o.get("devices", [0])
     dev = f"cuda:{devices[rank]}"
     group = None
@@ -346,8 +364,7 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
             os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             dist.init_process_group("nccl", device_id=torch.device(dev))
     opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
-                         save_gdn=bool(o.get("mtp", True)), host_pages=int(o.get("host_pages", 0)),
-                         dev_pages=o.get("dev_pages"), use_graphs=not st.nograph)
+                         save_gdn=bool(o.get("mtp", True)), host_pages=host_pages, dev_pages=dev_pages, use_graphs=not st.nograph)
     log = (lambda m: print(m, file=sys.stderr, flush=True)) if rank == 0 else None
     if "model_dir" in o and o["model_dir"]:
         from .models.config import check_hf_config
