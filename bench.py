@@ -104,7 +104,11 @@ def main():
     t0 = time.time()
     pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     prefill_note = None
-    try:
+    # under a lock-step guard: a failure that shows on some ranks only makes every rank fall back together
+    from qwb200.utils.lockstep import Lockstep
+    first_try = Lockstep(dist, dev, check=eng.dm.check_error, sync=torch.cuda.synchronize)
+
+    def fill_context():
         if token_major:
             eng.prefill(0, ctx[:512], want_logits=False)      # warm the prefill path (buffers, kernel attributes), then start over
             torch.cuda.synchronize()
@@ -113,8 +117,9 @@ def main():
         pe0.record()
         eng.prefill(0, ctx, want_logits=True)
         pe1.record()
-        torch.cuda.synchronize()
-        eng.dm.check_error()
+    first_try.attempt(fill_context)
+    try:
+        first_try.sync_point()
     except RuntimeError as ex:
         if not token_major:
             raise
@@ -185,7 +190,6 @@ def main():
     sampler.stop()
     # the extras run under a lock-step guard: a failure that shows on some ranks only (a bounded wait that ran out) is
     # spread to all ranks at the next sync point, so that their collectives never get out of step
-    from qwb200.utils.lockstep import Lockstep
     guard = Lockstep(dist, dev, check=eng.dm.check_error, sync=torch.cuda.synchronize)
     attempt, sync_point = guard.attempt, guard.sync_point
 
