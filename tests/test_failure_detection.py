@@ -121,3 +121,79 @@ def test_heartbeat_across_processes():
     assert got[2] == (4, "left")
     assert "peer failure" in got[0][1] and ("rank 2: shutting down" in got[0][1] or "rank 1: silent" in got[0][1])
     assert 1 <= got[0][0] < 60                     # noticed within a few steps, long before the loop's end
+
+
+# ---- the prefill channel's protocol (flags, tickets, per-kind sequence numbers) on CPU ranks
+def test_tp_channel_sums_in_rank_order_and_counts_per_kind():
+    import numpy as np
+    from qwb200.parallel.cpu_protocol import TpWorld, run_tp_ranks
+    w = TpWorld(4, kinds=3, words=64)
+
+    def body(rk):
+        outs = []
+        for step in range(5):                             # kinds interleaved: each keeps its own count
+            for kind in (0, 2):
+                v = np.arange(48, dtype=np.float32) * (rk.rank + 1) + step + kind
+                seq = rk.send(kind, v, ctas=5)
+                got = rk.receive(kind, 48, seq)
+                outs.append(got)
+                rk.rendezvous()                           # the buffer of a kind is reused: everybody has read it
+        return outs, list(rk.seq)
+    res = run_tp_ranks(w, body, spin_seconds=5.0)
+    assert all(e.code == 0 for e in w.err)
+    for outs, seqs in res:
+        assert seqs == [5, 0, 5]
+        i = 0
+        for step in range(5):
+            for kind in (0, 2):
+                want = sum(np.arange(48, dtype=np.float32) * (r + 1) + step + kind for r in range(4))
+                assert np.array_equal(outs[i], want)
+                i += 1
+
+
+def test_tp_channel_late_host_times_out_without_a_rendezvous_and_not_with_one():
+    """A rank whose host reaches the chunk later than its peers' bounded wait: without a rendezvous before the chunk the
+    peers give up and name it; with one (or with a limit longer than the delay) the chunk completes."""
+    import time
+    import numpy as np
+    from qwb200.parallel.cpu_protocol import ERR_WAIT_TIMEOUT, TpWorld, run_tp_ranks
+
+    def chunk(rk, rendezvous, delay):
+        if rk.rank == 1:
+            time.sleep(delay)                             # its host is still allocating buffers
+        if rendezvous and not rk.rendezvous():
+            return None
+        seq = rk.send(0, np.full(8, rk.rank + 1.0, dtype=np.float32))
+        return rk.receive(0, 8, seq)
+    w = TpWorld(2, kinds=1, words=8)
+    res = run_tp_ranks(w, lambda rk: chunk(rk, False, 0.6), spin_seconds=0.2)
+    assert res[0] is None and w.err[0].code == ERR_WAIT_TIMEOUT
+    assert (w.err[0].detail >> 24) & 7 == 1 and w.err[0].detail & 0xffffff == 1          # waited for rank 1, collective 1
+    w = TpWorld(2, kinds=1, words=8)
+    res = run_tp_ranks(w, lambda rk: chunk(rk, True, 0.6), spin_seconds=0.2)
+    assert all(e.code == 0 for e in w.err) and np.array_equal(res[0], np.full(8, 3.0)) and np.array_equal(res[1], res[0])
+    w = TpWorld(2, kinds=1, words=8)
+    res = run_tp_ranks(w, lambda rk: chunk(rk, False, 0.3), spin_seconds=5.0)               # a limit above the delay
+    assert all(e.code == 0 for e in w.err) and np.array_equal(res[0], np.full(8, 3.0))
+
+
+def test_tp_channel_missing_rank_is_reported_once_and_everyone_stops_waiting():
+    import numpy as np
+    from qwb200.parallel.cpu_protocol import ERR_WAIT_TIMEOUT, TpWorld, run_tp_ranks
+    w = TpWorld(4, kinds=2, words=16)
+
+    def body(rk):
+        if rk.rank == 2:
+            return "left"                                 # never sends
+        seq = rk.send(1, np.ones(16, dtype=np.float32))
+        first = rk.receive(1, 16, seq)
+        t0 = time.monotonic()
+        seq2 = rk.send(0, np.ones(4, dtype=np.float32))
+        second = rk.receive(0, 4, seq2)                   # the error word is set: no second wait of the full limit
+        return first, second, time.monotonic() - t0
+    import time
+    res = run_tp_ranks(w, body, spin_seconds=0.3)
+    for r in (0, 1, 3):
+        first, second, dt = res[r]
+        assert first is None and second is None and dt < 0.2
+        assert w.err[r].code == ERR_WAIT_TIMEOUT and (w.err[r].detail >> 24) & 7 == 2
