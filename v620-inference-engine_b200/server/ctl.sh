@@ -3,6 +3,7 @@
 #
 #   ctl.sh start [qwserve arguments...]     e.g.  ctl.sh start --model-dir /models/qw --ple-dir /models/ples_fp8 --devices 0,1,2,3
 #   ctl.sh stop | restart [args...] | status | logs | smoke
+#   ctl.sh idle-stop [SECONDS=60]           stop the server once it has had nothing to do for that long (frees its GPUs)
 #
 # State lives in $QW_RUN_DIR (default: ./run next to this script): qwserve.pid, qwserve.log, qwserve.args.
 # stop sends SIGTERM to the recorded pid only (the server drains its requests and gives the prefix cache time to flush),
@@ -48,6 +49,7 @@ case "${1:-}" in
     restart) shift; stop; start "$@" ;;
     status) if running; then echo "running (pid $(cat "$PIDFILE"))"; else echo "stopped"; exit 3; fi ;;
     logs) tail -n "${2:-100}" "$LOG" ;;
+    idle-stop) "$PY" -m qwserve.idle --url "http://127.0.0.1:$(p=$(port); echo "${p:-8000}")" --idle "${2:-60}" && stop ;;
     smoke) "$PY" -m qwserve.smoke --url "http://127.0.0.1:$(p=$(port); echo "${p:-8000}")" --follow-up ;;
-    *) sed -n '2,12p' "${BASH_SOURCE[0]}"; exit 2 ;;
+    *) sed -n '2,13p' "${BASH_SOURCE[0]}"; exit 2 ;;
 esac
