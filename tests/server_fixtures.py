@@ -116,6 +116,15 @@ class FakeEngine:
         self.prompt_left[s] -= min(n, self.prompt_left[s])
         return self.prompt_left[s] == 0
 
+    def prefill_batch(self, slots, max_tokens):
+        self._enter("prefill_batch")
+        out = []
+        for s, n in zip(slots, max_tokens):
+            self.prefill_order.append(s)
+            self.prompt_left[s] -= min(n, self.prompt_left[s])
+            out.append(self.prompt_left[s] == 0)
+        return out
+
     def set_stop_tokens(self, s, ids):
         pass
 

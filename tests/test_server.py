@@ -354,3 +354,43 @@ def test_request_sharing_a_long_prefix_waits_for_the_one_in_flight():
         sched._prefill()
     sched._admit()
     assert b.slot >= 0
+
+
+def test_short_prompts_are_prefilled_by_one_engine_call():
+    """Three prompts whose uncached part fits one piece go in with a single prefill_batch call and each gets its first
+    token; a long prompt beside them keeps its own pieces; a failing batch call fails exactly its requests."""
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(8192, 8192, 8192, 8192), start=False)
+    firsts = {}
+
+    def req(n, tag):
+        r = Request(tokens=Tokens([65 + (i % 7) + tag for i in range(n)]), max_new=4, sampling=Sampling(), stop_ids=[eng.eos],
+                    on_token=lambda t, lp, top, tag=tag: firsts.setdefault(tag, t))
+        r.in_think = False
+        return r
+    long_, a, b, c = req(5000, 0), req(300, 1), req(700, 2), req(120, 3)
+    for r in (long_, a, b, c):
+        sched.waiting.append(r)
+    sched._admit()
+    assert all(r.slot >= 0 for r in (long_, a, b, c))
+    sched._prefill()
+    assert eng.calls.count("prefill_batch") == 1 and "prefill_some" not in eng.calls
+    assert a.prefill_done and b.prefill_done and c.prefill_done and not long_.prefill_done
+    assert set(firsts) == {1, 2, 3} and sched.stats["batched_prefills"] == 1
+    assert sorted(eng.prefill_order) == sorted([a.slot, b.slot, c.slot])
+    while sched.prefilling:
+        sched._prefill()                               # the long prompt goes on piece by piece, alone
+    assert long_.prefill_done and eng.calls.count("prefill_batch") == 1 and eng.calls.count("prefill_some") == 3
+    # a batch call that raises: its requests fail, the scheduler goes on
+    srv2, sched2, eng2, _ = make_server("ok", slots=(4096, 4096, 4096), start=False)
+    x, y = req(200, 4), req(300, 5)
+    for r in (x, y):
+        sched2.waiting.append(r)
+    sched2._admit()
+
+    def boom(slots, max_tokens):
+        raise RuntimeError("engine said no")
+    eng2.prefill_batch = boom
+    sched2._prefill()
+    assert "engine said no" in x.error and "engine said no" in y.error and not sched2.prefilling

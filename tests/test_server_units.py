@@ -168,3 +168,22 @@ def test_spill_plan_from_serving_options():
     assert cap == 10240 and dev == 2 * 32 and host == 2 * 8
     assert spill_plan([32768] * 2, 16384, True) == (16384, None, 0)                         # nothing to spill
     assert spill_plan([1024], 4096, False, dev_pages=2, host_pages=6) == (4096, 2, 6)       # explicit pages win
+
+
+def test_capi_prefill_batch_reads_and_writes_the_callers_arrays():
+    """qw_prefill_batch's Python side: slots and limits come from the caller's arrays, every slot's piece runs in one call of
+    the session ops, and the flags go back into the caller's array."""
+    import ctypes as C
+    import types
+    from qwb200.capi_impl import CApi, SessionOps
+    seen = []
+
+    class Ses:
+        def prefill_some(self, slot, max_tokens):
+            seen.append((slot, max_tokens))
+            return slot != 2                      # slot 2's prompt is not in yet
+    ops = SessionOps(Ses(), None)
+    api = CApi(ops)
+    slots, mt, done = (C.c_int32 * 3)(1, 2, 0), (C.c_int64 * 3)(2048, 2048, 512), (C.c_int32 * 3)(9, 9, 9)
+    assert api.prefill_batch(3, C.addressof(slots), C.addressof(mt), C.addressof(done)) == 0
+    assert seen == [(1, 2048), (2, 2048), (0, 512)] and list(done) == [1, 0, 1]

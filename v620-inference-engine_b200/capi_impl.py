@@ -98,6 +98,11 @@ class SessionOps:
     def prefill_some(self, slot, max_tokens):
         return bool(self.s.prefill_some(slot, max_tokens))
 
+    def prefill_batch(self, slots, max_tokens):
+        """One piece of every slot's prompt, one after the other (the chunked scan takes one sequence per chunk), in one
+        call: on several ranks one round trip instead of one per slot."""
+        return [bool(self.s.prefill_some(s_, m_)) for s_, m_ in zip(slots, max_tokens)]
+
     def sample_prompt(self, slot, sp):
         return self.s.sample_prompt(slot, sp)
 
@@ -215,8 +220,8 @@ class CApi:
         sl = _i32(slots, n)
         mt = np.ctypeslib.as_array(C.cast(max_tokens, C.POINTER(C.c_int64)), shape=(n,)).tolist()
         d = np.ctypeslib.as_array(C.cast(done, C.POINTER(C.c_int32)), shape=(n,))
-        for i in range(n):
-            d[i] = 1 if self.ops.prefill_some(sl[i], mt[i]) else 0
+        for i, ok in enumerate(self.ops.prefill_batch(sl, mt)):
+            d[i] = 1 if ok else 0
         return 0
 
     def has_vision(self):

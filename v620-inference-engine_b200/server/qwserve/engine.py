@@ -138,6 +138,13 @@ class Engine:
     def prefill_some(self, slot: int, max_tokens: int) -> bool:
         return bool(self._ck(self.lib.qw_prefill_some(self.h, slot, C.c_int64(max_tokens))))
 
+    def prefill_batch(self, slots: Sequence[int], max_tokens: Sequence[int]) -> List[bool]:
+        """``prefill_some`` for several slots in one call; returns which prompts are in."""
+        n = len(slots)
+        sl, mt, done = (C.c_int32 * n)(*slots), (C.c_int64 * n)(*max_tokens), (C.c_int32 * n)()
+        self._ck(self.lib.qw_prefill_batch(self.h, n, sl, mt, done))
+        return [bool(x) for x in done]
+
     def sample_prompt(self, slot: int, sp: Sampling) -> Tuple[int, float]:
         lp = C.c_float(0)
         return self._ck(self.lib.qw_sample_prompt(self.h, slot, C.byref(sp), C.byref(lp))), lp.value

@@ -72,6 +72,7 @@ class Scheduler:
                  share_min: int = 1024, share_wait: float = 30.0, load_wait: float = 30.0):
         self.e, self.k = engine, drafts if getattr(engine, "has_mtp", False) else 0
         self.piece, self.decode_share, self.max_step = prefill_piece, decode_share, max_step
+        self.max_batch_prefill = 8          # short prompts prefilled by one engine call
         self.stuck_seconds, self.exit_grace, self.log = stuck_seconds, exit_grace, log
         self.log_interval, self._logged_at, self._logged_tokens = log_interval, time.time(), 0
         # A request whose prompt shares at least `share_min` tokens with one that is being prefilled waits (at most `share_wait`
@@ -322,19 +323,45 @@ class Scheduler:
             r.finish = "abort"
             self._finish(r)
             return True
+        # several prompts whose uncached part fits one piece go in with one engine call (on several GPUs one round trip to
+        # the worker ranks instead of one per prompt); reference: _batch, server/qwserve/scheduler.py:315-398
+        short = [q for q in self.prefilling if not q.cancelled and len(q.tokens) - q.reused <= self.piece][:self.max_batch_prefill]
+        if len(short) >= 2 and hasattr(self.e, "prefill_batch"):
+            try:
+                done = self._call(self.e.prefill_batch, [q.slot for q in short], [self.piece] * len(short))
+            except Exception as ex:
+                for q in short:                 # which slots advanced is unknown: none of these prompts is retried
+                    self.prefilling.remove(q)
+                    self._fail(q, str(ex))
+                return True
+            for q, d in zip(short, done):
+                if d:
+                    self._prompt_in(q)
+            self.stats["batched_prefills"] += 1
+            return True
         try:
             done = self._call(self.e.prefill_some, r.slot, self.piece)
             if done:
-                tok, lp = self._call(self.e.sample_prompt, r.slot, r.sampling)
-                self.prefilling.pop(0)
-                r.prefill_done, r.t_first = True, time.time()
-                self._emit(r, [tok], [lp], -1, False)
-                if not r.finish:
-                    self.running.append(r)
+                self._prompt_in(r)
         except Exception as ex:
-            self.prefilling.remove(r)
+            if r in self.prefilling:
+                self.prefilling.remove(r)
             self._fail(r, str(ex))
         return True
+
+    def _prompt_in(self, r: "Request") -> None:
+        """The prompt is in: sample its first token and move the request to the running set."""
+        try:
+            tok, lp = self._call(self.e.sample_prompt, r.slot, r.sampling)
+            self.prefilling.remove(r)
+            r.prefill_done, r.t_first = True, time.time()
+            self._emit(r, [tok], [lp], -1, False)
+            if not r.finish:
+                self.running.append(r)
+        except Exception as ex:
+            if r in self.prefilling:
+                self.prefilling.remove(r)
+            self._fail(r, str(ex))
 
     def _emit(self, r: Request, toks, lps, first_row, stopped):
         for j, (t, lp) in enumerate(zip(toks, lps)):
