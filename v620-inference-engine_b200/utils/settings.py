@@ -93,7 +93,7 @@ class Settings:
                "QW_MOE_PAIR_MAX", "QW_NO_SPLIT", "QW_POOL_ARENA", "QW_POOL_PREPIN", "QW_POOL_SERIAL", "QW_PREFILL_BATCH",
                "QW_PREFILL_PIPELINE", "QW_RESERVE_AHEAD", "QW_SHARE_MIN", "QW_SHARE_WAIT", "QW_SLOT_MOVE_IDLE_S", "QW_SNAP_SYSTEM_MIN",
                "QW_SPEC_BASE", "QW_SPEC_COST", "QW_SPEC_MIXED", "QW_SPILL_LOCALITY", "QW_SPILL_MARGIN_GB",
-               "QW_SPILL_NC", "QW_SPILL_NUMA", "QW_SPILL_STAGE", "QW_VIT_GEMM_ATTN", "QW_MOE_MMA", "QW_SKIP"}
+               "QW_SPILL_NC", "QW_SPILL_NUMA", "QW_VIT_GEMM_ATTN", "QW_MOE_MMA", "QW_SKIP"}
 
     def validate(self) -> "Settings":
         def need(cond, msg):
