@@ -394,3 +394,58 @@ def test_short_prompts_are_prefilled_by_one_engine_call():
     eng2.prefill_batch = boom
     sched2._prefill()
     assert "engine said no" in x.error and "engine said no" in y.error and not sched2.prefilling
+
+
+def test_watchdog_exits_only_after_the_grace_and_forgets_a_recovery(monkeypatch):
+    """The watchdog thread: an engine failure that lasts longer than the grace ends the process with code 3 (so that a
+    supervisor restarts it); an unhealthy spell that ends within the grace is forgotten."""
+    import os
+    from qwserve.scheduler import Scheduler
+    from server_fixtures import FakeEngine
+    logs, exits = [], []
+    eng = FakeEngine(lambda p: [66])
+    sched = Scheduler(eng, exit_grace=1.5, log=logs.append)
+
+    def fake_exit(code):
+        exits.append(code)
+        sched.stop_flag.set()
+    monkeypatch.setattr(os, "_exit", fake_exit)
+    sched.start(watchdog=True)
+    eng.failed_with = "rank 2 is gone"
+    time.sleep(1.3)                        # first unhealthy check has run, the grace has not passed
+    assert not exits and any("unhealthy: engine failure: rank 2 is gone" in ln for ln in logs)
+    eng.failed_with = ""
+    time.sleep(1.2)                        # healthy again: the spell is forgotten
+    assert not exits and sched.unhealthy_since == 0.0
+    eng.failed_with = "rank 2 is gone"
+    t0 = time.time()
+    while not exits and time.time() - t0 < 8:
+        time.sleep(0.1)
+    assert exits == [3] and any(ln.startswith("exiting after") for ln in logs)
+    assert time.time() - t0 >= 1.5
+    sched.shutdown()
+
+
+def test_request_and_stats_log_lines():
+    """One line per finished request with its phases, and a stats line at most every log interval while there is work."""
+    import re
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    logs = []
+    srv, sched, eng, pr = make_server("ok", log=logs.append, start=False)
+    sched.log_interval = 0.05
+    sched.start(watchdog=False)
+    done = threading.Event()
+    r = Request(tokens=Tokens([65] * 300), max_new=8, sampling=Sampling(), stop_ids=[eng.eos], rid="abc123", on_done=lambda reason: done.set())
+    sched.submit(r)
+    assert done.wait(5)
+    t0 = time.time()
+    while not any(ln.startswith("stats:") for ln in logs) and time.time() - t0 < 4:
+        time.sleep(0.05)
+    sched.shutdown()
+    req = [ln for ln in logs if ln.startswith("req abc123")]
+    assert len(req) == 1
+    m = re.match(r"req abc123 slot=(\d+) prompt=300 cached=0 new=(\d+) finish=stop queue=\d+ms prefill=\d+ms \(\d+ tok/s\) decode=[\d.]+ tok/s$", req[0])
+    assert m and int(m.group(2)) == r.emitted
+    st = [ln for ln in logs if ln.startswith("stats:")]
+    assert st and re.search(r"\d+ running, \d+ prefilling, \d+ waiting; [\d.]+ tok/s; \d+ done, \d+ failed; step [\d.]+ ms; prompt tokens from cache \d+%", st[0])

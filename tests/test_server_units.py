@@ -187,3 +187,25 @@ def test_capi_prefill_batch_reads_and_writes_the_callers_arrays():
     slots, mt, done = (C.c_int32 * 3)(1, 2, 0), (C.c_int64 * 3)(2048, 2048, 512), (C.c_int32 * 3)(9, 9, 9)
     assert api.prefill_batch(3, C.addressof(slots), C.addressof(mt), C.addressof(done)) == 0
     assert seen == [(1, 2048), (2, 2048), (0, 512)] and list(done) == [1, 0, 1]
+
+
+def test_sampling_defaults_from_the_checkpoint(tmp_path):
+    """Built-in defaults by mode < the checkpoint's generation_config.json < the request's own fields."""
+    import json as _json
+    from qwserve.api import DEFAULTS_PLAIN, DEFAULTS_THINKING, model_sampling_defaults, sampling_of
+    assert model_sampling_defaults(None) == {} and model_sampling_defaults(str(tmp_path)) == {}
+    (tmp_path / "generation_config.json").write_text("{ not json")
+    assert model_sampling_defaults(str(tmp_path)) == {}
+    (tmp_path / "generation_config.json").write_text(_json.dumps(
+        {"temperature": 0.6, "top_k": 40, "top_p": "0.9", "do_sample": True, "min_p": False, "eos_token_id": [1, 2], "repetition_penalty": 1.05}))
+    d = model_sampling_defaults(str(tmp_path))
+    assert d == {"temperature": 0.6, "top_k": 40, "repetition_penalty": 1.05}          # numbers only: no strings, no booleans, no other keys
+    s = sampling_of({}, thinking=True)
+    near = lambda x, y: abs(x - y) < 1e-6                                                 # the struct holds 32-bit floats
+    assert near(s.temperature, DEFAULTS_THINKING["temperature"]) and near(s.top_p, DEFAULTS_THINKING["top_p"]) and s.top_k == DEFAULTS_THINKING["top_k"]
+    s = sampling_of({}, thinking=False, model_defaults=d)
+    assert near(s.temperature, 0.6) and s.top_k == 40 and near(s.repetition_penalty, 1.05) and near(s.top_p, DEFAULTS_PLAIN["top_p"])
+    s = sampling_of({"temperature": 0.0, "top_k": 1, "seed": 7}, thinking=False, model_defaults=d)
+    assert s.temperature == 0.0 and s.top_k == 1 and s.seed == 7 and near(s.repetition_penalty, 1.05)
+    a, b = sampling_of({}, True), sampling_of({}, True)
+    assert a.seed != b.seed                                                               # no seed given: a fresh one per request

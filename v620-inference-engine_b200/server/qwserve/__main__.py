@@ -67,8 +67,9 @@ def main(argv=None):
     sched = Scheduler(eng, drafts=a.mtp, prefill_piece=min(int(envf("QW_PREFILL_PIECE", 2048)), a.prefill_chunk),
                       decode_share=envf("QW_DECODE_SHARE", 0.25), stuck_seconds=envf("QW_STUCK_SECONDS", 300),
                       exit_grace=envf("QW_EXIT_GRACE", 30), log_interval=envf("QW_LOG_INTERVAL", 30), log=logging.info)
+    from .api import model_sampling_defaults
     srv = Server(eng, prompter, sched, a.served_model_name, preprocessor=pre, default_effort=a.reasoning_effort,
-                 default_budget=a.thinking_budget)
+                 default_budget=a.thinking_budget, sampling_defaults=model_sampling_defaults(a.model_dir))
     im_end = prompter.token_id("<|im_end|>")
     if im_end is not None:
         eng.set_boundary_token(im_end)

@@ -32,9 +32,30 @@ DEFAULTS_THINKING = dict(temperature=1.0, top_p=0.95, top_k=20, min_p=0.0, prese
 DEFAULTS_PLAIN = dict(temperature=0.7, top_p=0.8, top_k=20, min_p=0.0, presence_penalty=1.5)
 
 
-def sampling_of(body: Dict[str, Any], thinking: bool) -> Sampling:
+SAMPLING_FIELDS = ("temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "repetition_penalty")
+
+
+def model_sampling_defaults(model_dir: Optional[str]) -> Dict[str, float]:
+    """The numeric sampling fields of the checkpoint's ``generation_config.json`` (none when the file is missing or
+    unreadable).  They stand between the built-in defaults and a request's own fields, as vLLM does it
+    (the reference: server/qwserve/scheduler.py:42-51)."""
+    import os
+    if not model_dir:
+        return {}
+    try:
+        with open(os.path.join(model_dir, "generation_config.json")) as f:
+            cfg = json.load(f)
+    except (OSError, ValueError):
+        return {}
+    if not isinstance(cfg, dict):
+        return {}
+    return {k: cfg[k] for k in SAMPLING_FIELDS if isinstance(cfg.get(k), (int, float)) and not isinstance(cfg[k], bool)}
+
+
+def sampling_of(body: Dict[str, Any], thinking: bool, model_defaults: Optional[Dict[str, float]] = None) -> Sampling:
     d = dict(DEFAULTS_THINKING if thinking else DEFAULTS_PLAIN)
-    for k in ("temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "repetition_penalty"):
+    d.update(model_defaults or {})
+    for k in SAMPLING_FIELDS:
         if body.get(k) is not None:
             d[k] = body[k]
     seed = body.get("seed")
@@ -46,8 +67,10 @@ def sampling_of(body: Dict[str, Any], thinking: bool) -> Sampling:
 
 class Server:
     def __init__(self, engine, prompter: Prompter, sched: Scheduler, model_name: str, preprocessor=None,
-                 default_effort: Optional[str] = None, default_budget: int = 0, max_new_default: int = 32768):
+                 default_effort: Optional[str] = None, default_budget: int = 0, max_new_default: int = 32768,
+                 sampling_defaults: Optional[Dict[str, float]] = None):
         self.engine, self.prompter, self.sched, self.model_name = engine, prompter, sched, model_name
+        self.sampling_defaults = dict(sampling_defaults or {})
         self.pre = preprocessor
         self.default_effort, self.default_budget, self.max_new_default = default_effort, default_budget, max_new_default
         self.pool = concurrent.futures.ThreadPoolExecutor(max_workers=4, thread_name_prefix="qw-prep")
@@ -109,7 +132,7 @@ class Server:
         lp_k = 0
         if body.get("logprobs"):
             lp_k = max(1, min(20, int(body.get("top_logprobs") or 1))) if not isinstance(body["logprobs"], bool) or body.get("top_logprobs") else 1
-        return Request(tokens=Tokens(ids), max_new=n_new, sampling=sampling_of(body, thinking), stop_ids=list(self.eos),
+        return Request(tokens=Tokens(ids), max_new=n_new, sampling=sampling_of(body, thinking, self.sampling_defaults), stop_ids=list(self.eos),
                        logprobs=lp_k, thinking_budget=budget, think_open=self.tags.think_open if self.tags.think_open is not None else -1,
                        think_close_id=self.tags.think_close if self.tags.think_close is not None else -1,
                        think_close=list(self.close_tokens), start_in_think=starts_thinking,
