@@ -449,3 +449,46 @@ def test_request_and_stats_log_lines():
     assert m and int(m.group(2)) == r.emitted
     st = [ln for ln in logs if ln.startswith("stats:")]
     assert st and re.search(r"\d+ running, \d+ prefilling, \d+ waiting; [\d.]+ tok/s; \d+ done, \d+ failed; step [\d.]+ ms; prompt tokens from cache \d+%", st[0])
+
+
+def test_event_loop_stays_responsive_while_the_engine_is_busy():
+    """Engine calls run on the scheduler's thread: with every generate step taking 200 ms, /health and /tokenize still
+    answer well within a step while a completion is being generated."""
+    srv, sched, eng, pr = make_server("eight tk", step_seconds=0.2)
+
+    async def fn(c):
+        job = asyncio.ensure_future(c.post("/v1/chat/completions", json={"messages": MSG}))
+        await asyncio.sleep(0.3)                       # the generation is under way
+        worst = 0.0
+        for _ in range(10):
+            t0 = time.time()
+            r = await c.get("/health")
+            assert r.status == 200
+            r = await c.post("/tokenize", json={"prompt": "hello there"})
+            assert r.status == 200
+            worst = max(worst, time.time() - t0)
+            await asyncio.sleep(0.02)
+        assert not job.done()                          # still generating: the probes ran alongside it
+        out = await (await job).json()
+        return worst, out
+    worst, out = with_client(srv, fn)
+    assert out["choices"][0]["finish_reason"] == "stop"
+    assert worst < 0.1, f"a probe took {worst * 1e3:.0f} ms while the engine stepped"
+    sched.shutdown()
+
+
+def test_token_arrays_are_marshalled_once():
+    """The prompt's int32 array is built on first use and reused by every later engine call on the same tokens."""
+    from qwserve.engine import Tokens
+    t = Tokens(range(50000))
+    t0 = time.time()
+    a = t.array()
+    first = time.time() - t0
+    t0 = time.time()
+    for _ in range(100):
+        assert t.array() is a
+    again = (time.time() - t0) / 100
+    assert again < first / 20 and a[49999] == 49999 and len(a) == 50000
+    t.append(7)                                         # a changed list is marshalled again
+    b = t.array()
+    assert b is not a and len(b) == 50001 and b[50000] == 7

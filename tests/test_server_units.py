@@ -209,3 +209,41 @@ def test_sampling_defaults_from_the_checkpoint(tmp_path):
     assert s.temperature == 0.0 and s.top_k == 1 and s.seed == 7 and near(s.repetition_penalty, 1.05)
     a, b = sampling_of({}, True), sampling_of({}, True)
     assert a.seed != b.seed                                                               # no seed given: a fresh one per request
+
+
+def test_tool_call_parser_round_trip_and_truncation_fuzz():
+    """Generated calls: any set of typed arguments rendered in the model's format parses back to the same values, and
+    no prefix of a rendered call (a generation cut off anywhere) makes the parser raise."""
+    import json
+    from hypothesis import given, settings, strategies as st
+    from qwserve.tool_calls import parse_tool_call
+    ident = st.text(alphabet="abcdefghijklmnopqrstuvwxyz_", min_size=1, max_size=8)
+    plain = st.text(alphabet=st.characters(blacklist_categories=("Cs",), blacklist_characters="\r"), max_size=40).filter(
+        lambda s: "<parameter=" not in s and "</parameter>" not in s and "</function>" not in s and "<function=" not in s
+        and not s.startswith("\n") and not s.endswith("\n"))
+    value = st.one_of(st.tuples(st.just("integer"), st.integers(-10**9, 10**9)),
+                      st.tuples(st.just("number"), st.floats(allow_nan=False, allow_infinity=False, width=32)),
+                      st.tuples(st.just("boolean"), st.booleans()),
+                      st.tuples(st.just("string"), plain),
+                      st.tuples(st.just("array"), st.lists(st.integers(0, 9), max_size=4)),
+                      st.tuples(st.just("object"), st.dictionaries(ident, st.integers(0, 9), max_size=3)))
+
+    def render(name, args):
+        out = [f"<function={name}>"]
+        for k, (ty, v) in args.items():
+            txt = v if ty == "string" else json.dumps(v)
+            out.append(f"<parameter={k}>\n{txt}\n</parameter>")
+        return "\n".join(out) + "\n</function>"
+
+    @settings(max_examples=150, deadline=None)
+    @given(ident, st.dictionaries(ident, value, max_size=5), st.integers(0, 10**6))
+    def check(name, args, cut):
+        tools = [{"type": "function", "function": {"name": name, "parameters": {"type": "object", "properties": {
+            k: {"type": ty} for k, (ty, _) in args.items()}}}}]
+        text = render(name, args)
+        call = parse_tool_call("some words before " + text, tools)
+        assert call["function"]["name"] == name
+        assert json.loads(call["function"]["arguments"]) == {k: v for k, (_, v) in args.items()}
+        part = parse_tool_call(text[:cut % (len(text) + 1)], tools)            # cut anywhere: a call or nothing, never an exception
+        assert part is None or json.loads(part["function"]["arguments"]) is not None
+    check()
