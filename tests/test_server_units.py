@@ -247,3 +247,53 @@ def test_tool_call_parser_round_trip_and_truncation_fuzz():
         part = parse_tool_call(text[:cut % (len(text) + 1)], tools)            # cut anywhere: a call or nothing, never an exception
         assert part is None or json.loads(part["function"]["arguments"]) is not None
     check()
+
+
+def _fake_ffmpeg(tmp_path, monkeypatch, frames=90, w=64, h=48, fps="30/1", fail=False, short_second_pass=False):
+    """Stand-ins for ffprobe / ffmpeg on PATH: the "video" decodes to `frames` raw frames, frame i filled with byte i."""
+    import stat
+    import sys
+    d = tmp_path / "bin"
+    d.mkdir(exist_ok=True)
+    (d / "ffprobe").write_text(f"#!{sys.executable}\nimport json\nprint(json.dumps({{'streams': [{{'width': {w}, 'height': {h}, 'r_frame_rate': '{fps}'}}]}}))\n")
+    count = tmp_path / "passes"
+    (d / "ffmpeg").write_text(
+        f"#!{sys.executable}\nimport os, sys\n"
+        f"p = {str(count)!r}\nn = int(open(p).read()) + 1 if os.path.exists(p) else 1\nopen(p, 'w').write(str(n))\n"
+        f"frames = {frames} - (5 if {short_second_pass} and n == 2 else 0)\n"
+        f"try:\n"
+        f"    for i in range(frames):\n        sys.stdout.buffer.write(bytes([i % 256]) * ({w} * {h} * 3))\n"
+        f"    sys.stdout.buffer.flush()\nexcept BrokenPipeError:\n    os._exit(0)\n"
+        f"if {fail}:\n    sys.stderr.write('moov atom not found')\n    sys.exit(1)\n")
+    for n in ("ffprobe", "ffmpeg"):
+        os.chmod(d / n, os.stat(d / n).st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(d) + os.pathsep + os.environ["PATH"])
+
+
+def test_video_is_decoded_as_a_stream(tmp_path, monkeypatch):
+    """Two passes over the file (count, then pick): the sampled frames are the ones the sampling rule names, equal to
+    decoding everything first, and a failing or shrinking ffmpeg is reported as a bad video, not a crash."""
+    from qwserve import vision
+    from qwserve.vision import Preprocessor, count_frames, frames_at
+    pre = Preprocessor(None)
+    _fake_ffmpeg(tmp_path, monkeypatch)
+    assert count_frames("x.mp4", 64, 48) == 90
+    got = [int(f[0, 0, 0]) for f in frames_at("x.mp4", 64, 48, [0, 3, 3, 89])]
+    assert got == [0, 3, 3, 89]
+    (tmp_path / "passes").unlink()
+    m = pre.video_bytes(b"not really a video")
+    assert int((tmp_path / "passes").read_text()) == 2                       # one counting pass, one picking pass
+    all_frames = np.stack([np.full((48, 64, 3), i, np.uint8) for i in range(90)])
+    want = pre.video(all_frames, 30.0)
+    assert m.kind == "video" and m.grid == want.grid and m.timestamps == want.timestamps and m.key == want.key
+    assert np.array_equal(m.patches, want.patches)
+    _fake_ffmpeg(tmp_path, monkeypatch, fail=True)
+    with pytest.raises(ValueError, match="ffmpeg failed .*moov atom"):
+        pre.video_bytes(b"broken")
+    _fake_ffmpeg(tmp_path, monkeypatch, short_second_pass=True)
+    (tmp_path / "passes").unlink()
+    with pytest.raises(ValueError, match="fewer frames"):
+        pre.video_bytes(b"shrinks")
+    _fake_ffmpeg(tmp_path, monkeypatch, w=0)
+    with pytest.raises(ValueError, match="no size"):
+        pre.video_bytes(b"no size")

@@ -145,17 +145,22 @@ class Preprocessor:
         return np.linspace(0, total - 1, n).round().astype(int)
 
     def video(self, frames: np.ndarray, src_fps: float) -> MediaItem:
-        """frames uint8 [N, H, W, 3] decoded at ``src_fps``."""
-        from PIL import Image
+        """frames uint8 [N, H, W, 3] decoded at ``src_fps`` (all of them in memory: tests and short clips)."""
         idx = self.sample_indices(len(frames), src_fps)
-        _, h0, w0, _ = frames.shape
+        return self.video_sampled((frames[i] for i in idx), idx, src_fps, frames.shape[1], frames.shape[2])
+
+    def video_sampled(self, picked, idx: np.ndarray, src_fps: float, h0: int, w0: int) -> MediaItem:
+        """``picked`` yields the frames at the source indices ``idx`` (uint8 [h0, w0, 3]), one at a time; each is resized
+        and normalised as it arrives, so only the sampled frames at model resolution are ever held."""
+        from PIL import Image
         h, w = video_smart_resize(len(idx), h0, w0, self.vid_min, self.vid_max)
         out = []
-        for i in idx:
-            f = frames[i]
+        for f in picked:
             if (h, w) != (h0, w0):
                 f = np.asarray(Image.fromarray(f).resize((w, h), Image.BICUBIC))
             out.append(normalize(f, self.vid_mean, self.vid_std))
+        if len(out) != len(idx):
+            raise ValueError("the video ended before its last sampled frame")
         if len(out) % FRAMES_PER_PATCH:
             out.append(out[-1])
             idx = np.append(idx, idx[-1])
@@ -164,26 +169,115 @@ class Preprocessor:
         return MediaItem("video", rows, grid, content_key(rows, grid), stamps)
 
     def video_bytes(self, data: bytes) -> MediaItem:
-        """Decode with the ffmpeg executable (raw rgb24 over a pipe)."""
+        """Decode with the ffmpeg executable, streaming: raw rgb24 frames come over a pipe one at a time and are never
+        all in memory (a minute of 1080p is 11 GB raw).  Two passes over the file: the first counts the frames ffmpeg
+        really decodes (container metadata is not reliable), the second keeps the sampled ones and stops ffmpeg after the
+        last of them.  (Reference behaviour: server/qwserve/vision.py:205-275.)"""
         if not shutil.which("ffmpeg") or not shutil.which("ffprobe"):
             raise ValueError("video input needs ffmpeg and ffprobe on PATH")
         import tempfile
         with tempfile.NamedTemporaryFile(suffix=".bin") as f:
             f.write(data)
             f.flush()
-            probe = subprocess.run(["ffprobe", "-v", "error", "-select_streams", "v:0", "-show_entries",
-                                    "stream=width,height,r_frame_rate", "-of", "json", f.name],
-                                   capture_output=True, timeout=60, check=True)
-            st = json.loads(probe.stdout)["streams"][0]
-            w, h = int(st["width"]), int(st["height"])
-            num, den = st["r_frame_rate"].split("/")
-            fps = float(num) / max(1.0, float(den))
-            raw = subprocess.run(["ffmpeg", "-v", "error", "-i", f.name, "-f", "rawvideo", "-pix_fmt", "rgb24", "-"],
-                                 capture_output=True, timeout=300, check=True).stdout
-        n = len(raw) // (w * h * 3)
-        if n == 0:
-            raise ValueError("no frames decoded")
-        return self.video(np.frombuffer(raw[:n * w * h * 3], np.uint8).reshape(n, h, w, 3), fps)
+            try:
+                probe = subprocess.run(["ffprobe", "-v", "error", "-select_streams", "v:0", "-show_entries",
+                                        "stream=width,height,r_frame_rate", "-of", "json", f.name],
+                                       capture_output=True, timeout=60, check=True)
+                st = json.loads(probe.stdout)["streams"][0]
+                w, h = int(st["width"]), int(st["height"])
+                num, _, den = str(st["r_frame_rate"]).partition("/")
+                fps = float(num) / max(1.0, float(den or 1))
+            except (subprocess.SubprocessError, ValueError, KeyError, IndexError) as ex:
+                raise ValueError(f"not a video ffprobe can read ({type(ex).__name__})") from ex
+            if w <= 0 or h <= 0 or fps <= 0:
+                raise ValueError("the video reports no size or frame rate")
+            total = count_frames(f.name, w, h)
+            if total == 0:
+                raise ValueError("no frames decoded")
+            idx = self.sample_indices(total, fps)
+            return self.video_sampled(frames_at(f.name, w, h, idx), idx, fps, h, w)
+
+
+FFMPEG_SECONDS = 300.0
+
+
+class _RawVideo:
+    """ffmpeg decoding a file to raw rgb24 on a pipe, killed after ``FFMPEG_SECONDS``.  Its stderr goes to a file: a pipe
+    that nobody reads would stall it.  ``close(finished)``: a pass that read the whole stream requires ffmpeg to have
+    succeeded; a pass that stopped early just ends it."""
+
+    def __init__(self, path: str):
+        import tempfile
+        import threading
+        self.err = tempfile.TemporaryFile()
+        self.proc = subprocess.Popen(["ffmpeg", "-v", "error", "-i", path, "-f", "rawvideo", "-pix_fmt", "rgb24", "-"],
+                                     stdout=subprocess.PIPE, stderr=self.err)
+        self.timer = threading.Timer(FFMPEG_SECONDS, self.proc.kill)
+        self.timer.daemon = True
+        self.timer.start()
+
+    def fill(self, buf: bytearray) -> int:
+        """Read until ``buf`` is full or the stream ends; returns the bytes read."""
+        view, got = memoryview(buf), 0
+        while got < len(buf):
+            n = self.proc.stdout.readinto(view[got:])
+            if not n:
+                break
+            got += n
+        return got
+
+    def close(self, finished: bool) -> None:
+        self.timer.cancel()
+        self.proc.stdout.close()
+        if not finished:
+            self.proc.kill()
+        code = self.proc.wait()
+        try:
+            if finished and code != 0:
+                self.err.seek(0)
+                raise ValueError(f"ffmpeg failed ({code}): {self.err.read()[-300:].decode(errors='replace').strip()}")
+        finally:
+            self.err.close()
+
+
+def count_frames(path: str, w: int, h: int) -> int:
+    """How many frames ffmpeg decodes from the file, keeping none of them."""
+    size = w * h * 3
+    rv = _RawVideo(path)
+    done, total = False, 0
+    try:
+        chunk = bytearray(max(size, 4 << 20) // size * size)
+        while True:
+            n = rv.fill(chunk)
+            total += n
+            if n < len(chunk):
+                break
+        done = True
+    finally:
+        rv.close(done)
+    if total % size:
+        raise ValueError("the decoded video does not match the size it reports")
+    return total // size
+
+
+def frames_at(path: str, w: int, h: int, idx: Sequence[int]):
+    """Yields the frames at the source indices ``idx`` (ascending; an index may repeat) as uint8 [h, w, 3]; every other
+    frame is read and dropped, and decoding stops after the last index."""
+    buf = bytearray(w * h * 3)
+    rv = _RawVideo(path)
+    i = j = 0
+    try:
+        while j < len(idx):
+            if rv.fill(buf) < len(buf):
+                raise ValueError("the video has fewer frames than on the first pass")
+            if idx[j] == i:
+                frame = np.frombuffer(bytes(buf), np.uint8).reshape(h, w, 3)
+                while j < len(idx) and idx[j] == i:
+                    yield frame
+                    j += 1
+            i += 1
+    finally:
+        rv.close(False)
 
 
 # ---- fetching
