@@ -18,6 +18,7 @@ def parse_args(argv=None):
     p.add_argument("--slots", default="131072,32768,32768,32768", help="context capacity of each slot, comma separated")
     p.add_argument("--kv-spill", choices=["on", "off"], default="off", help="keep KV pages beyond the resident window in host memory")
     p.add_argument("--slot-max-tokens", type=int, default=0, help="with --kv-spill on: total capacity of a slot")
+    p.add_argument("--weight-cache-dir", default=None, help="directory for the converted-weights cache (faster restarts)")
     p.add_argument("--prefill-chunk", type=int, default=4096)
     p.add_argument("--reasoning-effort", default=None, choices=[None, "low", "medium", "high", "xhigh"])
     p.add_argument("--thinking-budget", type=int, default=0, help="default reasoning budget in tokens (0 = unlimited)")
@@ -48,6 +49,8 @@ def main(argv=None):
         opts["synthetic"] = a.synthetic
     if a.kv_spill == "on":
         opts["kv_spill"], opts["slot_max_tokens"] = True, a.slot_max_tokens
+    if a.weight_cache_dir:
+        opts["weight_cache_dir"] = a.weight_cache_dir
     if a.disk_cache_dir:
         opts["disk_cache_dir"], opts["disk_cache_gb"] = a.disk_cache_dir, a.disk_cache_gb
     eng = Engine(opts, a.lib)
