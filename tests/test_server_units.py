@@ -168,6 +168,12 @@ def test_spill_plan_from_serving_options():
     assert cap == 10240 and dev == 2 * 32 and host == 2 * 8
     assert spill_plan([32768] * 2, 16384, True) == (16384, None, 0)                         # nothing to spill
     assert spill_plan([1024], 4096, False, dev_pages=2, host_pages=6) == (4096, 2, 6)       # explicit pages win
+    # the reference's per-slot list: tokens beyond each slot's device part; slots it does not name get slot_max_tokens - slots[i]
+    assert spill_plan([32768, 32768], 0, False, slot_spill=[0, 98304]) == (131072, 2 * 128, 2 * 384)
+    assert spill_plan([131072, 32768, 32768], 262144, False, slot_spill=[0]) == (262144, 3 * 512, 3 * 512)
+    assert spill_plan([8192, 8192], 0, False, slot_spill=[0, 0]) == (8192, None, 0)          # all zero: no spill
+    with pytest.raises(ValueError):
+        spill_plan([8192], 0, False, slot_spill=[256, 256])
 
 
 def test_capi_prefill_batch_reads_and_writes_the_callers_arrays():

@@ -4,15 +4,19 @@ import pytest
 
 def test_settings_from_env_aliases_validation_and_unknowns():
     from qwb200.utils.settings import Settings
-    s = Settings.from_env({"QW_TRACE": "1", "QW_SLOTS": "65536,8192", "QW_SPILL": "on", "QW_DECODE_SHARE": "0.5", "QW_PREFILL_CHUNK": "2048",
+    s = Settings.from_env({"QW_TRACE": "1", "QW_SLOTS": "65536,8192", "QW_KV_SPILL": "on", "QW_DECODE_SHARE": "0.5", "QW_PREFILL_CHUNK": "2048",
                            "QW_HOST_CACHE_GB": "16", "QW_COMM_SPLIT": "3", "QW_NOT_A_THING": "x", "HOME": "/root"}, prefill_piece=1024)
     assert s.trace and s.kv_spill and s.slots == [65536, 8192] and s.decode_share == 0.5 and s.prefill_chunk == 2048
     assert s.prefill_piece == 1024 and s.host_cache_gb == 16.0 and s.unknown == ["QW_NOT_A_THING"]
+    # the reference's spill variables: a per-slot list of tokens beyond the device part, and a switch that forces spill off
+    t = Settings.from_env({"QW_SLOT_SPILL": "0,131072", "QW_SPILL": "0", "QW_SLOT_MAX_TOKENS": "524288"})
+    assert t.slot_spill == [0, 131072] and t.spill is False and t.slot_max_tokens == 524288 and not t.unknown
+    assert Settings.from_env({}).spill is True and Settings.from_env({}).slot_spill == []
     d = s.describe()
     assert "trace=True" in d and "QW_NOT_A_THING" in d and "stuck_seconds" not in d
     assert "all defaults" in Settings.from_env({}).describe()
     for bad in ({"QW_PREFILL_CHUNK": "1000"}, {"QW_DECODE_SHARE": "0"}, {"QW_TRACE": "maybe"}, {"QW_SLOTS": "12"}, {"QW_SPILL_POLICY": "x"},
-                {"QW_SPEC_MAX_ROWS": "64"}):
+                {"QW_SPEC_MAX_ROWS": "64"}, {"QW_SLOT_SPILL": "100"}, {"QW_SLOT_MAX_TOKENS": "1000"}):
         with pytest.raises(ValueError):
             Settings.from_env(bad)
     with pytest.raises(ValueError):

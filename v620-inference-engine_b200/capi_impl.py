@@ -4,7 +4,7 @@ Every method takes the C call's scalars and the *addresses* of its buffers, read
 ctypes and forwards to the :class:`~qwb200.session.session.Session`.  ``open`` builds the engine from
 the options JSON: ``model_dir`` (a checkpoint) or ``synthetic`` (``"full" | "slice2" | "tiny"``, random
 weights), ``ple_dir`` or a synthetic table, ``slots`` (a list of capacities; the largest is used for all
-slots), ``prefill_chunk``, ``host_cache_gb``, ``disk_cache_dir``, ``disk_cache_gb``, ``devices``, ``weight_cache_dir``,
+slots), ``prefill_chunk``, ``host_cache_gb``, ``disk_cache_dir``, ``disk_cache_gb``, ``devices``, ``weight_cache_dir``, ``slot_spill``,
 ``warmup`` (capture every graph at start, default on), ``vision``.
 """
 from __future__ import annotations
@@ -305,17 +305,25 @@ def open(options_json: str) -> CApi:
     return CApi(group.local, group)
 
 
-def spill_plan(slots, slot_max_tokens: int, kv_spill: bool, dev_pages=None, host_pages: int = 0, page: int = 256):
+def spill_plan(slots, slot_max_tokens: int, kv_spill: bool, dev_pages=None, host_pages: int = 0, page: int = 256, slot_spill=()):
     """(slot capacity in tokens, device pages or None, host pages) from the serving options.  Without spill every slot
-    holds ``slot_max_tokens`` (or the largest entry of ``slots``) tokens in device memory.  With ``kv_spill`` a slot
-    holds ``slot_max_tokens`` tokens of which the first max(slots) stay in device memory and the rest live in pinned host
-    pages (the engine's slots are uniform: the reference's per-slot device capacities become the largest of them).
+    holds ``slot_max_tokens`` (or the largest entry of ``slots``) tokens in device memory.  With spill a slot's first
+    max(slots) tokens stay in device memory and the rest live in pinned host pages; its capacity is ``slot_max_tokens``
+    or, where ``slot_spill`` names tokens beyond a slot's device part (the reference's per-slot list; slots it does not
+    name get ``slot_max_tokens - slots[i]``, src/engine/engine.hip:53-69), the largest ``slots[i] + slot_spill[i]``.
+    The engine's slots are uniform: the reference's per-slot capacities become the largest of them.
     Explicit ``dev_pages`` / ``host_pages`` win."""
     n = len(slots)
     resident = max(int(x) for x in slots)
     cap = int(slot_max_tokens) if slot_max_tokens else resident
     if dev_pages is not None or host_pages:
         return cap, dev_pages, int(host_pages)
+    spill = [int(x) for x in slot_spill]
+    if len(spill) > n:
+        raise ValueError("more slot_spill entries than slots")
+    if spill:
+        per = [int(slots[i]) + (spill[i] if i < len(spill) else max(0, int(slot_max_tokens) - int(slots[i]))) for i in range(n)]
+        cap, kv_spill = max(per), True
     if not kv_spill or cap <= resident:
         return max(cap, resident) if not kv_spill else cap, None, 0
     cap_pages, res_pages = (cap + page - 1) // page, (resident + page - 1) // page
@@ -353,8 +361,11 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
     slots = o.get("slots", [8192])
     if isinstance(slots, int):
         slots = [8192] * slots
-    cap, dev_pages, host_pages = spill_plan(slots, int(o.get("slot_max_tokens") or 0), bool(o.get("kv_spill") or st.kv_spill),
-                                            o.get("dev_pages"), int(o.get("host_pages", 0)))
+    # KV spill: asked for by the option or QW_KV_SPILL, or implied by a per-slot list; QW_SPILL=0 forces it off
+    slot_spill = (o.get("slot_spill") or st.slot_spill) if st.spill else []
+    kv_spill = bool(o.get("kv_spill") or st.kv_spill or slot_spill) and st.spill
+    cap, dev_pages, host_pages = spill_plan(slots, int(o.get("slot_max_tokens") or (st.slot_max_tokens if kv_spill else 0) or 0), kv_spill,
+                                            o.get("dev_pages"), int(o.get("host_pages", 0)), slot_spill=slot_spill)
     devices = o.get("devices", [0])
     dev = f"cuda:{devices[rank]}"
     group = None

@@ -44,7 +44,9 @@ class Settings:
     gpu_sampling: bool = True           # QW_GPU_SAMPLING
     slots: List[int] = field(default_factory=lambda: [131072, 32768, 32768, 32768])      # QW_SLOTS
     slot_max_tokens: int = 0            # QW_SLOT_MAX_TOKENS (with spill)
-    kv_spill: bool = False              # QW_KV_SPILL / QW_SPILL / QW_SLOT_SPILL
+    kv_spill: bool = False              # QW_KV_SPILL (on | off)
+    slot_spill: List[int] = field(default_factory=list)     # QW_SLOT_SPILL: tokens beyond each slot's device part, per slot ("0,131072,...")
+    spill: bool = True                  # QW_SPILL=0 forces KV spill off whatever else asks for it
     spill_cache_mb: int = 256           # QW_SPILL_CACHE_MB: device cache in front of the host KV pages (0 = none)
     spill_cache_stats: bool = False     # QW_SPILL_CACHE_STATS: count hits and misses
     spill_stage: bool = True            # QW_SPILL_STAGE: prefill attention reads spilled pages from a device copy made per layer
@@ -85,7 +87,7 @@ class Settings:
     video_max_pixels: int = 0           # QW_VIDEO_MAX_PIXELS (0 = the model's own limit)
     unknown: List[str] = field(default_factory=list)
 
-    ALIASES = {"QW_SPILL": "kv_spill", "QW_SLOT_SPILL": "kv_spill"}
+    ALIASES = {}                        # old variable name -> field (none at present)
     # variables of the reference that have no meaning in this engine (PCIe transport, int8 copies, rank threads, ...):
     # accepted and ignored, so an old environment file does not produce warnings
     IGNORED = {"QW_COMM_CONCURRENT_MAX", "QW_COMM_PUSH2D", "QW_COMM_RECV_BYTES", "QW_COMM_ROWWISE", "QW_COMM_SPLIT", "QW_INT8_DENSE",
@@ -105,6 +107,8 @@ class Settings:
         need(self.prefill_lanes in (0, 1, 2), "prefill_lanes must be 0, 1 or 2")
         need(1 <= self.spec_max_rows <= 32, "spec_max_rows must be in 1..32")
         need(len(self.slots) >= 1 and all(s >= 256 for s in self.slots), "slots: at least one slot of >= 256 tokens")
+        need(all(s >= 0 and s % 256 == 0 for s in self.slot_spill), "slot_spill: multiples of 256 tokens")
+        need(self.slot_max_tokens >= 0 and self.slot_max_tokens % 256 == 0, "slot_max_tokens must be a multiple of 256")
         need(self.spill_policy in ("auto", "bind", "preferred", "interleave", "process"), "spill_policy")
         need(self.reasoning_effort in ("", "low", "medium", "high", "xhigh"), "reasoning_effort")
         need(self.host_cache_gb >= 0 and self.disk_cache_gb >= 0 and self.vision_cache_gb >= 0, "cache sizes must not be negative")
