@@ -217,3 +217,41 @@ def test_block_store_snapshot_by_address_round_trip():
     assert st.get_snapshot_into(k1, np.zeros(100, dtype=np.uint8)) == -1
     assert st.get_snapshot_into(k0, out) == -1
     assert st.get(k1, snapshot=True)[0] == bytes(src)
+
+
+def test_block_store_thins_snapshots_that_crowd_the_next_one(tmp_path):
+    """Snapshots closer than the gap to the next kept snapshot further down the conversation are dropped (RAM and file),
+    deepest first; anchors, snapshots that were restored from, leaves and branch points stay."""
+    st = H.BlockStore(9, 1, ram_budget=1 << 22, disk_dir=str(tmp_path), disk_budget=1 << 24)
+    toks = list(range(5000, 5000 + 6 * 256))
+    parent, keys = st.root, []
+    for i in range(6):
+        k = st.save_block(parent, i * 256, toks[i * 256:(i + 1) * 256], bytes([i + 1]) * 512)
+        keys.append(k)
+        parent = k
+        assert st.save_snapshot(k, bytes([65 + i]) * 300, None, anchor=(i == 2))
+    st.flush()
+    snap_file = lambda k: os.path.join(str(tmp_path), f"{k:016x}.qws")
+    assert all(os.path.exists(snap_file(k)) for k in keys)
+    # ends 256 512 768* 1024 1280 1536 (the leaf; * = anchor), gap 600: 1280 and 1024 crowd the leaf; 768 is an anchor;
+    # 512 is 256 before the anchor -> dropped; 256 is 512 before it -> dropped too
+    assert st.thin(600) == 4
+    has = [st.info(k)["has_snap"] for k in keys]
+    assert has == [False, False, True, False, False, True]
+    assert [os.path.exists(snap_file(k)) for k in keys] == has
+    assert st.get(keys[3], snapshot=True) is None and st.get(keys[5], snapshot=True)[0] == bytes([70]) * 300
+    assert st.get(keys[3]) == bytes([4]) * 512                                   # the blocks themselves are untouched
+    assert st.thin(600) == 0                                                      # nothing left to drop
+    path, depth = st.lookup(toks + [1])
+    assert path == keys and depth == 6                                            # the deepest snapshot still serves the whole prefix
+    st.close()
+    # a gap smaller than the spacing drops nothing; a branch point is never dropped
+    st = H.BlockStore(9, 1, ram_budget=1 << 22, disk_dir=None)
+    a = st.save_block(st.root, 0, [1] * 256, b"a" * 64)
+    st.save_snapshot(a, b"s" * 32, None, anchor=False)
+    b1 = st.save_block(a, 256, [2] * 256, b"b" * 64)
+    b2 = st.save_block(a, 256, [3] * 256, b"c" * 64)
+    st.save_snapshot(b1, b"t" * 32, None, anchor=False)
+    st.save_snapshot(b2, b"u" * 32, None, anchor=False)
+    assert st.thin(10000) == 0 and st.info(a)["has_snap"]
+    st.close()

@@ -382,17 +382,32 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
     opts = EngineOptions(slots=len(slots), slot_tokens=cap, prefill_chunk=int(o.get("prefill_chunk", 4096)),
                          save_gdn=bool(o.get("mtp", True)), host_pages=host_pages, dev_pages=dev_pages, use_graphs=not st.nograph)
     log = (lambda m: print(m, file=sys.stderr, flush=True)) if rank == 0 else None
+    def preflight(cfg):
+        """Before anything slow: wait for a busy GPU if asked to, then refuse what cannot fit, with the numbers."""
+        if not torch.cuda.is_available():
+            return
+        from .engine import memory_estimate as ME
+        say = log or (lambda m: None)
+        if st.start_wait_s > 0:
+            ME.wait_for_device(lambda: torch.cuda.mem_get_info(devices[rank]), st.start_wait_s, say)
+        if st.vram_check:
+            plan = ME.estimate(cfg, world, slots=len(slots), slot_tokens=cap, dev_pages=dev_pages, host_pages=host_pages,
+                               max_rows=opts.max_rows, prefill_chunk=opts.prefill_chunk, save_gdn=opts.save_gdn)
+            say("memory estimate per GPU (GB): " + ", ".join(f"{k[:-3]} {v:.1f}" for k, v in plan.items()))
+            ME.check(plan, torch.cuda.mem_get_info(devices[rank])[1], ME.host_available_bytes(), local_ranks=world)
     if "model_dir" in o and o["model_dir"]:
         from .models.config import check_hf_config
         from .models.ple import PleTable
         cfg = ModelConfig.full()
         check_hf_config(cfg, o["model_dir"])
-        table = PleTable.load(cfg, o["ple_dir"], pin=True) if o.get("ple_dir") else None
+        preflight(cfg)
+        table = PleTable.load(cfg, o["ple_dir"], pin=st.ple_pin) if o.get("ple_dir") else None
         eng = Engine.from_checkpoint(cfg, o["model_dir"], table, opts, ranks=world, rank=rank, device=dev,
                                      weight_cache_dir=o.get("weight_cache_dir") or st.weight_cache_dir or None, log=log)
     else:
         kind = o.get("synthetic", "tiny")
         cfg = {"full": ModelConfig.full, "slice2": ModelConfig.slice2, "tiny": ModelConfig.tiny}[kind]()
+        preflight(cfg)
         eng = Engine.synthetic(cfg, opts, ranks=world, rank=rank, device=dev, exact=(kind != "full"),
                                ple_rows=int(o.get("ple_rows", 1 << 16)), ple_pinned=torch.cuda.is_available())
     if world > 1:
@@ -422,6 +437,6 @@ def build_ops(o: dict, rank: int, world: int, master_port: int) -> SessionOps:
             vc = VisionConfig(depth=int(o.get("vision_depth", 2)), out_dim=cfg.hidden)
             enc = VisionEncoder(vc, synth_vision_weights(vc, seed=1), dev)
         if enc is not None:
-            vision = VisionFrontend(enc, int(float(o.get("vision_cache_gb", 2)) * (1 << 30)))
+            vision = VisionFrontend(enc, int(float(o.get("vision_cache_gb", st.vision_cache_gb)) * (1 << 30)))
             eng.vision_lookup = vision.lookup
     return SessionOps(ses, vision)

@@ -51,6 +51,7 @@ class GpuSampler:
         self.host = H.HostSampler(seed)
         self.rng = np.random.default_rng(seed)
         self.fallbacks = 0
+        self.host_only = False          # QW_GPU_SAMPLING=0: every row is drawn by the host sampler (a diagnostic: one logits row copied per draw)
 
     def reset_slot(self, slot: int):
         self.gen[slot].zero_()
@@ -90,7 +91,7 @@ class GpuSampler:
         out = self.out_host[:M * 16].numpy().view(_OUT_DT)
         toks, lps = [int(x) for x in out["token"]], [float(x) for x in out["logprob"]]
         for i in range(M):
-            if out["fallback"][i] or (force_host is not None and force_host[i]):
+            if out["fallback"][i] or self.host_only or (force_host is not None and force_host[i]):
                 self.fallbacks += 1
                 hist, pend = hists[i] if hists else ((), 0)
                 toks[i], lps[i] = self.host.sample(logits[i].float().cpu().numpy(), params[i].to_host(), hist, pend)

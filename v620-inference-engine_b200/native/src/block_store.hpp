@@ -238,20 +238,39 @@ public:
         std::unique_lock<std::mutex> lk(qmu_);
         qdone_.wait(lk, [&] { return queue_.empty() && !writing_; });
     }
-    // Drops snapshots that are closer than `gap` tokens to the next kept one (never anchors or branch points).
+    // Drops snapshots that are closer than `gap` tokens to the next kept one further down the same conversation.  Never an
+    // anchor, a snapshot that was restored from (hits), a leaf or a branch point.  Deepest first, so that "the next kept
+    // one" is already decided when a snapshot is looked at; the result does not depend on the map's order.
+    // (Role of the reference's QW_SNAP_KEEP_GAP thinning: src/session/block_store.cpp:499-541.)
     int thin(int64_t gap) {
         std::lock_guard<std::mutex> lk(mu_);
-        int dropped = 0;
+        std::vector<Node *> cand;
         for (auto &kv : nodes_) {
             Node &nd = kv.second;
-            if (!nd.has_snap || nd.anchor || nd.hits > 0 || nd.children != 1) continue;
-            const Node &child = nodes_.at(children_[nd.key][0]);
-            if (child.has_snap && child.end() - nd.end() < gap) {
-                ram_ -= nd.snap.size();
-                nd.snap.clear(); nd.logits.clear();
-                nd.has_snap = false;
-                ++dropped;
+            if (nd.has_snap && !nd.anchor && nd.hits == 0 && nd.children == 1) cand.push_back(&nd);
+        }
+        std::sort(cand.begin(), cand.end(), [](const Node *a, const Node *b) { return a->end() != b->end() ? a->end() > b->end() : a->key < b->key; });
+        int dropped = 0;
+        for (Node *nd : cand) {
+            // the nearest snapshot below, following only children
+            const Node *next = nd;
+            for (;;) {
+                auto ch = children_.find(next->key);
+                if (ch == children_.end() || ch->second.size() != 1) { next = nullptr; break; }
+                next = &nodes_.at(ch->second[0]);
+                if (next->has_snap) break;
             }
+            if (!next || next->end() - nd->end() >= gap) continue;
+            ram_ -= nd->snap.size();
+            if (nd->snap_disk) {
+                disk_ -= std::min(disk_, sizeof(DiskHeader) + nd->logits.size() * 4 + nd->snap_bytes);
+                std::remove(path(nd->key, true).c_str());
+                nd->snap_disk = false;
+            }
+            nd->snap.clear(); nd->snap.shrink_to_fit(); nd->logits.clear();
+            nd->has_snap = false;
+            nd->snap_bytes = 0;
+            ++dropped;
         }
         return dropped;
     }
@@ -339,6 +358,10 @@ private:
         auto it = nodes_.find(key);
         if (it == nodes_.end()) return;
         const size_t bytes = sizeof h + toks.size() * 4 + logits.size() * 4 + payload.size();
+        if (snap && !it->second.has_snap) {          // the snapshot was dropped while its file was being written
+            std::remove(fin.c_str());
+            return;
+        }
         (snap ? it->second.snap_disk : it->second.kv_disk) = true;
         disk_ += bytes;
         enforce();

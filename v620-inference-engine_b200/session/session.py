@@ -104,6 +104,8 @@ class Session:
         from ..utils import settings as _settings
         from ..utils.trace import PhaseTrace
         self.gen_trace = PhaseTrace(_settings.get().trace, "generate")     # QW_TRACE: per-phase milliseconds of generate()
+        self.spec_log = bool(_settings.get().spec_log)                     # QW_SPEC_LOG: one line per speculative step and request
+        self.spec_max_rows = int(_settings.get().spec_max_rows)            # QW_SPEC_MAX_ROWS: longest verification run of a request (0 = the engine's limit)
         self.io = StateIO(engine.dm)
         n = engine.opts.slots
         self.slots = [SlotInfo() for _ in range(n)]
@@ -116,11 +118,16 @@ class Session:
         self.pool = None
         if torch.cuda.is_available() and (host_cache_bytes > 0 or bool(disk_cache_dir)):          # no store tier: nothing to stage, nothing to pin
             try:
-                self.pool = H.PinnedPool(self.io.kv_block_bytes, arena_bytes=max(64 << 20, 16 * self.io.kv_block_bytes), standing_units=2,
+                # QW_POOL_RESERVE_GB: pinned units kept ready for a burst of saves (0: two units; pinning more happens in the
+                # background and can stall the host's launches while it runs)
+                standing = max(2, int(_settings.get().pool_reserve_gb * (1 << 30)) // max(1, self.io.kv_block_bytes))
+                self.pool = H.PinnedPool(self.io.kv_block_bytes, arena_bytes=max(64 << 20, 16 * self.io.kv_block_bytes), standing_units=standing,
                                          use_cuda=True)
             except Exception:
                 self.pool = None          # no pinned memory to be had: blocks take the pageable path
         self.sampler = GpuSampler(engine.dm.lib, engine.dm.dev, engine.cfg.vocab, n, engine.opts.max_rows, seed)
+        self.sampler.host_only = not _settings.get().gpu_sampling
+        self.snap_keep_gap = int(_settings.get().snap_keep_gap)          # QW_SNAP_KEEP_GAP: thin stored snapshots closer than this to the next one
         self.vram_snaps: List[VramSnap] = []
         self.snap_min_gap = max(BLOCK, int(_settings.get().snap_min_gap))
         self.prompt_tokens = self.reused_tokens = self.blend_candidate_tokens = 0
@@ -406,6 +413,8 @@ class Session:
                 self.store.save_snapshot_from(si.block_keys[-1], addr, nb, anchor)
             else:
                 self.store.save_snapshot(si.block_keys[-1], self.io.export_recurrent(slot), None, anchor)
+            if self.snap_keep_gap > 0:
+                self.store.thin(self.snap_keep_gap)
         si.timing["save_s"] += time.time() - t0
 
     def sample_prompt(self, slot: int, p: SamplingParams) -> Tuple[int, float]:
@@ -463,6 +472,8 @@ class Session:
             if r.budget < 1:
                 raise ValueError("a request needs a budget of at least one token")
             kk = min(k, r.budget - 1, e.MAX_DRAFTS) if (e.mtp and sl.mtp_hidden is not None) else 0
+            if self.spec_max_rows > 0:
+                kk = min(kk, self.spec_max_rows - 1)
             if kk > 0 and force_accept is None:
                 si = self.slots[r.slot]
                 if si.plain_left > 0:
@@ -564,6 +575,8 @@ class Session:
                     si.plain_stretch = PLAIN_FIRST                        # a good spell: the next stretch starts short again
             tr.count("drafts", len(d))
             tr.count("accepted", n_acc - 1)
+            if self.spec_log and d:
+                print(f"spec: slot {r.slot} pos {self.e.slot[r.slot].n} drafts {len(d)} accepted {n_acc - 1} rate {si.accept:.2f}", flush=True)
             stopped = bool(emitted) and emitted[-1] in si.stop
             outs.append(StepOut(emitted, lps[row0:row0 + len(emitted)], sum(n_acc_all[:-1]), stopped))
             keep_rows.append(logits[row0:row0 + n_acc])

@@ -41,7 +41,7 @@ class Settings:
     nograph: bool = False               # QW_NOGRAPH: run steps without CUDA graphs
     no_mtp: bool = False                # QW_NO_MTP
     no_vision: bool = False             # QW_NO_VISION
-    gpu_sampling: bool = True           # QW_GPU_SAMPLING
+    gpu_sampling: bool = True           # QW_GPU_SAMPLING: 0 draws every token with the host sampler
     slots: List[int] = field(default_factory=lambda: [131072, 32768, 32768, 32768])      # QW_SLOTS
     slot_max_tokens: int = 0            # QW_SLOT_MAX_TOKENS (with spill)
     kv_spill: bool = False              # QW_KV_SPILL (on | off)
@@ -58,27 +58,25 @@ class Settings:
     gdn_sequential: bool = False        # QW_GDN_SEQUENTIAL: token-major prefill scans GDN layers row by row (not chunked)
     prefill_py: bool = False            # QW_PREFILL_PY: token-major prefill scheduled from Python, kernel by kernel (one GPU; the native runtime is the default)
     prefill_lanes: int = 0              # QW_PREFILL_LANES: micro-batches per chunk, 1 or 2 (0 = two on eight GPUs, one below)
-    spec_max_rows: int = 8              # QW_SPEC_MAX_ROWS: rows of one verification step
+    spec_max_rows: int = 0              # QW_SPEC_MAX_ROWS: longest verification run of one request, pending token included (0 = the engine's limit, 13)
     weight_cache_dir: str = ""          # QW_WEIGHT_CACHE_DIR
     ple_dir: str = ""                   # QW_PLE_DIR
     ple_pin: bool = True                # QW_PLE_PIN
-    load_threads: int = 8               # QW_LOAD_THREADS
-    vram_check: bool = True             # QW_VRAM_CHECK
+    vram_check: bool = True             # QW_VRAM_CHECK: refuse a configuration whose estimate does not fit the GPU or the host, before loading
     # ---- session / caches
     host_cache_gb: float = 128.0        # QW_HOST_CACHE_GB
     disk_cache_dir: str = ""            # QW_DISK_CACHE_DIR
     disk_cache_gb: float = 200.0        # QW_DISK_CACHE_GB
     snap_min_gap: int = 1024            # QW_SNAP_MIN_GAP
-    snap_keep_gap: int = 0              # QW_SNAP_KEEP_GAP
-    slot_move: bool = True              # QW_SLOT_MOVE
-    pool_reserve_gb: float = 2.0        # QW_POOL_RESERVE_GB
+    snap_keep_gap: int = 0              # QW_SNAP_KEEP_GAP: stored snapshots closer than this many tokens to the next kept one are dropped (0 = keep all)
+    pool_reserve_gb: float = 0.0        # QW_POOL_RESERVE_GB: pinned block units kept ready for a burst of prefix-cache saves (0 = two units)
     vision_cache_gb: float = 2.0        # QW_VISION_CACHE_GB
     # ---- server
     decode_share: float = 0.25          # QW_DECODE_SHARE
     stuck_seconds: float = 300.0        # QW_STUCK_SECONDS
     exit_grace: float = 30.0            # QW_EXIT_GRACE
     watchdog_exit: bool = True          # QW_WATCHDOG_EXIT
-    start_wait_s: float = 600.0         # QW_START_WAIT_S
+    start_wait_s: float = 0.0           # QW_START_WAIT_S: at start, wait up to this long for another process to leave the GPUs (0 = do not wait)
     thinking_budget: int = 0            # QW_THINKING_BUDGET
     reasoning_effort: str = ""          # QW_REASONING_EFFORT
     media_fetch: bool = True            # QW_MEDIA_FETCH
@@ -91,9 +89,9 @@ class Settings:
     # variables of the reference that have no meaning in this engine (PCIe transport, int8 copies, rank threads, ...):
     # accepted and ignored, so an old environment file does not produce warnings
     IGNORED = {"QW_COMM_CONCURRENT_MAX", "QW_COMM_PUSH2D", "QW_COMM_RECV_BYTES", "QW_COMM_ROWWISE", "QW_COMM_SPLIT", "QW_INT8_DENSE",
-               "QW_INT8_DIR", "QW_INT8_DUMP", "QW_INT8_EXPERTS", "QW_INT8_SKIP", "QW_KV_PAIRS", "QW_KV_PAIR_CHECK", "QW_LOAD_SERIAL",
+               "QW_INT8_DIR", "QW_INT8_DUMP", "QW_INT8_EXPERTS", "QW_INT8_SKIP", "QW_KV_PAIRS", "QW_KV_PAIR_CHECK", "QW_LOAD_SERIAL", "QW_LOAD_THREADS",
                "QW_MOE_PAIR_MAX", "QW_NO_SPLIT", "QW_POOL_ARENA", "QW_POOL_PREPIN", "QW_POOL_SERIAL", "QW_PREFILL_BATCH",
-               "QW_PREFILL_PIPELINE", "QW_RESERVE_AHEAD", "QW_SHARE_MIN", "QW_SHARE_WAIT", "QW_SLOT_MOVE_IDLE_S", "QW_SNAP_SYSTEM_MIN",
+               "QW_PREFILL_PIPELINE", "QW_RESERVE_AHEAD", "QW_SHARE_MIN", "QW_SHARE_WAIT", "QW_SLOT_MOVE", "QW_SLOT_MOVE_IDLE_S", "QW_SNAP_SYSTEM_MIN",
                "QW_SPEC_BASE", "QW_SPEC_COST", "QW_SPEC_MIXED", "QW_SPILL_LOCALITY", "QW_SPILL_MARGIN_GB",
                "QW_SPILL_NC", "QW_SPILL_NUMA", "QW_VIT_GEMM_ATTN", "QW_MOE_MMA", "QW_SKIP"}
 
@@ -105,7 +103,7 @@ class Settings:
         need(self.prefill_piece > 0 and self.prefill_piece % 256 == 0, "prefill_piece must be a positive multiple of 256")
         need(0.0 < self.decode_share <= 1.0, "decode_share must be in (0, 1]")
         need(self.prefill_lanes in (0, 1, 2), "prefill_lanes must be 0, 1 or 2")
-        need(1 <= self.spec_max_rows <= 32, "spec_max_rows must be in 1..32")
+        need(0 <= self.spec_max_rows <= 32, "spec_max_rows must be in 0..32")
         need(len(self.slots) >= 1 and all(s >= 256 for s in self.slots), "slots: at least one slot of >= 256 tokens")
         need(all(s >= 0 and s % 256 == 0 for s in self.slot_spill), "slot_spill: multiples of 256 tokens")
         need(self.slot_max_tokens >= 0 and self.slot_max_tokens % 256 == 0, "slot_max_tokens must be a multiple of 256")
