@@ -255,3 +255,15 @@ def test_block_store_thins_snapshots_that_crowd_the_next_one(tmp_path):
     st.save_snapshot(b2, b"u" * 32, None, anchor=False)
     assert st.thin(10000) == 0 and st.info(a)["has_snap"]
     st.close()
+
+
+def test_thread_pool_visits_every_index_once():
+    """The worker pool behind the PLE gather and the fp32 oracle: many short loops back to back (late helpers must not
+    disturb the next loop), sizes that do not divide, a grain larger than the loop, one thread."""
+    L = H.lib()
+    for threads in (1, 2, 8):
+        pool = L.qwh_pool_new(threads)
+        assert L.qwh_pool_size(pool) == threads
+        for n, grain, rounds in ((1, 1, 50), (7, 1, 2000), (1000, 1, 500), (1001, 64, 500), (100, 1000, 50), (100003, 17, 20), (0, 1, 3)):
+            assert L.qwh_pool_check(pool, n, grain, rounds) == 0, (threads, n, grain)
+        L.qwh_pool_free(pool)

@@ -296,7 +296,10 @@ def test_dashboard_and_shutdown_persist():
     async def fn(c):
         await c.post("/v1/chat/completions", json={"messages": MSG})
         page = await c.get("/")
-        m = await c.get("/metrics.json")
+        again = await c.get("/dashboard", headers={"If-None-Match": page.headers["ETag"]})
+        bad = await c.get("/metrics.json?tail=lots")
+        m = await c.get("/metrics.json?tail=5")
+        assert again.status == 304 and bad.status == 400
         return page.status, (await page.text())[:15], await m.json()
     ps, head, m = with_client(srv, fn)
     assert ps == 200 and head.lower().startswith("<!doctype html>")

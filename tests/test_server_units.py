@@ -280,12 +280,16 @@ def test_video_is_decoded_as_a_stream(tmp_path, monkeypatch):
     """Two passes over the file (count, then pick): the sampled frames are the ones the sampling rule names, equal to
     decoding everything first, and a failing or shrinking ffmpeg is reported as a bad video, not a crash."""
     from qwserve import vision
-    from qwserve.vision import Preprocessor, count_frames, frames_at
+    from qwserve.vision import Preprocessor, VideoPipe
     pre = Preprocessor(None)
     _fake_ffmpeg(tmp_path, monkeypatch)
-    assert count_frames("x.mp4", 64, 48) == 90
-    got = [int(f[0, 0, 0]) for f in frames_at("x.mp4", 64, 48, [0, 3, 3, 89])]
-    assert got == [0, 3, 3, 89]
+    with VideoPipe("x.mp4", 64, 48) as pipe:
+        assert sum(1 for _ in pipe.frames()) == 90
+    with VideoPipe("x.mp4", 64, 48) as pipe:
+        picked = list(pipe.pick([0, 3, 3, 89]))
+    assert [int(f[0, 0, 0]) for f in picked] == [0, 3, 3, 89] and picked[0].shape == (48, 64, 3)
+    with VideoPipe("x.mp4", 64, 48) as pipe:                                  # stopping early just ends ffmpeg
+        assert [int(f[0, 0, 0]) for f in pipe.pick([2])] == [2]
     (tmp_path / "passes").unlink()
     m = pre.video_bytes(b"not really a video")
     assert int((tmp_path / "passes").read_text()) == 2                       # one counting pass, one picking pass

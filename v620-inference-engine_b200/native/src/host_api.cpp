@@ -44,6 +44,27 @@ API int qwh_ngram_ids(void *h, const int32_t *hist, int n_hist, const int32_t *t
 // ---- thread pool
 API void *qwh_pool_new(int threads) { return new ThreadPool(threads); }
 API void qwh_pool_free(void *p) { delete static_cast<ThreadPool *>(p); }
+API int qwh_pool_size(void *p) { return static_cast<ThreadPool *>(p)->size(); }
+// Self check: `rounds` loops over [0, n) in pieces of at least `grain`; every index must be visited exactly once per loop
+// and no piece may be shorter than it has to be.  Returns the number of violations seen.
+API long long qwh_pool_check(void *p, long long n, long long grain, int rounds) {
+    ThreadPool &pool = *static_cast<ThreadPool *>(p);
+    std::vector<unsigned char> hits(size_t(n > 0 ? n : 0));
+    long long bad = 0;
+    for (int r = 0; r < rounds; ++r) {
+        std::fill(hits.begin(), hits.end(), 0);
+        std::atomic<long long> pieces{0}, wrong{0};
+        pool.parallel_for(n, grain, [&](int64_t lo, int64_t hi) {
+            if (lo < 0 || hi > n || lo >= hi) wrong.fetch_add(1);
+            for (int64_t i = lo; i < hi && i < n; ++i) ++hits[size_t(i)];
+            pieces.fetch_add(1);
+        });
+        bad += wrong.load();
+        for (unsigned char h : hits) bad += h != 1;
+        if (n > 0 && (pieces.load() < 1 || pieces.load() > (long long)pool.size() * 4)) ++bad;
+    }
+    return bad;
+}
 
 // ---- PLE table
 API void *qwh_ple_open(const char *dir, int width) { GUARD(return new PleTable(dir, width);, nullptr) }

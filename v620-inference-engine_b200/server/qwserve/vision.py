@@ -191,93 +191,90 @@ class Preprocessor:
                 raise ValueError(f"not a video ffprobe can read ({type(ex).__name__})") from ex
             if w <= 0 or h <= 0 or fps <= 0:
                 raise ValueError("the video reports no size or frame rate")
-            total = count_frames(f.name, w, h)
+            with VideoPipe(f.name, w, h) as pipe:                    # pass 1: how many frames are really there
+                total = sum(1 for _ in pipe.frames())
             if total == 0:
                 raise ValueError("no frames decoded")
             idx = self.sample_indices(total, fps)
-            return self.video_sampled(frames_at(f.name, w, h, idx), idx, fps, h, w)
+            with VideoPipe(f.name, w, h) as pipe:                    # pass 2: keep the sampled ones, stop after the last
+                return self.video_sampled(pipe.pick(idx), idx, fps, h, w)
 
 
 FFMPEG_SECONDS = 300.0
 
 
-class _RawVideo:
-    """ffmpeg decoding a file to raw rgb24 on a pipe, killed after ``FFMPEG_SECONDS``.  Its stderr goes to a file: a pipe
-    that nobody reads would stall it.  ``close(finished)``: a pass that read the whole stream requires ffmpeg to have
-    succeeded; a pass that stopped early just ends it."""
+class VideoPipe:
+    """One ffmpeg process turning a file into raw rgb24 frames on its standard output, read one frame at a time.
 
-    def __init__(self, path: str):
+        with VideoPipe(path, w, h) as pipe:
+            for frame in pipe.frames(): ...          # uint8 [h, w, 3] views of one reused buffer
+
+    Leaving the block after the stream was read to its end checks ffmpeg's exit code (a decode error is a bad video);
+    leaving it earlier just ends the process.  A watchdog ends an ffmpeg that runs longer than ``FFMPEG_SECONDS``.
+    Diagnostics go to a scratch file, since an unread pipe would block the child once it fills."""
+
+    def __init__(self, path: str, w: int, h: int):
+        self.cmd = ["ffmpeg", "-v", "error", "-i", path, "-f", "rawvideo", "-pix_fmt", "rgb24", "-"]
+        self.shape = (h, w, 3)
+        self.nbytes = h * w * 3
+        self.exhausted = False
+
+    def __enter__(self):
         import tempfile
         import threading
-        self.err = tempfile.TemporaryFile()
-        self.proc = subprocess.Popen(["ffmpeg", "-v", "error", "-i", path, "-f", "rawvideo", "-pix_fmt", "rgb24", "-"],
-                                     stdout=subprocess.PIPE, stderr=self.err)
-        self.timer = threading.Timer(FFMPEG_SECONDS, self.proc.kill)
-        self.timer.daemon = True
-        self.timer.start()
+        self.log = tempfile.TemporaryFile()
+        self.child = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=self.log, bufsize=0)
+        self.watchdog = threading.Timer(FFMPEG_SECONDS, self.child.kill)
+        self.watchdog.daemon = True
+        self.watchdog.start()
+        return self
 
-    def fill(self, buf: bytearray) -> int:
-        """Read until ``buf`` is full or the stream ends; returns the bytes read."""
-        view, got = memoryview(buf), 0
-        while got < len(buf):
-            n = self.proc.stdout.readinto(view[got:])
-            if not n:
-                break
-            got += n
-        return got
-
-    def close(self, finished: bool) -> None:
-        self.timer.cancel()
-        self.proc.stdout.close()
-        if not finished:
-            self.proc.kill()
-        code = self.proc.wait()
-        try:
-            if finished and code != 0:
-                self.err.seek(0)
-                raise ValueError(f"ffmpeg failed ({code}): {self.err.read()[-300:].decode(errors='replace').strip()}")
-        finally:
-            self.err.close()
-
-
-def count_frames(path: str, w: int, h: int) -> int:
-    """How many frames ffmpeg decodes from the file, keeping none of them."""
-    size = w * h * 3
-    rv = _RawVideo(path)
-    done, total = False, 0
-    try:
-        chunk = bytearray(max(size, 4 << 20) // size * size)
+    def frames(self):
+        buf = np.empty(self.nbytes, np.uint8)
+        view = memoryview(buf)
         while True:
-            n = rv.fill(chunk)
-            total += n
-            if n < len(chunk):
-                break
-        done = True
-    finally:
-        rv.close(done)
-    if total % size:
-        raise ValueError("the decoded video does not match the size it reports")
-    return total // size
+            have = 0
+            while have < self.nbytes:
+                got = self.child.stdout.readinto(view[have:])
+                if not got:
+                    break
+                have += got
+            if have == 0:
+                self.exhausted = True
+                return
+            if have < self.nbytes:
+                raise ValueError("the decoded video does not match the size it reports")
+            yield buf.reshape(self.shape)
 
+    def pick(self, idx: Sequence[int]):
+        """Copies of the frames at the ascending source indices ``idx`` (an index may repeat); decoding stops after the last."""
+        want = [int(i) for i in idx]
+        at = 0
+        for n, frame in enumerate(self.frames()):
+            if at < len(want) and want[at] == n:
+                keep = frame.copy()
+                while at < len(want) and want[at] == n:
+                    yield keep
+                    at += 1
+            if at == len(want):
+                return
+        if at < len(want):
+            raise ValueError("the video has fewer frames than on the first pass")
 
-def frames_at(path: str, w: int, h: int, idx: Sequence[int]):
-    """Yields the frames at the source indices ``idx`` (ascending; an index may repeat) as uint8 [h, w, 3]; every other
-    frame is read and dropped, and decoding stops after the last index."""
-    buf = bytearray(w * h * 3)
-    rv = _RawVideo(path)
-    i = j = 0
-    try:
-        while j < len(idx):
-            if rv.fill(buf) < len(buf):
-                raise ValueError("the video has fewer frames than on the first pass")
-            if idx[j] == i:
-                frame = np.frombuffer(bytes(buf), np.uint8).reshape(h, w, 3)
-                while j < len(idx) and idx[j] == i:
-                    yield frame
-                    j += 1
-            i += 1
-    finally:
-        rv.close(False)
+    def __exit__(self, exc_type, exc, tb):
+        self.watchdog.cancel()
+        self.child.stdout.close()
+        if not self.exhausted:
+            self.child.kill()
+        code = self.child.wait()
+        try:
+            if exc_type is None and self.exhausted and code != 0:
+                self.log.seek(0)
+                tail = self.log.read()[-300:].decode(errors="replace").strip()
+                raise ValueError(f"ffmpeg failed ({code}): {tail}")
+        finally:
+            self.log.close()
+        return False
 
 
 # ---- fetching
