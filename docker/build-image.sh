@@ -1,0 +1,28 @@
+#!/usr/bin/env bash
+# Build the engine's image from this checkout, here or on a remote docker host.
+#
+#   docker/build-image.sh                      # local docker
+#   docker/build-image.sh user@gpu-host        # the tree goes over ssh as a tar stream; nothing is cloned there
+#   docker/build-image.sh user@gpu-host tag
+#
+# The image is tagged qw-b200:<short commit> (or the tag given) and qw-b200:latest.  Built libraries, caches and the
+# repository's history stay out of the build context; the kernels are compiled inside the image.
+set -euo pipefail
+
+root=$(cd "$(dirname "${BASH_SOURCE[0]}")/.." && pwd)
+where=${1:-local}
+rev=$(git -C "$root" rev-parse --short HEAD 2>/dev/null || echo dev)
+tag=${2:-qw-b200:$rev}
+
+context() {
+    tar -C "$root" --exclude=./.git --exclude=./gpurun_out --exclude=./_work --exclude=./baseline --exclude='*.so' \
+        --exclude=__pycache__ --exclude=.pytest_cache -cf - .
+}
+build=(docker build -t "$tag" -t qw-b200:latest -f docker/Dockerfile -)
+
+if [ "$where" = local ]; then
+    context | "${build[@]}"
+else
+    context | ssh "$where" "$(printf '%q ' "${build[@]}")"
+fi
+echo "built $tag on $where"
