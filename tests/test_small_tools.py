@@ -37,3 +37,13 @@ def test_text_tokens_round_trip(tmp_path):
     assert tt.main([str(tmp_path / "tok.json"), str(tmp_path / "ids"), str(tmp_path / "x.txt"), str(tmp_path / "y.txt")]) == 0
     assert tt.read_ids(str(tmp_path / "ids")) == [0, 1, 1, 1, 2, 0]
     assert tt.main([]) == 2
+
+
+def test_prefill_bench_reads_a_token_file(tmp_path):
+    from qwb200.tools.prefill_bench import read_token_file
+    f = tmp_path / "ids.txt"
+    f.write_text("1, 2,3\n4 5\t6,\n")
+    assert read_token_file(str(f), 10) == [1, 2, 3, 4, 5, 6]
+    import pytest
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        read_token_file(str(f), 6)

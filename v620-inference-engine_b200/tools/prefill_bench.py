@@ -1,6 +1,7 @@
 """Prefill throughput and where the time goes, on one GPU or on N (one process per GPU under torchrun):
 
     python -m qwb200.tools.prefill_bench [--tokens 4096] [--chunk 4096] [--ctx 0] [--layers 0] [--lanes 0] [--by-step]
+                                         [--tokens-file ids.txt] [--energy]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         -m qwb200.tools.prefill_bench ...
 
@@ -8,7 +9,10 @@ Tokens per second of one prompt through the token-major path (CUDA events on the
 with ``--by-step``, a second pass in which the native runtime brackets every step of a chunk with events and adds the
 device time up per category (mixer glue / mixer GEMMs / projections / GDN / QSA / out projection (+ reduce-scatter) /
 routing / expert GEMMs / shared down + combine / PLE / MTP pass / guard waits).  On several ranks a step's time
-includes what it waits for inside the kernel, which is the point.
+includes what it waits for inside the kernel, which is the point.  ``--tokens-file`` takes the prompt (context first, then
+the measured part) from a file of token ids instead of random ids: real text routes to fewer distinct experts per chunk
+and re-selects attention groups, so its numbers differ from the random-token floor.  ``--energy`` integrates this rank's
+GPU power (NVML) over the best timed repetition and reports joules per prompt token.
 
 (The reference's tool: bench/prefill_bench with --ctx / --tokens-file.)"""
 import argparse
@@ -21,6 +25,16 @@ import torch
 
 from ..engine.engine import Engine, EngineOptions
 from ..models.config import ModelConfig
+
+def read_token_file(path: str, vocab: int):
+    """Token ids separated by white space and / or commas; ids outside the vocabulary are refused."""
+    with open(path) as f:
+        ids = [int(x) for x in f.read().replace(",", " ").split()]
+    bad = [t for t in ids if not 0 <= t < vocab]
+    if bad:
+        raise ValueError(f"{path}: {len(bad)} ids outside the vocabulary (first: {bad[0]})")
+    return ids
+
 
 CATS = ["mixer pre-norm (+ pending block output)", "mixer GEMMs", "projection GEMM", "GDN conv + scan", "QSA prep / scores / select / attend", "out projection",
         "router GEMM + routing + sort", "expert GEMMs + swiglu", "shared down + combine", "PLE", "other", "MTP pass", "guard waits", "mixer norm (after the sums of squares)", "mixer mid (after the down projection)",
@@ -36,6 +50,8 @@ def main():
     ap.add_argument("--lanes", type=int, default=0, help="micro-batches per chunk (0: the default of the rank count)")
     ap.add_argument("--by-step", action="store_true", help="a second pass with the runtime's per-category step timing")
     ap.add_argument("--repeat", type=int, default=2, help="timed repetitions (the best is reported)")
+    ap.add_argument("--tokens-file", default=None, help="token ids of the prompt (context + measured part) instead of random ids")
+    ap.add_argument("--energy", action="store_true", help="integrate this rank's GPU power over each timed repetition")
     a = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -59,6 +75,11 @@ def main():
         eng = Engine.synthetic(cfg, opts, device=dev, ple_rows=1 << 20)
     g = torch.Generator().manual_seed(3)
     toks = torch.randint(0, cfg.vocab, (a.ctx + a.tokens,), generator=g).tolist()
+    if a.tokens_file:
+        toks = read_token_file(a.tokens_file, cfg.vocab)
+        if len(toks) < a.ctx + a.tokens:
+            raise SystemExit(f"--tokens-file holds {len(toks)} ids, --ctx + --tokens asks for {a.ctx + a.tokens}")
+        toks = toks[:a.ctx + a.tokens]
 
     def sync():
         if dist is not None:
@@ -72,22 +93,33 @@ def main():
         sync()
 
     eng.prefill(0, toks[:min(512, a.tokens)], want_logits=False)          # warm-up
-    best = None
+    best, energy = None, None
     for _ in range(max(1, a.repeat)):
         fresh()
+        meter = None
+        if a.energy:
+            from ..utils.power import PowerMeter
+            meter = PowerMeter(indices=[local]).start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         eng.prefill(0, toks[a.ctx:], want_logits=True)
         e1.record()
         sync()
+        used = meter.stop() if meter is not None else None
         eng.dm.check_error()
         t = torch.tensor([e0.elapsed_time(e1)], device=dev)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        best = float(t) if best is None else min(best, float(t))
+        if best is None or float(t) < best:
+            best, energy = float(t), used
     pf = eng.prefiller
     out = {"tokens": a.tokens, "ctx": a.ctx, "ranks": world, "lanes": pf.lanes, "chunk": pf.T, "ms": round(best, 2),
            "tok_s": round(a.tokens / best * 1e3), "launches_per_chunk": int(eng.dm.lib.qwrt_prefill_last_launches())}
+    if energy is not None and energy.get("ok"):
+        out["energy"] = {"gpu": local, "avg_w": energy["avg_w"], "joules": round(energy["kilojoules"] * 1e3, 1),
+                         "joules_per_token": round(energy["kilojoules"] * 1e3 / a.tokens, 4)}
+    if a.tokens_file:
+        out["tokens_file"] = os.path.basename(a.tokens_file)
     if a.by_step:
         lib = eng.dm.lib
         lib.qwrt_prefill_profile.argtypes = [C.c_int]
