@@ -155,13 +155,21 @@ class Session:
         c = self._common(slot, tokens)
         return c if c == len(self.e.slot[slot].tokens) and c < len(tokens) else 0
 
+    def kept_if_chosen(self, slot: int, tokens: Sequence[int]) -> int:
+        """Tokens of the prompt that need no prefill if the request goes to this slot: what the slot would continue from in
+        place, or the deepest device snapshot of the slot inside what it shares with the prompt (an edited or regenerated
+        last message goes back to the boundary before it).  What the block store holds is the same for every slot and
+        does not enter the choice."""
+        snap = self._best_vram_snapshot(slot, tokens)
+        return max(self.reusable(slot, tokens), snap.n if snap is not None else 0)
+
     def acquire(self, tokens: Sequence[int], max_new: int) -> int:
         need = len(tokens) + max(1, max_new)
         best, best_r = -1, -1
         for i, si in enumerate(self.slots):
             if si.busy or self.slot_capacity(i) < need:
                 continue
-            r = self.reusable(i, tokens)
+            r = self.kept_if_chosen(i, tokens)
             if best < 0 or r > best_r or (r == best_r and si.used < self.slots[best].used):
                 best, best_r = i, r
         if best >= 0:
