@@ -495,3 +495,40 @@ def test_token_arrays_are_marshalled_once():
     t.append(7)                                         # a changed list is marshalled again
     b = t.array()
     assert b is not a and len(b) == 50001 and b[50000] == 7
+
+
+def test_cancelled_requests_leave_at_every_stage():
+    """A request cancelled while it waits, while its prompt goes in (even when shorter prompts are ahead of it) or while it
+    generates ends with "abort" and gives its slot back; the others are not disturbed."""
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    srv, sched, eng, pr = make_server("ok", slots=(8192, 8192), piece=256, start=False)
+    eng.reply = lambda prompt: [66] * 50
+    ends = {}
+
+    def req(name, n, max_new=8):
+        r = Request(tokens=Tokens([65] * n), max_new=max_new, sampling=Sampling(), stop_ids=[eng.eos], rid=name)
+        r.on_done = lambda reason, name=name: ends.setdefault(name, reason)
+        return r
+    long_r, short_r, waiting_r = req("long", 4000), req("short", 600), req("waiting", 100)
+    for r in (long_r, short_r, waiting_r):
+        sched.submit(r)
+    sched._drain_inbox()
+    sched._admit()                                            # two slots: long and short are admitted, the third waits
+    assert [r.rid for r in sched.prefilling] == ["long", "short"] and [r.rid for r in sched.waiting] == ["waiting"]
+    sched._prefill()                                          # the shorter prompt goes first
+    assert eng.prefill_order == [short_r.slot]
+    sched.cancel(long_r)                                      # cancelled while a shorter prompt is still ahead of it
+    sched.cancel(waiting_r)
+    sched._prefill()
+    assert ends["long"] == "abort" and not eng.busy[long_r.slot] and [r.rid for r in sched.prefilling] == ["short"]
+    sched._admit()
+    assert ends["waiting"] == "abort" and not sched.waiting
+    while sched.prefilling:
+        sched._prefill()
+    assert [r.rid for r in sched.running] == ["short"]
+    sched._step()
+    sched.cancel(short_r)
+    sched._step()
+    assert ends["short"] == "abort" and not sched.running and eng.busy == [False, False]
+    assert sched.stats["failed"] == 0

@@ -316,13 +316,15 @@ class Scheduler:
     def _prefill(self) -> bool:
         if not self.prefilling:
             return False
+        gone = [q for q in self.prefilling if q.cancelled]                 # wherever they stand in the order: their slots are needed
+        for q in gone:
+            self.prefilling.remove(q)
+            q.finish = "abort"
+            self._finish(q)
+        if gone:
+            return True
         self.prefilling.sort(key=lambda r: len(r.tokens) - r.reused)       # short prompts first
         r = self.prefilling[0]
-        if r.cancelled:
-            self.prefilling.pop(0)
-            r.finish = "abort"
-            self._finish(r)
-            return True
         # several prompts whose uncached part fits one piece go in with one engine call (on several GPUs one round trip to
         # the worker ranks instead of one per prompt); reference: _batch, server/qwserve/scheduler.py:315-398
         short = [q for q in self.prefilling if not q.cancelled and len(q.tokens) - q.reused <= self.piece][:self.max_batch_prefill]
