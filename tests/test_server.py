@@ -532,3 +532,29 @@ def test_cancelled_requests_leave_at_every_stage():
     sched._step()
     assert ends["short"] == "abort" and not sched.running and eng.busy == [False, False]
     assert sched.stats["failed"] == 0
+
+
+def test_a_client_that_goes_away_frees_its_slot():
+    """A streaming client closes the connection mid-answer: the request is cancelled, its slot comes back, and the next
+    request is served."""
+    srv, sched, eng, pr = make_server("</think>" + "word " * 400, slots=(8192,), step_seconds=0.01)
+
+    async def fn(c):
+        r = await c.post("/v1/chat/completions", json={"messages": MSG, "stream": True, "max_tokens": 4000})
+        got = 0
+        async for line in r.content:
+            if line.startswith(b"data: "):
+                got += 1
+            if got >= 5:
+                break
+        r.close()                                           # the client goes away in the middle of the answer
+        t0 = time.time()
+        while eng.busy[0] and time.time() - t0 < 5:
+            await asyncio.sleep(0.05)
+        freed = not eng.busy[0]
+        nxt = await (await c.post("/v1/chat/completions", json={"messages": MSG, "max_tokens": 6})).json()
+        return freed, nxt
+    freed, nxt = with_client(srv, fn)
+    assert freed and nxt["choices"][0]["finish_reason"] == "length" and nxt["usage"]["completion_tokens"] == 6
+    assert sched.counts()["failed"] == 0
+    sched.shutdown()
