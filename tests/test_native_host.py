@@ -267,3 +267,30 @@ def test_thread_pool_visits_every_index_once():
         for n, grain, rounds in ((1, 1, 50), (7, 1, 2000), (1000, 1, 500), (1001, 64, 500), (100, 1000, 50), (100003, 17, 20), (0, 1, 3)):
             assert L.qwh_pool_check(pool, n, grain, rounds) == 0, (threads, n, grain)
         L.qwh_pool_free(pool)
+
+
+def test_sampler_partial_ordering_equals_the_full_sort():
+    """The host sampler orders only as many candidates as a truncation looks at; token and log-probability must equal
+    the straightforward form that sorts them all - flat, typical and peaked distributions, ties, every truncation mix."""
+    L = H.lib()
+    V = 60000
+    rng = np.random.default_rng(3)
+    cases = [dict(temperature=1.0), dict(temperature=1.0, top_k=20, top_p=0.95), dict(temperature=1.0, top_k=200, top_p=0.9, min_p=0.001),
+             dict(temperature=1.0, top_p=0.95), dict(temperature=1.0, top_p=0.9999), dict(temperature=1.3, min_p=0.05),
+             dict(temperature=1.0, min_p=1e-9), dict(temperature=0.7, top_p=0.9, min_p=0.01), dict(temperature=1.0, top_k=100000, top_p=0.9),
+             dict(temperature=1.0, top_k=20, top_p=0.95, presence_penalty=1.5, repetition_penalty=1.1)]
+    try:
+        for sigma in (0.3, 3.0, 9.0):
+            for trial in range(4):
+                logits = (rng.standard_normal(V) * sigma).astype(np.float32)
+                if trial == 3:
+                    logits[:3000] = logits[0]                     # a plateau of equal logits: ties go to the lower index
+                hist = [int(x) for x in rng.integers(0, V, 300)]
+                for kw in cases:
+                    got = []
+                    for full in (1, 0):
+                        L.qwh_sampler_full_sort(full)
+                        got.append(H.HostSampler(seed=1).sample(logits, H.Sampling.make(seed=50 + trial, **kw), hist=hist, prompt_end=100))
+                    assert got[0] == got[1], (sigma, trial, kw, got)
+    finally:
+        L.qwh_sampler_full_sort(0)

@@ -33,7 +33,7 @@ def lib() -> C.CDLL:
             "qwh_last_error": (C.c_char_p, []),
             "qwh_ngram_new": (P, [I, I, I, I, LL, ULL, I, I]), "qwh_ngram_free": (None, [P]), "qwh_ngram_total_rows": (LL, [P]),
             "qwh_ngram_sizes": (I, [P, P, P, P]), "qwh_ngram_ids": (I, [P, P, I, P, I, P]),
-            "qwh_pool_new": (P, [I]), "qwh_pool_free": (None, [P]), "qwh_pool_size": (I, [P]), "qwh_pool_check": (LL, [P, LL, LL, I]),
+            "qwh_sampler_full_sort": (None, [I]), "qwh_pool_new": (P, [I]), "qwh_pool_free": (None, [P]), "qwh_pool_size": (I, [P]), "qwh_pool_check": (LL, [P, LL, LL, I]),
             "qwh_ple_open": (P, [C.c_char_p, I]), "qwh_ple_free": (None, [P]), "qwh_ple_rows": (LL, [P]), "qwh_ple_layout": (I, [P]),
             "qwh_ple_gather": (I, [P, P, I, I, P, P]), "qwh_ple_pin": (I, [P, I, I]),
             "qwh_st_open": (P, [C.c_char_p]), "qwh_st_add": (I, [P, C.c_char_p]), "qwh_st_free": (None, [P]), "qwh_st_count": (I, [P]),

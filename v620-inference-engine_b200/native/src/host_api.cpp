@@ -154,6 +154,7 @@ API int qwh_sample(const float *logits, int V, const qwh_sampling *p, const int3
           sp.repetition_penalty = p->repetition_penalty; sp.seed = p->seed;
           return sample_token(logits, V, sp, hist, size_t(n_hist), size_t(prompt_end), *static_cast<std::mt19937_64 *>(rng), logprob);, -1)
 }
+API void qwh_sampler_full_sort(int on) { sampler_full_sort_flag() = on; }
 API int qwh_top_logprobs(const float *logits, int V, int k, int32_t *ids, float *lps) { return top_logprobs(logits, V, k, ids, lps); }
 API float qwh_lse(const float *logits, int V) { return log_sum_exp(logits, V); }
 

@@ -22,6 +22,10 @@ struct SamplingParams {
     uint64_t seed = 0;
 };
 
+// test switch: 1 = every truncation sorts all candidates (the straightforward form the shortcuts are checked against)
+inline int &sampler_full_sort_flag() { static int f = 0; return f; }
+inline bool sampler_full_sort() { return sampler_full_sort_flag() != 0; }
+
 inline float log_sum_exp(const float *l, int V) {
     const float mx = *std::max_element(l, l + V);
     double z = 0;
@@ -71,21 +75,52 @@ inline int32_t sample_token(const float *raw, int V, const SamplingParams &p, co
     std::vector<size_t> order(idx.size());
     std::iota(order.begin(), order.end(), size_t(0));
     auto by_logit = [&](size_t a, size_t b) { return L[idx[a]] > L[idx[b]] || (L[idx[a]] == L[idx[b]] && idx[a] < idx[b]); };
-    size_t K = order.size();
+    const size_t n = order.size();
+    size_t K = n;
     if (p.top_k > 0 && size_t(p.top_k) < K) K = size_t(p.top_k);
-    if (p.top_p < 1.f || p.top_k > 0 || p.min_p > 0.f) {
-        if (K < order.size()) std::partial_sort(order.begin(), order.begin() + ptrdiff_t(K), order.end(), by_logit);
-        else std::sort(order.begin(), order.end(), by_logit);
+    // Only as much of the order as the truncation looks at is ever sorted (by_logit is a strict total order, so the first m
+    // entries of a partial sort are the first m of the full sort): a vocabulary of 250k candidates costs a few
+    // milliseconds instead of fifty.  sampler_full_sort() switches the shortcut off (the tests compare the two).
+    auto sort_first = [&](size_t m) {
+        if (m >= n / 2 || sampler_full_sort()) {
+            std::sort(order.begin(), order.end(), by_logit);
+        } else if (m <= 64) {
+            std::partial_sort(order.begin(), order.begin() + ptrdiff_t(m), order.end(), by_logit);
+        } else {                                              // select the m first (linear), then order them
+            std::nth_element(order.begin(), order.begin() + ptrdiff_t(m), order.end(), by_logit);
+            std::sort(order.begin(), order.begin() + ptrdiff_t(m), by_logit);
+        }
+    };
+    const bool truncating = p.top_p < 1.f || p.top_k > 0 || p.min_p > 0.f;
+    size_t keep = K;
+    const bool k_sorted = truncating && (K < n || p.top_k > 0);          // top-k: its K entries are sorted up front
+    if (k_sorted) {
+        sort_first(K);
+    } else if (truncating && p.top_p >= 1.f) {
+        // min-p alone: the kept tokens are exactly those that weigh at least min_p times the heaviest (weight 1)
+        size_t heavy = 0;
+        for (size_t i = 0; i < n; ++i) heavy += w[i] >= double(p.min_p) ? 1 : 0;
+        sort_first(std::max<size_t>(heavy, 1));
     }
     double z = 0;
-    for (size_t i = 0; i < K; ++i) z += w[order[i]];
+    if (p.top_k > 0) for (size_t i = 0; i < K; ++i) z += w[order[i]];
     const double norm = p.top_k > 0 ? z : z_all;
-    size_t keep = K;
     if (p.top_p < 1.f) {
-        double acc = 0;
-        for (size_t i = 0; i < K; ++i) {
-            acc += w[order[i]] / norm;
-            if (acc >= p.top_p) { keep = i + 1; break; }
+        // top-p: the shortest prefix whose mass reaches p; without top-k the sorted part is widened until it holds that prefix
+        size_t sorted = k_sorted ? K : 0;
+        for (;;) {
+            if (sorted < K) {
+                sorted = std::min(K, std::max<size_t>(1024, sorted * 8));
+                sort_first(sorted);
+                if (sampler_full_sort()) sorted = K;
+            }
+            double acc = 0;
+            bool found = false;
+            for (size_t i = 0; i < sorted; ++i) {
+                acc += w[order[i]] / norm;
+                if (acc >= p.top_p) { keep = i + 1; found = true; break; }
+            }
+            if (found || sorted >= K) break;
         }
     }
     if (p.min_p > 0.f) {
