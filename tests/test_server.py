@@ -407,25 +407,29 @@ def test_watchdog_exits_only_after_the_grace_and_forgets_a_recovery(monkeypatch)
     from server_fixtures import FakeEngine
     logs, exits = [], []
     eng = FakeEngine(lambda p: [66])
-    sched = Scheduler(eng, exit_grace=1.5, log=logs.append)
+    sched = Scheduler(eng, exit_grace=3.0, log=logs.append)
 
     def fake_exit(code):
         exits.append(code)
         sched.stop_flag.set()
     monkeypatch.setattr(os, "_exit", fake_exit)
+
+    def wait_for(cond, limit):
+        t0 = time.time()
+        while not cond() and time.time() - t0 < limit:
+            time.sleep(0.05)
+        return cond()
     sched.start(watchdog=True)
     eng.failed_with = "rank 2 is gone"
-    time.sleep(1.3)                        # first unhealthy check has run, the grace has not passed
-    assert not exits and any("unhealthy: engine failure: rank 2 is gone" in ln for ln in logs)
+    assert wait_for(lambda: any("unhealthy: engine failure: rank 2 is gone" in ln for ln in logs), 2.5)
+    assert not exits                                        # seen, but the grace has not passed
     eng.failed_with = ""
-    time.sleep(1.2)                        # healthy again: the spell is forgotten
-    assert not exits and sched.unhealthy_since == 0.0
+    assert wait_for(lambda: sched.unhealthy_since == 0.0, 2.5) and not exits      # healthy again: the spell is forgotten
     eng.failed_with = "rank 2 is gone"
     t0 = time.time()
-    while not exits and time.time() - t0 < 8:
-        time.sleep(0.1)
+    assert wait_for(lambda: bool(exits), 12)
     assert exits == [3] and any(ln.startswith("exiting after") for ln in logs)
-    assert time.time() - t0 >= 1.5
+    assert time.time() - t0 >= 3.0                          # a full grace counted from the new spell, not from the first one
     sched.shutdown()
 
 

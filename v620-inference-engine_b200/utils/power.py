@@ -32,13 +32,15 @@ class PowerMeter:
         self.t0 = self.t1 = 0.0
 
     def _run(self):
-        last_t, last_w = time.perf_counter(), self.read()
+        # the integral covers exactly [t0, t1]: the first reading stands for the moment of start() (the thread may come up a
+        # little later), the last one for the moment of stop()
+        last_t, last_w = self.t0, self.read()
         while not self._stop.wait(self.period):
             t, w = time.perf_counter(), self.read()
             self.joules += 0.5 * (w + last_w) * (t - last_t)          # trapezoid between two samples
             last_t, last_w = t, w
-        t, w = time.perf_counter(), self.read()
-        self.joules += 0.5 * (w + last_w) * (t - last_t)
+        w = self.read()
+        self.joules += 0.5 * (w + last_w) * max(0.0, self.t1 - last_t)
 
     def start(self) -> "PowerMeter":
         self.joules = 0.0
