@@ -294,3 +294,52 @@ def test_sampler_partial_ordering_equals_the_full_sort():
                     assert got[0] == got[1], (sigma, trial, kw, got)
     finally:
         L.qwh_sampler_full_sort(0)
+
+
+def test_spec_planner_decisions():
+    """Native planner of the speculative step: the expected-rate rule, stretches without drafts, limits, acceptance."""
+    base, beta = 1.25, 0.25
+    pl = H.SpecPlanner(3, base, beta, 0.3, 32, 48, 176)
+    for a in (0.0, 0.2, 0.5, 0.8, 0.99):
+        for k_max in (1, 2, 5, 12):
+            best, bk, expect, p = 0.0, 1, 1.0, 1.0
+            for K in range(1, k_max + 1):
+                p *= a
+                expect += p
+                r = expect / (base + beta * (K - 1))
+                if r > best:
+                    best, bk = r, K
+            rate, k = pl.best_rate(a, k_max)
+            assert abs(rate - best) < 1e-12 and k == bk
+    assert [s.accept for s in pl.slots] == [0.5] * 3 and pl.slots[0].plain_stretch == 32
+    # acceptance 0.5 pays with one draft (1.5 / 1.25); 0.1 does not: a stretch starts and the next one will be longer
+    assert pl.plan([0], [64], [1000], [True], 4, 12, 0, 32, False) == [1]
+    pl.slots[1].accept = 0.1
+    assert pl.plan([1], [64], [1000], [True], 4, 12, 0, 32, False) == [0]
+    assert (pl.slots[1].plain_left, pl.slots[1].plain_stretch) == (32, 80)
+    assert pl.plan([1], [64], [1000], [True], 4, 12, 0, 32, False) == [0] and pl.slots[1].plain_left == 32       # inside the stretch: untouched
+    for left in range(31, -1, -1):
+        assert pl.note_plain_step(1) == left
+    assert abs(pl.slots[1].accept - 0.3) < 1e-12                                      # the stretch is over: the next step probes
+    assert pl.plan([1], [64], [1000], [True], 4, 12, 0, 32, False) == [1]
+    # forced runs ignore the rule; budget, room, the run limit and the row limit all bind
+    assert pl.plan([1, 2], [64, 3], [1000, 1000], [True, True], 5, 12, 0, 32, True) == [5, 2]
+    assert pl.plan([1, 2], [64, 64], [2, 1000], [True, False], 5, 12, 4, 32, True) == [2, 0]
+    assert pl.plan([0, 1, 2], [64] * 3, [1000] * 3, [True] * 3, 12, 12, 0, 20, True) == [5, 6, 6]      # the first of the longest runs is trimmed first
+    import pytest
+    with pytest.raises(ValueError, match="budget"):
+        pl.plan([0], [0], [10], [True], 4, 12, 0, 32, False)
+    with pytest.raises(ValueError, match="slot 2 is full"):
+        pl.plan([0, 2], [8, 8], [10, -1], [True, True], 4, 12, 0, 32, False)
+    with pytest.raises(ValueError, match="more requests"):
+        pl.plan([0, 1, 2], [8] * 3, [10] * 3, [False] * 3, 4, 12, 0, 2, False)
+    # acceptance: drafts equal to what was drawn behind them are kept, a stop token ends the run, the average moves by a tenth
+    pl.slots[0].accept = 0.5
+    assert pl.accept(0, [7, 8, 9, 1], [7, 8, 5], [], None) == 3                        # two drafts kept, the third differs
+    assert abs(pl.slots[0].accept - (0.45 + 0.1 * 2 / 3)) < 1e-12
+    assert pl.accept(0, [7, 8, 9, 1], [7, 8, 9], [8], None) == 2                        # 8 is a stop token: nothing behind it
+    assert pl.accept(0, [7], [], [], None) == 1 and pl.accept(0, [1, 2, 3], [9, 9], [], 5) == 3      # forced: all drafts, at most
+    pl.slots[0].plain_stretch = 128
+    pl.slots[0].accept = 0.6
+    pl.accept(0, [1, 2], [1], [], None)
+    assert pl.slots[0].plain_stretch == 32                                            # a good spell resets the stretch length

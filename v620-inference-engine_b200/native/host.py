@@ -33,6 +33,10 @@ def lib() -> C.CDLL:
             "qwh_last_error": (C.c_char_p, []),
             "qwh_ngram_new": (P, [I, I, I, I, LL, ULL, I, I]), "qwh_ngram_free": (None, [P]), "qwh_ngram_total_rows": (LL, [P]),
             "qwh_ngram_sizes": (I, [P, P, P, P]), "qwh_ngram_ids": (I, [P, P, I, P, I, P]),
+            "qwh_spec_new": (P, [I, C.c_double, C.c_double, C.c_double, I, I, I]), "qwh_spec_free": (None, [P]), "qwh_spec_slots": (P, [P]),
+            "qwh_spec_draft_count": (I, [P, I, I]), "qwh_spec_best_rate": (C.c_double, [P, C.c_double, I, P]),
+            "qwh_spec_plan": (I, [P, I, P, P, P, P, I, I, I, I, I, P, P]), "qwh_spec_note_plain_step": (I, [P, I]),
+            "qwh_spec_accept": (I, [P, I, P, P, I, P, I, I]),
             "qwh_sampler_full_sort": (None, [I]), "qwh_pool_new": (P, [I]), "qwh_pool_free": (None, [P]), "qwh_pool_size": (I, [P]), "qwh_pool_check": (LL, [P, LL, LL, I]),
             "qwh_ple_open": (P, [C.c_char_p, I]), "qwh_ple_free": (None, [P]), "qwh_ple_rows": (LL, [P]), "qwh_ple_layout": (I, [P]),
             "qwh_ple_gather": (I, [P, P, I, I, P, P]), "qwh_ple_pin": (I, [P, I, I]),
@@ -223,6 +227,56 @@ class BlockStore:
         lib().qwh_store_stats(self.s, out)
         names = ["hits", "tokens_restored", "snapshots_saved", "ram_bytes", "disk_bytes", "blocks", "snapshots"]
         return dict(zip(names, [int(x) for x in out]))
+
+
+class SpecSlot(C.Structure):
+    """One slot's speculative-decoding state as the native planner keeps it (src/spec_planner.hpp); the session reads
+    and writes these fields in place."""
+    _fields_ = [("accept", C.c_double), ("plain_left", C.c_int32), ("plain_stretch", C.c_int32)]
+
+
+class SpecPlanner:
+    """How many drafts each request of a step gets, the stretches without drafts, and what is kept of a verified run:
+    src/spec_planner.hpp."""
+    ERRORS = {-1: "a request needs a budget of at least one token", -2: "slot {slot} is full", -3: "more requests than rows in a step"}
+
+    def __init__(self, slots: int, base: float, beta: float, probe_accept: float, plain_first: int, plain_grow: int, plain_max: int):
+        self.h = lib().qwh_spec_new(slots, base, beta, probe_accept, plain_first, plain_grow, plain_max)
+        self.n = slots
+        self.slots = (SpecSlot * slots).from_address(lib().qwh_spec_slots(self.h))       # the planner's own memory
+
+    def best_rate(self, a: float, k_max: int) -> Tuple[float, int]:
+        k = C.c_int(0)
+        r = lib().qwh_spec_best_rate(self.h, a, k_max, C.byref(k))
+        return float(r), k.value
+
+    def draft_count(self, slot: int, k_max: int) -> int:
+        return int(lib().qwh_spec_draft_count(self.h, slot, k_max))
+
+    def plan(self, slots: Sequence[int], budgets: Sequence[int], room: Sequence[int], can_draft: Sequence[bool], k: int, max_drafts: int,
+             max_run: int, max_rows: int, forced: bool) -> List[int]:
+        n = len(slots)
+        sl, bu, ro = _i32(slots), np.asarray(budgets, dtype=np.int64), np.asarray(room, dtype=np.int64)
+        cd = np.asarray(can_draft, dtype=np.uint8)
+        want, bad = np.zeros(max(n, 1), dtype=np.int32), C.c_int(-1)
+        rc = lib().qwh_spec_plan(self.h, n, sl.ctypes.data, bu.ctypes.data, ro.ctypes.data, cd.ctypes.data, int(k), int(max_drafts), int(max_run),
+                                 int(max_rows), int(bool(forced)), want.ctypes.data, C.byref(bad))
+        if rc != 0:
+            raise ValueError(self.ERRORS[rc].format(slot=slots[bad.value] if 0 <= bad.value < n else "?"))
+        return [int(x) for x in want[:n]]
+
+    def note_plain_step(self, slot: int) -> int:
+        return int(lib().qwh_spec_note_plain_step(self.h, slot))
+
+    def accept(self, slot: int, sampled: Sequence[int], drafts: Sequence[int], stop: Sequence[int], forced: Optional[int]) -> int:
+        s, d, st = _i32(sampled), _i32(drafts), _i32(stop)
+        return int(lib().qwh_spec_accept(self.h, slot, s.ctypes.data, d.ctypes.data, len(d), st.ctypes.data, len(st), -1 if forced is None else int(forced)))
+
+    def __del__(self):
+        if getattr(self, "h", None) and lib is not None:
+            self.slots = None
+            lib().qwh_spec_free(self.h)
+            self.h = None
 
 
 class HostSampler:

@@ -9,6 +9,7 @@
 #include "chunker.hpp"
 #include "ngram_ple.hpp"
 #include "sampler.hpp"
+#include "spec_planner.hpp"
 
 using namespace qwh;
 
@@ -157,6 +158,28 @@ API int qwh_sample(const float *logits, int V, const qwh_sampling *p, const int3
 API void qwh_sampler_full_sort(int on) { sampler_full_sort_flag() = on; }
 API int qwh_top_logprobs(const float *logits, int V, int k, int32_t *ids, float *lps) { return top_logprobs(logits, V, k, ids, lps); }
 API float qwh_lse(const float *logits, int V) { return log_sum_exp(logits, V); }
+
+// ---- speculative-step planner
+API void *qwh_spec_new(int slots, double base, double beta, double probe_accept, int plain_first, int plain_grow, int plain_max) {
+    return new SpecPlanner(slots, SpecTuning{base, beta, probe_accept, plain_first, plain_grow, plain_max});
+}
+API void qwh_spec_free(void *h) { delete static_cast<SpecPlanner *>(h); }
+API void *qwh_spec_slots(void *h) { return static_cast<SpecPlanner *>(h)->slots(); }
+API int qwh_spec_draft_count(void *h, int slot, int k_max) { return static_cast<SpecPlanner *>(h)->draft_count(slot, k_max); }
+API double qwh_spec_best_rate(void *h, double a, int k_max, int *k) {
+    double r;
+    static_cast<SpecPlanner *>(h)->best_rate(a, k_max, &r, k);
+    return r;
+}
+API int qwh_spec_plan(void *h, int n, const int32_t *slot, const long long *budget, const long long *room, const unsigned char *can_draft, int k,
+                      int max_drafts, int max_run, int max_rows, int forced, int32_t *want, int *bad) {
+    return static_cast<SpecPlanner *>(h)->plan(n, slot, reinterpret_cast<const int64_t *>(budget), reinterpret_cast<const int64_t *>(room), can_draft, k,
+                                              max_drafts, max_run, max_rows, forced, want, bad);
+}
+API int qwh_spec_note_plain_step(void *h, int slot) { return static_cast<SpecPlanner *>(h)->note_plain_step(slot); }
+API int qwh_spec_accept(void *h, int slot, const int32_t *sampled, const int32_t *drafts, int n_drafts, const int32_t *stop, int n_stop, int forced) {
+    return static_cast<SpecPlanner *>(h)->accept(slot, sampled, drafts, n_drafts, stop, n_stop, forced);
+}
 
 // ---- chunker
 API int qwh_chunk(const int32_t *tok, long long n, int boundary, long long *starts, long long *lens, unsigned long long *hashes, int cap) {

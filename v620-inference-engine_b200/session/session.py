@@ -57,15 +57,24 @@ class SlotInfo:
     prompt_end: int = 0
     stop: List[int] = field(default_factory=list)
     logits: Optional[torch.Tensor] = None                 # logits after the prompt (device)
-    accept: float = 0.5                                    # running draft acceptance
     drafts: List[int] = field(default_factory=list)
     drafts_for: int = -1
     block_keys: List[int] = field(default_factory=list)   # store keys of the slot's full blocks, in order
     last_capture: int = 0                                 # position of the newest device snapshot taken during this prompt
-    plain_left: int = 0                                   # steps left of a stretch without drafts
-    plain_stretch: int = 32                               # length of the next such stretch (32 -> 80 -> 128 -> 176)
+    # running draft acceptance, steps left of a stretch without drafts, length of the next stretch (32 -> 80 -> 128 -> 176):
+    # kept by the native planner; ``accept`` / ``plain_left`` / ``plain_stretch`` below read and write its memory
+    spec: H.SpecSlot = field(default_factory=lambda: H.SpecSlot(0.5, 0, PLAIN_FIRST), repr=False)
     missed: list = field(default_factory=list)            # MTP rows skipped during the stretch: (hidden, next token, position)
     timing: Dict[str, float] = field(default_factory=lambda: {"restore_s": 0.0, "prefill_s": 0.0, "save_s": 0.0, "pin_wait_s": 0.0})
+
+
+def _spec_field(name):
+    return property(lambda self: getattr(self.spec, name), lambda self, v: setattr(self.spec, name, v))
+
+
+SlotInfo.accept = _spec_field("accept")
+SlotInfo.plain_left = _spec_field("plain_left")
+SlotInfo.plain_stretch = _spec_field("plain_stretch")
 
 
 @dataclass
@@ -104,17 +113,6 @@ def common_prefix(a: Sequence[int], b: Sequence[int], block: int = 4096) -> int:
     return n
 
 
-def best_rate(a: float, k_max: int) -> Tuple[float, int]:
-    best, expect, p, bk = 0.0, 1.0, 1.0, 1
-    for K in range(1, k_max + 1):
-        p *= a
-        expect += p
-        rate = expect / (SPEC_BASE + SPEC_BETA * (K - 1))
-        if rate > best:
-            best, bk = rate, K
-    return best, bk
-
-
 class Session:
     def __init__(self, engine: Engine, host_cache_bytes: int = 8 << 30, disk_cache_dir: Optional[str] = None,
                  disk_cache_bytes: int = 0, prefill_piece: int = 2048, seed: int = 0):
@@ -128,6 +126,10 @@ class Session:
         self.io = StateIO(engine.dm)
         n = engine.opts.slots
         self.slots = [SlotInfo() for _ in range(n)]
+        # how many drafts, stretches without drafts, what is kept of a verified run: decided natively (native/src/spec_planner.hpp)
+        self.planner = H.SpecPlanner(n, SPEC_BASE, SPEC_BETA, PROBE_ACCEPT, PLAIN_FIRST, PLAIN_GROW, PLAIN_MAX)
+        for i, si in enumerate(self.slots):
+            si.spec = self.planner.slots[i]
         self.clock = 0
         self.boundary = -1
         self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
@@ -470,10 +472,7 @@ class Session:
 
     # ---- generation with speculative decoding
     def draft_count(self, slot: int, k_max: int) -> int:
-        if k_max <= 1:
-            return k_max
-        rate, k = best_rate(self.slots[slot].accept, k_max)
-        return k if rate >= 1.0 else 0
+        return self.planner.draft_count(slot, k_max)
 
     def generate(self, reqs: Sequence[StepReq], k: int, force_accept: Optional[int] = None) -> List[StepOut]:
         """One step for every request: its pending token plus up to k drafts are decoded, 1..k+1 tokens are emitted.
@@ -488,32 +487,10 @@ class Session:
         e = self.e
         # ---- plan (no state is touched here)
         max_rows = min(e.dm.max_rows, 32)
-        want = []
-        for r in reqs:
-            sl = e.slot[r.slot]
-            if r.budget < 1:
-                raise ValueError("a request needs a budget of at least one token")
-            kk = min(k, r.budget - 1, e.MAX_DRAFTS) if (e.mtp and sl.mtp_hidden is not None) else 0
-            if self.spec_max_rows > 0:
-                kk = min(kk, self.spec_max_rows - 1)
-            if kk > 0 and force_accept is None:
-                si = self.slots[r.slot]
-                if si.plain_left > 0:
-                    kk = 0                                # inside a stretch without drafts
-                else:
-                    kk = self.draft_count(r.slot, kk)
-                    if kk == 0 and k > 1:                 # drafting stopped paying: a stretch of plain steps starts
-                        si.plain_left = si.plain_stretch
-                        si.plain_stretch = min(PLAIN_MAX, si.plain_stretch + PLAIN_GROW)
-            if sl.n + kk + 1 > e.dm.slot_tokens:
-                kk = e.dm.slot_tokens - sl.n - 1
-                if kk < 0:
-                    raise ValueError(f"slot {r.slot} is full")
-            want.append(kk)
-        if len(reqs) > max_rows:
-            raise ValueError("more requests than rows in a step")
-        while sum(want) + len(reqs) > max_rows:          # trim the longest draft runs first
-            want[want.index(max(want))] -= 1
+        can_draft = [bool(e.mtp and e.slot[r.slot].mtp_hidden is not None) for r in reqs]
+        room = [e.dm.slot_tokens - e.slot[r.slot].n - 1 for r in reqs]
+        want = self.planner.plan([r.slot for r in reqs], [r.budget for r in reqs], room, can_draft, k, e.MAX_DRAFTS, self.spec_max_rows, max_rows,
+                                 forced=force_accept is not None)
         spec = e.mtp and "gdn_save" in e.dm.buf
         try:
             return self._generate_planned(reqs, want, spec, force_accept)
@@ -533,9 +510,7 @@ class Session:
                 if want[i] == 0 and si.plain_left > 0 and sl.mtp_hidden is not None:
                     si.missed.append((sl.mtp_hidden, int(r.pending), sl.n - 1))
                     del si.missed[:-MISSED_MAX]
-                    si.plain_left -= 1
-                    if si.plain_left == 0:
-                        si.accept = max(si.accept, PROBE_ACCEPT)          # the next step probes with a short draft run
+                    self.planner.note_plain_step(r.slot)                  # at the stretch's end the next step probes with a short draft run
                 elif want[i] > 0 and si.missed:
                     self.catch_up_rows += len(si.missed)
                     e.mtp_catch_up(r.slot, si.missed)
@@ -582,19 +557,13 @@ class Session:
             si = self.slots[r.slot]
             d = drafts[i]
             t = toks[row0:row0 + len(runs[i])]
+            # drafts that equal the tokens sampled behind them, up to a stop token; the slot's acceptance average moves
+            n_acc = self.planner.accept(r.slot, t, d, si.stop, force_accept)
             if force_accept is not None:
-                n_acc = min(force_accept, len(d)) + 1
                 emitted = (d[:n_acc - 1] + [t[n_acc - 1]])[:r.budget]
             else:
-                n_acc = 1
-                while n_acc <= len(d) and t[n_acc - 1] == d[n_acc - 1] and t[n_acc - 1] not in si.stop:
-                    n_acc += 1
                 emitted = t[:n_acc][:r.budget]
             n_acc_all.append(n_acc)
-            if d:
-                si.accept = 0.9 * si.accept + 0.1 * ((n_acc - 1) / len(d))
-                if si.accept >= 0.5:
-                    si.plain_stretch = PLAIN_FIRST                        # a good spell: the next stretch starts short again
             tr.count("drafts", len(d))
             tr.count("accepted", n_acc - 1)
             if self.spec_log and d:
