@@ -343,3 +343,36 @@ def test_spec_planner_decisions():
     pl.slots[0].accept = 0.6
     pl.accept(0, [1, 2], [1], [], None)
     assert pl.slots[0].plain_stretch == 32                                            # a good spell resets the stretch length
+
+
+def test_slot_and_prompt_decisions():
+    """Native slot logic: slot choice, the four ways to start a prompt, snapshot choice, capture planning."""
+    # most kept, then least recently used; busy and too small slots never
+    assert H.choose_slot([False, False, False], [100, 100, 100], [0, 50, 50], [3, 9, 4], 60) == 2
+    assert H.choose_slot([False, True, False], [100, 100, 40], [10, 90, 99], [1, 2, 3], 60) == 0
+    assert H.choose_slot([True, True], [100, 100], [0, 0], [1, 2], 10) == -1
+    # a device snapshot must beat both others; in place wins a tie with the store; nothing to reuse: reset
+    assert H.start_way(100, 300, 256) == H.START_DEVICE_SNAPSHOT and H.start_way(300, 300, 256) == H.START_IN_PLACE
+    assert H.start_way(256, 0, 256) == H.START_IN_PLACE and H.start_way(100, 200, 512) == H.START_STORE
+    assert H.start_way(0, 0, 0) == H.START_RESET and H.start_way(0, 5, 0) == H.START_DEVICE_SNAPSHOT
+    # the deepest snapshot inside the common part; one as deep as the prompt only with its logits
+    assert H.best_snapshot([100, 300, 500], [False, False, False], 400, 1000) == 1
+    assert H.best_snapshot([100, 300], [False, True], 300, 300) == 1 and H.best_snapshot([100, 300], [False, False], 300, 300) == 0
+    assert H.best_snapshot([500], [True], 400, 1000) == -1 and H.best_snapshot([0], [True], 10, 20) == -1
+    # capture planning against the plain loop
+    rng = np.random.default_rng(8)
+    for _ in range(300):
+        n = int(rng.integers(2, 400))
+        prompt = [int(x) for x in rng.integers(0, 6, n)]
+        done = int(rng.integers(0, n))
+        end = int(rng.integers(done + 1, n + 1))
+        last, gap, boundary = int(rng.integers(0, done + 1)), int(rng.integers(1, 60)), 3
+        lo, want = max(done + 1, last + gap), end
+        for p in range(min(end, n - 1), lo - 1, -1):
+            if prompt[p] == boundary:
+                want = p
+                break
+        top = min(end, n - 1)
+        assert H.capture_point(prompt[done:top + 1], done, n, done, end, last, boundary, gap) == want
+        assert H.capture_point(prompt, 0, n, done, end, last, boundary, gap) == want
+        assert H.capture_point(prompt[done:top + 1], done, n, done, end, last, -1, gap) == end

@@ -37,6 +37,8 @@ def lib() -> C.CDLL:
             "qwh_spec_draft_count": (I, [P, I, I]), "qwh_spec_best_rate": (C.c_double, [P, C.c_double, I, P]),
             "qwh_spec_plan": (I, [P, I, P, P, P, P, I, I, I, I, I, P, P]), "qwh_spec_note_plain_step": (I, [P, I]),
             "qwh_spec_accept": (I, [P, I, P, P, I, P, I, I]),
+            "qwh_choose_slot": (I, [I, P, P, P, P, LL]), "qwh_start_way": (I, [LL, LL, LL]),
+            "qwh_capture_point": (LL, [P, LL, LL, LL, LL, I, LL]), "qwh_best_snapshot": (I, [I, P, P, LL, LL]),
             "qwh_sampler_full_sort": (None, [I]), "qwh_pool_new": (P, [I]), "qwh_pool_free": (None, [P]), "qwh_pool_size": (I, [P]), "qwh_pool_check": (LL, [P, LL, LL, I]),
             "qwh_ple_open": (P, [C.c_char_p, I]), "qwh_ple_free": (None, [P]), "qwh_ple_rows": (LL, [P]), "qwh_ple_layout": (I, [P]),
             "qwh_ple_gather": (I, [P, P, I, I, P, P]), "qwh_ple_pin": (I, [P, I, I]),
@@ -227,6 +229,35 @@ class BlockStore:
         lib().qwh_store_stats(self.s, out)
         names = ["hits", "tokens_restored", "snapshots_saved", "ram_bytes", "disk_bytes", "blocks", "snapshots"]
         return dict(zip(names, [int(x) for x in out]))
+
+
+START_RESET, START_IN_PLACE, START_DEVICE_SNAPSHOT, START_STORE = 0, 1, 2, 3
+
+
+def choose_slot(busy: Sequence[bool], capacity: Sequence[int], kept: Sequence[int], used: Sequence[int], need: int) -> int:
+    """The free slot that holds ``need`` tokens and keeps the most of the prompt, then the least recently used (-1: none)."""
+    b = np.asarray(busy, dtype=np.uint8)
+    c, k, u = (np.asarray(x, dtype=np.int64) for x in (capacity, kept, used))
+    return int(lib().qwh_choose_slot(len(b), b.ctypes.data, c.ctypes.data, k.ctypes.data, u.ctypes.data, int(need)))
+
+
+def start_way(keep: int, snapshot: int, stored: int) -> int:
+    """How a prompt starts: one of START_RESET / START_IN_PLACE / START_DEVICE_SNAPSHOT / START_STORE (src/slot_logic.hpp)."""
+    return int(lib().qwh_start_way(int(keep), int(snapshot), int(stored)))
+
+
+def capture_point(piece: Sequence[int], first: int, prompt_len: int, done: int, end: int, last_capture: int, boundary: int, min_gap: int) -> int:
+    """Where the prefill piece [done, end) should end for a device snapshot at a message boundary.  ``piece`` holds the
+    prompt's tokens from position ``first`` on (only the part the search can look at needs to be passed)."""
+    t = _i32(piece)
+    r = lib().qwh_capture_point(t.ctypes.data, min(int(prompt_len), int(first) + len(t)) - int(first), int(done) - int(first), int(end) - int(first),
+                                int(last_capture) - int(first), int(boundary), int(min_gap))
+    return int(r) + int(first)
+
+
+def best_snapshot(depths: Sequence[int], has_logits: Sequence[bool], common: int, prompt_len: int) -> int:
+    d, h = np.asarray(depths, dtype=np.int64), np.asarray(has_logits, dtype=np.uint8)
+    return int(lib().qwh_best_snapshot(len(d), d.ctypes.data, h.ctypes.data, int(common), int(prompt_len)))
 
 
 class SpecSlot(C.Structure):

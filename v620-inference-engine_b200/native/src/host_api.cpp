@@ -9,6 +9,7 @@
 #include "chunker.hpp"
 #include "ngram_ple.hpp"
 #include "sampler.hpp"
+#include "slot_logic.hpp"
 #include "spec_planner.hpp"
 
 using namespace qwh;
@@ -158,6 +159,19 @@ API int qwh_sample(const float *logits, int V, const qwh_sampling *p, const int3
 API void qwh_sampler_full_sort(int on) { sampler_full_sort_flag() = on; }
 API int qwh_top_logprobs(const float *logits, int V, int k, int32_t *ids, float *lps) { return top_logprobs(logits, V, k, ids, lps); }
 API float qwh_lse(const float *logits, int V) { return log_sum_exp(logits, V); }
+
+// ---- slot and prompt decisions
+API int qwh_choose_slot(int n, const unsigned char *busy, const long long *capacity, const long long *kept, const long long *used, long long need) {
+    return choose_slot(n, busy, reinterpret_cast<const int64_t *>(capacity), reinterpret_cast<const int64_t *>(kept),
+                       reinterpret_cast<const int64_t *>(used), need);
+}
+API int qwh_start_way(long long keep, long long snapshot, long long stored) { return start_way(keep, snapshot, stored); }
+API long long qwh_capture_point(const int32_t *prompt, long long n, long long done, long long end, long long last_capture, int boundary, long long min_gap) {
+    return capture_point(prompt, n, done, end, last_capture, boundary, min_gap);
+}
+API int qwh_best_snapshot(int m, const long long *snap_n, const unsigned char *has_logits, long long common, long long prompt_len) {
+    return best_snapshot(m, reinterpret_cast<const int64_t *>(snap_n), has_logits, common, prompt_len);
+}
 
 // ---- speculative-step planner
 API void *qwh_spec_new(int slots, double base, double beta, double probe_accept, int plain_first, int plain_grow, int plain_max) {

@@ -181,13 +181,10 @@ class Session:
 
     def acquire(self, tokens: Sequence[int], max_new: int) -> int:
         need = len(tokens) + max(1, max_new)
-        best, best_r = -1, -1
-        for i, si in enumerate(self.slots):
-            if si.busy or self.slot_capacity(i) < need:
-                continue
-            r = self.kept_if_chosen(i, tokens)
-            if best < 0 or r > best_r or (r == best_r and si.used < self.slots[best].used):
-                best, best_r = i, r
+        n = len(self.slots)
+        free = [not si.busy and self.slot_capacity(i) >= need for i, si in enumerate(self.slots)]
+        kept = [self.kept_if_chosen(i, tokens) if free[i] else 0 for i in range(n)]
+        best = H.choose_slot([si.busy for si in self.slots], [self.slot_capacity(i) for i in range(n)], kept, [si.used for si in self.slots], need)
         if best >= 0:
             self.clock += 1
             self.slots[best].busy = True
@@ -227,12 +224,13 @@ class Session:
         stored = depth * BLOCK
         snap = self._best_vram_snapshot(slot, toks)
         si.last_capture = 0
-        if snap is not None and snap.n > max(keep, stored):
+        way = H.start_way(keep, snap.n if snap is not None else 0, stored)
+        if way == H.START_DEVICE_SNAPSHOT:
             self._restore_vram_snapshot(slot, snap, toks)
             self.reused_tokens += snap.n
             si.last_capture = snap.n
             return snap.n
-        if keep >= stored and keep > 0:
+        if way == H.START_IN_PLACE:
             self.reused_tokens += keep
             self.sampler_sync(slot, toks[:keep], keep)
             si.last_capture = keep
@@ -305,16 +303,11 @@ class Session:
     def _best_vram_snapshot(self, slot: int, toks: Sequence[int]) -> Optional[VramSnap]:
         """The deepest snapshot of this slot that lies inside what the slot and the prompt have in common (at least one
         prompt token must remain to be prefilled unless the snapshot carries the logits of its position)."""
-        common = self._common(slot, toks)
-        best = None
-        for v in self.vram_snaps:
-            if v.slot != slot or v.n > common or v.n < 1:
-                continue
-            if v.n >= len(toks) and not (v.n == len(toks) and v.logits is not None):
-                continue
-            if best is None or v.n > best.n:
-                best = v
-        return best
+        mine = [v for v in self.vram_snaps if v.slot == slot]
+        if not mine:
+            return None
+        i = H.best_snapshot([v.n for v in mine], [v.logits is not None for v in mine], self._common(slot, toks), len(toks))
+        return mine[i] if i >= 0 else None
 
     def _restore_vram_snapshot(self, slot: int, snap: VramSnap, toks: Sequence[int]) -> None:
         si, sl = self.slots[slot], self.e.slot[slot]
@@ -336,11 +329,8 @@ class Session:
         plan_captures, src/session/prefix_cache.cpp:41-78).  ``end`` when there is none."""
         if self.boundary < 0:
             return end
-        lo = max(done + 1, last_capture + self.snap_min_gap)
-        for p in range(min(end, len(prompt) - 1), lo - 1, -1):
-            if prompt[p] == self.boundary:
-                return p
-        return end
+        top = min(end, len(prompt) - 1)
+        return H.capture_point(prompt[done:top + 1], done, len(prompt), done, end, last_capture, self.boundary, self.snap_min_gap)
 
     def prefetch(self, tokens: Sequence[int]) -> int:
         """Start reading, in the background, the stored blocks on the prompt's path that are only on disk, so that
