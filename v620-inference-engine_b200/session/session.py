@@ -64,6 +64,7 @@ class SlotInfo:
     # running draft acceptance, steps left of a stretch without drafts, length of the next stretch (32 -> 80 -> 128 -> 176):
     # kept by the native planner; ``accept`` / ``plain_left`` / ``plain_stretch`` below read and write its memory
     spec: H.SpecSlot = field(default_factory=lambda: H.SpecSlot(0.5, 0, PLAIN_FIRST), repr=False)
+    spec_owner: object = field(default=None, repr=False)
     missed: list = field(default_factory=list)            # MTP rows skipped during the stretch: (hidden, next token, position)
     timing: Dict[str, float] = field(default_factory=lambda: {"restore_s": 0.0, "prefill_s": 0.0, "save_s": 0.0, "pin_wait_s": 0.0})
 
@@ -130,6 +131,7 @@ class Session:
         self.planner = H.SpecPlanner(n, SPEC_BASE, SPEC_BETA, PROBE_ACCEPT, PLAIN_FIRST, PLAIN_GROW, PLAIN_MAX)
         for i, si in enumerate(self.slots):
             si.spec = self.planner.slots[i]
+            si.spec_owner = self.planner          # the struct lives in the planner's memory: keep it alive as long as the slot record
         self.clock = 0
         self.boundary = -1
         self.piece = max(BLOCK, prefill_piece // BLOCK * BLOCK)
