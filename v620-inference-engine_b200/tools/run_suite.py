@@ -5,7 +5,7 @@ JSON line collected into one report.
 
 Stages: ``kernels`` (gemm_bench, gemv_bench, launch_bench), ``decode`` (bench.py: decode, prefill, long prefill, the
 speculative sweep; rows_bench), ``prefill`` (prefill_bench with the split by step), ``serving`` (long_context_bench,
-cold_prefill_bench, pin_bench), ``comm`` (comm_bench, p2p_bench; only with --gpus > 1).  A stage that fails is recorded
+cold_prefill_bench, pin_bench, spill_locality), ``comm`` (comm_bench, p2p_bench; only with --gpus > 1).  A stage that fails is recorded
 with its exit code and the end of its output; the suite goes on.  For an A/B comparison run the suite in two
 checkouts and compare the reports.  (The reference's bench/run_suite.sh is the same harness as a shell script.)"""
 import argparse
@@ -30,7 +30,8 @@ def stages(gpus: int, quick: bool):
         "prefill": [("prefill_bench", mod("prefill_bench", "--by-step", dist=multi, port=29542))],
         "serving": [("long_context_bench", mod("long_context_bench", *(["--tokens", "32768", "--resident", "8192", "--slots", "4"] if quick else []))),
                     ("cold_prefill_bench", mod("cold_prefill_bench", *(["--tokens", "16384", "--reps", "1"] if quick else []))),
-                    ("pin_bench", mod("pin_bench", "--decode-steps", "200"))],
+                    ("pin_bench", mod("pin_bench", "--decode-steps", "200")),
+                    ("spill_locality", mod("spill_locality", *(["--tokens", "16384", "--resident", "4096", "--steps", "64"] if quick else [])))],
         "comm": [("comm_bench", mod("comm_bench", "--prefill-rows", "4096", dist=True, port=29543)), ("p2p_bench", mod("p2p_bench", dist=True, port=29544))] if multi else [],
     }
     return s
