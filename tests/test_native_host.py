@@ -376,3 +376,21 @@ def test_slot_and_prompt_decisions():
         assert H.capture_point(prompt[done:top + 1], done, n, done, end, last, boundary, gap) == want
         assert H.capture_point(prompt, 0, n, done, end, last, boundary, gap) == want
         assert H.capture_point(prompt[done:top + 1], done, n, done, end, last, -1, gap) == end
+
+
+def test_block_store_reads_files_with_the_older_block_magic(tmp_path):
+    """A cache directory written with the first block format (magic QWBLOCK1) is indexed and served like the current one."""
+    st = H.BlockStore(5, 1, 1 << 20, str(tmp_path), 1 << 22)
+    toks = list(range(300, 556))
+    k = st.save_block(st.root, 0, toks, b"v" * 777)
+    st.flush()
+    st.close()
+    f = os.path.join(str(tmp_path), f"{k:016x}.qwb")
+    raw = bytearray(open(f, "rb").read())
+    assert raw[:8] == b"QWBLOCK2"
+    raw[:8] = b"QWBLOCK1"
+    open(f, "wb").write(bytes(raw))
+    st2 = H.BlockStore(5, 1, 1 << 20, str(tmp_path), 1 << 22)
+    path, _ = st2.lookup(toks + [1])
+    assert path == [k] and st2.get(k) == b"v" * 777
+    st2.close()
