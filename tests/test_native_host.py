@@ -1,6 +1,7 @@
 """Native host runtime (C++): hasher, PLE table, block store + disk tier, sampler, chunker."""
 import os
 import struct
+import time
 
 import numpy as np
 import pytest
@@ -394,3 +395,41 @@ def test_block_store_reads_files_with_the_older_block_magic(tmp_path):
     path, _ = st2.lookup(toks + [1])
     assert path == [k] and st2.get(k) == b"v" * 777
     st2.close()
+
+
+def test_block_store_concurrent_reads_from_disk(tmp_path):
+    """Blocks that live only on disk are read by several threads at once, with background prefetches running: every
+    reader gets its block's bytes, nothing deadlocks."""
+    import threading
+    st = H.BlockStore(6, 1, ram_budget=8 << 10, disk_dir=str(tmp_path), disk_budget=1 << 24)       # RAM holds almost nothing
+    parent, keys = st.root, []
+    for i in range(24):
+        k = st.save_block(parent, i * 256, [1000 * i + j for j in range(256)], bytes([i]) * 4096)
+        keys.append(k)
+        parent = k
+    st.flush()
+    st.close()
+    st = H.BlockStore(6, 1, ram_budget=8 << 10, disk_dir=str(tmp_path), disk_budget=1 << 24)
+    errors = []
+
+    def reader(offset):
+        try:
+            for rep in range(20):
+                i = (offset * 5 + rep * 7) % len(keys)
+                got = st.get(keys[i])
+                if got != bytes([i]) * 4096:
+                    errors.append((offset, i, None if got is None else len(got)))
+        except Exception as ex:          # noqa: BLE001
+            errors.append((offset, repr(ex)))
+    ts = [threading.Thread(target=reader, args=(o,)) for o in range(8)]
+    for t in ts:
+        t.start()
+    st.prefetch(keys[:12], last_snapshot=False)
+    for t in ts:
+        t.join(timeout=30)
+        assert not t.is_alive()
+    t0 = time.time()
+    while st.loads_pending() and time.time() - t0 < 10:
+        time.sleep(0.01)
+    assert not errors and st.loads_pending() == 0
+    st.close()
