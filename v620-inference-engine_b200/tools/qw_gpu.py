@@ -3,6 +3,8 @@ the format of the CPU reference (`native/qw_ref --logprobs`), so the two can be 
 (reference: tools/qw_gpu.hip with --logprobs / --prefill-n / --token-by-token).
 
     python -m qwb200.tools.qw_gpu --model DIR [--ple DIR] --prompt 1,2,3 [--new 16] [--logprobs FILE] [--token-by-token]
+                                  [--prefill-n N]      # the first N prompt tokens through the prefill path, the rest through decode steps:
+                                                       # log-probabilities from position N - 1 on then test decoding on top of prefilled state
     python -m qwb200.tools.qw_gpu --synthetic tiny --prompt 5,6,7 --new 8"""
 import argparse
 
@@ -22,6 +24,7 @@ def main():
     ap.add_argument("--logprobs")
     ap.add_argument("--token-by-token", action="store_true", help="feed the prompt through decode steps instead of prefill")
     ap.add_argument("--weight-cache-dir")
+    ap.add_argument("--prefill-n", type=int, default=0, help="prefill this many prompt tokens, feed the rest through decode steps")
     a = ap.parse_args()
     prompt = [int(t) for t in a.prompt.split(",")]
     opts = EngineOptions(slots=1, slot_tokens=max(1024, len(prompt) + a.new + 256), use_graphs=not a.token_by_token)
@@ -44,7 +47,14 @@ def main():
         top = int(ls.argmax())
         nxt = toks[pos + 1] if pos + 1 < len(toks) else top
         lp.write(f"{pos} {nxt} {float(ls[nxt]):.6f} {top} {float(ls[top]):.6f}\n")
-    if a.token_by_token or lp is not None:
+    if 0 < a.prefill_n <= len(prompt) and not a.token_by_token:
+        logits = eng.prefill(0, prompt[:a.prefill_n]).clone()
+        record(a.prefill_n - 1, logits)
+        for pos in range(a.prefill_n, len(prompt)):
+            eng.decode([0], [prompt[pos]])
+            logits = eng.dm.buf["logits"][0].clone()
+            record(pos, logits)
+    elif a.token_by_token or lp is not None:
         for pos, t in enumerate(prompt):              # every position's logits are wanted: one step per token
             eng.decode([0], [t])
             logits = eng.dm.buf["logits"][0].clone()
