@@ -3,7 +3,6 @@ a scripted session.  Every one of the 29 functions is called through C; the scri
 returns known values, so argument order, pointer marshalling, struct layouts, return conventions (>= 0 ok, -1 + qw_error)
 and the error path are checked where they are implemented - in the shim and the two Python sides of it."""
 import ctypes as C
-import json
 import os
 import sys
 import types
@@ -175,3 +174,46 @@ def test_open_failure_reports_the_reason(monkeypatch):
         E.Engine({"synthetic": "full"}, nbuild.ENGINE_LIB)
     with pytest.raises(E.EngineError, match="devices must list"):
         E.Engine({"devices": [0, 1, 2]}, nbuild.ENGINE_LIB)
+
+
+def test_media_prompts_through_the_c_abi(monkeypatch):
+    """qw_acquire_media / qw_begin_prompt with media descriptors: the structs are read through the shim, the pad tokens of
+    the prompt reach the session as vision token ids, the same ids in every call of the request."""
+    import numpy as np
+    from qwb200 import capi_impl
+    from qwb200.models.config import ModelConfig
+    from qwb200.native import build as nbuild
+    from qwb200.vision import VisionConfig
+    from qwb200.vision.frontend import VisionFrontend
+    from qwserve import engine as E
+
+    class Enc:
+        cfg = VisionConfig(depth=1, out_dim=ModelConfig.tiny().hidden)
+
+        def encode(self, *a):
+            raise AssertionError("the tower runs only when a slice is looked up")
+    cfg, vc = ModelConfig.tiny(), Enc.cfg
+    ses = ScriptedSession()
+    monkeypatch.setattr(capi_impl, "build_ops", lambda o, r, w, p: capi_impl.SessionOps(ses, VisionFrontend(Enc(), 1 << 20)))
+    eng = E.Engine({"synthetic": "tiny"}, nbuild.ENGINE_LIB)
+    try:
+        assert eng.has_vision is True
+        h, w = 4, 6
+        n_img = h * w // (vc.merge * vc.merge)
+        patches = np.random.default_rng(2).standard_normal((2 * h * w, vc.patch_in)).astype(np.float32)
+        starts = np.asarray([3], dtype=np.int64)
+        toks = E.Tokens([5, 6, 7] + [cfg.image_pad] * n_img + [8, 9])
+        m = E.Media(hash=99, video=0, t=1, h=h, w=w, patches=patches.ctypes.data, starts=starts.ctypes.data)
+        assert eng.acquire(toks, 10, media=[m]) == 1
+        got = ses.calls[-1][1]
+        assert got[:3] == [5, 6, 7] and got[-2:] == [8, 9] and all(t < 0 for t in got[3:3 + n_img]) and len(set(got[3:3 + n_img])) == n_img
+        assert eng.begin_prompt(1, toks, media=[m]) == 256 and ses.calls[-1][2] == got
+        eng.prefetch(1, toks, media=[m])
+        assert ses.calls[-1] == ("prefetch", got)
+        # a media slice that lies outside the prompt is refused with a message, not a crash
+        bad = np.asarray([len(toks)], dtype=np.int64)
+        m2 = E.Media(hash=100, video=0, t=1, h=h, w=w, patches=patches.ctypes.data, starts=bad.ctypes.data)
+        with pytest.raises(E.EngineError):
+            eng.acquire(toks, 10, media=[m2])
+    finally:
+        eng.close()
