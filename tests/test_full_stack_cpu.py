@@ -1,0 +1,129 @@
+"""The whole host stack on CPU: HTTP -> scheduler -> the server's ctypes binding -> libqw_engine.so -> CApi -> the real
+Session (native planner, block store, chunker) -> a rule-based engine.  Speculative serving returns the text of plain
+serving, a repeated prompt is served from the slot's snapshot, concurrent requests do not disturb one another."""
+import asyncio
+
+import pytest
+
+from rule_engine import RuleEngine, make_session
+from server_fixtures import make_prompter
+
+aiohttp = pytest.importorskip("aiohttp")
+from aiohttp.test_utils import TestClient, TestServer  # noqa: E402
+
+MSG = [{"role": "user", "content": "tell me something"}]
+
+
+def serve(monkeypatch, drafts, wrong=lambda pos: False, slots=3):
+    from qwb200 import capi_impl
+    from qwb200.native import build as nbuild
+    from qwserve import engine as E
+    from qwserve.api import Server
+    from qwserve.scheduler import Scheduler
+    nbuild.build()
+    rule = RuleEngine(vocab=512, modulus=256, slots=slots, wrong=wrong)
+    holder = {}
+
+    def build_ops(o, rank, world, port):
+        holder["ses"] = make_session(monkeypatch, rule, host_cache_bytes=8 << 20)
+        return capi_impl.SessionOps(holder["ses"], None)
+    monkeypatch.setattr(capi_impl, "build_ops", build_ops)
+    eng = E.Engine({"synthetic": "tiny"}, nbuild.ENGINE_LIB)
+    pr = make_prompter()
+    sched = Scheduler(eng, drafts=drafts, prefill_piece=512, log=lambda *_: None)
+    srv = Server(eng, pr, sched, "qw-rule")
+    sched.start(watchdog=False)
+    return srv, sched, eng, rule, holder
+
+
+def with_client(srv, fn):
+    from qwserve.api import make_app
+
+    async def go():
+        async with TestClient(TestServer(make_app(srv, dashboard=False))) as c:
+            return await fn(c)
+    return asyncio.run(go())
+
+
+def chat(c, **kw):
+    body = {"messages": MSG, "max_tokens": 40, "temperature": 0, "chat_template_kwargs": {"enable_thinking": False}}
+    body.update(kw)
+    return c.post("/v1/chat/completions", json=body)
+
+
+def test_speculative_serving_equals_plain_serving(monkeypatch):
+    texts = {}
+    for drafts, wrong in ((0, lambda p: False), (3, lambda p: False), (3, lambda p: p % 4 == 0)):
+        srv, sched, eng, rule, holder = serve(monkeypatch, drafts, wrong)
+
+        async def fn(c):
+            r = await chat(c)
+            assert r.status == 200
+            return await r.json()
+        out = with_client(srv, fn)
+        sched.shutdown()
+        eng.close()
+        ch = out["choices"][0]
+        assert ch["finish_reason"] == "length" and out["usage"]["completion_tokens"] == 40
+        texts[(drafts, wrong(4))] = ch["message"]["content"]
+        if drafts:
+            assert rule.draft_calls > 0 and max(max(r) for r in rule.verify_rows) > 1          # drafts really ran through the C ABI
+    assert len(set(texts.values())) == 1 and len(next(iter(texts.values()))) > 0
+
+
+def test_repeated_prompt_and_concurrent_requests(monkeypatch):
+    srv, sched, eng, rule, holder = serve(monkeypatch, drafts=2)
+
+    async def fn(c):
+        a = await (await chat(c)).json()
+        fed = rule.fed
+        b = await (await chat(c)).json()                       # the same prompt again: nothing of it is fed a second time
+        refed = rule.fed - fed - b["usage"]["completion_tokens"]
+        rs = await asyncio.gather(*[chat(c, messages=[{"role": "user", "content": f"question number {i}"}], max_tokens=16 + i) for i in range(3)])
+        many = [await r.json() for r in rs]
+        solo = []
+        for i in range(3):
+            solo.append(await (await chat(c, messages=[{"role": "user", "content": f"question number {i}"}], max_tokens=16 + i)).json())
+        await asyncio.sleep(1.3)                               # the scheduler refreshes the cache counters once a second
+        health = await (await c.get("/health")).json()
+        return a, b, refed, many, solo, health
+    a, b, refed, many, solo, health = with_client(srv, fn)
+    sched.shutdown()
+    eng.close()
+    assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    assert b["usage"]["prompt_tokens_details"]["cached_tokens"] == b["usage"]["prompt_tokens"] and refed <= 0
+    for m, s_, i in zip(many, solo, range(3)):
+        assert m["choices"][0]["message"]["content"] == s_["choices"][0]["message"]["content"]      # batched with others == alone
+        assert m["usage"]["completion_tokens"] == 16 + i
+    assert health["status"] == "ok" and health["prefix_cache"]["prompt_tokens"] > 0 and health["prefix_cache"]["reused_tokens"] > 0
+    assert health["decode"]["completed"] == 8 and health["decode"]["failed"] == 0
+
+
+def test_stop_token_and_streaming_through_the_stack(monkeypatch):
+    """The rule predicts the end-of-message token from the row of position 70 on: the answer stops there (drafts past it are dropped),
+    and the streamed frames add up to the non-streamed answer."""
+    import json
+    srv, sched, eng, rule, holder = serve(monkeypatch, drafts=3)
+    rule.stop_after, rule.stop_token = 70, make_prompter().token_id("<|im_end|>")
+
+    async def fn(c):
+        plain = await (await chat(c, max_tokens=200)).json()
+        r = await chat(c, max_tokens=200, stream=True, messages=[{"role": "user", "content": "tell me something else"}])
+        text, finish = "", None
+        async for line in r.content:
+            line = line.decode().strip()
+            if line.startswith("data: ") and line != "data: [DONE]":
+                f = json.loads(line[6:])
+                if f.get("choices"):
+                    text += f["choices"][0]["delta"].get("content") or ""
+                    finish = f["choices"][0].get("finish_reason") or finish
+        again = await (await chat(c, max_tokens=200, messages=[{"role": "user", "content": "tell me something else"}])).json()
+        return plain, text, finish, again
+    plain, text, finish, again = with_client(srv, fn)
+    sched.shutdown()
+    eng.close()
+    ch = plain["choices"][0]
+    assert ch["finish_reason"] == "stop" and 0 < plain["usage"]["completion_tokens"] < 60
+    # the row of position 70 is the first that predicts the stop token, which then sits at position 71 and ends the answer
+    assert plain["usage"]["prompt_tokens"] + plain["usage"]["completion_tokens"] == 72
+    assert finish == "stop" and text == again["choices"][0]["message"]["content"]
