@@ -127,3 +127,55 @@ def test_stop_token_and_streaming_through_the_stack(monkeypatch):
     # the row of position 70 is the first that predicts the stop token, which then sits at position 71 and ends the answer
     assert plain["usage"]["prompt_tokens"] + plain["usage"]["completion_tokens"] == 72
     assert finish == "stop" and text == again["choices"][0]["message"]["content"]
+
+
+def test_soak_many_requests_shared_prefixes_unreliable_drafts(monkeypatch):
+    """Thirty requests at once on three slots: a long shared system prompt (restored from the block store into whichever
+    slot comes free), prompts of several lengths, drafts that are wrong at pseudo-random positions, a few clients that
+    go away.  Every answer equals the answer of the same request served alone without drafts, and every slot's state
+    stays the state of the tokens it holds."""
+    import random
+    rnd = random.Random(11)
+    system = "You are a careful assistant. " * 40                     # ~1,200 byte tokens: four full blocks and a bit
+    reqs = []
+    for i in range(30):
+        msgs = ([{"role": "system", "content": system}] if i % 3 else []) + [{"role": "user", "content": f"request {i}: " + "x" * rnd.randrange(0, 300)}]
+        reqs.append(dict(messages=msgs, max_tokens=rnd.randrange(4, 50)))
+
+    def run(drafts, wrong, concurrent, drop=()):
+        srv, sched, eng, rule, holder = serve(monkeypatch, drafts, wrong)
+
+        async def one(c, i, r):
+            if i in drop:                                          # a client that leaves after the first frames
+                resp = await chat(c, stream=True, **r)
+                n = 0
+                async for line in resp.content:
+                    n += line.startswith(b"data: ")
+                    if n >= 2:
+                        break
+                resp.close()
+                return None
+            return (await (await chat(c, **r)).json())["choices"][0]["message"]["content"]
+
+        async def fn(c):
+            if concurrent:
+                return await asyncio.gather(*[one(c, i, r) for i, r in enumerate(reqs)])
+            return [await one(c, i, r) for i, r in enumerate(reqs)]
+        out = with_client(srv, fn)
+        import time
+        t0 = time.time()
+        while any(s_.busy for s_ in holder["ses"].slots) and time.time() - t0 < 5:
+            time.sleep(0.05)
+        stats = holder["ses"].cache_stats()
+        ok = all(rule.consistent(s, rule.slot[s].tokens) for s in range(3))
+        busy = [s_.busy for s_ in holder["ses"].slots]
+        sched.shutdown()
+        eng.close()
+        return out, stats, ok, busy, rule
+    want, _, ok0, _, _ = run(0, lambda p: False, concurrent=False)
+    got, stats, ok1, busy, rule = run(4, lambda p: (p * 2654435761) % 7 < 2, concurrent=True, drop={5, 17})
+    assert ok0 and ok1 and busy == [False, False, False]
+    for i, (g, w) in enumerate(zip(got, want)):
+        if i not in (5, 17):
+            assert g == w, i
+    assert stats["reused_tokens"] >= 1024 and stats["hits"] >= 1 and rule.draft_calls > 0
