@@ -16,13 +16,15 @@ def message(rnd, n):
 
 
 @pytest.mark.parametrize("seed", range(12))
-def test_random_conversations_keep_every_invariant(monkeypatch, seed):
+def test_random_conversations_keep_every_invariant(monkeypatch, tmp_path, seed):
     from qwb200.engine.sampling import SamplingParams
     from qwb200.session.session import StepReq
     rnd = random.Random(seed)
     pattern = rnd.randrange(2, 9)
     eng = RuleEngine(vocab=1000, slots=3, cap=6144, wrong=lambda p: (p * 2654435761 >> 3) % pattern == 0)
-    ses = make_session(monkeypatch, eng, host_cache_bytes=(64 << 20) if seed % 4 else (96 << 10), prefill_piece=rnd.choice([256, 512, 1024]))
+    disk = dict(disk_cache_dir=str(tmp_path), disk_cache_bytes=64 << 20) if seed % 3 == 2 else {}      # some runs with a disk tier under a tiny RAM tier
+    ram = (96 << 10) if (seed % 4 == 0 or disk) else (64 << 20)
+    ses = make_session(monkeypatch, eng, host_cache_bytes=ram, prefill_piece=rnd.choice([256, 512, 1024]), **disk)
     ses.set_boundary_token(BOUNDARY)
     ses.snap_min_gap = rnd.choice([256, 512, 1024])
     ses.snap_keep_gap = rnd.choice([0, 0, 600])
@@ -52,6 +54,12 @@ def test_random_conversations_keep_every_invariant(monkeypatch, seed):
             assert held, "no slot although none is held"
             ses.release(held.pop(rnd.randrange(len(held))))
             slot = ses.acquire(prompt, n_new)
+        if disk and rnd.random() < 0.5:                              # read-ahead of stored blocks that are only on disk
+            ses.prefetch(prompt)
+            import time
+            t0 = time.time()
+            while ses.loads_pending() and time.time() - t0 < 5:
+                time.sleep(0.002)
         reused = ses.begin_prompt(slot, prompt)
         shared = max([0] + [next((i for i, (a, b) in enumerate(zip(prompt, p + g)) if a != b), min(len(prompt), len(p + g))) for p, g in seen])
         assert 0 <= reused <= min(shared, len(prompt)) and (reused < len(prompt) or prompt in [p for p, _ in seen])
@@ -79,5 +87,8 @@ def test_random_conversations_keep_every_invariant(monkeypatch, seed):
             held.append(slot)
         else:
             ses.release(slot)
+    ses.persist()
     st = ses.cache_stats()
+    if disk:
+        assert st["disk_bytes"] > 0
     assert st["prompt_tokens"] == sum(len(p) for p, _ in seen) and st["reused_tokens"] <= st["prompt_tokens"]
