@@ -562,3 +562,70 @@ def test_a_client_that_goes_away_frees_its_slot():
     assert freed and nxt["choices"][0]["finish_reason"] == "length" and nxt["usage"]["completion_tokens"] == 6
     assert sched.counts()["failed"] == 0
     sched.shutdown()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_scheduler_soak_with_injected_failures(seed):
+    """Sixty requests of mixed sizes on three slots with failures injected at random: prompts the engine refuses, steps
+    that raise for one slot, clients that cancel.  Every request ends exactly once, every slot comes back, the scheduler
+    thread survives, and the requests nothing was done to end normally."""
+    import random
+    from qwserve.engine import Sampling, Tokens
+    from qwserve.scheduler import Request
+    rnd = random.Random(seed)
+    srv, sched, eng, pr = make_server("ok", slots=(4096, 2048, 2048), piece=256, drafts=rnd.choice([0, 2]))
+    eng.reply = lambda prompt: [66 + len(prompt) % 7] * 30
+    eng.poison = 13
+    ends, lock = {}, threading.Lock()
+    reqs = []
+    for i in range(60):
+        n = rnd.choice([10, 100, 300, 900, 1800])
+        toks = [65] * n
+        fate = rnd.choices(["ok", "poison", "cancel", "step_error"], weights=[6, 1, 2, 1])[0]
+        if fate == "poison":
+            toks[rnd.randrange(n)] = 13
+        r = Request(tokens=Tokens(toks), max_new=rnd.randrange(1, 25), sampling=Sampling(), stop_ids=[eng.eos], rid=f"r{i}")
+
+        def done(reason, i=i):
+            with lock:
+                ends.setdefault(i, []).append(reason)
+        r.on_done = done
+        reqs.append((r, fate))
+    for r, fate in reqs:
+        sched.submit(r)
+        if rnd.random() < 0.3:
+            time.sleep(0.002)
+    t0 = time.time()
+    while len(ends) < len(reqs) and time.time() - t0 < 30:
+        for r, fate in reqs:
+            if fate == "cancel" and not r.cancelled and rnd.random() < 0.05:
+                sched.cancel(r)
+            if fate == "step_error" and r.slot >= 0 and r.prefill_done and not r.finish and not r.error and r.slot not in eng.generate_error:
+                eng.generate_error[r.slot] = "injected failure"
+        for s_ in list(eng.generate_error):                       # the failure is a one-off: clear it once its request has ended
+            if not any(r.slot == s_ and not (r.finish or r.error) for r, _ in reqs):
+                eng.generate_error.pop(s_, None)
+        time.sleep(0.005)
+    for r, fate in reqs:
+        if fate == "cancel":
+            sched.cancel(r)
+    t0 = time.time()
+    while len(ends) < len(reqs) and time.time() - t0 < 10:
+        time.sleep(0.01)
+    assert len(ends) == len(reqs) and all(len(v) == 1 for v in ends.values()), {k: v for k, v in ends.items() if len(v) != 1}
+    assert sched.thread.is_alive() and sched.health() is None
+    t0 = time.time()
+    while any(eng.busy) and time.time() - t0 < 2:
+        time.sleep(0.01)
+    assert eng.busy == [False, False, False]
+    for i, (r, fate) in enumerate(reqs):
+        reason = ends[i][0]
+        if fate == "ok":
+            assert reason in ("stop", "length"), (i, reason)
+        elif fate == "poison":
+            assert reason.startswith("error: poisoned prompt")
+        elif fate == "cancel":
+            assert reason in ("abort", "stop", "length")          # it may have finished before the cancel arrived
+    c = sched.counts()
+    assert c["completed"] + c["failed"] >= 40 and c["running"] == 0 and c["waiting"] == 0 and c["prefilling"] == 0
+    sched.shutdown()
