@@ -433,3 +433,66 @@ def test_block_store_concurrent_reads_from_disk(tmp_path):
         time.sleep(0.01)
     assert not errors and st.loads_pending() == 0
     st.close()
+
+
+@pytest.mark.parametrize("disk", [False, True])
+def test_block_store_random_operations_keep_the_contract(tmp_path, disk):
+    """Random saves of branching conversations, snapshots, look-ups, reads, thinning and budget pressure: whatever the
+    store still returns is byte for byte what was saved under that key, look-ups return a chain of the prompt's own
+    blocks with the depth of a real snapshot, and the budgets hold."""
+    import random
+    rnd = random.Random(5 + disk)
+    ram = 48 << 10
+    st = H.BlockStore(3, 1, ram_budget=ram, disk_dir=str(tmp_path) if disk else None, disk_budget=(256 << 10) if disk else 0)
+    saved, snaps = {}, {}                    # key -> payload; key -> snapshot payload
+    convs = []                               # token lists (multiples of 256)
+    for step in range(400):
+        op = rnd.random()
+        if op < 0.45 or not convs:
+            base = list(rnd.choice(convs)) if convs and rnd.random() < 0.6 else []
+            base = base[:256 * rnd.randrange(0, len(base) // 256 + 1)]
+            toks = base + [rnd.randrange(50) for _ in range(256 * rnd.randrange(1, 4))]
+            path, _ = st.lookup(toks + [1])
+            parent = path[-1] if path else st.root
+            for bi in range(len(path), len(toks) // 256):
+                h = hash((parent, tuple(toks[bi * 256:(bi + 1) * 256]))) & 0xFFFFFF          # a block's payload is a function of what it holds
+                payload = bytes([h % 256]) * (500 + h % 2500)
+                k = st.save_block(parent, bi * 256, toks[bi * 256:(bi + 1) * 256], payload)
+                if k == 0:
+                    break
+                assert k == H.BlockStore.key(parent, toks[bi * 256:(bi + 1) * 256])
+                saved[k] = payload
+                parent = k
+                if rnd.random() < 0.5:
+                    sp = bytes([(h >> 8) % 256]) * 200
+                    if st.save_snapshot(k, sp, None, anchor=rnd.random() < 0.1):
+                        snaps[k] = sp
+            convs.append(toks)
+        elif op < 0.8:
+            toks = list(rnd.choice(convs))
+            cut = rnd.randrange(1, len(toks) + 1)
+            q = toks[:cut] + ([rnd.randrange(50, 60)] * rnd.randrange(0, 300))
+            path, depth = st.lookup(q)
+            assert len(path) <= len(q) // 256 and 0 <= depth <= len(path)
+            parent = st.root
+            for bi, k in enumerate(path):                          # a chain of the prompt's own blocks
+                assert k == H.BlockStore.key(parent, q[bi * 256:(bi + 1) * 256])
+                parent = k
+            for k in path:
+                got = st.get(k)
+                assert got is None or got == saved[k]
+            if depth:
+                got = st.get(path[depth - 1], snapshot=True)
+                assert got is None or got[0] == snaps[path[depth - 1]]
+        elif op < 0.9:
+            st.thin(rnd.choice([300, 600, 2000]))
+        else:
+            if disk:
+                st.flush()
+            s_ = st.stats()
+            assert s_["ram_bytes"] <= ram + 4096 or disk          # without a disk tier the RAM budget is enforced at once
+    if disk:
+        st.flush()
+        s_ = st.stats()
+        assert s_["disk_bytes"] <= (256 << 10) + 8192
+    st.close()
