@@ -496,3 +496,21 @@ def test_block_store_random_operations_keep_the_contract(tmp_path, disk):
         s_ = st.stats()
         assert s_["disk_bytes"] <= (256 << 10) + 8192
     st.close()
+
+
+def test_chunker_edit_locality_and_bounds():
+    """An edit in the middle of a prompt changes the chunks around it and leaves the rest alone; chunk lengths stay inside
+    the minimum / maximum except at a message boundary and at the end."""
+    rng = np.random.default_rng(21)
+    toks = rng.integers(0, 50000, size=20000).tolist()
+    a = H.chunk_prompt(toks, -1)
+    edited = list(toks)
+    edited[10000:10010] = rng.integers(0, 50000, size=10).tolist()
+    b = H.chunk_prompt(edited, -1)
+    ha, hb = [c[2] for c in a], [c[2] for c in b]
+    assert len(set(ha) ^ set(hb)) <= 6                        # only the chunks next to the edit differ
+    before = [c for c in a if c[0] + c[1] <= 9000]
+    after = [c for c in a if c[0] >= 13000]
+    assert before and after and all(c in b for c in before) and all(c in b for c in after)
+    assert all(128 <= c[1] <= 2048 for c in a[:-1]) and 0 < a[-1][1] <= 2048
+    assert H.chunk_prompt([], -1) == [] and sum(c[1] for c in H.chunk_prompt(toks[:100], -1)) == 100
