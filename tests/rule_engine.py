@@ -181,3 +181,30 @@ def make_session(monkeypatch, engine, **kw):
     ses = S.Session(engine, **kw)
     ses.io.e = engine
     return ses
+
+
+class RuleOps:
+    """A rank's ``SessionOps`` over a real Session on a RuleEngine, plus ``dump`` (what the rank holds, for comparing
+    ranks).  ``build_rank`` is the ``--builder`` of worker processes."""
+
+    def __new__(cls, o):
+        from qwb200 import capi_impl
+        from qwb200.session import session as S
+        S.GpuSampler, S.StateIO = ArgmaxSampler, RuleIO
+        wrong = (lambda p: p % 3 == 0) if o.get("unreliable_drafts") else (lambda p: False)
+        eng = RuleEngine(vocab=512, modulus=256, slots=int(o.get("slots", 3)), wrong=wrong)
+        ses = S.Session(eng, host_cache_bytes=8 << 20)
+        ses.io.e = eng
+
+        class Ops(capi_impl.SessionOps):
+            def dump(self, path):
+                import json
+                with open(f"{path}.rank{o.get('rank', 0)}", "w") as f:
+                    json.dump({"tokens": [sl.tokens for sl in eng.slot], "state": eng.state, "fed": eng.fed,
+                               "stats": {k: int(v) for k, v in ses.cache_stats().items()}}, f)
+                return 0
+        return Ops(ses, None)
+
+
+def build_rank(open_message, world):
+    return RuleOps(dict(open_message.get("options", {}), rank=open_message.get("rank", 0)))

@@ -1,0 +1,51 @@
+"""Two ranks on CPU, each a real Session over the rule-based engine, behind one ``CApi``: rank 0 in this process, rank 1
+a worker process that replays every call.  Nothing is exchanged but the calls, so the ranks stay in step only if
+everything above the kernels is deterministic - slot choice, reuse decisions, draft counts, acceptance."""
+import json
+import os
+import sys
+
+from rule_engine import RuleOps
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TESTS = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_two_ranks_replay_a_serving_session_identically(tmp_path):
+    from qwb200.capi_impl import CApi
+    from qwb200.engine.sampling import SamplingParams
+    from qwb200.parallel.rank_group import RankGroup
+    from qwb200.session.session import StepReq
+    opts = {"slots": 3, "unreliable_drafts": True}
+    env = dict(os.environ, PYTHONPATH=TESTS + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    group = RankGroup.spawn(2, ["--builder", "rule_engine:build_rank"], {"options": opts, "master_port": 0},
+                            lambda: RuleOps(dict(opts, rank=0)), ready_timeout=120, ack_timeout=60, env=env)
+    api = CApi(group.local, group)
+    try:
+        ops = api.ops                                      # the group: every call runs on both ranks
+        system = [(i * 37) % 250 for i in range(700)]
+        pending = {}
+        for turn, tail in enumerate(([1, 2, 3], [9, 8, 7, 6], [1, 2, 3])):
+            prompt = system + tail
+            slot = ops.acquire(prompt, 64)
+            assert slot >= 0
+            ops.begin_prompt(slot, prompt)
+            while not ops.prefill_some(slot, 256):
+                pass
+            tok, _ = ops.sample_prompt(slot, SamplingParams())
+            pending[slot] = tok
+            for _ in range(6):                             # speculative steps for every request in flight
+                outs = ops.generate([StepReq(s, t, 32, 0, SamplingParams()) for s, t in sorted(pending.items())], 3)
+                for (s, _), o in zip(sorted(pending.items()), outs):
+                    pending[s] = o.tokens[-1]
+            if turn == 1:                                  # one request ends: its slot is free for the repeat of the first prompt
+                ops.release(slot)
+                del pending[slot]
+        assert api.failure() == ""
+        ops.dump(str(tmp_path / "state"))
+        a = json.load(open(tmp_path / "state.rank0"))
+        b = json.load(open(tmp_path / "state.rank1"))
+        assert a == b and a["fed"] > 700 and any(len(t) > 700 for t in a["tokens"])
+        assert a["stats"]["reused_tokens"] >= 512          # the shared system prompt came from the store or a snapshot on both ranks
+    finally:
+        api.close()

@@ -1,10 +1,12 @@
 """A worker rank of a multi-GPU engine (``parallel/rank_group.py``): connects to rank 0, builds its shard of the engine
 from the options it is sent, and replays rank 0's calls.
 
-    python -m qwb200.parallel.worker --address 127.0.0.1:PORT --authkey HEX --rank R --world N [--fake]
+    python -m qwb200.parallel.worker --address 127.0.0.1:PORT --authkey HEX --rank R --world N [--fake | --builder MOD:FUNC]
 
 ``--fake`` builds a recorder instead of an engine (no GPU): the host-side protocol's tests use it, also to inject
-failures - a call that raises, a call that never returns, a process that exits.
+failures - a call that raises, a call that never returns, a process that exits.  ``--builder MOD:FUNC`` builds the rank's
+object with ``FUNC(open_message, world)`` from module ``MOD`` instead of the engine (tests that run real sessions over
+a stand-in engine on every rank).
 """
 import argparse
 import os
@@ -45,11 +47,17 @@ def main() -> int:
     ap.add_argument("--rank", type=int, required=True)
     ap.add_argument("--world", type=int, required=True)
     ap.add_argument("--fake", action="store_true")
+    ap.add_argument("--builder", default=None)
     a = ap.parse_args()
     from .rank_group import connect, serve
     conn = connect(a.address, a.authkey, a.rank)
     if a.fake:
         return serve(conn, lambda o: FakeOps(o))
+    if a.builder:
+        import importlib
+        mod, _, fn = a.builder.partition(":")
+        make = getattr(importlib.import_module(mod), fn)
+        return serve(conn, lambda o: make(o, a.world))
 
     def build(o: dict):
         from ..capi_impl import build_ops
