@@ -208,3 +208,21 @@ class RuleOps:
 
 def build_rank(open_message, world):
     return RuleOps(dict(open_message.get("options", {}), rank=open_message.get("rank", 0)))
+
+
+class StubTower:
+    """Stands where the vision encoder stands: the front end needs its geometry until a slice is looked up."""
+
+    def __init__(self, hidden=64):
+        from qwb200.vision import VisionConfig
+        self.cfg = VisionConfig(depth=1, out_dim=hidden)
+
+    def encode(self, *a):
+        raise AssertionError("the tower runs only when a slice is looked up")
+
+
+def build_rank_with_vision(open_message, world):
+    from qwb200.vision.frontend import VisionFrontend
+    ops = build_rank(open_message, world)
+    ops.vision = VisionFrontend(StubTower(), 1 << 20)
+    return ops

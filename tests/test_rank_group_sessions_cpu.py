@@ -49,3 +49,41 @@ def test_two_ranks_replay_a_serving_session_identically(tmp_path):
         assert a["stats"]["reused_tokens"] >= 512          # the shared system prompt came from the store or a snapshot on both ranks
     finally:
         api.close()
+
+
+def test_media_prompts_reach_every_rank(tmp_path):
+    """A prompt with an image on two ranks: the media descriptors are read on rank 0, travel to the worker by value, both
+    ranks map the pad tokens to the same vision ids and feed the same tokens."""
+    import ctypes as C
+    import numpy as np
+    from qwb200.capi_impl import CApi, QwMedia
+    from qwb200.models.config import ModelConfig
+    from qwb200.parallel.rank_group import RankGroup
+    from rule_engine import StubTower, build_rank_with_vision
+    opts = {"slots": 2}
+    env = dict(os.environ, PYTHONPATH=TESTS + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    group = RankGroup.spawn(2, ["--builder", "rule_engine:build_rank_with_vision"], {"options": opts, "master_port": 0},
+                            lambda: build_rank_with_vision({"options": opts, "rank": 0}, 2), ready_timeout=120, ack_timeout=60, env=env)
+    api = CApi(group.local, group)
+    try:
+        vc, cfg = StubTower().cfg, ModelConfig.tiny()
+        h, w = 4, 6
+        n_img = h * w // (vc.merge * vc.merge)
+        patches = np.random.default_rng(3).standard_normal((2 * h * w, vc.patch_in)).astype(np.float32)
+        starts = np.asarray([4], dtype=np.int64)
+        toks = np.asarray([5, 6, 7, 8] + [cfg.image_pad] * n_img + [9, 10, 11], dtype=np.int32)
+        m = (QwMedia * 1)(QwMedia(hash=77, video=0, t=1, h=h, w=w, patches=patches.ctypes.data_as(C.POINTER(C.c_float)),
+                                  starts=starts.ctypes.data_as(C.POINTER(C.c_int64))))
+        slot = api.acquire(toks.ctypes.data, len(toks), 16, C.addressof(m), 1)
+        assert slot >= 0
+        api.begin_prompt(slot, toks.ctypes.data, len(toks), C.addressof(m), 1)
+        while not api.prefill_some(slot, 256):
+            pass
+        assert api.failure() == ""
+        api.ops.dump(str(tmp_path / "media"))
+        a = json.load(open(tmp_path / "media.rank0"))
+        b = json.load(open(tmp_path / "media.rank1"))
+        fed = a["tokens"][slot]
+        assert a == b and len(fed) == len(toks) and all(t < 0 for t in fed[4:4 + n_img]) and fed[:4] == [5, 6, 7, 8]
+    finally:
+        api.close()
