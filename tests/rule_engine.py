@@ -109,8 +109,11 @@ class RuleEngine:
         return len(flat)
 
     def accept_batch(self, slots, runs, n_acc):
-        for s, run, na in zip(slots, runs, n_acc):
+        self.accepts = getattr(self, "accepts", 0) + 1
+        for i, (s, run, na) in enumerate(zip(slots, runs, n_acc)):
             self._feed(s, run[:na])
+            if self.accepts == getattr(self, "fail_accept_at", -1) and i == 0:
+                raise RuntimeError("injected: the accept launch failed after the first request's rows were kept")
 
     def mtp_catch_up(self, slot, rows):
         self.caught_up.append((slot, [(t, p) for _, t, p in rows]))

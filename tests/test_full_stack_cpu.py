@@ -179,3 +179,42 @@ def test_soak_many_requests_shared_prefixes_unreliable_drafts(monkeypatch):
         if i not in (5, 17):
             assert g == w, i
     assert stats["reused_tokens"] >= 1024 and stats["hits"] >= 1 and rule.draft_calls > 0
+
+
+def test_a_step_that_fails_half_way_fails_its_batch_and_nothing_else(monkeypatch):
+    """The engine raises in the middle of a step, after one request's rows were kept: the requests of that step end with
+    an error (none is retried: its pending token may have been decoded already), their slots come back, and the same
+    prompts served again afterwards give the answers of an undisturbed server."""
+    srv, sched, eng, rule, holder = serve(monkeypatch, drafts=2)
+    rule.fail_accept_at = 6
+    prompts = [[{"role": "user", "content": f"case {i} " + "y" * (40 * i)}] for i in range(3)]
+
+    async def fn(c):
+        first = await asyncio.gather(*[chat(c, messages=m, max_tokens=30) for m in prompts])
+        first = [(r.status, await r.json()) for r in first]
+        again = [await (await chat(c, messages=m, max_tokens=30)).json() for m in prompts]
+        health = await (await c.get("/health")).json()
+        return first, again, health
+    first, again, health = with_client(srv, fn)
+    busy = [s_.busy for s_ in holder["ses"].slots]
+    ok = all(rule.consistent(s, rule.slot[s].tokens) for s in range(3))
+    sched.shutdown()
+    eng.close()
+    failed = [st for st, body in first if st != 200 or "error" in body]
+    assert failed and all(st == 500 for st, _ in first if st != 200)
+    assert "step failed after slot state changed" in json_of(first)
+    assert busy == [False, False, False] and ok and health["status"] == "ok"
+    # an undisturbed server gives the reference answers
+    srv2, sched2, eng2, rule2, _ = serve(monkeypatch, drafts=0)
+
+    async def fn2(c):
+        return [await (await chat(c, messages=m, max_tokens=30)).json() for m in prompts]
+    want = with_client(srv2, fn2)
+    sched2.shutdown()
+    eng2.close()
+    assert [a["choices"][0]["message"]["content"] for a in again] == [w["choices"][0]["message"]["content"] for w in want]
+
+
+def json_of(first):
+    import json
+    return json.dumps([b for _, b in first])
