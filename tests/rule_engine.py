@@ -48,7 +48,11 @@ class RuleEngine:
     def _logits(self, toks, positions):
         rows = torch.full((len(toks), self.V), -10.0)
         for i, (t, p) in enumerate(zip(toks, positions)):
-            rows[i, self.nxt(t, p)] = 10.0
+            top = self.nxt(t, p)
+            rows[i, top] = 10.0
+            if getattr(self, "spread", False):          # a distribution worth sampling from: four close candidates
+                for j, v in enumerate((9.6, 9.3, 8.9)):
+                    rows[i, (top + 17 * (j + 1)) % self.modulus] = v
         return rows
 
     # ---- what the session calls
@@ -229,3 +233,28 @@ def build_rank_with_vision(open_message, world):
     ops = build_rank(open_message, world)
     ops.vision = VisionFrontend(StubTower(), 1 << 20)
     return ops
+
+
+class HostRowSampler:
+    """``GpuSampler``'s interface over the native host sampler: every row is drawn on the host from its history, which
+    is what the engine does for rows the GPU sampler hands back."""
+
+    def __init__(self, *a, **kw):
+        from qwb200.native import host as H
+        self.host = H.HostSampler(kw.get("seed", 0) if kw else 0)
+        self.host_only = True
+
+    def reset_slot(self, slot):
+        pass
+
+    def note_tokens(self, slot, tokens, generated):
+        pass
+
+    def sample(self, logits, params, slots, positions, hists=None, force_host=None):
+        toks, lps = [], []
+        for i, p in enumerate(params):
+            hist, pend = hists[i]
+            t, lp = self.host.sample(logits[i].float().numpy(), p.to_host(), list(hist), pend)
+            toks.append(int(t))
+            lps.append(float(lp))
+        return toks, lps
