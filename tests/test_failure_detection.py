@@ -78,7 +78,7 @@ def _hb_worker(rank, world, port, q):
     from torch.distributed import TCPStore
     from qwb200.parallel.heartbeat import Heartbeat
     store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=20))
-    hb = Heartbeat(store, rank, world, interval=0.05, limit=0.6)
+    hb = Heartbeat(store, rank, world, interval=0.05, limit=3.0)      # generous: a starved process on a busy box is not a failure
     hb.start()
     store.set(f"ready/{rank}", "1")
     for r in range(world):
@@ -95,20 +95,23 @@ def _hb_worker(rank, world, port, q):
                 return
             if rank == 1 and step == 3:
                 hb.stop_flag.set()                # rank 1 stops beating without saying anything
-                time.sleep(3.0)
+                time.sleep(5.0)
                 q.put((rank, steps, "silent"))
                 return
             time.sleep(0.05)
         q.put((rank, steps, "never noticed"))
     except RuntimeError as ex:
         q.put((rank, steps, str(ex)))
-        time.sleep(3.5 if rank == 0 else 0.0)     # the store's server outlives its clients
+        time.sleep(6.0 if rank == 0 else 0.0)     # the store's server outlives its clients
 
 
 def test_heartbeat_across_processes():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29650
+    import socket
+    with socket.socket() as sk:                    # a port nobody holds right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     ps = [ctx.Process(target=_hb_worker, args=(r, 3, port, q)) for r in range(3)]
     for p in ps:
         p.start()

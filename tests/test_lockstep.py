@@ -37,7 +37,10 @@ def worker(rank, world, port, fail_rank, q):
 def test_failure_on_one_rank_raises_on_both_at_the_sync_point(fail_rank):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29650 + (fail_rank & 7)
+    import socket
+    with socket.socket() as sk:                    # a port nobody holds right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     ps = [ctx.Process(target=worker, args=(r, 2, port, fail_rank, q)) for r in range(2)]
     [p.start() for p in ps]
     got = sorted(q.get(timeout=120) for _ in ps)
