@@ -92,17 +92,26 @@ def _hb_worker(rank, world, port, q):
                 hb.leave("shutting down")         # between steps, nothing in flight
                 q.put((rank, steps, "left"))
                 time.sleep(1.0)                   # keep the store's clients alive while the others notice
+                store.set(f"done/{rank}", "1")
                 return
             if rank == 1 and step == 3:
                 hb.stop_flag.set()                # rank 1 stops beating without saying anything
                 time.sleep(5.0)
                 q.put((rank, steps, "silent"))
+                store.set(f"done/{rank}", "1")
                 return
             time.sleep(0.05)
         q.put((rank, steps, "never noticed"))
     except RuntimeError as ex:
         q.put((rank, steps, str(ex)))
-        time.sleep(6.0 if rank == 0 else 0.0)     # the store's server outlives its clients
+        if rank == 0:                             # the store's server outlives its clients: wait until they say they are done
+            try:
+                store.wait([f"done/{r}" for r in range(1, world)], __import__("datetime").timedelta(seconds=30))
+            except Exception:
+                pass
+            time.sleep(0.3)
+        else:
+            store.set(f"done/{rank}", "1")
 
 
 def test_heartbeat_across_processes():
