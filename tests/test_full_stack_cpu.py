@@ -218,3 +218,23 @@ def test_a_step_that_fails_half_way_fails_its_batch_and_nothing_else(monkeypatch
 def json_of(first):
     import json
     return json.dumps([b for _, b in first])
+
+
+def test_logprobs_through_the_stack(monkeypatch):
+    """``logprobs`` with ``top_logprobs``: every emitted token comes with its log-probability and the most likely tokens of
+    its row - the row index the session reports for a speculative step must be the row the token was drawn from, so the
+    first alternative is the token itself (the draw is greedy here) with the same log-probability."""
+    srv, sched, eng, rule, holder = serve(monkeypatch, drafts=3, wrong=lambda p: p % 5 == 0)
+    rule.spread = True
+
+    async def fn(c):
+        return await (await chat(c, max_tokens=24, logprobs=True, top_logprobs=3)).json()
+    out = with_client(srv, fn)
+    sched.shutdown()
+    eng.close()
+    entries = out["choices"][0]["logprobs"]["content"]
+    assert len(entries) == 24
+    for e in entries:
+        top = e["top_logprobs"]
+        assert len(top) == 3 and top[0]["token"] == e["token"] and abs(top[0]["logprob"] - e["logprob"]) < 1e-4
+        assert top[0]["logprob"] >= top[1]["logprob"] >= top[2]["logprob"] and e["logprob"] < 0
