@@ -238,3 +238,28 @@ def test_logprobs_through_the_stack(monkeypatch):
         top = e["top_logprobs"]
         assert len(top) == 3 and top[0]["token"] == e["token"] and abs(top[0]["logprob"] - e["logprob"]) < 1e-4
         assert top[0]["logprob"] >= top[1]["logprob"] >= top[2]["logprob"] and e["logprob"] < 0
+
+
+def test_forced_end_of_reasoning_through_the_stack(monkeypatch):
+    """A model that never stops reasoning, a budget of eight tokens: the closing tokens are fed as given (each by a plain
+    one-token step whose own draw is dropped), the answer follows, and the slot holds exactly what was emitted."""
+    srv, sched, eng, rule, holder = serve(monkeypatch, drafts=3)
+    pr = make_prompter()
+
+    async def fn(c):
+        body = {"messages": MSG, "max_tokens": 40, "temperature": 0, "thinking_budget": 8}
+        return await (await c.post("/v1/chat/completions", json=body)).json()
+    out = with_client(srv, fn)
+    held = [list(rule.slot[s].tokens) for s in range(3) if rule.slot[s].tokens]
+    ok = all(rule.consistent(s, rule.slot[s].tokens) for s in range(3))
+    sched.shutdown()
+    eng.close()
+    m = out["choices"][0]["message"]
+    close = pr.encode("\n</think>\n\n")
+    assert out["usage"]["completion_tokens"] == 40 and out["usage"]["completion_tokens_details"]["reasoning_tokens"] >= 8
+    assert m["reasoning_content"] and m["content"] and ok and len(held) == 1
+    toks = held[0]
+    at = next(i for i in range(len(toks)) if toks[i:i + len(close)] == close)          # the forced tokens are in the slot, in order
+    think_open = pr.token_id("<think>")
+    opened = max(i for i, t in enumerate(toks[:at]) if t == think_open)
+    assert 8 <= at - opened - 1 <= 8 + 3 + 1                                             # the budget, plus at most one speculative step's overshoot
