@@ -194,10 +194,12 @@ class RuleOps:
     """A rank's ``SessionOps`` over a real Session on a RuleEngine, plus ``dump`` (what the rank holds, for comparing
     ranks).  ``build_rank`` is the ``--builder`` of worker processes."""
 
-    def __new__(cls, o):
+    def __new__(cls, o, patch_module=False):
         from qwb200 import capi_impl
         from qwb200.session import session as S
-        S.GpuSampler, S.StateIO = ArgmaxSampler, RuleIO
+        if patch_module:          # a worker process of its own; in the test process the caller patches (and restores) the module
+            S.GpuSampler, S.StateIO = ArgmaxSampler, RuleIO
+        assert S.GpuSampler is ArgmaxSampler and S.StateIO is RuleIO, "patch qwb200.session.session first"
         wrong = (lambda p: p % 3 == 0) if o.get("unreliable_drafts") else (lambda p: False)
         eng = RuleEngine(vocab=512, modulus=256, slots=int(o.get("slots", 3)), wrong=wrong)
         ses = S.Session(eng, host_cache_bytes=8 << 20)
@@ -213,8 +215,14 @@ class RuleOps:
         return Ops(ses, None)
 
 
-def build_rank(open_message, world):
-    return RuleOps(dict(open_message.get("options", {}), rank=open_message.get("rank", 0)))
+def build_rank(open_message, world, patch_module=True):
+    return RuleOps(dict(open_message.get("options", {}), rank=open_message.get("rank", 0)), patch_module=patch_module)
+
+
+def patch_session_module(monkeypatch):
+    from qwb200.session import session as S
+    monkeypatch.setattr(S, "GpuSampler", ArgmaxSampler)
+    monkeypatch.setattr(S, "StateIO", RuleIO)
 
 
 class StubTower:
@@ -228,9 +236,9 @@ class StubTower:
         raise AssertionError("the tower runs only when a slice is looked up")
 
 
-def build_rank_with_vision(open_message, world):
+def build_rank_with_vision(open_message, world, patch_module=True):
     from qwb200.vision.frontend import VisionFrontend
-    ops = build_rank(open_message, world)
+    ops = build_rank(open_message, world, patch_module)
     ops.vision = VisionFrontend(StubTower(), 1 << 20)
     return ops
 

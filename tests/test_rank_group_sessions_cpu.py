@@ -5,13 +5,14 @@ import json
 import os
 import sys
 
-from rule_engine import RuleOps
+from rule_engine import RuleOps, patch_session_module
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TESTS = os.path.dirname(os.path.abspath(__file__))
 
 
-def test_two_ranks_replay_a_serving_session_identically(tmp_path):
+def test_two_ranks_replay_a_serving_session_identically(tmp_path, monkeypatch):
+    patch_session_module(monkeypatch)
     from qwb200.capi_impl import CApi
     from qwb200.engine.sampling import SamplingParams
     from qwb200.parallel.rank_group import RankGroup
@@ -51,7 +52,8 @@ def test_two_ranks_replay_a_serving_session_identically(tmp_path):
         api.close()
 
 
-def test_media_prompts_reach_every_rank(tmp_path):
+def test_media_prompts_reach_every_rank(tmp_path, monkeypatch):
+    patch_session_module(monkeypatch)
     """A prompt with an image on two ranks: the media descriptors are read on rank 0, travel to the worker by value, both
     ranks map the pad tokens to the same vision ids and feed the same tokens."""
     import ctypes as C
@@ -63,7 +65,7 @@ def test_media_prompts_reach_every_rank(tmp_path):
     opts = {"slots": 2}
     env = dict(os.environ, PYTHONPATH=TESTS + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     group = RankGroup.spawn(2, ["--builder", "rule_engine:build_rank_with_vision"], {"options": opts, "master_port": 0},
-                            lambda: build_rank_with_vision({"options": opts, "rank": 0}, 2), ready_timeout=120, ack_timeout=60, env=env)
+                            lambda: build_rank_with_vision({"options": opts, "rank": 0}, 2, patch_module=False), ready_timeout=120, ack_timeout=60, env=env)
     api = CApi(group.local, group)
     try:
         vc, cfg = StubTower().cfg, ModelConfig.tiny()
