@@ -12,7 +12,13 @@ target=$1
 dir=${2:-qw-b200}
 root=$(cd "$(dirname "${BASH_SOURCE[0]}")/../.." && pwd)
 
-tar -C "$root" --exclude=./.git --exclude=./gpurun_out --exclude=./_work --exclude=./baseline --exclude='*.so' \
-    --exclude=__pycache__ --exclude=.pytest_cache --exclude='build' --exclude='build_checked' -cf - . |
-    ssh -o BatchMode=yes "$target" "mkdir -p $(printf '%q' "$dir") && tar -C $(printf '%q' "$dir") -xf - && cd $(printf '%q' "$dir") && python3 -m qwb200.build"
+files() {
+    # the tracked files of a git checkout; of a plain copy everything but built libraries and caches
+    if git -C "$root" rev-parse --is-inside-work-tree >/dev/null 2>&1; then
+        git -C "$root" ls-files -z | tar -C "$root" --null -T - -cf -
+    else
+        tar -C "$root" --exclude='*.so' --exclude=__pycache__ --exclude=.pytest_cache --exclude=build --exclude=build_checked -cf - .
+    fi
+}
+files | ssh -o BatchMode=yes "$target" "mkdir -p $(printf '%q' "$dir") && tar -C $(printf '%q' "$dir") -xf - && cd $(printf '%q' "$dir") && python3 -m qwb200.build"
 echo "deployed to $target:$dir"
